@@ -1,0 +1,202 @@
+// C ABI of the B200 (sm_100a) decode-layer library, libmk_b200.so.
+//
+// Conventions are those of the reference's host ABI (sgl_muse_mega/muse_spark/sm103/host/abi.h:1-9): every bind struct
+// holds only uint64_t / int64_t / double fields, one declaration per line (device pointers as uint64_t, 0 = absent);
+// every int-returning function returns 0 on success and -1 on failure with the reason in mk_last_error(); the caller
+// owns all device memory, the library owns the MkModule / MkLaunch handles; a launch is bound ONCE and
+// mk_launch(handle, stream, pdl) is the only per-step call (no allocation, no synchronisation: graph-capturable).
+//
+// Differences from the reference, by design: the kernels are linked into the library (no cubin file is loaded, so
+// mk_module_load takes image == NULL), shapes are run-time fields of MkLayerShape instead of per-image compile-time
+// constants, and device-side waits never trap: they give up after a bound and record why in a status block that
+// mk_launch_status reads.
+#pragma once
+
+#include <stdint.h>
+
+// capacity of the peer arrays: the largest tensor-parallel world (abi.h:15)
+#define MKH_RANKS 8
+// stages of one layer launch, in launch order (mk_launch_step runs a sub-range)
+#define MKH_LAYER_STAGES 17
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct MkModule MkModule;
+typedef struct MkLaunch MkLaunch;
+
+// replaces abi.h:24 mk_last_error
+const char* mk_last_error(void);
+
+// replaces abi.h:30 mk_module_load. The kernels are built into this library: image must be NULL and bytes 0. Binds the
+// module to the calling thread's current CUDA device, which must be compute capability 10.x.
+int mk_module_load(const void* image, uint64_t bytes, const char* code_prefetch_prefix, MkModule** out);
+// replaces abi.h:36 mk_module_free
+void mk_module_free(MkModule* module);
+
+// replaces abi.h:40 mk_launch. Enqueues every kernel of the bound launch on `stream` (a cudaStream_t as an integer);
+// pdl != 0 adds the programmatic-dependent-launch attribute to each kernel after the first.
+int mk_launch(const MkLaunch* launch, uint64_t stream, int pdl);
+// Test hook with no counterpart in the reference: enqueues stages [first, first + count) only. Lets a test interleave
+// the stages of several ranks' launches on one GPU, so that their exchanges run without the ranks waiting on each other.
+int mk_launch_step(const MkLaunch* launch, uint64_t stream, int64_t first, int64_t count);
+// replaces abi.h:41 mk_launch_free
+void mk_launch_free(MkLaunch* launch);
+
+// replaces abi.h:43-51 MkLaunchInfo / mk_launch_info
+typedef struct MkLaunchInfo {
+    int64_t grid;         // largest grid among the launch's kernels
+    int64_t block;        // largest block
+    int64_t cluster;      // cluster width (1: none)
+    int64_t smem;         // largest dynamic shared memory request
+    int64_t kernels;      // kernels enqueued by one mk_launch
+    int64_t param_bytes;  // bytes of the packed parameter record
+} MkLaunchInfo;
+int mk_launch_info(const MkLaunch* launch, MkLaunchInfo* out);
+
+// No counterpart in the reference (its waits trap, K/README.md:111-121). Copies the launch's device status block to the
+// host (synchronises the stream first). code 0 = clean; otherwise the wait that gave up.
+typedef struct MkLaunchStatus {
+    int64_t code;      // 0 ok, 1 exchange flag wait expired, 2 grid counter wait expired
+    int64_t stage;     // stage index that recorded it
+    int64_t block;     // blockIdx.x
+    int64_t observed;  // value seen
+    int64_t expected;  // value waited for
+} MkLaunchStatus;
+int mk_launch_status(const MkLaunch* launch, uint64_t stream, MkLaunchStatus* out);
+
+// ---- one decoder layer ----
+
+// Run-time shape of one rank's layer launch (the reference bakes these per image: abi.h:60-101 MkLayerConstants).
+typedef struct MkLayerShape {
+    int64_t rows;         // window rows M (1..16)
+    int64_t hidden;       // model width H
+    int64_t moe_hidden;   // expert width P (pooler output)
+    int64_t q_heads;      // this rank's query heads
+    int64_t kv_heads;     // this rank's kv heads
+    int64_t experts;      // routed experts E
+    int64_t topk;         // experts per row
+    int64_t inter;        // full expert intermediate I
+    int64_t ranks;        // tensor-parallel world
+    int64_t node_ranks;   // ranks of a node group (pooler / unpooler gathers)
+    int64_t rank;         // this rank
+    int64_t window;       // sliding window (keys p with pos - p <= window); 0 = global attention
+    int64_t bf16;         // 1: bf16 experts, 0: NVFP4
+    int64_t tail;         // 1: last layer (ends at the final norm, no successor head)
+    int64_t next_rope;    // 1: the successor is a sliding-window layer (RoPE rows applied)
+} MkLayerShape;
+
+// Buffer extents the caller allocates for a shape (replaces abi.h:60-102 mk_layer_constants).
+typedef struct MkLayerConstants {
+    int64_t stages;          // kernels per launch
+    int64_t slots;           // route slots = rows x topk
+    int64_t qkv_row;         // [q | k | v | o-gate] row width
+    int64_t kv_row_bytes;    // one K (or V) pool row
+    int64_t inter_rank;      // I / ranks
+    int64_t hidden_rank;     // P / ranks (W2 rows per rank)
+    int64_t ar_bytes;        // all-reduce workspace: ranks x rows x H bf16
+    int64_t pool_ag_bytes;   // pooler gather row block: rows x P bf16
+    int64_t unpool_ag_bytes; // unpooler gather: rows x H bf16
+    int64_t z_bytes;         // gathered h codes: slots x I/2 (bf16 variant: slots x I x 2)
+    int64_t z_sf_bytes;      // gathered h scales: slots x I/16
+    int64_t z_ex_bytes;      // gathered h exponents: slots x I/16 (int8)
+    int64_t zb_bytes;        // gathered expert outputs: slots x P bf16
+    int64_t ws_bytes;        // private scratch (attention partials, split-K partials, counters, route tables)
+    int64_t attn_splits;     // split-KV partitions per kv head
+    int64_t flag_words;      // u32 exchange flags per rank
+    int64_t status_bytes;    // device status block
+} MkLayerConstants;
+int mk_layer_constants(const MkLayerShape* shape, MkLayerConstants* out);
+
+// One layer launch's operands (replaces abi.h:106-211 MkLayerBind; same names where the meaning is the same).
+typedef struct MkLayerBind {
+    // attention
+    uint64_t qkv_in;      // this layer's head row [rows, qkv_row] bf16 (written by the predecessor)
+    uint64_t k_cache;     // this layer's pool, [kv_rows, kv heads x 64] bf16
+    uint64_t v_cache;
+    int64_t kv_rows;
+    uint64_t page_table;  // i64 [page_stride] byte offsets by position
+    uint64_t kv_len;      // i32 [1]: context length + rows
+    int64_t page_stride;
+    uint64_t x_attn;      // out [rows, q_heads x 64] bf16
+    // o_proj + all-reduce + post-attention norm
+    uint64_t w_o;         // [H, q_heads x 64] bf16
+    uint64_t ar;          // this rank's all-reduce workspace (ar_bytes)
+    uint64_t ar_peer[MKH_RANKS];  // every rank's workspace (own included); 0 = rank absent (slot pre-filled)
+    uint64_t branch;      // out [rows, H] bf16 (the all-reduce sum)
+    uint64_t stream_in;   // [rows, H] f32
+    uint64_t alpha;
+    uint64_t beta;
+    uint64_t prenorm_w;
+    uint64_t stream_out;  // out [rows, H] f32 (the post-attention residual)
+    uint64_t h3;          // out [rows, H] bf16
+    uint64_t h3f;         // out [rows, H] f32
+    // pooler || router -> top-k -> pre-expert norm + quant -> route tables
+    uint64_t w_p;         // [P, H] bf16 (replicated; this rank computes its node block)
+    uint64_t pool_ag;     // this rank's pooler gather buffer
+    uint64_t pool_ag_peer[MKH_RANKS];
+    uint64_t w_r;         // [E, H] f32
+    uint64_t logits;      // out [rows, E] f32
+    double router_mult;
+    uint64_t expert_bias;
+    uint64_t topk_idx32;  // out [rows, topk] i32
+    uint64_t topk_w;      // out [rows, topk] f32
+    double route_scale;
+    uint64_t gamma;       // pre-expert norm weight [P] bf16
+    double eps;
+    uint64_t q;           // out: NVFP4 rows [rows, P/2] u8 (bf16 variant: [rows, P] bf16)
+    uint64_t sf;          // out [rows, P/16] u8
+    uint64_t x_scale;     // out [rows] f32
+    // experts
+    uint64_t w1_gate;     // NVFP4: [E, I_s, P/2] u8; bf16: [E, I_s, P] bf16
+    uint64_t w1_gate_sf;  // [E, I_s, P/16] u8
+    uint64_t w1_up;
+    uint64_t w1_up_sf;
+    uint64_t w2;          // NVFP4: [E, H_s, I/2] u8; bf16: [E, H_s, I] bf16
+    uint64_t w2_sf;       // [E, H_s, I/16] u8
+    uint64_t g1_alphas;
+    uint64_t g1_scale_c;
+    uint64_t g2_alphas;
+    uint64_t z;           // gathered h planes of this rank
+    uint64_t z_sf;
+    uint64_t z_ex;
+    uint64_t zb;
+    uint64_t z_peer[MKH_RANKS];
+    uint64_t zsf_peer[MKH_RANKS];
+    uint64_t zex_peer[MKH_RANKS];
+    uint64_t zb_peer[MKH_RANKS];
+    uint64_t gamma_p1;
+    uint64_t y;           // out [rows, P] bf16
+    // next-layer phase
+    uint64_t w_up;        // unpooler [H, P] bf16
+    uint64_t unpool_ag;
+    uint64_t unpool_ag_peer[MKH_RANKS];
+    uint64_t c_alpha;
+    uint64_t c_beta;
+    uint64_t c_pre_w;
+    uint64_t c_post_w;
+    uint64_t c_stream_out;  // out [rows, H] f32
+    uint64_t h3q;           // out [rows, H] bf16: the successor's normed input (tail: the final norm's rows)
+    uint64_t w_qkv;         // successor's [qkv_row, H] bf16
+    uint64_t qkv_out;       // out [rows, qkv_row] bf16
+    uint64_t cos_sin;       // [rows, 64] f32
+    uint64_t cache_loc;     // i32 [rows]: pool slots of the window's rows
+    uint64_t next_k_cache;
+    uint64_t next_v_cache;
+    int64_t next_kv_rows;
+    double q_scale;
+    double qkv_eps;
+    // exchange flags and private scratch
+    uint64_t flags;         // this rank's u32 [flag_words]
+    uint64_t flags_peer[MKH_RANKS];
+    uint64_t ws;            // ws_bytes of private scratch, zeroed once by the caller
+    uint64_t status;        // status_bytes, zeroed once by the caller
+    int64_t b_live;         // live window rows (abi.h:208-210)
+    int64_t wait_budget;    // polls before an exchange wait gives up (0: library default)
+} MkLayerBind;
+int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind* bind, MkLaunch** out);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,455 @@
+// Host side of the C ABI (include/mk_abi.h): module handle, bind-once launch records, the layer's launch list.
+// Counterpart of the reference's host launcher (sm103/host/runtime.cu:429-520 core, :679-989 layer bind): bind checks
+// every operand once and freezes one argument record per kernel; mk_launch only enqueues.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "../../include/mk_abi.h"
+#include "stages.h"
+
+namespace mk {
+
+// ---- errors ----
+static thread_local char g_error[512] = "";
+
+static int fail(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+    return -1;
+}
+
+#define MK_REQUIRE(cond, ...) \
+    do {                      \
+        if (!(cond)) return fail(__VA_ARGS__); \
+    } while (0)
+
+static int cuda_fail(cudaError_t e, const char* what) { return fail("%s: %s", what, cudaGetErrorString(e)); }
+
+}  // namespace mk
+
+struct MkModule {
+    int device;
+};
+
+enum Stage {
+    ST_ATTN_SPLIT = 0, ST_ATTN_COMBINE, ST_OPROJ, ST_POST_NORM, ST_POOLER, ST_ROUTER, ST_TOPK, ST_NQ, ST_TABLES, ST_G1,
+    ST_HROW, ST_G2, ST_COMBINE, ST_UNPOOL, ST_CROSS_NORM, ST_QKV, ST_ROWOPS, ST_COUNT
+};
+static_assert(ST_COUNT == MKH_LAYER_STAGES, "stage list and ABI constant disagree");
+
+struct MkLaunch {
+    bool pack_only;
+    int device;
+    MkLayerShape shape;
+    MkLayerConstants consts;
+    MkLayerBind bind;
+    mk::AttnArgs attn;
+    mk::GemmArgs oproj, pooler, router, unpool, qkv;
+    int ks_oproj, ks_pooler, ks_router, ks_unpool, ks_qkv;
+    mk::NormArgs post_norm, cross_norm;
+    mk::TopkArgs topk;
+    mk::NqArgs nq;
+    mk::CombineArgs combine;
+    mk::RowopsArgs rowops;
+    mk::ExpertArgs ex;
+    mk::RouteTables* rt;
+    unsigned char* z_sfd;
+    float* rowscale;
+    int* status;
+    int max_active, slots_live;
+    bool stage_on[ST_COUNT];
+};
+
+using namespace mk;
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static int attn_splits_for(const MkLayerShape& s) {
+    int sp = 144 / (int)s.kv_heads;
+    if (sp < 1) sp = 1;
+    if (sp > 72) sp = 72;
+    return sp;
+}
+
+static int check_shape(const MkLayerShape* s) {
+    MK_REQUIRE(s != nullptr, "shape is NULL");
+    MK_REQUIRE(s->rows >= 1 && s->rows <= kMaxRows, "rows %lld outside 1..16", (long long)s->rows);
+    MK_REQUIRE(s->topk >= 1 && s->rows * s->topk <= kMaxSlots, "rows x topk %lld exceeds %d", (long long)(s->rows * s->topk), kMaxSlots);
+    MK_REQUIRE(s->topk <= 32, "topk %lld exceeds 32", (long long)s->topk);
+    MK_REQUIRE(s->experts >= s->topk && s->experts <= 1024 && s->experts % 16 == 0, "experts %lld unsupported", (long long)s->experts);
+    MK_REQUIRE(s->ranks == 1 || s->ranks == 2 || s->ranks == 4 || s->ranks == 8, "ranks %lld not 1/2/4/8", (long long)s->ranks);
+    MK_REQUIRE(s->rank >= 0 && s->rank < s->ranks, "rank %lld outside the world", (long long)s->rank);
+    MK_REQUIRE(s->node_ranks >= 1 && s->ranks % s->node_ranks == 0, "node_ranks %lld does not divide ranks", (long long)s->node_ranks);
+    MK_REQUIRE(s->hidden >= 256 && s->hidden <= 8192 && s->hidden % 128 == 0, "hidden %lld unsupported", (long long)s->hidden);
+    MK_REQUIRE(s->moe_hidden % (32 * s->node_ranks) == 0 && s->moe_hidden % (16 * s->ranks) == 0 && s->moe_hidden <= 6144,
+               "moe_hidden %lld unsupported", (long long)s->moe_hidden);
+    MK_REQUIRE(s->inter % (16 * s->ranks) == 0 && s->inter % 32 == 0 && s->inter <= 6144, "inter %lld unsupported", (long long)s->inter);
+    MK_REQUIRE(s->hidden % (32 * s->node_ranks) == 0, "hidden %lld not divisible over the node group", (long long)s->hidden);
+    MK_REQUIRE(s->q_heads >= 1 && s->kv_heads >= 1 && s->q_heads % s->kv_heads == 0, "heads %lld / %lld", (long long)s->q_heads, (long long)s->kv_heads);
+    MK_REQUIRE(s->rows * (s->q_heads / s->kv_heads) <= 128, "rows x heads per kv head exceeds 128");
+    MK_REQUIRE(s->window >= 0, "negative window");
+    MK_REQUIRE(gemm_ksplit(false, (int)s->hidden) > 0 && gemm_ksplit(true, (int)s->hidden) > 0, "hidden %lld has no K split", (long long)s->hidden);
+    MK_REQUIRE(gemm_ksplit(false, (int)s->moe_hidden) > 0, "moe_hidden %lld has no K split", (long long)s->moe_hidden);
+    MK_REQUIRE(gemm_ksplit(false, (int)(s->q_heads * kHeadDim)) > 0, "o_proj K %lld has no K split", (long long)(s->q_heads * kHeadDim));
+    return 0;
+}
+
+static void fill_constants(const MkLayerShape& s, MkLayerConstants* c) {
+    memset(c, 0, sizeof *c);
+    const int64_t M = s.rows, slots = s.rows * s.topk;
+    c->stages = ST_COUNT;
+    c->slots = slots;
+    c->qkv_row = 2 * (s.q_heads + s.kv_heads) * kHeadDim;
+    c->kv_row_bytes = s.kv_heads * kHeadDim * 2;
+    c->inter_rank = s.inter / s.ranks;
+    c->hidden_rank = s.moe_hidden / s.ranks;
+    c->ar_bytes = s.ranks * M * s.hidden * 2;
+    c->pool_ag_bytes = M * s.moe_hidden * 2;
+    c->unpool_ag_bytes = M * s.hidden * 2;
+    c->z_bytes = s.bf16 ? slots * s.inter * 2 : slots * s.inter / 2;
+    c->z_sf_bytes = slots * s.inter / 16;
+    c->z_ex_bytes = slots * s.inter / 16;
+    c->zb_bytes = slots * s.moe_hidden * 2;
+    c->attn_splits = attn_splits_for(s);
+    c->flag_words = 64;
+    c->status_bytes = 64;
+    // scratch carve: attention partials | gemm partials | gemm counters | route tables | z_sfd | rowscale
+    const int64_t R = M * (s.q_heads / s.kv_heads);
+    size_t off = 0;
+    off += align_up((size_t)s.kv_heads * c->attn_splits * R * 66 * 4, 256);
+    int64_t nmax = c->qkv_row;
+    if (s.hidden > nmax) nmax = s.hidden;
+    off += align_up((size_t)16 * 16 * nmax * 4, 256);  // up to 16 K chunks of [16, N] f32
+    off += align_up((size_t)1024 * 4, 256);
+    off += align_up(sizeof(RouteTables), 256);
+    off += align_up((size_t)slots * s.inter / 16, 256);
+    off += align_up((size_t)slots * 4, 256);
+    c->ws_bytes = (int64_t)off;
+}
+
+extern "C" {
+
+const char* mk_last_error(void) { return g_error; }
+
+int mk_module_load(const void* image, uint64_t bytes, const char* code_prefetch_prefix, MkModule** out) {
+    (void)code_prefetch_prefix;
+    MK_REQUIRE(out != nullptr, "out is NULL");
+    MK_REQUIRE(image == nullptr && bytes == 0, "this library carries its kernels: pass image NULL, bytes 0");
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDeviceProperties");
+    MK_REQUIRE(prop.major == 10, "device %d is compute capability %d.%d; the kernels are built for sm_100a", dev, prop.major, prop.minor);
+    e = gemm_prepare();
+    if (e != cudaSuccess) return cuda_fail(e, "gemm_prepare");
+    e = experts_prepare();
+    if (e != cudaSuccess) return cuda_fail(e, "experts_prepare");
+    MkModule* m = new (std::nothrow) MkModule{dev};
+    MK_REQUIRE(m != nullptr, "out of host memory");
+    *out = m;
+    return 0;
+}
+
+void mk_module_free(MkModule* module) { delete module; }
+
+int mk_layer_constants(const MkLayerShape* shape, MkLayerConstants* out) {
+    MK_REQUIRE(out != nullptr, "out is NULL");
+    if (check_shape(shape)) return -1;
+    fill_constants(*shape, out);
+    return 0;
+}
+
+#define NEED(field) MK_REQUIRE(b->field != 0, "bind field " #field " is 0")
+#define ALIGNED16(field) MK_REQUIRE((b->field & 15) == 0, "bind field " #field " is not 16-byte aligned")
+
+int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind* b, MkLaunch** out) {
+    MK_REQUIRE(out != nullptr && b != nullptr, "bind or out is NULL");
+    if (check_shape(shape)) return -1;
+    const MkLayerShape& s = *shape;
+    MkLaunch* L = new (std::nothrow) MkLaunch();
+    MK_REQUIRE(L != nullptr, "out of host memory");
+    struct Guard {
+        MkLaunch* l;
+        ~Guard() { delete l; }
+    } guard{L};
+    L->pack_only = module == nullptr;
+    L->device = module ? module->device : -1;
+    L->shape = s;
+    L->bind = *b;
+    fill_constants(s, &L->consts);
+    const MkLayerConstants& c = L->consts;
+    const int M = (int)s.rows, H = (int)s.hidden, P = (int)s.moe_hidden, E = (int)s.experts, K = (int)s.topk, I = (int)s.inter;
+    const int qh = (int)s.q_heads, kvh = (int)s.kv_heads, G = qh / kvh, R = M * G;
+    const int I_s = (int)c.inter_rank, H_s = (int)c.hidden_rank, slots = (int)c.slots;
+    const int b_live = b->b_live > 0 ? (int)b->b_live : M;
+    MK_REQUIRE(b_live <= M, "b_live %d exceeds rows %d", b_live, M);
+    const bool fp4 = !s.bf16, tail = s.tail != 0;
+
+    NEED(qkv_in); NEED(k_cache); NEED(v_cache); NEED(page_table); NEED(kv_len); NEED(x_attn);
+    NEED(w_o); NEED(ar); NEED(branch); NEED(stream_in); NEED(alpha); NEED(beta); NEED(prenorm_w); NEED(stream_out); NEED(h3); NEED(h3f);
+    NEED(w_p); NEED(pool_ag); NEED(w_r); NEED(logits); NEED(expert_bias); NEED(topk_idx32); NEED(topk_w); NEED(gamma); NEED(q);
+    NEED(w1_gate); NEED(w1_up); NEED(w2); NEED(z); NEED(zb); NEED(gamma_p1); NEED(y);
+    NEED(w_up); NEED(unpool_ag); NEED(c_alpha); NEED(c_beta); NEED(c_pre_w); NEED(c_post_w); NEED(c_stream_out); NEED(h3q);
+    NEED(ws); NEED(status);
+    if (fp4) {
+        NEED(sf); NEED(x_scale); NEED(w1_gate_sf); NEED(w1_up_sf); NEED(w2_sf); NEED(g1_alphas); NEED(g1_scale_c); NEED(g2_alphas);
+        NEED(z_sf); NEED(z_ex);
+    }
+    if (!tail) {
+        NEED(w_qkv); NEED(qkv_out); NEED(cache_loc); NEED(next_k_cache); NEED(next_v_cache);
+        if (s.next_rope) NEED(cos_sin);
+    }
+    ALIGNED16(qkv_in); ALIGNED16(k_cache); ALIGNED16(v_cache); ALIGNED16(w_o); ALIGNED16(w_p); ALIGNED16(w_r); ALIGNED16(w_up);
+    ALIGNED16(w_qkv); ALIGNED16(w1_gate); ALIGNED16(w1_up); ALIGNED16(w2); ALIGNED16(h3); ALIGNED16(h3f); ALIGNED16(y);
+    ALIGNED16(x_attn); ALIGNED16(h3q); ALIGNED16(q); ALIGNED16(z); ALIGNED16(ws); ALIGNED16(pool_ag); ALIGNED16(ar);
+    ALIGNED16(unpool_ag); ALIGNED16(zb); ALIGNED16(w1_gate_sf); ALIGNED16(w1_up_sf); ALIGNED16(w2_sf); ALIGNED16(z_sf);
+    MK_REQUIRE(c.kv_row_bytes % 16 == 0, "kv row is not a multiple of 16 bytes");
+    MK_REQUIRE(b->page_stride >= M, "page_stride %lld smaller than the window", (long long)b->page_stride);
+    MK_REQUIRE(b->ar_peer[s.rank] == 0 || b->ar_peer[s.rank] == b->ar, "ar_peer[rank] must be this rank's workspace");
+
+    // peers: a present peer receives this rank's pushes; this rank's own buffer is always a destination
+    auto peers = [&](const uint64_t* arr, uint64_t own, void** dst, int first, int count) {
+        int n = 0;
+        for (int r = first; r < first + count; ++r) {
+            const uint64_t p = r == s.rank ? own : arr[r];
+            if (p) dst[n++] = (void*)p;
+        }
+        return n;
+    };
+    const int node0 = (int)(s.rank - s.rank % s.node_ranks), nr = (int)s.node_ranks, jnode = (int)(s.rank % s.node_ranks);
+
+    // scratch carve (must follow fill_constants)
+    unsigned char* ws = (unsigned char*)b->ws;
+    size_t off = 0;
+    float* attn_ws = (float*)(ws + off);
+    off += align_up((size_t)kvh * c.attn_splits * R * 66 * 4, 256);
+    float* gpart = (float*)(ws + off);
+    int64_t nmax = c.qkv_row > s.hidden ? c.qkv_row : s.hidden;
+    off += align_up((size_t)16 * 16 * nmax * 4, 256);
+    unsigned* gcnt = (unsigned*)(ws + off);
+    off += align_up((size_t)1024 * 4, 256);
+    L->rt = (RouteTables*)(ws + off);
+    off += align_up(sizeof(RouteTables), 256);
+    L->z_sfd = ws + off;
+    off += align_up((size_t)slots * I / 16, 256);
+    L->rowscale = (float*)(ws + off);
+    off += align_up((size_t)slots * 4, 256);
+    MK_REQUIRE((int64_t)off == c.ws_bytes, "internal: scratch carve %zu != %lld", off, (long long)c.ws_bytes);
+    L->status = (int*)b->status;
+    L->max_active = slots < E ? slots : E;
+    L->slots_live = b_live * K;
+    for (int i = 0; i < ST_COUNT; ++i) L->stage_on[i] = true;
+    L->stage_on[ST_HROW] = fp4;
+    L->stage_on[ST_QKV] = L->stage_on[ST_ROWOPS] = !tail;
+
+    // attention
+    L->attn = AttnArgs{(const bf16*)b->qkv_in, (const unsigned char*)b->k_cache, (const unsigned char*)b->v_cache,
+                       (const long long*)b->page_table, (const int*)b->kv_len, attn_ws, (bf16*)b->x_attn,
+                       M, qh, kvh, G, R, (int)c.qkv_row, (int)s.window, (int)c.attn_splits};
+    // GEMMs
+    auto gemm = [&](GemmArgs& g, int& ks, bool wf32, uint64_t w, uint64_t x, int N, int Kd, int ldw) -> int {
+        memset(&g, 0, sizeof g);
+        g.w = (const void*)w;
+        g.x = (const void*)x;
+        g.M = M; g.N = N; g.K = Kd; g.ldw = ldw; g.ldx = Kd;
+        g.partial = gpart;
+        g.counter = gcnt;
+        g.out_f32 = 0;
+        ks = gemm_ksplit(wf32, Kd);
+        MK_REQUIRE(ks > 0 && ks <= 16, "K %d has no supported split", Kd);
+        MK_REQUIRE(N % gemm_bn(wf32) == 0, "N %d is not a multiple of the %d-row tile", N, gemm_bn(wf32));
+        MK_REQUIRE(N / gemm_bn(wf32) <= 1024, "N %d has too many tiles", N);
+        return 0;
+    };
+    // o_proj: x_attn [M, qh 64] . w_o [H, qh 64]^T -> this rank's slot of every present rank's workspace
+    if (gemm(L->oproj, L->ks_oproj, false, b->w_o, b->x_attn, H, qh * kHeadDim, qh * kHeadDim)) return -1;
+    {
+        void* dst[kMaxRanks];
+        const int n = peers(b->ar_peer, b->ar, dst, 0, (int)s.ranks);
+        for (int i = 0; i < n; ++i) L->oproj.out[i] = (bf16*)dst[i] + (size_t)s.rank * M * H;
+        L->oproj.n_out = n;
+        L->oproj.ldo = H;
+        L->oproj.col0 = 0;
+    }
+    // pooler: the node block of rows [j P/nr, (j+1) P/nr) -> the node's gather rows
+    if (gemm(L->pooler, L->ks_pooler, false, b->w_p + (uint64_t)jnode * (P / nr) * H * 2, b->h3, P / nr, H, H)) return -1;
+    L->pooler.n_out = peers(b->pool_ag_peer, b->pool_ag, L->pooler.out, node0, nr);
+    L->pooler.ldo = P;
+    L->pooler.col0 = jnode * (P / nr);
+    // router: f32 weights through tf32, f32 activations, f32 logits (replicated on every rank)
+    if (gemm(L->router, L->ks_router, true, b->w_r, b->h3f, E, H, H)) return -1;
+    L->router.out[0] = (void*)b->logits;
+    L->router.n_out = 1;
+    L->router.ldo = E;
+    L->router.out_f32 = 1;
+    // unpooler: node block of [H, P]
+    if (gemm(L->unpool, L->ks_unpool, false, b->w_up + (uint64_t)jnode * (H / nr) * P * 2, b->y, H / nr, P, P)) return -1;
+    L->unpool.n_out = peers(b->unpool_ag_peer, b->unpool_ag, L->unpool.out, node0, nr);
+    L->unpool.ldo = H;
+    L->unpool.col0 = jnode * (H / nr);
+    // successor's qkv
+    if (!tail) {
+        if (gemm(L->qkv, L->ks_qkv, false, b->w_qkv, b->h3q, (int)c.qkv_row, H, H)) return -1;
+        L->qkv.out[0] = (void*)b->qkv_out;
+        L->qkv.n_out = 1;
+        L->qkv.ldo = (int)c.qkv_row;
+    }
+    // norms
+    L->post_norm = NormArgs{0, H, (int)s.ranks, (const bf16*)b->ar, (bf16*)b->branch, (const float*)b->stream_in,
+                            (const float*)b->alpha, (const float*)b->beta, (const bf16*)b->prenorm_w, nullptr,
+                            (float*)b->stream_out, (bf16*)b->h3, (float*)b->h3f, M};
+    L->cross_norm = NormArgs{1, H, (int)s.ranks, (const bf16*)b->unpool_ag, nullptr, (const float*)b->stream_out,
+                             (const float*)b->c_alpha, (const float*)b->c_beta, (const bf16*)b->c_pre_w, (const bf16*)b->c_post_w,
+                             (float*)b->c_stream_out, (bf16*)b->h3q, nullptr, M};
+    L->topk = TopkArgs{(const float*)b->logits, (const float*)b->expert_bias, (int*)b->topk_idx32, (float*)b->topk_w,
+                       b->router_mult, (float)b->route_scale, E, K, M};
+    L->nq = NqArgs{(const bf16*)b->pool_ag, (const bf16*)b->gamma, (unsigned char*)b->q, (unsigned char*)b->sf,
+                   (float*)b->x_scale, (float)b->eps, P, (int)s.bf16};
+    L->combine = CombineArgs{(const bf16*)b->zb, (const float*)b->topk_w, (const bf16*)b->gamma_p1, (bf16*)b->y, P, K, b_live};
+    L->rowops = RowopsArgs{(bf16*)b->qkv_out, s.next_rope ? (const float*)b->cos_sin : nullptr, (const int*)b->cache_loc,
+                           (unsigned char*)b->next_k_cache, (unsigned char*)b->next_v_cache, (float)b->q_scale, (float)b->qkv_eps,
+                           M, qh, kvh, (int)c.qkv_row, (int)c.kv_row_bytes};
+    // experts
+    ExpertArgs& ex = L->ex;
+    memset(&ex, 0, sizeof ex);
+    ex.rt = L->rt;
+    ex.P = P; ex.I = I; ex.I_s = I_s; ex.H_s = H_s; ex.rank = (int)s.rank; ex.ranks = (int)s.ranks; ex.topk = K; ex.wbf16 = (int)s.bf16;
+    ex.xq = (const unsigned char*)b->q;
+    ex.x_sf = (const unsigned char*)b->sf;
+    ex.x_scale = (const float*)b->x_scale;
+    ex.w1_gate = (const unsigned char*)b->w1_gate;
+    ex.w1_gate_sf = (const unsigned char*)b->w1_gate_sf;
+    ex.w1_up = (const unsigned char*)b->w1_up;
+    ex.w1_up_sf = (const unsigned char*)b->w1_up_sf;
+    ex.g1_alphas = (const float*)b->g1_alphas;
+    ex.g1_scale_c = (const float*)b->g1_scale_c;
+    ex.n_peer = peers(b->z_peer, b->z, (void**)ex.z_peer, 0, (int)s.ranks);
+    if (fp4) {
+        const int n1 = peers(b->zsf_peer, b->z_sf, (void**)ex.zsf_peer, 0, (int)s.ranks);
+        const int n2 = peers(b->zex_peer, b->z_ex, (void**)ex.zex_peer, 0, (int)s.ranks);
+        MK_REQUIRE(n1 == ex.n_peer && n2 == ex.n_peer, "z_peer / zsf_peer / zex_peer name different ranks");
+    }
+    {
+        const int n3 = peers(b->zb_peer, b->zb, (void**)ex.zb_peer, 0, (int)s.ranks);
+        MK_REQUIRE(n3 == ex.n_peer, "zb_peer and z_peer name different ranks");
+    }
+    ex.z = (const unsigned char*)b->z;
+    ex.z_sfd = L->z_sfd;
+    ex.rowscale = L->rowscale;
+    ex.w2 = (const unsigned char*)b->w2;
+    ex.w2_sf = (const unsigned char*)b->w2_sf;
+    ex.g2_alphas = (const float*)b->g2_alphas;
+    MK_REQUIRE(g1_smem(P) <= 200 * 1024 && g2_smem(I) <= 200 * 1024, "expert rows exceed shared memory");
+    *out = L;
+    guard.l = nullptr;
+    return 0;
+}
+
+static int run_stage(const MkLaunch* L, int st, cudaStream_t s, bool pdl) {
+    if (!L->stage_on[st]) return 0;
+    cudaError_t e = cudaSuccess;
+    switch (st) {
+        case ST_ATTN_SPLIT: e = attn_split_launch(L->attn, s, pdl); break;
+        case ST_ATTN_COMBINE: e = attn_combine_launch(L->attn, s, pdl); break;
+        case ST_OPROJ: e = gemm_launch(L->oproj, false, L->ks_oproj, s, pdl); break;
+        case ST_POST_NORM: e = resid_norm_launch(L->post_norm, s, pdl); break;
+        case ST_POOLER: e = gemm_launch(L->pooler, false, L->ks_pooler, s, pdl); break;
+        case ST_ROUTER: e = gemm_launch(L->router, true, L->ks_router, s, pdl); break;
+        case ST_TOPK: e = topk_launch(L->topk, s, pdl); break;
+        case ST_NQ: e = nq_launch(L->nq, (int)L->shape.rows, s, pdl); break;
+        case ST_TABLES:
+            e = route_tables_launch(L->topk.ids, L->topk.E, L->topk.k, L->combine.b_live, L->rt, s, pdl);
+            break;
+        case ST_G1: e = g1_launch(L->ex, L->max_active, s, pdl); break;
+        case ST_HROW:
+            e = hrow_launch((const unsigned char*)L->bind.z_sf, (const signed char*)L->bind.z_ex, (int)L->shape.inter / 16,
+                            L->slots_live, (int)L->consts.slots, L->z_sfd, L->rowscale, s, pdl);
+            break;
+        case ST_G2: e = g2_launch(L->ex, L->max_active, s, pdl); break;
+        case ST_COMBINE: e = combine_launch(L->combine, (int)L->shape.rows, s, pdl); break;
+        case ST_UNPOOL: e = gemm_launch(L->unpool, false, L->ks_unpool, s, pdl); break;
+        case ST_CROSS_NORM: e = resid_norm_launch(L->cross_norm, s, pdl); break;
+        case ST_QKV: e = gemm_launch(L->qkv, false, L->ks_qkv, s, pdl); break;
+        case ST_ROWOPS: e = rowops_launch(L->rowops, s, pdl); break;
+        default: return fail("stage %d does not exist", st);
+    }
+    if (e != cudaSuccess) return fail("stage %d launch: %s", st, cudaGetErrorString(e));
+    return 0;
+}
+
+int mk_launch_step(const MkLaunch* launch, uint64_t stream, int64_t first, int64_t count) {
+    MK_REQUIRE(launch != nullptr, "launch is NULL");
+    MK_REQUIRE(!launch->pack_only, "a pack-only record (bound without a module) cannot launch");
+    MK_REQUIRE(first >= 0 && count >= 0 && first + count <= ST_COUNT, "stages [%lld, %lld) outside 0..%d", (long long)first,
+               (long long)(first + count), ST_COUNT);
+    for (int st = (int)first; st < first + count; ++st)
+        if (run_stage(launch, st, (cudaStream_t)stream, false)) return -1;
+    return 0;
+}
+
+int mk_launch(const MkLaunch* launch, uint64_t stream, int pdl) {
+    MK_REQUIRE(launch != nullptr, "launch is NULL");
+    MK_REQUIRE(!launch->pack_only, "a pack-only record (bound without a module) cannot launch");
+    for (int st = 0; st < ST_COUNT; ++st)
+        if (run_stage(launch, st, (cudaStream_t)stream, pdl != 0 && st > 0)) return -1;
+    return 0;
+}
+
+void mk_launch_free(MkLaunch* launch) { delete launch; }
+
+int mk_launch_info(const MkLaunch* launch, MkLaunchInfo* out) {
+    MK_REQUIRE(launch != nullptr && out != nullptr, "launch or out is NULL");
+    const MkLaunch* L = launch;
+    int kernels = 0;
+    for (int i = 0; i < ST_COUNT; ++i) kernels += L->stage_on[i];
+    int64_t grid = 0, smem = 0;
+    auto gg = [&](const GemmArgs& g, bool f32, int ks) {
+        const int64_t n = (int64_t)(g.N / gemm_bn(f32)) * ks;
+        if (n > grid) grid = n;
+        const int64_t sm = (int64_t)gemm_smem(f32, g.K, ks);
+        if (sm > smem) smem = sm;
+    };
+    gg(L->oproj, false, L->ks_oproj);
+    gg(L->pooler, false, L->ks_pooler);
+    gg(L->router, true, L->ks_router);
+    gg(L->unpool, false, L->ks_unpool);
+    if (!L->shape.tail) gg(L->qkv, false, L->ks_qkv);
+    const int64_t g1 = (int64_t)(L->ex.I_s / 16) * L->max_active, g2 = (int64_t)(L->ex.H_s / 16) * L->max_active;
+    if (g1 > grid) grid = g1;
+    if (g2 > grid) grid = g2;
+    if ((int64_t)g1_smem(L->ex.P) > smem) smem = (int64_t)g1_smem(L->ex.P);
+    if ((int64_t)g2_smem(L->ex.I) > smem) smem = (int64_t)g2_smem(L->ex.I);
+    out->grid = grid;
+    out->block = 1024;
+    out->cluster = 1;
+    out->smem = smem;
+    out->kernels = kernels;
+    out->param_bytes = (int64_t)sizeof(MkLaunch);
+    return 0;
+}
+
+int mk_launch_status(const MkLaunch* launch, uint64_t stream, MkLaunchStatus* out) {
+    MK_REQUIRE(launch != nullptr && out != nullptr, "launch or out is NULL");
+    MK_REQUIRE(!launch->pack_only, "a pack-only record has no device status");
+    cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+    int host[8] = {0};
+    e = cudaMemcpy(host, launch->status, sizeof host, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(status)");
+    out->code = host[0];
+    out->stage = host[1];
+    out->block = host[2];
+    out->observed = host[3];
+    out->expected = host[4];
+    return 0;
+}
+
+}  // extern "C"

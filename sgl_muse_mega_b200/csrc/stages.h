@@ -1,0 +1,113 @@
+// Argument records and host entry points of the layer's kernels (one record per kernel, frozen at bind time).
+#pragma once
+
+#include "params.h"
+
+namespace mk {
+
+struct AttnArgs {
+    const bf16* qkv;
+    const unsigned char* k_cache;
+    const unsigned char* v_cache;
+    const long long* page_table;
+    const int* kv_len;
+    float* ws;
+    bf16* x_attn;
+    int M, qh, kvh, G, R, qkv_row, window, splits;
+};
+struct NormArgs {
+    int mode, H, ranks;
+    const bf16* src;
+    bf16* branch;
+    const float* stream_in;
+    const float* alpha;
+    const float* beta;
+    const bf16* pre_w;
+    const bf16* post_w;
+    float* stream_out;
+    bf16* normed;
+    float* normed_f32;
+    int M;
+};
+struct TopkArgs {
+    const float* logits;
+    const float* bias;
+    int* ids;
+    float* w;
+    double mult;
+    float route_scale;
+    int E, k, M;
+};
+struct NqArgs {
+    const bf16* pooled;
+    const bf16* gamma;
+    unsigned char* q;
+    unsigned char* sf;
+    float* x_scale;
+    float eps;
+    int P, bf16_out;
+};
+struct CombineArgs {
+    const bf16* zb;
+    const float* w;
+    const bf16* gamma_p1;
+    bf16* y;
+    int P, k, b_live;
+};
+struct RowopsArgs {
+    bf16* qkv;
+    const float* cos_sin;
+    const int* cache_loc;
+    unsigned char* k_cache;
+    unsigned char* v_cache;
+    float q_scale, eps;
+    int M, qh, kvh, qkv_row, kv_row_bytes;
+};
+struct ExpertArgs {
+    const RouteTables* rt;
+    int P, I, I_s, H_s, rank, ranks, topk, wbf16;
+    const unsigned char* xq;
+    const unsigned char* x_sf;
+    const float* x_scale;
+    const unsigned char* w1_gate;
+    const unsigned char* w1_gate_sf;
+    const unsigned char* w1_up;
+    const unsigned char* w1_up_sf;
+    const float* g1_alphas;
+    const float* g1_scale_c;
+    unsigned char* z_peer[kMaxRanks];
+    unsigned char* zsf_peer[kMaxRanks];
+    signed char* zex_peer[kMaxRanks];
+    int n_peer;
+    const unsigned char* z;
+    const unsigned char* z_sfd;
+    const float* rowscale;
+    const unsigned char* w2;
+    const unsigned char* w2_sf;
+    const float* g2_alphas;
+    bf16* zb_peer[kMaxRanks];
+};
+
+int gemm_ksplit(bool wf32, int K);
+int gemm_bn(bool wf32);
+size_t gemm_smem(bool wf32, int K, int ksplit);
+cudaError_t gemm_prepare();
+cudaError_t gemm_launch(const GemmArgs& a, bool wf32, int ksplit, cudaStream_t stream, bool pdl);
+cudaError_t attn_split_launch(const AttnArgs& a, cudaStream_t stream, bool pdl);
+cudaError_t attn_combine_launch(const AttnArgs& a, cudaStream_t stream, bool pdl);
+cudaError_t resid_norm_launch(const NormArgs& a, cudaStream_t s, bool pdl);
+cudaError_t topk_launch(const TopkArgs& a, cudaStream_t s, bool pdl);
+cudaError_t nq_launch(const NqArgs& a, int M, cudaStream_t s, bool pdl);
+cudaError_t route_tables_launch(const int* ids, int E, int k, int b_live, RouteTables* rt, cudaStream_t s, bool pdl);
+cudaError_t hrow_launch(const unsigned char* z_sf, const signed char* z_ex, int groups, int slots_live, int slots,
+                        unsigned char* z_sfd, float* rowscale, cudaStream_t s, bool pdl);
+cudaError_t combine_launch(const CombineArgs& a, int M, cudaStream_t s, bool pdl);
+cudaError_t rowops_launch(const RowopsArgs& a, cudaStream_t s, bool pdl);
+size_t g1_smem(int P);
+size_t g2_smem(int I);
+cudaError_t experts_prepare();
+cudaError_t g1_launch(const ExpertArgs& a, int max_active, cudaStream_t s, bool pdl);
+cudaError_t g2_launch(const ExpertArgs& a, int max_active, cudaStream_t s, bool pdl);
+
+
+}  // namespace mk

@@ -1,0 +1,176 @@
+"""Device state and binding of one decoder-layer launch per rank.
+
+Counterpart of the reference's ``sm103/buffers.py:42-399`` (device + symmetric state) and of ``Stack.layer_bind`` in
+``sm103/verify.py:246-386``: every buffer a layer launch reads or writes is allocated here once, the bind struct is
+filled by field name and the launch record is bound once; ``LayerRank.launch`` is then the only per-step call.
+
+``LayerWorld`` holds every rank of a tensor-parallel world on ONE device and wires their exchange buffers to each other
+as peers. It serves the parity tests (the ranks' stages are interleaved with ``Launch.step`` so that every exchange has
+all its contributions) and the single-GPU benchmark of one rank's slice (the other ranks' contributions stay in place
+from a first interleaved pass). On a multi-GPU world the same bind takes the peers' mapped pointers instead.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ...common import host
+from ..config import Config
+
+# stage groups between which every rank must have finished before any rank continues (the exchanges)
+STAGE_GROUPS = ((0, 3), (3, 2), (5, 5), (10, 2), (12, 2), (14, 3))
+STAGE_NAMES = (
+    "attn_split", "attn_combine", "o_proj", "post_norm", "pooler", "router", "topk", "nq", "route_tables", "g1",
+    "h_row", "g2", "combine", "unpooler", "cross_norm", "qkv", "rowops",
+)  # fmt: skip
+
+
+def layer_shape(cfg: Config, case, rank: int):
+    return host.make(
+        "MkLayerShape",
+        rows=case.rows, hidden=cfg.hidden, moe_hidden=cfg.moe_hidden, q_heads=cfg.q_heads_rank,
+        kv_heads=cfg.kv_heads_rank, experts=cfg.experts, topk=cfg.topk, inter=cfg.moe_inter, ranks=cfg.tp,
+        node_ranks=cfg.node_ranks, rank=rank, window=0 if case.global_attn else cfg.swa_window,
+        bf16=int(case.bf16), tail=int(case.tail), next_rope=int(not (case.next_global or case.tail)),
+    )  # fmt: skip
+
+
+class LayerRank:
+    """One rank's weights (moved to the device), buffers and bound launch of one layer."""
+
+    def __init__(self, lib: host.Library, module, case, rank: int, device, kv_rows: Optional[int] = None):
+        cfg = case.cfg
+        self.lib, self.case, self.rank, self.device = lib, case, rank, device
+        self.shape = layer_shape(cfg, case, rank)
+        self.consts = c = lib.layer_constants(self.shape)
+        t = case.ranks[rank]
+        dev = lambda x: None if x is None else x.to(device).contiguous()  # noqa: E731
+        self.w = {k: dev(v) for k, v in vars(t).items()}
+        M, H, P, E, K = case.rows, cfg.hidden, cfg.moe_hidden, cfg.experts, cfg.topk
+        bf, f32, u8, i32 = torch.bfloat16, torch.float32, torch.uint8, torch.int32
+
+        def z(shape, dtype):
+            return torch.zeros(shape, dtype=dtype, device=device)
+
+        def raw(nbytes):
+            return z((int(nbytes),), u8)
+
+        # KV pools of this layer (context rows then the window's rows, identity slots) and of the successor
+        kv_rows = kv_rows or (case.ctx + M + 127) // 128 * 128
+        kvw = cfg.kv_heads_rank * cfg.head_dim
+        self.k_cache, self.v_cache = z((kv_rows, kvw), bf), z((kv_rows, kvw), bf)
+        self.k_cache[: case.ctx] = self.w["k_ctx"].reshape(case.ctx, kvw)
+        self.v_cache[: case.ctx] = self.w["v_ctx"].reshape(case.ctx, kvw)
+        qo, ko = cfg.q_heads_rank * 64, (cfg.q_heads_rank + cfg.kv_heads_rank) * 64
+        self.k_cache[case.ctx : case.ctx + M] = self.w["qkv_in"][:, qo:ko]
+        self.v_cache[case.ctx : case.ctx + M] = self.w["qkv_in"][:, ko : ko + kvw]
+        self.next_k, self.next_v = z((kv_rows, kvw), bf), z((kv_rows, kvw), bf)
+        self.page_table = torch.arange(kv_rows, dtype=torch.int64, device=device) * c.kv_row_bytes
+        self.kv_len = torch.tensor([case.ctx + M], dtype=i32, device=device)
+        self.cache_loc = torch.arange(case.ctx, case.ctx + M, dtype=i32, device=device)
+        self.kv_rows = kv_rows
+        # outputs
+        self.o = dict(
+            x_attn=z((M, cfg.q_heads_rank * 64), bf), branch=z((M, H), bf), stream_mid=z((M, H), f32), h3=z((M, H), bf),
+            h3f=z((M, H), f32), logits=z((M, E), f32), ids=z((M, K), i32), w=z((M, K), f32),
+            xq=z((M, P), bf) if case.bf16 else z((M, P // 2), u8), x_sf=z((M, P // 16), u8), x_scale=z((M,), f32),
+            y=z((M, P), bf), stream_out=z((M, H), f32), h3_next=z((M, H), bf), qkv_next=z((M, c.qkv_row), bf),
+        )  # fmt: skip
+        # exchange buffers (symmetric across the ranks)
+        self.ar = raw(c.ar_bytes)
+        self.pool_ag = z((M, P), bf)
+        self.unpool_ag = z((M, H), bf)
+        self.z, self.z_sf, self.z_ex, self.zb = raw(c.z_bytes), raw(c.z_sf_bytes), raw(c.z_ex_bytes), raw(c.zb_bytes)
+        self.flags = z((c.flag_words,), i32)
+        self.ws = raw(c.ws_bytes)
+        self.status = raw(c.status_bytes)
+        self.module = module
+        self.launch_record = None
+
+    def bind(self, peers: Optional[list] = None, b_live: int = 0):
+        """Binds the launch; ``peers`` = every rank's ``LayerRank`` (own included) or None for a lone rank."""
+        cfg, case, w, o = self.case.cfg, self.case, self.w, self.o
+        n = cfg.tp
+
+        def peer(attr):
+            if peers is None:
+                return [getattr(self, attr) if r == self.rank else None for r in range(n)]
+            return [getattr(p, attr) if p is not None else None for p in peers]
+
+        fp4 = not case.bf16
+        bind = host.make(
+            "MkLayerBind",
+            qkv_in=w["qkv_in"], k_cache=self.k_cache, v_cache=self.v_cache, kv_rows=self.kv_rows,
+            page_table=self.page_table, kv_len=self.kv_len, page_stride=self.kv_rows, x_attn=o["x_attn"],
+            w_o=w["o_proj"], ar=self.ar, ar_peer=peer("ar"), branch=o["branch"], stream_in=w["stream_in"],
+            alpha=w["post_alpha"], beta=w["post_beta"], prenorm_w=w["post_pre_w"], stream_out=o["stream_mid"],
+            h3=o["h3"], h3f=o["h3f"], w_p=w["pooler"], pool_ag=self.pool_ag, pool_ag_peer=peer("pool_ag"),
+            w_r=w["router"], logits=o["logits"], router_mult=case.router_mult, expert_bias=w["expert_bias"],
+            topk_idx32=o["ids"], topk_w=o["w"], route_scale=cfg.route_scale, gamma=w["pre_gamma"], eps=case.pre_eps,
+            q=o["xq"], sf=o["x_sf"], x_scale=o["x_scale"],
+            w1_gate=w["gate_q"] if fp4 else w["gate"], w1_gate_sf=w["gate_sf"], w1_up=w["up_q"] if fp4 else w["up"],
+            w1_up_sf=w["up_sf"], w2=w["w2_q"] if fp4 else w["w2"], w2_sf=w["w2_sf"], g1_alphas=w["g1_alphas"],
+            g1_scale_c=w["g1_scale_c"], g2_alphas=w["g2_alphas"], z=self.z, z_sf=self.z_sf, z_ex=self.z_ex, zb=self.zb,
+            z_peer=peer("z"), zsf_peer=peer("z_sf"), zex_peer=peer("z_ex"), zb_peer=peer("zb"),
+            gamma_p1=w["gamma_p1"], y=o["y"], w_up=w["unpooler"], unpool_ag=self.unpool_ag,
+            unpool_ag_peer=peer("unpool_ag"), c_alpha=w["cross_alpha"], c_beta=w["cross_beta"], c_pre_w=w["cross_pre_w"],
+            c_post_w=w["cross_post_w"], c_stream_out=o["stream_out"], h3q=o["h3_next"], w_qkv=w["next_qkv"],
+            qkv_out=o["qkv_next"], cos_sin=w["next_cos_sin"], cache_loc=self.cache_loc, next_k_cache=self.next_k,
+            next_v_cache=self.next_v, next_kv_rows=self.kv_rows, q_scale=cfg.q_scale, qkv_eps=cfg.rms_eps,
+            flags=self.flags, flags_peer=peer("flags"), ws=self.ws, status=self.status, b_live=b_live, wait_budget=0,
+        )  # fmt: skip
+        self.launch_record = self.lib.layer_bind(self.module, self.shape, bind)
+        return self.launch_record
+
+    def launch(self, stream: int, pdl: bool = False) -> None:
+        self.launch_record(stream, pdl)
+
+    # ---- gathered views (what the oracle calls pooled / zb / ffn_out / the h planes) ----
+    def values(self) -> dict:
+        """The layer's named values as the oracle names them (device tensors)."""
+        cfg, case, c = self.case.cfg, self.case, self.consts
+        M, K, P, I = case.rows, cfg.topk, cfg.moe_hidden, cfg.moe_inter
+        out = dict(self.o)
+        out["pooled"] = self.pool_ag
+        out["ffn_out"] = self.unpool_ag
+        out["zb"] = self.zb.view(torch.bfloat16).view(M, K, P)
+        if case.bf16:
+            out["x"] = out.pop("xq")
+            out.pop("x_sf"), out.pop("x_scale")
+        if case.tail:
+            out.pop("qkv_next")
+        out.pop("h3f")
+        return out
+
+    def h_planes(self):
+        cfg, case = self.case.cfg, self.case
+        M, K, I = case.rows, cfg.topk, cfg.moe_inter
+        return (
+            self.z.view(M, K, I // 2),
+            self.z_sf.view(M, K, I // 16),
+            self.z_ex.view(torch.int8).view(M, K, I // 16).to(torch.int32),
+        )
+
+
+class LayerWorld:
+    """Every rank of the world on one device, exchange buffers wired as peers (see the module docstring)."""
+
+    def __init__(self, case, device, lib: Optional[host.Library] = None, ranks: Optional[list] = None, b_live: int = 0):
+        self.lib = lib or host.library()
+        self.case, self.device = case, device
+        with torch.cuda.device(device):
+            self.module = self.lib.load()
+        n = case.cfg.tp
+        self.ranks = [LayerRank(self.lib, self.module, case, r, device) for r in range(n)]
+        for r in self.ranks:
+            r.bind(self.ranks, b_live)
+
+    def run_interleaved(self, stream: Optional[int] = None) -> None:
+        """All ranks, stage group by stage group: every exchange sees every rank's contribution."""
+        s = torch.cuda.current_stream(self.device).cuda_stream if stream is None else stream
+        for first, count in STAGE_GROUPS:
+            for r in self.ranks:
+                r.launch_record.step(s, first, count)

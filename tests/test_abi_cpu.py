@@ -1,0 +1,96 @@
+"""The C-ABI library without a GPU: it loads, exports every symbol the header declares, computes buffer extents and
+validates binds (pack-only records, as the reference's CPU parameter-block tests use them: test_param_blocks.py)."""
+
+import ctypes
+import re
+
+import pytest
+import torch
+
+from golden_cases import CASES
+from sgl_muse_mega_b200.common import host
+from sgl_muse_mega_b200.muse_spark.b200 import layer as L
+from sgl_muse_mega_b200.muse_spark.b200 import synthetic
+from sgl_muse_mega_b200.muse_spark.config import Config
+
+
+@pytest.fixture(scope="module")
+def lib():
+    return host.library()
+
+
+def declared_functions():
+    text = host.HEADER.read_text()
+    return sorted(set(re.findall(r"^(?:int|void|const char\*)\s+(mk_\w+)\s*\(", text, re.M)))
+
+
+def test_exports_every_declared_symbol(lib):
+    names = declared_functions()
+    assert set(names) == set(host.EXPORTS), (names, host.EXPORTS)
+    for n in names:
+        assert getattr(lib.dll, n) is not None, n
+
+
+def test_struct_mirrors_have_only_abi_scalars():
+    for name, cls in host.STRUCTS.items():
+        assert ctypes.sizeof(cls) % 8 == 0, name
+        assert cls._fields_, name
+
+
+def test_make_demands_every_field():
+    with pytest.raises(ValueError, match="missing"):
+        host.make("MkLayerShape", rows=16)
+
+
+def test_constants_full_shape(lib):
+    cfg = Config()
+    shape = host.make(
+        "MkLayerShape", rows=16, hidden=cfg.hidden, moe_hidden=cfg.moe_hidden, q_heads=cfg.q_heads_rank,
+        kv_heads=cfg.kv_heads_rank, experts=cfg.experts, topk=cfg.topk, inter=cfg.moe_inter, ranks=8, node_ranks=4,
+        rank=3, window=2047, bf16=0, tail=0, next_rope=1,
+    )  # fmt: skip
+    c = lib.layer_constants(shape)
+    assert c.stages == host.MACROS["MKH_LAYER_STAGES"]
+    assert (c.slots, c.qkv_row, c.kv_row_bytes, c.inter_rank, c.hidden_rank) == (128, 2304, 256, 512, 512)
+    assert c.ar_bytes == 8 * 16 * 8192 * 2 and c.zb_bytes == 128 * 4096 * 2 and c.z_bytes == 128 * 2048
+    assert c.ws_bytes > 0 and c.ws_bytes % 256 == 0
+
+
+@pytest.mark.parametrize("field,value,msg", [("rows", 17, "rows"), ("ranks", 3, "ranks"), ("hidden", 100, "hidden")])
+def test_bad_shapes_are_refused(lib, field, value, msg):
+    kw = dict(rows=16, hidden=1024, moe_hidden=1024, q_heads=8, kv_heads=1, experts=16, topk=8, inter=1024, ranks=8,
+              node_ranks=4, rank=0, window=7, bf16=0, tail=0, next_rope=1)  # fmt: skip
+    kw[field] = value
+    shape = host.make("MkLayerShape", **kw)
+    c = host.STRUCTS["MkLayerConstants"]()
+    assert lib.dll.mk_layer_constants(ctypes.byref(shape), ctypes.byref(c)) == -1
+    assert msg in lib.dll.mk_last_error().decode()
+
+
+def test_pack_only_bind_and_refusals(lib):
+    """A bind without a module validates every operand and yields a record that reports its geometry but cannot launch."""
+    cfg, kw = CASES["small_fp4_swa_tp2"]
+    case = synthetic.layer_case(cfg, **kw)
+    rank = L.LayerRank(lib, None, case, 0, torch.device("cpu"))
+    rec = rank.bind()
+    info = rec.info()
+    assert info.kernels == 17 and info.grid > 0 and info.smem > 0
+    with pytest.raises(RuntimeError, match="pack-only"):
+        rec(0, False)
+    # a missing operand is named
+    rank.w["o_proj"] = None
+    with pytest.raises(RuntimeError, match="w_o"):
+        rank.bind()
+
+
+def test_module_load_needs_builtin_image(lib):
+    out = ctypes.c_void_p()
+    assert lib.dll.mk_module_load(b"xx", 2, None, ctypes.byref(out)) == -1
+    assert "image NULL" in lib.dll.mk_last_error().decode()
+
+
+def test_tail_and_bf16_variants_drop_stages(lib):
+    cfg, kw = CASES["small_bf16_tail_tp4"]
+    case = synthetic.layer_case(cfg, **kw)
+    rec = L.LayerRank(lib, None, case, 1, torch.device("cpu")).bind()
+    assert rec.info().kernels == 17 - 3  # no h-row view (bf16), no successor qkv + rowops (tail)
