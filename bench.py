@@ -1,0 +1,346 @@
+"""Benchmark of the decode hot path: one full-shape Muse-Spark-Open decoder layer, one rank's TP8 slice per GPU, the
+16-row verify window (DFlash2 block 16) over an 8192-token bf16 paged KV cache.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one layer launch through the C ABI (mk_launch of a bound layer). Consecutive steps walk a ring of distinct
+layers (3 sliding-window : 1 global, as the model interleaves them) so that no weight byte is read from L2: the ring is
+several times larger than the 126 MB L2. Prints ONE JSON line (rank 0).
+
+The CPU leg (``cpu_baseline`` and ``--impl reference``) times the CPU oracle port of the reference's torch layer
+(oracle/muse_layer.py, which restates test/reference/muse_spark.py) on the host cores. It is the only place this file
+touches ``oracle/``.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "decoder-layer latency, batch-1 verify window M=16 (per-layer us vs HBM roofline)"
+WORKLOAD = "configs[1]: one full-shape Muse-Spark-Open decoder layer, TP8/EP8 slice on 1 B200, M=16, ctx 8192, NVFP4 experts"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--ring", type=int, default=8, help="distinct layers in the ring")
+    ap.add_argument("--ctx", type=int, default=8192)
+    ap.add_argument("--rows", type=int, default=16)
+    ap.add_argument("--seed", type=int, default=1)
+    ap.add_argument("--cpu-sample-experts", type=int, default=24)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    return ap.parse_args()
+
+
+def peaks() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---- algorithmic bytes (per layer, per GPU) ---------------------------------------------------------------------------
+
+
+def layer_bytes(cfg, d: int, ctx: int, rows: int, global_attn: bool) -> dict:
+    """Weight + KV bytes one layer launch must read: qkv, o_proj, the node block of pooler and unpooler, the router
+    (f32), d distinct experts' W1 + W2 codes and scales, and the visible KV rows (K and V)."""
+    tp, g, H, P = cfg.tp, cfg.node_ranks, cfg.hidden, cfg.moe_hidden
+    qkv = cfg.qkv_row * H * 2
+    o = H * cfg.oproj_k * 2
+    pool = P * H * 2 // g
+    unpool = H * P * 2 // g
+    router = cfg.experts * H * 4
+    per_expert_g1 = 2 * cfg.inter_rank * (P // 2 + P // 16)
+    per_expert_g2 = cfg.moe_hidden_rank * (cfg.moe_inter // 2 + cfg.moe_inter // 16)
+    keys = ctx + rows if global_attn else min(ctx + rows, cfg.swa_window + rows)
+    kv = 2 * keys * cfg.kv_row_bytes
+    dense = qkv + o + pool + unpool + router
+    return dict(dense=dense, g1=d * per_expert_g1, g2=d * per_expert_g2, kv=kv,
+                total=dense + d * (per_expert_g1 + per_expert_g2) + kv)  # fmt: skip
+
+
+# ---- clocks -----------------------------------------------------------------------------------------------------------
+
+
+class ClockSampler:
+    FIELDS = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )  # fmt: skip
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6 or not parts[0].isdigit():
+                continue
+            sm.append(int(parts[0]))
+            mx.append(int(parts[1]))
+            for n, v in zip(names, parts[2:6]):
+                if v.lower() == "active":
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [s for s in sm if s >= 0.5 * max(mx)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---- CPU leg ----------------------------------------------------------------------------------------------------------
+
+
+def cpu_layer_sample(args, threads: int, repeats: int = 1) -> dict:
+    """The CPU oracle on one full-shape layer of the whole TP8 world (all 8 ranks' slices), routing confined to a hot
+    subset of experts so that the weights fit in host memory; returns the wall time per rank slice."""
+    import torch
+
+    from oracle import muse_layer as O
+    from oracle.cases import rank_layers
+    from sgl_muse_mega_b200.muse_spark.b200 import synthetic
+    from sgl_muse_mega_b200.muse_spark.config import Config
+
+    torch.set_num_threads(threads)
+    cfg = Config()
+    synthetic.set_device("cpu")
+    hot = torch.randperm(cfg.experts, generator=torch.Generator().manual_seed(args.seed))[: args.cpu_sample_experts]
+    case = synthetic.layer_case(cfg, rows=args.rows, ctx=args.ctx, band="baseline", seed=args.seed, experts_subset=hot)
+    layers = rank_layers(case)
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        O.run_layer(layers, cfg.node_ranks)
+        times.append(time.perf_counter() - t0)
+    wall = statistics.median(times)
+    return {
+        "wall_s": wall,
+        "us_per_rank_layer": wall / cfg.tp * 1e6,
+        "sample": f"1 full-shape layer, all {cfg.tp} rank slices of the TP8 world, M={args.rows}, ctx={args.ctx}, routing "
+        f"confined to {args.cpu_sample_experts} experts; value = wall / {cfg.tp} ranks; median of {repeats}",
+    }
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    t0 = time.perf_counter()
+    r = cpu_layer_sample(args, threads, repeats=max(1, min(args.steps, 3)))
+    v = r["us_per_rank_layer"]
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "us", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": v / 1e3, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "dtype": "nvfp4 weights x nvfp4/bf16 activations, f64 accumulate (CPU oracle)", "data": "synthetic",
+        "config": {"workload": WORKLOAD},
+        "cpu_baseline": {"value": v, "unit": "us", "cores": threads, "kind": "port", "sample": r["sample"]},
+        "e2e": {"value": v, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t0,
+    }  # fmt: skip
+    print(json.dumps(line), flush=True)
+
+
+# ---- GPU leg ----------------------------------------------------------------------------------------------------------
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from sgl_muse_mega_b200.common import host
+    from sgl_muse_mega_b200.muse_spark.b200 import layer as L
+    from sgl_muse_mega_b200.muse_spark.b200 import synthetic
+    from sgl_muse_mega_b200.muse_spark.config import Config
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device: there is no CPU fallback"
+    device = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    cfg = Config()
+    lib = host.library()
+    module = lib.load()
+    synthetic.set_device(device)
+    # a ring of distinct layers: global iff i % 4 == 3 here (3 swa : 1 global). Each GPU holds the slice of TP rank
+    # `rank % 8`; with N GPUs the ranks are independent replicas of the per-GPU work (no exchange partner is waited for).
+    tp_rank = rank % cfg.tp
+    ring = []
+    for i in range(args.ring):
+        glob = i % 4 == 3
+        case = synthetic.layer_case(cfg, rows=args.rows, ctx=args.ctx, global_attn=glob, next_global=(i + 1) % 4 == 3,
+                                    band="baseline", seed=args.seed, layer=2 + i, only_ranks=[tp_rank])  # fmt: skip
+        lr = L.LayerRank(lib, module, case, tp_rank, device, tensors=case.ranks[0])
+        # the absent ranks' contributions: values of the right kind already in the exchange buffers
+        g = torch.Generator(device=device).manual_seed(1000 + i)
+        lr.ar.view(torch.bfloat16).copy_(torch.randn(lr.ar.numel() // 2, generator=g, device=device) * 0.3)
+        lr.pool_ag.copy_(torch.randn(lr.pool_ag.shape, generator=g, device=device))
+        lr.unpool_ag.copy_(torch.randn(lr.unpool_ag.shape, generator=g, device=device))
+        lr.z.copy_(torch.randint(0, 256, lr.z.shape, generator=g, device=device, dtype=torch.uint8))
+        lr.z_sf.copy_(torch.randint(0x30, 0x40, lr.z_sf.shape, generator=g, device=device, dtype=torch.uint8))
+        lr.z_ex.copy_(torch.randint(0, 3, lr.z_ex.shape, generator=g, device=device, dtype=torch.uint8))
+        lr.zb.view(torch.bfloat16).copy_(torch.randn(lr.zb.numel() // 2, generator=g, device=device))
+        lr.bind(None)
+        case.ranks = []  # the device copies live in lr.w
+        ring.append(lr)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream(device)
+    s = stream.cuda_stream
+    info = ring[0].launch_record.info()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    # ---- kernel-resident timing: inputs already in HBM --------------------------------------------------------------
+    for i in range(args.warmup):
+        ring[i % args.ring].launch(s, True)
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for i in range(args.steps):
+        ring[i % args.ring].launch(s, True)
+    ev1.record(stream)
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    us_layer = ms * 1e3 / args.steps
+    for lr in ring:
+        st = lr.launch_record.status(s)
+        assert st.code == 0, f"device status {st.code} at stage {st.stage}"
+    # distinct experts actually routed, per ring layer (drives the algorithmic bytes)
+    d_list = [int(torch.unique(lr.o["ids"]).numel()) for lr in ring]
+    byt = [layer_bytes(cfg, d, args.ctx, args.rows, lr.case.global_attn) for d, lr in zip(d_list, ring)]
+    steps_per_layer = [len(range(i, args.steps, args.ring)) for i in range(args.ring)]
+    total_bytes = sum(b["total"] * n for b, n in zip(byt, steps_per_layer))
+    peak, peak_kind = peaks()
+    layer_gbs = total_bytes / (ms * 1e-3) / 1e9
+
+    # ---- dominant kernel (g1, the gate/up expert GEMM): CUDA events around that stage alone -------------------------
+    G1 = L.STAGE_NAMES.index("g1")
+    k_steps = max(8, min(args.steps, 64))
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(k_steps)]
+    barrier()
+    for i, (a, b) in enumerate(pairs):
+        lr = ring[i % args.ring]
+        lr.launch_record.step(s, 0, G1)
+        a.record(stream)
+        lr.launch_record.step(s, G1, 1)
+        b.record(stream)
+        lr.launch_record.step(s, G1 + 1, len(L.STAGE_NAMES) - G1 - 1)
+    barrier()
+    g1_ms = [a.elapsed_time(b) for a, b in pairs]
+    g1_bytes = sum(byt[i % args.ring]["g1"] for i in range(k_steps))
+    g1_gbs = g1_bytes / (sum(g1_ms) * 1e-3) / 1e9
+
+    # ---- end to end: host buffers in, host buffers out, through the same C-ABI launch -------------------------------
+    M, H = args.rows, cfg.hidden
+    h_qkv = torch.randn(M, cfg.qkv_row).bfloat16().pin_memory()
+    h_stream = torch.randn(M, H).pin_memory()
+    h_out_stream = torch.empty(M, H).pin_memory()
+    h_out_qkv = torch.empty(M, cfg.qkv_row, dtype=torch.bfloat16).pin_memory()
+    h2d = h_qkv.numel() * 2 + h_stream.numel() * 4
+    d2h = h_out_stream.numel() * 4 + h_out_qkv.numel() * 2
+
+    def e2e_step(i):
+        lr = ring[i % args.ring]
+        with torch.cuda.stream(stream):
+            lr.w["qkv_in"].copy_(h_qkv, non_blocking=True)
+            lr.w["stream_in"].copy_(h_stream, non_blocking=True)
+            lr.launch(s, True)
+            h_out_stream.copy_(lr.o["stream_out"], non_blocking=True)
+            h_out_qkv.copy_(lr.o["qkv_next"], non_blocking=True)
+        stream.synchronize()
+
+    for i in range(min(args.warmup, 8)):
+        e2e_step(i)
+    barrier()
+    e_steps = max(8, min(args.steps, 200))
+    t0 = time.perf_counter()
+    for i in range(e_steps):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    e2e_us = (time.perf_counter() - t0) / e_steps * 1e6
+    if world > 1:
+        t = torch.tensor([e2e_us], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_us = float(t.item())
+    clocks = sampler.stop() if sampler else None
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        r = cpu_layer_sample(args, threads, repeats=3)
+        cpu = {"value": r["us_per_rank_layer"], "unit": "us", "cores": threads, "kind": "port", "sample": r["sample"]}
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": us_layer, "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": us_layer / 1e3, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "nvfp4 experts (e2m1 x e4m3 block scales), bf16 dense, f32 accumulate", "data": "synthetic",
+            "config": {
+                "workload": WORKLOAD, "rows": args.rows, "ctx": args.ctx, "ring_layers": args.ring,
+                "ring_bytes": int(sum(b["total"] for b in byt)), "l2": "inputs larger than L2 (ring of distinct layers)",
+                "distinct_experts_per_layer": d_list, "multi_gpu": "independent replicas of the per-GPU slice" if world > 1 else "1 GPU",
+                "kernels_per_step": int(info.kernels),
+            },
+            "layer_roofline": {"bound": "hbm", "achieved": layer_gbs, "peak": peak, "unit": "GB/s", "frac": layer_gbs / peak,
+                               "bytes_per_layer": int(total_bytes / args.steps), "peak_kind": peak_kind},
+            "roofline": {"bound": "hbm", "kernel": "g1_kernel", "achieved": g1_gbs, "peak": peak, "unit": "GB/s",
+                         "frac": g1_gbs / peak, "traffic": None, "peak_kind": peak_kind,
+                         "us_per_launch": sum(g1_ms) / k_steps * 1e3},
+            "e2e": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(info.kernels) * args.steps,
+            "clocks": clocks,
+            "cpu_baseline": cpu,
+        }  # fmt: skip
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

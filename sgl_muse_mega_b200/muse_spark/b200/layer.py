@@ -41,12 +41,12 @@ def layer_shape(cfg: Config, case, rank: int):
 class LayerRank:
     """One rank's weights (moved to the device), buffers and bound launch of one layer."""
 
-    def __init__(self, lib: host.Library, module, case, rank: int, device, kv_rows: Optional[int] = None):
+    def __init__(self, lib: host.Library, module, case, rank: int, device, kv_rows: Optional[int] = None, tensors=None):
         cfg = case.cfg
         self.lib, self.case, self.rank, self.device = lib, case, rank, device
         self.shape = layer_shape(cfg, case, rank)
         self.consts = c = lib.layer_constants(self.shape)
-        t = case.ranks[rank]
+        t = tensors if tensors is not None else case.ranks[rank]
         dev = lambda x: None if x is None else x.to(device).contiguous()  # noqa: E731
         self.w = {k: dev(v) for k, v in vars(t).items()}
         M, H, P, E, K = case.rows, cfg.hidden, cfg.moe_hidden, cfg.experts, cfg.topk

@@ -27,30 +27,40 @@ from ..config import Config
 E2M1_RMS = math.sqrt(sum(v * v for v in (0, 0.5, 1, 1.5, 2, 3, 4, 6)) / 8)
 
 
+# Draws happen on this device: the CPU by default (oracle and kernels then see the same bytes); the benchmark sets a
+# CUDA device to draw its gigabytes of weights in place (a different stream of numbers, same distributions).
+_DEVICE = torch.device("cpu")
+
+
+def set_device(device) -> None:
+    global _DEVICE
+    _DEVICE = torch.device(device)
+
+
 def keyed(*key) -> torch.Generator:
-    g = torch.Generator()
+    g = torch.Generator(device=_DEVICE)
     g.manual_seed(int.from_bytes(hashlib.sha256(repr(key).encode()).digest()[:7], "little"))
     return g
 
 
 def normal(shape, std, dtype, *key):
-    return (torch.randn(shape, generator=keyed(*key)) * std).to(dtype)
+    return (torch.randn(shape, generator=keyed(*key), device=_DEVICE) * std).to(dtype)
 
 
 def uniform(shape, lo, hi, dtype, *key):
-    return (torch.rand(shape, generator=keyed(*key)) * (hi - lo) + lo).to(dtype)
+    return (torch.rand(shape, generator=keyed(*key), device=_DEVICE) * (hi - lo) + lo).to(dtype)
 
 
 def code_bytes(shape, *key):
-    return torch.randint(0, 256, shape, generator=keyed(*key), dtype=torch.uint8)
+    return torch.randint(0, 256, shape, generator=keyed(*key), dtype=torch.uint8, device=_DEVICE)
 
 
 def scale_bytes(shape, band: str, *key):
     g = keyed(*key)
     if band == "reference":
-        ex = torch.randint(6, 8, shape, generator=g, dtype=torch.uint8)
-        return (ex << 3) | torch.randint(0, 8, shape, generator=g, dtype=torch.uint8)
-    v = torch.randn(shape, generator=g).abs() * 0.02
+        ex = torch.randint(6, 8, shape, generator=g, dtype=torch.uint8, device=_DEVICE)
+        return (ex << 3) | torch.randint(0, 8, shape, generator=g, dtype=torch.uint8, device=_DEVICE)
+    v = torch.randn(shape, generator=g, device=_DEVICE).abs() * 0.02
     return v.clamp(max=448.0).to(torch.float8_e4m3fn).view(torch.uint8)
 
 
@@ -164,7 +174,7 @@ def layer_case(
     def norm_w(name, n):
         return uniform((n,), 0.8, 1.2, bf, seed, name, layer)
 
-    bias = torch.zeros(E, dtype=f32)
+    bias = torch.zeros(E, dtype=f32, device=_DEVICE)
     if bias_scale:
         bias = normal((E,), 1.0, f32, seed, "popularity", layer) * bias_scale
     if experts_subset is not None:
@@ -187,7 +197,7 @@ def layer_case(
         stream_in=normal((rows, H), 1.0, f32, seed, "stream_in", layer),
     )
     pos = torch.arange(ctx, ctx + rows)
-    cos_sin = None if (next_global or tail) else rope_rows(cfg, pos)
+    cos_sin = None if (next_global or tail) else rope_rows(cfg, pos).to(_DEVICE)
     if band == "reference":
         s2 = 1.0 / (math.sqrt(P) * E2M1_RMS * _ref_sf_rms())
         alphas = dict(
@@ -196,7 +206,8 @@ def layer_case(
             g2_alphas=uniform((E,), 0.9 * s2, 1.1 * s2, f32, seed, "g2a", layer),
         )
     else:
-        alphas = dict(g1_alphas=torch.ones(E), g1_scale_c=torch.ones(E), g2_alphas=torch.ones(E))
+        one = torch.ones(E, device=_DEVICE)
+        alphas = dict(g1_alphas=one, g1_scale_c=one.clone(), g2_alphas=one.clone())
     for r in only_ranks if only_ranks is not None else range(cfg.tp):
 
         def kv(name):
@@ -228,8 +239,8 @@ def layer_case(
                         code_bytes((E, nrows, k // 2), seed, name, layer, r),
                         scale_bytes((E, nrows, k // 16), band, seed, name + "_sf", layer, r),
                     )
-                q = torch.zeros(E, nrows, k // 2, dtype=torch.uint8)
-                s = torch.zeros(E, nrows, k // 16, dtype=torch.uint8)
+                q = torch.zeros(E, nrows, k // 2, dtype=torch.uint8, device=_DEVICE)
+                s = torch.zeros(E, nrows, k // 16, dtype=torch.uint8, device=_DEVICE)
                 n = len(experts_subset)
                 q[experts_subset.long()] = code_bytes((n, nrows, k // 2), seed, name, layer, r)
                 s[experts_subset.long()] = scale_bytes((n, nrows, k // 16), band, seed, name + "_sf", layer, r)
