@@ -197,6 +197,36 @@ typedef struct MkLayerBind {
 } MkLayerBind;
 int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind* bind, MkLaunch** out);
 
+// ---- layer 0's head: qkv GEMM + qk-norm + RoPE + K/V append as a stand-alone launch ----
+
+// Replaces abi.h:255-270 MkQkvBind / mk_qkv_bind (same names for the same operands); rows, heads and the scratch are
+// run-time fields here.
+typedef struct MkQkvBind {
+    uint64_t w;          // [qkv_row, hidden] bf16, rows [q | k | v | o-gate]
+    uint64_t x;          // [rows, hidden] bf16 normed input
+    uint64_t out;        // [rows, qkv_row] bf16
+    uint64_t cos_sin;    // [rows, 64] f32 {cos[32] | sin[32]}; 0 = no RoPE (global layer)
+    uint64_t cache_loc;  // i32 [rows] pool slots of the window's rows
+    uint64_t k_cache;    // [kv_rows, kv_heads x 64] bf16; 0 = no append
+    uint64_t v_cache;
+    double q_scale;
+    double eps;
+    int64_t hidden;
+    int64_t rows;
+    int64_t q_heads;
+    int64_t kv_heads;
+    uint64_t ws;         // ws_bytes of scratch (split-K partial sums and arrival counters), zeroed once by the caller
+    int64_t ws_bytes;
+} MkQkvBind;
+typedef struct MkQkvConstants {
+    int64_t qkv_row;       // 2 (q_heads + kv_heads) 64
+    int64_t kv_row_bytes;  // kv_heads x 64 bf16
+    int64_t ws_bytes;      // scratch the bind needs
+    int64_t kernels;       // kernels per launch
+} MkQkvConstants;
+int mk_qkv_constants(const MkQkvBind* bind, MkQkvConstants* out);
+int mk_qkv_bind(MkModule* module, const MkQkvBind* bind, MkLaunch** out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -75,7 +75,7 @@ def make(struct: str, **values) -> ctypes.Structure:
 
 EXPORTS = (
     "mk_last_error", "mk_module_load", "mk_module_free", "mk_launch", "mk_launch_step", "mk_launch_free",
-    "mk_launch_info", "mk_launch_status", "mk_layer_constants", "mk_layer_bind",
+    "mk_launch_info", "mk_launch_status", "mk_layer_constants", "mk_layer_bind", "mk_qkv_constants", "mk_qkv_bind",
 )  # fmt: skip
 
 
@@ -100,6 +100,8 @@ class Library:
         d.mk_launch_status.argtypes = [vp, ctypes.c_uint64, P(STRUCTS["MkLaunchStatus"])]
         d.mk_layer_constants.argtypes = [P(STRUCTS["MkLayerShape"]), P(STRUCTS["MkLayerConstants"])]
         d.mk_layer_bind.argtypes = [vp, P(STRUCTS["MkLayerShape"]), P(STRUCTS["MkLayerBind"]), P(vp)]
+        d.mk_qkv_constants.argtypes = [P(STRUCTS["MkQkvBind"]), P(STRUCTS["MkQkvConstants"])]
+        d.mk_qkv_bind.argtypes = [vp, P(STRUCTS["MkQkvBind"]), P(vp)]
 
     def check(self, rc: int, what: str) -> None:
         if rc != 0:
@@ -123,6 +125,17 @@ class Library:
             self.dll.mk_layer_bind(module.handle if module else None, ctypes.byref(shape), ctypes.byref(bind), ctypes.byref(out)),
             "mk_layer_bind",
         )
+        return Launch(self, out, module)
+
+
+    def qkv_constants(self, bind) -> ctypes.Structure:
+        c = STRUCTS["MkQkvConstants"]()
+        self.check(self.dll.mk_qkv_constants(ctypes.byref(bind), ctypes.byref(c)), "mk_qkv_constants")
+        return c
+
+    def qkv_bind(self, module: "Module | None", bind) -> "Launch":
+        out = ctypes.c_void_p()
+        self.check(self.dll.mk_qkv_bind(module.handle if module else None, ctypes.byref(bind), ctypes.byref(out)), "mk_qkv_bind")
         return Launch(self, out, module)
 
 

@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <new>
 
 #include "../../include/mk_abi.h"
@@ -436,12 +437,88 @@ int mk_launch_info(const MkLaunch* launch, MkLaunchInfo* out) {
     return 0;
 }
 
+// ---- layer 0's head ----
+
+static int qkv_check(const MkQkvBind* b, MkQkvConstants* c) {
+    MK_REQUIRE(b != nullptr, "bind is NULL");
+    MK_REQUIRE(b->rows >= 1 && b->rows <= kMaxRows, "rows %lld outside 1..16", (long long)b->rows);
+    MK_REQUIRE(b->q_heads >= 1 && b->kv_heads >= 1, "heads must be positive");
+    MK_REQUIRE(b->hidden >= 256 && b->hidden <= 8192 && gemm_ksplit(false, (int)b->hidden) > 0, "hidden %lld unsupported",
+               (long long)b->hidden);
+    c->qkv_row = 2 * (b->q_heads + b->kv_heads) * kHeadDim;
+    c->kv_row_bytes = b->kv_heads * kHeadDim * 2;
+    MK_REQUIRE(c->qkv_row / gemm_bn(false) <= 1024, "qkv row %lld too wide", (long long)c->qkv_row);
+    c->ws_bytes = (int64_t)align_up((size_t)16 * 16 * c->qkv_row * 4, 256) + 4096;
+    c->kernels = 2;
+    return 0;
+}
+
+// Fills the two argument records of the head from a bind and a scratch pointer (partials first, then the counters).
+static int qkv_fill(const MkQkvBind* b, const MkQkvConstants& c, unsigned char* scratch, GemmArgs& g, int& ks, RowopsArgs& r) {
+    memset(&g, 0, sizeof g);
+    g.w = (const void*)b->w;
+    g.x = (const void*)b->x;
+    g.M = (int)b->rows; g.N = (int)c.qkv_row; g.K = (int)b->hidden; g.ldw = g.ldx = (int)b->hidden;
+    g.partial = (float*)scratch;
+    g.counter = (unsigned*)(scratch + align_up((size_t)16 * 16 * c.qkv_row * 4, 256));
+    g.out[0] = (void*)b->out;
+    g.n_out = 1;
+    g.ldo = (int)c.qkv_row;
+    ks = gemm_ksplit(false, g.K);
+    MK_REQUIRE(ks > 0 && ks <= 16, "hidden %d has no supported K split", g.K);
+    r = RowopsArgs{(bf16*)b->out, (const float*)b->cos_sin, (const int*)b->cache_loc, (unsigned char*)b->k_cache,
+                   (unsigned char*)b->v_cache, (float)b->q_scale, (float)b->eps, (int)b->rows, (int)b->q_heads,
+                   (int)b->kv_heads, (int)c.qkv_row, (int)c.kv_row_bytes};
+    return 0;
+}
+
+int mk_qkv_constants(const MkQkvBind* bind, MkQkvConstants* out) {
+    MK_REQUIRE(out != nullptr, "out is NULL");
+    return qkv_check(bind, out);
+}
+
+int mk_qkv_bind(MkModule* module, const MkQkvBind* b, MkLaunch** out) {
+    MK_REQUIRE(out != nullptr, "out is NULL");
+    MkQkvConstants c;
+    if (qkv_check(b, &c)) return -1;
+    NEED(w); NEED(x); NEED(out); NEED(cache_loc); NEED(ws);
+    ALIGNED16(w); ALIGNED16(x); ALIGNED16(out); ALIGNED16(ws);
+    MK_REQUIRE((b->k_cache == 0) == (b->v_cache == 0), "k_cache and v_cache must be given together");
+    MK_REQUIRE(b->ws_bytes >= c.ws_bytes, "ws_bytes %lld smaller than the %lld this shape needs", (long long)b->ws_bytes,
+               (long long)c.ws_bytes);
+    MkLaunch* L = new (std::nothrow) MkLaunch();
+    MK_REQUIRE(L != nullptr, "out of host memory");
+    L->pack_only = module == nullptr;
+    L->device = module ? module->device : -1;
+    memset(&L->shape, 0, sizeof L->shape);
+    L->status = nullptr;
+    for (int i = 0; i < ST_COUNT; ++i) L->stage_on[i] = false;
+    L->stage_on[ST_QKV] = L->stage_on[ST_ROWOPS] = true;
+    if (qkv_fill(b, c, (unsigned char*)b->ws, L->qkv, L->ks_qkv, L->rowops)) {
+        delete L;
+        return -1;
+    }
+    // geometry fields mk_launch_info reads
+    L->oproj = L->pooler = L->router = L->unpool = L->qkv;
+    L->ks_oproj = L->ks_pooler = L->ks_unpool = L->ks_qkv;
+    L->ks_router = gemm_ksplit(true, L->qkv.K);
+    L->router.N = gemm_bn(true);
+    memset(&L->ex, 0, sizeof L->ex);
+    L->max_active = 0;
+    *out = L;
+    return 0;
+}
+
 int mk_launch_status(const MkLaunch* launch, uint64_t stream, MkLaunchStatus* out) {
     MK_REQUIRE(launch != nullptr && out != nullptr, "launch or out is NULL");
     MK_REQUIRE(!launch->pack_only, "a pack-only record has no device status");
     cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
     int host[8] = {0};
+    if (launch->status == nullptr) {
+        memset(out, 0, sizeof *out);
+        return 0;
+    }
     e = cudaMemcpy(host, launch->status, sizeof host, cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(status)");
     out->code = host[0];
