@@ -227,6 +227,19 @@ typedef struct MkQkvConstants {
 int mk_qkv_constants(const MkQkvBind* bind, MkQkvConstants* out);
 int mk_qkv_bind(MkModule* module, const MkQkvBind* bind, MkLaunch** out);
 
+// No counterpart in the reference. The same head (qkv GEMM + qk norm + RoPE + K/V append) for callers that must not
+// allocate: a serving process whose memory pool claimed the whole device at start-up, so that a later cudaMalloc fails or
+// fragments it, or a latency-critical section where an allocation would stall the device. Nothing is allocated, on the
+// device or through any library: the split-K partial sums and arrival counters live in a fixed 4 MiB + 4 KiB array that is
+// part of the library's device image (every GPU that loads the library holds it until the process exits). `ws` and
+// `ws_bytes` of the bind are ignored; every other field means what it means for mk_qkv_bind, and no MkLaunch is created:
+// the call enqueues the kernels on `stream` directly.
+// Limits: qkv_row = 2 (q_heads + kv_heads) 64 <= 4096 and hidden <= 8192; larger shapes are refused with an error.
+// The first call on a device looks up the array's address for that device (the device must be current) and should
+// therefore be made before any stream capture begins. All calls share the one array: two calls whose kernels overlap on
+// the GPU (different streams, no dependency) race on it; calls on one stream are safe back to back.
+int mk_qkv_launch_static(const MkQkvBind* bind, uint64_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -76,6 +76,7 @@ def make(struct: str, **values) -> ctypes.Structure:
 EXPORTS = (
     "mk_last_error", "mk_module_load", "mk_module_free", "mk_launch", "mk_launch_step", "mk_launch_free",
     "mk_launch_info", "mk_launch_status", "mk_layer_constants", "mk_layer_bind", "mk_qkv_constants", "mk_qkv_bind",
+    "mk_qkv_launch_static",
 )  # fmt: skip
 
 
@@ -102,6 +103,7 @@ class Library:
         d.mk_layer_bind.argtypes = [vp, P(STRUCTS["MkLayerShape"]), P(STRUCTS["MkLayerBind"]), P(vp)]
         d.mk_qkv_constants.argtypes = [P(STRUCTS["MkQkvBind"]), P(STRUCTS["MkQkvConstants"])]
         d.mk_qkv_bind.argtypes = [vp, P(STRUCTS["MkQkvBind"]), P(vp)]
+        d.mk_qkv_launch_static.argtypes = [P(STRUCTS["MkQkvBind"]), ctypes.c_uint64]
 
     def check(self, rc: int, what: str) -> None:
         if rc != 0:

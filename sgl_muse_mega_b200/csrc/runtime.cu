@@ -509,6 +509,67 @@ int mk_qkv_bind(MkModule* module, const MkQkvBind* b, MkLaunch** out) {
     return 0;
 }
 
+// ---- the head without any allocation: scratch inside the library's device image ----
+
+// 16 K chunks x 16 rows x 4096 columns of f32 partial sums, then 1024 arrival counters.
+static constexpr size_t kStaticPartialBytes = (size_t)16 * 16 * 4096 * 4;
+static constexpr size_t kStaticCounterBytes = 4096;
+static constexpr int64_t kStaticMaxQkvRow = 4096;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticPartialBytes + kStaticCounterBytes];
+// On the host the array's name is only a handle for the runtime, not a device address: the address each device uses is
+// looked up once with that device current and kept here.
+static constexpr int kStaticMaxDevices = 64;
+static unsigned char* g_static_addr[kStaticMaxDevices];
+static std::mutex g_static_mutex;
+
+static int static_scratch_for_current_device(unsigned char** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    MK_REQUIRE(dev >= 0 && dev < kStaticMaxDevices, "device ordinal %d beyond the %d this entry point tracks", dev, kStaticMaxDevices);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (g_static_addr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+        MK_REQUIRE(p != nullptr, "the static scratch has no address on device %d", dev);
+        e = gemm_prepare();
+        if (e != cudaSuccess) return cuda_fail(e, "gemm_prepare");
+        g_static_addr[dev] = (unsigned char*)p;
+    }
+    *out = g_static_addr[dev];
+    return 0;
+}
+
+int mk_qkv_launch_static(const MkQkvBind* b, uint64_t stream) {
+    MkQkvConstants c;
+    if (qkv_check(b, &c)) return -1;
+    NEED(w); NEED(x); NEED(out); NEED(cache_loc);
+    ALIGNED16(w); ALIGNED16(x); ALIGNED16(out);
+    MK_REQUIRE((b->k_cache == 0) == (b->v_cache == 0), "k_cache and v_cache must be given together");
+    MK_REQUIRE(c.qkv_row <= kStaticMaxQkvRow,
+               "qkv row of %lld columns exceeds the %lld the built-in scratch holds: use mk_qkv_bind with caller scratch",
+               (long long)c.qkv_row, (long long)kStaticMaxQkvRow);
+    unsigned char* scratch = nullptr;
+    if (static_scratch_for_current_device(&scratch)) return -1;
+    GemmArgs g;
+    RowopsArgs r;
+    int ks = 0;
+    if (qkv_fill(b, c, scratch, g, ks, r)) return -1;
+    MK_REQUIRE((unsigned char*)g.counter + kStaticCounterBytes <= scratch + sizeof g_static_scratch &&
+                   (size_t)(g.N / gemm_bn(false)) * 4 <= kStaticCounterBytes,
+               "internal: counters outside the built-in scratch");
+    // the array keeps whatever the previous call left: the arrival counters must start at zero (the partial sums are
+    // fully overwritten before they are read)
+    cudaError_t e = cudaMemsetAsync(g.counter, 0, kStaticCounterBytes, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(static counters)");
+    e = gemm_launch(g, false, ks, (cudaStream_t)stream, false);
+    if (e != cudaSuccess) return cuda_fail(e, "qkv GEMM launch");
+    e = rowops_launch(r, (cudaStream_t)stream, false);
+    if (e != cudaSuccess) return cuda_fail(e, "qkv row ops launch");
+    return 0;
+}
+
 int mk_launch_status(const MkLaunch* launch, uint64_t stream, MkLaunchStatus* out) {
     MK_REQUIRE(launch != nullptr && out != nullptr, "launch or out is NULL");
     MK_REQUIRE(!launch->pack_only, "a pack-only record has no device status");
