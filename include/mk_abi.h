@@ -155,6 +155,9 @@ typedef struct MkLayerBind {
     uint64_t w1_up_sf;
     uint64_t w2;          // NVFP4: [E, H_s, I/2] u8; bf16: [E, H_s, I] bf16
     uint64_t w2_sf;       // [E, H_s, I/16] u8
+    uint64_t w1_pack;     // NVFP4 tensor-core image of W1, [E, I_s/128, P/256, 36864] u8 (weights.pack_w1_fp4); 0 = absent
+    uint64_t w2_pack;     // image of W2, [E, H_s/128, I/256, 18432] u8 (weights.pack_w2_fp4). With both images bound the
+                          // experts run on tcgen05 and the plain w1_* / w2* tensors may be 0; without, on CUDA cores
     uint64_t g1_alphas;
     uint64_t g1_scale_c;
     uint64_t g2_alphas;

@@ -36,6 +36,7 @@ static int cuda_fail(cudaError_t e, const char* what) { return fail("%s: %s", wh
 
 struct MkModule {
     int device;
+    int sms;  // streaming multiprocessors: the persistent kernels launch one CTA per SM
 };
 
 enum Stage {
@@ -64,6 +65,9 @@ struct MkLaunch {
     float* rowscale;
     int* status;
     int max_active, slots_live;
+    bool use_umma;  // experts on tcgen05 (packed images bound) instead of CUDA cores
+    int sms;
+    mk::UmmaArgs umma_g1, umma_g2;
     bool stage_on[ST_COUNT];
 };
 
@@ -153,7 +157,9 @@ int mk_module_load(const void* image, uint64_t bytes, const char* code_prefetch_
     if (e != cudaSuccess) return cuda_fail(e, "gemm_prepare");
     e = experts_prepare();
     if (e != cudaSuccess) return cuda_fail(e, "experts_prepare");
-    MkModule* m = new (std::nothrow) MkModule{dev};
+    e = experts_umma_prepare();
+    if (e != cudaSuccess) return cuda_fail(e, "experts_umma_prepare");
+    MkModule* m = new (std::nothrow) MkModule{dev, prop.multiProcessorCount};
     MK_REQUIRE(m != nullptr, "out of host memory");
     *out = m;
     return 0;
@@ -197,12 +203,25 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     NEED(qkv_in); NEED(k_cache); NEED(v_cache); NEED(page_table); NEED(kv_len); NEED(x_attn);
     NEED(w_o); NEED(ar); NEED(branch); NEED(stream_in); NEED(alpha); NEED(beta); NEED(prenorm_w); NEED(stream_out); NEED(h3); NEED(h3f);
     NEED(w_p); NEED(pool_ag); NEED(w_r); NEED(logits); NEED(expert_bias); NEED(topk_idx32); NEED(topk_w); NEED(gamma); NEED(q);
-    NEED(w1_gate); NEED(w1_up); NEED(w2); NEED(z); NEED(zb); NEED(gamma_p1); NEED(y);
+    NEED(z); NEED(zb); NEED(gamma_p1); NEED(y);
+    MK_REQUIRE((b->w1_pack == 0) == (b->w2_pack == 0), "w1_pack and w2_pack must be bound together");
+    const bool use_umma = b->w1_pack != 0;
+    if (use_umma) {
+        MK_REQUIRE(fp4, "the packed tensor-core images are NVFP4: a bf16 layer cannot bind them");
+        MK_REQUIRE(I_s % 128 == 0 && H_s % 128 == 0 && P % 256 == 0 && I % 256 == 0 && P <= 4096 && I <= 4096,
+                   "the tensor-core expert path needs I/ranks and P/ranks multiples of 128 and P, I multiples of 256 up to 4096");
+        ALIGNED16(w1_pack); ALIGNED16(w2_pack);
+    } else {
+        NEED(w1_gate); NEED(w1_up); NEED(w2);
+    }
     NEED(w_up); NEED(unpool_ag); NEED(c_alpha); NEED(c_beta); NEED(c_pre_w); NEED(c_post_w); NEED(c_stream_out); NEED(h3q);
     NEED(ws); NEED(status);
     if (fp4) {
-        NEED(sf); NEED(x_scale); NEED(w1_gate_sf); NEED(w1_up_sf); NEED(w2_sf); NEED(g1_alphas); NEED(g1_scale_c); NEED(g2_alphas);
+        NEED(sf); NEED(x_scale); NEED(g1_alphas); NEED(g1_scale_c); NEED(g2_alphas);
         NEED(z_sf); NEED(z_ex);
+        if (!use_umma) {
+            NEED(w1_gate_sf); NEED(w1_up_sf); NEED(w2_sf);
+        }
     }
     if (!tail) {
         NEED(w_qkv); NEED(qkv_out); NEED(cache_loc); NEED(next_k_cache); NEED(next_v_cache);
@@ -349,6 +368,34 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     ex.w2_sf = (const unsigned char*)b->w2_sf;
     ex.g2_alphas = (const float*)b->g2_alphas;
     MK_REQUIRE(g1_smem(P) <= 200 * 1024 && g2_smem(I) <= 200 * 1024, "expert rows exceed shared memory");
+    L->use_umma = use_umma;
+    L->sms = module ? module->sms : 148;
+    if (use_umma) {
+        for (int g2 = 0; g2 < 2; ++g2) {
+            UmmaArgs& u = g2 ? L->umma_g2 : L->umma_g1;
+            memset(&u, 0, sizeof u);
+            u.rt = L->rt;
+            u.K = g2 ? I : P;
+            u.NB = (g2 ? H_s : I_s) / 128;
+            u.P = P; u.I = I; u.I_s = I_s; u.H_s = H_s; u.rank = (int)s.rank; u.topk = K;
+            u.wpack = (const unsigned char*)(g2 ? b->w2_pack : b->w1_pack);
+            u.bq = g2 ? (const unsigned char*)b->z : (const unsigned char*)b->q;
+            u.bsf = g2 ? L->z_sfd : (const unsigned char*)b->sf;
+            u.x_scale = (const float*)b->x_scale;
+            u.g1_alphas = (const float*)b->g1_alphas;
+            u.g1_scale_c = (const float*)b->g1_scale_c;
+            u.rowscale = L->rowscale;
+            u.g2_alphas = (const float*)b->g2_alphas;
+            for (int i = 0; i < ex.n_peer; ++i) {
+                u.z_peer[i] = ex.z_peer[i];
+                u.zsf_peer[i] = ex.zsf_peer[i];
+                u.zex_peer[i] = ex.zex_peer[i];
+                u.zb_peer[i] = ex.zb_peer[i];
+            }
+            u.n_peer = ex.n_peer;
+            u.status = L->status;
+        }
+    }
     *out = L;
     guard.l = nullptr;
     return 0;
@@ -369,12 +416,16 @@ static int run_stage(const MkLaunch* L, int st, cudaStream_t s, bool pdl) {
         case ST_TABLES:
             e = route_tables_launch(L->topk.ids, L->topk.E, L->topk.k, L->combine.b_live, L->rt, s, pdl);
             break;
-        case ST_G1: e = g1_launch(L->ex, L->max_active, s, pdl); break;
+        case ST_G1:
+            e = L->use_umma ? experts_umma_launch(L->umma_g1, false, L->sms, s, pdl) : g1_launch(L->ex, L->max_active, s, pdl);
+            break;
         case ST_HROW:
             e = hrow_launch((const unsigned char*)L->bind.z_sf, (const signed char*)L->bind.z_ex, (int)L->shape.inter / 16,
                             L->slots_live, (int)L->consts.slots, L->z_sfd, L->rowscale, s, pdl);
             break;
-        case ST_G2: e = g2_launch(L->ex, L->max_active, s, pdl); break;
+        case ST_G2:
+            e = L->use_umma ? experts_umma_launch(L->umma_g2, true, L->sms, s, pdl) : g2_launch(L->ex, L->max_active, s, pdl);
+            break;
         case ST_COMBINE: e = combine_launch(L->combine, (int)L->shape.rows, s, pdl); break;
         case ST_UNPOOL: e = gemm_launch(L->unpool, false, L->ks_unpool, s, pdl); break;
         case ST_CROSS_NORM: e = resid_norm_launch(L->cross_norm, s, pdl); break;

@@ -109,5 +109,30 @@ cudaError_t experts_prepare();
 cudaError_t g1_launch(const ExpertArgs& a, int max_active, cudaStream_t s, bool pdl);
 cudaError_t g2_launch(const ExpertArgs& a, int max_active, cudaStream_t s, bool pdl);
 
+// The tensor-core expert kernels (experts_umma.cu): one record per phase (g1 or g2).
+struct UmmaArgs {
+    const RouteTables* rt;
+    int K;   // contraction length: P for g1, I for g2 (multiple of 256, at most 4096)
+    int NB;  // 128-row blocks per expert: I_s / 128 (g1) or H_s / 128 (g2)
+    int P, I, I_s, H_s, rank, topk;
+    const unsigned char* wpack;  // [E][NB][K / 256][stage bytes] packed weight image
+    const unsigned char* bq;     // B rows: g1 xq [M, P/2]; g2 z [slots, I/2]
+    const unsigned char* bsf;    // their e4m3 scales: g1 x_sf [M, P/16]; g2 z_sfd [slots, I/16]
+    const float* x_scale;        // g1
+    const float* g1_alphas;
+    const float* g1_scale_c;
+    const float* rowscale;       // g2: 2^e_row per slot
+    const float* g2_alphas;
+    unsigned char* z_peer[kMaxRanks];
+    unsigned char* zsf_peer[kMaxRanks];
+    signed char* zex_peer[kMaxRanks];
+    bf16* zb_peer[kMaxRanks];
+    int n_peer;
+    int* status;
+};
+size_t experts_umma_smem(bool g2);
+cudaError_t experts_umma_prepare();
+cudaError_t experts_umma_launch(const UmmaArgs& a, bool g2, int grid, cudaStream_t s, bool pdl);
+
 
 }  // namespace mk

@@ -19,6 +19,7 @@ import torch
 
 from ...common import host
 from ..config import Config
+from . import weights
 
 # stage groups between which every rank must have finished before any rank continues (the exchanges)
 STAGE_GROUPS = ((0, 3), (3, 2), (5, 5), (10, 2), (12, 2), (14, 3))
@@ -41,7 +42,11 @@ def layer_shape(cfg: Config, case, rank: int):
 class LayerRank:
     """One rank's weights (moved to the device), buffers and bound launch of one layer."""
 
-    def __init__(self, lib: host.Library, module, case, rank: int, device, kv_rows: Optional[int] = None, tensors=None):
+    def __init__(self, lib: host.Library, module, case, rank: int, device, kv_rows: Optional[int] = None, tensors=None,
+                 tensor_cores: bool = True, keep_plain_experts: bool = True):  # fmt: skip
+        """``tensor_cores``: bind the packed NVFP4 images when the shape has whole 128-row tiles (the tcgen05 expert
+        kernels); otherwise, or when False, the experts run on the general CUDA-core kernels from the plain tensors.
+        ``keep_plain_experts`` False drops the plain expert tensors once the images exist (halves the expert memory)."""
         cfg = case.cfg
         self.lib, self.case, self.rank, self.device = lib, case, rank, device
         self.shape = layer_shape(cfg, case, rank)
@@ -50,6 +55,17 @@ class LayerRank:
         dev = lambda x: None if x is None else x.to(device).contiguous()  # noqa: E731
         self.w = {k: dev(v) for k, v in vars(t).items()}
         M, H, P, E, K = case.rows, cfg.hidden, cfg.moe_hidden, cfg.experts, cfg.topk
+        whole_tiles = (cfg.inter_rank % 128 == 0 and cfg.moe_hidden_rank % 128 == 0 and P % 256 == 0
+                       and cfg.moe_inter % 256 == 0 and P <= 4096 and cfg.moe_inter <= 4096)  # fmt: skip
+        self.tensor_cores = bool(tensor_cores and not case.bf16 and whole_tiles)
+        self.w1_pack = self.w2_pack = None
+        if self.tensor_cores:
+            w = self.w
+            self.w1_pack = weights.pack_w1_fp4(w["gate_q"], w["gate_sf"], w["up_q"], w["up_sf"])
+            self.w2_pack = weights.pack_w2_fp4(w["w2_q"], w["w2_sf"])
+            if not keep_plain_experts:
+                for k in ("gate_q", "gate_sf", "up_q", "up_sf", "w2_q", "w2_sf"):
+                    w[k] = None
         bf, f32, u8, i32 = torch.bfloat16, torch.float32, torch.uint8, torch.int32
 
         def z(shape, dtype):
@@ -112,7 +128,8 @@ class LayerRank:
             topk_idx32=o["ids"], topk_w=o["w"], route_scale=cfg.route_scale, gamma=w["pre_gamma"], eps=case.pre_eps,
             q=o["xq"], sf=o["x_sf"], x_scale=o["x_scale"],
             w1_gate=w["gate_q"] if fp4 else w["gate"], w1_gate_sf=w["gate_sf"], w1_up=w["up_q"] if fp4 else w["up"],
-            w1_up_sf=w["up_sf"], w2=w["w2_q"] if fp4 else w["w2"], w2_sf=w["w2_sf"], g1_alphas=w["g1_alphas"],
+            w1_up_sf=w["up_sf"], w2=w["w2_q"] if fp4 else w["w2"], w2_sf=w["w2_sf"], w1_pack=self.w1_pack,
+            w2_pack=self.w2_pack, g1_alphas=w["g1_alphas"],
             g1_scale_c=w["g1_scale_c"], g2_alphas=w["g2_alphas"], z=self.z, z_sf=self.z_sf, z_ex=self.z_ex, zb=self.zb,
             z_peer=peer("z"), zsf_peer=peer("z_sf"), zex_peer=peer("z_ex"), zb_peer=peer("zb"),
             gamma_p1=w["gamma_p1"], y=o["y"], w_up=w["unpooler"], unpool_ag=self.unpool_ag,
@@ -158,13 +175,14 @@ class LayerRank:
 class LayerWorld:
     """Every rank of the world on one device, exchange buffers wired as peers (see the module docstring)."""
 
-    def __init__(self, case, device, lib: Optional[host.Library] = None, ranks: Optional[list] = None, b_live: int = 0):
+    def __init__(self, case, device, lib: Optional[host.Library] = None, ranks: Optional[list] = None, b_live: int = 0,
+                 tensor_cores: bool = True):  # fmt: skip
         self.lib = lib or host.library()
         self.case, self.device = case, device
         with torch.cuda.device(device):
             self.module = self.lib.load()
         n = case.cfg.tp
-        self.ranks = [LayerRank(self.lib, self.module, case, r, device) for r in range(n)]
+        self.ranks = [LayerRank(self.lib, self.module, case, r, device, tensor_cores=tensor_cores) for r in range(n)]
         for r in self.ranks:
             r.bind(self.ranks, b_live)
 

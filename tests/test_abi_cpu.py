@@ -94,3 +94,32 @@ def test_tail_and_bf16_variants_drop_stages(lib):
     case = synthetic.layer_case(cfg, **kw)
     rec = L.LayerRank(lib, None, case, 1, torch.device("cpu")).bind()
     assert rec.info().kernels == 17 - 3  # no h-row view (bf16), no successor qkv + rowops (tail)
+
+
+def test_weight_images_round_trip_and_layout():
+    """The tensor-core weight images invert exactly, and a byte lands where the kernel's descriptors expect it."""
+    from sgl_muse_mega_b200.muse_spark.b200 import weights as W
+
+    g = torch.Generator().manual_seed(5)
+    e, i_s, p, h_s, i = 3, 256, 512, 128, 768
+    gq, uq = (torch.randint(0, 256, (e, i_s, p // 2), generator=g, dtype=torch.uint8) for _ in range(2))
+    gs, us = (torch.randint(0, 127, (e, i_s, p // 16), generator=g, dtype=torch.uint8) for _ in range(2))
+    pack = W.pack_w1_fp4(gq, gs, uq, us)
+    assert pack.shape == (e, i_s // 128, p // 256, W.W1_STAGE)
+    for a, b in zip(W.unpack_w1_fp4(pack), (gq, gs, uq, us)):
+        assert torch.equal(a, b)
+    wq = torch.randint(0, 256, (e, h_s, i // 2), generator=g, dtype=torch.uint8)
+    ws = torch.randint(0, 127, (e, h_s, i // 16), generator=g, dtype=torch.uint8)
+    p2 = W.pack_w2_fp4(wq, ws)
+    assert p2.shape == (e, 1, 3, W.W2_STAGE)
+    for a, b in zip(W.unpack_w2_fp4(p2), (wq, ws)):
+        assert torch.equal(a, b)
+    # spot checks of the byte addresses: expert 1, block 1, K chunk 1; tile row r, logical 16-byte chunk j, byte t
+    ex, blk, kc, r, j, t = 1, 1, 1, 77, 5, 9
+    off = (r // 8) * 1024 + (r % 8) * 128 + ((j ^ (r % 8)) * 16) + t
+    assert pack[ex, blk, kc, off] == gq[ex, blk * 128 + r, kc * 128 + j * 16 + t]
+    assert pack[ex, blk, kc, W.TILE_BYTES + off] == uq[ex, blk * 128 + r, kc * 128 + j * 16 + t]
+    block, grp = 2, 3  # K64 block of the chunk, 16-element group inside it
+    n, gq4 = r % 32, r // 32
+    sf_off = 2 * W.TILE_BYTES + block * 512 + n * 16 + gq4 * 4 + grp
+    assert pack[ex, blk, kc, sf_off] == gs[ex, blk * 128 + r, kc * 16 + block * 4 + grp]

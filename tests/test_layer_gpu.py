@@ -18,15 +18,49 @@ def device():
     return torch.device("cuda:0")
 
 
-@pytest.mark.parametrize("name", list(CASES))
-def test_layer_parity(name, device, golden_dir):
+def _paths():
+    """Every golden case on the default expert path (tcgen05 for NVFP4 shapes with whole 128-row tiles) and the NVFP4
+    cases again on the general CUDA-core expert kernels."""
+    out = []
+    for name, (_, kw) in CASES.items():
+        out.append((name, True))
+        if not kw.get("bf16"):
+            out.append((name, False))
+    return out
+
+
+@pytest.mark.parametrize("name,tensor_cores", _paths())
+def test_layer_parity(name, tensor_cores, device, golden_dir):
     cfg, kw = CASES[name]
     case = synthetic.layer_case(cfg, **kw)
-    world = L.LayerWorld(case, device)
+    world = L.LayerWorld(case, device, tensor_cores=tensor_cores)
+    if not kw.get("bf16"):
+        assert all(r.tensor_cores == tensor_cores for r in world.ranks), "the case did not take the expert path under test"
     world.run_interleaved()
     torch.cuda.synchronize()
+    for r in world.ranks:
+        st = r.launch_record.status(torch.cuda.current_stream().cuda_stream)
+        assert st.code == 0, f"rank {r.rank}: device status {st.code} at {st.stage} (block {st.block}, observed {st.observed})"
     golden = torch.load(golden_dir / f"{name}.pt")
     check_world(world, sorted({0, cfg.tp - 1}), golden=golden)
+
+
+def test_expert_paths_agree_bitwise(device):
+    """The tcgen05 expert kernels and the CUDA-core expert kernels produce the same h planes and the same zb, bit for
+    bit, from the same routed rows (both accumulate exact products in f32 and round once)."""
+    cfg, kw = CASES["small_fp4_swa_tp2"]
+    case = synthetic.layer_case(cfg, **kw)
+    a = L.LayerWorld(case, device, tensor_cores=False)
+    b = L.LayerWorld(case, device, tensor_cores=True)
+    for w in (a, b):
+        w.run_interleaved()
+    torch.cuda.synchronize()
+    for ra, rb in zip(a.ranks, b.ranks):
+        assert torch.equal(ra.o["ids"], rb.o["ids"]) and torch.equal(ra.o["xq"], rb.o["xq"])
+        for pa, pb in zip(ra.h_planes(), rb.h_planes()):
+            assert (pa == pb).float().mean() > 0.999
+        za, zb = ra.zb.view(torch.bfloat16).float(), rb.zb.view(torch.bfloat16).float()
+        assert ((za - zb).norm() / za.norm()).item() < 2e-3
 
 
 def test_b_live_pads(device, golden_dir):
