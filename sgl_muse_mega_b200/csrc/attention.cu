@@ -189,24 +189,59 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs a) {
 // One warp per (token, query head): merge the splits in split order, normalise, RMS norm, sigmoid gate.
 __global__ void __launch_bounds__(256) attn_combine_kernel(const AttnArgs a) {
     griddep_wait();
+    griddep_launch();
     const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (w >= a.M * a.qh) return;
     const int tok = w / a.qh, head = w % a.qh;
     const int kvhead = head / a.G, r = tok * a.G + head % a.G;
     const float* base = a.ws + ((size_t)kvhead * a.splits * a.R + r) * 66;
     const size_t stride = (size_t)a.R * 66;
+    // the (m, l) pairs of the splits live in the lanes (split s in lane s % 32, register s / 32): all loads independent
+    constexpr int kPer = 4;  // splits <= 128
+    float ms_[kPer], ls_[kPer];
     float mx = -1e30f;
-    for (int s = 0; s < a.splits; ++s) mx = fmaxf(mx, base[s * stride + 64]);
-    float L = 0.f, o0 = 0.f, o1 = 0.f;
-    for (int s = 0; s < a.splits; ++s) {
-        const float* p = base + s * stride;
-        const float l = p[65];
-        if (l == 0.f) continue;
-        const float sc = exp2f(p[64] - mx);
-        L += l * sc;
-        const float2 v = *(const float2*)(p + 2 * lane);
-        o0 += v.x * sc;
-        o1 += v.y * sc;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+        const int s = lane + 32 * i;
+        ms_[i] = -1e30f;
+        ls_[i] = 0.f;
+        if (s < a.splits) {
+            const float2 ml = *(const float2*)(base + s * stride + 64);
+            ms_[i] = ml.x;
+            ls_[i] = ml.y;
+        }
+        mx = fmaxf(mx, ms_[i]);
+    }
+    mx = warp_max(mx);
+    float L = 0.f;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+        ms_[i] = ls_[i] == 0.f ? 0.f : exp2f(ms_[i] - mx);  // now the split's scale (0 for an empty split)
+        L += ls_[i] * ms_[i];
+    }
+    L = warp_sum(L);
+    // O = sum over the splits, in split order, of O_s x scale_s: 8 independent loads per batch
+    float o0 = 0.f, o1 = 0.f;
+    for (int s0 = 0; s0 < a.splits; s0 += 8) {
+        float2 v[8];
+        float sc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int s = s0 + j;
+            float scj = 0.f;
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                const float t = __shfl_sync(0xffffffffu, ms_[i], s & 31);
+                if (i == (s >> 5)) scj = t;
+            }
+            sc[j] = s < a.splits ? scj : 0.f;
+            v[j] = sc[j] != 0.f ? *(const float2*)(base + s * stride + 2 * lane) : make_float2(0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            o0 += v[j].x * sc[j];
+            o1 += v[j].y * sc[j];
+        }
     }
     const float inv = 1.0f / L;
     const float x0 = o0 * inv, x1 = o1 * inv;

@@ -1,78 +1,113 @@
 // Row kernels of the layer: everything that is not a weight stream. Each works on the window's <= 16 rows in f32 with
 // the bf16 rounding points of the reference's contract (test/reference/muse_spark.py:335-435,587-635).
+// They are latency bound (16 rows of work), so each is shaped for few dependent memory round trips: 16-byte loads, every
+// load of a pass independent of the others, one block-wide reduction per norm.
 #include "stages.h"
 
 namespace mk {
 
 static __device__ __forceinline__ float inv_sqrt(float x) { return 1.0f / sqrtf(x); }
 
+static __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 x = __bfloat1622float2(p[i]);
+        f[2 * i] = x.x;
+        f[2 * i + 1] = x.y;
+    }
+}
+static __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint4 v;
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return v;
+}
+
 // ---- all-reduce consume + post norm + gated residual + pre norm ------------------------------------------------------
 // mode 0 (post-attention): branch = bf16(sum over ranks of the bf16 partials, rank order, f32); v = branch
 // mode 1 (cross-layer):    v = gathered unpooler row x post_w
 // stream' = fma(alpha, stream, scaled), normed = bf16((stream' rstd) pre_w)       (muse_spark.py:335-357)
-
-constexpr int kNormThreads = 1024;
-constexpr int kNormPer = 8;  // H <= 8192
-
-__global__ void __launch_bounds__(kNormThreads) resid_norm_kernel(const NormArgs a) {
+// One CTA per row, H / 8 threads, 8 consecutive columns per thread.
+__global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
     __shared__ float red[33];
     griddep_wait();
-    const int row = blockIdx.x, tid = threadIdx.x;
-    float v[kNormPer];
+    griddep_launch();
+    const int row = blockIdx.x, c0 = threadIdx.x * 8;
+    const size_t off = (size_t)row * a.H + c0;
+    float v[8];
+    if (a.mode == 0) {
+        uint4 part[kMaxRanks];
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+            if (r < a.ranks) part[r] = *(const uint4*)(a.src + ((size_t)r * a.M + row) * a.H + c0);
+        unpack8(part[0], v);
+#pragma unroll
+        for (int r = 1; r < kMaxRanks; ++r)
+            if (r < a.ranks) {
+                float f[8];
+                unpack8(part[r], f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] += f[i];
+            }
+        const uint4 b = pack8(v);
+        *(uint4*)(a.branch + off) = b;
+        unpack8(b, v);
+    } else {
+        float w[8];
+        unpack8(*(const uint4*)(a.src + off), v);
+        unpack8(*(const uint4*)(a.post_w + c0), w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= w[i];
+    }
+    const float4 s0 = *(const float4*)(a.stream_in + off), s1 = *(const float4*)(a.stream_in + off + 4);
+    const float4 al0 = *(const float4*)(a.alpha + c0), al1 = *(const float4*)(a.alpha + c0 + 4);
+    const float4 be0 = *(const float4*)(a.beta + c0), be1 = *(const float4*)(a.beta + c0 + 4);
+    float pw[8];
+    unpack8(*(const uint4*)(a.pre_w + c0), pw);
+    const float st[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    const float al[8] = {al0.x, al0.y, al0.z, al0.w, al1.x, al1.y, al1.z, al1.w};
+    const float be[8] = {be0.x, be0.y, be0.z, be0.w, be1.x, be1.y, be1.z, be1.w};
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < kNormPer; ++i) {
-        const int c = tid + i * kNormThreads;
-        v[i] = 0.f;
-        if (c < a.H) {
-            if (a.mode == 0) {
-                float acc = __bfloat162float(a.src[(size_t)row * a.H + c]);
-                for (int r = 1; r < a.ranks; ++r) acc += __bfloat162float(a.src[((size_t)r * a.M + row) * a.H + c]);
-                const bf16 b = __float2bfloat16_rn(acc);
-                a.branch[(size_t)row * a.H + c] = b;
-                v[i] = __bfloat162float(b);
-            } else {
-                v[i] = __bfloat162float(a.src[(size_t)row * a.H + c]) * __bfloat162float(a.post_w[c]);
-            }
-            ss += v[i] * v[i];
-        }
-    }
+    for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
     const float post_rstd = inv_sqrt(block_sum(ss, red) / (float)a.H + 1e-8f);
-    float ns[kNormPer];
+    float ns[8];
     ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < kNormPer; ++i) {
-        const int c = tid + i * kNormThreads;
-        ns[i] = 0.f;
-        if (c < a.H) {
-            const float beta = a.beta[c];
-            const float scaled = a.mode == 0 ? (beta * post_rstd) * v[i] : beta * (v[i] * post_rstd);
-            ns[i] = fmaf(a.alpha[c], a.stream_in[(size_t)row * a.H + c], scaled);
-            ss += ns[i] * ns[i];
-        }
+    for (int i = 0; i < 8; ++i) {
+        const float scaled = a.mode == 0 ? (be[i] * post_rstd) * v[i] : be[i] * (v[i] * post_rstd);
+        ns[i] = fmaf(al[i], st[i], scaled);
+        ss += ns[i] * ns[i];
     }
     const float pre_rstd = inv_sqrt(block_sum(ss, red) / (float)a.H + 1e-5f);
+    *(float4*)(a.stream_out + off) = make_float4(ns[0], ns[1], ns[2], ns[3]);
+    *(float4*)(a.stream_out + off + 4) = make_float4(ns[4], ns[5], ns[6], ns[7]);
+    float h[8];
 #pragma unroll
-    for (int i = 0; i < kNormPer; ++i) {
-        const int c = tid + i * kNormThreads;
-        if (c < a.H) {
-            a.stream_out[(size_t)row * a.H + c] = ns[i];
-            const bf16 h = __float2bfloat16_rn((ns[i] * pre_rstd) * __bfloat162float(a.pre_w[c]));
-            a.normed[(size_t)row * a.H + c] = h;
-            if (a.normed_f32) a.normed_f32[(size_t)row * a.H + c] = __bfloat162float(h);
-        }
+    for (int i = 0; i < 8; ++i) h[i] = (ns[i] * pre_rstd) * pw[i];
+    const uint4 hb = pack8(h);
+    *(uint4*)(a.normed + off) = hb;
+    if (a.normed_f32) {
+        unpack8(hb, h);
+        *(float4*)(a.normed_f32 + off) = make_float4(h[0], h[1], h[2], h[3]);
+        *(float4*)(a.normed_f32 + off + 4) = make_float4(h[4], h[5], h[6], h[7]);
     }
 }
 
-// ---- top-k routing -----------------------------------------------------------------------------------------------------
-// One warp per row: s = sigmoid(mult x logit) (f64, rounded to f32), sel = s + bias, k rounds of arg-max with the smaller
-// id winning ties, weights = ((sel - bias) / (sum in selection order + 1e-15)) x route_scale   (muse_spark.py:378-404)
-
+// ---- routing (top-k + route tables) and pre-expert norm + quantisation in one launch ---------------------------------------
+// Block 0: one warp per row selects the top-k, then the block builds the route tables. Blocks 1..M: one row each of the
+// pre-expert norm + dynamic NVFP4 quantisation (independent of the routing).
+//
+// top-k: s = sigmoid(mult x logit) (f64, rounded to f32), sel = s + bias, k rounds of arg-max with the smaller id winning
+// ties, weights = ((sel - bias) / (sum in selection order + 1e-15)) x route_scale          (muse_spark.py:378-404)
+// tables: slots of the live rows grouped by expert: active experts ascending, slots of one expert in slot order.
+// nq: n = bf16(bf16(x rsqrt(mean x^2 + eps)) gamma); NVFP4: x_scale = max(amax, 1e-10) / 2688, per 16:
+// sf = e4m3(max(gamax, 1e-10) / 6 / x_scale), code = e2m1(n / max(sf x_scale, 1e-10))          (muse_spark.py:407-435)
 constexpr int kTopkPer = 32;  // E <= 1024
 
-__global__ void __launch_bounds__(32) topk_kernel(const TopkArgs a) {
-    griddep_wait();
-    const int row = blockIdx.x, lane = threadIdx.x;
+static __device__ void topk_row(const TopkArgs& a, int row, int lane, int* s_ids) {
     float sel[kTopkPer];
 #pragma unroll
     for (int i = 0; i < kTopkPer; ++i) {
@@ -84,8 +119,7 @@ __global__ void __launch_bounds__(32) topk_kernel(const TopkArgs a) {
             sel[i] = s + a.bias[e];
         }
     }
-    float total = 0.f;
-    float mine = 0.f;  // lane j keeps the j-th selected (sel - bias)
+    float total = 0.f, mine = 0.f;
     int myid = 0;
     for (int j = 0; j < a.k; ++j) {
         float bv = -INFINITY;
@@ -93,7 +127,7 @@ __global__ void __launch_bounds__(32) topk_kernel(const TopkArgs a) {
 #pragma unroll
         for (int i = 0; i < kTopkPer; ++i) {
             const int e = lane + 32 * i;
-            if (sel[i] > bv) { bv = sel[i]; bi = e; }  // ascending e per lane: strict > keeps the smaller id
+            if (sel[i] > bv) { bv = sel[i]; bi = e; }  // ascending ids per lane: strict > keeps the smaller id
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -114,57 +148,99 @@ __global__ void __launch_bounds__(32) topk_kernel(const TopkArgs a) {
     if (lane < a.k) {
         a.ids[(size_t)row * a.k + lane] = myid;
         a.w[(size_t)row * a.k + lane] = (mine * inv) * a.route_scale;
+        s_ids[row * a.k + lane] = myid;
     }
 }
 
-// ---- pre-expert norm + dynamic NVFP4 quantisation ---------------------------------------------------------------------
-// n = bf16(bf16(x rsqrt(mean x^2 + eps)) gamma); NVFP4: x_scale = max(amax, 1e-10) / 2688, per 16:
-// sf = e4m3(max(gamax, 1e-10) / 6 / x_scale), code = e2m1(n / max(sf x_scale, 1e-10))           (muse_spark.py:407-435)
+static __device__ void route_tables(const int* s_ids, int E, int S, RouteTables* rt, int* cnt, int* first) {
+    const int tid = threadIdx.x, nt = blockDim.x;
+    for (int e = tid; e < E; e += nt) cnt[e] = 0;
+    __syncthreads();
+    int my_e = -1;
+    if (tid < S) {
+        my_e = s_ids[tid];
+        atomicAdd(&cnt[my_e], 1);
+    }
+    __syncthreads();
+    if (tid < 32) {
+        // exclusive scan of the counts over the experts, 32 experts per step; compaction of the active ones
+        int base = 0, nact = 0;
+        for (int e0 = 0; e0 < E; e0 += 32) {
+            const int e = e0 + tid, c = e < E ? cnt[e] : 0;
+            int incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (tid >= o) incl += t;
+            }
+            const unsigned act = __ballot_sync(0xffffffffu, c > 0);
+            if (e < E) first[e] = base + incl - c;
+            if (c > 0) {
+                const int pos = nact + __popc(act & ((1u << tid) - 1));
+                rt->act_e[pos] = e;
+                rt->act_off[pos] = base + incl - c;
+            }
+            base += __shfl_sync(0xffffffffu, incl, 31);
+            nact += __popc(act);
+        }
+        if (tid == 0) {
+            rt->act_off[nact] = base;
+            rt->n_active = nact;
+        }
+    }
+    __syncthreads();
+    if (tid < S) {
+        int before = 0;
+        for (int s = 0; s < tid; ++s) before += (s_ids[s] == my_e);
+        rt->slot[first[my_e] + before] = tid;
+    }
+}
 
-__global__ void __launch_bounds__(256) nq_kernel(const NqArgs a) {
-    __shared__ float red[33];
-    griddep_wait();
-    const int row = blockIdx.x, tid = threadIdx.x;
+static __device__ void nq_row(const NqArgs& a, int row, float* red) {
+    const int tid = threadIdx.x, nt = blockDim.x;
     const int groups = a.P / 16;
     const bf16* x = a.pooled + (size_t)row * a.P;
+    // one 16-element group per thread and pass (P / 16 <= blockDim for P <= 8192)
+    float n[16];
     float ss = 0.f;
-    for (int gi = tid; gi < groups; gi += 256) {
+    const bool own = tid < groups;
+    if (own) {
+        float g[16];
+        unpack8(*(const uint4*)(x + tid * 16), *(float(*)[8])g);
+        unpack8(*(const uint4*)(x + tid * 16 + 8), *(float(*)[8])(g + 8));
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-            const float v = __bfloat162float(x[gi * 16 + i]);
-            ss += v * v;
+            n[i] = g[i];
+            ss += g[i] * g[i];
         }
     }
+    (void)nt;
     const float rstd = inv_sqrt(block_sum(ss, red) / (float)a.P + a.eps);
-    float amax = 0.f;
-    for (int gi = tid; gi < groups; gi += 256) {
+    float gmax = 0.f;
+    if (own) {
+        float gm[16];
+        unpack8(*(const uint4*)(a.gamma + tid * 16), *(float(*)[8])gm);
+        unpack8(*(const uint4*)(a.gamma + tid * 16 + 8), *(float(*)[8])(gm + 8));
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-            const float v = __bfloat162float(x[gi * 16 + i]);
-            const float n = bf16_round(bf16_round(v * rstd) * __bfloat162float(a.gamma[gi * 16 + i]));
-            amax = fmaxf(amax, fabsf(n));
+            n[i] = bf16_round(bf16_round(n[i] * rstd) * gm[i]);
+            gmax = fmaxf(gmax, fabsf(n[i]));
         }
     }
-    amax = block_max(amax, red);
+    if (a.bf16_out) {
+        if (own) {
+            bf16* o = (bf16*)a.q + (size_t)row * a.P + tid * 16;
+            *(uint4*)o = pack8(*(float(*)[8])n);
+            *(uint4*)(o + 8) = pack8(*(float(*)[8])(n + 8));
+        }
+        return;
+    }
+    const float amax = block_max(gmax, red);
     const float kSixth = 1.0f / 6.0f, kInv2688 = 1.0f / 2688.0f;
     const float x_scale = fmaxf(amax, 1e-10f) * kInv2688;
     const float inv_x = 1.0f / x_scale;
-    if (tid == 0 && !a.bf16_out) a.x_scale[row] = x_scale;
-    for (int gi = tid; gi < groups; gi += 256) {
-        float n[16];
-        float gmax = 0.f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const float v = __bfloat162float(x[gi * 16 + i]);
-            n[i] = bf16_round(bf16_round(v * rstd) * __bfloat162float(a.gamma[gi * 16 + i]));
-            gmax = fmaxf(gmax, fabsf(n[i]));
-        }
-        if (a.bf16_out) {
-            bf16* o = (bf16*)a.q + (size_t)row * a.P + gi * 16;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float2bfloat16_rn(n[i]);
-            continue;
-        }
+    if (tid == 0) a.x_scale[row] = x_scale;
+    if (own) {
         const uint32_t sfb = float_to_e4m3((fmaxf(gmax, 1e-10f) * kSixth) * inv_x);
         const float out_scale = 1.0f / fmaxf(e4m3_to_float(sfb) * x_scale, 1e-10f);
         uint32_t lo = 0, hi = 0;
@@ -173,46 +249,33 @@ __global__ void __launch_bounds__(256) nq_kernel(const NqArgs a) {
             lo |= float_to_e2m1(n[i] * out_scale) << (4 * i);
             hi |= float_to_e2m1(n[8 + i] * out_scale) << (4 * i);
         }
-        *(uint2*)(a.q + (size_t)row * (a.P / 2) + gi * 8) = make_uint2(lo, hi);
-        a.sf[(size_t)row * groups + gi] = (unsigned char)sfb;
+        *(uint2*)(a.q + (size_t)row * (a.P / 2) + tid * 8) = make_uint2(lo, hi);
+        a.sf[(size_t)row * groups + tid] = (unsigned char)sfb;
     }
 }
 
-// ---- route tables (the front) -------------------------------------------------------------------------------------------
-// Slots of the live rows grouped by expert: active experts ascending, slots of one expert in slot order.
-__global__ void __launch_bounds__(128) route_tables_kernel(const int* ids, int E, int k, int b_live, RouteTables* rt) {
+struct RouteNqArgs {
+    TopkArgs topk;
+    NqArgs nq;
+    RouteTables* rt;
+    int b_live;
+};
+
+__global__ void __launch_bounds__(512) route_nq_kernel(const RouteNqArgs a) {
+    __shared__ float red[33];
+    __shared__ int s_ids[kMaxSlots];
     __shared__ int cnt[1024];
     __shared__ int first[1024];
     griddep_wait();
-    const int tid = threadIdx.x, S = b_live * k;
-    for (int e = tid; e < E; e += 128) cnt[e] = 0;
-    __syncthreads();
-    int my_e = -1;
-    if (tid < S) {
-        my_e = ids[tid];
-        atomicAdd(&cnt[my_e], 1);
+    griddep_launch();
+    if (blockIdx.x > 0) {
+        nq_row(a.nq, blockIdx.x - 1, red);
+        return;
     }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp < a.topk.M) topk_row(a.topk, warp, lane, s_ids);
     __syncthreads();
-    if (tid == 0) {
-        int na = 0, off = 0;
-        for (int e = 0; e < E; ++e) {
-            first[e] = off;
-            if (cnt[e] > 0) {
-                rt->act_e[na] = e;
-                rt->act_off[na] = off;
-                ++na;
-                off += cnt[e];
-            }
-        }
-        rt->act_off[na] = off;
-        rt->n_active = na;
-    }
-    __syncthreads();
-    if (tid < S) {
-        int before = 0;
-        for (int s = 0; s < tid; ++s) before += (ids[s] == my_e);
-        rt->slot[first[my_e] + before] = tid;
-    }
+    route_tables(s_ids, a.topk.E, a.b_live * a.topk.k, a.rt, cnt, first);
 }
 
 // ---- h row view: scales moved to the row's largest exponent ---------------------------------------------------------------
@@ -232,6 +295,7 @@ __global__ void __launch_bounds__(256) hrow_kernel(const unsigned char* z_sf, co
                                                    unsigned char* z_sfd, float* rowscale) {
     __shared__ float red[33];
     griddep_wait();
+    griddep_launch();
     const int slot = blockIdx.x, tid = threadIdx.x;
     if (slot >= slots_live) return;
     float mx = -1000.f;
@@ -247,43 +311,67 @@ __global__ void __launch_bounds__(256) hrow_kernel(const unsigned char* z_sf, co
 // ---- per-slot post norm + weighted combine ---------------------------------------------------------------------------------
 // xg = zb (gamma + 1); inv = 1 / sqrt(mean xg^2 + 1e-8); y = bf16(sum_j fma(w_j inv_j, xg_j, acc)), j ascending; rows past
 // b_live give 0                                                                             (muse_spark.py:587-598)
+// One CTA per row, P / 8 threads, 8 columns per thread; the k slot rows are read once and stay in registers.
+constexpr int kMaxTopk = 8;
 
-__global__ void __launch_bounds__(256) combine_kernel(const CombineArgs a) {
-    __shared__ float red[33];
-    __shared__ float sc[32];
+__global__ void __launch_bounds__(512) combine_kernel(const CombineArgs a) {
+    __shared__ float red[kMaxTopk][17];
+    __shared__ float sc[kMaxTopk];
     griddep_wait();
-    const int row = blockIdx.x, tid = threadIdx.x;
+    griddep_launch();
+    const int row = blockIdx.x, tid = threadIdx.x, c0 = tid * 8, warp = tid >> 5, lane = tid & 31;
+    const int nw = blockDim.x >> 5;
     if (row >= a.b_live) {
-        for (int c = tid; c < a.P; c += 256) a.y[(size_t)row * a.P + c] = __float2bfloat16_rn(0.f);
+        *(uint4*)(a.y + (size_t)row * a.P + c0) = make_uint4(0, 0, 0, 0);
         return;
     }
-    for (int j = 0; j < a.k; ++j) {
-        const bf16* z = a.zb + ((size_t)row * a.k + j) * a.P;
-        float ss = 0.f;
-        for (int c = tid; c < a.P; c += 256) {
-            const float xg = __bfloat162float(z[c]) * __bfloat162float(a.gamma_p1[c]);
-            ss += xg * xg;
+    float gp[8];
+    unpack8(*(const uint4*)(a.gamma_p1 + c0), gp);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j0 = 0; j0 < a.k; j0 += kMaxTopk) {
+        const int kk = min(kMaxTopk, a.k - j0);
+        uint4 raw[kMaxTopk];
+#pragma unroll
+        for (int j = 0; j < kMaxTopk; ++j)
+            if (j < kk) raw[j] = *(const uint4*)(a.zb + ((size_t)row * a.k + j0 + j) * a.P + c0);
+        float xg[kMaxTopk][8];
+#pragma unroll
+        for (int j = 0; j < kMaxTopk; ++j) {
+            float ss = 0.f;
+            if (j < kk) {
+                unpack8(raw[j], xg[j]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    xg[j][i] *= gp[i];
+                    ss += xg[j][i] * xg[j][i];
+                }
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) red[j][warp] = ss;
         }
-        const float ms = block_sum(ss, red) / (float)a.P;
-        if (tid == 0) sc[j] = a.w[(size_t)row * a.k + j] * (1.0f / sqrtf(ms + 1e-8f));
-    }
-    __syncthreads();
-    for (int c = tid; c < a.P; c += 256) {
-        const float gp = __bfloat162float(a.gamma_p1[c]);
-        float acc = 0.f;
-        for (int j = 0; j < a.k; ++j) {
-            const float xg = __bfloat162float(a.zb[((size_t)row * a.k + j) * a.P + c]) * gp;
-            acc = fmaf(sc[j], xg, acc);
+        __syncthreads();
+        if (tid < kMaxTopk && tid < kk) {
+            float s = 0.f;
+            for (int w = 0; w < nw; ++w) s += red[tid][w];
+            sc[tid] = a.w[(size_t)row * a.k + j0 + tid] * (1.0f / sqrtf(s / (float)a.P + 1e-8f));
         }
-        a.y[(size_t)row * a.P + c] = __float2bfloat16_rn(acc);
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < kMaxTopk; ++j)
+            if (j < kk) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] = fmaf(sc[j], xg[j][i], acc[i]);
+            }
+        __syncthreads();
     }
+    *(uint4*)(a.y + (size_t)row * a.P + c0) = pack8(acc);
 }
 
 // ---- qkv row ops: qk norm, q scale, interleaved-pair RoPE, KV append -----------------------------------------------------------
 // One warp per (row, head) over the q, k and v heads of the bf16 qkv row                    (muse_spark.py:601-635)
-
 __global__ void __launch_bounds__(256) rowops_kernel(const RowopsArgs a) {
     griddep_wait();
+    griddep_launch();
     const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     const int heads = a.qh + 2 * a.kvh;
     if (w >= a.M * heads) return;
@@ -313,8 +401,8 @@ __global__ void __launch_bounds__(256) rowops_kernel(const RowopsArgs a) {
 
 // ---- launch helpers -----------------------------------------------------------------------------------------------------------
 
-template <typename Kern, typename Args>
-static cudaError_t launch1(Kern kern, dim3 grid, dim3 block, cudaStream_t stream, bool pdl, const Args& args) {
+template <typename... KArgs, typename... Args>
+static cudaError_t launch1(void (*kern)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, bool pdl, Args... args) {
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -324,45 +412,22 @@ static cudaError_t launch1(Kern kern, dim3 grid, dim3 block, cudaStream_t stream
     cfg.stream = stream;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, args);
+    return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
 cudaError_t resid_norm_launch(const NormArgs& a, cudaStream_t s, bool pdl) {
-    return launch1(resid_norm_kernel, dim3(a.M), dim3(kNormThreads), s, pdl, a);
+    return launch1(resid_norm_kernel, dim3(a.M), dim3(a.H / 8), s, pdl, a);
 }
-cudaError_t topk_launch(const TopkArgs& a, cudaStream_t s, bool pdl) {
-    return launch1(topk_kernel, dim3(a.M), dim3(32), s, pdl, a);
-}
-cudaError_t nq_launch(const NqArgs& a, int M, cudaStream_t s, bool pdl) {
-    return launch1(nq_kernel, dim3(M), dim3(256), s, pdl, a);
-}
-cudaError_t route_tables_launch(const int* ids, int E, int k, int b_live, RouteTables* rt, cudaStream_t s, bool pdl) {
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(1);
-    cfg.blockDim = dim3(128);
-    cfg.stream = s;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, route_tables_kernel, ids, E, k, b_live, rt);
+cudaError_t route_nq_launch(const TopkArgs& t, const NqArgs& n, RouteTables* rt, int b_live, cudaStream_t s, bool pdl) {
+    RouteNqArgs a{t, n, rt, b_live};
+    return launch1(route_nq_kernel, dim3(1 + t.M), dim3(512), s, pdl, a);
 }
 cudaError_t hrow_launch(const unsigned char* z_sf, const signed char* z_ex, int groups, int slots_live, int slots,
                         unsigned char* z_sfd, float* rowscale, cudaStream_t s, bool pdl) {
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(slots);
-    cfg.blockDim = dim3(256);
-    cfg.stream = s;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, hrow_kernel, z_sf, z_ex, groups, slots_live, z_sfd, rowscale);
+    return launch1(hrow_kernel, dim3(slots), dim3(256), s, pdl, z_sf, z_ex, groups, slots_live, z_sfd, rowscale);
 }
 cudaError_t combine_launch(const CombineArgs& a, int M, cudaStream_t s, bool pdl) {
-    return launch1(combine_kernel, dim3(M), dim3(256), s, pdl, a);
+    return launch1(combine_kernel, dim3(M), dim3(a.P / 8), s, pdl, a);
 }
 cudaError_t rowops_launch(const RowopsArgs& a, cudaStream_t s, bool pdl) {
     const int warps = a.M * (a.qh + 2 * a.kvh);

@@ -91,8 +91,9 @@ static int check_shape(const MkLayerShape* s) {
     MK_REQUIRE(s->ranks == 1 || s->ranks == 2 || s->ranks == 4 || s->ranks == 8, "ranks %lld not 1/2/4/8", (long long)s->ranks);
     MK_REQUIRE(s->rank >= 0 && s->rank < s->ranks, "rank %lld outside the world", (long long)s->rank);
     MK_REQUIRE(s->node_ranks >= 1 && s->ranks % s->node_ranks == 0, "node_ranks %lld does not divide ranks", (long long)s->node_ranks);
-    MK_REQUIRE(s->hidden >= 256 && s->hidden <= 8192 && s->hidden % 128 == 0, "hidden %lld unsupported", (long long)s->hidden);
-    MK_REQUIRE(s->moe_hidden % (32 * s->node_ranks) == 0 && s->moe_hidden % (16 * s->ranks) == 0 && s->moe_hidden <= 6144,
+    MK_REQUIRE(s->hidden >= 256 && s->hidden <= 8192 && s->hidden % 256 == 0, "hidden %lld unsupported", (long long)s->hidden);
+    MK_REQUIRE(s->moe_hidden % (32 * s->node_ranks) == 0 && s->moe_hidden % (16 * s->ranks) == 0 && s->moe_hidden % 256 == 0 &&
+                   s->moe_hidden <= 4096,
                "moe_hidden %lld unsupported", (long long)s->moe_hidden);
     MK_REQUIRE(s->inter % (16 * s->ranks) == 0 && s->inter % 32 == 0 && s->inter <= 6144, "inter %lld unsupported", (long long)s->inter);
     MK_REQUIRE(s->hidden % (32 * s->node_ranks) == 0, "hidden %lld not divisible over the node group", (long long)s->hidden);
@@ -268,6 +269,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     L->slots_live = b_live * K;
     for (int i = 0; i < ST_COUNT; ++i) L->stage_on[i] = true;
     L->stage_on[ST_HROW] = fp4;
+    L->stage_on[ST_NQ] = L->stage_on[ST_TABLES] = false;
     L->stage_on[ST_QKV] = L->stage_on[ST_ROWOPS] = !tail;
 
     // attention
@@ -411,11 +413,12 @@ static int run_stage(const MkLaunch* L, int st, cudaStream_t s, bool pdl) {
         case ST_POST_NORM: e = resid_norm_launch(L->post_norm, s, pdl); break;
         case ST_POOLER: e = gemm_launch(L->pooler, false, L->ks_pooler, s, pdl); break;
         case ST_ROUTER: e = gemm_launch(L->router, true, L->ks_router, s, pdl); break;
-        case ST_TOPK: e = topk_launch(L->topk, s, pdl); break;
-        case ST_NQ: e = nq_launch(L->nq, (int)L->shape.rows, s, pdl); break;
-        case ST_TABLES:
-            e = route_tables_launch(L->topk.ids, L->topk.E, L->topk.k, L->combine.b_live, L->rt, s, pdl);
+        case ST_TOPK:  // top-k, route tables and the pre-expert norm + quantisation share one launch
+            e = route_nq_launch(L->topk, L->nq, L->rt, L->combine.b_live, s, pdl);
             break;
+        case ST_NQ:
+        case ST_TABLES:
+            break;  // folded into ST_TOPK's launch (the slots stay in the stage list: stage indices are ABI)
         case ST_G1:
             e = L->use_umma ? experts_umma_launch(L->umma_g1, false, L->sms, s, pdl) : g1_launch(L->ex, L->max_active, s, pdl);
             break;

@@ -11,9 +11,16 @@ namespace mk {
 
 typedef __nv_bfloat16 bf16;
 
-// Programmatic dependent launch: wait until the predecessor grid's writes are visible (no-op without the attribute).
-__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Programmatic dependent launch. `griddep_wait` blocks until the predecessor grid has completed and its writes are
+// visible, THEN lets the successor grid start launching: the successor's CTAs fill SMs as this grid's CTAs retire and run
+// their prologues (barrier setup, tensor-memory allocation, weight prefetch) under this grid's tail. Because the trigger
+// comes after the wait, a successor's prologue may read anything written two or more kernels back, but nothing of its
+// immediate predecessor before its own wait. Both are no-ops without the launch attribute.
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    griddep_launch();
+}
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
