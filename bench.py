@@ -270,6 +270,23 @@ def run_ours(args) -> None:
     g1_bytes = sum(byt[i % args.ring]["g1"] for i in range(k_steps))
     g1_gbs = g1_bytes / (sum(g1_ms) * 1e-3) / 1e9
 
+    # ---- per-stage breakdown (diagnostic): every stage launched alone between two events; serialised, so the sum
+    # exceeds the layer time measured above (no PDL overlap here)
+    n_st = len(L.STAGE_NAMES)
+    stage_ms = [0.0] * n_st
+    reps = max(4, min(args.steps, 24))
+    for i in range(reps):
+        lr = ring[i % args.ring]
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_st + 1)]
+        evs[0].record(stream)
+        for st in range(n_st):
+            lr.launch_record.step(s, st, 1)
+            evs[st + 1].record(stream)
+        stream.synchronize()
+        for st in range(n_st):
+            stage_ms[st] += evs[st].elapsed_time(evs[st + 1])
+    stage_us = {name: round(t / reps * 1e3, 2) for name, t in zip(L.STAGE_NAMES, stage_ms) if t > 0}
+
     # ---- end to end: host buffers in, host buffers out, through the same C-ABI launch -------------------------------
     M, H = args.rows, cfg.hidden
     h_qkv = torch.randn(M, cfg.qkv_row).bfloat16().pin_memory()
@@ -327,6 +344,7 @@ def run_ours(args) -> None:
                          "us_per_launch": sum(g1_ms) / k_steps * 1e3},
             "e2e": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(info.kernels) * args.steps,
+            "stage_us_serialised": stage_us,
             "clocks": clocks,
             "cpu_baseline": cpu,
         }  # fmt: skip

@@ -70,7 +70,7 @@ template <bool G2>
 __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) {
     constexpr int TILES = G2 ? 1 : 2;
     constexpr uint32_t STAGE = TILES * (kTileBytes + kSfBytes);
-    constexpr int S = G2 ? 8 : 4;
+    constexpr int S = G2 ? 10 : 5;
     constexpr uint32_t IDESC = idesc_nvf4(128, 16);
 
     extern __shared__ unsigned char smem_raw[];
@@ -203,28 +203,49 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
                 }
             }
             bar_sync(1, 128);
-            // codes -> swizzled K-major tile rows (rows >= n_tok are zero)
-            const int row_bytes = a.K / 2;
-            for (int idx = te; idx < kMaxRows * KCH * 8; idx += 128) {
-                const int tk = idx / (KCH * 8), rem = idx - tk * (KCH * 8), kc = rem >> 3, j = rem & 7;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (tk < n_tok) v = *(const uint4*)(a.bq + (size_t)m.row[tk] * row_bytes + kc * 128 + j * 16);
-                *(uint4*)(xs + kc * 2048 + (tk >> 3) * 1024 + (tk & 7) * 128 + ((j ^ (tk & 7)) << 4)) = v;
+            // codes -> swizzled K-major tile rows. Only the n_tok live rows are written: a stale row only feeds accumulator
+            // columns that no epilogue reads (the columns of an MMA are independent). All loads of a batch are issued
+            // before the first store, so a batch costs one memory round trip, not one per chunk.
+            const int row_bytes = a.K / 2, per_row = KCH * 8, total = n_tok * per_row;
+            for (int base = 0; base < total; base += 128 * 8) {
+                uint4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int idx = base + u * 128 + te;
+                    if (idx < total) {
+                        const int tk = idx / per_row, rem = idx - tk * per_row;
+                        v[u] = *(const uint4*)(a.bq + (size_t)m.row[tk] * row_bytes + rem * 16);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int idx = base + u * 128 + te;
+                    if (idx < total) {
+                        const int tk = idx / per_row, rem = idx - tk * per_row, kc = rem >> 3, j = rem & 7;
+                        *(uint4*)(xs + kc * 2048 + (tk >> 3) * 1024 + (tk & 7) * 128 + ((j ^ (tk & 7)) << 4)) = v[u];
+                    }
+                }
             }
             // row scales -> tensor memory: lane l = row l, one word (4 e4m3) per K64 block at a column stride of 4;
-            // every epilogue warp writes its own 32-lane quadrant with the same words
+            // every epilogue warp writes its own 32-lane quadrant with the same words. The row's words are fetched in one
+            // batch of 16-byte loads, then stored 16 columns at a time.
             const bool live = lane < n_tok;
             const uint32_t* sfrow = (const uint32_t*)(a.bsf + (size_t)(live ? m.row[lane] : 0) * (a.K / 16));
-            for (int b0 = 0; b0 < KCH * 4; b0 += 4) {
-                uint32_t r[16];
-                const uint4 w = live ? *(const uint4*)(sfrow + b0) : make_uint4(0, 0, 0, 0);
+            uint4 w[kMaxKChunks];
 #pragma unroll
-                for (int k = 0; k < 16; ++k) r[k] = 0;
-                r[0] = w.x;
-                r[4] = w.y;
-                r[8] = w.z;
-                r[12] = w.w;
-                tmem_st16(tmem + lane_base + kColSfb + b0 * 4, r);
+            for (int c = 0; c < kMaxKChunks; ++c) w[c] = (live && c < KCH) ? *(const uint4*)(sfrow + c * 4) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int c = 0; c < kMaxKChunks; ++c) {
+                if (c < KCH) {
+                    uint32_t r[16];
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) r[k] = 0;
+                    r[0] = w[c].x;
+                    r[4] = w[c].y;
+                    r[8] = w[c].z;
+                    r[12] = w[c].w;
+                    tmem_st16(tmem + lane_base + kColSfb + c * 16, r);
+                }
             }
             tmem_st_wait();
             tc_fence_before();
@@ -313,7 +334,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
 
 size_t experts_umma_smem(bool g2) {
     const size_t stage = (g2 ? 1 : 2) * (size_t)(kTileBytes + kSfBytes);
-    const int S = g2 ? 8 : 4;
+    const int S = g2 ? 10 : 5;
     return 1024 + S * stage + kMaxKChunks * 2048 + (16 * 129 + 1) * 4 + 2 * sizeof(UnitMeta) + 16 + (2 * S + 5) * 8 + 16;
 }
 

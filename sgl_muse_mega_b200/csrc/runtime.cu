@@ -53,7 +53,9 @@ struct MkLaunch {
     MkLayerBind bind;
     mk::AttnArgs attn;
     mk::GemmArgs oproj, pooler, router, unpool, qkv;
-    int ks_oproj, ks_pooler, ks_router, ks_unpool, ks_qkv;
+    mk::GemmGwsArgs head_gemm;  // the stand-alone qkv head (split-K through global scratch)
+    int head_ks;
+    bool is_head;
     mk::NormArgs post_norm, cross_norm;
     mk::TopkArgs topk;
     mk::NqArgs nq;
@@ -100,9 +102,7 @@ static int check_shape(const MkLayerShape* s) {
     MK_REQUIRE(s->q_heads >= 1 && s->kv_heads >= 1 && s->q_heads % s->kv_heads == 0, "heads %lld / %lld", (long long)s->q_heads, (long long)s->kv_heads);
     MK_REQUIRE(s->rows * (s->q_heads / s->kv_heads) <= 128, "rows x heads per kv head exceeds 128");
     MK_REQUIRE(s->window >= 0, "negative window");
-    MK_REQUIRE(gemm_ksplit(false, (int)s->hidden) > 0 && gemm_ksplit(true, (int)s->hidden) > 0, "hidden %lld has no K split", (long long)s->hidden);
-    MK_REQUIRE(gemm_ksplit(false, (int)s->moe_hidden) > 0, "moe_hidden %lld has no K split", (long long)s->moe_hidden);
-    MK_REQUIRE(gemm_ksplit(false, (int)(s->q_heads * kHeadDim)) > 0, "o_proj K %lld has no K split", (long long)(s->q_heads * kHeadDim));
+    MK_REQUIRE(s->experts % 16 == 0 && s->hidden % 64 == 0, "experts / hidden are not whole GEMM tiles");
     return 0;
 }
 
@@ -156,6 +156,8 @@ int mk_module_load(const void* image, uint64_t bytes, const char* code_prefetch_
     MK_REQUIRE(prop.major == 10, "device %d is compute capability %d.%d; the kernels are built for sm_100a", dev, prop.major, prop.minor);
     e = gemm_prepare();
     if (e != cudaSuccess) return cuda_fail(e, "gemm_prepare");
+    e = gemm_gws_prepare();
+    if (e != cudaSuccess) return cuda_fail(e, "gemm_gws_prepare");
     e = experts_prepare();
     if (e != cudaSuccess) return cuda_fail(e, "experts_prepare");
     e = experts_umma_prepare();
@@ -270,29 +272,28 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     for (int i = 0; i < ST_COUNT; ++i) L->stage_on[i] = true;
     L->stage_on[ST_HROW] = fp4;
     L->stage_on[ST_NQ] = L->stage_on[ST_TABLES] = false;
-    L->stage_on[ST_QKV] = L->stage_on[ST_ROWOPS] = !tail;
+    L->stage_on[ST_QKV] = !tail;
+    L->stage_on[ST_ROWOPS] = false;  // folded into the qkv GEMM's epilogue
 
     // attention
     L->attn = AttnArgs{(const bf16*)b->qkv_in, (const unsigned char*)b->k_cache, (const unsigned char*)b->v_cache,
                        (const long long*)b->page_table, (const int*)b->kv_len, attn_ws, (bf16*)b->x_attn,
                        M, qh, kvh, G, R, (int)c.qkv_row, (int)s.window, (int)c.attn_splits};
     // GEMMs
-    auto gemm = [&](GemmArgs& g, int& ks, bool wf32, uint64_t w, uint64_t x, int N, int Kd, int ldw) -> int {
+    (void)gpart;
+    (void)gcnt;
+    auto gemm = [&](GemmArgs& g, int mode, bool wf32, uint64_t w, uint64_t x, int N, int Kd, int ldw) -> int {
         memset(&g, 0, sizeof g);
         g.w = (const void*)w;
         g.x = (const void*)x;
         g.M = M; g.N = N; g.K = Kd; g.ldw = ldw; g.ldx = Kd;
-        g.partial = gpart;
-        g.counter = gcnt;
-        g.out_f32 = 0;
-        ks = gemm_ksplit(wf32, Kd);
-        MK_REQUIRE(ks > 0 && ks <= 16, "K %d has no supported split", Kd);
-        MK_REQUIRE(N % gemm_bn(wf32) == 0, "N %d is not a multiple of the %d-row tile", N, gemm_bn(wf32));
-        MK_REQUIRE(N / gemm_bn(wf32) <= 1024, "N %d has too many tiles", N);
+        g.mode = mode;
+        g.status = L->status;
+        MK_REQUIRE(gemm_plan(wf32, mode, N, Kd, module ? module->sms : 148, &g.wn, &g.ksplit) == 0, "GEMM [%d x %d] has no tile / K-split plan", N, Kd);
         return 0;
     };
     // o_proj: x_attn [M, qh 64] . w_o [H, qh 64]^T -> this rank's slot of every present rank's workspace
-    if (gemm(L->oproj, L->ks_oproj, false, b->w_o, b->x_attn, H, qh * kHeadDim, qh * kHeadDim)) return -1;
+    if (gemm(L->oproj, 0, false, b->w_o, b->x_attn, H, qh * kHeadDim, qh * kHeadDim)) return -1;
     {
         void* dst[kMaxRanks];
         const int n = peers(b->ar_peer, b->ar, dst, 0, (int)s.ranks);
@@ -302,27 +303,37 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
         L->oproj.col0 = 0;
     }
     // pooler: the node block of rows [j P/nr, (j+1) P/nr) -> the node's gather rows
-    if (gemm(L->pooler, L->ks_pooler, false, b->w_p + (uint64_t)jnode * (P / nr) * H * 2, b->h3, P / nr, H, H)) return -1;
+    if (gemm(L->pooler, 0, false, b->w_p + (uint64_t)jnode * (P / nr) * H * 2, b->h3, P / nr, H, H)) return -1;
     L->pooler.n_out = peers(b->pool_ag_peer, b->pool_ag, L->pooler.out, node0, nr);
     L->pooler.ldo = P;
     L->pooler.col0 = jnode * (P / nr);
     // router: f32 weights through tf32, f32 activations, f32 logits (replicated on every rank)
-    if (gemm(L->router, L->ks_router, true, b->w_r, b->h3f, E, H, H)) return -1;
+    if (gemm(L->router, 0, true, b->w_r, b->h3f, E, H, H)) return -1;
     L->router.out[0] = (void*)b->logits;
     L->router.n_out = 1;
     L->router.ldo = E;
     L->router.out_f32 = 1;
     // unpooler: node block of [H, P]
-    if (gemm(L->unpool, L->ks_unpool, false, b->w_up + (uint64_t)jnode * (H / nr) * P * 2, b->y, H / nr, P, P)) return -1;
+    if (gemm(L->unpool, 0, false, b->w_up + (uint64_t)jnode * (H / nr) * P * 2, b->y, H / nr, P, P)) return -1;
     L->unpool.n_out = peers(b->unpool_ag_peer, b->unpool_ag, L->unpool.out, node0, nr);
     L->unpool.ldo = H;
     L->unpool.col0 = jnode * (H / nr);
     // successor's qkv
     if (!tail) {
-        if (gemm(L->qkv, L->ks_qkv, false, b->w_qkv, b->h3q, (int)c.qkv_row, H, H)) return -1;
+        if (gemm(L->qkv, 1, false, b->w_qkv, b->h3q, (int)c.qkv_row, H, H)) return -1;
         L->qkv.out[0] = (void*)b->qkv_out;
         L->qkv.n_out = 1;
         L->qkv.ldo = (int)c.qkv_row;
+        // the row ops ride the GEMM's epilogue (one head per tile)
+        L->qkv.cos_sin = s.next_rope ? (const float*)b->cos_sin : nullptr;
+        L->qkv.cache_loc = (const int*)b->cache_loc;
+        L->qkv.k_cache = (unsigned char*)b->next_k_cache;
+        L->qkv.v_cache = (unsigned char*)b->next_v_cache;
+        L->qkv.q_scale = (float)b->q_scale;
+        L->qkv.eps = (float)b->qkv_eps;
+        L->qkv.qh = qh;
+        L->qkv.kvh = kvh;
+        L->qkv.kv_row_bytes = (int)c.kv_row_bytes;
     }
     // norms
     L->post_norm = NormArgs{0, H, (int)s.ranks, (const bf16*)b->ar, (bf16*)b->branch, (const float*)b->stream_in,
@@ -409,10 +420,10 @@ static int run_stage(const MkLaunch* L, int st, cudaStream_t s, bool pdl) {
     switch (st) {
         case ST_ATTN_SPLIT: e = attn_split_launch(L->attn, s, pdl); break;
         case ST_ATTN_COMBINE: e = attn_combine_launch(L->attn, s, pdl); break;
-        case ST_OPROJ: e = gemm_launch(L->oproj, false, L->ks_oproj, s, pdl); break;
+        case ST_OPROJ: e = gemm_launch(L->oproj, false, s, pdl); break;
         case ST_POST_NORM: e = resid_norm_launch(L->post_norm, s, pdl); break;
-        case ST_POOLER: e = gemm_launch(L->pooler, false, L->ks_pooler, s, pdl); break;
-        case ST_ROUTER: e = gemm_launch(L->router, true, L->ks_router, s, pdl); break;
+        case ST_POOLER: e = gemm_launch(L->pooler, false, s, pdl); break;
+        case ST_ROUTER: e = gemm_launch(L->router, true, s, pdl); break;
         case ST_TOPK:  // top-k, route tables and the pre-expert norm + quantisation share one launch
             e = route_nq_launch(L->topk, L->nq, L->rt, L->combine.b_live, s, pdl);
             break;
@@ -430,9 +441,11 @@ static int run_stage(const MkLaunch* L, int st, cudaStream_t s, bool pdl) {
             e = L->use_umma ? experts_umma_launch(L->umma_g2, true, L->sms, s, pdl) : g2_launch(L->ex, L->max_active, s, pdl);
             break;
         case ST_COMBINE: e = combine_launch(L->combine, (int)L->shape.rows, s, pdl); break;
-        case ST_UNPOOL: e = gemm_launch(L->unpool, false, L->ks_unpool, s, pdl); break;
+        case ST_UNPOOL: e = gemm_launch(L->unpool, false, s, pdl); break;
         case ST_CROSS_NORM: e = resid_norm_launch(L->cross_norm, s, pdl); break;
-        case ST_QKV: e = gemm_launch(L->qkv, false, L->ks_qkv, s, pdl); break;
+        case ST_QKV:
+            e = L->is_head ? gemm_gws_launch(L->head_gemm, false, L->head_ks, s, pdl) : gemm_launch(L->qkv, false, s, pdl);
+            break;
         case ST_ROWOPS: e = rowops_launch(L->rowops, s, pdl); break;
         default: return fail("stage %d does not exist", st);
     }
@@ -466,17 +479,22 @@ int mk_launch_info(const MkLaunch* launch, MkLaunchInfo* out) {
     int kernels = 0;
     for (int i = 0; i < ST_COUNT; ++i) kernels += L->stage_on[i];
     int64_t grid = 0, smem = 0;
-    auto gg = [&](const GemmArgs& g, bool f32, int ks) {
-        const int64_t n = (int64_t)(g.N / gemm_bn(f32)) * ks;
+    auto gg = [&](const GemmArgs& g, bool f32) {
+        const int64_t n = gemm_grid(g);
         if (n > grid) grid = n;
-        const int64_t sm = (int64_t)gemm_smem(f32, g.K, ks);
+        const int64_t sm = (int64_t)gemm_smem(g, f32);
         if (sm > smem) smem = sm;
     };
-    gg(L->oproj, false, L->ks_oproj);
-    gg(L->pooler, false, L->ks_pooler);
-    gg(L->router, true, L->ks_router);
-    gg(L->unpool, false, L->ks_unpool);
-    if (!L->shape.tail) gg(L->qkv, false, L->ks_qkv);
+    if (L->is_head) {
+        grid = (int64_t)(L->head_gemm.N / gemm_gws_bn(false)) * L->head_ks;
+        smem = (int64_t)gemm_gws_smem(false, L->head_gemm.K, L->head_ks);
+    } else {
+        gg(L->oproj, false);
+        gg(L->pooler, false);
+        gg(L->router, true);
+        gg(L->unpool, false);
+        if (!L->shape.tail) gg(L->qkv, false);
+    }
     const int64_t g1 = (int64_t)(L->ex.I_s / 16) * L->max_active, g2 = (int64_t)(L->ex.H_s / 16) * L->max_active;
     if (g1 > grid) grid = g1;
     if (g2 > grid) grid = g2;
@@ -497,18 +515,18 @@ static int qkv_check(const MkQkvBind* b, MkQkvConstants* c) {
     MK_REQUIRE(b != nullptr, "bind is NULL");
     MK_REQUIRE(b->rows >= 1 && b->rows <= kMaxRows, "rows %lld outside 1..16", (long long)b->rows);
     MK_REQUIRE(b->q_heads >= 1 && b->kv_heads >= 1, "heads must be positive");
-    MK_REQUIRE(b->hidden >= 256 && b->hidden <= 8192 && gemm_ksplit(false, (int)b->hidden) > 0, "hidden %lld unsupported",
+    MK_REQUIRE(b->hidden >= 256 && b->hidden <= 8192 && gemm_gws_ksplit(false, (int)b->hidden) > 0, "hidden %lld unsupported",
                (long long)b->hidden);
     c->qkv_row = 2 * (b->q_heads + b->kv_heads) * kHeadDim;
     c->kv_row_bytes = b->kv_heads * kHeadDim * 2;
-    MK_REQUIRE(c->qkv_row / gemm_bn(false) <= 1024, "qkv row %lld too wide", (long long)c->qkv_row);
+    MK_REQUIRE(c->qkv_row / gemm_gws_bn(false) <= 1024, "qkv row %lld too wide", (long long)c->qkv_row);
     c->ws_bytes = (int64_t)align_up((size_t)16 * 16 * c->qkv_row * 4, 256) + 4096;
     c->kernels = 2;
     return 0;
 }
 
 // Fills the two argument records of the head from a bind and a scratch pointer (partials first, then the counters).
-static int qkv_fill(const MkQkvBind* b, const MkQkvConstants& c, unsigned char* scratch, GemmArgs& g, int& ks, RowopsArgs& r) {
+static int qkv_fill(const MkQkvBind* b, const MkQkvConstants& c, unsigned char* scratch, GemmGwsArgs& g, int& ks, RowopsArgs& r) {
     memset(&g, 0, sizeof g);
     g.w = (const void*)b->w;
     g.x = (const void*)b->x;
@@ -518,7 +536,7 @@ static int qkv_fill(const MkQkvBind* b, const MkQkvConstants& c, unsigned char* 
     g.out[0] = (void*)b->out;
     g.n_out = 1;
     g.ldo = (int)c.qkv_row;
-    ks = gemm_ksplit(false, g.K);
+    ks = gemm_gws_ksplit(false, g.K);
     MK_REQUIRE(ks > 0 && ks <= 16, "hidden %d has no supported K split", g.K);
     r = RowopsArgs{(bf16*)b->out, (const float*)b->cos_sin, (const int*)b->cache_loc, (unsigned char*)b->k_cache,
                    (unsigned char*)b->v_cache, (float)b->q_scale, (float)b->eps, (int)b->rows, (int)b->q_heads,
@@ -548,15 +566,11 @@ int mk_qkv_bind(MkModule* module, const MkQkvBind* b, MkLaunch** out) {
     L->status = nullptr;
     for (int i = 0; i < ST_COUNT; ++i) L->stage_on[i] = false;
     L->stage_on[ST_QKV] = L->stage_on[ST_ROWOPS] = true;
-    if (qkv_fill(b, c, (unsigned char*)b->ws, L->qkv, L->ks_qkv, L->rowops)) {
+    L->is_head = true;
+    if (qkv_fill(b, c, (unsigned char*)b->ws, L->head_gemm, L->head_ks, L->rowops)) {
         delete L;
         return -1;
     }
-    // geometry fields mk_launch_info reads
-    L->oproj = L->pooler = L->router = L->unpool = L->qkv;
-    L->ks_oproj = L->ks_pooler = L->ks_unpool = L->ks_qkv;
-    L->ks_router = gemm_ksplit(true, L->qkv.K);
-    L->router.N = gemm_bn(true);
     memset(&L->ex, 0, sizeof L->ex);
     L->max_active = 0;
     *out = L;
@@ -587,8 +601,8 @@ static int static_scratch_for_current_device(unsigned char** out) {
         e = cudaGetSymbolAddress(&p, g_static_scratch);
         if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
         MK_REQUIRE(p != nullptr, "the static scratch has no address on device %d", dev);
-        e = gemm_prepare();
-        if (e != cudaSuccess) return cuda_fail(e, "gemm_prepare");
+        e = gemm_gws_prepare();
+        if (e != cudaSuccess) return cuda_fail(e, "gemm_gws_prepare");
         g_static_addr[dev] = (unsigned char*)p;
     }
     *out = g_static_addr[dev];
@@ -606,18 +620,18 @@ int mk_qkv_launch_static(const MkQkvBind* b, uint64_t stream) {
                (long long)c.qkv_row, (long long)kStaticMaxQkvRow);
     unsigned char* scratch = nullptr;
     if (static_scratch_for_current_device(&scratch)) return -1;
-    GemmArgs g;
+    GemmGwsArgs g;
     RowopsArgs r;
     int ks = 0;
     if (qkv_fill(b, c, scratch, g, ks, r)) return -1;
     MK_REQUIRE((unsigned char*)g.counter + kStaticCounterBytes <= scratch + sizeof g_static_scratch &&
-                   (size_t)(g.N / gemm_bn(false)) * 4 <= kStaticCounterBytes,
+                   (size_t)(g.N / gemm_gws_bn(false)) * 4 <= kStaticCounterBytes,
                "internal: counters outside the built-in scratch");
     // the array keeps whatever the previous call left: the arrival counters must start at zero (the partial sums are
     // fully overwritten before they are read)
     cudaError_t e = cudaMemsetAsync(g.counter, 0, kStaticCounterBytes, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(static counters)");
-    e = gemm_launch(g, false, ks, (cudaStream_t)stream, false);
+    e = gemm_gws_launch(g, false, ks, (cudaStream_t)stream, false);
     if (e != cudaSuccess) return cuda_fail(e, "qkv GEMM launch");
     e = rowops_launch(r, (cudaStream_t)stream, false);
     if (e != cudaSuccess) return cuda_fail(e, "qkv row ops launch");

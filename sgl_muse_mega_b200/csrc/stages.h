@@ -88,11 +88,32 @@ struct ExpertArgs {
     bf16* zb_peer[kMaxRanks];
 };
 
-int gemm_ksplit(bool wf32, int K);
-int gemm_bn(bool wf32);
-size_t gemm_smem(bool wf32, int K, int ksplit);
+// gemm.cu: cluster split-K, no global scratch. gemm_plan fills wn / ksplit of a GEMM (-1: the shape has no valid plan).
+int gemm_plan(bool wf32, int mode, int N, int K, int max_ctas, int* wn_out, int* ksplit_out);
+size_t gemm_smem(const GemmArgs& a, bool wf32);
+int gemm_grid(const GemmArgs& a);
 cudaError_t gemm_prepare();
-cudaError_t gemm_launch(const GemmArgs& a, bool wf32, int ksplit, cudaStream_t stream, bool pdl);
+cudaError_t gemm_launch(const GemmArgs& a, bool wf32, cudaStream_t stream, bool pdl);
+
+// gemm_gws.cu: split-K through global scratch (the stand-alone qkv head).
+struct GemmGwsArgs {
+    const void* w;        // [N, K] row-major weights (bf16 or f32)
+    const void* x;        // [M, K] row-major activations (bf16, or f32 for f32 weights)
+    int M, N, K;
+    int ldw, ldx;         // row strides in elements
+    float* partial;       // [ksplit, 16, N] f32 partial sums (ksplit > 1)
+    unsigned* counter;    // [N / BN] arrival counters (zero between launches)
+    void* out[kMaxRanks]; // destinations, each [M, ldo]
+    int n_out;
+    int ldo;              // row stride of out in elements
+    int col0;             // first output column of this N range
+    int out_f32;          // 1: f32 outputs, 0: bf16
+};
+int gemm_gws_ksplit(bool wf32, int K);
+int gemm_gws_bn(bool wf32);
+size_t gemm_gws_smem(bool wf32, int K, int ksplit);
+cudaError_t gemm_gws_prepare();
+cudaError_t gemm_gws_launch(const GemmGwsArgs& a, bool wf32, int ksplit, cudaStream_t stream, bool pdl);
 cudaError_t attn_split_launch(const AttnArgs& a, cudaStream_t stream, bool pdl);
 cudaError_t attn_combine_launch(const AttnArgs& a, cudaStream_t stream, bool pdl);
 cudaError_t resid_norm_launch(const NormArgs& a, cudaStream_t s, bool pdl);
