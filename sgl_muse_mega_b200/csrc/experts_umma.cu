@@ -11,14 +11,22 @@
 //     [tile 0: 128 rows x 128 B][tile 1 (g1 only)][scales tile 0: 4 x 512 B][scales tile 1]
 // with the tiles already in the 128-byte-swizzle canonical layout and the scales in the 32 x 16 B image that
 // tcgen05.cp.32x128b.warpx4 moves into tensor memory (byte n 16 + g 4 + k of a 512-B tile = scale of tile row 32 g + n,
-// 16-element group k of that K64 block). One stage = one bulk copy = 36 KiB (g1) or 18 KiB (g2), no tensor map.
+// 16-element group k of that K64 block). One stage = 36 KiB (g1) or 18 KiB (g2) of bulk copies, no tensor map.
 //
 // Roles (256 threads): warp 0 lane 0 streams weight stages (full/empty mbarriers), warp 1 lane 0 copies the scales to
-// tensor memory and issues the MMAs, warp 2 owns the tensor-memory allocation, warps 4-7 stage the routed rows (codes
-// into swizzled shared memory, their scales into tensor memory with tcgen05.st) and run the epilogues from tensor memory:
+// tensor memory and issues the MMAs, warps 2-3 stage the routed rows two units ahead (codes into swizzled shared memory,
+// their scale words and the unit's metadata beside them; warp 2 also owns the tensor-memory allocation), warps 4-7 move
+// the staged scale words into tensor memory with tcgen05.st and run the epilogues from tensor memory:
 // g1: gate/up -> bf16 -> SwiGLU -> per-16 requantisation of h -> the gathered planes of every peer;
 // g2: x 2^e_row x alpha -> bf16 -> the gathered zb columns of every peer.
 // Arithmetic contract: test/reference/muse_spark.py:438-563; reference kernels sm103/kernels/moe.cuh:1018-2458.
+//
+// Everything a unit needs besides its weights is fetched two units ahead, so that the rows of unit i + 2 are staged while
+// unit i + 1 computes: two row tiles and two sets of row-scale words in shared memory, two accumulators in tensor memory.
+// The row scales' place in tensor memory is single (256 columns: the block-scaled MMA wants a scale address on a
+// 4-column boundary, so one K64 block takes 4 columns); it is refilled from shared memory in well under a microsecond once
+// the previous unit's MMAs have completed. Measured before (everything staged after the previous unit): 5.4 us per unit
+// with the weight ring full and the memory system idle, a third of the kernel.
 //
 // Tensor memory (512 columns): [0,64) two accumulator buffers of (gate 16 | up 16) columns, [64,96) weight scales of the
 // stage in flight (4 columns per K64 block and tile), [128,384) row scales, one word per K64 block at a stride of 4.
@@ -38,6 +46,7 @@ constexpr uint32_t kSfBytes = 4 * 512;      // 4 K64 blocks x (128 rows x 4 byte
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColAcc = 0, kColSfa = 64, kColSfb = 128;
 constexpr int kMaxKChunks = 16;  // K <= 4096
+constexpr uint32_t kXsBytes = kMaxKChunks * 2048;
 
 struct UnitMeta {
     int n_tok, expert;
@@ -70,22 +79,25 @@ template <bool G2>
 __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) {
     constexpr int TILES = G2 ? 1 : 2;
     constexpr uint32_t STAGE = TILES * (kTileBytes + kSfBytes);
-    constexpr int S = G2 ? 10 : 5;
+    constexpr int S = G2 ? 8 : 4;
     constexpr uint32_t IDESC = idesc_nvf4(128, 16);
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* stages = smem;
-    unsigned char* xs = smem + S * STAGE;                   // K/256 chunks of [16 rows x 128 B], swizzled
-    float* zs = (float*)(xs + kMaxKChunks * 2048);          // g1: [16 rows][129] transpose buffer
-    UnitMeta* meta = (UnitMeta*)(zs + 16 * 129 + 1);        // two units in flight
-    uint64_t* bars = (uint64_t*)(((uintptr_t)(meta + 2) + 15) & ~(uintptr_t)15);
+    unsigned char* xs = smem + S * STAGE;                   // 2 buffers of K/256 chunks of [16 rows x 128 B], swizzled
+    uint32_t* sfw = (uint32_t*)(xs + 2 * kXsBytes);         // 2 x [16 rows][64] row-scale words (4 e4m3 per K64 block)
+    UnitMeta* meta = (UnitMeta*)(sfw + 2 * kMaxRows * 64);  // two units in flight
+    RouteTables* rt = (RouteTables*)(meta + 2);             // the launch's route tables, copied once
+    uint64_t* bars = (uint64_t*)(((uintptr_t)(rt + 1) + 15) & ~(uintptr_t)15);
     uint64_t* full = bars;
     uint64_t* empty = bars + S;
-    uint64_t* x_ready = bars + 2 * S;
-    uint64_t* acc_full = bars + 2 * S + 1;
-    uint64_t* acc_empty = bars + 2 * S + 3;
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * S + 5);
+    uint64_t* x_ready = bars + 2 * S;        // [2]
+    uint64_t* acc_full = bars + 2 * S + 2;   // [2]
+    uint64_t* acc_empty = bars + 2 * S + 4;  // [2]
+    uint64_t* staged = bars + 2 * S + 6;     // [2] stager -> epilogue warps: rows, words and metadata of a unit are in place
+    uint64_t* buf_free = bars + 2 * S + 8;   // [2] epilogue warps -> stager: the unit that used the buffer is finished
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * S + 10);
     volatile int* abort = (volatile int*)(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -94,11 +106,13 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], 1);
         }
-        mbar_init(x_ready, 128);
-        mbar_init(&acc_full[0], 1);
-        mbar_init(&acc_full[1], 1);
-        mbar_init(&acc_empty[0], 128);
-        mbar_init(&acc_empty[1], 128);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&x_ready[i], 128);
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], 128);
+            mbar_init(&staged[i], 64);
+            mbar_init(&buf_free[i], 128);
+        }
         *abort = 0;
         mbar_fence_init();
     }
@@ -109,7 +123,9 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
     const uint32_t tmem = *tmem_slot;
 
     griddep_wait();
-    const RouteTables* rt = a.rt;
+    // one round trip for the route tables every unit looks up
+    for (int i = tid; i < (int)(sizeof(RouteTables) / 4); i += 256) ((int*)rt)[i] = ((const int*)a.rt)[i];
+    __syncthreads();
     const int NB = a.NB, KCH = a.K / 256;
     const int n_units = rt->n_active * NB;
 
@@ -141,12 +157,13 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
             int i = 0;
             for (int u = blockIdx.x; u < n_units && !*abort; u += gridDim.x, ++i) {
                 const int buf = i & 1;
-                if (!mbar_wait(x_ready, i & 1, abort) || !mbar_wait(&acc_empty[buf], ((i >> 1) & 1) ^ 1, abort)) {
+                const uint32_t ph = (i >> 1) & 1;
+                if (!mbar_wait(&x_ready[buf], ph, abort) || !mbar_wait(&acc_empty[buf], ph ^ 1, abort)) {
                     record_abort(a.status, abort, 3, 110 + G2, i);
                     break;
                 }
                 tc_fence_after();
-                const uint32_t xs_addr = smem_u32(xs);
+                const uint32_t xs_addr = smem_u32(xs + buf * kXsBytes);
                 bool ok = true;
                 for (int kc = 0; kc < KCH; ++kc, ++it) {
                     const uint32_t s = it % S, round = it / S;
@@ -177,94 +194,116 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
                 tc_commit(&acc_full[buf]);
             }
         }
-    } else if (warp >= 4) {
-        // ---- routed rows in, epilogue out ----
+    } else if (warp < 4) {
+        // ---- stager: the B operand of unit j into buffer j & 1, two units ahead of the MMAs ----
+        const int ts = tid - 64;  // 0..63
+        int j = 0;
+        for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++j) {
+            const int buf = j & 1;
+            bool ok = j < 2 || mbar_wait(&buf_free[buf], ((j - 2) >> 1) & 1, abort);
+            ok = bar_all(3, 64, ok);
+            if (!ok) {
+                if (ts == 0) record_abort(a.status, abort, 3, 140 + G2, j);
+                break;
+            }
+            UnitMeta& m = meta[buf];
+            unsigned char* xb = xs + buf * kXsBytes;
+            uint32_t* wb = sfw + buf * (kMaxRows * 64);
+            const int ai = u / NB, s0 = rt->act_off[ai], n_tok = rt->act_off[ai + 1] - s0, e = rt->act_e[ai];
+            const int row_bytes = a.K / 2, per_row = KCH * 8, total = n_tok * per_row, wq = KCH, wtotal = n_tok * wq;
+            // every global load of the unit is issued before the first store: one memory round trip
+            int slot = 0, row = 0;
+            float sc = 0.f, cc = 0.f;
+            if (ts < n_tok) {
+                slot = rt->slot[s0 + ts];
+                row = G2 ? slot : slot / a.topk;
+                sc = G2 ? a.rowscale[slot] : a.g1_alphas[e] * a.x_scale[row];
+            }
+            if (ts == 0) cc = G2 ? a.g2_alphas[e] : a.g1_scale_c[e];
+            uint4 wv[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int idx = k * 64 + ts;  // 16 rows x 16 uint4 at most
+                if (idx < wtotal) {
+                    const int tk = idx / wq, c = idx - tk * wq;
+                    const int sl = rt->slot[s0 + tk];
+                    wv[k] = *(const uint4*)(a.bsf + (size_t)(G2 ? sl : sl / a.topk) * (a.K / 16) + c * 16);
+                }
+            }
+            for (int base = 0; base < total; base += 64 * 8) {
+                uint4 v[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int idx = base + k * 64 + ts;
+                    if (idx < total) {
+                        const int tk = idx / per_row, rem = idx - tk * per_row;
+                        const int sl = rt->slot[s0 + tk];
+                        v[k] = *(const uint4*)(a.bq + (size_t)(G2 ? sl : sl / a.topk) * row_bytes + rem * 16);
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int idx = base + k * 64 + ts;
+                    if (idx < total) {
+                        const int tk = idx / per_row, rem = idx - tk * per_row, kc = rem >> 3, jj = rem & 7;
+                        // only live rows are written: a stale row feeds accumulator columns that no epilogue reads
+                        *(uint4*)(xb + kc * 2048 + (tk >> 3) * 1024 + (tk & 7) * 128 + ((jj ^ (tk & 7)) << 4)) = v[k];
+                    }
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int idx = k * 64 + ts;
+                if (idx < wtotal) {
+                    const int tk = idx / wq, c = idx - tk * wq;
+                    *(uint4*)(wb + tk * 64 + c * 4) = wv[k];
+                }
+            }
+            if (ts < kMaxRows) {
+                m.slot[ts] = slot;
+                m.row[ts] = row;
+                m.s[ts] = sc;
+                if (ts == 0) {
+                    m.n_tok = n_tok;
+                    m.expert = e;
+                    m.c = cc;
+                }
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(&staged[buf]);
+        }
+    } else {
+        // ---- scale words -> tensor memory, epilogue out ----
         const int q = warp - 4, te = tid - 128;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
 
-        auto load_b = [&](int u, int i) {
-            UnitMeta& m = meta[i & 1];
-            const int ai = u / NB, s0 = rt->act_off[ai], n_tok = rt->act_off[ai + 1] - s0, e = rt->act_e[ai];
-            if (te < kMaxRows) {
-                int slot = 0, row = 0;
-                float sc = 0.f;
-                if (te < n_tok) {
-                    slot = rt->slot[s0 + te];
-                    row = G2 ? slot : slot / a.topk;
-                    sc = G2 ? a.rowscale[slot] : a.g1_alphas[e] * a.x_scale[row];
-                }
-                m.slot[te] = slot;
-                m.row[te] = row;
-                m.s[te] = sc;
-                if (te == 0) {
-                    m.n_tok = n_tok;
-                    m.expert = e;
-                    m.c = G2 ? a.g2_alphas[e] : a.g1_scale_c[e];
-                }
-            }
-            bar_sync(1, 128);
-            // codes -> swizzled K-major tile rows. Only the n_tok live rows are written: a stale row only feeds accumulator
-            // columns that no epilogue reads (the columns of an MMA are independent). All loads of a batch are issued
-            // before the first store, so a batch costs one memory round trip, not one per chunk.
-            const int row_bytes = a.K / 2, per_row = KCH * 8, total = n_tok * per_row;
-            for (int base = 0; base < total; base += 128 * 8) {
-                uint4 v[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int idx = base + u * 128 + te;
-                    if (idx < total) {
-                        const int tk = idx / per_row, rem = idx - tk * per_row;
-                        v[u] = *(const uint4*)(a.bq + (size_t)m.row[tk] * row_bytes + rem * 16);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int idx = base + u * 128 + te;
-                    if (idx < total) {
-                        const int tk = idx / per_row, rem = idx - tk * per_row, kc = rem >> 3, j = rem & 7;
-                        *(uint4*)(xs + kc * 2048 + (tk >> 3) * 1024 + (tk & 7) * 128 + ((j ^ (tk & 7)) << 4)) = v[u];
-                    }
-                }
-            }
-            // row scales -> tensor memory: lane l = row l, one word (4 e4m3) per K64 block at a column stride of 4;
-            // every epilogue warp writes its own 32-lane quadrant with the same words. The row's words are fetched in one
-            // batch of 16-byte loads, then stored 16 columns at a time.
-            const bool live = lane < n_tok;
-            const uint32_t* sfrow = (const uint32_t*)(a.bsf + (size_t)(live ? m.row[lane] : 0) * (a.K / 16));
-            uint4 w[kMaxKChunks];
-#pragma unroll
-            for (int c = 0; c < kMaxKChunks; ++c) w[c] = (live && c < KCH) ? *(const uint4*)(sfrow + c * 4) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int c = 0; c < kMaxKChunks; ++c) {
-                if (c < KCH) {
-                    uint32_t r[16];
-#pragma unroll
-                    for (int k = 0; k < 16; ++k) r[k] = 0;
-                    r[0] = w[c].x;
-                    r[4] = w[c].y;
-                    r[8] = w[c].z;
-                    r[12] = w[c].w;
-                    tmem_st16(tmem + lane_base + kColSfb + c * 16, r);
-                }
+        // Unit i's row scales from shared to tensor memory (lane l = row l, the word of K64 block b at column 4 b; every
+        // epilogue warp fills its own 32-lane quadrant), then the unit's B operand is handed to the MMA thread. Called once
+        // the MMAs of unit i - 1 have completed: they were the last readers of these columns. Returns false on a timeout.
+        auto publish = [&](int i) -> bool {
+            const int buf = i & 1;
+            if (!bar_all(2, 128, mbar_wait(&staged[buf], (i >> 1) & 1, abort))) return false;
+            const uint32_t* src = sfw + buf * (kMaxRows * 64) + (lane & 15) * 64;
+            for (int c = 0; c < KCH; ++c) {
+                const uint4 w = *(const uint4*)(src + c * 4);
+                const uint32_t r[16] = {w.x, 0, 0, 0, w.y, 0, 0, 0, w.z, 0, 0, 0, w.w, 0, 0, 0};
+                tmem_st16(tmem + lane_base + kColSfb + c * 16, r);
             }
             tmem_st_wait();
             tc_fence_before();
-            fence_proxy_async_smem();
-            mbar_arrive(x_ready);
+            mbar_arrive(&x_ready[buf]);
+            return true;
         };
 
+        const int u0 = blockIdx.x, stride = gridDim.x;
+        bool alive = u0 >= n_units || publish(0);
         int i = 0;
-        if ((int)blockIdx.x < n_units) load_b(blockIdx.x, 0);
-        for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++i) {
+        for (int u = u0; alive && u < n_units; u += stride, ++i) {
             const int buf = i & 1;
-            // all 128 epilogue threads agree on the outcome before any of them meets the others at a barrier again
-            const bool ok = bar_all(2, 128, mbar_wait(&acc_full[buf], (i >> 1) & 1, abort));
-            if (!ok) {
-                if (te == 0) record_abort(a.status, abort, 3, 130 + G2, i);
-                break;
-            }
+            // all 128 epilogue threads agree on the outcome of a wait before any of them meets the others at a barrier again
+            if (!bar_all(2, 128, mbar_wait(&acc_full[buf], (i >> 1) & 1, abort))) break;
             tc_fence_after();
-            if (u + (int)gridDim.x < n_units) load_b(u + gridDim.x, i + 1);
+            if (u + stride < n_units && !publish(i + 1)) break;
             const UnitMeta& m = meta[buf];
             const int blk = u % NB, n_tok = m.n_tok;
             const int mrow = q * 32 + lane;  // weight row of this thread inside the block
@@ -273,43 +312,36 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
                 tmem_ld16(tmem + lane_base + kColAcc + buf * 32, rg);
                 tmem_ld16(tmem + lane_base + kColAcc + buf * 32 + 16, ru);
                 tmem_ld_wait();
+                // a quantisation group is 16 consecutive features = 16 consecutive lanes: the group's maximum and its
+                // packed codes are formed with shuffles inside each half warp, one routed row at a time
 #pragma unroll
                 for (int t = 0; t < kMaxRows; ++t) {
                     if (t < n_tok) {
                         const float a1 = m.s[t];
                         const float g = bf16_round(__uint_as_float(rg[t]) * a1), up = bf16_round(__uint_as_float(ru[t]) * a1);
-                        zs[t * 129 + mrow] = ((g / (1.0f + expf(-g))) * up) * m.c;
+                        const float z = ((g / (1.0f + expf(-g))) * up) * m.c;
+                        float amax = fabsf(z);
+#pragma unroll
+                        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                        const int eg = prov_exp_u(amax);
+                        const float down = __uint_as_float((uint32_t)(127 - eg) << 23);
+                        const uint32_t sfb = float_to_e4m3((amax * down) * (1.0f / 6.0f));
+                        const float d = e4m3_to_float(sfb);
+                        const float inv = d > 0.f ? 1.0f / d : 0.f;
+                        uint32_t word = float_to_e2m1((z * down) * inv) << (4 * (lane & 7));
+#pragma unroll
+                        for (int o = 4; o > 0; o >>= 1) word |= __shfl_xor_sync(0xffffffffu, word, o);
+                        const uint32_t other = __shfl_xor_sync(0xffffffffu, word, 8);
+                        if ((lane & 15) == 0) {
+                            const int slot = m.slot[t], gcol = (a.rank * a.I_s + blk * 128) / 16 + (mrow >> 4);
+                            for (int p = 0; p < a.n_peer; ++p) {
+                                *(uint2*)(a.z_peer[p] + (size_t)slot * (a.I / 2) + gcol * 8) = make_uint2(word, other);
+                                a.zsf_peer[p][(size_t)slot * (a.I / 16) + gcol] = (unsigned char)sfb;
+                                a.zex_peer[p][(size_t)slot * (a.I / 16) + gcol] = (signed char)eg;
+                            }
+                        }
                     }
                 }
-                bar_sync(1, 128);
-                const int t = te >> 3, gi = te & 7;
-                if (t < n_tok) {
-                    float z[16];
-                    float amax = 0.f;
-#pragma unroll
-                    for (int k = 0; k < 16; ++k) {
-                        z[k] = zs[t * 129 + gi * 16 + k];
-                        amax = fmaxf(amax, fabsf(z[k]));
-                    }
-                    const int eg = prov_exp_u(amax);
-                    const float down = __uint_as_float((uint32_t)(127 - eg) << 23);
-                    const uint32_t sfb = float_to_e4m3((amax * down) * (1.0f / 6.0f));
-                    const float d = e4m3_to_float(sfb);
-                    const float inv = d > 0.f ? 1.0f / d : 0.f;
-                    uint32_t lo = 0, hi = 0;
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        lo |= float_to_e2m1((z[k] * down) * inv) << (4 * k);
-                        hi |= float_to_e2m1((z[8 + k] * down) * inv) << (4 * k);
-                    }
-                    const int slot = m.slot[t], gcol = (a.rank * a.I_s + blk * 128) / 16 + gi;
-                    for (int p = 0; p < a.n_peer; ++p) {
-                        *(uint2*)(a.z_peer[p] + (size_t)slot * (a.I / 2) + gcol * 8) = make_uint2(lo, hi);
-                        a.zsf_peer[p][(size_t)slot * (a.I / 16) + gcol] = (unsigned char)sfb;
-                        a.zex_peer[p][(size_t)slot * (a.I / 16) + gcol] = (signed char)eg;
-                    }
-                }
-                bar_sync(1, 128);
             } else {
                 uint32_t r[16];
                 tmem_ld16(tmem + lane_base + kColAcc + buf * 32, r);
@@ -325,7 +357,9 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
             }
             tc_fence_before();
             mbar_arrive(&acc_empty[buf]);
+            mbar_arrive(&buf_free[buf]);
         }
+        if (te == 0 && *abort == 0 && i * stride + u0 < n_units) record_abort(a.status, abort, 3, 130 + G2, i);
     }
     tc_fence_before();
     __syncthreads();
@@ -334,8 +368,9 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
 
 size_t experts_umma_smem(bool g2) {
     const size_t stage = (g2 ? 1 : 2) * (size_t)(kTileBytes + kSfBytes);
-    const int S = g2 ? 10 : 5;
-    return 1024 + S * stage + kMaxKChunks * 2048 + (16 * 129 + 1) * 4 + 2 * sizeof(UnitMeta) + 16 + (2 * S + 5) * 8 + 16;
+    const int S = g2 ? 8 : 4;
+    return 1024 + S * stage + 2 * kXsBytes + 2 * kMaxRows * 64 * 4 + 2 * sizeof(UnitMeta) + sizeof(RouteTables) + 16 +
+           (2 * S + 10) * 8 + 16;
 }
 
 cudaError_t experts_umma_prepare() {

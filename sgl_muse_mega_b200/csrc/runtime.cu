@@ -124,7 +124,7 @@ static void fill_constants(const MkLayerShape& s, MkLayerConstants* c) {
     c->zb_bytes = slots * s.moe_hidden * 2;
     c->attn_splits = attn_splits_for(s);
     c->flag_words = 64;
-    c->status_bytes = 64;
+    c->status_bytes = 4096;
     // scratch carve: attention partials | gemm partials | gemm counters | route tables | z_sfd | rowscale
     const int64_t R = M * (s.q_heads / s.kv_heads);
     size_t off = 0;
