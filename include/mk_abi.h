@@ -200,6 +200,112 @@ typedef struct MkLayerBind {
 } MkLayerBind;
 int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind* bind, MkLaunch** out);
 
+// ---- the rest of the verify step ----
+
+// Window feeds (replaces abi.h:216-239 MkFeedsBind / mk_feeds_bind, same field names): the step's RoPE rows, cache-write
+// slots, kv_len and the position -> byte-offset tables of one request.
+typedef struct MkFeedsBind {
+    uint64_t positions;          // i64 [rows]
+    uint64_t cos_sin_cache;      // f32 [cos_sin_rows, head_dim]; 0 = the rope rows are written elsewhere
+    int64_t cos_sin_rows;
+    uint64_t out_cache_loc;      // i64 [rows]
+    uint64_t swa_out_cache_loc;  // i64 [rows] or 0
+    uint64_t seq_lens;           // i64 [1]
+    uint64_t req_pool_indices;   // i64 [1]
+    uint64_t req_to_token;       // i32 [r2t_rows, r2t_width]
+    int64_t r2t_rows;
+    int64_t r2t_width;
+    uint64_t full_to_swa;        // i64 [swa_map_len] or 0
+    int64_t swa_map_len;
+    uint64_t cos_sin;            // out f32 [rows, head_dim]
+    uint64_t loc_full;           // out i32 [rows]
+    uint64_t loc_swa;            // out i32 [rows]
+    uint64_t kv_len;             // out i32 [1]
+    uint64_t pt_full;            // out i64 [r2t_width]
+    uint64_t pt_swa;             // out i64 [r2t_width] or 0
+    int64_t rows;
+    int64_t head_dim;
+    int64_t kv_row_bytes;
+    uint64_t status;             // i32 [16] or 0: an out-of-range position or request index is recorded here (code 4), not trapped
+} MkFeedsBind;
+int mk_feeds_bind(MkModule* module, const MkFeedsBind* bind, MkLaunch** out);
+
+// The fused entry (replaces abi.h:242-254 MkEntryBind / mk_entry_bind): embedding row from the owning rank's vocab
+// shard, weightless embed norm, layer 0's pre-attention norm.
+typedef struct MkEntryBind {
+    uint64_t ids;                    // i64 [rows]
+    uint64_t embed_peer[MKH_RANKS];  // every rank's vocab shard [shard_rows, hidden] bf16
+    int64_t shard_rows;
+    int64_t ranks;
+    uint64_t pre_w;                  // bf16 [hidden]
+    uint64_t residual;               // out f32 [rows, hidden]
+    uint64_t normed;                 // out bf16 [rows, hidden]
+    int64_t rows;
+    int64_t hidden;
+    double eps_embed;
+    double eps_pre;
+} MkEntryBind;
+int mk_entry_bind(MkModule* module, const MkEntryBind* bind, MkLaunch** out);
+
+// lm_head (replaces abi.h:257-270 MkLmHeadBind / mk_lm_head_bind): this rank's vocab shard against the final hidden
+// rows, f32, written into every present rank's gathered logits row at column col0 (peer stores; the reference multicasts).
+typedef struct MkLmHeadBind {
+    uint64_t w;                    // bf16 [n_out, hidden]: the rank's vocab rows
+    uint64_t x;                    // bf16 [rows, hidden]
+    uint64_t out_peer[MKH_RANKS];  // every rank's gathered logits f32 [rows, v_total] (own included); 0 = absent
+    int64_t rank;
+    int64_t v_total;
+    int64_t col0;
+    int64_t n_out;
+    int64_t hidden;
+    int64_t rows;
+    uint64_t status;               // i32 [16] or 0: a weight copy that never landed is recorded here (code 3), not trapped
+} MkLmHeadBind;
+int mk_lm_head_bind(MkModule* module, const MkLmHeadBind* bind, MkLaunch** out);
+
+// Soft cap over the gathered logits (replaces abi.h:273-286 MkSoftcapBind / mk_softcap_bind).
+typedef struct MkSoftcapBind {
+    uint64_t x;    // f32 [numel]
+    uint64_t out;  // f32 [numel]
+    int64_t numel;
+    double scale;
+    double cap;
+} MkSoftcapBind;
+int mk_softcap_bind(MkModule* module, const MkSoftcapBind* bind, MkLaunch** out);
+
+// Greedy verify-accept on the gathered logits (replaces the accept half of abi.h mk_dflash_verify_accept_bind; the
+// lm_head half is mk_lm_head_bind): first-arg-max of the soft-capped rows, greedy prefix accept or the forced table,
+// the step words [P, ANCHOR, ACCEPT, COMMIT, ITER, OUT_COUNT, -, -], the committed-token ring, the next step's feeds.
+typedef struct MkAcceptBind {
+    uint64_t logits;           // f32 [rows, vocab] gathered, before the soft cap
+    int64_t vocab;
+    int64_t rows;
+    int64_t b_live;
+    double scale;
+    double cap;
+    uint64_t tokens;           // i64 [rows]: the window's ids [anchor, d_1 ..]
+    uint64_t accept_override;  // i32 [n_override] forced accept per iteration, or 0
+    int64_t n_override;
+    uint64_t words;            // i64 [8], read and advanced
+    uint64_t out_ring;         // i32 [ring]
+    int64_t ring;
+    uint64_t top1;             // out i32 [rows]
+    uint64_t counter;          // u32 [1], zeroed once by the caller
+    uint64_t cos_sin_cache;    // f32 [cos_sin_rows, 64]
+    int64_t cos_sin_rows;
+    uint64_t cos_sin;          // out: next target feeds (each may be 0)
+    uint64_t loc_full;
+    uint64_t loc_swa;
+    uint64_t kv_len;
+    uint64_t dcos_sin_cache;   // f32 [dcos_sin_rows, 128]
+    int64_t dcos_sin_rows;
+    uint64_t dcos_sin;         // out: next draft feeds [2 b_live, 128] (each may be 0)
+    uint64_t dslot;
+    uint64_t dkv_len;
+    int64_t dring;
+} MkAcceptBind;
+int mk_accept_bind(MkModule* module, const MkAcceptBind* bind, MkLaunch** out);
+
 // ---- layer 0's head: qkv GEMM + qk-norm + RoPE + K/V append as a stand-alone launch ----
 
 // Replaces abi.h:255-270 MkQkvBind / mk_qkv_bind (same names for the same operands); rows, heads and the scratch are

@@ -76,7 +76,7 @@ def make(struct: str, **values) -> ctypes.Structure:
 EXPORTS = (
     "mk_last_error", "mk_module_load", "mk_module_free", "mk_launch", "mk_launch_step", "mk_launch_free",
     "mk_launch_info", "mk_launch_status", "mk_layer_constants", "mk_layer_bind", "mk_qkv_constants", "mk_qkv_bind",
-    "mk_qkv_launch_static",
+    "mk_qkv_launch_static", "mk_feeds_bind", "mk_entry_bind", "mk_lm_head_bind", "mk_softcap_bind", "mk_accept_bind",
 )  # fmt: skip
 
 
@@ -104,6 +104,9 @@ class Library:
         d.mk_qkv_constants.argtypes = [P(STRUCTS["MkQkvBind"]), P(STRUCTS["MkQkvConstants"])]
         d.mk_qkv_bind.argtypes = [vp, P(STRUCTS["MkQkvBind"]), P(vp)]
         d.mk_qkv_launch_static.argtypes = [P(STRUCTS["MkQkvBind"]), ctypes.c_uint64]
+        for fn, st in (("mk_feeds_bind", "MkFeedsBind"), ("mk_entry_bind", "MkEntryBind"), ("mk_lm_head_bind", "MkLmHeadBind"),
+                       ("mk_softcap_bind", "MkSoftcapBind"), ("mk_accept_bind", "MkAcceptBind")):  # fmt: skip
+            getattr(d, fn).argtypes = [vp, P(STRUCTS[st]), P(vp)]
 
     def check(self, rc: int, what: str) -> None:
         if rc != 0:
@@ -138,6 +141,14 @@ class Library:
     def qkv_bind(self, module: "Module | None", bind) -> "Launch":
         out = ctypes.c_void_p()
         self.check(self.dll.mk_qkv_bind(module.handle if module else None, ctypes.byref(bind), ctypes.byref(out)), "mk_qkv_bind")
+        return Launch(self, out, module)
+
+
+    def bind(self, fn_name: str, module: "Module | None", bind) -> "Launch":
+        """Any ``mk_*_bind(module, bind, out)`` entry point by name (feeds, entry, lm_head, softcap, accept)."""
+        out = ctypes.c_void_p()
+        fn = getattr(self.dll, fn_name)
+        self.check(fn(module.handle if module else None, ctypes.byref(bind), ctypes.byref(out)), fn_name)
         return Launch(self, out, module)
 
 

@@ -81,10 +81,12 @@ __global__ void __launch_bounds__(256) skinny_gemm_kernel(const GemmArgs a) {
         s_abort = 0;
         umma::mbar_init(&bar, 1);
         umma::mbar_fence_init();
-        umma::mbar_arrive_expect_tx(&bar, (uint32_t)(C::BN * KC * C::ES));
+        // the last tile of an N that is not a multiple of BN has fewer rows: rows past N are neither fetched nor stored
+        const int valid = min(C::BN, a.N - nb * C::BN);
+        umma::mbar_arrive_expect_tx(&bar, (uint32_t)(valid * KC * C::ES));
     }
     __syncthreads();
-    if (tid < C::BN)
+    if (tid < C::BN && nb * C::BN + tid < a.N)
         umma::bulk_g2s(wsm + tid * row_bytes, (const unsigned char*)a.w + ((size_t)(nb * C::BN + tid) * a.ldw + k0) * C::ES,
                        (uint32_t)(KC * C::ES), &bar);
 
@@ -177,7 +179,8 @@ __global__ void __launch_bounds__(256) skinny_gemm_kernel(const GemmArgs a) {
             return v;
         };
         if (a.mode == 0) {
-            for (int n = lane; n < C::BN; n += 32) gemm_store(a, m, nb * C::BN + n, total(n));
+            for (int n = lane; n < C::BN; n += 32)
+                if (nb * C::BN + n < a.N) gemm_store(a, m, nb * C::BN + n, total(n));
         } else {
             // one head: lane owns the pair (2 lane, 2 lane + 1)
             const int head = nb;
@@ -219,10 +222,10 @@ static size_t smem_bytes(bool wf32, int K, int ksplit) {
 // splits whose weight tile and activation slice fit shared memory and give every warp whole 64-byte steps, the largest
 // that keeps the grid within one wave of `max_ctas` CTAs, else the smallest (fewest CTAs beyond one wave).
 int gemm_plan(bool wf32, int mode, int N, int K, int max_ctas, int* wn_out, int* ksplit_out) {
-    (void)mode;
     const int wn = wf32 ? 1 : 4;
     const int bn = 16 * wn, wk = 8 / wn, kstep = wf32 ? 16 : 32;
-    if (N % bn) return -1;
+    if (mode == 1 && N % bn) return -1;  // a head tile must be whole; plain tiles may have a short last tile
+    const int nblocks = (N + bn - 1) / bn;
     int best = -1, smallest = -1;
     for (int ks = 8; ks >= 1; ks >>= 1) {
         if (K % ks) continue;
@@ -230,7 +233,7 @@ int gemm_plan(bool wf32, int mode, int N, int K, int max_ctas, int* wn_out, int*
         if (kc % (wk * kstep)) continue;
         if (smem_bytes(wf32, K, ks) > 220 * 1024) continue;
         smallest = ks;
-        if (best < 0 && (long long)(N / bn) * ks <= max_ctas) best = ks;
+        if (best < 0 && (long long)nblocks * ks <= max_ctas) best = ks;
     }
     const int ks = best > 0 ? best : smallest;
     if (ks < 0) return -1;
@@ -240,7 +243,7 @@ int gemm_plan(bool wf32, int mode, int N, int K, int max_ctas, int* wn_out, int*
 }
 
 size_t gemm_smem(const GemmArgs& a, bool wf32) { return smem_bytes(wf32, a.K, a.ksplit); }
-int gemm_grid(const GemmArgs& a) { return (a.N / (16 * a.wn)) * a.ksplit; }
+int gemm_grid(const GemmArgs& a) { return ((a.N + 16 * a.wn - 1) / (16 * a.wn)) * a.ksplit; }
 
 cudaError_t gemm_prepare() {
     cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
@@ -250,7 +253,7 @@ cudaError_t gemm_prepare() {
 
 cudaError_t gemm_launch(const GemmArgs& a, bool wf32, cudaStream_t stream, bool pdl) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(a.N / (16 * a.wn), a.ksplit, 1);
+    cfg.gridDim = dim3((a.N + 16 * a.wn - 1) / (16 * a.wn), a.ksplit, 1);
     cfg.blockDim = dim3(256, 1, 1);
     cfg.dynamicSmemBytes = gemm_smem(a, wf32);
     cfg.stream = stream;

@@ -71,7 +71,16 @@ struct MkLaunch {
     int sms;
     mk::UmmaArgs umma_g1, umma_g2;
     bool stage_on[ST_COUNT];
+    // stand-alone launches around the layers (feeds, entry, lm_head, soft cap, accept): n_ops > 0 replaces the stage list
+    int n_ops;
+    int op_kind[4];
+    mk::FeedsArgs feeds;
+    mk::EntryArgs entry;
+    mk::SoftcapArgs softcap;
+    mk::AcceptArgs accept;
+    mk::GemmArgs op_gemm;
 };
+enum OpKind { OP_FEEDS = 1, OP_ENTRY, OP_GEMM_BF16, OP_SOFTCAP, OP_ACCEPT };
 
 using namespace mk;
 
@@ -455,6 +464,7 @@ static int run_stage(const MkLaunch* L, int st, cudaStream_t s, bool pdl) {
 
 int mk_launch_step(const MkLaunch* launch, uint64_t stream, int64_t first, int64_t count) {
     MK_REQUIRE(launch != nullptr, "launch is NULL");
+    MK_REQUIRE(launch->n_ops == 0, "mk_launch_step addresses the stages of a layer launch");
     MK_REQUIRE(!launch->pack_only, "a pack-only record (bound without a module) cannot launch");
     MK_REQUIRE(first >= 0 && count >= 0 && first + count <= ST_COUNT, "stages [%lld, %lld) outside 0..%d", (long long)first,
                (long long)(first + count), ST_COUNT);
@@ -463,9 +473,26 @@ int mk_launch_step(const MkLaunch* launch, uint64_t stream, int64_t first, int64
     return 0;
 }
 
+static int run_ops(const MkLaunch* L, cudaStream_t s, bool pdl) {
+    for (int i = 0; i < L->n_ops; ++i) {
+        cudaError_t e = cudaSuccess;
+        switch (L->op_kind[i]) {
+            case OP_FEEDS: e = feeds_launch(L->feeds, s, pdl); break;
+            case OP_ENTRY: e = entry_launch(L->entry, s, pdl); break;
+            case OP_GEMM_BF16: e = gemm_launch(L->op_gemm, false, s, pdl); break;
+            case OP_SOFTCAP: e = softcap_launch(L->softcap, s, pdl); break;
+            case OP_ACCEPT: e = accept_launch(L->accept, s, pdl); break;
+            default: return fail("op %d does not exist", L->op_kind[i]);
+        }
+        if (e != cudaSuccess) return fail("op %d launch: %s", L->op_kind[i], cudaGetErrorString(e));
+    }
+    return 0;
+}
+
 int mk_launch(const MkLaunch* launch, uint64_t stream, int pdl) {
     MK_REQUIRE(launch != nullptr, "launch is NULL");
     MK_REQUIRE(!launch->pack_only, "a pack-only record (bound without a module) cannot launch");
+    if (launch->n_ops > 0) return run_ops(launch, (cudaStream_t)stream, pdl != 0);
     for (int st = 0; st < ST_COUNT; ++st)
         if (run_stage(launch, st, (cudaStream_t)stream, pdl != 0 && st > 0)) return -1;
     return 0;
@@ -476,6 +503,16 @@ void mk_launch_free(MkLaunch* launch) { delete launch; }
 int mk_launch_info(const MkLaunch* launch, MkLaunchInfo* out) {
     MK_REQUIRE(launch != nullptr && out != nullptr, "launch or out is NULL");
     const MkLaunch* L = launch;
+    if (L->n_ops > 0) {
+        memset(out, 0, sizeof *out);
+        out->kernels = L->n_ops;
+        out->block = 1024;
+        out->cluster = 1;
+        out->grid = L->op_kind[0] == OP_GEMM_BF16 ? gemm_grid(L->op_gemm) : 16;
+        out->smem = L->op_kind[0] == OP_GEMM_BF16 ? (int64_t)gemm_smem(L->op_gemm, false) : 0;
+        out->param_bytes = (int64_t)sizeof(MkLaunch);
+        return 0;
+    }
     int kernels = 0;
     for (int i = 0; i < ST_COUNT; ++i) kernels += L->stage_on[i];
     int64_t grid = 0, smem = 0;
@@ -506,6 +543,123 @@ int mk_launch_info(const MkLaunch* launch, MkLaunchInfo* out) {
     out->smem = smem;
     out->kernels = kernels;
     out->param_bytes = (int64_t)sizeof(MkLaunch);
+    return 0;
+}
+
+// ---- feeds, entry, lm_head, soft cap, accept ----
+
+static MkLaunch* new_op_launch(MkModule* module, int kind) {
+    MkLaunch* L = new (std::nothrow) MkLaunch();
+    if (L == nullptr) return nullptr;
+    L->pack_only = module == nullptr;
+    L->device = module ? module->device : -1;
+    L->sms = module ? module->sms : 148;
+    L->n_ops = 1;
+    L->op_kind[0] = kind;
+    return L;
+}
+
+int mk_feeds_bind(MkModule* module, const MkFeedsBind* b, MkLaunch** out) {
+    MK_REQUIRE(out != nullptr && b != nullptr, "bind or out is NULL");
+    NEED(positions); NEED(out_cache_loc); NEED(seq_lens); NEED(req_pool_indices); NEED(req_to_token);
+    NEED(loc_full); NEED(kv_len); NEED(pt_full);
+    MK_REQUIRE(b->rows >= 1 && b->rows <= kMaxRows, "rows %lld outside 1..16", (long long)b->rows);
+    MK_REQUIRE(b->r2t_rows >= 1 && b->r2t_width >= b->rows, "req_to_token is %lld x %lld", (long long)b->r2t_rows, (long long)b->r2t_width);
+    MK_REQUIRE(b->cos_sin_cache == 0 || (b->cos_sin != 0 && b->cos_sin_rows > 0 && b->head_dim > 0), "rope cache without rows or output");
+    MK_REQUIRE((b->swa_out_cache_loc == 0) == (b->loc_swa == 0), "swa_out_cache_loc and loc_swa go together");
+    MK_REQUIRE((b->full_to_swa == 0) == (b->pt_swa == 0), "full_to_swa and pt_swa go together");
+    MkLaunch* L = new_op_launch(module, OP_FEEDS);
+    MK_REQUIRE(L != nullptr, "out of host memory");
+    L->feeds = FeedsArgs{(const long long*)b->positions, (const float*)b->cos_sin_cache, b->cos_sin_rows, (const long long*)b->out_cache_loc,
+                         (const long long*)b->swa_out_cache_loc, (const long long*)b->seq_lens, (const long long*)b->req_pool_indices,
+                         (const int*)b->req_to_token, b->r2t_rows, b->r2t_width, (const long long*)b->full_to_swa, b->swa_map_len,
+                         (float*)b->cos_sin, (int*)b->loc_full, (int*)b->loc_swa, (int*)b->kv_len, (long long*)b->pt_full,
+                         (long long*)b->pt_swa, (int)b->rows, (int)b->head_dim, (int)b->kv_row_bytes, (int*)b->status};
+    L->status = (int*)b->status;
+    *out = L;
+    return 0;
+}
+
+int mk_entry_bind(MkModule* module, const MkEntryBind* b, MkLaunch** out) {
+    MK_REQUIRE(out != nullptr && b != nullptr, "bind or out is NULL");
+    NEED(ids); NEED(pre_w); NEED(residual); NEED(normed);
+    MK_REQUIRE(b->rows >= 1 && b->rows <= kMaxRows, "rows %lld outside 1..16", (long long)b->rows);
+    MK_REQUIRE(b->hidden >= 256 && b->hidden <= 8192 && b->hidden % 256 == 0, "hidden %lld unsupported", (long long)b->hidden);
+    MK_REQUIRE(b->ranks >= 1 && b->ranks <= MKH_RANKS && b->shard_rows >= 1, "ranks %lld / shard_rows %lld", (long long)b->ranks, (long long)b->shard_rows);
+    MkLaunch* L = new_op_launch(module, OP_ENTRY);
+    MK_REQUIRE(L != nullptr, "out of host memory");
+    EntryArgs& e = L->entry;
+    memset(&e, 0, sizeof e);
+    e.ids = (const long long*)b->ids;
+    for (int r = 0; r < b->ranks; ++r) {
+        if (b->embed_peer[r] == 0 || (b->embed_peer[r] & 15)) {
+            delete L;
+            return fail("embed_peer[%d] is 0 or not 16-byte aligned", r);
+        }
+        e.embed[r] = (const bf16*)b->embed_peer[r];
+    }
+    e.shard_rows = b->shard_rows; e.ranks = (int)b->ranks; e.pre_w = (const bf16*)b->pre_w; e.residual = (float*)b->residual;
+    e.normed = (bf16*)b->normed; e.rows = (int)b->rows; e.hidden = (int)b->hidden; e.eps_embed = (float)b->eps_embed; e.eps_pre = (float)b->eps_pre;
+    *out = L;
+    return 0;
+}
+
+int mk_lm_head_bind(MkModule* module, const MkLmHeadBind* b, MkLaunch** out) {
+    MK_REQUIRE(out != nullptr && b != nullptr, "bind or out is NULL");
+    NEED(w); NEED(x);
+    ALIGNED16(w); ALIGNED16(x);
+    MK_REQUIRE(b->rows >= 1 && b->rows <= kMaxRows, "rows %lld outside 1..16", (long long)b->rows);
+    MK_REQUIRE(b->rank >= 0 && b->rank < MKH_RANKS && b->out_peer[b->rank] != 0, "out_peer[rank] (this rank's logits) is 0");
+    MK_REQUIRE(b->n_out >= 1 && b->col0 >= 0 && b->col0 + b->n_out <= b->v_total, "columns [%lld, %lld) outside %lld", (long long)b->col0,
+               (long long)(b->col0 + b->n_out), (long long)b->v_total);
+    MkLaunch* L = new_op_launch(module, OP_GEMM_BF16);
+    MK_REQUIRE(L != nullptr, "out of host memory");
+    GemmArgs& g = L->op_gemm;
+    memset(&g, 0, sizeof g);
+    g.w = (const void*)b->w; g.x = (const void*)b->x;
+    g.M = (int)b->rows; g.N = (int)b->n_out; g.K = (int)b->hidden; g.ldw = g.ldx = (int)b->hidden;
+    if (gemm_plan(false, 0, g.N, g.K, L->sms, &g.wn, &g.ksplit)) {
+        delete L;
+        return fail("lm_head [%lld x %lld] has no tile / K-split plan", (long long)b->n_out, (long long)b->hidden);
+    }
+    for (int r = 0; r < MKH_RANKS; ++r)
+        if (b->out_peer[r]) g.out[g.n_out++] = (void*)b->out_peer[r];
+    g.ldo = (int)b->v_total; g.col0 = (int)b->col0; g.out_f32 = 1;
+    g.status = L->status = (int*)b->status;
+    *out = L;
+    return 0;
+}
+
+int mk_softcap_bind(MkModule* module, const MkSoftcapBind* b, MkLaunch** out) {
+    MK_REQUIRE(out != nullptr && b != nullptr, "bind or out is NULL");
+    NEED(x); NEED(out);
+    MK_REQUIRE(b->numel >= 1 && b->cap > 0, "numel %lld / cap %g", (long long)b->numel, b->cap);
+    MkLaunch* L = new_op_launch(module, OP_SOFTCAP);
+    MK_REQUIRE(L != nullptr, "out of host memory");
+    L->softcap = SoftcapArgs{(const float*)b->x, (float*)b->out, b->numel, (float)b->scale, (float)b->cap};
+    *out = L;
+    return 0;
+}
+
+int mk_accept_bind(MkModule* module, const MkAcceptBind* b, MkLaunch** out) {
+    MK_REQUIRE(out != nullptr && b != nullptr, "bind or out is NULL");
+    NEED(logits); NEED(tokens); NEED(words); NEED(out_ring); NEED(top1); NEED(counter);
+    MK_REQUIRE(b->rows >= 1 && b->rows <= kMaxRows && b->b_live >= 1 && b->b_live <= b->rows, "rows %lld / b_live %lld", (long long)b->rows,
+               (long long)b->b_live);
+    MK_REQUIRE(b->vocab >= 1 && b->ring >= b->rows && b->cap > 0, "vocab %lld / ring %lld / cap %g", (long long)b->vocab, (long long)b->ring, b->cap);
+    MK_REQUIRE(b->accept_override == 0 || b->n_override >= 1, "accept_override without entries");
+    MK_REQUIRE(b->cos_sin == 0 || (b->cos_sin_cache != 0 && b->cos_sin_rows >= 1), "cos_sin without its cache");
+    MK_REQUIRE(b->dslot == 0 || (b->dkv_len != 0 && b->dring >= 1), "dslot without dkv_len / dring");
+    MK_REQUIRE(b->dcos_sin == 0 || (b->dslot != 0 && b->dcos_sin_cache != 0 && b->dcos_sin_rows >= 1), "dcos_sin without dslot or its cache");
+    MkLaunch* L = new_op_launch(module, OP_ACCEPT);
+    MK_REQUIRE(L != nullptr, "out of host memory");
+    L->accept = AcceptArgs{(const float*)b->logits, (int)b->vocab, (int)b->rows, (int)b->b_live, (float)b->scale, (float)b->cap,
+                           (const long long*)b->tokens, (const int*)b->accept_override, (int)b->n_override, (long long*)b->words,
+                           (int*)b->out_ring, (int)b->ring, (int*)b->top1, (unsigned*)b->counter, (const float*)b->cos_sin_cache,
+                           b->cos_sin_rows, (float*)b->cos_sin, (int*)b->loc_full, (int*)b->loc_swa, (int*)b->kv_len,
+                           (const float*)b->dcos_sin_cache, b->dcos_sin_rows, (float*)b->dcos_sin, (int*)b->dslot, (int*)b->dkv_len,
+                           (int)b->dring};
+    *out = L;
     return 0;
 }
 

@@ -150,6 +150,75 @@ struct UmmaArgs {
     int n_peer;
     int* status;
 };
+// headtail.cu: the kernels around the decoder layers
+struct FeedsArgs {
+    const long long* positions;       // i64 [rows]
+    const float* cos_sin_cache;       // f32 [cos_sin_rows, head_dim]
+    long long cos_sin_rows;
+    const long long* out_cache_loc;   // i64 [rows]
+    const long long* swa_out_cache_loc;
+    const long long* seq_lens;        // i64 [1]
+    const long long* req_pool_indices;
+    const int* req_to_token;          // i32 [r2t_rows, r2t_width]
+    long long r2t_rows, r2t_width;
+    const long long* full_to_swa;     // i64 [swa_map_len] or null
+    long long swa_map_len;
+    float* cos_sin;                   // out f32 [rows, head_dim]
+    int* loc_full;
+    int* loc_swa;
+    int* kv_len;
+    long long* pt_full;               // out i64 [r2t_width] byte offsets
+    long long* pt_swa;
+    int rows, head_dim, kv_row_bytes;
+    int* status;
+};
+struct EntryArgs {
+    const long long* ids;             // i64 [rows]
+    const bf16* embed[kMaxRanks];     // every rank's vocab shard [shard_rows, hidden]
+    long long shard_rows;
+    int ranks;
+    const bf16* pre_w;
+    float* residual;                  // out f32 [rows, hidden]
+    bf16* normed;                     // out bf16 [rows, hidden]
+    int rows, hidden;
+    float eps_embed, eps_pre;
+};
+struct SoftcapArgs {
+    const float* x;
+    float* out;
+    long long numel;
+    float scale, cap;
+};
+struct AcceptArgs {
+    const float* logits;              // f32 [rows, vocab] gathered, before the soft cap
+    int vocab, rows, b_live;
+    float scale, cap;
+    const long long* tokens;          // i64 [rows] the window's ids [anchor, d_1 ..]
+    const int* accept_override;       // forced accepts per iteration (mod n_override) or null
+    int n_override;
+    long long* words;                 // i64 [8]: P, ANCHOR, ACCEPT, COMMIT, ITER, OUT_COUNT
+    int* out_ring;
+    int ring;
+    int* top1;                        // out i32 [rows]
+    unsigned* counter;                // one arrival counter, zero between launches
+    const float* cos_sin_cache;       // f32 [cos_sin_rows, 64]
+    long long cos_sin_rows;
+    float* cos_sin;                   // next target feeds (any may be null)
+    int* loc_full;
+    int* loc_swa;
+    int* kv_len;
+    const float* dcos_sin_cache;      // f32 [dcos_sin_rows, 128]
+    long long dcos_sin_rows;
+    float* dcos_sin;                  // next draft feeds: [2 B, 128]
+    int* dslot;
+    int* dkv_len;
+    int dring;
+};
+cudaError_t feeds_launch(const FeedsArgs& a, cudaStream_t s, bool pdl);
+cudaError_t entry_launch(const EntryArgs& a, cudaStream_t s, bool pdl);
+cudaError_t softcap_launch(const SoftcapArgs& a, cudaStream_t s, bool pdl);
+cudaError_t accept_launch(const AcceptArgs& a, cudaStream_t s, bool pdl);
+
 size_t experts_umma_smem(bool g2);
 cudaError_t experts_umma_prepare();
 cudaError_t experts_umma_launch(const UmmaArgs& a, bool g2, int grid, cudaStream_t s, bool pdl);

@@ -43,8 +43,12 @@ class LayerRank:
     """One rank's weights (moved to the device), buffers and bound launch of one layer."""
 
     def __init__(self, lib: host.Library, module, case, rank: int, device, kv_rows: Optional[int] = None, tensors=None,
-                 tensor_cores: bool = True, keep_plain_experts: bool = True):  # fmt: skip
-        """``tensor_cores``: bind the packed NVFP4 images when the shape has whole 128-row tiles (the tcgen05 expert
+                 tensor_cores: bool = True, keep_plain_experts: bool = True, io: Optional[dict] = None):  # fmt: skip
+        """``io`` replaces buffers this layer would allocate with ones it shares with its neighbours in a stack: inputs
+        ``qkv_in`` / ``stream_in`` (the predecessor's outputs), ``k_cache`` / ``v_cache`` (the pools the predecessor
+        appended to), the step's feeds ``page_table`` / ``kv_len`` / ``cache_loc`` / ``next_cos_sin`` and the
+        successor's pools ``next_k`` / ``next_v``.
+        ``tensor_cores``: bind the packed NVFP4 images when the shape has whole 128-row tiles (the tcgen05 expert
         kernels); otherwise, or when False, the experts run on the general CUDA-core kernels from the plain tensors.
         ``keep_plain_experts`` False drops the plain expert tensors once the images exist (halves the expert memory)."""
         cfg = case.cfg
@@ -53,7 +57,12 @@ class LayerRank:
         self.consts = c = lib.layer_constants(self.shape)
         t = tensors if tensors is not None else case.ranks[rank]
         dev = lambda x: None if x is None else x.to(device).contiguous()  # noqa: E731
-        self.w = {k: dev(v) for k, v in vars(t).items()}
+        io = dict(io or {})
+        skip = set(io) | ({"k_ctx", "v_ctx"} if "k_cache" in io else set())
+        self.w = {k: (None if k in skip else dev(v)) for k, v in vars(t).items()}
+        for k in ("qkv_in", "stream_in", "next_cos_sin"):
+            if k in io:
+                self.w[k] = io[k]
         M, H, P, E, K = case.rows, cfg.hidden, cfg.moe_hidden, cfg.experts, cfg.topk
         whole_tiles = (cfg.inter_rank % 128 == 0 and cfg.moe_hidden_rank % 128 == 0 and P % 256 == 0
                        and cfg.moe_inter % 256 == 0 and P <= 4096 and cfg.moe_inter <= 4096)  # fmt: skip
@@ -77,16 +86,31 @@ class LayerRank:
         # KV pools of this layer (context rows then the window's rows, identity slots) and of the successor
         kv_rows = kv_rows or (case.ctx + M + 127) // 128 * 128
         kvw = cfg.kv_heads_rank * cfg.head_dim
-        self.k_cache, self.v_cache = z((kv_rows, kvw), bf), z((kv_rows, kvw), bf)
-        self.k_cache[: case.ctx] = self.w["k_ctx"].reshape(case.ctx, kvw)
-        self.v_cache[: case.ctx] = self.w["v_ctx"].reshape(case.ctx, kvw)
-        qo, ko = cfg.q_heads_rank * 64, (cfg.q_heads_rank + cfg.kv_heads_rank) * 64
-        self.k_cache[case.ctx : case.ctx + M] = self.w["qkv_in"][:, qo:ko]
-        self.v_cache[case.ctx : case.ctx + M] = self.w["qkv_in"][:, ko : ko + kvw]
-        self.next_k, self.next_v = z((kv_rows, kvw), bf), z((kv_rows, kvw), bf)
-        self.page_table = torch.arange(kv_rows, dtype=torch.int64, device=device) * c.kv_row_bytes
-        self.kv_len = torch.tensor([case.ctx + M], dtype=i32, device=device)
-        self.cache_loc = torch.arange(case.ctx, case.ctx + M, dtype=i32, device=device)
+        if "k_cache" in io:
+            self.k_cache, self.v_cache = io["k_cache"], io["v_cache"]
+            kv_rows = self.k_cache.shape[0]
+        else:
+            self.k_cache, self.v_cache = z((kv_rows, kvw), bf), z((kv_rows, kvw), bf)
+            self.k_cache[: case.ctx] = self.w["k_ctx"].reshape(case.ctx, kvw)
+            self.v_cache[: case.ctx] = self.w["v_ctx"].reshape(case.ctx, kvw)
+            if "qkv_in" not in io:
+                qo, ko = cfg.q_heads_rank * 64, (cfg.q_heads_rank + cfg.kv_heads_rank) * 64
+                self.k_cache[case.ctx : case.ctx + M] = self.w["qkv_in"][:, qo:ko]
+                self.v_cache[case.ctx : case.ctx + M] = self.w["qkv_in"][:, ko : ko + kvw]
+        if "next_k" in io:
+            self.next_k, self.next_v = io["next_k"], io["next_v"]
+        else:
+            self.next_k, self.next_v = z((kv_rows, kvw), bf), z((kv_rows, kvw), bf)
+        self.next_kv_rows = self.next_k.shape[0]
+        self.page_table = io.get("page_table")
+        if self.page_table is None:
+            self.page_table = torch.arange(kv_rows, dtype=torch.int64, device=device) * c.kv_row_bytes
+        self.kv_len = io.get("kv_len")
+        if self.kv_len is None:
+            self.kv_len = torch.tensor([case.ctx + M], dtype=i32, device=device)
+        self.cache_loc = io.get("cache_loc")
+        if self.cache_loc is None:
+            self.cache_loc = torch.arange(case.ctx, case.ctx + M, dtype=i32, device=device)
         self.kv_rows = kv_rows
         # outputs
         self.o = dict(
@@ -120,7 +144,7 @@ class LayerRank:
         bind = host.make(
             "MkLayerBind",
             qkv_in=w["qkv_in"], k_cache=self.k_cache, v_cache=self.v_cache, kv_rows=self.kv_rows,
-            page_table=self.page_table, kv_len=self.kv_len, page_stride=self.kv_rows, x_attn=o["x_attn"],
+            page_table=self.page_table, kv_len=self.kv_len, page_stride=self.page_table.numel(), x_attn=o["x_attn"],
             w_o=w["o_proj"], ar=self.ar, ar_peer=peer("ar"), branch=o["branch"], stream_in=w["stream_in"],
             alpha=w["post_alpha"], beta=w["post_beta"], prenorm_w=w["post_pre_w"], stream_out=o["stream_mid"],
             h3=o["h3"], h3f=o["h3f"], w_p=w["pooler"], pool_ag=self.pool_ag, pool_ag_peer=peer("pool_ag"),
@@ -136,7 +160,7 @@ class LayerRank:
             unpool_ag_peer=peer("unpool_ag"), c_alpha=w["cross_alpha"], c_beta=w["cross_beta"], c_pre_w=w["cross_pre_w"],
             c_post_w=w["cross_post_w"], c_stream_out=o["stream_out"], h3q=o["h3_next"], w_qkv=w["next_qkv"],
             qkv_out=o["qkv_next"], cos_sin=w["next_cos_sin"], cache_loc=self.cache_loc, next_k_cache=self.next_k,
-            next_v_cache=self.next_v, next_kv_rows=self.kv_rows, q_scale=cfg.q_scale, qkv_eps=cfg.rms_eps,
+            next_v_cache=self.next_v, next_kv_rows=self.next_kv_rows, q_scale=cfg.q_scale, qkv_eps=cfg.rms_eps,
             flags=self.flags, flags_peer=peer("flags"), ws=self.ws, status=self.status, b_live=b_live, wait_budget=0,
         )  # fmt: skip
         self.launch_record = self.lib.layer_bind(self.module, self.shape, bind)

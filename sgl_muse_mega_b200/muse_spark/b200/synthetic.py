@@ -252,3 +252,50 @@ def layer_case(
             t.update(gate_q=gq, gate_sf=gs, up_q=uq, up_sf=us, w2_q=wq, w2_sf=ws, **alphas)
         case.ranks.append(RankTensors(**t))
     return case
+
+
+@dataclass
+class StackCase:
+    """A run of decoder layers with the step's head and tail: per rank the vocab shard of the embedding and of the
+    lm_head and layer 0's qkv weights; replicated: layer 0's pre-attention norm weight and the RoPE cache."""
+
+    cfg: Config
+    rows: int
+    ctx: int
+    seed: int
+    layers: list  # LayerCase per layer, in order
+    embed: list  # per drawn rank: [vocab_rank, H] bf16
+    lm_head: list  # per drawn rank: [vocab_rank, H] bf16
+    qkv0: list  # per drawn rank: [qkv_row, H] bf16
+    pre_w0: torch.Tensor  # [H] bf16
+    cos_sin_cache: torch.Tensor  # [positions, 64] f32
+    ranks: list  # the ranks drawn, in the order of the per-rank lists
+
+
+def stack_case(cfg: Config, *, n_layers: int, rows: int, ctx: int, seed: int = 0, band: str = "baseline",
+               only_ranks: Optional[list] = None, max_pos: Optional[int] = None, first_layer: int = 0) -> StackCase:  # fmt: skip
+    """Layers ``first_layer .. first_layer + n_layers - 1`` of a model of ``cfg.layers`` layers with the variants the
+    model gives them (sliding-window / global by ``cfg.is_global``, bf16 experts by ``cfg.bf16_moe_layers``); the last
+    drawn layer is the tail (its cross-layer norm is the final norm, no successor head)."""
+    ranks = list(only_ranks) if only_ranks is not None else list(range(cfg.tp))
+    bf = torch.bfloat16
+    layers = []
+    for j in range(n_layers):
+        i = first_layer + j
+        tail = j == n_layers - 1
+        layers.append(
+            layer_case(cfg, rows=rows, ctx=ctx, global_attn=cfg.is_global(i), bf16=cfg.is_bf16(i),
+                       next_global=(not tail) and cfg.is_global(i + 1), tail=tail, band=band, seed=seed, layer=i,
+                       only_ranks=ranks)  # fmt: skip
+        )
+    H = cfg.hidden
+    cache = rope_rows(cfg, torch.arange(max_pos or (ctx + 64 * rows))).to(_DEVICE)
+    return StackCase(
+        cfg, rows, ctx, seed, layers,
+        embed=[normal((cfg.vocab_rank, H), 1.0, bf, seed, "embed", r) for r in ranks],
+        lm_head=[normal((cfg.vocab_rank, H), H**-0.5, bf, seed, "lm_head", r) for r in ranks],
+        qkv0=[normal((cfg.qkv_row, H), H**-0.5, bf, seed, "qkv0", r) for r in ranks],
+        pre_w0=uniform((H,), 0.8, 1.2, bf, seed, "pre_w0"),
+        cos_sin_cache=cache,
+        ranks=ranks,
+    )  # fmt: skip

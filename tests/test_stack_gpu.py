@@ -1,0 +1,157 @@
+"""A run of decoder layers with the step's head and tail (entry, layer 0's head, chained layer launches, lm_head, greedy
+accept) against the chained CPU oracle: per-stage with the kernel's own inputs, end to end, across steps and as one CUDA
+graph."""
+
+from dataclasses import replace
+
+import pytest
+import torch
+
+from oracle import dflash_accept as A
+from oracle import muse_layer as O
+from oracle import stack as OS
+from parity import check_world
+from sgl_muse_mega_b200.muse_spark.b200 import headtail as HT
+from sgl_muse_mega_b200.muse_spark.b200 import stack as S
+from sgl_muse_mega_b200.muse_spark.b200 import synthetic
+from sgl_muse_mega_b200.muse_spark.config import Config
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def small_cfg(tp: int) -> Config:
+    return Config(hidden=1024, q_heads=64, kv_heads=8, experts=16, topk=8, moe_hidden=1024, moe_inter=1024, swa_window=7,
+                  vocab=4096, layers=4, bf16_moe_layers=(0,), tp=tp, node_ranks=min(4, tp))  # fmt: skip
+
+
+class LayerView:
+    """Layer j of a stack world in the shape ``parity.check_world`` reads: the case carries the inputs the kernels
+    actually consumed (the predecessor's outputs on the device)."""
+
+    def __init__(self, world: S.StackWorld, j: int):
+        lc = world.case.layers[j]
+        ranks = []
+        for st, t in zip(world.ranks, lc.ranks):
+            lr = st.layers[j]
+            cs = None if t.next_cos_sin is None else st.feeds.cos_sin.cpu()
+            ranks.append(replace(t, qkv_in=lr.w["qkv_in"].cpu(), stream_in=lr.w["stream_in"].cpu(), next_cos_sin=cs))
+        self.case = replace(lc, ranks=ranks)
+        self.ranks = [st.layers[j] for st in world.ranks]
+
+
+def run_world(tp, rows, ctx, seed, **kw):
+    cfg = small_cfg(tp)
+    case = synthetic.stack_case(cfg, n_layers=4, rows=rows, ctx=ctx, seed=seed)
+    world = S.StackWorld(case, DEV, **kw)
+    tokens = torch.randint(0, cfg.vocab, (rows,), generator=torch.Generator().manual_seed(seed))
+    for st in world.ranks:
+        st.tokens.copy_(tokens)
+    return cfg, case, world, tokens
+
+
+@pytest.mark.parametrize("tp,rows,ctx", [(2, 16, 24), (1, 5, 40)])
+def test_stack_stagewise_and_end_to_end(tp, rows, ctx):
+    cfg, case, world, tokens = run_world(tp, rows, ctx, 21)
+    # snapshot each layer's view right after the run (the accept rewrites the feeds for the next step)
+    s = torch.cuda.current_stream().cuda_stream
+    for st in world.ranks:
+        st.feeds.launch(s)
+    torch.cuda.synchronize()
+    cos_sin0 = world.ranks[0].feeds.cos_sin.cpu().clone()
+    world.run_interleaved(feeds=False)
+    torch.cuda.synchronize()
+    for st in world.ranks:
+        assert st.statuses() == []
+    st0 = world.ranks[0]
+    # entry and layer 0's head against the oracle fed the same ids
+    ent = O.entry(tokens, case.embed, case.pre_w0, cfg.rms_eps, cfg.rms_eps)
+    for name, got in (("residual", st0.entry.residual.cpu()), ("normed", st0.entry.normed.cpu())):
+        _, rel, ok = O.compare(got, ent[name], name)
+        assert ok, (name, rel)
+    assert torch.equal(cos_sin0, case.cos_sin_cache[ctx : ctx + rows])
+    for r, st in enumerate(world.ranks):
+        ref = O.qkv_rowops(st.entry.normed.cpu(), case.qkv0[r], cfg.q_heads_rank, cfg.kv_heads_rank, cfg.q_scale,
+                           cfg.rms_eps, cos_sin0)  # fmt: skip
+        _, rel, ok = O.compare(st.qkv_head.out.cpu(), ref, "qkv_next")
+        assert ok, rel
+    # every layer, stage by stage, fed what the kernels consumed (the feeds' rope rows were still this step's when the
+    # layers ran; restore them for the comparison)
+    for st in world.ranks:
+        st.feeds.cos_sin.copy_(cos_sin0)
+    for j in range(len(case.layers)):
+        check_world(LayerView(world, j), list(range(tp)))
+    # the tail: logits of the kernel's own final hidden rows, their arg-max, the accept
+    hidden = st0.hidden.cpu()
+    for r, st in enumerate(world.ranks):
+        assert torch.equal(st.gathered, st0.gathered)
+    capped = O.logits_out(hidden, case.lm_head, cfg.output_multiplier, cfg.softcap)
+    got_capped = torch.tanh((st0.gathered.cpu() * cfg.output_multiplier) / cfg.softcap) * cfg.softcap
+    _, rel, ok = O.compare(got_capped, capped, "logits_out")
+    assert ok, rel
+    top1 = A.first_argmax(got_capped)
+    assert torch.equal(st0.accept.top1.cpu().long(), top1)
+    step = A.greedy_accept(tokens, got_capped, ctx)
+    words, ring = A.step_words(torch.tensor([ctx, 0, 0, 0, 0, 0, 0, 0]), torch.zeros(64, dtype=torch.int32), step, tokens)
+    for st in world.ranks:
+        assert torch.equal(st.accept.words.cpu(), words) and torch.equal(st.accept.out_ring.cpu(), ring)
+    # end to end against the unforced oracle chain: loose (the quantisers do not compose), but the same model
+    ref = OS.run_stack(case, tokens, ctx)
+    _, rel, _ = O.compare(hidden, ref["hidden"], "h3_next", tol=1.0)
+    assert rel < 0.25, rel
+    err = (got_capped - ref["logits"]).abs().max().item()
+    top2 = ref["logits"][0].topk(2).values
+    if float(top2[0] - top2[1]) > 4 * err:
+        assert int(top1[0]) == int(A.first_argmax(ref["logits"])[0])
+
+
+def test_stack_steps_with_forced_accept_and_graph():
+    """Three steps of a lone tp-1 stack with the forced-accept table (6 accepted drafts per step), eager and as one CUDA
+    graph: words, ring, feeds and the logits are bit-identical, and each step's KV rows land at the committed positions."""
+    cfg = small_cfg(1)
+    rows, ctx = 16, 24
+    case = synthetic.stack_case(cfg, n_layers=4, rows=rows, ctx=ctx, seed=5)
+    forced = torch.tensor([6], dtype=torch.int32, device=DEV)
+    gen = torch.Generator().manual_seed(1)
+    toks = [torch.randint(0, cfg.vocab, (rows,), generator=gen) for _ in range(3)]
+
+    def run(graph: bool):
+        st = S.Stack(case, 0, DEV, accept_override=forced)
+        st.bind()
+        s = torch.cuda.current_stream().cuda_stream
+        st.feeds.launch(s)
+        torch.cuda.synchronize()
+        if graph:
+            st.capture()  # its warm-up launch advanced the state: rewind
+            st.accept.words.zero_()
+            st.accept.words[HT.WORDS["P"]] = ctx
+            st.accept.out_ring.zero_()
+            st.feeds.launch(s)
+            for k, v in st.pools:
+                k[ctx:].zero_(), v[ctx:].zero_()
+            torch.cuda.synchronize()
+        out = []
+        for t in toks:
+            st.tokens.copy_(t)
+            if graph:
+                st.step()
+            else:
+                st.launch_all(s, pdl=False)
+            torch.cuda.synchronize()
+            out.append(dict(words=st.accept.words.cpu().clone(), ring=st.accept.out_ring.cpu().clone(),
+                            logits=st.gathered.cpu().clone(), kv_len=st.feeds.kv_len.cpu().clone(),
+                            loc=st.feeds.loc_swa.cpu().clone(), k0=st.pools[0][0].cpu().clone()))  # fmt: skip
+        assert st.statuses() == []
+        return out
+
+    eager, graph = run(False), run(True)
+    for i, (a, b) in enumerate(zip(eager, graph)):
+        for k in a:
+            assert torch.equal(a[k], b[k]), (i, k)
+        p = ctx + 7 * (i + 1)
+        assert a["words"][:5].tolist() == [p, int(a["ring"][7 * i + 6]), 6, 7, i + 1]
+        assert a["kv_len"].item() == p + rows and a["loc"].tolist() == list(range(p, p + rows))
+        assert a["ring"][7 * i : 7 * i + 6].tolist() == toks[i][1:7].tolist()
+    # step 1 wrote its window's K rows at positions ctx + 7 .. : the first 7 rows of step 0's window stay committed
+    assert torch.equal(eager[1]["k0"][ctx : ctx + 7], eager[0]["k0"][ctx : ctx + 7])
+    assert not torch.equal(eager[1]["k0"][ctx + 7 : ctx + 16], eager[0]["k0"][ctx + 7 : ctx + 16])
