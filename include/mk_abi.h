@@ -58,8 +58,9 @@ int mk_launch_info(const MkLaunch* launch, MkLaunchInfo* out);
 // No counterpart in the reference (its waits trap, K/README.md:111-121). Copies the launch's device status block to the
 // host (synchronises the stream first). code 0 = clean; otherwise the wait that gave up.
 typedef struct MkLaunchStatus {
-    int64_t code;      // 0 ok, 1 exchange flag wait expired, 2 grid counter wait expired
-    int64_t stage;     // stage index that recorded it
+    int64_t code;      // 0 ok, 1 an exchange wait ran out (a peer never signalled), 3 a bulk copy or tensor-core barrier
+                       // never completed, 4 an out-of-range position / request index was clamped
+    int64_t stage;     // stage index that recorded it (exchange waits), or a kernel-specific site number
     int64_t block;     // blockIdx.x
     int64_t observed;  // value seen
     int64_t expected;  // value waited for
@@ -191,8 +192,13 @@ typedef struct MkLayerBind {
     double q_scale;
     double qkv_eps;
     // exchange flags and private scratch
-    uint64_t flags;         // this rank's u32 [flag_words]
-    uint64_t flags_peer[MKH_RANKS];
+    // The flag block: u32 [flag_words], zeroed once by the caller, one per rank; it may be shared by all launches of a
+    // rank (the layers of a stack, the lm_head, the accept). Words [0, 8): one counter per exchange point (0 all-reduce,
+    // 1 pooler gather, 2 h planes, 3 expert outputs, 4 unpooler gather, 5 logits), advanced by every contributing rank's
+    // producer kernel once per launch; words [8, 24) are the owner's bookkeeping. flags 0: no signalling, the launches of
+    // the ranks are ordered by the caller (all ranks on one stream).
+    uint64_t flags;
+    uint64_t flags_peer[MKH_RANKS];  // the peers' flag blocks (0: absent), same presence as the *_peer data buffers
     uint64_t ws;            // ws_bytes of private scratch, zeroed once by the caller
     uint64_t status;        // status_bytes, zeroed once by the caller
     int64_t b_live;         // live window rows (abi.h:208-210)
@@ -260,6 +266,8 @@ typedef struct MkLmHeadBind {
     int64_t hidden;
     int64_t rows;
     uint64_t status;               // i32 [16] or 0: a weight copy that never landed is recorded here (code 3), not trapped
+    uint64_t flags;                // this rank's flag block and the peers' (as MkLayerBind); 0: no signalling
+    uint64_t flags_peer[MKH_RANKS];
 } MkLmHeadBind;
 int mk_lm_head_bind(MkModule* module, const MkLmHeadBind* bind, MkLaunch** out);
 
@@ -270,6 +278,10 @@ typedef struct MkSoftcapBind {
     int64_t numel;
     double scale;
     double cap;
+    uint64_t flags;        // this rank's flag block: wait for `contributors` lm_head shards per launch; 0: no wait
+    int64_t contributors;
+    int64_t wait_budget;   // polls (0: library default)
+    uint64_t status;       // i32 [16] or 0: a wait that ran out is recorded here (code 1)
 } MkSoftcapBind;
 int mk_softcap_bind(MkModule* module, const MkSoftcapBind* bind, MkLaunch** out);
 
@@ -303,8 +315,25 @@ typedef struct MkAcceptBind {
     uint64_t dslot;
     uint64_t dkv_len;
     int64_t dring;
+    uint64_t flags;            // as MkSoftcapBind
+    int64_t contributors;
+    int64_t wait_budget;
+    uint64_t status;
 } MkAcceptBind;
 int mk_accept_bind(MkModule* module, const MkAcceptBind* bind, MkLaunch** out);
+
+// ---- memory shared between the ranks' processes ----
+
+// Replaces the reference's symmetric allocations (sm103/buffers.py Symmetric, made there through torch's symmetric-memory
+// rendezvous): one process per GPU allocates its exchange buffers once, hands the 64-byte handle to its peers through any
+// channel (the host side uses torch.distributed.all_gather_object), and every peer maps the allocation into its own
+// address space; the kernels then store into the peers' buffers directly over NVLink. Plain CUDA IPC handles: no
+// multicast object is ever bound to the memory.
+#define MK_SYMM_HANDLE_BYTES 64
+int mk_symm_alloc(int64_t bytes, uint64_t* ptr, unsigned char* handle);  // device memory on the current device, zeroed
+int mk_symm_open(const unsigned char* handle, uint64_t* ptr);            // a peer's allocation, peer access enabled on demand
+int mk_symm_close(uint64_t ptr);                                         // unmaps what mk_symm_open returned
+int mk_symm_free(uint64_t ptr);                                          // frees what mk_symm_alloc returned
 
 // ---- layer 0's head: qkv GEMM + qk-norm + RoPE + K/V append as a stand-alone launch ----
 

@@ -73,10 +73,14 @@ def make(struct: str, **values) -> ctypes.Structure:
     return out
 
 
+SYMM_HANDLE_BYTES = 64  # MK_SYMM_HANDLE_BYTES
+
+
 EXPORTS = (
     "mk_last_error", "mk_module_load", "mk_module_free", "mk_launch", "mk_launch_step", "mk_launch_free",
     "mk_launch_info", "mk_launch_status", "mk_layer_constants", "mk_layer_bind", "mk_qkv_constants", "mk_qkv_bind",
     "mk_qkv_launch_static", "mk_feeds_bind", "mk_entry_bind", "mk_lm_head_bind", "mk_softcap_bind", "mk_accept_bind",
+    "mk_symm_alloc", "mk_symm_open", "mk_symm_close", "mk_symm_free",
 )  # fmt: skip
 
 
@@ -107,6 +111,10 @@ class Library:
         for fn, st in (("mk_feeds_bind", "MkFeedsBind"), ("mk_entry_bind", "MkEntryBind"), ("mk_lm_head_bind", "MkLmHeadBind"),
                        ("mk_softcap_bind", "MkSoftcapBind"), ("mk_accept_bind", "MkAcceptBind")):  # fmt: skip
             getattr(d, fn).argtypes = [vp, P(STRUCTS[st]), P(vp)]
+        d.mk_symm_alloc.argtypes = [ctypes.c_int64, P(ctypes.c_uint64), ctypes.c_char_p]
+        d.mk_symm_open.argtypes = [ctypes.c_char_p, P(ctypes.c_uint64)]
+        d.mk_symm_close.argtypes = [ctypes.c_uint64]
+        d.mk_symm_free.argtypes = [ctypes.c_uint64]
 
     def check(self, rc: int, what: str) -> None:
         if rc != 0:
@@ -150,6 +158,25 @@ class Library:
         fn = getattr(self.dll, fn_name)
         self.check(fn(module.handle if module else None, ctypes.byref(bind), ctypes.byref(out)), fn_name)
         return Launch(self, out, module)
+
+
+    # ---- memory shared between the ranks' processes ----
+    def symm_alloc(self, nbytes: int) -> tuple[int, bytes]:
+        """(device pointer, 64-byte handle) of zeroed memory on the current device that peer processes can map."""
+        ptr, handle = ctypes.c_uint64(), ctypes.create_string_buffer(SYMM_HANDLE_BYTES)
+        self.check(self.dll.mk_symm_alloc(nbytes, ctypes.byref(ptr), handle), "mk_symm_alloc")
+        return ptr.value, handle.raw
+
+    def symm_open(self, handle: bytes) -> int:
+        ptr = ctypes.c_uint64()
+        self.check(self.dll.mk_symm_open(handle, ctypes.byref(ptr)), "mk_symm_open")
+        return ptr.value
+
+    def symm_close(self, ptr: int) -> None:
+        self.check(self.dll.mk_symm_close(ptr), "mk_symm_close")
+
+    def symm_free(self, ptr: int) -> None:
+        self.check(self.dll.mk_symm_free(ptr), "mk_symm_free")
 
 
 def _free_with(obj, fn, handle) -> None:

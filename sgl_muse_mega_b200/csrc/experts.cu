@@ -95,7 +95,10 @@ __global__ void __launch_bounds__(256) g1_kernel(const ExpertArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     griddep_wait();
     const int ai = blockIdx.y;
-    if (ai >= a.rt->n_active) return;
+    if (ai >= a.rt->n_active) {  // an idle CTA still arrives at the exchange
+        xchg_signal(a.sig_g1);
+        return;
+    }
     const int e = a.rt->act_e[ai], s0 = a.rt->act_off[ai], n_tok = a.rt->act_off[ai + 1] - s0;
     const int fg = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     float* accs = (float*)smem;                       // [32 rows][16 tokens]
@@ -157,8 +160,7 @@ __global__ void __launch_bounds__(256) g1_kernel(const ExpertArgs a) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) dst[i] = out[i];
             }
-            return;
-        }
+        } else {
         const float a1 = a.g1_alphas[e] * a.x_scale[tok], c1 = a.g1_scale_c[e];
         float amax = 0.f;
 #pragma unroll
@@ -184,15 +186,21 @@ __global__ void __launch_bounds__(256) g1_kernel(const ExpertArgs a) {
             a.zsf_peer[p][(size_t)slot * (a.I / 16) + gcol] = (unsigned char)sfb;
             a.zex_peer[p][(size_t)slot * (a.I / 16) + gcol] = (signed char)eg;
         }
+        }
     }
+    xchg_signal(a.sig_g1);
 }
 
 // g2: grid (H_s / 16, max_active), 256 threads, dynamic smem = 16 rows x I two-byte elements + accumulators
 __global__ void __launch_bounds__(256) g2_kernel(const ExpertArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     griddep_wait();
+    xchg_wait(a.wait_g2);
     const int ai = blockIdx.y;
-    if (ai >= a.rt->n_active) return;
+    if (ai >= a.rt->n_active) {
+        xchg_signal(a.sig_g2);
+        return;
+    }
     const int e = a.rt->act_e[ai], s0 = a.rt->act_off[ai], n_tok = a.rt->act_off[ai + 1] - s0;
     const int rg = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     float* accs = (float*)smem;  // [16 rows][16 tokens]
@@ -242,6 +250,7 @@ __global__ void __launch_bounds__(256) g2_kernel(const ExpertArgs a) {
         const bf16 b = __float2bfloat16_rn(v);
         for (int p = 0; p < a.n_peer; ++p) a.zb_peer[p][(size_t)slot * a.P + a.rank * a.H_s + rg * 16 + ri] = b;
     }
+    xchg_signal(a.sig_g2);
 }
 
 size_t g1_smem(int P) { return 32 * 16 * sizeof(float) + (size_t)kMaxRows * P * 2; }

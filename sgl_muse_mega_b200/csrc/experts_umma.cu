@@ -364,6 +364,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
     tc_fence_before();
     __syncthreads();
     if (warp == 2) tmem_dealloc(tmem, kTmemCols);
+    xchg_signal(a.sig);  // every CTA arrives, also one that had no unit
 }
 
 size_t experts_umma_smem(bool g2) {

@@ -209,6 +209,7 @@ __global__ void __launch_bounds__(256) skinny_gemm_kernel(const GemmArgs a) {
     }
     // no CTA leaves while another may still read its partial tile
     if (ksplit > 1) cluster_sync_all();
+    xchg_signal(a.sig);
 }
 
 // ---- host side ----

@@ -99,6 +99,7 @@ __global__ void __launch_bounds__(1024) entry_kernel(const EntryArgs a) {
 // ---- soft cap ---------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) softcap_kernel(const SoftcapArgs a) {
     griddep_wait();
+    xchg_wait(a.wait);
     for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < a.numel; i += (long long)gridDim.x * 256)
         a.out[i] = tanhf((a.x[i] * a.scale) / a.cap) * a.cap;
 }
@@ -130,6 +131,7 @@ __global__ void __launch_bounds__(1024) accept_kernel(const AcceptArgs a) {
     __shared__ int s_last;
     __shared__ long long s_cc, s_p;
     griddep_wait();
+    xchg_wait(a.wait);
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* x = a.logits + (size_t)row * a.vocab;
     Best best{-INFINITY, 0x7fffffff, 0};

@@ -12,6 +12,79 @@ constexpr int kMaxRows = 16;
 constexpr int kMaxSlots = 128;  // rows x topk
 constexpr int kHeadDim = 64;
 
+// ---- cross-GPU exchange points -----------------------------------------------------------------------------------------
+// A tensor-parallel world of one process per GPU synchronises each exchange (the kernels store their results straight
+// into the peers' buffers) with one counter word per exchange point in every rank's flag block:
+//   producer kernel   every CTA: stores, barrier, system fence, arrive on a local counter; the last CTA advances the local
+//                     epoch word and adds 1 to the exchange's word on every rank that received data (own included);
+//   consumer kernel   after its programmatic-launch wait, one thread per CTA polls its own word until it reaches
+//                     epoch x contributors, at most `budget` polls; a wait that runs out records itself in the status
+//                     block and the kernel carries on (its outputs are then meaningless, nothing hangs).
+// The words only grow; a launch sequence replayed from a CUDA graph needs no host-side reset. All-zero records (the
+// default) switch the mechanism off: a world emulated on one GPU orders its launches on the stream instead.
+constexpr int kXchgPoints = 8;   // words [0, 8) of the flag block: exchange counters (written by peers)
+constexpr int kXchgEpoch = 8;    // words [8, 16): this rank's epoch per exchange (local)
+constexpr int kXchgDone = 16;    // words [16, 24): CTA arrival counters of the producers (local)
+constexpr int kXchgWords = 32;
+
+struct XchgSignal {
+    unsigned* flag[kMaxRanks];  // the exchange's word on every receiving rank
+    int n;                      // 0: off
+    unsigned* done;
+    unsigned* epoch;
+};
+struct XchgWait {
+    const unsigned* flag;       // this rank's word of the exchange; null: off
+    const unsigned* epoch;
+    unsigned contributors;      // signals per epoch
+    long long budget;           // polls before giving up
+    int* status;
+    int stage;                  // recorded with a wait that ran out
+};
+
+// Every thread of every CTA calls this after the kernel's last store to a peer.
+__device__ __forceinline__ void xchg_signal(const XchgSignal& x) {
+    if (x.n == 0) return;
+    __syncthreads();
+    if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
+        __threadfence_system();
+        const unsigned total = gridDim.x * gridDim.y * gridDim.z;
+        if (atomicAdd(x.done, 1u) == total - 1) {
+            *x.done = 0;
+            *(volatile unsigned*)x.epoch = *(volatile unsigned*)x.epoch + 1;
+            __threadfence_system();
+            for (int i = 0; i < x.n; ++i) atomicAdd_system(x.flag[i], 1u);
+        }
+    }
+}
+
+// Every thread of every CTA calls this after griddep_wait() and before the first read of exchanged data.
+__device__ __forceinline__ void xchg_wait(const XchgWait& w) {
+    if (w.flag == nullptr) return;
+    if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
+        const unsigned want = *(volatile const unsigned*)w.epoch * w.contributors;
+        long long polls = 0;
+        for (;;) {
+            unsigned seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(w.flag) : "memory");
+            if ((int)(seen - want) >= 0) break;
+            // a failure already on record (an earlier wait that ran out): do not wait a full budget again
+            if ((polls & 1023) == 1023 && w.status != nullptr && *(volatile int*)w.status != 0) break;
+            if (++polls > w.budget) {  // give up: record once per launch, never trap
+                if (w.status != nullptr && atomicCAS(w.status, 0, 1) == 0) {
+                    w.status[1] = w.stage;
+                    w.status[2] = (int)blockIdx.x;
+                    w.status[3] = (int)seen;
+                    w.status[4] = (int)want;
+                }
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+    __syncthreads();
+}
+
 // Route tables in the private scratch, written by the routing kernel each launch.
 struct RouteTables {
     int n_active;                   // distinct routed experts
@@ -42,6 +115,7 @@ struct GemmArgs {
     float q_scale, eps;
     int qh, kvh, kv_row_bytes;
     int* status;          // the launch's status block (a bulk copy that never lands records itself); may be null
+    XchgSignal sig;       // the exchange this GEMM's peer stores feed (off when n == 0)
 };
 
 }  // namespace mk

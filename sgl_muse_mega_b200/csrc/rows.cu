@@ -34,6 +34,7 @@ __global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
     __shared__ float red[33];
     griddep_wait();
     griddep_launch();
+    xchg_wait(a.wait);  // the all-reduce partials (mode 0) or the unpooler gather (mode 1) of every contributing rank
     const int row = blockIdx.x, c0 = threadIdx.x * 8;
     const size_t off = (size_t)row * a.H + c0;
     float v[8];
@@ -269,6 +270,7 @@ __global__ void __launch_bounds__(512) route_nq_kernel(const RouteNqArgs a) {
     griddep_wait();
     griddep_launch();
     if (blockIdx.x > 0) {
+        xchg_wait(a.nq.wait);  // the pooler gather of the node's ranks
         nq_row(a.nq, blockIdx.x - 1, red);
         return;
     }
@@ -292,10 +294,11 @@ __device__ __forceinline__ uint32_t scale_down_byte(uint32_t byte, int delta) {
 }
 
 __global__ void __launch_bounds__(256) hrow_kernel(const unsigned char* z_sf, const signed char* z_ex, int groups, int slots_live,
-                                                   unsigned char* z_sfd, float* rowscale) {
+                                                   unsigned char* z_sfd, float* rowscale, const XchgWait wait) {
     __shared__ float red[33];
     griddep_wait();
     griddep_launch();
+    xchg_wait(wait);  // every rank's column band of the h planes
     const int slot = blockIdx.x, tid = threadIdx.x;
     if (slot >= slots_live) return;
     float mx = -1000.f;
@@ -321,6 +324,7 @@ __global__ void __launch_bounds__(512) combine_kernel(const CombineArgs a) {
     griddep_launch();
     const int row = blockIdx.x, tid = threadIdx.x, c0 = tid * 8, warp = tid >> 5, lane = tid & 31;
     const int nw = blockDim.x >> 5;
+    xchg_wait(a.wait);  // every rank's column band of the expert outputs
     if (row >= a.b_live) {
         *(uint4*)(a.y + (size_t)row * a.P + c0) = make_uint4(0, 0, 0, 0);
         return;
@@ -423,8 +427,8 @@ cudaError_t route_nq_launch(const TopkArgs& t, const NqArgs& n, RouteTables* rt,
     return launch1(route_nq_kernel, dim3(1 + t.M), dim3(512), s, pdl, a);
 }
 cudaError_t hrow_launch(const unsigned char* z_sf, const signed char* z_ex, int groups, int slots_live, int slots,
-                        unsigned char* z_sfd, float* rowscale, cudaStream_t s, bool pdl) {
-    return launch1(hrow_kernel, dim3(slots), dim3(256), s, pdl, z_sf, z_ex, groups, slots_live, z_sfd, rowscale);
+                        unsigned char* z_sfd, float* rowscale, const XchgWait& wait, cudaStream_t s, bool pdl) {
+    return launch1(hrow_kernel, dim3(slots), dim3(256), s, pdl, z_sf, z_ex, groups, slots_live, z_sfd, rowscale, wait);
 }
 cudaError_t combine_launch(const CombineArgs& a, int M, cudaStream_t s, bool pdl) {
     return launch1(combine_kernel, dim3(M), dim3(a.P / 8), s, pdl, a);

@@ -71,6 +71,7 @@ struct MkLaunch {
     int sms;
     mk::UmmaArgs umma_g1, umma_g2;
     bool stage_on[ST_COUNT];
+    mk::XchgWait hrow_wait;
     // stand-alone launches around the layers (feeds, entry, lm_head, soft cap, accept): n_ops > 0 replaces the stage list
     int n_ops;
     int op_kind[4];
@@ -80,6 +81,9 @@ struct MkLaunch {
     mk::AcceptArgs accept;
     mk::GemmArgs op_gemm;
 };
+// exchange points (word index in a rank's flag block) and the default poll budget of a wait (~64 ns a poll: about 0.3 s)
+enum XchgPoint { XP_AR = 0, XP_POOL, XP_Z, XP_ZB, XP_UNPOOL, XP_LOGITS };
+static const long long kDefaultWaitBudget = 1ll << 22;
 enum OpKind { OP_FEEDS = 1, OP_ENTRY, OP_GEMM_BF16, OP_SOFTCAP, OP_ACCEPT };
 
 using namespace mk;
@@ -258,6 +262,31 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     };
     const int node0 = (int)(s.rank - s.rank % s.node_ranks), nr = (int)s.node_ranks, jnode = (int)(s.rank % s.node_ranks);
 
+    // exchange points: the ranks of a group that are present (own flag block and the peers' that are bound) signal and are
+    // waited for; without a flag block the launches rely on stream order alone
+    unsigned* const flags = (unsigned*)b->flags;
+    const long long budget = b->wait_budget > 0 ? b->wait_budget : kDefaultWaitBudget;
+    auto flag_of = [&](int r) -> unsigned* { return (unsigned*)(r == s.rank ? b->flags : b->flags_peer[r]); };
+    auto signal_to = [&](XchgSignal& x, int point, int first, int count) {
+        memset(&x, 0, sizeof x);
+        if (flags == nullptr) return;
+        for (int r = first; r < first + count; ++r)
+            if (flag_of(r)) x.flag[x.n++] = flag_of(r) + point;
+        x.done = flags + kXchgDone + point;
+        x.epoch = flags + kXchgEpoch + point;
+    };
+    auto wait_for = [&](XchgWait& w, int point, int first, int count, int stage) {
+        memset(&w, 0, sizeof w);
+        if (flags == nullptr) return;
+        for (int r = first; r < first + count; ++r) w.contributors += flag_of(r) != nullptr;
+        w.flag = flags + point;
+        w.epoch = flags + kXchgEpoch + point;
+        w.budget = budget;
+        w.status = (int*)b->status;
+        w.stage = stage;
+    };
+    const int all = (int)s.ranks;
+
     // scratch carve (must follow fill_constants)
     unsigned char* ws = (unsigned char*)b->ws;
     size_t off = 0;
@@ -310,12 +339,14 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
         L->oproj.n_out = n;
         L->oproj.ldo = H;
         L->oproj.col0 = 0;
+        signal_to(L->oproj.sig, XP_AR, 0, all);
     }
     // pooler: the node block of rows [j P/nr, (j+1) P/nr) -> the node's gather rows
     if (gemm(L->pooler, 0, false, b->w_p + (uint64_t)jnode * (P / nr) * H * 2, b->h3, P / nr, H, H)) return -1;
     L->pooler.n_out = peers(b->pool_ag_peer, b->pool_ag, L->pooler.out, node0, nr);
     L->pooler.ldo = P;
     L->pooler.col0 = jnode * (P / nr);
+    signal_to(L->pooler.sig, XP_POOL, node0, nr);
     // router: f32 weights through tf32, f32 activations, f32 logits (replicated on every rank)
     if (gemm(L->router, 0, true, b->w_r, b->h3f, E, H, H)) return -1;
     L->router.out[0] = (void*)b->logits;
@@ -327,6 +358,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     L->unpool.n_out = peers(b->unpool_ag_peer, b->unpool_ag, L->unpool.out, node0, nr);
     L->unpool.ldo = H;
     L->unpool.col0 = jnode * (H / nr);
+    signal_to(L->unpool.sig, XP_UNPOOL, node0, nr);
     // successor's qkv
     if (!tail) {
         if (gemm(L->qkv, 1, false, b->w_qkv, b->h3q, (int)c.qkv_row, H, H)) return -1;
@@ -351,11 +383,16 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     L->cross_norm = NormArgs{1, H, (int)s.ranks, (const bf16*)b->unpool_ag, nullptr, (const float*)b->stream_out,
                              (const float*)b->c_alpha, (const float*)b->c_beta, (const bf16*)b->c_pre_w, (const bf16*)b->c_post_w,
                              (float*)b->c_stream_out, (bf16*)b->h3q, nullptr, M};
+    wait_for(L->post_norm.wait, XP_AR, 0, all, ST_POST_NORM);
+    wait_for(L->cross_norm.wait, XP_UNPOOL, node0, nr, ST_CROSS_NORM);
     L->topk = TopkArgs{(const float*)b->logits, (const float*)b->expert_bias, (int*)b->topk_idx32, (float*)b->topk_w,
                        b->router_mult, (float)b->route_scale, E, K, M};
     L->nq = NqArgs{(const bf16*)b->pool_ag, (const bf16*)b->gamma, (unsigned char*)b->q, (unsigned char*)b->sf,
                    (float*)b->x_scale, (float)b->eps, P, (int)s.bf16};
     L->combine = CombineArgs{(const bf16*)b->zb, (const float*)b->topk_w, (const bf16*)b->gamma_p1, (bf16*)b->y, P, K, b_live};
+    wait_for(L->nq.wait, XP_POOL, node0, nr, ST_NQ);
+    wait_for(L->combine.wait, XP_ZB, 0, all, ST_COMBINE);
+    wait_for(L->hrow_wait, XP_Z, 0, all, ST_HROW);
     L->rowops = RowopsArgs{(bf16*)b->qkv_out, s.next_rope ? (const float*)b->cos_sin : nullptr, (const int*)b->cache_loc,
                            (unsigned char*)b->next_k_cache, (unsigned char*)b->next_v_cache, (float)b->q_scale, (float)b->qkv_eps,
                            M, qh, kvh, (int)c.qkv_row, (int)c.kv_row_bytes};
@@ -389,6 +426,9 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     ex.w2 = (const unsigned char*)b->w2;
     ex.w2_sf = (const unsigned char*)b->w2_sf;
     ex.g2_alphas = (const float*)b->g2_alphas;
+    signal_to(ex.sig_g1, XP_Z, 0, all);
+    signal_to(ex.sig_g2, XP_ZB, 0, all);
+    if (!fp4) wait_for(ex.wait_g2, XP_Z, 0, all, ST_G2);  // no h-row kernel in a bf16 layer: g2 itself waits
     MK_REQUIRE(g1_smem(P) <= 200 * 1024 && g2_smem(I) <= 200 * 1024, "expert rows exceed shared memory");
     L->use_umma = use_umma;
     L->sms = module ? module->sms : 148;
@@ -416,6 +456,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
             }
             u.n_peer = ex.n_peer;
             u.status = L->status;
+            u.sig = g2 ? ex.sig_g2 : ex.sig_g1;
         }
     }
     *out = L;
@@ -444,7 +485,7 @@ static int run_stage(const MkLaunch* L, int st, cudaStream_t s, bool pdl) {
             break;
         case ST_HROW:
             e = hrow_launch((const unsigned char*)L->bind.z_sf, (const signed char*)L->bind.z_ex, (int)L->shape.inter / 16,
-                            L->slots_live, (int)L->consts.slots, L->z_sfd, L->rowscale, s, pdl);
+                            L->slots_live, (int)L->consts.slots, L->z_sfd, L->rowscale, L->hrow_wait, s, pdl);
             break;
         case ST_G2:
             e = L->use_umma ? experts_umma_launch(L->umma_g2, true, L->sms, s, pdl) : g2_launch(L->ex, L->max_active, s, pdl);
@@ -548,6 +589,18 @@ int mk_launch_info(const MkLaunch* launch, MkLaunchInfo* out) {
 
 // ---- feeds, entry, lm_head, soft cap, accept ----
 
+// the wait of the step's tail (soft cap or accept) for every rank's lm_head shard
+static void logits_wait(XchgWait& w, uint64_t flags, int64_t contributors, int64_t budget, uint64_t status) {
+    memset(&w, 0, sizeof w);
+    if (flags == 0 || contributors <= 0) return;
+    w.flag = (const unsigned*)flags + XP_LOGITS;
+    w.epoch = (const unsigned*)flags + kXchgEpoch + XP_LOGITS;
+    w.contributors = (unsigned)contributors;
+    w.budget = budget > 0 ? budget : kDefaultWaitBudget;
+    w.status = (int*)status;
+    w.stage = 100 + XP_LOGITS;
+}
+
 static MkLaunch* new_op_launch(MkModule* module, int kind) {
     MkLaunch* L = new (std::nothrow) MkLaunch();
     if (L == nullptr) return nullptr;
@@ -626,6 +679,19 @@ int mk_lm_head_bind(MkModule* module, const MkLmHeadBind* b, MkLaunch** out) {
         if (b->out_peer[r]) g.out[g.n_out++] = (void*)b->out_peer[r];
     g.ldo = (int)b->v_total; g.col0 = (int)b->col0; g.out_f32 = 1;
     g.status = L->status = (int*)b->status;
+    if (b->flags) {
+        unsigned* const flags = (unsigned*)b->flags;
+        for (int r = 0; r < MKH_RANKS; ++r) {
+            unsigned* f = (unsigned*)(r == b->rank ? b->flags : b->flags_peer[r]);
+            if ((f != nullptr) != (b->out_peer[r] != 0)) {
+                delete L;
+                return fail("flags_peer[%d] and out_peer[%d] disagree on the rank's presence", r, r);
+            }
+            if (f) g.sig.flag[g.sig.n++] = f + XP_LOGITS;
+        }
+        g.sig.done = flags + kXchgDone + XP_LOGITS;
+        g.sig.epoch = flags + kXchgEpoch + XP_LOGITS;
+    }
     *out = L;
     return 0;
 }
@@ -637,6 +703,8 @@ int mk_softcap_bind(MkModule* module, const MkSoftcapBind* b, MkLaunch** out) {
     MkLaunch* L = new_op_launch(module, OP_SOFTCAP);
     MK_REQUIRE(L != nullptr, "out of host memory");
     L->softcap = SoftcapArgs{(const float*)b->x, (float*)b->out, b->numel, (float)b->scale, (float)b->cap};
+    logits_wait(L->softcap.wait, b->flags, b->contributors, b->wait_budget, b->status);
+    L->status = (int*)b->status;
     *out = L;
     return 0;
 }
@@ -659,6 +727,8 @@ int mk_accept_bind(MkModule* module, const MkAcceptBind* b, MkLaunch** out) {
                            b->cos_sin_rows, (float*)b->cos_sin, (int*)b->loc_full, (int*)b->loc_swa, (int*)b->kv_len,
                            (const float*)b->dcos_sin_cache, b->dcos_sin_rows, (float*)b->dcos_sin, (int*)b->dslot, (int*)b->dkv_len,
                            (int)b->dring};
+    logits_wait(L->accept.wait, b->flags, b->contributors, b->wait_budget, b->status);
+    L->status = (int*)b->status;
     *out = L;
     return 0;
 }
@@ -789,6 +859,52 @@ int mk_qkv_launch_static(const MkQkvBind* b, uint64_t stream) {
     if (e != cudaSuccess) return cuda_fail(e, "qkv GEMM launch");
     e = rowops_launch(r, (cudaStream_t)stream, false);
     if (e != cudaSuccess) return cuda_fail(e, "qkv row ops launch");
+    return 0;
+}
+
+// ---- memory shared between the ranks' processes ----
+
+int mk_symm_alloc(int64_t bytes, uint64_t* ptr, unsigned char* handle) {
+    MK_REQUIRE(ptr != nullptr && handle != nullptr, "ptr or handle is NULL");
+    MK_REQUIRE(bytes > 0, "bytes %lld", (long long)bytes);
+    static_assert(sizeof(cudaIpcMemHandle_t) <= MK_SYMM_HANDLE_BYTES, "handle does not fit");
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, (size_t)bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc");
+    e = cudaMemset(p, 0, (size_t)bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return cuda_fail(e, "cudaIpcGetMemHandle");
+    }
+    memset(handle, 0, MK_SYMM_HANDLE_BYTES);
+    memcpy(handle, &h, sizeof h);
+    *ptr = (uint64_t)p;
+    return 0;
+}
+
+int mk_symm_open(const unsigned char* handle, uint64_t* ptr) {
+    MK_REQUIRE(ptr != nullptr && handle != nullptr, "ptr or handle is NULL");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof h);
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaIpcOpenMemHandle");
+    *ptr = (uint64_t)p;
+    return 0;
+}
+
+int mk_symm_close(uint64_t ptr) {
+    cudaError_t e = cudaIpcCloseMemHandle((void*)ptr);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaIpcCloseMemHandle");
+    return 0;
+}
+
+int mk_symm_free(uint64_t ptr) {
+    cudaError_t e = cudaFree((void*)ptr);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFree");
     return 0;
 }
 

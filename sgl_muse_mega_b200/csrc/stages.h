@@ -28,6 +28,7 @@ struct NormArgs {
     bf16* normed;
     float* normed_f32;
     int M;
+    XchgWait wait;
 };
 struct TopkArgs {
     const float* logits;
@@ -46,6 +47,7 @@ struct NqArgs {
     float* x_scale;
     float eps;
     int P, bf16_out;
+    XchgWait wait;
 };
 struct CombineArgs {
     const bf16* zb;
@@ -53,6 +55,7 @@ struct CombineArgs {
     const bf16* gamma_p1;
     bf16* y;
     int P, k, b_live;
+    XchgWait wait;
 };
 struct RowopsArgs {
     bf16* qkv;
@@ -86,6 +89,8 @@ struct ExpertArgs {
     const unsigned char* w2_sf;
     const float* g2_alphas;
     bf16* zb_peer[kMaxRanks];
+    XchgSignal sig_g1, sig_g2;  // the h planes (g1) and the expert outputs (g2) that go to every rank
+    XchgWait wait_g2;           // a bf16 layer has no h-row kernel: g2 itself waits for the h planes
 };
 
 // gemm.cu: cluster split-K, no global scratch. gemm_plan fills wn / ksplit of a GEMM (-1: the shape has no valid plan).
@@ -120,7 +125,7 @@ cudaError_t resid_norm_launch(const NormArgs& a, cudaStream_t s, bool pdl);
 // one launch: block 0 routes (top-k + route tables), blocks 1..M run the pre-expert norm + quantisation of one row each
 cudaError_t route_nq_launch(const TopkArgs& t, const NqArgs& n, RouteTables* rt, int b_live, cudaStream_t s, bool pdl);
 cudaError_t hrow_launch(const unsigned char* z_sf, const signed char* z_ex, int groups, int slots_live, int slots,
-                        unsigned char* z_sfd, float* rowscale, cudaStream_t s, bool pdl);
+                        unsigned char* z_sfd, float* rowscale, const XchgWait& wait, cudaStream_t s, bool pdl);
 cudaError_t combine_launch(const CombineArgs& a, int M, cudaStream_t s, bool pdl);
 cudaError_t rowops_launch(const RowopsArgs& a, cudaStream_t s, bool pdl);
 size_t g1_smem(int P);
@@ -149,6 +154,7 @@ struct UmmaArgs {
     bf16* zb_peer[kMaxRanks];
     int n_peer;
     int* status;
+    XchgSignal sig;  // the exchange this phase's peer stores feed
 };
 // headtail.cu: the kernels around the decoder layers
 struct FeedsArgs {
@@ -188,6 +194,7 @@ struct SoftcapArgs {
     float* out;
     long long numel;
     float scale, cap;
+    XchgWait wait;
 };
 struct AcceptArgs {
     const float* logits;              // f32 [rows, vocab] gathered, before the soft cap
@@ -213,6 +220,7 @@ struct AcceptArgs {
     int* dslot;
     int* dkv_len;
     int dring;
+    XchgWait wait;                    // the lm_head shards of every rank
 };
 cudaError_t feeds_launch(const FeedsArgs& a, cudaStream_t s, bool pdl);
 cudaError_t entry_launch(const EntryArgs& a, cudaStream_t s, bool pdl);

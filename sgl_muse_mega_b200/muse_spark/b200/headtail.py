@@ -56,12 +56,16 @@ class Entry:
     """ids -> residual (f32) and layer 0's normed input (bf16); ``embed_shards`` are every rank's vocab rows (this
     rank's own tensor and its peers' mapped buffers)."""
 
-    def __init__(self, lib: host.Library, module, *, ids, embed_shards: Sequence[torch.Tensor], pre_w,
-                 eps_embed: float = 1e-5, eps_pre: float = 1e-5):  # fmt: skip
+    def __init__(self, lib: host.Library, module, *, ids, embed_shards: Sequence, pre_w, eps_embed: float = 1e-5,
+                 eps_pre: float = 1e-5, shard_rows: Optional[int] = None, hidden: Optional[int] = None,
+                 residual=None, normed=None):  # fmt: skip
+        """``embed_shards``: tensors, or device addresses (then ``shard_rows`` and ``hidden`` say their shape).
+        ``residual`` / ``normed``: the outputs, when the caller has already bound other launches to them."""
         dev, rows = ids.device, ids.shape[0]
-        shard_rows, hidden = embed_shards[0].shape
-        self.residual = _z(rows, hidden, dtype=torch.float32, device=dev)
-        self.normed = _z(rows, hidden, dtype=torch.bfloat16, device=dev)
+        if shard_rows is None:
+            shard_rows, hidden = embed_shards[0].shape
+        self.residual = residual if residual is not None else _z(rows, hidden, dtype=torch.float32, device=dev)
+        self.normed = normed if normed is not None else _z(rows, hidden, dtype=torch.bfloat16, device=dev)
         self.keep = (ids, list(embed_shards), pre_w)
         self.bind = host.make(
             "MkEntryBind", ids=ids, embed_peer=list(embed_shards), shard_rows=shard_rows, ranks=len(embed_shards),
@@ -75,14 +79,19 @@ class LmHead:
     """One rank's vocab shard against the final hidden rows, f32, stored at column ``rank * n_out`` of every rank's
     gathered logits (``gathered[r]`` is rank r's [rows, v_total] buffer; absent ranks are None)."""
 
-    def __init__(self, lib: host.Library, module, *, w, x, gathered: Sequence[Optional[torch.Tensor]], rank: int):
+    def __init__(self, lib: host.Library, module, *, w, x, gathered: Sequence[Optional[torch.Tensor]], rank: int,
+                 flags=None, flags_peer: Sequence = (), v_total: Optional[int] = None):  # fmt: skip
+        """``gathered``: tensors, or device addresses (then ``v_total`` is their row length). ``flags`` /
+        ``flags_peer``: this rank's flag block and the peers' (present exactly where ``gathered`` is): the GEMM then
+        signals the logits exchange on every rank it stored to."""
         n_out, hidden = w.shape
-        own = gathered[rank]
+        if v_total is None:
+            v_total = gathered[rank].shape[1]
         self.status = _z(16, dtype=torch.int32, device=x.device)
         self.keep = (w, x, list(gathered))
         self.bind = host.make(
-            "MkLmHeadBind", w=w, x=x, out_peer=list(gathered), rank=rank, v_total=own.shape[1], col0=rank * n_out,
-            n_out=n_out, hidden=hidden, rows=x.shape[0], status=self.status,
+            "MkLmHeadBind", w=w, x=x, out_peer=list(gathered), rank=rank, v_total=v_total, col0=rank * n_out,
+            n_out=n_out, hidden=hidden, rows=x.shape[0], status=self.status, flags=flags, flags_peer=list(flags_peer),
         )  # fmt: skip
         self.launch = lib.bind("mk_lm_head_bind", module, self.bind)
 
@@ -90,9 +99,12 @@ class LmHead:
 class Softcap:
     """cap tanh(x scale / cap) over the gathered logits, into ``out`` (the serving framework's logits tensor)."""
 
-    def __init__(self, lib: host.Library, module, *, x, out, scale: float, cap: float):
-        self.keep = (x, out)
-        self.bind = host.make("MkSoftcapBind", x=x, out=out, numel=x.numel(), scale=scale, cap=cap)
+    def __init__(self, lib: host.Library, module, *, x, out, scale: float, cap: float, flags=None, contributors: int = 0,
+                 wait_budget: int = 0):  # fmt: skip
+        self.status = _z(16, dtype=torch.int32, device=x.device)
+        self.keep = (x, out, flags)
+        self.bind = host.make("MkSoftcapBind", x=x, out=out, numel=x.numel(), scale=scale, cap=cap, flags=flags,
+                              contributors=contributors, wait_budget=wait_budget, status=self.status)  # fmt: skip
         self.launch = lib.bind("mk_softcap_bind", module, self.bind)
 
 
@@ -103,13 +115,15 @@ class Accept:
 
     def __init__(self, lib: host.Library, module, *, logits, tokens, b_live: int, scale: float, cap: float, ring: int = 64,
                  accept_override: Optional[torch.Tensor] = None, cos_sin_cache=None, cos_sin=None, loc_full=None,
-                 loc_swa=None, kv_len=None, dcos_sin_cache=None, dring: int = 0):  # fmt: skip
+                 loc_swa=None, kv_len=None, dcos_sin_cache=None, dring: int = 0, flags=None, contributors: int = 0,
+                 wait_budget: int = 0):  # fmt: skip
         dev = logits.device
         rows, vocab = logits.shape
         self.words = _z(N_WORDS, dtype=torch.int64, device=dev)
         self.out_ring = _z(ring, dtype=torch.int32, device=dev)
         self.top1 = _z(rows, dtype=torch.int32, device=dev)
         self.counter = _z(1, dtype=torch.int32, device=dev)
+        self.status = _z(16, dtype=torch.int32, device=dev)
         draft = dcos_sin_cache is not None
         self.dcos_sin = _z(2 * b_live, 128, dtype=torch.float32, device=dev) if draft else None
         self.dslot = _z(2 * b_live, dtype=torch.int32, device=dev) if draft else None
@@ -122,6 +136,7 @@ class Accept:
             cos_sin_cache=cos_sin_cache, cos_sin_rows=0 if cos_sin_cache is None else cos_sin_cache.shape[0],
             cos_sin=cos_sin, loc_full=loc_full, loc_swa=loc_swa, kv_len=kv_len, dcos_sin_cache=dcos_sin_cache,
             dcos_sin_rows=0 if dcos_sin_cache is None else dcos_sin_cache.shape[0], dcos_sin=self.dcos_sin,
-            dslot=self.dslot, dkv_len=self.dkv_len, dring=dring,
+            dslot=self.dslot, dkv_len=self.dkv_len, dring=dring, flags=flags, contributors=contributors,
+            wait_budget=wait_budget, status=self.status,
         )  # fmt: skip
         self.launch = lib.bind("mk_accept_bind", module, self.bind)

@@ -47,7 +47,9 @@ class LayerRank:
         """``io`` replaces buffers this layer would allocate with ones it shares with its neighbours in a stack: inputs
         ``qkv_in`` / ``stream_in`` (the predecessor's outputs), ``k_cache`` / ``v_cache`` (the pools the predecessor
         appended to), the step's feeds ``page_table`` / ``kv_len`` / ``cache_loc`` / ``next_cos_sin`` and the
-        successor's pools ``next_k`` / ``next_v``.
+        successor's pools ``next_k`` / ``next_v``, and the exchange buffers one rank's layers share (``ar``, ``z``,
+        ``z_sf``, ``z_ex``, ``zb``: byte tensors at least as large as this layer needs; ``pool_ag``, ``unpool_ag``,
+        ``flags``).
         ``tensor_cores``: bind the packed NVFP4 images when the shape has whole 128-row tiles (the tcgen05 expert
         kernels); otherwise, or when False, the experts run on the general CUDA-core kernels from the plain tensors.
         ``keep_plain_experts`` False drops the plain expert tensors once the images exist (halves the expert memory)."""
@@ -120,18 +122,24 @@ class LayerRank:
             y=z((M, P), bf), stream_out=z((M, H), f32), h3_next=z((M, H), bf), qkv_next=z((M, c.qkv_row), bf),
         )  # fmt: skip
         # exchange buffers (symmetric across the ranks)
-        self.ar = raw(c.ar_bytes)
-        self.pool_ag = z((M, P), bf)
-        self.unpool_ag = z((M, H), bf)
-        self.z, self.z_sf, self.z_ex, self.zb = raw(c.z_bytes), raw(c.z_sf_bytes), raw(c.z_ex_bytes), raw(c.zb_bytes)
-        self.flags = z((c.flag_words,), i32)
+        def shared(name, nbytes):
+            return io[name][: int(nbytes)] if name in io else raw(nbytes)
+
+        self.ar = shared("ar", c.ar_bytes)
+        self.pool_ag = io["pool_ag"] if "pool_ag" in io else z((M, P), bf)
+        self.unpool_ag = io["unpool_ag"] if "unpool_ag" in io else z((M, H), bf)
+        self.z, self.z_sf = shared("z", c.z_bytes), shared("z_sf", c.z_sf_bytes)
+        self.z_ex, self.zb = shared("z_ex", c.z_ex_bytes), shared("zb", c.zb_bytes)
+        self.flags = io["flags"] if "flags" in io else z((c.flag_words,), i32)
         self.ws = raw(c.ws_bytes)
         self.status = raw(c.status_bytes)
         self.module = module
         self.launch_record = None
 
-    def bind(self, peers: Optional[list] = None, b_live: int = 0):
-        """Binds the launch; ``peers`` = every rank's ``LayerRank`` (own included) or None for a lone rank."""
+    def bind(self, peers: Optional[list] = None, b_live: int = 0, wait_budget: int = 0):
+        """Binds the launch; ``peers`` = per rank an object whose attributes ``ar``, ``pool_ag``, ``unpool_ag``, ``z``,
+        ``z_sf``, ``z_ex``, ``zb``, ``flags`` are that rank's exchange buffers (tensors, or device addresses of buffers
+        mapped from another process): every rank's ``LayerRank`` (own included), or None for a lone rank."""
         cfg, case, w, o = self.case.cfg, self.case, self.w, self.o
         n = cfg.tp
 
@@ -161,7 +169,7 @@ class LayerRank:
             c_post_w=w["cross_post_w"], c_stream_out=o["stream_out"], h3q=o["h3_next"], w_qkv=w["next_qkv"],
             qkv_out=o["qkv_next"], cos_sin=w["next_cos_sin"], cache_loc=self.cache_loc, next_k_cache=self.next_k,
             next_v_cache=self.next_v, next_kv_rows=self.next_kv_rows, q_scale=cfg.q_scale, qkv_eps=cfg.rms_eps,
-            flags=self.flags, flags_peer=peer("flags"), ws=self.ws, status=self.status, b_live=b_live, wait_budget=0,
+            flags=self.flags, flags_peer=peer("flags"), ws=self.ws, status=self.status, b_live=b_live, wait_budget=wait_budget,
         )  # fmt: skip
         self.launch_record = self.lib.layer_bind(self.module, self.shape, bind)
         return self.launch_record

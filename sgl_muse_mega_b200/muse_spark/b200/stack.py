@@ -4,9 +4,13 @@ soft cap when the caller wants the logits).
 
 Counterpart of the reference's ``Stack`` (``sm103/verify.py:90-470``): every launch record is bound at construction,
 ``launch_all`` enqueues them in order with programmatic dependent launch between neighbours, ``capture`` records that
-sequence into one CUDA graph, ``step`` replays it. ``StackWorld`` holds every rank of a tensor-parallel world on one
-device (parity tests and single-GPU runs): the ranks' launches are interleaved group by group so that every exchange
-has all its contributions before any rank reads it.
+sequence into one CUDA graph, ``step`` replays it.
+
+Everything a peer rank reads or writes (the exchange buffers all layers share, the flag block, the gathered logits and
+the embedding shard) lives in one arena per rank (``common/symm.py``): a CUDA-IPC allocation when the ranks are separate
+processes on separate GPUs, ordinary tensors when ``StackWorld`` holds every rank of the world on one device (parity
+tests and single-GPU runs; there the ranks' launches are interleaved group by group so that every exchange has all its
+contributions before any rank reads it).
 """
 
 from __future__ import annotations
@@ -15,32 +19,70 @@ from typing import Optional
 
 import torch
 
-from ...common import host
+from ...common import host, symm
 from . import headtail as HT
 from .head import QkvHead
 from .layer import STAGE_GROUPS, LayerRank
 
+EXCHANGE = ("ar", "pool_ag", "unpool_ag", "z", "z_sf", "z_ex", "zb", "flags", "gathered", "embed")
+
+
+def exchange_layout(cfg, rows: int) -> symm.Layout:
+    """The arena of one rank; depends on the model and the window only, so every rank carves the same offsets."""
+    u8, bf = torch.uint8, torch.bfloat16
+    slots = rows * cfg.topk
+    lay = symm.Layout()
+    lay.add("flags", (64,), torch.int32)
+    lay.add("ar", (cfg.tp * rows * cfg.hidden * 2,), u8)
+    lay.add("pool_ag", (rows, cfg.moe_hidden), bf)
+    lay.add("unpool_ag", (rows, cfg.hidden), bf)
+    lay.add("z", (slots * cfg.moe_inter * 2,), u8)  # the bf16 variant's size; NVFP4 layers use the first quarter
+    lay.add("z_sf", (slots * cfg.moe_inter // 16,), u8)
+    lay.add("z_ex", (slots * cfg.moe_inter // 16,), u8)
+    lay.add("zb", (slots * cfg.moe_hidden * 2,), u8)
+    lay.add("gathered", (rows, cfg.vocab), torch.float32)
+    lay.add("embed", (cfg.vocab_rank, cfg.hidden), bf)
+    return lay
+
+
+class ExchangeView:
+    """A rank's exchange buffers by device address (own arena or a peer's mapped one)."""
+
+    def __init__(self, arena):
+        for name in EXCHANGE:
+            setattr(self, name, arena.ptr(name))
+
+
+class PeerStack:
+    """What a rank needs of a peer that lives in another process: its arena, mapped."""
+
+    def __init__(self, arena):
+        self.arena, self.view = arena, ExchangeView(arena)
+
 
 class Stack:
-    def __init__(self, case, rank: int, device, lib: Optional[host.Library] = None, module=None, *,
+    def __init__(self, case, rank: int, device, lib: Optional[host.Library] = None, module=None, *, arena=None,
                  kv_rows: Optional[int] = None, tensor_cores: bool = True, keep_plain_experts: bool = True,
                  greedy: bool = True, accept_override: Optional[torch.Tensor] = None, ring: int = 64,
-                 b_live: int = 0):  # fmt: skip
-        """``case``: a ``synthetic.StackCase``; ``rank`` must be one of ``case.ranks``. ``greedy`` False ends the step
-        with the soft cap (the logits go to ``self.logits_out``) instead of the accept."""
+                 b_live: int = 0, wait_budget: int = 0):  # fmt: skip
+        """``case``: a ``synthetic.StackCase``; ``rank`` must be one of ``case.ranks``. ``arena``: the rank's exchange
+        memory carved by ``exchange_layout`` (default: ordinary tensors, for a world inside one process). ``greedy``
+        False ends the step with the soft cap (the logits go to ``self.logits_out``) instead of the accept."""
         self.lib = lib or host.library()
         if module is None:
             with torch.cuda.device(device):
                 module = self.lib.load()
         self.module, self.case, self.rank, self.device = module, case, rank, device
         cfg, M = case.cfg, case.rows
-        self.b_live = b_live or M
+        self.b_live, self.wait_budget = b_live or M, wait_budget
         slot = case.ranks.index(rank)
         dev = lambda t: t.to(device).contiguous()  # noqa: E731
         i64, i32, bf = torch.int64, torch.int32, torch.bfloat16
         kv_rows = kv_rows or (case.ctx + 8 * M + 127) // 128 * 128
         kvw = cfg.kv_heads_rank * cfg.head_dim
         self.kv_rows = kv_rows
+        self.arena = arena if arena is not None else symm.LocalArena(exchange_layout(cfg, M), device)
+        self.view = ExchangeView(self.arena)
         # ---- the serving framework's side of the feeds: identity slots (position p lives in pool row p) ----
         self.positions = torch.arange(case.ctx, case.ctx + M, dtype=i64, device=device)
         self.out_cache_loc = self.positions.clone()
@@ -51,19 +93,19 @@ class Stack:
         self.swa_out_cache_loc = self.out_cache_loc.clone()
         self.cos_sin_cache = dev(case.cos_sin_cache)
         self.tokens = torch.zeros(M, dtype=i64, device=device)
-        self.feeds = HT.WindowFeeds(
+        self.feeds = f = HT.WindowFeeds(
             self.lib, module, positions=self.positions, cos_sin_cache=self.cos_sin_cache,
             out_cache_loc=self.out_cache_loc, swa_out_cache_loc=self.swa_out_cache_loc, seq_lens=self.seq_lens,
             req_pool_indices=self.req_pool_indices, req_to_token=self.req_to_token, full_to_swa=self.full_to_swa,
             kv_row_bytes=kvw * 2,
         )  # fmt: skip
-        f = self.feeds
-        # ---- weights of the head and tail; peers' embedding shards are wired in bind() ----
-        self.embed = dev(case.embed[slot])
+        # ---- weights of the head and tail (the embedding shard sits in the arena: the peers' entries read it) ----
+        self.embed = self.arena.tensor("embed")
+        self.embed.copy_(case.embed[slot])
         self.pre_w0 = dev(case.pre_w0)
         self.qkv0 = dev(case.qkv0[slot])
         self.lm_head_w = dev(case.lm_head[slot])
-        self.gathered = torch.zeros(M, cfg.vocab, dtype=torch.float32, device=device)
+        self.gathered = self.arena.tensor("gathered")
         self.logits_out = None if greedy else torch.zeros(M, cfg.vocab, dtype=torch.float32, device=device)
         self.greedy, self.accept_override, self.ring = greedy, accept_override, ring
         # ---- the KV pools: one pair per layer; context rows from the case ----
@@ -74,27 +116,29 @@ class Stack:
             k[: case.ctx] = t.k_ctx.reshape(case.ctx, kvw).to(device)
             v[: case.ctx] = t.v_ctx.reshape(case.ctx, kvw).to(device)
             self.pools.append((k, v))
-        # ---- layers, chained through io ----
-        self.entry = None
-        self.layers: list[LayerRank] = []
-        self._slot = slot
-        self._keep_plain = keep_plain_experts
-        self._tensor_cores = tensor_cores
-        self.normed0 = torch.zeros(M, cfg.hidden, dtype=bf, device=device)
+        # ---- the entry and layer 0's head (the peers' shards are wired in bind) ----
         self.residual0 = torch.zeros(M, cfg.hidden, dtype=torch.float32, device=device)
-        self.qkv_in0 = torch.zeros(M, cfg.qkv_row, dtype=bf, device=device)
-        qkv_in, stream_in = self.qkv_in0, self.residual0
+        self.normed0 = torch.zeros(M, cfg.hidden, dtype=bf, device=device)
+        l0 = case.layers[0]
+        self.qkv_head = QkvHead(
+            self.lib, module, w=self.qkv0, x=self.normed0, q_heads=cfg.q_heads_rank, kv_heads=cfg.kv_heads_rank,
+            q_scale=cfg.q_scale, eps=cfg.rms_eps, cos_sin=None if l0.global_attn else f.cos_sin,
+            cache_loc=f.loc_full if l0.global_attn else f.loc_swa, k_cache=self.pools[0][0], v_cache=self.pools[0][1],
+        )  # fmt: skip
+        # ---- layers, chained through io; the exchange buffers are the arena's, shared by all layers ----
+        shared = {k: self.arena.tensor(k) for k in ("ar", "pool_ag", "unpool_ag", "z", "z_sf", "z_ex", "zb", "flags")}
+        self.layers: list[LayerRank] = []
+        qkv_in, stream_in = self.qkv_head.out, self.residual0
         n = len(case.layers)
         for j, lc in enumerate(case.layers):
             k, v = self.pools[j]
             nk, nv = self.pools[j + 1] if j + 1 < n else self.pools[j]
             nxt_global = j + 1 < n and case.layers[j + 1].global_attn
-            io = dict(qkv_in=qkv_in, stream_in=stream_in, k_cache=k, v_cache=v, next_k=nk, next_v=nv,
+            io = dict(shared, qkv_in=qkv_in, stream_in=stream_in, k_cache=k, v_cache=v, next_k=nk, next_v=nv,
                       page_table=f.pt_full if lc.global_attn else f.pt_swa, kv_len=f.kv_len,
-                      cache_loc=f.loc_full if nxt_global else f.loc_swa,
-                      next_cos_sin=None if (lc.tail or lc.next_global) else f.cos_sin)  # fmt: skip
-            if io["next_cos_sin"] is None:
-                io.pop("next_cos_sin")
+                      cache_loc=f.loc_full if nxt_global else f.loc_swa)  # fmt: skip
+            if not (lc.tail or lc.next_global):
+                io["next_cos_sin"] = f.cos_sin
             lr = LayerRank(self.lib, module, lc, rank, device, tensors=lc.ranks[slot], tensor_cores=tensor_cores,
                            keep_plain_experts=keep_plain_experts, io=io)  # fmt: skip
             self.layers.append(lr)
@@ -104,42 +148,41 @@ class Stack:
 
     # ---- binding ----
     def bind(self, peers: Optional[list] = None) -> None:
-        """``peers``: every rank's ``Stack`` (own included, None for absent ranks) or None for a lone rank."""
+        """``peers``: per rank a ``Stack`` (same process) or ``PeerStack`` (mapped arena), own included, None for an
+        absent rank; or None altogether for a lone rank."""
         cfg, case, M = self.case.cfg, self.case, self.case.rows
         n = cfg.tp
         f = self.feeds
         if peers is None:
             peers = [self if r == self.rank else None for r in range(n)]
-        # the entry reads the owner rank's shard: an absent rank's rows read this rank's shard (a lone-rank timing run)
-        shards = [(p.embed if p is not None else self.embed) for p in peers]
+        views = [None if p is None else p.view for p in peers]
+        present = sum(v is not None for v in views)
+        # the entry reads the owner rank's shard; an absent rank's rows read this rank's shard (a lone-rank timing run)
+        shards = [(v.embed if v is not None else self.view.embed) for v in views]
         self.entry = HT.Entry(self.lib, self.module, ids=self.tokens, embed_shards=shards, pre_w=self.pre_w0,
-                              eps_embed=cfg.rms_eps, eps_pre=cfg.rms_eps)  # fmt: skip
-        self.residual0, self.normed0 = self.entry.residual, self.entry.normed
-        l0 = case.layers[0]
-        self.qkv_head = QkvHead(
-            self.lib, self.module, w=self.qkv0, x=self.normed0, q_heads=cfg.q_heads_rank, kv_heads=cfg.kv_heads_rank,
-            q_scale=cfg.q_scale, eps=cfg.rms_eps, cos_sin=None if l0.global_attn else f.cos_sin,
-            cache_loc=f.loc_full if l0.global_attn else f.loc_swa, k_cache=self.pools[0][0], v_cache=self.pools[0][1],
-        )  # fmt: skip
-        # layer 0 was built before the entry and the head existed: point it at their outputs
-        self.layers[0].w["qkv_in"] = self.qkv_head.out
-        self.layers[0].w["stream_in"] = self.residual0
-        for j, lr in enumerate(self.layers):
-            lr.bind([None if p is None else p.layers[j] for p in peers], self.b_live if self.b_live != M else 0)
+                              eps_embed=cfg.rms_eps, eps_pre=cfg.rms_eps, shard_rows=cfg.vocab_rank, hidden=cfg.hidden,
+                              residual=self.residual0, normed=self.normed0)  # fmt: skip
+        live = self.b_live if self.b_live != M else 0
+        for lr in self.layers:
+            lr.bind(views, live, self.wait_budget)
+        flags = self.arena.tensor("flags")
         self.lm_head = HT.LmHead(self.lib, self.module, w=self.lm_head_w, x=self.hidden,
-                                 gathered=[None if p is None else p.gathered for p in peers], rank=self.rank)  # fmt: skip
+                                 gathered=[None if v is None else v.gathered for v in views], rank=self.rank,
+                                 flags=flags, flags_peer=[None if v is None else v.flags for v in views],
+                                 v_total=cfg.vocab)  # fmt: skip
         if self.greedy:
             self.accept = HT.Accept(
                 self.lib, self.module, logits=self.gathered, tokens=self.tokens, b_live=self.b_live,
                 scale=cfg.output_multiplier, cap=cfg.softcap, ring=self.ring, accept_override=self.accept_override,
                 cos_sin_cache=self.cos_sin_cache, cos_sin=f.cos_sin, loc_full=f.loc_full, loc_swa=f.loc_swa,
-                kv_len=f.kv_len,
+                kv_len=f.kv_len, flags=flags, contributors=present, wait_budget=self.wait_budget,
             )  # fmt: skip
             self.accept.words[HT.WORDS["P"]] = case.ctx
             self.tail = self.accept
         else:
             self.tail = HT.Softcap(self.lib, self.module, x=self.gathered, out=self.logits_out,
-                                   scale=cfg.output_multiplier, cap=cfg.softcap)  # fmt: skip
+                                   scale=cfg.output_multiplier, cap=cfg.softcap, flags=flags, contributors=present,
+                                   wait_budget=self.wait_budget)  # fmt: skip
         self.bound = True
 
     # ---- launching ----
@@ -150,27 +193,29 @@ class Stack:
         return k + sum(lr.launch_record.info().kernels for lr in self.layers)
 
     def launch_head(self, s: int, pdl: bool = False) -> None:
-        self.entry.launch(s, pdl)
+        self.entry.launch(s, False)
         self.qkv_head.launch(s, pdl)
 
     def launch_all(self, s: int, pdl: bool = True, feeds: bool = False) -> None:
         if feeds:
             self.feeds.launch(s, False)
-        self.entry.launch(s, False)
-        self.qkv_head.launch(s, pdl)
+        self.launch_head(s, pdl)
         for lr in self.layers:
             lr.launch(s, pdl)
         self.lm_head.launch(s, pdl)
         self.tail.launch(s, pdl)
 
-    def capture(self, pdl: bool = True) -> torch.cuda.CUDAGraph:
-        """One CUDA graph of the whole step on a side stream; ``step`` replays it."""
+    def capture(self, pdl: bool = True, warmup: bool = True) -> torch.cuda.CUDAGraph:
+        """One CUDA graph of the whole step on a side stream; ``step`` replays it. ``warmup`` runs the step once before
+        the capture (it advances the step's state like any step). A world of several processes must capture with
+        ``warmup`` on every rank or on none: the exchange counters have to stay in step."""
         g = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream(self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):
-            self.launch_all(side.cuda_stream, pdl)  # warm-up outside the capture
-            side.synchronize()
+            if warmup:
+                self.launch_all(side.cuda_stream, pdl)
+                side.synchronize()
             with torch.cuda.graph(g, stream=side):
                 self.launch_all(torch.cuda.current_stream(self.device).cuda_stream, pdl)
         torch.cuda.current_stream(self.device).wait_stream(side)
@@ -180,13 +225,25 @@ class Stack:
     def step(self) -> None:
         self.graph.replay()
 
-    def statuses(self) -> list:
-        """(launch name, code) of every launch whose device status word is non-zero."""
+    def rewind(self) -> None:
+        """Back to the state before the first step (words, ring, feeds, window rows of the pools); the exchange
+        counters keep counting."""
         s = torch.cuda.current_stream(self.device).cuda_stream
+        if self.greedy:
+            self.accept.words.zero_()
+            self.accept.words[HT.WORDS["P"]] = self.case.ctx
+            self.accept.out_ring.zero_()
+        self.feeds.launch(s)
+        for k, v in self.pools:
+            k[self.case.ctx :].zero_(), v[self.case.ctx :].zero_()
+
+    def statuses(self) -> list:
+        """(launch name, code, stage, observed) of every launch whose device status word is non-zero."""
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        recs = [("feeds", self.feeds.launch), ("lm_head", self.lm_head.launch), ("tail", self.tail.launch)]
+        recs += [(f"layer{j}", lr.launch_record) for j, lr in enumerate(self.layers)]
         bad = []
-        for name, rec in [("feeds", self.feeds.launch), ("lm_head", self.lm_head.launch)] + [
-            (f"layer{j}", lr.launch_record) for j, lr in enumerate(self.layers)
-        ]:
+        for name, rec in recs:
             st = rec.status(s)
             if st.code:
                 bad.append((name, st.code, st.stage, st.observed))
@@ -222,3 +279,17 @@ class StackWorld:
             st.lm_head.launch(s)
         for st in self.ranks:
             st.tail.launch(s)
+
+
+def connect_world(stack: Stack, group=None) -> list:
+    """A world of one process per GPU: swaps the arenas' handles over ``torch.distributed``, maps the peers and binds
+    ``stack`` against them. Returns the peer list (keep it alive as long as the stack launches)."""
+    import torch.distributed as dist
+
+    n, r = stack.case.cfg.tp, stack.rank
+    assert dist.get_world_size(group) == n and dist.get_rank(group) == r, "one process per rank of the model's world"
+    arenas = symm.connect(stack.arena, r, n, group, stack.lib)
+    peers = [stack if i == r else PeerStack(a) for i, a in enumerate(arenas)]
+    stack.bind(peers)
+    dist.barrier(group)
+    return peers

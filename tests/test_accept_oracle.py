@@ -94,16 +94,18 @@ def test_bind_argument_checks():
     assert _lib().bind("mk_entry_bind", None, host.make("MkEntryBind", **e)).info().kernels == 1
     _expect("mk_entry_bind", host.make("MkEntryBind", **{**e, "hidden": 1000}), "hidden 1000")
     _expect("mk_entry_bind", host.make("MkEntryBind", **{**e, "ranks": 3}), r"embed_peer\[2\]")
-    h = dict(w=p, x=p, out_peer=[p], rank=0, v_total=1000, col0=0, n_out=250, hidden=1024, rows=16, status=0)
+    h = dict(w=p, x=p, out_peer=[p], rank=0, v_total=1000, col0=0, n_out=250, hidden=1024, rows=16, status=0, flags=0,
+             flags_peer=[])
     assert _lib().bind("mk_lm_head_bind", None, host.make("MkLmHeadBind", **h)).info().kernels == 1
     _expect("mk_lm_head_bind", host.make("MkLmHeadBind", **{**h, "col0": 800}), "columns")
     _expect("mk_lm_head_bind", host.make("MkLmHeadBind", **{**h, "rank": 1}), "out_peer")
     a = dict(logits=p, vocab=1000, rows=16, b_live=16, scale=1.0, cap=20.0, tokens=p, accept_override=0, n_override=0,
              words=p, out_ring=p, ring=64, top1=p, counter=p, cos_sin_cache=0, cos_sin_rows=0, cos_sin=0, loc_full=0,
-             loc_swa=0, kv_len=0, dcos_sin_cache=0, dcos_sin_rows=0, dcos_sin=0, dslot=0, dkv_len=0, dring=0)  # fmt: skip
+             loc_swa=0, kv_len=0, dcos_sin_cache=0, dcos_sin_rows=0, dcos_sin=0, dslot=0, dkv_len=0, dring=0, flags=0,
+             contributors=0, wait_budget=0, status=0)  # fmt: skip
     assert _lib().bind("mk_accept_bind", None, host.make("MkAcceptBind", **a)).info().kernels == 1
     _expect("mk_accept_bind", host.make("MkAcceptBind", **{**a, "b_live": 17}), "b_live")
     _expect("mk_accept_bind", host.make("MkAcceptBind", **{**a, "ring": 8}), "ring")
     _expect("mk_accept_bind", host.make("MkAcceptBind", **{**a, "dslot": p}), "dslot")
-    s = dict(x=p, out=p, numel=0, scale=1.0, cap=20.0)
+    s = dict(x=p, out=p, numel=0, scale=1.0, cap=20.0, flags=0, contributors=0, wait_budget=0, status=0)
     _expect("mk_softcap_bind", host.make("MkSoftcapBind", **s), "numel")

@@ -1,0 +1,119 @@
+"""A tensor-parallel world of one process per GPU (needs two B200s; skipped on a one-GPU box): the ranks exchange
+through each other's mapped arenas with the in-kernel flag protocol, and every rank's step words, arg-max and gathered
+logits are bit-identical to the same world emulated on one GPU (all ranks in one process, launches interleaved)."""
+
+import os
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from sgl_muse_mega_b200.muse_spark.b200 import synthetic
+from sgl_muse_mega_b200.muse_spark.config import Config
+
+pytestmark = pytest.mark.gpu
+STEPS = 3
+
+
+def cfg_for(tp: int) -> Config:
+    return Config(hidden=1024, q_heads=64, kv_heads=8, experts=16, topk=8, moe_hidden=1024, moe_inter=1024, swa_window=7,
+                  vocab=4096, layers=4, bf16_moe_layers=(0,), tp=tp, node_ranks=min(4, tp))  # fmt: skip
+
+
+def tokens_for(cfg, rows):
+    gen = torch.Generator().manual_seed(31)
+    return [torch.randint(0, cfg.vocab, (rows,), generator=gen) for _ in range(STEPS)]
+
+
+def _rank_main(rank, world, port, graph, out):
+    import torch.distributed as dist
+
+    from sgl_muse_mega_b200.common import host, symm
+    from sgl_muse_mega_b200.muse_spark.b200 import stack as S
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    device = torch.device(f"cuda:{rank}")
+    torch.cuda.set_device(device)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        cfg = cfg_for(world)
+        rows, ctx = 16, 24
+        case = synthetic.stack_case(cfg, n_layers=4, rows=rows, ctx=ctx, seed=21, only_ranks=[rank])
+        lib = host.library()
+        module = lib.load()
+        arena = symm.Arena(lib, S.exchange_layout(cfg, rows), device)
+        forced = torch.tensor([6], dtype=torch.int32, device=device)
+        st = S.Stack(case, rank, device, lib, module, arena=arena, accept_override=forced, wait_budget=1 << 24)
+        peers = S.connect_world(st)
+        s = torch.cuda.current_stream().cuda_stream
+        st.feeds.launch(s)
+        torch.cuda.synchronize()
+        if graph:
+            st.capture(warmup=False)
+        res = []
+        for t in tokens_for(cfg, rows):
+            st.tokens.copy_(t)
+            if graph:
+                st.step()
+            else:
+                st.launch_all(s, pdl=True)
+            torch.cuda.synchronize()
+            res.append(dict(words=st.accept.words.cpu(), top1=st.accept.top1.cpu(), logits=st.gathered.cpu().clone()))
+        dist.barrier()
+        out[rank] = dict(res=res, status=st.statuses())
+        del peers
+    finally:
+        dist.destroy_process_group()
+
+
+def emulated(world):
+    from sgl_muse_mega_b200.muse_spark.b200 import stack as S
+
+    cfg = cfg_for(world)
+    rows, ctx = 16, 24
+    dev = torch.device("cuda:0")
+    case = synthetic.stack_case(cfg, n_layers=4, rows=rows, ctx=ctx, seed=21)
+    forced = torch.tensor([6], dtype=torch.int32, device=dev)
+    w = S.StackWorld(case, dev, accept_override=forced)
+    res = []
+    first = True
+    for t in tokens_for(cfg, rows):
+        for st in w.ranks:
+            st.tokens.copy_(t)
+        w.run_interleaved(feeds=first)
+        first = False
+        torch.cuda.synchronize()
+        res.append([dict(words=st.accept.words.cpu(), top1=st.accept.top1.cpu(), logits=st.gathered.cpu().clone())
+                    for st in w.ranks])  # fmt: skip
+    for st in w.ranks:
+        assert st.statuses() == []
+    return res
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_two_gpu_world_matches_the_emulated_world(graph):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    ref = emulated(world)
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as m:
+        out = m.dict()
+        port = 29900 + os.getpid() % 200 + int(graph)
+        procs = [ctx.Process(target=_rank_main, args=(r, world, port, graph, out)) for r in range(world)]
+        for p in procs:
+            p.start()
+        try:
+            for p in procs:
+                p.join(600)
+                assert p.exitcode == 0, f"rank process exit code {p.exitcode}"
+        finally:
+            for p in procs:  # only the processes started above, by handle
+                if p.is_alive():
+                    p.kill()
+        got = dict(out)
+    for r in range(world):
+        assert got[r]["status"] == [], got[r]["status"]
+        for i in range(STEPS):
+            for k in ("words", "top1", "logits"):
+                assert torch.equal(got[r]["res"][i][k], ref[i][r][k]), (r, i, k)
