@@ -265,7 +265,9 @@ class StackWorld:
         for st in self.ranks:
             st.bind(full)
 
-    def run_interleaved(self, feeds: bool = True) -> None:
+    def run_interleaved(self, feeds: bool = True, after_layer=None) -> None:
+        """``after_layer(j)`` is called once layer j is enqueued on every rank (the parity tests read the shared exchange
+        buffers there, before the next layer overwrites them)."""
         s = torch.cuda.current_stream(self.device).cuda_stream
         for st in self.ranks:
             if feeds:
@@ -275,6 +277,8 @@ class StackWorld:
             for first, count in STAGE_GROUPS:
                 for st in self.ranks:
                     st.layers[j].launch_record.step(s, first, count)
+            if after_layer is not None:
+                after_layer(j)
         for st in self.ranks:
             st.lm_head.launch(s)
         for st in self.ranks:
