@@ -15,6 +15,7 @@ touches ``oracle/``.
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
 import os
 import statistics
@@ -42,6 +43,9 @@ def parse():
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--cpu-sample-experts", type=int, default=24)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--decode-layers", type=int, default=62, help="layers of the whole-step leg (0: skip it)")
+    ap.add_argument("--decode-steps", type=int, default=24)
+    ap.add_argument("--accept", type=int, default=6, help="forced accept length of the whole-step leg")
     return ap.parse_args()
 
 
@@ -168,6 +172,127 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+# ---- the whole verify step: every layer of the model plus head and tail, one CUDA graph ------------------------------
+
+
+def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) -> dict:
+    """Builds this rank's slice of a ``--decode-layers`` model (layer variants as the model interleaves them), binds it
+    against the present ranks (``world`` processes, one per GPU; alone: no peers) and times the step: CUDA graph replays
+    with the forced accept length, the layers alone, and end to end with the ids coming from and the step words going
+    to pinned host memory."""
+    import torch
+    import torch.distributed as dist
+
+    from sgl_muse_mega_b200.common import symm
+    from sgl_muse_mega_b200.muse_spark.b200 import stack as S
+    from sgl_muse_mega_b200.muse_spark.b200 import synthetic
+
+    tp_rank = rank % cfg.tp
+    n_layers, K, W = args.decode_layers, args.decode_steps, 3
+    commit = args.accept + 1
+    total_steps = 3 * (K + W) + 8
+    rows = args.rows
+    kv_rows = (args.ctx + commit * total_steps + rows + 127) // 128 * 128
+    model = cfg
+    if n_layers != cfg.layers:  # a shorter model for quick runs: bf16 experts in its first and last layer, as the full one
+        model = dataclasses.replace(cfg, layers=n_layers, bf16_moe_layers=(0, n_layers - 1) if n_layers > 2 else ())
+    case = synthetic.stack_case(model, n_layers=n_layers, rows=rows, ctx=args.ctx, seed=args.seed, only_ranks=[tp_rank],
+                                max_pos=kv_rows + rows, lazy=True)  # fmt: skip
+    forced = torch.tensor([args.accept], dtype=torch.int32, device=device)
+    arena = symm.Arena(lib, S.exchange_layout(model, rows), device) if world > 1 else None
+    st = S.Stack(case, tp_rank, device, lib, module, arena=arena, kv_rows=kv_rows, keep_plain_experts=False,
+                 accept_override=forced, wait_budget=1 << 25)  # fmt: skip
+    peers = S.connect_world(st) if world > 1 else st.bind()
+    s = stream.cuda_stream
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    gen = torch.Generator().manual_seed(args.seed)
+    h_tokens = torch.randint(0, model.vocab, (rows,), generator=gen).pin_memory()
+    h_words = torch.zeros(8, dtype=torch.int64).pin_memory()
+    with torch.cuda.stream(stream):
+        st.tokens.copy_(h_tokens)
+        st.feeds.launch(s)
+    barrier()
+    with torch.cuda.stream(stream):
+        st.capture(pdl=True, warmup=True)
+    barrier()
+    # ---- graph replays, inputs resident ----
+    with torch.cuda.stream(stream):
+        for _ in range(W):
+            st.step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(K):
+            st.step()
+        e1.record(stream)
+    barrier()
+    step_ms = max_over_ranks(e0.elapsed_time(e1) / K)
+    # ---- the layers alone (eager launches with programmatic dependent launch), same exchange partners ----
+    with torch.cuda.stream(stream):
+        for lr in st.layers:
+            lr.launch(s, True)
+    barrier()
+    reps = max(2, min(8, K // 4))
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(reps):
+            for lr in st.layers:
+                lr.launch(s, True)
+        e1.record(stream)
+    barrier()
+    layer_us = max_over_ranks(e0.elapsed_time(e1) / (reps * n_layers) * 1e3)
+    # ---- end to end: ids from pinned host memory, step words back ----
+    def e2e_step():
+        with torch.cuda.stream(stream):
+            st.tokens.copy_(h_tokens, non_blocking=True)
+            st.step()
+            h_words.copy_(st.accept.words, non_blocking=True)
+        stream.synchronize()
+
+    for _ in range(W):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) / K * 1e3)
+    bad = st.statuses()
+    assert bad == [], f"device status after the whole-step leg: {bad}"
+    assert int(h_words[2]) == args.accept and int(h_words[3]) == commit, h_words.tolist()
+    d_list = [int(torch.unique(lr.o["ids"]).numel()) for lr in st.layers]
+    byts = [layer_bytes(cfg, d, int(h_words[0]), rows, lr.case.global_attn) for d, lr in zip(d_list, st.layers)]
+    for b, lr in zip(byts, st.layers):
+        if lr.case.bf16:  # bf16 experts: 2 bytes an element instead of 0.5625
+            scale = 2.0 / 0.5625
+            b["total"] += int((b["g1"] + b["g2"]) * (scale - 1))
+    out = {
+        "layers": n_layers, "accept_len": args.accept, "tokens_per_step": commit, "ms_per_step": step_ms,
+        "tok_s": commit / (step_ms * 1e-3), "e2e_ms_per_step": e2e_ms, "e2e_tok_s": commit / (e2e_ms * 1e-3),
+        "h2d_bytes_per_step": h_tokens.numel() * 8, "d2h_bytes_per_step": 64,
+        "layer_only_us": layer_us, "kernels_per_step": st.kernels,
+        "bytes_per_step": int(sum(b["total"] for b in byts)), "mean_distinct_experts": sum(d_list) / len(d_list),
+        "present_ranks": world if world > 1 else 1, "model_ranks": cfg.tp,
+        "draft": "not in the step: the draft model's kernels are not built yet; ids come from the host",
+    }  # fmt: skip
+    del peers
+    return out, st
+
+
 # ---- GPU leg ----------------------------------------------------------------------------------------------------------
 
 
@@ -192,6 +317,10 @@ def run_ours(args) -> None:
     lib = host.library()
     module = lib.load()
     synthetic.set_device(device)
+    if world > 1:
+        run_world(args, cfg, lib, module, device, rank, world, local)
+        dist.destroy_process_group()
+        return
     # a ring of distinct layers: global iff i % 4 == 3 here (3 swa : 1 global). Each GPU holds the slice of TP rank
     # `rank % 8`; with N GPUs the ranks are independent replicas of the per-GPU work (no exchange partner is waited for).
     tp_rank = rank % cfg.tp
@@ -321,6 +450,12 @@ def run_ours(args) -> None:
         e2e_us = float(t.item())
     clocks = sampler.stop() if sampler else None
 
+    dec = None
+    if args.decode_layers > 0:
+        del ring, lr
+        torch.cuda.empty_cache()
+        dec, _st = decode_leg(args, cfg, lib, module, device, rank, world, stream)
+        del _st
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         threads = os.cpu_count() or 1
@@ -345,12 +480,79 @@ def run_ours(args) -> None:
             "e2e": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(info.kernels) * args.steps,
             "stage_us_serialised": stage_us,
+            "decode": dec,
             "clocks": clocks,
             "cpu_baseline": cpu,
         }  # fmt: skip
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_world(args, cfg, lib, module, device, rank: int, world: int, local: int) -> None:
+    """N > 1: one process per GPU, ranks 0 .. N - 1 of the model's TP8 world present (N = 8: the whole world), exchanging
+    through each other's memory inside the kernels. Per-GPU work is the same TP8 slice at every N (weak scaling)."""
+    import torch
+    import torch.distributed as dist
+
+    from sgl_muse_mega_b200.muse_spark.b200 import layer as L
+
+    stream = torch.cuda.Stream(device)
+    s = stream.cuda_stream
+    sampler = ClockSampler(local) if rank == 0 else None
+    assert args.decode_layers > 0, "the multi-GPU run times the layers of the whole-step leg"
+    dec, st = decode_leg(args, cfg, lib, module, device, rank, world, stream)
+    n_layers = dec["layers"]
+    peak, peak_kind = peaks()
+    # the dominant kernel (g1) between events, every rank stepping the same stages in the same order
+    G1 = L.STAGE_NAMES.index("g1")
+    fp4 = [lr for lr in st.layers if not lr.case.bf16][:32]
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in fp4]
+    with torch.cuda.stream(stream):
+        for lr, (a, b) in zip(fp4, pairs):
+            lr.launch_record.step(s, 0, G1)
+            a.record(stream)
+            lr.launch_record.step(s, G1, 1)
+            b.record(stream)
+            lr.launch_record.step(s, G1 + 1, len(L.STAGE_NAMES) - G1 - 1)
+    torch.cuda.synchronize()
+    dist.barrier()
+    g1_ms = sum(a.elapsed_time(b) for a, b in pairs)
+    g1_bytes = sum(layer_bytes(cfg, int(torch.unique(lr.o["ids"]).numel()), args.ctx, args.rows, False)["g1"] for lr in fp4)
+    t = torch.tensor([g1_ms], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    g1_gbs = g1_bytes / (float(t.item()) * 1e-3) / 1e9
+    assert st.statuses() == []
+    clocks = sampler.stop() if sampler else None
+    if rank == 0:
+        us_layer = dec["layer_only_us"]
+        layer_gbs = dec["bytes_per_step"] / (us_layer * n_layers * 1e-6) / 1e9
+        line = {
+            "metric": METRIC, "value": us_layer, "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": us_layer / 1e3, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "nvfp4 experts (e2m1 x e4m3 block scales), bf16 dense, f32 accumulate", "data": "synthetic",
+            "config": {
+                "workload": WORKLOAD.replace("on 1 B200", f"per GPU, ranks 0..{world - 1} of the TP8 world on {world} B200s"),
+                "rows": args.rows, "ctx": args.ctx, "layers": n_layers,
+                "l2": "inputs larger than L2 (every layer of the model is distinct)",
+                "multi_gpu": f"{world} of 8 ranks present, in-kernel exchange through peer memory (flag-polled P2P stores)",
+                "kernels_per_step": dec["kernels_per_step"],
+                "timed": "the layer launches of the whole-step leg, eager with programmatic dependent launch",
+            },
+            "layer_roofline": {"bound": "hbm", "achieved": layer_gbs, "peak": peak, "unit": "GB/s", "frac": layer_gbs / peak,
+                               "bytes_per_layer": dec["bytes_per_step"] // n_layers, "peak_kind": peak_kind},
+            "roofline": {"bound": "hbm", "kernel": "experts_umma_kernel<g1>", "achieved": g1_gbs, "peak": peak, "unit": "GB/s",
+                         "frac": g1_gbs / peak, "traffic": None, "peak_kind": peak_kind,
+                         "us_per_launch": float(t.item()) / len(pairs) * 1e3},
+            "e2e": {"value": dec["e2e_ms_per_step"] * 1e3 / n_layers, "unit": "us",
+                    "h2d_bytes_per_step": dec["h2d_bytes_per_step"], "d2h_bytes_per_step": dec["d2h_bytes_per_step"],
+                    "note": "whole verify step through the CUDA graph with host ids in and step words out, divided by its layers"},
+            "gpu_launches": dec["kernels_per_step"] * (2 * args.decode_steps + 7),
+            "decode": dec,
+            "clocks": clocks,
+            "cpu_baseline": None,
+        }  # fmt: skip
+        print(json.dumps(line), flush=True)
 
 
 def main() -> None:

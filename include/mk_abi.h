@@ -59,7 +59,8 @@ int mk_launch_info(const MkLaunch* launch, MkLaunchInfo* out);
 // host (synchronises the stream first). code 0 = clean; otherwise the wait that gave up.
 typedef struct MkLaunchStatus {
     int64_t code;      // 0 ok, 1 an exchange wait ran out (a peer never signalled), 3 a bulk copy or tensor-core barrier
-                       // never completed, 4 an out-of-range position / request index was clamped
+                       // never completed, 4 an out-of-range position / request index was clamped, 6 a row's router
+                       // scores were NaN (it is routed to the lowest expert ids; its outputs are meaningless)
     int64_t stage;     // stage index that recorded it (exchange waits), or a kernel-specific site number
     int64_t block;     // blockIdx.x
     int64_t observed;  // value seen
@@ -319,6 +320,8 @@ typedef struct MkAcceptBind {
     int64_t contributors;
     int64_t wait_budget;
     uint64_t status;
+    int64_t pool_rows;         // rows of the KV pools behind loc_full / loc_swa (identity slots): a next window that would
+                               // not fit is clamped to the last rows and recorded (code 4); 0 = unchecked
 } MkAcceptBind;
 int mk_accept_bind(MkModule* module, const MkAcceptBind* bind, MkLaunch** out);
 

@@ -187,7 +187,12 @@ __global__ void __launch_bounds__(1024) accept_kernel(const AcceptArgs a) {
         s_p = p;
     }
     __syncthreads();
-    const long long cc = s_cc, pn = s_p + cc;
+    const long long cc = s_cc;
+    long long pn = s_p + cc;
+    if (a.pool_rows > 0 && pn + a.rows > a.pool_rows) {  // the next window would leave the pools: clamp and record
+        if (tid == 0 && a.status != nullptr && atomicCAS(a.status, 0, 4) == 0) a.status[1] = 320, a.status[3] = (int)pn;
+        pn = a.pool_rows - a.rows;
+    }
     // target feeds: the window's rows sit at positions P' .. P' + rows - 1, identity slots
     if (a.cos_sin != nullptr) {
         for (int i = tid; i < a.rows * 64; i += 1024) {

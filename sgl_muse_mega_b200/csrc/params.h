@@ -15,8 +15,9 @@ constexpr int kHeadDim = 64;
 // ---- cross-GPU exchange points -----------------------------------------------------------------------------------------
 // A tensor-parallel world of one process per GPU synchronises each exchange (the kernels store their results straight
 // into the peers' buffers) with one counter word per exchange point in every rank's flag block:
-//   producer kernel   every CTA: stores, barrier, system fence, arrive on a local counter; the last CTA advances the local
-//                     epoch word and adds 1 to the exchange's word on every rank that received data (own included);
+//   producer kernel   every CTA: stores, barrier, device-scope fence, arrive on a local counter; the last CTA advances the
+//                     local epoch word, fences at system scope and adds 1 to the exchange's word on every rank that
+//                     received data (own included);
 //   consumer kernel   after its programmatic-launch wait, one thread per CTA polls its own word until it reaches
 //                     epoch x contributors, at most `budget` polls; a wait that runs out records itself in the status
 //                     block and the kernel carries on (its outputs are then meaningless, nothing hangs).
@@ -30,6 +31,7 @@ constexpr int kXchgWords = 32;
 struct XchgSignal {
     unsigned* flag[kMaxRanks];  // the exchange's word on every receiving rank
     int n;                      // 0: off
+    int remote;                 // some receiver is another rank (system-scope ordering needed)
     unsigned* done;
     unsigned* epoch;
 };
@@ -47,13 +49,20 @@ __device__ __forceinline__ void xchg_signal(const XchgSignal& x) {
     if (x.n == 0) return;
     __syncthreads();
     if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
-        __threadfence_system();
+        // Every CTA publishes its stores at device scope and arrives; the last one to arrive has thereby observed all of
+        // them and alone pays the system-scope fence (microseconds) that orders them before the peers' flag words.
+        __threadfence();
         const unsigned total = gridDim.x * gridDim.y * gridDim.z;
         if (atomicAdd(x.done, 1u) == total - 1) {
             *x.done = 0;
             *(volatile unsigned*)x.epoch = *(volatile unsigned*)x.epoch + 1;
-            __threadfence_system();
-            for (int i = 0; i < x.n; ++i) atomicAdd_system(x.flag[i], 1u);
+            if (x.remote) {
+                __threadfence_system();
+                for (int i = 0; i < x.n; ++i) atomicAdd_system(x.flag[i], 1u);
+            } else {  // the only receiver is this GPU: device scope is enough
+                __threadfence();
+                for (int i = 0; i < x.n; ++i) atomicAdd(x.flag[i], 1u);
+            }
         }
     }
 }

@@ -110,6 +110,7 @@ constexpr int kTopkPer = 32;  // E <= 1024
 
 static __device__ void topk_row(const TopkArgs& a, int row, int lane, int* s_ids) {
     float sel[kTopkPer];
+    bool bad = false;
 #pragma unroll
     for (int i = 0; i < kTopkPer; ++i) {
         const int e = lane + 32 * i;
@@ -118,7 +119,18 @@ static __device__ void topk_row(const TopkArgs& a, int row, int lane, int* s_ids
             const double z = (double)a.logits[(size_t)row * a.E + e] * a.mult;
             const float s = (float)(1.0 / (1.0 + exp(-z)));
             sel[i] = s + a.bias[e];
+            // a NaN score (non-finite hidden rows upstream) must still leave k distinct, in-range experts: it ranks
+            // below every number, the lower id first; the status block records that the row was not routable
+            if (!(sel[i] == sel[i])) {
+                sel[i] = -3.0e38f;
+                bad = true;
+            }
+            sel[i] = fmaxf(sel[i], -3.0e38f);  // above the -inf that marks "taken" or "no such expert"
         }
+    }
+    if (__any_sync(0xffffffffu, bad) && lane == 0 && a.status != nullptr && atomicCAS(a.status, 0, 6) == 0) {
+        a.status[1] = 6;  // the routing stage
+        a.status[2] = row;
     }
     float total = 0.f, mine = 0.f;
     int myid = 0;

@@ -271,7 +271,10 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
         memset(&x, 0, sizeof x);
         if (flags == nullptr) return;
         for (int r = first; r < first + count; ++r)
-            if (flag_of(r)) x.flag[x.n++] = flag_of(r) + point;
+            if (flag_of(r)) {
+                x.flag[x.n++] = flag_of(r) + point;
+                x.remote |= r != s.rank;
+            }
         x.done = flags + kXchgDone + point;
         x.epoch = flags + kXchgEpoch + point;
     };
@@ -386,7 +389,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     wait_for(L->post_norm.wait, XP_AR, 0, all, ST_POST_NORM);
     wait_for(L->cross_norm.wait, XP_UNPOOL, node0, nr, ST_CROSS_NORM);
     L->topk = TopkArgs{(const float*)b->logits, (const float*)b->expert_bias, (int*)b->topk_idx32, (float*)b->topk_w,
-                       b->router_mult, (float)b->route_scale, E, K, M};
+                       b->router_mult, (float)b->route_scale, E, K, M, (int*)b->status};
     L->nq = NqArgs{(const bf16*)b->pool_ag, (const bf16*)b->gamma, (unsigned char*)b->q, (unsigned char*)b->sf,
                    (float*)b->x_scale, (float)b->eps, P, (int)s.bf16};
     L->combine = CombineArgs{(const bf16*)b->zb, (const float*)b->topk_w, (const bf16*)b->gamma_p1, (bf16*)b->y, P, K, b_live};
@@ -687,7 +690,10 @@ int mk_lm_head_bind(MkModule* module, const MkLmHeadBind* b, MkLaunch** out) {
                 delete L;
                 return fail("flags_peer[%d] and out_peer[%d] disagree on the rank's presence", r, r);
             }
-            if (f) g.sig.flag[g.sig.n++] = f + XP_LOGITS;
+            if (f) {
+                g.sig.flag[g.sig.n++] = f + XP_LOGITS;
+                g.sig.remote |= r != b->rank;
+            }
         }
         g.sig.done = flags + kXchgDone + XP_LOGITS;
         g.sig.epoch = flags + kXchgEpoch + XP_LOGITS;
@@ -728,6 +734,8 @@ int mk_accept_bind(MkModule* module, const MkAcceptBind* b, MkLaunch** out) {
                            (const float*)b->dcos_sin_cache, b->dcos_sin_rows, (float*)b->dcos_sin, (int*)b->dslot, (int*)b->dkv_len,
                            (int)b->dring};
     logits_wait(L->accept.wait, b->flags, b->contributors, b->wait_budget, b->status);
+    L->accept.pool_rows = b->pool_rows;
+    L->accept.status = (int*)b->status;
     L->status = (int*)b->status;
     *out = L;
     return 0;

@@ -38,6 +38,7 @@ struct TopkArgs {
     double mult;
     float route_scale;
     int E, k, M;
+    int* status;  // a row with NaN scores is recorded here (code 6); may be null
 };
 struct NqArgs {
     const bf16* pooled;
@@ -221,6 +222,8 @@ struct AcceptArgs {
     int* dkv_len;
     int dring;
     XchgWait wait;                    // the lm_head shards of every rank
+    long long pool_rows;              // 0: unchecked
+    int* status;
 };
 cudaError_t feeds_launch(const FeedsArgs& a, cudaStream_t s, bool pdl);
 cudaError_t entry_launch(const EntryArgs& a, cudaStream_t s, bool pdl);

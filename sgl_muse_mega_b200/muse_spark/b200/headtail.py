@@ -116,7 +116,7 @@ class Accept:
     def __init__(self, lib: host.Library, module, *, logits, tokens, b_live: int, scale: float, cap: float, ring: int = 64,
                  accept_override: Optional[torch.Tensor] = None, cos_sin_cache=None, cos_sin=None, loc_full=None,
                  loc_swa=None, kv_len=None, dcos_sin_cache=None, dring: int = 0, flags=None, contributors: int = 0,
-                 wait_budget: int = 0):  # fmt: skip
+                 wait_budget: int = 0, pool_rows: int = 0):  # fmt: skip
         dev = logits.device
         rows, vocab = logits.shape
         self.words = _z(N_WORDS, dtype=torch.int64, device=dev)
@@ -137,6 +137,6 @@ class Accept:
             cos_sin=cos_sin, loc_full=loc_full, loc_swa=loc_swa, kv_len=kv_len, dcos_sin_cache=dcos_sin_cache,
             dcos_sin_rows=0 if dcos_sin_cache is None else dcos_sin_cache.shape[0], dcos_sin=self.dcos_sin,
             dslot=self.dslot, dkv_len=self.dkv_len, dring=dring, flags=flags, contributors=contributors,
-            wait_budget=wait_budget, status=self.status,
+            wait_budget=wait_budget, status=self.status, pool_rows=pool_rows,
         )  # fmt: skip
         self.launch = lib.bind("mk_accept_bind", module, self.bind)

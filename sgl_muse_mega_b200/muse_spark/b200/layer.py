@@ -128,7 +128,11 @@ class LayerRank:
         self.ar = shared("ar", c.ar_bytes)
         self.pool_ag = io["pool_ag"] if "pool_ag" in io else z((M, P), bf)
         self.unpool_ag = io["unpool_ag"] if "unpool_ag" in io else z((M, H), bf)
-        self.z, self.z_sf = shared("z", c.z_bytes), shared("z_sf", c.z_sf_bytes)
+        # a stack keeps the bf16 layers' h rows apart from the NVFP4 layers' code planes ("z16"): a column band that an
+        # absent rank never writes then stays zero in both, instead of holding the other kind's bytes
+        self.z_name = "z16" if case.bf16 and "z16" in io else "z"
+        self.z, self.z_sf = shared(self.z_name, c.z_bytes), shared("z_sf", c.z_sf_bytes)
+        self.z16 = self.z
         self.z_ex, self.zb = shared("z_ex", c.z_ex_bytes), shared("zb", c.zb_bytes)
         self.flags = io["flags"] if "flags" in io else z((c.flag_words,), i32)
         self.ws = raw(c.ws_bytes)
@@ -163,7 +167,7 @@ class LayerRank:
             w1_up_sf=w["up_sf"], w2=w["w2_q"] if fp4 else w["w2"], w2_sf=w["w2_sf"], w1_pack=self.w1_pack,
             w2_pack=self.w2_pack, g1_alphas=w["g1_alphas"],
             g1_scale_c=w["g1_scale_c"], g2_alphas=w["g2_alphas"], z=self.z, z_sf=self.z_sf, z_ex=self.z_ex, zb=self.zb,
-            z_peer=peer("z"), zsf_peer=peer("z_sf"), zex_peer=peer("z_ex"), zb_peer=peer("zb"),
+            z_peer=peer(self.z_name), zsf_peer=peer("z_sf"), zex_peer=peer("z_ex"), zb_peer=peer("zb"),
             gamma_p1=w["gamma_p1"], y=o["y"], w_up=w["unpooler"], unpool_ag=self.unpool_ag,
             unpool_ag_peer=peer("unpool_ag"), c_alpha=w["cross_alpha"], c_beta=w["cross_beta"], c_pre_w=w["cross_pre_w"],
             c_post_w=w["cross_post_w"], c_stream_out=o["stream_out"], h3q=o["h3_next"], w_qkv=w["next_qkv"],

@@ -15,6 +15,7 @@ contributions before any rank reads it).
 
 from __future__ import annotations
 
+import dataclasses
 from typing import Optional
 
 import torch
@@ -24,7 +25,7 @@ from . import headtail as HT
 from .head import QkvHead
 from .layer import STAGE_GROUPS, LayerRank
 
-EXCHANGE = ("ar", "pool_ag", "unpool_ag", "z", "z_sf", "z_ex", "zb", "flags", "gathered", "embed")
+EXCHANGE = ("ar", "pool_ag", "unpool_ag", "z", "z16", "z_sf", "z_ex", "zb", "flags", "gathered", "embed")
 
 
 def exchange_layout(cfg, rows: int) -> symm.Layout:
@@ -36,7 +37,8 @@ def exchange_layout(cfg, rows: int) -> symm.Layout:
     lay.add("ar", (cfg.tp * rows * cfg.hidden * 2,), u8)
     lay.add("pool_ag", (rows, cfg.moe_hidden), bf)
     lay.add("unpool_ag", (rows, cfg.hidden), bf)
-    lay.add("z", (slots * cfg.moe_inter * 2,), u8)  # the bf16 variant's size; NVFP4 layers use the first quarter
+    lay.add("z", (slots * cfg.moe_inter // 2,), u8)  # the NVFP4 layers' h codes
+    lay.add("z16", (slots * cfg.moe_inter * 2,), u8)  # the bf16-expert layers' h rows, kept apart: see LayerRank
     lay.add("z_sf", (slots * cfg.moe_inter // 16,), u8)
     lay.add("z_ex", (slots * cfg.moe_inter // 16,), u8)
     lay.add("zb", (slots * cfg.moe_hidden * 2,), u8)
@@ -109,38 +111,40 @@ class Stack:
         self.logits_out = None if greedy else torch.zeros(M, cfg.vocab, dtype=torch.float32, device=device)
         self.greedy, self.accept_override, self.ring = greedy, accept_override, ring
         # ---- the KV pools: one pair per layer; context rows from the case ----
-        self.pools = []
-        for lc in case.layers:
-            t = lc.ranks[slot]
-            k, v = (torch.zeros(kv_rows, kvw, dtype=bf, device=device) for _ in range(2))
-            k[: case.ctx] = t.k_ctx.reshape(case.ctx, kvw).to(device)
-            v[: case.ctx] = t.v_ctx.reshape(case.ctx, kvw).to(device)
-            self.pools.append((k, v))
+        n = len(case.layers)
+        self.pools = [tuple(torch.zeros(kv_rows, kvw, dtype=bf, device=device) for _ in range(2)) for _ in range(n)]
         # ---- the entry and layer 0's head (the peers' shards are wired in bind) ----
         self.residual0 = torch.zeros(M, cfg.hidden, dtype=torch.float32, device=device)
         self.normed0 = torch.zeros(M, cfg.hidden, dtype=bf, device=device)
-        l0 = case.layers[0]
+        global0 = cfg.is_global(case.first_layer)
         self.qkv_head = QkvHead(
             self.lib, module, w=self.qkv0, x=self.normed0, q_heads=cfg.q_heads_rank, kv_heads=cfg.kv_heads_rank,
-            q_scale=cfg.q_scale, eps=cfg.rms_eps, cos_sin=None if l0.global_attn else f.cos_sin,
-            cache_loc=f.loc_full if l0.global_attn else f.loc_swa, k_cache=self.pools[0][0], v_cache=self.pools[0][1],
+            q_scale=cfg.q_scale, eps=cfg.rms_eps, cos_sin=None if global0 else f.cos_sin,
+            cache_loc=f.loc_full if global0 else f.loc_swa, k_cache=self.pools[0][0], v_cache=self.pools[0][1],
         )  # fmt: skip
-        # ---- layers, chained through io; the exchange buffers are the arena's, shared by all layers ----
-        shared = {k: self.arena.tensor(k) for k in ("ar", "pool_ag", "unpool_ag", "z", "z_sf", "z_ex", "zb", "flags")}
+        # ---- layers, chained through io; the exchange buffers are the arena's, shared by all layers. One layer's
+        # weights at a time: ``case.layers`` may draw them on demand, and without ``keep_plain_experts`` nothing of a
+        # layer but its packed images and dense weights stays on the device ----
+        shared = {k: self.arena.tensor(k) for k in ("ar", "pool_ag", "unpool_ag", "z", "z16", "z_sf", "z_ex", "zb", "flags")}
         self.layers: list[LayerRank] = []
         qkv_in, stream_in = self.qkv_head.out, self.residual0
-        n = len(case.layers)
-        for j, lc in enumerate(case.layers):
+        for j in range(n):
+            lc = case.layers[j]
+            t = lc.ranks[slot]
             k, v = self.pools[j]
+            k[: case.ctx] = t.k_ctx.reshape(case.ctx, kvw).to(device)
+            v[: case.ctx] = t.v_ctx.reshape(case.ctx, kvw).to(device)
             nk, nv = self.pools[j + 1] if j + 1 < n else self.pools[j]
-            nxt_global = j + 1 < n and case.layers[j + 1].global_attn
             io = dict(shared, qkv_in=qkv_in, stream_in=stream_in, k_cache=k, v_cache=v, next_k=nk, next_v=nv,
                       page_table=f.pt_full if lc.global_attn else f.pt_swa, kv_len=f.kv_len,
-                      cache_loc=f.loc_full if nxt_global else f.loc_swa)  # fmt: skip
+                      cache_loc=f.loc_full if lc.next_global else f.loc_swa)  # fmt: skip
             if not (lc.tail or lc.next_global):
                 io["next_cos_sin"] = f.cos_sin
-            lr = LayerRank(self.lib, module, lc, rank, device, tensors=lc.ranks[slot], tensor_cores=tensor_cores,
+            lr = LayerRank(self.lib, module, lc, rank, device, tensors=t, tensor_cores=tensor_cores,
                            keep_plain_experts=keep_plain_experts, io=io)  # fmt: skip
+            if not keep_plain_experts:
+                lr.case = dataclasses.replace(lc, ranks=[])  # the device copies live in lr.w
+            del lc, t
             self.layers.append(lr)
             qkv_in, stream_in = lr.o["qkv_next"], lr.o["stream_out"]
         self.hidden = self.layers[-1].o["h3_next"]
@@ -176,6 +180,7 @@ class Stack:
                 scale=cfg.output_multiplier, cap=cfg.softcap, ring=self.ring, accept_override=self.accept_override,
                 cos_sin_cache=self.cos_sin_cache, cos_sin=f.cos_sin, loc_full=f.loc_full, loc_swa=f.loc_swa,
                 kv_len=f.kv_len, flags=flags, contributors=present, wait_budget=self.wait_budget,
+                pool_rows=self.kv_rows,
             )  # fmt: skip
             self.accept.words[HT.WORDS["P"]] = case.ctx
             self.tail = self.accept
@@ -290,10 +295,12 @@ def connect_world(stack: Stack, group=None) -> list:
     ``stack`` against them. Returns the peer list (keep it alive as long as the stack launches)."""
     import torch.distributed as dist
 
-    n, r = stack.case.cfg.tp, stack.rank
-    assert dist.get_world_size(group) == n and dist.get_rank(group) == r, "one process per rank of the model's world"
+    n, r = dist.get_world_size(group), stack.rank
+    tp = stack.case.cfg.tp
+    assert n <= tp and dist.get_rank(group) == r, "one process per present rank of the model's world, ranks 0 .. n - 1"
     arenas = symm.connect(stack.arena, r, n, group, stack.lib)
-    peers = [stack if i == r else PeerStack(a) for i, a in enumerate(arenas)]
+    # a world smaller than the model's (ranks n .. tp - 1 absent) exchanges among the present ranks only
+    peers = [stack if i == r else PeerStack(a) for i, a in enumerate(arenas)] + [None] * (tp - n)
     stack.bind(peers)
     dist.barrier(group)
     return peers

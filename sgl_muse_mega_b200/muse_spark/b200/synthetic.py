@@ -270,24 +270,42 @@ class StackCase:
     pre_w0: torch.Tensor  # [H] bf16
     cos_sin_cache: torch.Tensor  # [positions, 64] f32
     ranks: list  # the ranks drawn, in the order of the per-rank lists
+    first_layer: int = 0  # model index of layers[0]
+
+
+class LazyLayers:
+    """The layers of a stack drawn on demand, one ``LayerCase`` per access and none kept: a 62-layer model's plain
+    weights never sit in memory together."""
+
+    def __init__(self, n: int, draw):
+        self.n, self.draw = n, draw
+
+    def __len__(self) -> int:
+        return self.n
+
+    def __getitem__(self, j: int) -> LayerCase:
+        if not 0 <= j < self.n:
+            raise IndexError(j)
+        return self.draw(j)
 
 
 def stack_case(cfg: Config, *, n_layers: int, rows: int, ctx: int, seed: int = 0, band: str = "baseline",
-               only_ranks: Optional[list] = None, max_pos: Optional[int] = None, first_layer: int = 0) -> StackCase:  # fmt: skip
+               only_ranks: Optional[list] = None, max_pos: Optional[int] = None, first_layer: int = 0,
+               lazy: bool = False) -> StackCase:  # fmt: skip
     """Layers ``first_layer .. first_layer + n_layers - 1`` of a model of ``cfg.layers`` layers with the variants the
     model gives them (sliding-window / global by ``cfg.is_global``, bf16 experts by ``cfg.bf16_moe_layers``); the last
     drawn layer is the tail (its cross-layer norm is the final norm, no successor head)."""
     ranks = list(only_ranks) if only_ranks is not None else list(range(cfg.tp))
     bf = torch.bfloat16
-    layers = []
-    for j in range(n_layers):
+
+    def draw(j: int) -> LayerCase:
         i = first_layer + j
         tail = j == n_layers - 1
-        layers.append(
-            layer_case(cfg, rows=rows, ctx=ctx, global_attn=cfg.is_global(i), bf16=cfg.is_bf16(i),
-                       next_global=(not tail) and cfg.is_global(i + 1), tail=tail, band=band, seed=seed, layer=i,
-                       only_ranks=ranks)  # fmt: skip
-        )
+        return layer_case(cfg, rows=rows, ctx=ctx, global_attn=cfg.is_global(i), bf16=cfg.is_bf16(i),
+                          next_global=(not tail) and cfg.is_global(i + 1), tail=tail, band=band, seed=seed, layer=i,
+                          only_ranks=ranks)  # fmt: skip
+
+    layers = LazyLayers(n_layers, draw) if lazy else [draw(j) for j in range(n_layers)]
     H = cfg.hidden
     cache = rope_rows(cfg, torch.arange(max_pos or (ctx + 64 * rows))).to(_DEVICE)
     return StackCase(
@@ -298,4 +316,5 @@ def stack_case(cfg: Config, *, n_layers: int, rows: int, ctx: int, seed: int = 0
         pre_w0=uniform((H,), 0.8, 1.2, bf, seed, "pre_w0"),
         cos_sin_cache=cache,
         ranks=ranks,
+        first_layer=first_layer,
     )  # fmt: skip

@@ -102,7 +102,7 @@ def test_bind_argument_checks():
     a = dict(logits=p, vocab=1000, rows=16, b_live=16, scale=1.0, cap=20.0, tokens=p, accept_override=0, n_override=0,
              words=p, out_ring=p, ring=64, top1=p, counter=p, cos_sin_cache=0, cos_sin_rows=0, cos_sin=0, loc_full=0,
              loc_swa=0, kv_len=0, dcos_sin_cache=0, dcos_sin_rows=0, dcos_sin=0, dslot=0, dkv_len=0, dring=0, flags=0,
-             contributors=0, wait_budget=0, status=0)  # fmt: skip
+             contributors=0, wait_budget=0, status=0, pool_rows=0)  # fmt: skip
     assert _lib().bind("mk_accept_bind", None, host.make("MkAcceptBind", **a)).info().kernels == 1
     _expect("mk_accept_bind", host.make("MkAcceptBind", **{**a, "b_live": 17}), "b_live")
     _expect("mk_accept_bind", host.make("MkAcceptBind", **{**a, "ring": 8}), "ring")

@@ -105,3 +105,24 @@ def test_replay_is_bitwise_deterministic(device):
         for other in (second, third, fourth):
             assert torch.equal(first[k].view(torch.uint8), other[k].view(torch.uint8)), k
     assert rank.launch_record.status(stream.cuda_stream).code == 0
+
+
+def test_non_finite_rows_are_routed_in_range_and_recorded(device):
+    """A NaN residual row gives NaN router scores: the routing still names k distinct experts of the model for it (the
+    lowest ids), the other rows are untouched, and the status block says which stage met it; nothing traps."""
+    cfg, kw = CASES["small_fp4_swa_tp1_m5"]
+    case = synthetic.layer_case(cfg, **kw)
+    clean = L.LayerWorld(case, device)
+    clean.run_interleaved()
+    world = L.LayerWorld(case, device)
+    rank = world.ranks[0]
+    rank.w["stream_in"][2] = float("nan")
+    world.run_interleaved()
+    torch.cuda.synchronize()
+    ids = rank.o["ids"].cpu()
+    assert int(ids.min()) >= 0 and int(ids.max()) < cfg.experts
+    assert ids[2].tolist() == list(range(cfg.topk))
+    keep = [0, 1, 3, 4]
+    assert torch.equal(ids[keep], clean.ranks[0].o["ids"].cpu()[keep])
+    st = rank.launch_record.status(torch.cuda.current_stream().cuda_stream)
+    assert (st.code, st.stage, st.block) == (6, 6, 2)

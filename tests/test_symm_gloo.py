@@ -97,7 +97,7 @@ def test_layout_is_aligned_and_sized_for_the_full_model():
     assert all(off % symm.ALIGN == 0 for off, _, _ in lay.items.values())
     sizes = {k: symm._nbytes(s, d) for k, (_, s, d) in lay.items.items()}
     assert sizes["ar"] == 8 * 16 * 8192 * 2 and sizes["gathered"] == 16 * 202048 * 4
-    assert sizes["embed"] == 25256 * 8192 * 2 and sizes["z"] == 128 * 4096 * 2
+    assert sizes["embed"] == 25256 * 8192 * 2 and sizes["z16"] == 128 * 4096 * 2 and sizes["z"] == 128 * 4096 // 2
     assert lay.nbytes < 450 * 2**20
     with pytest.raises(ValueError):
         lay.add("ar", (1,), torch.uint8)
