@@ -43,6 +43,7 @@ def parse():
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--cpu-sample-experts", type=int, default=24)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--fused", action="store_true", help="the dense stages as two persistent segment kernels")
     ap.add_argument("--decode-layers", type=int, default=62, help="layers of the whole-step leg (0: skip it)")
     ap.add_argument("--decode-steps", type=int, default=24)
     ap.add_argument("--accept", type=int, default=6, help="forced accept length of the whole-step leg")
@@ -340,7 +341,7 @@ def run_ours(args) -> None:
         lr.z_sf.copy_(torch.randint(0x30, 0x40, lr.z_sf.shape, generator=g, device=device, dtype=torch.uint8))
         lr.z_ex.copy_(torch.randint(0, 3, lr.z_ex.shape, generator=g, device=device, dtype=torch.uint8))
         lr.zb.view(torch.bfloat16).copy_(torch.randn(lr.zb.numel() // 2, generator=g, device=device))
-        lr.bind(None)
+        lr.bind(None, fused=args.fused)
         case.ranks = []  # the device copies live in lr.w
         ring.append(lr)
     torch.cuda.synchronize()

@@ -204,6 +204,12 @@ typedef struct MkLayerBind {
     uint64_t status;        // status_bytes, zeroed once by the caller
     int64_t b_live;         // live window rows (abi.h:208-210)
     int64_t wait_budget;    // polls before an exchange wait gives up (0: library default)
+    // 1: mk_launch runs the dense stages (o_proj .. routing, combine .. successor's qkv head) as two persistent kernels of one
+    // CTA per SM with grid barriers between their stages, 7 kernels a layer instead of 14. Their exchange waits poll for
+    // peers that run at the same time: for a lone rank or one process per GPU, never for several ranks launched one after
+    // the other on one GPU. mk_launch_step always runs the per-stage kernels. Shapes the fused form does not tile keep the
+    // per-stage kernels (mk_launch_info.kernels tells which form was bound).
+    int64_t fused;
 } MkLayerBind;
 int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind* bind, MkLaunch** out);
 

@@ -68,10 +68,16 @@ __device__ __forceinline__ void xchg_signal(const XchgSignal& x) {
 }
 
 // Every thread of every CTA calls this after griddep_wait() and before the first read of exchanged data.
-__device__ __forceinline__ void xchg_wait(const XchgWait& w) {
+// `epoch` is the exchange's epoch to wait for. A consumer kernel that runs after its own rank's producer kernel reads it
+// from the epoch word (xchg_wait); a kernel that holds producer and consumer reads the word once at its start, before any
+// of its CTAs can have signalled, and waits for that value + 1 (xchg_epoch / xchg_wait_epoch).
+__device__ __forceinline__ unsigned xchg_epoch(const XchgWait& w) {
+    return w.flag == nullptr ? 0u : *(volatile const unsigned*)w.epoch;
+}
+__device__ __forceinline__ void xchg_wait_epoch(const XchgWait& w, unsigned epoch) {
     if (w.flag == nullptr) return;
     if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
-        const unsigned want = *(volatile const unsigned*)w.epoch * w.contributors;
+        const unsigned want = epoch * w.contributors;
         long long polls = 0;
         for (;;) {
             unsigned seen;
@@ -93,6 +99,7 @@ __device__ __forceinline__ void xchg_wait(const XchgWait& w) {
     }
     __syncthreads();
 }
+__device__ __forceinline__ void xchg_wait(const XchgWait& w) { xchg_wait_epoch(w, xchg_epoch(w)); }
 
 // Route tables in the private scratch, written by the routing kernel each launch.
 struct RouteTables {

@@ -415,6 +415,12 @@ __global__ void __launch_bounds__(256) rowops_kernel(const RowopsArgs a) {
     if (head >= a.qh && a.k_cache) *(__nv_bfloat162*)(a.k_cache + slot_off + (head - a.qh) * 128 + 4 * lane) = out;
 }
 
+}  // namespace mk
+
+#include "segments.cuh"
+
+namespace mk {
+
 // ---- launch helpers -----------------------------------------------------------------------------------------------------------
 
 template <typename... KArgs, typename... Args>

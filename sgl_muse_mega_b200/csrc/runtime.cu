@@ -72,6 +72,9 @@ struct MkLaunch {
     mk::UmmaArgs umma_g1, umma_g2;
     bool stage_on[ST_COUNT];
     mk::XchgWait hrow_wait;
+    bool use_segments;  // mk_launch runs the dense stages as the two persistent segment kernels
+    mk::SegAArgs seg_a;
+    mk::SegBArgs seg_b;
     // stand-alone launches around the layers (feeds, entry, lm_head, soft cap, accept): n_ops > 0 replaces the stage list
     int n_ops;
     int op_kind[4];
@@ -94,6 +97,12 @@ static int attn_splits_for(const MkLayerShape& s) {
     int sp = 144 / (int)s.kv_heads;
     if (sp < 1) sp = 1;
     if (sp > 72) sp = 72;
+    // a sliding-window layer never sees more than window + rows keys: more splits than 64-key blocks would only add empty
+    // partials for the merge to read
+    if (s.window > 0) {
+        const int blocks = (int)((s.window + s.rows + 63) / 64) + 1;
+        if (sp > blocks) sp = blocks;
+    }
     return sp;
 }
 
@@ -175,6 +184,8 @@ int mk_module_load(const void* image, uint64_t bytes, const char* code_prefetch_
     if (e != cudaSuccess) return cuda_fail(e, "experts_prepare");
     e = experts_umma_prepare();
     if (e != cudaSuccess) return cuda_fail(e, "experts_umma_prepare");
+    e = segments_prepare();
+    if (e != cudaSuccess) return cuda_fail(e, "segments_prepare");
     MkModule* m = new (std::nothrow) MkModule{dev, prop.multiProcessorCount};
     MK_REQUIRE(m != nullptr, "out of host memory");
     *out = m;
@@ -462,6 +473,65 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
             u.sig = g2 ? ex.sig_g2 : ex.sig_g1;
         }
     }
+    // The fused form of the dense stages (segments.cuh): two persistent kernels with grid barriers. Its exchange waits
+    // poll for peers that run at the same time, so it serves a lone rank or one process per GPU; a world emulated on one
+    // GPU steps the per-stage kernels (mk_launch_step) instead. Shapes outside its tiling keep the per-stage kernels.
+    L->use_segments = false;
+    const bool seg_shapes = (qh * kHeadDim) % 512 == 0 && H % 512 == 0 && P % 512 == 0 && H <= 8192 && P <= 4096 &&
+                            (size_t)(P / nr + E) <= (size_t)nmax;
+    if (b->fused && seg_shapes) {
+        L->use_segments = true;
+        auto seg_gemm = [&](SegGemm& g, const GemmArgs& src, bool f32, float* part) {
+            const int es = f32 ? 4 : 2;
+            g.w = (const unsigned char*)src.w;
+            g.x = (const unsigned char*)src.x;
+            g.ldw = (long long)src.ldw * es;
+            g.ldx = (long long)src.ldx * es;
+            g.N = src.N; g.K = src.K; g.M = src.M; g.f32 = f32 ? 1 : 0;
+            g.part = part;
+        };
+        const GridBarrier gb{(unsigned long long*)gcnt, budget, L->status};
+        SegAArgs& A = L->seg_a;
+        memset(&A, 0, sizeof A);
+        seg_gemm(A.oproj, L->oproj, false, gpart);
+        seg_gemm(A.pooler, L->pooler, false, gpart);
+        seg_gemm(A.router, L->router, true, gpart + (size_t)16 * 16 * (P / nr));
+        for (int i = 0; i < L->oproj.n_out; ++i) A.ar_out[i] = (bf16*)L->oproj.out[i];
+        A.n_ar = L->oproj.n_out;
+        A.ar_off = 0;  // the destinations already point at this rank's slot
+        A.sig_ar = L->oproj.sig;
+        A.post_norm = L->post_norm;
+        for (int i = 0; i < L->pooler.n_out; ++i) A.pool_out[i] = (bf16*)L->pooler.out[i];
+        A.n_pool = L->pooler.n_out;
+        A.pool_ld = L->pooler.ldo;
+        A.pool_col0 = L->pooler.col0;
+        A.sig_pool = L->pooler.sig;
+        A.logits = (float*)b->logits;
+        A.topk = L->topk;
+        A.nq = L->nq;
+        A.rt = L->rt;
+        A.b_live = b_live;
+        A.gb = gb;
+        A.status = L->status;
+        SegBArgs& B = L->seg_b;
+        memset(&B, 0, sizeof B);
+        B.combine = L->combine;
+        B.M = M;
+        seg_gemm(B.unpool, L->unpool, false, gpart);
+        for (int i = 0; i < L->unpool.n_out; ++i) B.unpool_out[i] = (bf16*)L->unpool.out[i];
+        B.n_unpool = L->unpool.n_out;
+        B.unpool_ld = L->unpool.ldo;
+        B.unpool_col0 = L->unpool.col0;
+        B.sig_unpool = L->unpool.sig;
+        B.cross_norm = L->cross_norm;
+        B.tail = tail ? 1 : 0;
+        if (!tail) {
+            seg_gemm(B.qkv, L->qkv, false, gpart);
+            B.qkv_epi = L->qkv;
+        }
+        B.gb = gb;
+        B.status = L->status;
+    }
     *out = L;
     guard.l = nullptr;
     return 0;
@@ -537,6 +607,18 @@ int mk_launch(const MkLaunch* launch, uint64_t stream, int pdl) {
     MK_REQUIRE(launch != nullptr, "launch is NULL");
     MK_REQUIRE(!launch->pack_only, "a pack-only record (bound without a module) cannot launch");
     if (launch->n_ops > 0) return run_ops(launch, (cudaStream_t)stream, pdl != 0);
+    if (launch->use_segments) {
+        const MkLaunch* L = launch;
+        cudaStream_t s = (cudaStream_t)stream;
+        const bool p = pdl != 0;
+        if (run_stage(L, ST_ATTN_SPLIT, s, false) || run_stage(L, ST_ATTN_COMBINE, s, p)) return -1;
+        cudaError_t e = seg_a_launch(L->seg_a, L->sms, s, p);
+        if (e != cudaSuccess) return fail("segment A launch: %s", cudaGetErrorString(e));
+        if (run_stage(L, ST_G1, s, p) || run_stage(L, ST_HROW, s, p) || run_stage(L, ST_G2, s, p)) return -1;
+        e = seg_b_launch(L->seg_b, L->sms, s, p);
+        if (e != cudaSuccess) return fail("segment B launch: %s", cudaGetErrorString(e));
+        return 0;
+    }
     for (int st = 0; st < ST_COUNT; ++st)
         if (run_stage(launch, st, (cudaStream_t)stream, pdl != 0 && st > 0)) return -1;
     return 0;
@@ -559,6 +641,7 @@ int mk_launch_info(const MkLaunch* launch, MkLaunchInfo* out) {
     }
     int kernels = 0;
     for (int i = 0; i < ST_COUNT; ++i) kernels += L->stage_on[i];
+    if (L->use_segments) kernels = 6 + (L->stage_on[ST_HROW] ? 1 : 0);  // attention x 2, segment A, g1, [h row], g2, segment B
     int64_t grid = 0, smem = 0;
     auto gg = [&](const GemmArgs& g, bool f32) {
         const int64_t n = gemm_grid(g);

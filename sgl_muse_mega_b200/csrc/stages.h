@@ -230,6 +230,56 @@ cudaError_t entry_launch(const EntryArgs& a, cudaStream_t s, bool pdl);
 cudaError_t softcap_launch(const SoftcapArgs& a, cudaStream_t s, bool pdl);
 cudaError_t accept_launch(const AcceptArgs& a, cudaStream_t s, bool pdl);
 
+// segments.cuh (compiled with rows.cu): the dense GEMMs and the row work between them as two persistent kernels
+struct SegGemm {
+    const unsigned char* w;  // [N, K] row-major
+    const unsigned char* x;  // [M, K] row-major (bf16, or f32 with f32 weights)
+    long long ldw, ldx;      // row strides in bytes
+    int N, K, M;
+    int f32;                 // 1: f32 weights through tf32 (tile 16 rows), 0: bf16 (tile 64 rows)
+    float* part;             // [K / 512][16][N] f32 partial sums
+};
+struct GridBarrier {
+    unsigned long long* count;  // starts at a multiple of the grid size and only grows
+    long long budget;
+    int* status;
+};
+struct SegAArgs {  // o_proj .. routing
+    SegGemm oproj, pooler, router;
+    bf16* ar_out[kMaxRanks];    // every present rank's all-reduce workspace
+    int n_ar;
+    long long ar_off;           // this rank's slot in a workspace (elements)
+    XchgSignal sig_ar;
+    NormArgs post_norm;
+    bf16* pool_out[kMaxRanks];  // the node group's gather rows
+    int n_pool, pool_ld, pool_col0;
+    XchgSignal sig_pool;
+    float* logits;
+    TopkArgs topk;
+    NqArgs nq;
+    RouteTables* rt;
+    int b_live;
+    GridBarrier gb;
+    int* status;
+};
+struct SegBArgs {  // combine .. successor's qkv head
+    CombineArgs combine;
+    int M;
+    SegGemm unpool, qkv;
+    bf16* unpool_out[kMaxRanks];
+    int n_unpool, unpool_ld, unpool_col0;
+    XchgSignal sig_unpool;
+    NormArgs cross_norm;
+    GemmArgs qkv_epi;           // the epilogue operands of the qkv head (out, cos_sin, cache_loc, pools, scales)
+    int tail;                   // 1: no successor (the cross-layer norm is the final norm)
+    GridBarrier gb;
+    int* status;
+};
+size_t segments_smem();
+cudaError_t segments_prepare();
+cudaError_t seg_a_launch(const SegAArgs& a, int grid, cudaStream_t s, bool pdl);
+cudaError_t seg_b_launch(const SegBArgs& a, int grid, cudaStream_t s, bool pdl);
+
 size_t experts_umma_smem(bool g2);
 cudaError_t experts_umma_prepare();
 cudaError_t experts_umma_launch(const UmmaArgs& a, bool g2, int grid, cudaStream_t s, bool pdl);

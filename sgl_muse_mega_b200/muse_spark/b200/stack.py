@@ -66,7 +66,7 @@ class Stack:
     def __init__(self, case, rank: int, device, lib: Optional[host.Library] = None, module=None, *, arena=None,
                  kv_rows: Optional[int] = None, tensor_cores: bool = True, keep_plain_experts: bool = True,
                  greedy: bool = True, accept_override: Optional[torch.Tensor] = None, ring: int = 64,
-                 b_live: int = 0, wait_budget: int = 0):  # fmt: skip
+                 b_live: int = 0, wait_budget: int = 0, fused: bool = False):  # fmt: skip
         """``case``: a ``synthetic.StackCase``; ``rank`` must be one of ``case.ranks``. ``arena``: the rank's exchange
         memory carved by ``exchange_layout`` (default: ordinary tensors, for a world inside one process). ``greedy``
         False ends the step with the soft cap (the logits go to ``self.logits_out``) instead of the accept."""
@@ -76,7 +76,7 @@ class Stack:
                 module = self.lib.load()
         self.module, self.case, self.rank, self.device = module, case, rank, device
         cfg, M = case.cfg, case.rows
-        self.b_live, self.wait_budget = b_live or M, wait_budget
+        self.b_live, self.wait_budget, self.fused = b_live or M, wait_budget, fused
         slot = case.ranks.index(rank)
         dev = lambda t: t.to(device).contiguous()  # noqa: E731
         i64, i32, bf = torch.int64, torch.int32, torch.bfloat16
@@ -161,6 +161,9 @@ class Stack:
             peers = [self if r == self.rank else None for r in range(n)]
         views = [None if p is None else p.view for p in peers]
         present = sum(v is not None for v in views)
+        # the fused segment kernels only on request, and never for peers that live in this process (they are launched one
+        # after the other on this GPU, and a segment's exchange waits poll for ranks that run at the same time)
+        fused = self.fused and not any(isinstance(p, Stack) and p is not self for p in peers)
         # the entry reads the owner rank's shard; an absent rank's rows read this rank's shard (a lone-rank timing run)
         shards = [(v.embed if v is not None else self.view.embed) for v in views]
         self.entry = HT.Entry(self.lib, self.module, ids=self.tokens, embed_shards=shards, pre_w=self.pre_w0,
@@ -168,7 +171,7 @@ class Stack:
                               residual=self.residual0, normed=self.normed0)  # fmt: skip
         live = self.b_live if self.b_live != M else 0
         for lr in self.layers:
-            lr.bind(views, live, self.wait_budget)
+            lr.bind(views, live, self.wait_budget, fused=fused)
         flags = self.arena.tensor("flags")
         self.lm_head = HT.LmHead(self.lib, self.module, w=self.lm_head_w, x=self.hidden,
                                  gathered=[None if v is None else v.gathered for v in views], rank=self.rank,

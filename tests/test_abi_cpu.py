@@ -72,9 +72,11 @@ def test_pack_only_bind_and_refusals(lib):
     cfg, kw = CASES["small_fp4_swa_tp2"]
     case = synthetic.layer_case(cfg, **kw)
     rank = L.LayerRank(lib, None, case, 0, torch.device("cpu"))
-    rec = rank.bind()
+    rec = rank.bind(fused=False)
     info = rec.info()
     assert info.kernels == 14 and info.grid > 0 and info.smem > 0  # 17 stage slots; top-k + tables + nq share a launch, the row ops ride the qkv GEMM
+    # the fused form on request: attention x 2, segment A, g1, h row, g2, segment B
+    assert rank.bind().info().kernels == 14 and rank.bind(fused=True).info().kernels == 7
     with pytest.raises(RuntimeError, match="pack-only"):
         rec(0, False)
     # a missing operand is named
@@ -92,8 +94,9 @@ def test_module_load_needs_builtin_image(lib):
 def test_tail_and_bf16_variants_drop_stages(lib):
     cfg, kw = CASES["small_bf16_tail_tp4"]
     case = synthetic.layer_case(cfg, **kw)
-    rec = L.LayerRank(lib, None, case, 1, torch.device("cpu")).bind()
-    assert rec.info().kernels == 14 - 2  # no h-row view (bf16), no successor qkv (tail)
+    rank = L.LayerRank(lib, None, case, 1, torch.device("cpu"))
+    assert rank.bind(fused=False).info().kernels == 14 - 2  # no h-row view (bf16), no successor qkv (tail)
+    assert rank.bind(fused=True).info().kernels == 7 - 1  # the fused form: no h-row view either
 
 
 def test_weight_images_round_trip_and_layout():

@@ -126,3 +126,60 @@ def test_non_finite_rows_are_routed_in_range_and_recorded(device):
     assert torch.equal(ids[keep], clean.ranks[0].o["ids"].cpu()[keep])
     st = rank.launch_record.status(torch.cuda.current_stream().cuda_stream)
     assert (st.code, st.stage, st.block) == (6, 6, 2)
+
+
+@pytest.mark.parametrize("name", ["small_fp4_swa_tp1_m5", "downscaled_m1"])
+def test_fused_layer_parity(name, device):
+    """The fused form (two persistent segment kernels around the expert kernels) through one mk_launch, stage by stage
+    against the oracle like the per-stage kernels."""
+    cfg, kw = CASES[name]
+    case = synthetic.layer_case(cfg, **kw)
+    world = L.LayerWorld(case, device)
+    rank = world.ranks[0]
+    rank.bind(world.ranks, fused=True)
+    assert rank.launch_record.info().kernels == 7
+    rank.launch(torch.cuda.current_stream().cuda_stream, pdl=True)
+    torch.cuda.synchronize()
+    assert rank.launch_record.status(torch.cuda.current_stream().cuda_stream).code == 0
+    check_world(world, [0])
+
+
+@pytest.mark.parametrize("name", ["small_fp4_swa_tp8", "small_bf16_tail_tp4", "small_fp4_global_tp8_baseline"])
+def test_fused_matches_per_stage_kernels_on_a_lone_rank(name, device):
+    """One rank of a larger world alone (its peers' contributions absent in both runs): the fused form and the per-stage
+    kernels give the same routing and the same values up to f32 summation order."""
+    cfg, kw = CASES[name]
+    case = synthetic.layer_case(cfg, **kw)
+    outs = []
+    for fused in (False, True):
+        rank = L.LayerRank(host_lib(), _module(device), case, 1, device)
+        rank.bind(None, fused=fused)
+        assert rank.launch_record.info().kernels == ((7 if not case.bf16 else 6) if fused else (14 if not case.tail else 12))
+        rank.launch(torch.cuda.current_stream().cuda_stream, pdl=True)
+        torch.cuda.synchronize()
+        assert rank.launch_record.status(torch.cuda.current_stream().cuda_stream).code == 0
+        outs.append({k: v.clone() for k, v in rank.values().items()})
+    a, b = outs
+    assert torch.equal(a["ids"], b["ids"])
+    for k in a:
+        if a[k].dtype in (torch.int32, torch.uint8):
+            continue
+        x, y = a[k].float(), b[k].float()
+        rel = ((x - y).norm() / y.norm().clamp_min(1e-20)).item()
+        assert rel < 2e-2, (k, rel)
+
+
+_MOD = {}
+
+
+def host_lib():
+    from sgl_muse_mega_b200.common import host
+
+    return host.library()
+
+
+def _module(device):
+    if device not in _MOD:
+        with torch.cuda.device(device):
+            _MOD[device] = host_lib().load()
+    return _MOD[device]
