@@ -66,7 +66,8 @@ class Stack:
     def __init__(self, case, rank: int, device, lib: Optional[host.Library] = None, module=None, *, arena=None,
                  kv_rows: Optional[int] = None, tensor_cores: bool = True, keep_plain_experts: bool = True,
                  greedy: bool = True, accept_override: Optional[torch.Tensor] = None, ring: int = 64,
-                 b_live: int = 0, wait_budget: int = 0, fused: bool = False):  # fmt: skip
+                 b_live: int = 0, wait_budget: int = 0, fused: bool = False, frame: Optional[dict] = None,
+                 pools: Optional[list] = None):  # fmt: skip
         """``case``: a ``synthetic.StackCase``; ``rank`` must be one of ``case.ranks``. ``arena``: the rank's exchange
         memory carved by ``exchange_layout`` (default: ordinary tensors, for a world inside one process). ``greedy``
         False ends the step with the soft cap (the logits go to ``self.logits_out``) instead of the accept."""
@@ -86,13 +87,19 @@ class Stack:
         self.arena = arena if arena is not None else symm.LocalArena(exchange_layout(cfg, M), device)
         self.view = ExchangeView(self.arena)
         # ---- the serving framework's side of the feeds: identity slots (position p lives in pool row p) ----
-        self.positions = torch.arange(case.ctx, case.ctx + M, dtype=i64, device=device)
-        self.out_cache_loc = self.positions.clone()
-        self.seq_lens = torch.tensor([case.ctx], dtype=i64, device=device)
-        self.req_pool_indices = torch.zeros(1, dtype=i64, device=device)
-        self.req_to_token = torch.arange(kv_rows, dtype=i32, device=device)[None].contiguous()
-        self.full_to_swa = torch.cat([torch.arange(kv_rows, dtype=i64), torch.tensor([-1])]).to(device)
-        self.swa_out_cache_loc = self.out_cache_loc.clone()
+        # (a serving framework hands its own batch tensors in through ``frame``; they are read on the device every step)
+        frame = dict(frame or {})
+        self.positions = frame.get("positions", torch.arange(case.ctx, case.ctx + M, dtype=i64, device=device))
+        self.out_cache_loc = frame.get("out_cache_loc", self.positions.clone())
+        self.seq_lens = frame.get("seq_lens", torch.tensor([case.ctx], dtype=i64, device=device))
+        self.req_pool_indices = frame.get("req_pool_indices", torch.zeros(1, dtype=i64, device=device))
+        self.req_to_token = frame.get("req_to_token")
+        if self.req_to_token is None:
+            self.req_to_token = torch.arange(kv_rows, dtype=i32, device=device)[None].contiguous()
+        self.full_to_swa = frame.get("full_to_swa")
+        if self.full_to_swa is None:
+            self.full_to_swa = torch.cat([torch.arange(kv_rows, dtype=i64), torch.tensor([-1])]).to(device)
+        self.swa_out_cache_loc = frame.get("swa_out_cache_loc", self.out_cache_loc.clone())
         self.cos_sin_cache = dev(case.cos_sin_cache)
         self.tokens = torch.zeros(M, dtype=i64, device=device)
         self.feeds = f = HT.WindowFeeds(
@@ -112,7 +119,11 @@ class Stack:
         self.greedy, self.accept_override, self.ring = greedy, accept_override, ring
         # ---- the KV pools: one pair per layer; context rows from the case ----
         n = len(case.layers)
-        self.pools = [tuple(torch.zeros(kv_rows, kvw, dtype=bf, device=device) for _ in range(2)) for _ in range(n)]
+        self.pools = pools
+        if self.pools is None:
+            self.pools = [tuple(torch.zeros(kv_rows, kvw, dtype=bf, device=device) for _ in range(2)) for _ in range(n)]
+        assert len(self.pools) == n and all(k.shape[1] == kvw for k, _ in self.pools), "one (K, V) pool pair per layer"
+        self.kv_rows = min(int(k.shape[0]) for k, _ in self.pools)
         # ---- the entry and layer 0's head (the peers' shards are wired in bind) ----
         self.residual0 = torch.zeros(M, cfg.hidden, dtype=torch.float32, device=device)
         self.normed0 = torch.zeros(M, cfg.hidden, dtype=bf, device=device)

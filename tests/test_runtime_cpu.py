@@ -1,0 +1,124 @@
+"""The SGLang-facing surface without a GPU: plugin registration and the spec's lookups (as the reference's
+test/unit/test_plugin.py), the refusal hooks, the tensors the build aliases, the expert reader's sharding and scale
+folding, and the executor's plan()."""
+
+from types import SimpleNamespace as NS
+
+import pytest
+import torch
+
+from fake_sglang import FakeCheckpoint, experts_of, fake_model
+from sgl_muse_mega_b200 import plugin, sglang_api
+from sgl_muse_mega_b200.muse_spark import spec as SP
+from sgl_muse_mega_b200.muse_spark.b200 import synthetic
+from sgl_muse_mega_b200.muse_spark.config import Config
+from sgl_muse_mega_b200.muse_spark.runtime import build as B
+from sgl_muse_mega_b200.muse_spark.runtime import executor as X
+from sgl_muse_mega_b200.muse_spark.runtime import shim
+
+
+def small_cfg(tp: int) -> Config:
+    return Config(hidden=1024, q_heads=64, kv_heads=8, experts=16, topk=8, moe_hidden=1024, moe_inter=1024, swa_window=7,
+                  vocab=4096, layers=3, bf16_moe_layers=(0,), tp=tp, node_ranks=min(4, tp))  # fmt: skip
+
+
+@pytest.fixture(scope="module")
+def case1():
+    return synthetic.stack_case(small_cfg(1), n_layers=3, rows=16, ctx=8, seed=2)
+
+
+def test_plugin_registers_the_spec_under_the_architecture():
+    plugin.register()
+    assert sglang_api.ENTRY_POINT == "nvidia_megakernel" and sglang_api.MEGAKERNEL_API_VERSION == 1
+    found, why = sglang_api.find_spec(architectures=["MuseSparkForConditionalGeneration"], isa="sm_100")
+    assert found is SP.SPEC and why is None
+    found, why = sglang_api.find_spec(architectures=["MuseSparkForConditionalGeneration"], isa="sm_103")
+    assert found is None and "sm_100" in why  # not this build's isa
+    found, why = sglang_api.find_spec(architectures=["LlamaForCausalLM"], isa="sm_100")
+    assert found is None and "no megakernel spec" in why
+    r = SP.SPEC.requires
+    assert r.isas == frozenset({"sm_100"}) and r.tp_sizes == frozenset({1, 2, 4, 8}) and r.resident_blocks == 148
+    assert SP.SPEC.max_rows == 16 and SP.SPEC.api_version == 1
+
+
+def test_alias_reasons_accept_the_model_and_name_what_is_wrong(case1):
+    cfg = case1.cfg
+    model = fake_model(case1)
+    assert B.alias_reasons(model, cfg, 0) == []
+    specs = B.alias_specs(model, cfg)
+    assert specs[(1, "cross_pre_w")][0] is model.model.language_model.layers[2].input_layernorm._frozen_weight
+    assert specs[(2, "cross_pre_w")][0] is model.model.language_model.norm._frozen_weight
+    assert (2, "next_qkv") not in specs and specs[(0, "next_qkv")][0] is model.model.language_model.layers[1].self_attn.qkv_proj.weight
+    # a wrong shape and a wrong dtype are named with their layer
+    lm = model.model.language_model
+    lm.layers[1].mlp.gate.weight = lm.layers[1].mlp.gate.weight.bfloat16()
+    lm.layers[2].self_attn.o_proj.weight = lm.layers[2].self_attn.o_proj.weight[:, :-64]
+    reasons = B.alias_reasons(model, cfg, 0)
+    assert any(r.startswith("layer 1 router is") and "bfloat16" in r for r in reasons)
+    assert any(r.startswith("layer 2 o_proj is") for r in reasons) and len(reasons) == 2
+    # a model without the expected modules is one reason, not an exception
+    del lm.layers[0].mlp.pre_expert_proj
+    assert B.alias_reasons(model, cfg, 0)[0].startswith("the loaded model lacks a tensor the kernels read")
+    # the full-size spec refuses this small model through the same hook
+    assert len(SP.model_disable_reasons(fake_model(case1), None)) > 10
+
+
+def test_vocab_shard_must_be_this_ranks_rows():
+    cfg = small_cfg(2)
+    case = synthetic.stack_case(cfg, n_layers=3, rows=16, ctx=8, seed=2, only_ranks=[1])
+    model = fake_model(case)
+    assert B.alias_reasons(model, cfg, 1) == []
+    assert any("shard starts at row" in r for r in B.alias_reasons(model, cfg, 0))
+
+
+def test_layer_experts_shards_the_checkpoint_and_folds_the_scales():
+    """A two-rank world's plain shards are stitched into checkpoint-shaped tensors [E, 2 I, ...] / [E, P, ...]; the reader
+    must hand each rank its own shard back, with g1_alphas = s2_gate, g1_scale_c = s2_up / s2_gate, g2_alphas = s2_down."""
+    cfg = small_cfg(2)
+    lc = synthetic.layer_case(cfg, rows=4, ctx=4, seed=9, layer=1, band="reference")
+    a, b = lc.ranks
+    p = "model.language_model.layers.1.mlp.experts."
+    cat = lambda x, y: torch.cat([x, y], 1)  # noqa: E731
+    s2 = torch.stack([a.g1_alphas, a.g1_alphas * a.g1_scale_c], 1)
+    ck = FakeCheckpoint({
+        p + "gate_up_proj": torch.cat([cat(a.gate_q, b.gate_q), cat(a.up_q, b.up_q)], 1),
+        p + "gate_up_proj_weight_scale": torch.cat([cat(a.gate_sf, b.gate_sf), cat(a.up_sf, b.up_sf)], 1),
+        p + "down_proj": cat(a.w2_q, b.w2_q),
+        p + "down_proj_weight_scale": cat(a.w2_sf, b.w2_sf),
+        p + "gate_up_proj_weight_scale_2": s2,
+        p + "down_proj_weight_scale_2": a.g2_alphas,
+    })  # fmt: skip
+    for rank, t in enumerate((a, b)):
+        got = B.layer_experts(ck, cfg, 1, rank, "cpu")
+        for k in ("gate_q", "gate_sf", "up_q", "up_sf", "w2_q", "w2_sf", "g1_alphas", "g2_alphas"):
+            assert torch.equal(got[k], getattr(t, k)), (rank, k)
+        assert torch.allclose(got["g1_scale_c"], t.g1_scale_c, rtol=1e-6)
+
+
+def test_model_case_aliases_the_models_tensors(case1):
+    cfg = case1.cfg
+    model = fake_model(case1)
+    mc = B.model_case(model, cfg, 0, "cpu", 16, experts_of(case1))
+    assert len(mc.layers) == 3 and mc.ctx == 0 and mc.ranks == [0]
+    l1 = mc.layers[1]
+    assert (l1.global_attn, l1.bf16, l1.tail, l1.next_global) == (True, False, False, False)
+    t = l1.ranks[0]
+    assert t.pooler.data_ptr() == model.model.language_model.layers[1].mlp.pre_expert_proj.weight.data_ptr()
+    assert t.next_qkv.data_ptr() == model.model.language_model.layers[2].self_attn.qkv_proj.weight.data_ptr()
+    assert torch.equal(t.gate_q, case1.layers[1].ranks[0].gate_q)
+    assert mc.layers[2].tail and mc.layers[2].ranks[0].next_qkv is None and mc.layers[0].bf16
+
+
+def test_plan_takes_only_the_batch_1_verify_step_of_one_block(case1):
+    v = X.Verify(case1.cfg, 16, case1, None, None, None, None, 0, "cpu", None, "test build")
+    assert v.widths == (16,) and v.summary() == "test build" and v.draft_sampler is None
+    fb = lambda mode, bs: shim.ForwardBatch(shim.ForwardMode(mode), bs, torch.tensor([40]), torch.tensor([0]), torch.arange(16))  # noqa: E731
+    ids = torch.zeros(16, dtype=torch.int64)
+    step = v.plan(ids, fb("target_verify", 1), view=NS())
+    assert step is not None and (step.mode, step.rows) == ("target_verify", 16)
+    assert v.plan(None, fb("target_verify", 1)) is None  # a forward without ids
+    assert v.plan(ids, fb("decode", 1)) is None
+    assert v.plan(ids, fb("target_verify", 2)) is None
+    assert v.plan(ids[:8], fb("target_verify", 1)) is None
+    with pytest.raises(RuntimeError, match="plan"):
+        v.forward(None, None, ids, None, fb("target_verify", 1))
