@@ -46,7 +46,7 @@ def parse():
     ap.add_argument("--fused", action="store_true", help="the dense stages as two persistent segment kernels")
     ap.add_argument("--decode-layers", type=int, default=62, help="layers of the whole-step leg (0: skip it)")
     ap.add_argument("--decode-steps", type=int, default=24)
-    ap.add_argument("--accept", type=int, default=6, help="forced accept length of the whole-step leg")
+    ap.add_argument("--accept", type=int, default=5, help="forced accept length of the whole-step leg (5 drafts + the bonus = 6 tokens a step)")
     return ap.parse_args()
 
 
@@ -451,6 +451,17 @@ def run_ours(args) -> None:
         e2e_us = float(t.item())
     clocks = sampler.stop() if sampler else None
 
+    seg_trace = None
+    if args.fused:
+        # stage timestamps CTA 0 of the two segment kernels left in the status block (ns of the global timer)
+        names_a = ["pdl_wait", "o_proj", "barrier", "ar_finish_signal", "post_norm_row", "barrier", "pooler_router", "barrier",
+                   "pool_finish_signal", "routing_nq"]  # fmt: skip
+        names_b = ["pdl_wait", "combine_row", "barrier", "unpooler", "barrier", "finish_cross_norm", "barrier", "qkv",
+                   "barrier", "qkv_rowops"]  # fmt: skip
+        t = ring[0].status.view(torch.int32)[64:192].view(torch.int64).cpu().tolist()
+        a, b = t[0:11], t[16:27]
+        seg_trace = {"segment_a": [[n, round((a[i + 1] - a[i]) / 1e3, 2)] for i, n in enumerate(names_a)],
+                     "segment_b": [[n, round((b[i + 1] - b[i]) / 1e3, 2)] for i, n in enumerate(names_b)]}  # fmt: skip
     dec = None
     if args.decode_layers > 0:
         del ring, lr
@@ -482,6 +493,7 @@ def run_ours(args) -> None:
             "gpu_launches": int(info.kernels) * args.steps,
             "stage_us_serialised": stage_us,
             "decode": dec,
+            "segment_trace_us": seg_trace,
             "clocks": clocks,
             "cpu_baseline": cpu,
         }  # fmt: skip

@@ -253,6 +253,127 @@ __global__ void __launch_bounds__(256) g2_kernel(const ExpertArgs a) {
     xchg_signal(a.sig_g2);
 }
 
+// ---- bf16 experts (the model's first and last layer) --------------------------------------------------------------------------
+// Weight streaming at M <= 16 rows per expert (1.3 rows on average): what matters is bytes in flight. These kernels keep
+// nothing in shared memory but the routed rows' addresses, so eight 256-thread CTAs fit an SM, and a lane requests four
+// 16-byte pieces of its weight row before it uses the first; the routed activation rows (<= 16 x 8 KB, shared by every CTA
+// of the expert) come through L1. One warp per weight row (g2) or per feature's gate and up rows (g1).
+template <int MAXT>
+__device__ __forceinline__ void bf16_row_dot_global(const bf16* __restrict__ w, int K, const bf16* const* xrow, int n_tok,
+                                                    float (&acc)[MAXT]) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int i = 0; i < MAXT; ++i) acc[i] = 0.f;
+    for (int k0 = lane * 8; k0 < K; k0 += 1024) {
+        uint4 c[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (k0 + u * 256 < K) c[u] = ldg_stream16(w + k0 + u * 256);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (k0 + u * 256 >= K) break;
+            const __nv_bfloat162* wp = (const __nv_bfloat162*)&c[u];
+            float wf[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(wp[i]);
+                wf[2 * i] = f.x;
+                wf[2 * i + 1] = f.y;
+            }
+            for (int tk = 0; tk < n_tok; ++tk) {
+                const uint4 xv = __ldg((const uint4*)(xrow[tk] + k0 + u * 256));
+                const __nv_bfloat162* xp = (const __nv_bfloat162*)&xv;
+                float a0 = 0.f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 x = __bfloat1622float2(xp[i]);
+                    a0 = fmaf(wf[2 * i], x.x, a0);
+                    a0 = fmaf(wf[2 * i + 1], x.y, a0);
+                }
+#pragma unroll
+                for (int i = 0; i < MAXT; ++i)
+                    if (i == tk) acc[i] += a0;
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < MAXT; ++i) acc[i] = warp_sum(acc[i]);
+}
+
+constexpr int kBf16Feat = 16;  // features (g1) or output rows (g2) per CTA: two per warp
+
+// g1, bf16: grid (I_s / 16, max_active). z[slot, rank I_s + f] = bf16(silu(bf16(gate . x)) bf16(up . x)) to every peer.
+__global__ void __launch_bounds__(256) g1_bf16_kernel(const ExpertArgs a) {
+    __shared__ const bf16* xrow[kMaxRows];
+    __shared__ int slots[kMaxRows];
+    griddep_wait();
+    const int ai = blockIdx.y;
+    if (ai >= a.rt->n_active) {
+        xchg_signal(a.sig_g1);
+        return;
+    }
+    const int e = a.rt->act_e[ai], s0 = a.rt->act_off[ai], n_tok = a.rt->act_off[ai + 1] - s0;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < n_tok) {
+        slots[tid] = a.rt->slot[s0 + tid];
+        xrow[tid] = (const bf16*)a.xq + (size_t)(slots[tid] / a.topk) * a.P;
+    }
+    __syncthreads();
+    for (int j = 0; j < kBf16Feat / 8; ++j) {
+        const int f = blockIdx.x * kBf16Feat + warp * (kBf16Feat / 8) + j;
+        float g[kMaxRows], u[kMaxRows];
+        bf16_row_dot_global<kMaxRows>((const bf16*)a.w1_gate + ((size_t)e * a.I_s + f) * a.P, a.P, xrow, n_tok, g);
+        bf16_row_dot_global<kMaxRows>((const bf16*)a.w1_up + ((size_t)e * a.I_s + f) * a.P, a.P, xrow, n_tok, u);
+        float gv = 0.f, uv = 0.f;
+#pragma unroll
+        for (int i = 0; i < kMaxRows; ++i)
+            if (i == lane) { gv = g[i]; uv = u[i]; }
+        if (lane < n_tok) {
+            gv = bf16_round(gv);
+            uv = bf16_round(uv);
+            const bf16 out = __float2bfloat16_rn((gv / (1.0f + expf(-gv))) * uv);
+            const size_t off = (size_t)slots[lane] * a.I + a.rank * a.I_s + f;
+            for (int p = 0; p < a.n_peer; ++p) ((bf16*)a.z_peer[p])[off] = out;
+        }
+    }
+    xchg_signal(a.sig_g1);
+}
+
+// g2, bf16: grid (H_s / 16, max_active). zb[slot, rank H_s + n] = bf16(w2[n] . z[slot]) to every peer.
+__global__ void __launch_bounds__(256) g2_bf16_kernel(const ExpertArgs a) {
+    __shared__ const bf16* xrow[kMaxRows];
+    __shared__ int slots[kMaxRows];
+    griddep_wait();
+    xchg_wait(a.wait_g2);
+    const int ai = blockIdx.y;
+    if (ai >= a.rt->n_active) {
+        xchg_signal(a.sig_g2);
+        return;
+    }
+    const int e = a.rt->act_e[ai], s0 = a.rt->act_off[ai], n_tok = a.rt->act_off[ai + 1] - s0;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < n_tok) {
+        slots[tid] = a.rt->slot[s0 + tid];
+        xrow[tid] = (const bf16*)a.z + (size_t)slots[tid] * a.I;
+    }
+    __syncthreads();
+    for (int j = 0; j < kBf16Feat / 8; ++j) {
+        const int n = blockIdx.x * kBf16Feat + warp * (kBf16Feat / 8) + j;
+        float acc[kMaxRows];
+        bf16_row_dot_global<kMaxRows>((const bf16*)a.w2 + ((size_t)e * a.H_s + n) * a.I, a.I, xrow, n_tok, acc);
+        float v = 0.f;
+#pragma unroll
+        for (int i = 0; i < kMaxRows; ++i)
+            if (i == lane) v = acc[i];
+        if (lane < n_tok) {
+            const bf16 b = __float2bfloat16_rn(v);
+            const size_t off = (size_t)slots[lane] * a.P + a.rank * a.H_s + n;
+            for (int p = 0; p < a.n_peer; ++p) a.zb_peer[p][off] = b;
+        }
+    }
+    xchg_signal(a.sig_g2);
+}
+
 size_t g1_smem(int P) { return 32 * 16 * sizeof(float) + (size_t)kMaxRows * P * 2; }
 size_t g2_smem(int I) { return 16 * 16 * sizeof(float) + (size_t)kMaxRows * I * 2; }
 
@@ -277,9 +398,11 @@ static cudaError_t launch_e(void (*kern)(const ExpertArgs), dim3 grid, size_t sm
 }
 
 cudaError_t g1_launch(const ExpertArgs& a, int max_active, cudaStream_t s, bool pdl) {
+    if (a.wbf16 && a.P % 8 == 0) return launch_e(g1_bf16_kernel, dim3(a.I_s / kBf16Feat, max_active), 0, s, pdl, a);
     return launch_e(g1_kernel, dim3(a.I_s / 16, max_active), g1_smem(a.P), s, pdl, a);
 }
 cudaError_t g2_launch(const ExpertArgs& a, int max_active, cudaStream_t s, bool pdl) {
+    if (a.wbf16 && a.I % 8 == 0) return launch_e(g2_bf16_kernel, dim3(a.H_s / kBf16Feat, max_active), 0, s, pdl, a);
     return launch_e(g2_kernel, dim3(a.H_s / 16, max_active), g2_smem(a.I), s, pdl, a);
 }
 
