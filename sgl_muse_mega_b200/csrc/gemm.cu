@@ -180,7 +180,17 @@ __global__ void __launch_bounds__(256) skinny_gemm_kernel(const GemmArgs a) {
         };
         if (a.mode == 0) {
             for (int n = lane; n < C::BN; n += 32)
-                if (nb * C::BN + n < a.N) gemm_store(a, m, nb * C::BN + n, total(n));
+                if (nb * C::BN + n < a.N) {
+                    const float v = total(n);
+                    gemm_store(a, m, nb * C::BN + n, v);
+                    if (a.score != nullptr) {
+                        // the router's selection score, here because this epilogue has a thread per logit while the
+                        // routing kernel has one warp per row: sigmoid in f64 rounded to f32, plus the expert's bias
+                        const int e = nb * C::BN + n;
+                        const float s = (float)(1.0 / (1.0 + exp(-((double)v * a.score_mult))));
+                        a.score[(size_t)m * a.N + e] = s + a.score_bias[e];
+                    }
+                }
         } else {
             // one head: lane owns the pair (2 lane, 2 lane + 1)
             const int head = nb;

@@ -132,6 +132,10 @@ struct GemmArgs {
     int qh, kvh, kv_row_bytes;
     int* status;          // the launch's status block (a bulk copy that never lands records itself); may be null
     XchgSignal sig;       // the exchange this GEMM's peer stores feed (off when n == 0)
+    // the router only: score[m, n] = f32(sigmoid_f64(out[m, n] x score_mult)) + score_bias[n], the routing's selection scores
+    float* score;
+    const float* score_bias;
+    double score_mult;
 };
 
 }  // namespace mk

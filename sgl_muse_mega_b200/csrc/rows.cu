@@ -108,17 +108,26 @@ __global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
 // sf = e4m3(max(gamax, 1e-10) / 6 / x_scale), code = e2m1(n / max(sf x_scale, 1e-10))          (muse_spark.py:407-435)
 constexpr int kTopkPer = 32;  // E <= 1024
 
-static __device__ void topk_row(const TopkArgs& a, int row, int lane, int* s_ids) {
-    float sel[kTopkPer];
+// PER = experts per lane (E <= 32 PER). The k selection rounds run on registers and shuffles only: a lane keeps its experts'
+// scores and biases, proposes its best, and the butterfly carries (score, id, bias) of the winner to every lane.
+template <int PER>
+static __device__ void topk_row_t(const TopkArgs& a, int row, int lane, int* s_ids) {
+    float sel[PER], bs[PER];
     bool bad = false;
 #pragma unroll
-    for (int i = 0; i < kTopkPer; ++i) {
+    for (int i = 0; i < PER; ++i) {
         const int e = lane + 32 * i;
         sel[i] = -INFINITY;
+        bs[i] = 0.f;
         if (e < a.E) {
-            const double z = (double)a.logits[(size_t)row * a.E + e] * a.mult;
-            const float s = (float)(1.0 / (1.0 + exp(-z)));
-            sel[i] = s + a.bias[e];
+            bs[i] = a.bias[e];
+            if (a.score != nullptr) {  // computed by the router GEMM's epilogue (one thread per logit)
+                sel[i] = a.score[(size_t)row * a.E + e];
+            } else {
+                const double z = (double)a.logits[(size_t)row * a.E + e] * a.mult;
+                const float s = (float)(1.0 / (1.0 + exp(-z)));
+                sel[i] = s + bs[i];
+            }
             // a NaN score (non-finite hidden rows upstream) must still leave k distinct, in-range experts: it ranks
             // below every number, the lower id first; the status block records that the row was not routable
             if (!(sel[i] == sel[i])) {
@@ -135,25 +144,26 @@ static __device__ void topk_row(const TopkArgs& a, int row, int lane, int* s_ids
     float total = 0.f, mine = 0.f;
     int myid = 0;
     for (int j = 0; j < a.k; ++j) {
-        float bv = -INFINITY;
+        float bv = -INFINITY, bb = 0.f;
         int bi = 0x7fffffff;
 #pragma unroll
-        for (int i = 0; i < kTopkPer; ++i) {
+        for (int i = 0; i < PER; ++i) {
             const int e = lane + 32 * i;
-            if (sel[i] > bv) { bv = sel[i]; bi = e; }  // ascending ids per lane: strict > keeps the smaller id
+            if (sel[i] > bv) { bv = sel[i]; bi = e; bb = bs[i]; }  // ascending ids per lane: strict > keeps the smaller id
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            const float ob = __shfl_xor_sync(0xffffffffu, bb, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; bb = ob; }
         }
-        const float sv = bv - a.bias[bi];
+        const float sv = bv - bb;
         total += sv;
         if (lane == j) { mine = sv; myid = bi; }
         if ((bi & 31) == lane) {
 #pragma unroll
-            for (int i = 0; i < kTopkPer; ++i)
+            for (int i = 0; i < PER; ++i)
                 if (i == (bi >> 5)) sel[i] = -INFINITY;
         }
     }
@@ -163,6 +173,12 @@ static __device__ void topk_row(const TopkArgs& a, int row, int lane, int* s_ids
         a.w[(size_t)row * a.k + lane] = (mine * inv) * a.route_scale;
         s_ids[row * a.k + lane] = myid;
     }
+}
+
+static __device__ void topk_row(const TopkArgs& a, int row, int lane, int* s_ids) {
+    if (a.E <= 256) topk_row_t<8>(a, row, lane, s_ids);
+    else if (a.E <= 512) topk_row_t<16>(a, row, lane, s_ids);
+    else topk_row_t<kTopkPer>(a, row, lane, s_ids);
 }
 
 static __device__ void route_tables(const int* s_ids, int E, int S, RouteTables* rt, int* cnt, int* first) {

@@ -367,6 +367,11 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     L->router.n_out = 1;
     L->router.ldo = E;
     L->router.out_f32 = 1;
+    // the routing's selection scores come out of this GEMM's epilogue (a thread per logit); they live at the start of the
+    // partial-sum scratch, which the per-stage kernels do not use otherwise
+    L->router.score = gpart;
+    L->router.score_bias = (const float*)b->expert_bias;
+    L->router.score_mult = b->router_mult;
     // unpooler: node block of [H, P]
     if (gemm(L->unpool, 0, false, b->w_up + (uint64_t)jnode * (H / nr) * P * 2, b->y, H / nr, P, P)) return -1;
     L->unpool.n_out = peers(b->unpool_ag_peer, b->unpool_ag, L->unpool.out, node0, nr);
@@ -400,7 +405,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     wait_for(L->post_norm.wait, XP_AR, 0, all, ST_POST_NORM);
     wait_for(L->cross_norm.wait, XP_UNPOOL, node0, nr, ST_CROSS_NORM);
     L->topk = TopkArgs{(const float*)b->logits, (const float*)b->expert_bias, (int*)b->topk_idx32, (float*)b->topk_w,
-                       b->router_mult, (float)b->route_scale, E, K, M, (int*)b->status};
+                       b->router_mult, (float)b->route_scale, E, K, M, (int*)b->status, gpart};
     L->nq = NqArgs{(const bf16*)b->pool_ag, (const bf16*)b->gamma, (unsigned char*)b->q, (unsigned char*)b->sf,
                    (float*)b->x_scale, (float)b->eps, P, (int)s.bf16};
     L->combine = CombineArgs{(const bf16*)b->zb, (const float*)b->topk_w, (const bf16*)b->gamma_p1, (bf16*)b->y, P, K, b_live};
@@ -508,6 +513,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
         A.sig_pool = L->pooler.sig;
         A.logits = (float*)b->logits;
         A.topk = L->topk;
+        A.topk.score = nullptr;  // the segment's routing stage computes the scores itself
         A.nq = L->nq;
         A.rt = L->rt;
         A.b_live = b_live;

@@ -39,6 +39,7 @@ struct TopkArgs {
     float route_scale;
     int E, k, M;
     int* status;  // a row with NaN scores is recorded here (code 6); may be null
+    const float* score;  // [M, E] selection scores from the router GEMM's epilogue, or null: computed here from the logits
 };
 struct NqArgs {
     const bf16* pooled;
