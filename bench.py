@@ -43,7 +43,8 @@ def parse():
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--cpu-sample-experts", type=int, default=24)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--fused", action="store_true", help="the dense stages as two persistent segment kernels")
+    ap.add_argument("--form", type=int, default=0, choices=(0, 1, 2),
+                    help="dense stages: 0 item-engine GEMM kernels, 1 two persistent segment kernels, 2 cluster split-K GEMMs")
     ap.add_argument("--decode-layers", type=int, default=62, help="layers of the whole-step leg (0: skip it)")
     ap.add_argument("--decode-steps", type=int, default=24)
     ap.add_argument("--accept", type=int, default=5, help="forced accept length of the whole-step leg (5 drafts + the bonus = 6 tokens a step)")
@@ -341,7 +342,7 @@ def run_ours(args) -> None:
         lr.z_sf.copy_(torch.randint(0x30, 0x40, lr.z_sf.shape, generator=g, device=device, dtype=torch.uint8))
         lr.z_ex.copy_(torch.randint(0, 3, lr.z_ex.shape, generator=g, device=device, dtype=torch.uint8))
         lr.zb.view(torch.bfloat16).copy_(torch.randn(lr.zb.numel() // 2, generator=g, device=device))
-        lr.bind(None, fused=args.fused)
+        lr.bind(None, fused=args.form)
         case.ranks = []  # the device copies live in lr.w
         ring.append(lr)
     torch.cuda.synchronize()
@@ -452,7 +453,7 @@ def run_ours(args) -> None:
     clocks = sampler.stop() if sampler else None
 
     seg_trace = None
-    if args.fused:
+    if args.form == 1:
         # stage timestamps CTA 0 of the two segment kernels left in the status block (ns of the global timer)
         names_a = ["pdl_wait", "o_proj", "barrier", "ar_finish_signal", "post_norm_row", "barrier", "pooler_router", "barrier",
                    "pool_finish_signal", "routing_nq"]  # fmt: skip

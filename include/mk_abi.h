@@ -36,7 +36,8 @@ int mk_module_load(const void* image, uint64_t bytes, const char* code_prefetch_
 void mk_module_free(MkModule* module);
 
 // replaces abi.h:40 mk_launch. Enqueues every kernel of the bound launch on `stream` (a cudaStream_t as an integer);
-// pdl != 0 adds the programmatic-dependent-launch attribute to each kernel after the first.
+// pdl != 0 adds the programmatic-dependent-launch attribute to every kernel, the first included (it then overlaps
+// its prologue with the tail of whatever kernel precedes it on the stream, e.g. the previous layer's last kernel).
 int mk_launch(const MkLaunch* launch, uint64_t stream, int pdl);
 // Test hook with no counterpart in the reference: enqueues stages [first, first + count) only. Lets a test interleave
 // the stages of several ranks' launches on one GPU, so that their exchanges run without the ranks waiting on each other.
@@ -204,11 +205,17 @@ typedef struct MkLayerBind {
     uint64_t status;        // status_bytes, zeroed once by the caller
     int64_t b_live;         // live window rows (abi.h:208-210)
     int64_t wait_budget;    // polls before an exchange wait gives up (0: library default)
-    // 1: mk_launch runs the dense stages (o_proj .. routing, combine .. successor's qkv head) as two persistent kernels of one
-    // CTA per SM with grid barriers between their stages, 7 kernels a layer instead of 14. Their exchange waits poll for
-    // peers that run at the same time: for a lone rank or one process per GPU, never for several ranks launched one after
-    // the other on one GPU. mk_launch_step always runs the per-stage kernels. Shapes the fused form does not tile keep the
-    // per-stage kernels (mk_launch_info.kernels tells which form was bound).
+    // Form of the dense stages (o_proj, pooler, router, unpooler, successor's qkv head), for shapes whose K dimensions are
+    // multiples of 512 (others always get form 2):
+    //   0  one launch per stage, the GEMMs on a persistent item engine (one 512-thread CTA per SM streams 64-row x 512-k
+    //      items through two buffers, partial sums per K chunk, one grid barrier, then the epilogue); pooler and router share
+    //      a launch: 13 kernels a layer;
+    //   1  mk_launch runs o_proj .. routing and combine .. qkv head as two persistent kernels with grid barriers between their
+    //      stages: 7 kernels a layer. Their exchange waits poll for peers that run at the same time: for a lone rank or one
+    //      process per GPU, never for several ranks launched one after the other on one GPU; mk_launch_step still runs
+    //      form 0;
+    //   2  one launch per stage with the cluster split-K GEMMs: 14 kernels a layer.
+    // mk_launch_info.kernels tells which form was bound.
     int64_t fused;
 } MkLayerBind;
 int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind* bind, MkLaunch** out);

@@ -73,6 +73,8 @@ struct MkLaunch {
     bool stage_on[ST_COUNT];
     mk::XchgWait hrow_wait;
     bool use_segments;  // mk_launch runs the dense stages as the two persistent segment kernels
+    bool seg_gemms;     // the per-stage list runs its GEMMs on the item engine (pooler + router in one launch)
+    mk::SegGemmArgs sg_oproj, sg_pool, sg_unpool, sg_qkv;
     mk::SegAArgs seg_a;
     mk::SegBArgs seg_b;
     // stand-alone launches around the layers (feeds, entry, lm_head, soft cap, accept): n_ops > 0 replaces the stage list
@@ -367,9 +369,10 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     L->router.n_out = 1;
     L->router.ldo = E;
     L->router.out_f32 = 1;
-    // the routing's selection scores come out of this GEMM's epilogue (a thread per logit); they live at the start of the
-    // partial-sum scratch, which the per-stage kernels do not use otherwise
-    L->router.score = gpart;
+    // the routing's selection scores come out of this GEMM's epilogue (a thread per logit); they live in the last
+    // 16 x 1024 floats of the partial-sum scratch (the partial sums never reach that far: checked with the GEMM tiling)
+    float* const scores = gpart + (size_t)256 * nmax - 16 * 1024;
+    L->router.score = scores;
     L->router.score_bias = (const float*)b->expert_bias;
     L->router.score_mult = b->router_mult;
     // unpooler: node block of [H, P]
@@ -405,7 +408,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     wait_for(L->post_norm.wait, XP_AR, 0, all, ST_POST_NORM);
     wait_for(L->cross_norm.wait, XP_UNPOOL, node0, nr, ST_CROSS_NORM);
     L->topk = TopkArgs{(const float*)b->logits, (const float*)b->expert_bias, (int*)b->topk_idx32, (float*)b->topk_w,
-                       b->router_mult, (float)b->route_scale, E, K, M, (int*)b->status, gpart};
+                       b->router_mult, (float)b->route_scale, E, K, M, (int*)b->status, scores};
     L->nq = NqArgs{(const bf16*)b->pool_ag, (const bf16*)b->gamma, (unsigned char*)b->q, (unsigned char*)b->sf,
                    (float*)b->x_scale, (float)b->eps, P, (int)s.bf16};
     L->combine = CombineArgs{(const bf16*)b->zb, (const float*)b->topk_w, (const bf16*)b->gamma_p1, (bf16*)b->y, P, K, b_live};
@@ -482,25 +485,62 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     // poll for peers that run at the same time, so it serves a lone rank or one process per GPU; a world emulated on one
     // GPU steps the per-stage kernels (mk_launch_step) instead. Shapes outside its tiling keep the per-stage kernels.
     L->use_segments = false;
+    L->seg_gemms = false;
+    const size_t part_cap = (size_t)256 * nmax - 16 * 1024;  // floats of partial-sum scratch below the routing scores
     const bool seg_shapes = (qh * kHeadDim) % 512 == 0 && H % 512 == 0 && P % 512 == 0 && H <= 8192 && P <= 4096 &&
-                            (size_t)(P / nr + E) <= (size_t)nmax;
-    if (b->fused && seg_shapes) {
-        L->use_segments = true;
-        auto seg_gemm = [&](SegGemm& g, const GemmArgs& src, bool f32, float* part) {
-            const int es = f32 ? 4 : 2;
-            g.w = (const unsigned char*)src.w;
-            g.x = (const unsigned char*)src.x;
-            g.ldw = (long long)src.ldw * es;
-            g.ldx = (long long)src.ldx * es;
-            g.N = src.N; g.K = src.K; g.M = src.M; g.f32 = f32 ? 1 : 0;
-            g.part = part;
+                            (size_t)(H / 512) * 16 * (P / nr + E) <= part_cap &&
+                            (size_t)(qh * kHeadDim / 512) * 16 * H <= part_cap && (size_t)(P / 512) * 16 * (H / nr) <= part_cap &&
+                            (size_t)(H / 512) * 16 * c.qkv_row <= part_cap;
+    auto seg_gemm = [&](SegGemm& g, const GemmArgs& src, bool f32, float* part) {
+        const int es = f32 ? 4 : 2;
+        g.w = (const unsigned char*)src.w;
+        g.x = (const unsigned char*)src.x;
+        g.ldw = (long long)src.ldw * es;
+        g.ldx = (long long)src.ldx * es;
+        g.N = src.N; g.K = src.K; g.M = src.M; g.f32 = f32 ? 1 : 0;
+        g.part = part;
+    };
+    // fused 0 (default): the per-stage launch list with its GEMMs on the item engine of segments.cuh where the shapes tile
+    // (pooler and router share a launch); fused 2: the cluster split-K GEMMs of gemm.cu everywhere; fused 1: two segments
+    if (b->fused != 2 && seg_shapes) {
+        L->seg_gemms = true;
+        const GridBarrier gb{(unsigned long long*)gcnt, budget, L->status};
+        auto stage = [&](SegGemmArgs& g, const GemmArgs& src, int finish) {
+            memset(&g, 0, sizeof g);
+            seg_gemm(g.g[0], src, false, gpart);
+            g.n_gemm = 1;
+            g.finish = finish;
+            for (int i = 0; i < src.n_out; ++i) g.out[i] = (bf16*)src.out[i];
+            g.n_out = src.n_out;
+            g.ldo = src.ldo;
+            g.off0 = src.col0;
+            g.sig = src.sig;
+            g.gb = gb;
+            g.status = L->status;
         };
+        stage(L->sg_oproj, L->oproj, 0);
+        stage(L->sg_pool, L->pooler, 1);
+        seg_gemm(L->sg_pool.g[1], L->router, true, gpart + (size_t)(H / 512) * 16 * (P / nr));
+        L->sg_pool.n_gemm = 2;
+        L->sg_pool.f32_out = (float*)b->logits;
+        L->sg_pool.score = scores;
+        L->sg_pool.score_bias = (const float*)b->expert_bias;
+        L->sg_pool.score_mult = b->router_mult;
+        stage(L->sg_unpool, L->unpool, 0);
+        if (!tail) {
+            stage(L->sg_qkv, L->qkv, 2);
+            L->sg_qkv.epi = L->qkv;
+        }
+        L->stage_on[ST_ROUTER] = false;  // rides the pooler's launch
+    }
+    if (b->fused == 1 && seg_shapes) {
+        L->use_segments = true;
         const GridBarrier gb{(unsigned long long*)gcnt, budget, L->status};
         SegAArgs& A = L->seg_a;
         memset(&A, 0, sizeof A);
         seg_gemm(A.oproj, L->oproj, false, gpart);
         seg_gemm(A.pooler, L->pooler, false, gpart);
-        seg_gemm(A.router, L->router, true, gpart + (size_t)16 * 16 * (P / nr));
+        seg_gemm(A.router, L->router, true, gpart + (size_t)(H / 512) * 16 * (P / nr));
         for (int i = 0; i < L->oproj.n_out; ++i) A.ar_out[i] = (bf16*)L->oproj.out[i];
         A.n_ar = L->oproj.n_out;
         A.ar_off = 0;  // the destinations already point at this rank's slot
@@ -549,9 +589,9 @@ static int run_stage(const MkLaunch* L, int st, cudaStream_t s, bool pdl) {
     switch (st) {
         case ST_ATTN_SPLIT: e = attn_split_launch(L->attn, s, pdl); break;
         case ST_ATTN_COMBINE: e = attn_combine_launch(L->attn, s, pdl); break;
-        case ST_OPROJ: e = gemm_launch(L->oproj, false, s, pdl); break;
+        case ST_OPROJ: e = L->seg_gemms ? seg_gemm_launch(L->sg_oproj, L->sms, s, pdl) : gemm_launch(L->oproj, false, s, pdl); break;
         case ST_POST_NORM: e = resid_norm_launch(L->post_norm, s, pdl); break;
-        case ST_POOLER: e = gemm_launch(L->pooler, false, s, pdl); break;
+        case ST_POOLER: e = L->seg_gemms ? seg_gemm_launch(L->sg_pool, L->sms, s, pdl) : gemm_launch(L->pooler, false, s, pdl); break;
         case ST_ROUTER: e = gemm_launch(L->router, true, s, pdl); break;
         case ST_TOPK:  // top-k, route tables and the pre-expert norm + quantisation share one launch
             e = route_nq_launch(L->topk, L->nq, L->rt, L->combine.b_live, s, pdl);
@@ -570,10 +610,12 @@ static int run_stage(const MkLaunch* L, int st, cudaStream_t s, bool pdl) {
             e = L->use_umma ? experts_umma_launch(L->umma_g2, true, L->sms, s, pdl) : g2_launch(L->ex, L->max_active, s, pdl);
             break;
         case ST_COMBINE: e = combine_launch(L->combine, (int)L->shape.rows, s, pdl); break;
-        case ST_UNPOOL: e = gemm_launch(L->unpool, false, s, pdl); break;
+        case ST_UNPOOL: e = L->seg_gemms ? seg_gemm_launch(L->sg_unpool, L->sms, s, pdl) : gemm_launch(L->unpool, false, s, pdl); break;
         case ST_CROSS_NORM: e = resid_norm_launch(L->cross_norm, s, pdl); break;
         case ST_QKV:
-            e = L->is_head ? gemm_gws_launch(L->head_gemm, false, L->head_ks, s, pdl) : gemm_launch(L->qkv, false, s, pdl);
+            e = L->is_head     ? gemm_gws_launch(L->head_gemm, false, L->head_ks, s, pdl)
+                : L->seg_gemms ? seg_gemm_launch(L->sg_qkv, L->sms, s, pdl)
+                               : gemm_launch(L->qkv, false, s, pdl);
             break;
         case ST_ROWOPS: e = rowops_launch(L->rowops, s, pdl); break;
         default: return fail("stage %d does not exist", st);
@@ -617,7 +659,7 @@ int mk_launch(const MkLaunch* launch, uint64_t stream, int pdl) {
         const MkLaunch* L = launch;
         cudaStream_t s = (cudaStream_t)stream;
         const bool p = pdl != 0;
-        if (run_stage(L, ST_ATTN_SPLIT, s, false) || run_stage(L, ST_ATTN_COMBINE, s, p)) return -1;
+        if (run_stage(L, ST_ATTN_SPLIT, s, p) || run_stage(L, ST_ATTN_COMBINE, s, p)) return -1;
         cudaError_t e = seg_a_launch(L->seg_a, L->sms, s, p);
         if (e != cudaSuccess) return fail("segment A launch: %s", cudaGetErrorString(e));
         if (run_stage(L, ST_G1, s, p) || run_stage(L, ST_HROW, s, p) || run_stage(L, ST_G2, s, p)) return -1;
@@ -626,7 +668,7 @@ int mk_launch(const MkLaunch* launch, uint64_t stream, int pdl) {
         return 0;
     }
     for (int st = 0; st < ST_COUNT; ++st)
-        if (run_stage(launch, st, (cudaStream_t)stream, pdl != 0 && st > 0)) return -1;
+        if (run_stage(launch, st, (cudaStream_t)stream, pdl != 0)) return -1;
     return 0;
 }
 

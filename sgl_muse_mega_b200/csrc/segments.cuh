@@ -472,6 +472,41 @@ __device__ __forceinline__ void seg_setup(SegPipe& p, SegShared& sh, unsigned ch
     __syncthreads();
 }
 
+// ---- one GEMM stage as a kernel of its own --------------------------------------------------------------------------------------
+// The same item engine behind one grid barrier and a finish, for the per-stage launch list: o_proj (bf16 push into the
+// all-reduce workspaces), pooler + router in one launch (bf16 push into the node's gather rows; f32 logits and the routing's
+// selection scores), unpooler (bf16 push), qkv (row ops). The row kernels around them stay separate launches.
+__global__ void __launch_bounds__(kSegThreads, 1) seg_gemm_kernel(const SegGemmArgs a) {
+    extern __shared__ __align__(128) unsigned char dyn[];
+    __shared__ SegShared sh;
+    SegPipe p;
+    seg_setup(p, sh, dyn, a.status);
+    SegStage st{{a.g[0], a.g[a.n_gemm > 1 ? 1 : 0]}, seg_items(a.g[0]), seg_items(a.g[0]) + (a.n_gemm > 1 ? seg_items(a.g[1]) : 0)};
+    seg_stage_prefetch_w(st, p);  // static weights: requested while the predecessor still runs
+    griddep_wait();
+    seg_stage_run(st, p);
+    grid_barrier(a.gb, 30 + a.finish);
+    if (a.finish == 2) {
+        seg_finish_qkv(a.g[0], a.epi);
+    } else {
+        seg_finish_bf16(a.g[0], a.out, a.n_out, a.ldo, a.off0);
+        if (a.finish == 1) {
+            // the router: f32 logits and, a thread per logit, the routing's selection scores (sigmoid in f64 rounded to
+            // f32, plus the expert's bias)
+            const SegGemm& g = a.g[1];
+            const int nsplit = g.K / kChunkK;
+            for (int i = blockIdx.x * kSegThreads + threadIdx.x; i < g.M * g.N; i += gridDim.x * kSegThreads) {
+                const int m = i / g.N, n = i - m * g.N;
+                float v = 0.f;
+                for (int ks = 0; ks < nsplit; ++ks) v += g.part[((size_t)ks * 16 + m) * g.N + n];
+                a.f32_out[i] = v;
+                if (a.score != nullptr) a.score[i] = (float)(1.0 / (1.0 + exp(-((double)v * a.score_mult)))) + a.score_bias[n];
+            }
+        }
+    }
+    xchg_signal(a.sig);
+}
+
 // ---- segment A -----------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kSegThreads, 1) segment_a_kernel(const SegAArgs a) {
     extern __shared__ __align__(128) unsigned char dyn[];
@@ -576,7 +611,9 @@ size_t segments_smem() { return kSegSmem; }
 cudaError_t segments_prepare() {
     cudaError_t e = cudaFuncSetAttribute(segment_a_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSegSmem);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(segment_b_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSegSmem);
+    e = cudaFuncSetAttribute(segment_b_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSegSmem);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(seg_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSegSmem);
 }
 
 template <typename Args>
@@ -593,6 +630,7 @@ static cudaError_t seg_launch(void (*kern)(const Args), const Args& a, int grid,
     cfg.numAttrs = pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, a);
 }
+cudaError_t seg_gemm_launch(const SegGemmArgs& a, int grid, cudaStream_t s, bool pdl) { return seg_launch(seg_gemm_kernel, a, grid, s, pdl); }
 cudaError_t seg_a_launch(const SegAArgs& a, int grid, cudaStream_t s, bool pdl) { return seg_launch(segment_a_kernel, a, grid, s, pdl); }
 cudaError_t seg_b_launch(const SegBArgs& a, int grid, cudaStream_t s, bool pdl) { return seg_launch(segment_b_kernel, a, grid, s, pdl); }
 

@@ -276,6 +276,23 @@ struct SegBArgs {  // combine .. successor's qkv head
     GridBarrier gb;
     int* status;
 };
+struct SegGemmArgs {  // one GEMM stage (or pooler + router) as a kernel of its own
+    SegGemm g[2];
+    int n_gemm;
+    int finish;                 // 0: bf16 push of g[0]; 1: the same plus f32 logits and routing scores of g[1]; 2: qkv row ops
+    bf16* out[kMaxRanks];
+    int n_out;
+    long long ldo, off0;
+    XchgSignal sig;
+    float* f32_out;
+    float* score;
+    const float* score_bias;
+    double score_mult;
+    GemmArgs epi;               // finish 2: the qkv head's epilogue operands
+    GridBarrier gb;
+    int* status;
+};
+cudaError_t seg_gemm_launch(const SegGemmArgs& a, int grid, cudaStream_t s, bool pdl);
 size_t segments_smem();
 cudaError_t segments_prepare();
 cudaError_t seg_a_launch(const SegAArgs& a, int grid, cudaStream_t s, bool pdl);

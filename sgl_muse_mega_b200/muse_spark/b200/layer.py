@@ -144,11 +144,11 @@ class LayerRank:
         """Binds the launch; ``peers`` = per rank an object whose attributes ``ar``, ``pool_ag``, ``unpool_ag``, ``z``,
         ``z_sf``, ``z_ex``, ``zb``, ``flags`` are that rank's exchange buffers (tensors, or device addresses of buffers
         mapped from another process): every rank's ``LayerRank`` (own included), or None for a lone rank.
-        ``fused``: ``launch`` runs the dense stages as the two persistent segment kernels (7 kernels a layer instead of
-        14). Off by default: measured on the full shape the fused form is the slower one (its grid barriers and row stages
-        cost more than the launches they save; the stage trace is in the profiling notes). Never for peers that are
-        launched one after the other on one GPU: its exchange waits poll for ranks that run at the same time."""
-        fused = bool(fused)
+        ``fused``: the form of the dense stages (``MkLayerBind.fused``): 0 / False / None = one launch per stage with
+        the GEMMs on the persistent item engine (13 kernels a layer), 1 / True = two persistent segment kernels (7 kernels;
+        measured slower on the full shape, and never for peers launched one after the other on one GPU: its exchange
+        waits poll for ranks that run at the same time), 2 = one launch per stage with the cluster split-K GEMMs (14)."""
+        fused = int(fused or 0)
         cfg, case, w, o = self.case.cfg, self.case, self.w, self.o
         n = cfg.tp
 
@@ -178,7 +178,7 @@ class LayerRank:
             c_post_w=w["cross_post_w"], c_stream_out=o["stream_out"], h3q=o["h3_next"], w_qkv=w["next_qkv"],
             qkv_out=o["qkv_next"], cos_sin=w["next_cos_sin"], cache_loc=self.cache_loc, next_k_cache=self.next_k,
             next_v_cache=self.next_v, next_kv_rows=self.next_kv_rows, q_scale=cfg.q_scale, qkv_eps=cfg.rms_eps,
-            flags=self.flags, flags_peer=peer("flags"), ws=self.ws, status=self.status, b_live=b_live, wait_budget=wait_budget, fused=int(bool(fused)),
+            flags=self.flags, flags_peer=peer("flags"), ws=self.ws, status=self.status, b_live=b_live, wait_budget=wait_budget, fused=fused,
         )  # fmt: skip
         self.launch_record = self.lib.layer_bind(self.module, self.shape, bind)
         return self.launch_record

@@ -72,11 +72,12 @@ def test_pack_only_bind_and_refusals(lib):
     cfg, kw = CASES["small_fp4_swa_tp2"]
     case = synthetic.layer_case(cfg, **kw)
     rank = L.LayerRank(lib, None, case, 0, torch.device("cpu"))
-    rec = rank.bind(fused=False)
+    rec = rank.bind(fused=2)
     info = rec.info()
     assert info.kernels == 14 and info.grid > 0 and info.smem > 0  # 17 stage slots; top-k + tables + nq share a launch, the row ops ride the qkv GEMM
     # the fused form on request: attention x 2, segment A, g1, h row, g2, segment B
-    assert rank.bind().info().kernels == 14 and rank.bind(fused=True).info().kernels == 7
+    # default: the GEMMs on the item engine, pooler + router in one launch
+    assert rank.bind().info().kernels == 13 and rank.bind(fused=1).info().kernels == 7
     with pytest.raises(RuntimeError, match="pack-only"):
         rec(0, False)
     # a missing operand is named
@@ -95,8 +96,9 @@ def test_tail_and_bf16_variants_drop_stages(lib):
     cfg, kw = CASES["small_bf16_tail_tp4"]
     case = synthetic.layer_case(cfg, **kw)
     rank = L.LayerRank(lib, None, case, 1, torch.device("cpu"))
-    assert rank.bind(fused=False).info().kernels == 14 - 2  # no h-row view (bf16), no successor qkv (tail)
-    assert rank.bind(fused=True).info().kernels == 7 - 1  # the fused form: no h-row view either
+    assert rank.bind(fused=2).info().kernels == 14 - 2  # no h-row view (bf16), no successor qkv (tail)
+    assert rank.bind(fused=0).info().kernels == 13 - 2
+    assert rank.bind(fused=1).info().kernels == 7 - 1  # the fused form: no h-row view either
 
 
 def test_weight_images_round_trip_and_layout():
