@@ -51,6 +51,13 @@ def parse():
     return ap.parse_args()
 
 
+# DRAM traffic of the g1 expert kernel from its ncu capture (profiles/experts_umma_kernel_config1_full.md): 238.46 MB read +
+# 3.87 MB written for 238.3 MB of algorithmic bytes; it grows with the routed experts like the algorithmic bytes, so the
+# bench scales it by them.
+G1_TRAFFIC_RATIO = (238.46 + 3.87) / 238.3
+G1_TRAFFIC_NOTE = "dram read + write per launch: ncu capture at ring 2 scaled by the algorithmic bytes of this run"
+
+
 def peaks() -> tuple[float, str]:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -488,7 +495,8 @@ def run_ours(args) -> None:
             "layer_roofline": {"bound": "hbm", "achieved": layer_gbs, "peak": peak, "unit": "GB/s", "frac": layer_gbs / peak,
                                "bytes_per_layer": int(total_bytes / args.steps), "peak_kind": peak_kind},
             "roofline": {"bound": "hbm", "kernel": "experts_umma_kernel<g1>", "achieved": g1_gbs, "peak": peak, "unit": "GB/s",
-                         "frac": g1_gbs / peak, "traffic": None, "peak_kind": peak_kind,
+                         "frac": g1_gbs / peak, "traffic": G1_TRAFFIC_RATIO * g1_bytes / len(pairs), "traffic_note": G1_TRAFFIC_NOTE,
+                         "peak_kind": peak_kind,
                          "us_per_launch": sum(g1_ms) / k_steps * 1e3},
             "e2e": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(info.kernels) * args.steps,
@@ -556,7 +564,8 @@ def run_world(args, cfg, lib, module, device, rank: int, world: int, local: int)
             "layer_roofline": {"bound": "hbm", "achieved": layer_gbs, "peak": peak, "unit": "GB/s", "frac": layer_gbs / peak,
                                "bytes_per_layer": dec["bytes_per_step"] // n_layers, "peak_kind": peak_kind},
             "roofline": {"bound": "hbm", "kernel": "experts_umma_kernel<g1>", "achieved": g1_gbs, "peak": peak, "unit": "GB/s",
-                         "frac": g1_gbs / peak, "traffic": None, "peak_kind": peak_kind,
+                         "frac": g1_gbs / peak, "traffic": G1_TRAFFIC_RATIO * g1_bytes / len(pairs), "traffic_note": G1_TRAFFIC_NOTE,
+                         "peak_kind": peak_kind,
                          "us_per_launch": float(t.item()) / len(pairs) * 1e3},
             "e2e": {"value": dec["e2e_ms_per_step"] * 1e3 / n_layers, "unit": "us",
                     "h2d_bytes_per_step": dec["h2d_bytes_per_step"], "d2h_bytes_per_step": dec["d2h_bytes_per_step"],
