@@ -75,6 +75,21 @@ __device__ __forceinline__ int prov_exp_u(float amax) {
 
 }  // namespace
 
+// Trace builds (-DUMMA_TRACE): CTA 0 stamps the global timer into words [64 + 128 G2, ...) of the status block, four per
+// unit: operands ready (MMA thread), last stage issued (MMA thread), accumulators complete (epilogue), next unit's row
+// scales published (epilogue). Measured on the full shape: 14.0 us (g1) / 6.5 us (g2) from ready to issued, i.e. the weight
+// stream at the SM's share of HBM bandwidth, then 1.5 us until the next unit is ready.
+#ifdef UMMA_TRACE
+#define UT(slot)                                                                                  \
+    if (blockIdx.x == 0 && a.status != nullptr && (slot) < 60) {                                  \
+        unsigned long long t_;                                                                    \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                    \
+        ((unsigned long long*)(a.status + 64 + 128 * G2))[(slot)] = t_;                           \
+    }
+#else
+#define UT(slot)
+#endif
+
 template <bool G2>
 __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) {
     constexpr int TILES = G2 ? 1 : 2;
@@ -163,6 +178,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
                     break;
                 }
                 tc_fence_after();
+                UT(4 * i + 0)
                 const uint32_t xs_addr = smem_u32(xs + buf * kXsBytes);
                 bool ok = true;
                 for (int kc = 0; kc < KCH; ++kc, ++it) {
@@ -191,6 +207,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
                     tc_commit(&empty[s]);
                 }
                 if (!ok) break;
+                UT(4 * i + 1)
                 tc_commit(&acc_full[buf]);
             }
         }
@@ -303,7 +320,9 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
             // all 128 epilogue threads agree on the outcome of a wait before any of them meets the others at a barrier again
             if (!bar_all(2, 128, mbar_wait(&acc_full[buf], (i >> 1) & 1, abort))) break;
             tc_fence_after();
+            if (te == 0) { UT(4 * i + 2) }
             if (u + stride < n_units && !publish(i + 1)) break;
+            if (te == 0) { UT(4 * i + 3) }
             const UnitMeta& m = meta[buf];
             const int blk = u % NB, n_tok = m.n_tok;
             const int mrow = q * 32 + lane;  // weight row of this thread inside the block
