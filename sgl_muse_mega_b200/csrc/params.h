@@ -79,6 +79,10 @@ __device__ __forceinline__ void xchg_wait_epoch(const XchgWait& w, unsigned epoc
     if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
         const unsigned want = epoch * w.contributors;
         long long polls = 0;
+#ifdef XCHG_TRACE
+        unsigned long long t0_;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0_));
+#endif
         for (;;) {
             unsigned seen;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(w.flag) : "memory");
@@ -96,6 +100,17 @@ __device__ __forceinline__ void xchg_wait_epoch(const XchgWait& w, unsigned epoc
             }
             __nanosleep(64);
         }
+#ifdef XCHG_TRACE
+        // trace builds: nanoseconds CTA 0 spent in this wait and the number of waits, per recorded stage (words 256.. of
+        // the status block, as u64 pairs indexed by stage % 32)
+        if (blockIdx.x == 0 && w.status != nullptr) {
+            unsigned long long t1_;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1_));
+            unsigned long long* acc_ = (unsigned long long*)(w.status + 256) + 2 * (w.stage & 31);
+            acc_[0] += t1_ - t0_;
+            acc_[1] += 1;
+        }
+#endif
     }
     __syncthreads();
 }
