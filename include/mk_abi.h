@@ -394,6 +394,174 @@ int mk_qkv_bind(MkModule* module, const MkQkvBind* bind, MkLaunch** out);
 // the GPU (different streams, no dependency) race on it; calls on one stream are safe back to back.
 int mk_qkv_launch_static(const MkQkvBind* bind, uint64_t stream);
 
+// ---- DFlash2 draft --------------------------------------------------------------------------------------------------------
+// The draft's half of a fused decode iteration (reference abi.h:301-545, :645-660; kernels/dflash/{head,layer,kv_sync}.cu):
+// context update, the block forward through the draft's layers, the candidate head with the selector lattice and walk, the
+// pool sync. Unlike the reference's per-image binds (one .so per kernel, weights in tile-packed layouts) the binds here
+// take the plain row-major shards and each yields a launch record of several kernels; every GEMM runs on the item engine
+// (64 rows x 512 k items), the row work between them in small kernels. Head dimension 128, 2 conv taps, top-16.
+//
+// The draft has a flag block of its own (as MkLayerBind.flags: 32 u32, zeroed once): exchange points 0 = gathered fc rows,
+// 1 / 2 = the attention / MLP sublayer's all-reduce, 5 = the draft's gathered logits.
+// Step words (i64): [0] P, the anchor's position; [1] the anchor token; [3] the last commit length.
+typedef struct MkDflashShape {
+    int64_t rows;          // block B (1 anchor + B - 1 mask rows), <= 16
+    int64_t hidden;        // multiple of 512, <= 8192
+    int64_t layers;        // <= 8
+    int64_t q_heads;       // this rank's
+    int64_t kv_heads;      // this rank's
+    int64_t inter;         // this rank's MLP columns, multiple of 512
+    int64_t features;      // captured target layers (fc K = features x hidden), <= 8
+    int64_t ranks;
+    int64_t rank;
+    int64_t window_left;   // keys a query sees on each side
+    int64_t conv_groups;   // hidden / conv group size
+    int64_t vocab;         // whole vocabulary
+    int64_t selector_rank; // even, <= 512
+} MkDflashShape;
+typedef struct MkDflashConstants {
+    int64_t ws_bytes;      // private scratch every draft bind of this shape shares (GEMM partial sums, barrier word, walk counter)
+    int64_t attn_splits;   // 64-key blocks the attention cuts the window into
+    int64_t attn_ws_bytes; // attention partials
+    int64_t topk_chunks;   // candidate lists per row
+    int64_t coeffs;        // conv coefficients per row: 2 sides x 2 taps x groups
+    int64_t qkv_row;       // (q_heads + 2 kv_heads) x 128
+    int64_t kv_rows_n;     // layers x 2 x kv_heads x 128: the context update's k / v columns
+} MkDflashConstants;
+int mk_dflash_constants(const MkDflashShape* shape, MkDflashConstants* out);
+
+// draft entry (reference mk_dflash_entry_bind, abi.h:322-349): feats = bf16(cap), ctx_raw = feats fc^T gathered over the
+// ranks, ctx = rms(ctx_raw) x hid_norm, every layer's context K (head norm, RoPE) / V rows of the last commit into the
+// draft's pools, then the block's embedding rows [anchor, mask ...] and layer 0's input norm. 6 kernels.
+typedef struct MkDflashEntryBind {
+    uint64_t cap[8];        // f32 [rows][hidden] each: the last verify's captured residuals
+    uint64_t words;
+    uint64_t embed_peer[8]; // every rank's vocab shard of the target embedding, bf16 [shard_rows][hidden]
+    int64_t shard_rows;
+    int64_t mask_id;
+    uint64_t w_fc;          // bf16 [hidden / ranks][features x hidden]
+    uint64_t hid_norm;
+    uint64_t in_norm;       // layer 0's input norm
+    uint64_t w_kv;          // bf16 [kv_rows_n][hidden]: per layer its k rows, then its v rows
+    uint64_t k_norm[8];
+    uint64_t k_pool[8];     // bf16 [pool_rows][kv_heads][128] per layer, slot = position % pool_rows
+    uint64_t v_pool[8];
+    int64_t pool_rows;
+    uint64_t rope;          // f32 [rope_rows][128]: cos | sin by position
+    int64_t rope_rows;
+    uint64_t feats;         // bf16 [rows][features x hidden]
+    uint64_t ctx_raw_peer[8];  // bf16 [rows][hidden] on every present rank (own included)
+    uint64_t ctx;           // bf16 [rows][hidden]
+    uint64_t kv;            // bf16 [rows][kv_rows_n]
+    uint64_t x;             // bf16 [rows][hidden]: the block's embedding rows = layer 0's residual
+    uint64_t h;             // bf16 [rows][hidden]: layer 0's normed input
+    uint64_t ws;
+    uint64_t flags;
+    uint64_t flags_peer[8];
+    uint64_t status;
+    int64_t wait_budget;
+    double eps;
+} MkDflashEntryBind;
+int mk_dflash_entry_bind(MkModule* module, const MkDflashShape* shape, const MkDflashEntryBind* bind, MkLaunch** out);
+
+// one draft layer from its normed input (reference mk_dflash_qkv_bind + mk_dflash_layer_bind, abi.h:353-491): conv
+// projection, conv, qkv, head norm + RoPE + K/V append, attention, o_proj partial pushed to every rank, all-reduce + conv
+// finish + post norm, conv projection, conv, gate_up with SwiGLU, down partial pushed, all-reduce + conv finish + the
+// successor's norm (the next layer's input norm, or the final norm). 13 kernels.
+typedef struct MkDflashLayerBind {
+    uint64_t h_in;          // bf16 [rows][hidden]
+    uint64_t res_in;
+    uint64_t words;
+    uint64_t attn_proj;
+    uint64_t attn_base;  // bf16 [coeffs][hidden], [2][2][hidden]
+    uint64_t mlp_proj;
+    uint64_t mlp_base;
+    uint64_t w_qkv;         // bf16 [qkv_row][hidden]: q rows, k rows, v rows
+    uint64_t q_norm;
+    uint64_t k_norm;
+    uint64_t w_o;           // bf16 [hidden][q_heads x 128]
+    uint64_t post_norm;
+    uint64_t w_gate_up;     // bf16 [2 inter][hidden]: gate rows, then up rows
+    uint64_t w_down;        // bf16 [hidden][inter]
+    uint64_t next_norm;     // the successor's norm weight
+    uint64_t k_pool;
+    uint64_t v_pool;
+    int64_t pool_rows;
+    uint64_t rope;
+    int64_t rope_rows;
+    uint64_t c_att;
+    uint64_t xa;
+    uint64_t qkv;
+    uint64_t q;
+    uint64_t attn_ws;
+    uint64_t o;   // bf16 [rows][coeffs], [rows][hidden], [rows][qkv_row], [rows][q x 128], f32 partials, bf16 [rows][q x 128]
+    uint64_t ar_attn_peer[8];                  // bf16 [ranks][16][hidden] on every present rank
+    uint64_t a;             // bf16 [rows][hidden] or 0: the finished attention sublayer output (for checks)
+    uint64_t h_post;
+    uint64_t res_post;
+    uint64_t c_mlp;
+    uint64_t xm;
+    uint64_t m;  // bf16 [rows][coeffs], [rows][hidden], [rows][inter]
+    uint64_t ar_mlp_peer[8];
+    uint64_t x_out;         // bf16 [rows][hidden] or 0: the finished MLP sublayer output (for checks)
+    uint64_t h_out;         // bf16 [rows][hidden]: the successor's normed input (the draft's y after the last layer)
+    uint64_t res_out;       // bf16 [rows][hidden], or 0 after the last layer
+    uint64_t ws;
+    uint64_t flags;
+    uint64_t flags_peer[8];
+    uint64_t status;
+    int64_t wait_budget;
+    double eps;
+} MkDflashLayerBind;
+int mk_dflash_layer_bind(MkModule* module, const MkDflashShape* shape, const MkDflashLayerBind* bind, MkLaunch** out);
+
+// draft head after the draft's own lm_head launch (mk_lm_head_bind over y rows 1.., f32 logits gathered on every rank;
+// reference mk_dflash_draft_head_bind, abi.h:497-544): hid = y W_P^T, per-row top-16 of the bf16-rounded logits (ties to
+// the smaller id), soft cap, the lattice score[e][p][c] = unary[e][c] + bf16(<bf16(A[pred] hid[e]), S[cand[e][c]]>), the
+// greedy walk, the verify window's ids. 3 kernels.
+typedef struct MkDflashDraftHeadBind {
+    uint64_t y;             // bf16 [rows][hidden]; rows 1 .. are read
+    uint64_t w_hproj;       // bf16 [selector_rank][hidden]
+    uint64_t hid;           // bf16 [rows - 1][selector_rank]
+    uint64_t logits;        // f32 [rows - 1][vocab]
+    uint64_t pred_codebook;
+    uint64_t succ_codebook;  // bf16 [vocab][selector_rank]
+    uint64_t words;
+    uint64_t keys;          // u64 [rows - 1][topk_chunks][16]
+    uint64_t cand;          // i64 [rows - 1][16]
+    uint64_t unary;         // f32 [rows - 1][16]
+    uint64_t scores;        // f32 [rows - 1][16][16]
+    uint64_t pick;          // i32 [rows - 1]
+    uint64_t drafts;        // i64 [rows - 1]
+    uint64_t verify_ids;    // i64 [rows]: the anchor, then the drafts
+    double mult;
+    double cap;
+    uint64_t ws;
+    uint64_t flags;         // the logits exchange is awaited when given
+    int64_t contributors;
+    uint64_t status;
+    int64_t wait_budget;
+} MkDflashDraftHeadBind;
+int mk_dflash_draft_head_bind(MkModule* module, const MkDflashShape* shape, const MkDflashDraftHeadBind* bind, MkLaunch** out);
+
+// draft_kv_sync (reference abi.h:645-660, kernels/dflash/kv_sync.cu): the committed positions' K / V rows from the draft's
+// pools into the serving engine's draft pool at the slots it allocated. state i64 [17]: the position the pool is complete
+// to, then the slots of the next positions. A pool and ring that disagree by more than 16 rows copy nothing and record
+// status code 4 (the reference traps).
+typedef struct MkDflashKvSyncBind {
+    uint64_t words;
+    uint64_t window;   // i64 [16]
+    uint64_t state;    // i64 [17]
+    uint64_t ring;     // u64 [n_buf] device array of base pointers
+    uint64_t pool;     // u64 [n_buf]
+    int64_t n_buf;
+    int64_t row_bytes; // multiple of 16
+    int64_t ring_rows;
+    int64_t lag;
+    uint64_t status;
+} MkDflashKvSyncBind;
+int mk_dflash_kv_sync_bind(MkModule* module, const MkDflashKvSyncBind* bind, MkLaunch** out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -255,6 +255,14 @@ def block_forward(cfg: DraftConfig, shards: list, kv: DraftKV, anchor: int, pos:
 # ---- (C) head, lattice, walk -----------------------------------------------------------------------------------------
 
 
+def candidates_from_logits(cfg: DraftConfig, logits: torch.Tensor):
+    """The global top-K of bf16-rounded logits [gamma, V] (ties to the smaller id) and their soft-capped values."""
+    lg = logits.to(BF).float()
+    ids = torch.arange(lg.shape[1]).expand_as(lg)
+    v, i = topk_low_id(lg, ids, cfg.top_k)
+    return i, softcap(v, cfg.output_multiplier, cfg.softcap)
+
+
 def candidates(cfg: DraftConfig, shards: list, y: torch.Tensor):
     """y [gamma, H] (block rows 1..) -> (ids [gamma, K] i64, unary [gamma, K] f32, the bf16-rounded logits [gamma, V]):
     per rank top-K of its vocab rows, then the global top-K of the gathered lists, then the soft cap."""
@@ -273,10 +281,15 @@ def lattice(w, y: torch.Tensor, cand: torch.Tensor, unary: torch.Tensor, anchor:
     """score[e, p, c] = unary[e, c] + bf16(sum_r bf16(A[pred(e, p), r] hid[e, r]) S[cand[e, c], r]); pred(0, .) = the
     anchor, pred(e, p) = cand[e - 1, p]. -> (scores f32 [gamma, K, K], hid bf16 [gamma, R])."""
     hid = mm(y, w.hidden_proj)
+    return lattice_from_hid(w, hid, cand, unary, anchor), hid
+
+
+def lattice_from_hid(w, hid: torch.Tensor, cand: torch.Tensor, unary: torch.Tensor, anchor: int) -> torch.Tensor:
+    """The lattice from the projected rows hid = bf16(W_P y) [gamma, R]."""
     pred = torch.cat([torch.full((1, cand.shape[1]), anchor, dtype=cand.dtype), cand[:-1]])
     prod = (w.pred_codebook[pred].float() * hid.float()[:, None, :]).to(BF)
     dot = torch.einsum("epr,ecr->epc", prod.to(F64), w.succ_codebook[cand].to(F64))
-    return unary[:, None, :] + dot.to(BF).float(), hid
+    return unary[:, None, :] + dot.to(BF).float()
 
 
 def walk(cand: torch.Tensor, scores: torch.Tensor):

@@ -80,7 +80,8 @@ EXPORTS = (
     "mk_last_error", "mk_module_load", "mk_module_free", "mk_launch", "mk_launch_step", "mk_launch_free",
     "mk_launch_info", "mk_launch_status", "mk_layer_constants", "mk_layer_bind", "mk_qkv_constants", "mk_qkv_bind",
     "mk_qkv_launch_static", "mk_feeds_bind", "mk_entry_bind", "mk_lm_head_bind", "mk_softcap_bind", "mk_accept_bind",
-    "mk_symm_alloc", "mk_symm_open", "mk_symm_close", "mk_symm_free",
+    "mk_symm_alloc", "mk_symm_open", "mk_symm_close", "mk_symm_free", "mk_dflash_constants", "mk_dflash_entry_bind",
+    "mk_dflash_layer_bind", "mk_dflash_draft_head_bind", "mk_dflash_kv_sync_bind",
 )  # fmt: skip
 
 
@@ -111,6 +112,11 @@ class Library:
         for fn, st in (("mk_feeds_bind", "MkFeedsBind"), ("mk_entry_bind", "MkEntryBind"), ("mk_lm_head_bind", "MkLmHeadBind"),
                        ("mk_softcap_bind", "MkSoftcapBind"), ("mk_accept_bind", "MkAcceptBind")):  # fmt: skip
             getattr(d, fn).argtypes = [vp, P(STRUCTS[st]), P(vp)]
+        d.mk_dflash_constants.argtypes = [P(STRUCTS["MkDflashShape"]), P(STRUCTS["MkDflashConstants"])]
+        for fn, st in (("mk_dflash_entry_bind", "MkDflashEntryBind"), ("mk_dflash_layer_bind", "MkDflashLayerBind"),
+                       ("mk_dflash_draft_head_bind", "MkDflashDraftHeadBind")):  # fmt: skip
+            getattr(d, fn).argtypes = [vp, P(STRUCTS["MkDflashShape"]), P(STRUCTS[st]), P(vp)]
+        d.mk_dflash_kv_sync_bind.argtypes = [vp, P(STRUCTS["MkDflashKvSyncBind"]), P(vp)]
         d.mk_symm_alloc.argtypes = [ctypes.c_int64, P(ctypes.c_uint64), ctypes.c_char_p]
         d.mk_symm_open.argtypes = [ctypes.c_char_p, P(ctypes.c_uint64)]
         d.mk_symm_close.argtypes = [ctypes.c_uint64]
@@ -159,6 +165,18 @@ class Library:
         self.check(fn(module.handle if module else None, ctypes.byref(bind), ctypes.byref(out)), fn_name)
         return Launch(self, out, module)
 
+
+    def dflash_constants(self, shape) -> ctypes.Structure:
+        c = STRUCTS["MkDflashConstants"]()
+        self.check(self.dll.mk_dflash_constants(ctypes.byref(shape), ctypes.byref(c)), "mk_dflash_constants")
+        return c
+
+    def dflash_bind(self, fn_name: str, module: "Module | None", shape, bind) -> "Launch":
+        """``mk_dflash_{entry,layer,draft_head}_bind(module, shape, bind, out)`` by name."""
+        out = ctypes.c_void_p()
+        fn = getattr(self.dll, fn_name)
+        self.check(fn(module.handle if module else None, ctypes.byref(shape), ctypes.byref(bind), ctypes.byref(out)), fn_name)
+        return Launch(self, out, module)
 
     # ---- memory shared between the ranks' processes ----
     def symm_alloc(self, nbytes: int) -> tuple[int, bytes]:

@@ -1,0 +1,635 @@
+// The DFlash2 draft's row kernels: everything between the draft's GEMMs (which run on the item engine of segments.cuh).
+//
+// Arithmetic follows the reference's test/reference/dflash2.py operation by operation (f32 elementwise steps in its order,
+// no fused multiply-add where it has a separate multiply and add, one bf16 rounding where it rounds):
+//   rms_norm / add_rms_norm :245-266   head_norm_rope :275-294   grouped_conv :297-316   attention :338-361
+//   topk_low_id :391-399   lattice :587-606   selector_walk :609-640   all_reduce :214-222
+// Sums of squares accumulate in f64 (the reference's mean is an f64 mean rounded to f32).
+//
+// Every kernel waits for its predecessor with griddepcontrol.wait before its first dependent read; exchange waits are
+// bounded (params.h). Nothing here traps: an index outside its table is clamped and recorded in the status block (code 4).
+#include "draft.h"
+
+namespace mk {
+
+namespace {
+
+constexpr int kRowThreads = 256;
+
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+// Block-wide f64 sum; `red` holds 33 doubles of shared memory.
+__device__ __forceinline__ double block_sum_d(double v, double* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum_d(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        double s = lane < nw ? red[lane] : 0.0;
+        s = warp_sum_d(s);
+        if (lane == 0) red[32] = s;
+    }
+    __syncthreads();
+    return red[32];
+}
+// 1 / sqrt(x) as two correctly rounded f32 operations
+__device__ __forceinline__ float rsqrt_exact(float x) { return __fdiv_rn(1.0f, __fsqrt_rn(x)); }
+
+__device__ __forceinline__ void record_clamp(int* status, int site, long long v) {
+    if (status != nullptr && atomicCAS(status, 0, 4) == 0) {
+        status[1] = site;
+        status[2] = (int)blockIdx.x;
+        status[3] = (int)v;
+    }
+}
+
+// ---- captured residuals -> fc's input rows ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kRowThreads) dfeats_kernel(const DFeatsArgs a) {
+    griddep_wait();
+    const int row = blockIdx.x / a.n_cap, f = blockIdx.x - row * a.n_cap;
+    const float4* src = (const float4*)(a.cap[f] + (size_t)row * a.hidden);
+    uint2* dst = (uint2*)(a.feats + ((size_t)row * a.n_cap + f) * a.hidden);
+    for (int i = threadIdx.x; i < a.hidden / 4; i += kRowThreads) {
+        const float4 v = src[i];
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        dst[i] = make_uint2(*(const unsigned*)&lo, *(const unsigned*)&hi);
+    }
+}
+
+// ---- norm rows -------------------------------------------------------------------------------------------------------------
+// The all-reduced value of (row, ch): the ranks' bf16 partials summed in rank order in f32, rounded to bf16.
+__device__ __forceinline__ float ar_value(const DNormArgs& a, int row, int ch) {
+    float acc = __bfloat162float(a.ar[(size_t)row * a.H + ch]);
+    for (int r = 1; r < a.ranks; ++r) acc = __fadd_rn(acc, __bfloat162float(a.ar[((size_t)r * 16 + row) * a.H + ch]));
+    return bf16_round(acc);
+}
+
+__global__ void __launch_bounds__(kRowThreads) dnorm_kernel(const DNormArgs a) {
+    __shared__ double red[33];
+    __shared__ long long s_tok;
+    griddep_wait();
+    xchg_wait(a.wait);
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const bf16* src = a.x ? a.x + (size_t)row * a.H : nullptr;
+    if (a.emb_ranks > 0) {
+        if (tid == 0) {
+            long long tok = row == 0 ? a.words[kWordAnchor] : a.mask_id;
+            const long long vocab = a.shard_rows * a.emb_ranks;
+            if (tok < 0 || tok >= vocab) {
+                record_clamp(a.status, 400, tok);
+                tok = tok < 0 ? 0 : vocab - 1;
+            }
+            s_tok = tok;
+        }
+        __syncthreads();
+        src = a.embed[s_tok / a.shard_rows] + (size_t)(s_tok % a.shard_rows) * a.H;
+    }
+    constexpr int kPer = 8192 / kRowThreads;  // H <= 8192
+    float s[kPer];
+    double sq = 0.0;
+    const int per = a.H / kRowThreads;
+    const int taps_stride = a.groups;  // coeff row: [side][tap][group]
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+        if (j >= per) break;
+        const int ch = tid + j * kRowThreads;
+        float x;
+        if (a.ar != nullptr) {
+            x = ar_value(a, row, ch);
+            if (a.coeff != nullptr) {  // the conv's side 1 over the all-reduced rows
+                const int g = ch / (a.H / a.groups);
+                const bf16* c = a.coeff + (size_t)row * 4 * a.groups + 2 * taps_stride;
+                const bf16* b1 = a.base + (size_t)2 * a.H;
+                float out = __fmul_rn(__fadd_rn(__bfloat162float(b1[ch]), __bfloat162float(c[g])), x);
+                if (row > 0) {
+                    const float xp = ar_value(a, row - 1, ch);
+                    out = __fadd_rn(out, __fmul_rn(__fadd_rn(__bfloat162float(b1[a.H + ch]), __bfloat162float(c[taps_stride + g])), xp));
+                }
+                x = bf16_round(out);
+            }
+        } else {
+            x = __bfloat162float(src[ch]);
+        }
+        if (a.x_out != nullptr) a.x_out[(size_t)row * a.H + ch] = __float2bfloat16_rn(x);
+        const float v = a.residual ? __fadd_rn(x, __bfloat162float(a.residual[(size_t)row * a.H + ch])) : x;
+        s[j] = v;
+        sq += (double)v * (double)v;
+    }
+    const float ms = (float)(block_sum_d(sq, red) / (double)a.H);
+    const float r = rsqrt_exact(__fadd_rn(ms, a.eps));
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+        if (j >= per) break;
+        const int ch = tid + j * kRowThreads;
+        a.h[(size_t)row * a.H + ch] = __float2bfloat16_rn(__fmul_rn(__fmul_rn(s[j], r), __bfloat162float(a.w[ch])));
+        if (a.res_out != nullptr) a.res_out[(size_t)row * a.H + ch] = __float2bfloat16_rn(s[j]);
+    }
+}
+
+// ---- grouped conv, side 0 -----------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kRowThreads) dconv_kernel(const DConvArgs a) {
+    griddep_wait();
+    const int row = blockIdx.x, per_group = a.H / a.groups;
+    const bf16* c = a.coeff + (size_t)row * 4 * a.groups;  // side 0: taps at [0, groups) and [groups, 2 groups)
+    for (int ch = threadIdx.x; ch < a.H; ch += kRowThreads) {
+        const int g = ch / per_group;
+        float out = __fmul_rn(__fadd_rn(__bfloat162float(a.base[ch]), __bfloat162float(c[g])), __bfloat162float(a.h[(size_t)row * a.H + ch]));
+        if (row > 0)
+            out = __fadd_rn(out, __fmul_rn(__fadd_rn(__bfloat162float(a.base[a.H + ch]), __bfloat162float(c[a.groups + g])),
+                                           __bfloat162float(a.h[(size_t)(row - 1) * a.H + ch])));
+        a.out[(size_t)row * a.H + ch] = __float2bfloat16_rn(out);
+    }
+}
+
+// ---- head norm + neox RoPE -----------------------------------------------------------------------------------------------------
+// One warp per 128-wide head: lane l holds elements 2l, 2l + 1 of the low half and of the high half. `round_normed`: the
+// block's q / k round the normed head to bf16 before the rotation, the context K does not.
+__device__ __forceinline__ void head_norm_rope(const bf16* x, const bf16* w, float eps, const float* cos_sin, bool round_normed,
+                                               bf16* out, int lane) {
+    const __nv_bfloat162 xl = *(const __nv_bfloat162*)(x + 2 * lane), xh = *(const __nv_bfloat162*)(x + 64 + 2 * lane);
+    float v[4] = {__low2float(xl), __high2float(xl), __low2float(xh), __high2float(xh)};
+    double sq = 0.0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sq += (double)v[i] * (double)v[i];
+    const float ms = (float)(warp_sum_d(sq) / 128.0);
+    const float r = rsqrt_exact(__fadd_rn(ms, eps));
+    const __nv_bfloat162 wl = *(const __nv_bfloat162*)(w + 2 * lane), wh = *(const __nv_bfloat162*)(w + 64 + 2 * lane);
+    const float wv[4] = {__low2float(wl), __high2float(wl), __low2float(wh), __high2float(wh)};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[i] = __fmul_rn(__fmul_rn(v[i], r), wv[i]);
+        if (round_normed) v[i] = bf16_round(v[i]);
+    }
+    const float2 c = *(const float2*)(cos_sin + 2 * lane), s = *(const float2*)(cos_sin + 64 + 2 * lane);
+    const float lo0 = __fsub_rn(__fmul_rn(v[0], c.x), __fmul_rn(v[2], s.x)), lo1 = __fsub_rn(__fmul_rn(v[1], c.y), __fmul_rn(v[3], s.y));
+    const float hi0 = __fadd_rn(__fmul_rn(v[2], c.x), __fmul_rn(v[0], s.x)), hi1 = __fadd_rn(__fmul_rn(v[3], c.y), __fmul_rn(v[1], s.y));
+    *(__nv_bfloat162*)(out + 2 * lane) = __floats2bfloat162_rn(lo0, lo1);
+    *(__nv_bfloat162*)(out + 64 + 2 * lane) = __floats2bfloat162_rn(hi0, hi1);
+}
+
+__device__ __forceinline__ long long clamp_pos(long long p, long long rows, int* status, int site) {
+    if (p < 0 || p >= rows) {
+        record_clamp(status, site, p);
+        p = p < 0 ? 0 : rows - 1;
+    }
+    return p;
+}
+
+__global__ void __launch_bounds__(kRowThreads) dqkv_rows_kernel(const DQkvRowsArgs a) {
+    griddep_wait();
+    const int lane = threadIdx.x & 31, heads = a.qh + 2 * a.kvh;
+    const long long P = a.words[kWordP];
+    for (int w = blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5); w < a.M * heads; w += gridDim.x * (kRowThreads / 32)) {
+        const int m = w / heads, head = w - m * heads;
+        const bf16* x = a.qkv + ((size_t)m * heads + head) * kDraftHeadDim;
+        const long long pos = clamp_pos(P + m, a.rope_rows, a.status, 410);
+        const size_t slot = (size_t)((P + m) % a.pool_rows + a.pool_rows) % a.pool_rows;
+        if (head < a.qh) {
+            head_norm_rope(x, a.q_norm, a.eps, a.rope + pos * kDraftHeadDim, true, a.q_out + ((size_t)m * a.qh + head) * kDraftHeadDim, lane);
+        } else if (head < a.qh + a.kvh) {
+            head_norm_rope(x, a.k_norm, a.eps, a.rope + pos * kDraftHeadDim, true,
+                           a.k_pool + (slot * a.kvh + (head - a.qh)) * kDraftHeadDim, lane);
+        } else {
+            uint2* dst = (uint2*)(a.v_pool + (slot * a.kvh + (head - a.qh - a.kvh)) * kDraftHeadDim);
+            dst[lane] = ((const uint2*)x)[lane];
+        }
+    }
+}
+
+// The context rows of the last commit: row i sits at position P - commit + i; rows >= commit are not written.
+__global__ void __launch_bounds__(kRowThreads) dctx_kv_kernel(const DCtxKvArgs a) {
+    griddep_wait();
+    const int lane = threadIdx.x & 31, per_row = a.layers * 2 * a.kvh;
+    const long long P = a.words[kWordP], commit = a.words[kWordCommit];
+    for (int w = blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5); w < a.M * per_row; w += gridDim.x * (kRowThreads / 32)) {
+        const int m = w / per_row, rest = w - m * per_row, layer = rest / (2 * a.kvh), hv = rest - layer * 2 * a.kvh;
+        if (m >= commit) continue;
+        const long long p = P - commit + m;
+        const long long pos = clamp_pos(p, a.rope_rows, a.status, 420);
+        const size_t slot = (size_t)(p % a.pool_rows + a.pool_rows) % a.pool_rows;
+        const bf16* x = a.kv + ((size_t)m * per_row + rest) * kDraftHeadDim;
+        if (hv < a.kvh) {
+            head_norm_rope(x, a.k_norm[layer], a.eps, a.rope + pos * kDraftHeadDim, false,
+                           a.k_pool[layer] + (slot * a.kvh + hv) * kDraftHeadDim, lane);
+        } else {
+            uint2* dst = (uint2*)(a.v_pool[layer] + (slot * a.kvh + (hv - a.kvh)) * kDraftHeadDim);
+            dst[lane] = ((const uint2*)x)[lane];
+        }
+    }
+}
+
+// ---- non-causal sliding-window attention, head dim 128 -----------------------------------------------------------------------------
+// grid (nsplit, kvh): a CTA scores the M x G query rows of one kv head against one block of 64 key positions and leaves
+// (max, sum, unnormalised output) per row; the merge kernel combines the blocks. f32 FMAs from shared memory: the block is
+// 2 x 128 x 64 x 128 multiply-adds, and at most 34 blocks x kv heads run side by side.
+constexpr int kAQ = 128;        // query rows per kv head (M x G <= 128)
+constexpr int kAKeys = kDraftKeysPerSplit;
+constexpr int kAKt = kAKeys + 4;  // padded row of the transposed key tile
+constexpr size_t kAttnSmem = ((size_t)kAQ * 128 + 128 * kAKt + (size_t)kAKeys * 128 + (size_t)kAQ * kAKeys + 2 * kAQ) * 4;
+
+__global__ void __launch_bounds__(256, 1) dattn_split_kernel(const DAttnArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    float* Qs = sm;                     // [128][128]
+    float* Kt = Qs + kAQ * 128;         // [128 d][68]
+    float* Vs = Kt + 128 * kAKt;        // [64][128]
+    float* Ps = Vs + kAKeys * 128;      // [128][64]
+    float* ms = Ps + kAQ * kAKeys;      // [128]
+    float* ls = ms + kAQ;
+    griddep_wait();
+    const int tid = threadIdx.x, split = blockIdx.x, h = blockIdx.y;
+    const int G = a.qh / a.kvh, R = a.M * G;
+    const long long P = a.words[kWordP];
+    const long long lo = P - a.left > 0 ? P - a.left : 0, hi = P + a.M - 1;
+    const long long key0 = lo + (long long)split * kAKeys;
+    float* wsb = a.ws + ((size_t)h * a.nsplit + split) * R * 132;
+    if (key0 > hi) {  // no keys here: an empty partial
+        for (int r = tid; r < R; r += 256) {
+            wsb[(size_t)r * 132] = -INFINITY;
+            wsb[(size_t)r * 132 + 1] = 0.f;
+        }
+        return;
+    }
+    // Q rows r = b G + g of this kv head
+    for (int i = tid; i < kAQ * 64; i += 256) {
+        const int r = i >> 6, d2 = i & 63;
+        float2 v = make_float2(0.f, 0.f);
+        if (r < R) {
+            const int b = r / G, g = r - b * G;
+            const __nv_bfloat162 q = *(const __nv_bfloat162*)(a.q + ((size_t)b * a.qh + h * G + g) * 128 + 2 * d2);
+            v = make_float2(__low2float(q), __high2float(q));
+        }
+        *(float2*)(Qs + r * 128 + 2 * d2) = v;
+    }
+    for (int i = tid; i < kAKeys * 64; i += 256) {
+        const int kk = i >> 6, d2 = i & 63;
+        const long long pk = key0 + kk;
+        float2 kf = make_float2(0.f, 0.f), vf = make_float2(0.f, 0.f);
+        if (pk <= hi) {
+            const size_t slot = (size_t)(pk % a.pool_rows);
+            const __nv_bfloat162 k2 = *(const __nv_bfloat162*)(a.k_pool + (slot * a.kvh + h) * 128 + 2 * d2);
+            const __nv_bfloat162 v2 = *(const __nv_bfloat162*)(a.v_pool + (slot * a.kvh + h) * 128 + 2 * d2);
+            kf = make_float2(__low2float(k2), __high2float(k2));
+            vf = make_float2(__low2float(v2), __high2float(v2));
+        }
+        Kt[(2 * d2) * kAKt + kk] = kf.x;
+        Kt[(2 * d2 + 1) * kAKt + kk] = kf.y;
+        *(float2*)(Vs + kk * 128 + 2 * d2) = vf;
+    }
+    __syncthreads();
+    const int ty = tid >> 4, tx = tid & 15;
+    {
+        float acc[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+        for (int d = 0; d < 128; ++d) {
+            const float4 k4 = *(const float4*)(Kt + d * kAKt + tx * 4);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float q = Qs[(ty * 8 + i) * 128 + d];
+                acc[i][0] = fmaf(q, k4.x, acc[i][0]);
+                acc[i][1] = fmaf(q, k4.y, acc[i][1]);
+                acc[i][2] = fmaf(q, k4.z, acc[i][2]);
+                acc[i][3] = fmaf(q, k4.w, acc[i][3]);
+            }
+        }
+        const float scale = 0.08838834764831845f;  // 128^-0.5
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int r = ty * 8 + i;
+            const long long pq = P + r / G;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const long long pk = key0 + tx * 4 + j;
+                const bool seen = r < R && pk <= hi && pk >= pq - a.left && pk <= pq + a.left;
+                Ps[r * kAKeys + tx * 4 + j] = seen ? acc[i][j] * scale : -INFINITY;
+            }
+        }
+    }
+    __syncthreads();
+    {
+        const int warp = tid >> 5, lane = tid & 31;
+        for (int r = warp; r < kAQ; r += 8) {
+            const float s0 = Ps[r * kAKeys + lane], s1 = Ps[r * kAKeys + 32 + lane];
+            const float m = warp_max(fmaxf(s0, s1));
+            const float p0 = m == -INFINITY ? 0.f : expf(s0 - m), p1 = m == -INFINITY ? 0.f : expf(s1 - m);
+            const float l = warp_sum(p0 + p1);
+            Ps[r * kAKeys + lane] = p0;
+            Ps[r * kAKeys + 32 + lane] = p1;
+            if (lane == 0) {
+                ms[r] = m;
+                ls[r] = l;
+            }
+        }
+    }
+    __syncthreads();
+    {
+        float acc[8][8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+        for (int kk = 0; kk < kAKeys; ++kk) {
+            const float4 va = *(const float4*)(Vs + kk * 128 + tx * 4), vb = *(const float4*)(Vs + kk * 128 + 64 + tx * 4);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float p = Ps[(ty * 8 + i) * kAKeys + kk];
+                acc[i][0] = fmaf(p, va.x, acc[i][0]);
+                acc[i][1] = fmaf(p, va.y, acc[i][1]);
+                acc[i][2] = fmaf(p, va.z, acc[i][2]);
+                acc[i][3] = fmaf(p, va.w, acc[i][3]);
+                acc[i][4] = fmaf(p, vb.x, acc[i][4]);
+                acc[i][5] = fmaf(p, vb.y, acc[i][5]);
+                acc[i][6] = fmaf(p, vb.z, acc[i][6]);
+                acc[i][7] = fmaf(p, vb.w, acc[i][7]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int r = ty * 8 + i;
+            if (r >= R) continue;
+            float* o = wsb + (size_t)r * 132;
+            if (tx == 0) {
+                o[0] = ms[r];
+                o[1] = ls[r];
+            }
+            *(float4*)(o + 4 + tx * 4) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+            *(float4*)(o + 4 + 64 + tx * 4) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+        }
+    }
+}
+
+// One warp per (window row, q head): the blocks' partials combined in block order.
+__global__ void __launch_bounds__(kRowThreads) dattn_merge_kernel(const DAttnArgs a) {
+    griddep_wait();
+    const int lane = threadIdx.x & 31, G = a.qh / a.kvh, R = a.M * G;
+    for (int w = blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5); w < a.M * a.qh; w += gridDim.x * (kRowThreads / 32)) {
+        const int b = w / a.qh, head = w - b * a.qh, h = head / G, r = b * G + (head - h * G);
+        const float* base = a.ws + ((size_t)h * a.nsplit * R + r) * 132;
+        float mx = -INFINITY;
+        for (int s = 0; s < a.nsplit; ++s) mx = fmaxf(mx, base[(size_t)s * R * 132]);
+        float l = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < a.nsplit; ++s) {
+            const float* p = base + (size_t)s * R * 132;
+            const float m = p[0];
+            if (m == -INFINITY) continue;
+            const float f = expf(m - mx);
+            l += p[1] * f;
+            const float2 v0 = *(const float2*)(p + 4 + 2 * lane), v1 = *(const float2*)(p + 4 + 64 + 2 * lane);
+            o[0] += v0.x * f;
+            o[1] += v0.y * f;
+            o[2] += v1.x * f;
+            o[3] += v1.y * f;
+        }
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        bf16* out = a.o + ((size_t)b * a.qh + head) * 128;
+        *(__nv_bfloat162*)(out + 2 * lane) = __floats2bfloat162_rn(o[0] * inv, o[1] * inv);
+        *(__nv_bfloat162*)(out + 64 + 2 * lane) = __floats2bfloat162_rn(o[2] * inv, o[3] * inv);
+    }
+}
+
+// ---- candidates: top-16 by (value descending, id ascending) -------------------------------------------------------------------------
+// A key orders both at once: the bf16-rounded logit as a sortable 32-bit pattern above the complemented id.
+__device__ __forceinline__ unsigned long long topk_key(float logit, unsigned id) {
+    unsigned u = __float_as_uint(bf16_round(logit));
+    if (logit != logit) u = 0xFFFFFFFFu;  // NaN sorts above every number, as torch's descending sort places it
+    else u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - id);
+}
+__device__ __forceinline__ float key_value(unsigned long long k) {
+    unsigned u = (unsigned)(k >> 32);
+    if (u == 0xFFFFFFFFu) return __uint_as_float(0x7FC00000u);
+    u = (u & 0x80000000u) ? (u & 0x7FFFFFFFu) : ~u;
+    return __uint_as_float(u);
+}
+__device__ __forceinline__ unsigned key_id(unsigned long long k) { return 0xFFFFFFFFu - (unsigned)(k & 0xFFFFFFFFull); }
+
+// 16 rounds of block arg-max over the threads' register-held keys (PER per thread; 0 = empty). out[round] = the key.
+template <int PER>
+__device__ __forceinline__ void block_top16(unsigned long long (&k)[PER], unsigned long long* out, unsigned long long* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int round = 0; round < kDraftTopK; ++round) {
+        unsigned long long best = 0;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) best = k[j] > best ? k[j] : best;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+            best = other > best ? other : best;
+        }
+        __syncthreads();
+        if (lane == 0) red[warp] = best;
+        __syncthreads();
+        unsigned long long win = 0;
+#pragma unroll
+        for (int w = 0; w < kRowThreads / 32; ++w) win = red[w] > win ? red[w] : win;
+        if (win != 0) {
+#pragma unroll
+            for (int j = 0; j < PER; ++j)
+                if (k[j] == win) k[j] = 0;
+        }
+        if (threadIdx.x == 0) out[round] = win;
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(kRowThreads) dtopk_kernel(const DTopkArgs a) {
+    __shared__ unsigned long long red[kRowThreads / 32];
+    griddep_wait();
+    xchg_wait(a.wait);
+    const int chunk = blockIdx.x, row = blockIdx.y;
+    constexpr int PER = kDraftTopkChunk / kRowThreads;
+    unsigned long long k[PER];
+    const long long start = (long long)chunk * kDraftTopkChunk;
+    const float* src = a.logits + (size_t)row * a.V;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const long long id = start + threadIdx.x + (long long)j * kRowThreads;
+        k[j] = id < a.V ? topk_key(src[id], (unsigned)id) : 0ull;
+    }
+    block_top16<PER>(k, a.keys + ((size_t)row * a.nchunk + chunk) * kDraftTopK, red);
+}
+
+// ---- lattice and walk ---------------------------------------------------------------------------------------------------------------
+constexpr int kMaxMergePer = kMaxMergeChunks * kDraftTopK / kRowThreads;
+
+// The global top-16 of a row from its chunks' lists -> s_out[16] keys.
+__device__ __forceinline__ void merge_row(const unsigned long long* keys, int nchunk, unsigned long long* s_out, unsigned long long* red) {
+    unsigned long long k[kMaxMergePer];
+    const int n = nchunk * kDraftTopK;
+#pragma unroll
+    for (int j = 0; j < kMaxMergePer; ++j) {
+        const int i = threadIdx.x + j * kRowThreads;
+        k[j] = i < n ? keys[i] : 0ull;
+    }
+    block_top16<kMaxMergePer>(k, s_out, red);
+}
+
+__global__ void __launch_bounds__(kRowThreads) dlattice_kernel(const DLatticeArgs a) {
+    __shared__ unsigned long long red[kRowThreads / 32];
+    __shared__ unsigned long long s_cur[kDraftTopK], s_prev[kDraftTopK];
+    __shared__ float s_hid[512];
+    __shared__ float s_unary[kDraftTopK];
+    __shared__ unsigned s_last;
+    griddep_wait();
+    const int e = blockIdx.x, tid = threadIdx.x;
+    merge_row(a.keys + (size_t)e * a.nchunk * kDraftTopK, a.nchunk, s_cur, red);
+    if (e > 0) merge_row(a.keys + (size_t)(e - 1) * a.nchunk * kDraftTopK, a.nchunk, s_prev, red);
+    for (int i = tid; i < a.R; i += kRowThreads) s_hid[i] = __bfloat162float(a.hid[(size_t)e * a.R + i]);
+    if (tid < kDraftTopK) {
+        const float v = key_value(s_cur[tid]);
+        const float u = __fmul_rn(tanhf(__fdiv_rn(__fmul_rn(v, a.mult), a.cap)), a.cap);
+        s_unary[tid] = u;
+        a.cand[(size_t)e * kDraftTopK + tid] = (long long)key_id(s_cur[tid]);
+        a.unary[(size_t)e * kDraftTopK + tid] = u;
+    }
+    __syncthreads();
+    {
+        const int p = tid >> 4, c = tid & 15;
+        long long pred = e == 0 ? a.words[kWordAnchor] : (long long)key_id(s_prev[p]);
+        if (pred < 0 || pred >= a.vocab) {
+            record_clamp(a.status, 430, pred);
+            pred = pred < 0 ? 0 : a.vocab - 1;
+        }
+        const bf16* A = a.pred + (size_t)pred * a.R;
+        const bf16* S = a.succ + (size_t)key_id(s_cur[c]) * a.R;
+        double dot = 0.0;
+        for (int r = 0; r < a.R; r += 2) {
+            const __nv_bfloat162 av = *(const __nv_bfloat162*)(A + r), sv = *(const __nv_bfloat162*)(S + r);
+            // the product A x hid is exact in f32 (two bf16 factors) and rounded to bf16 as the reference stores it
+            const float p0 = bf16_round(__fmul_rn(__low2float(av), s_hid[r])), p1 = bf16_round(__fmul_rn(__high2float(av), s_hid[r + 1]));
+            dot += (double)p0 * (double)__low2float(sv) + (double)p1 * (double)__high2float(sv);
+        }
+        a.scores[((size_t)e * kDraftTopK + p) * kDraftTopK + c] = __fadd_rn(s_unary[c], __bfloat162float(__double2bfloat16(dot)));
+    }
+    // the last block to finish walks the lattice
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(a.counter, 1u) == gridDim.x - 1 ? 1u : 0u;
+    __syncthreads();
+    if (s_last == 0) return;
+    __threadfence();
+    if (tid == 0) {
+        *a.counter = 0;
+        int prev = 0;
+        a.verify_ids[0] = a.words[kWordAnchor];
+        for (int s = 0; s < a.gamma; ++s) {
+            const volatile float* row = a.scores + ((size_t)s * kDraftTopK + prev) * kDraftTopK;
+            int idx = -1;
+            for (int c = 0; c < kDraftTopK && idx < 0; ++c)
+                if (row[c] != row[c]) idx = c;  // the first NaN wins
+            if (idx < 0) {
+                idx = 0;
+                float best = row[0];
+                for (int c = 1; c < kDraftTopK; ++c)
+                    if (row[c] > best) {
+                        best = row[c];
+                        idx = c;
+                    }
+            }
+            const long long tok = ((const volatile long long*)a.cand)[(size_t)s * kDraftTopK + idx];
+            a.drafts[s] = tok;
+            a.verify_ids[1 + s] = tok;
+            a.pick[s] = idx;
+            prev = idx;
+        }
+    }
+}
+
+// ---- the draft's rings -> the serving pool ---------------------------------------------------------------------------------------------
+// state[0]: the position up to which the pool holds the request's context; state[1 + i]: the pool slot of position
+// state[0] + i (the window slots of the iteration that committed them). lag 1 (an iteration's last launch): the rings
+// hold the positions below P - commit; lag 0 (after a draft that ran alone): below P. One CTA.
+__global__ void __launch_bounds__(kRowThreads) dkv_sync_kernel(const DKvSyncArgs a) {
+    __shared__ long long s_slot[16];
+    __shared__ long long s_from;
+    __shared__ int s_n;
+    griddep_wait();
+    const int t = threadIdx.x;
+    if (t == 0) {
+        const long long from = a.state[0], to = a.words[kWordP] - (a.lag ? a.words[kWordCommit] : 0);
+        long long n = to - from;
+        if (n < 0 || n > 16) {  // the pool and the rings disagree: copy nothing, say so
+            record_clamp(a.status, 440, n);
+            n = 0;
+        }
+        s_from = from;
+        s_n = (int)n;
+    }
+    if (t < 16) s_slot[t] = a.state[1 + t];
+    __syncthreads();
+    const long long from = s_from;
+    const int n = s_n, q = a.row_bytes / 16;
+    for (int i = t; i < a.n_buf * n * q; i += kRowThreads) {
+        const int k = i % q, r = i / q % n, b = i / (q * n);
+        const long long ring_row = ((from + r) % a.ring_rows + a.ring_rows) % a.ring_rows;
+        const uint4* src = (const uint4*)a.ring[b] + (size_t)ring_row * q + k;
+        ((uint4*)a.pool[b])[(size_t)s_slot[r] * q + k] = *src;
+    }
+    __syncthreads();
+    if (t == 0) a.state[0] = from + n;
+    if (a.lag && t < 16) a.state[1 + t] = a.window[t];
+}
+
+template <typename Args>
+cudaError_t launch_d(void (*kern)(const Args), dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl, const Args& a) {
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, a);
+}
+
+}  // namespace
+
+size_t dattn_smem() { return kAttnSmem; }
+
+cudaError_t draft_prepare() {
+    return cudaFuncSetAttribute(dattn_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
+}
+
+cudaError_t dfeats_launch(const DFeatsArgs& a, cudaStream_t s, bool pdl) {
+    return launch_d(dfeats_kernel, dim3(a.rows * a.n_cap), dim3(kRowThreads), 0, s, pdl, a);
+}
+cudaError_t dnorm_launch(const DNormArgs& a, cudaStream_t s, bool pdl) {
+    return launch_d(dnorm_kernel, dim3(a.M), dim3(kRowThreads), 0, s, pdl, a);
+}
+cudaError_t dconv_launch(const DConvArgs& a, cudaStream_t s, bool pdl) {
+    return launch_d(dconv_kernel, dim3(a.M), dim3(kRowThreads), 0, s, pdl, a);
+}
+cudaError_t dqkv_rows_launch(const DQkvRowsArgs& a, cudaStream_t s, bool pdl) {
+    const int warps = a.M * (a.qh + 2 * a.kvh);
+    return launch_d(dqkv_rows_kernel, dim3((warps + 7) / 8), dim3(kRowThreads), 0, s, pdl, a);
+}
+cudaError_t dctx_kv_launch(const DCtxKvArgs& a, cudaStream_t s, bool pdl) {
+    const int warps = a.M * a.layers * 2 * a.kvh;
+    return launch_d(dctx_kv_kernel, dim3((warps + 7) / 8), dim3(kRowThreads), 0, s, pdl, a);
+}
+cudaError_t dattn_split_launch(const DAttnArgs& a, cudaStream_t s, bool pdl) {
+    return launch_d(dattn_split_kernel, dim3(a.nsplit, a.kvh), dim3(256), kAttnSmem, s, pdl, a);
+}
+cudaError_t dattn_merge_launch(const DAttnArgs& a, cudaStream_t s, bool pdl) {
+    return launch_d(dattn_merge_kernel, dim3((a.M * a.qh + 7) / 8), dim3(kRowThreads), 0, s, pdl, a);
+}
+cudaError_t dtopk_launch(const DTopkArgs& a, cudaStream_t s, bool pdl) {
+    return launch_d(dtopk_kernel, dim3(a.nchunk, a.gamma), dim3(kRowThreads), 0, s, pdl, a);
+}
+cudaError_t dlattice_launch(const DLatticeArgs& a, cudaStream_t s, bool pdl) {
+    return launch_d(dlattice_kernel, dim3(a.gamma), dim3(kRowThreads), 0, s, pdl, a);
+}
+cudaError_t dkv_sync_launch(const DKvSyncArgs& a, cudaStream_t s, bool pdl) {
+    return launch_d(dkv_sync_kernel, dim3(1), dim3(kRowThreads), 0, s, pdl, a);
+}
+
+}  // namespace mk

@@ -10,6 +10,7 @@
 #include <new>
 
 #include "../../include/mk_abi.h"
+#include "draft.h"
 #include "stages.h"
 
 namespace mk {
@@ -85,6 +86,9 @@ struct MkLaunch {
     mk::SoftcapArgs softcap;
     mk::AcceptArgs accept;
     mk::GemmArgs op_gemm;
+    // the DFlash2 draft's launch lists: n_dops > 0 replaces both of the above
+    mk::DraftOp* dops;
+    int n_dops;
 };
 // exchange points (word index in a rank's flag block) and the default poll budget of a wait (~64 ns a poll: about 0.3 s)
 enum XchgPoint { XP_AR = 0, XP_POOL, XP_Z, XP_ZB, XP_UNPOOL, XP_LOGITS };
@@ -188,6 +192,8 @@ int mk_module_load(const void* image, uint64_t bytes, const char* code_prefetch_
     if (e != cudaSuccess) return cuda_fail(e, "experts_umma_prepare");
     e = segments_prepare();
     if (e != cudaSuccess) return cuda_fail(e, "segments_prepare");
+    e = draft_prepare();
+    if (e != cudaSuccess) return cuda_fail(e, "draft_prepare");
     MkModule* m = new (std::nothrow) MkModule{dev, prop.multiProcessorCount};
     MK_REQUIRE(m != nullptr, "out of host memory");
     *out = m;
@@ -624,10 +630,38 @@ static int run_stage(const MkLaunch* L, int st, cudaStream_t s, bool pdl) {
     return 0;
 }
 
+static int run_dops(const MkLaunch* L, int first, int last, cudaStream_t s, bool pdl) {
+    for (int i = first; i < last; ++i) {
+        const DraftOp& op = L->dops[i];
+        cudaError_t e = cudaSuccess;
+        switch (op.kind) {
+            case DOP_FEATS: e = dfeats_launch(op.feats, s, pdl); break;
+            case DOP_GEMM: e = seg_gemm_launch(op.gemm, L->sms, s, pdl); break;
+            case DOP_NORM: e = dnorm_launch(op.norm, s, pdl); break;
+            case DOP_CONV: e = dconv_launch(op.conv, s, pdl); break;
+            case DOP_QKV_ROWS: e = dqkv_rows_launch(op.rows, s, pdl); break;
+            case DOP_CTX_KV: e = dctx_kv_launch(op.ckv, s, pdl); break;
+            case DOP_ATTN_SPLIT: e = dattn_split_launch(op.attn, s, pdl); break;
+            case DOP_ATTN_MERGE: e = dattn_merge_launch(op.attn, s, pdl); break;
+            case DOP_TOPK: e = dtopk_launch(op.topk, s, pdl); break;
+            case DOP_LATTICE: e = dlattice_launch(op.lat, s, pdl); break;
+            case DOP_KV_SYNC: e = dkv_sync_launch(op.sync, s, pdl); break;
+            default: return fail("draft kernel kind %d does not exist", op.kind);
+        }
+        if (e != cudaSuccess) return fail("draft kernel %d (kind %d) launch: %s", i, op.kind, cudaGetErrorString(e));
+    }
+    return 0;
+}
+
 int mk_launch_step(const MkLaunch* launch, uint64_t stream, int64_t first, int64_t count) {
     MK_REQUIRE(launch != nullptr, "launch is NULL");
-    MK_REQUIRE(launch->n_ops == 0, "mk_launch_step addresses the stages of a layer launch");
     MK_REQUIRE(!launch->pack_only, "a pack-only record (bound without a module) cannot launch");
+    if (launch->n_dops > 0) {  // a draft launch: its kernels by index
+        MK_REQUIRE(first >= 0 && count >= 0 && first + count <= launch->n_dops, "kernels [%lld, %lld) outside 0..%d", (long long)first,
+                   (long long)(first + count), launch->n_dops);
+        return run_dops(launch, (int)first, (int)(first + count), (cudaStream_t)stream, false);
+    }
+    MK_REQUIRE(launch->n_ops == 0, "mk_launch_step addresses the stages of a layer launch");
     MK_REQUIRE(first >= 0 && count >= 0 && first + count <= ST_COUNT, "stages [%lld, %lld) outside 0..%d", (long long)first,
                (long long)(first + count), ST_COUNT);
     for (int st = (int)first; st < first + count; ++st)
@@ -654,6 +688,7 @@ static int run_ops(const MkLaunch* L, cudaStream_t s, bool pdl) {
 int mk_launch(const MkLaunch* launch, uint64_t stream, int pdl) {
     MK_REQUIRE(launch != nullptr, "launch is NULL");
     MK_REQUIRE(!launch->pack_only, "a pack-only record (bound without a module) cannot launch");
+    if (launch->n_dops > 0) return run_dops(launch, 0, launch->n_dops, (cudaStream_t)stream, pdl != 0);
     if (launch->n_ops > 0) return run_ops(launch, (cudaStream_t)stream, pdl != 0);
     if (launch->use_segments) {
         const MkLaunch* L = launch;
@@ -672,11 +707,24 @@ int mk_launch(const MkLaunch* launch, uint64_t stream, int pdl) {
     return 0;
 }
 
-void mk_launch_free(MkLaunch* launch) { delete launch; }
+void mk_launch_free(MkLaunch* launch) {
+    if (launch != nullptr) delete[] launch->dops;
+    delete launch;
+}
 
 int mk_launch_info(const MkLaunch* launch, MkLaunchInfo* out) {
     MK_REQUIRE(launch != nullptr && out != nullptr, "launch or out is NULL");
     const MkLaunch* L = launch;
+    if (L->n_dops > 0) {
+        memset(out, 0, sizeof *out);
+        out->kernels = L->n_dops;
+        out->grid = L->sms;
+        out->block = 512;
+        out->cluster = 1;
+        out->smem = (int64_t)segments_smem();
+        out->param_bytes = (int64_t)sizeof(MkLaunch) + (int64_t)L->n_dops * (int64_t)sizeof(DraftOp);
+        return 0;
+    }
     if (L->n_ops > 0) {
         memset(out, 0, sizeof *out);
         out->kernels = L->n_ops;
@@ -1068,3 +1116,5 @@ int mk_launch_status(const MkLaunch* launch, uint64_t stream, MkLaunchStatus* ou
 }
 
 }  // extern "C"
+
+#include "draft_host.inc"

@@ -261,6 +261,26 @@ __device__ __forceinline__ void seg_finish_bf16(const SegGemm& g, bf16* const* o
     }
 }
 
+// SwiGLU over a [gate rows | up rows] GEMM: out[m, n] = bf16(silu(bf16(gate[m, n])) x bf16(up[m, n])), n < N / 2; f32 steps
+// in the order gate / (1 + exp(-gate)) x up.
+__device__ __forceinline__ void seg_finish_silu(const SegGemm& g, bf16* const* out, int n_out, long long ldo, long long off0) {
+    const int nsplit = g.K / kChunkK, half = g.N / 2;
+    const long long total = (long long)g.M * half;
+    for (long long i = (long long)blockIdx.x * kSegThreads + threadIdx.x; i < total; i += (long long)gridDim.x * kSegThreads) {
+        const int m = (int)(i / half), n = (int)(i - (long long)m * half);
+        float gate = 0.f, up = 0.f;
+        for (int ks = 0; ks < nsplit; ++ks) {
+            const float* row = g.part + ((size_t)ks * 16 + m) * g.N;
+            gate += row[n];
+            up += row[half + n];
+        }
+        gate = bf16_round(gate);
+        up = bf16_round(up);
+        const bf16 b = __float2bfloat16_rn(__fmul_rn(__fdiv_rn(gate, __fadd_rn(1.0f, expf(-gate))), up));
+        for (int d = 0; d < n_out; ++d) out[d][off0 + (long long)m * ldo + n] = b;
+    }
+}
+
 // logits[m, n] = sum_ks part[ks][m][n] (f32), by one CTA.
 __device__ __forceinline__ void seg_finish_f32_cta(const SegGemm& g, float* out) {
     const int nsplit = g.K / kChunkK;
@@ -488,6 +508,8 @@ __global__ void __launch_bounds__(kSegThreads, 1) seg_gemm_kernel(const SegGemmA
     grid_barrier(a.gb, 30 + a.finish);
     if (a.finish == 2) {
         seg_finish_qkv(a.g[0], a.epi);
+    } else if (a.finish == 3) {
+        seg_finish_silu(a.g[0], a.out, a.n_out, a.ldo, a.off0);
     } else {
         seg_finish_bf16(a.g[0], a.out, a.n_out, a.ldo, a.off0);
         if (a.finish == 1) {

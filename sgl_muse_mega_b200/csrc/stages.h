@@ -279,7 +279,8 @@ struct SegBArgs {  // combine .. successor's qkv head
 struct SegGemmArgs {  // one GEMM stage (or pooler + router) as a kernel of its own
     SegGemm g[2];
     int n_gemm;
-    int finish;                 // 0: bf16 push of g[0]; 1: the same plus f32 logits and routing scores of g[1]; 2: qkv row ops
+    int finish;                 // 0: bf16 push of g[0]; 1: the same plus f32 logits and routing scores of g[1]; 2: qkv row ops;
+                                // 3: SwiGLU of g[0]'s [gate | up] columns
     bf16* out[kMaxRanks];
     int n_out;
     long long ldo, off0;
