@@ -1,0 +1,77 @@
+"""One fused DFlash2 decode iteration on a rank: the draft's launches, then the target's verify step and greedy accept.
+
+Mirrors the reference's ``sm103/dflash/iteration.py:670-684`` (``Iteration.launches``: draft_entry, draft_qkv, the draft
+layers, draft_head, then the verify launches and verify_accept) and ``runtime/iteration.py:384-412`` (``Fused.step``: one
+CUDA graph replay per step). Everything a step needs from the previous one lives on the device:
+
+    accept -> step words (P, anchor, commit)            -> the draft's positions, anchor row, context rows
+    verify -> the capture layers' output residuals      -> the draft's fc input rows
+    draft  -> the verify window's ids [anchor, drafts]  -> the target entry's ids
+
+so ``step()`` is a graph replay with no host input.
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from ..stack import Stack
+from .draft import DraftRank
+from .weights import DraftConfig, DraftWeights, TargetShared
+
+
+class Iteration:
+    def __init__(self, stack: Stack, dcfg: DraftConfig, dw: DraftWeights, *, capture: Optional[Sequence[int]] = None,
+                 pool_rows: int = 4096, rope_rows: Optional[int] = None, peers: Optional[Sequence] = None, exchange=None,
+                 wait_budget: int = 0):  # fmt: skip
+        """``stack``: the bound target stack of this rank (greedy tail). ``capture``: indices into ``stack.layers`` whose
+        output residual feeds the draft (default: ``dcfg.capture`` relative to the stack's first layer). ``peers`` /
+        ``exchange``: the draft's exchange buffers of a world of several processes (``DraftRank.bind``)."""
+        assert stack.bound and stack.greedy, "the iteration ends with the greedy accept of a bound stack"
+        cfg = stack.case.cfg
+        assert (dcfg.hidden, dcfg.vocab) == (cfg.hidden, cfg.vocab), "the draft borrows the target's embedding and lm_head"
+        first = stack.case.first_layer
+        capture = list(capture) if capture is not None else [c - first for c in dcfg.capture]
+        assert len(capture) == dcfg.features and all(0 <= c < len(stack.layers) for c in capture), capture
+        self.stack, self.capture = stack, capture
+        caps = [stack.layers[c].o["stream_out"] for c in capture]
+        t = TargetShared(stack.embed, stack.lm_head_w)
+        rope_rows = rope_rows or stack.kv_rows
+        self.draft = DraftRank(
+            dcfg, dw, t, stack.rank, cfg.tp, stack.device, rows=stack.case.rows, pool_rows=pool_rows, rope_rows=rope_rows,
+            lib=stack.lib, module=stack.module, words=stack.accept.words, caps=caps, verify_ids=stack.tokens, exchange=exchange,
+            wait_budget=wait_budget,
+        )  # fmt: skip
+        self.draft.bind(peers)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+
+    @property
+    def kernels(self) -> int:
+        return self.draft.kernels() + self.stack.kernels
+
+    def launch_all(self, s: int, pdl: bool = True) -> None:
+        self.draft.launch_all(s, pdl)
+        self.stack.launch_all(s, pdl)
+
+    def capture_graph(self, pdl: bool = True, warmup: bool = True) -> torch.cuda.CUDAGraph:
+        dev = self.stack.device
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            if warmup:
+                self.launch_all(side.cuda_stream, pdl)
+                side.synchronize()
+            with torch.cuda.graph(g, stream=side):
+                self.launch_all(torch.cuda.current_stream(dev).cuda_stream, pdl)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self.graph = g
+        return g
+
+    def step(self) -> None:
+        self.graph.replay()
+
+    def statuses(self) -> list:
+        return self.draft.statuses() + self.stack.statuses()

@@ -92,3 +92,39 @@ def draft_case(cfg: DraftConfig, ranks: int, rows: int, pos: int, commit: int, s
     hist_v = [_draw(g, (n_hist, cfg.kv_heads, cfg.head_dim), 1.0) for _ in range(cfg.layers)]
     return DraftCase(cfg, ranks, rows, w, t, [shard(cfg, w, t, r, ranks) for r in range(ranks)], caps, anchor, pos, commit,
                      hist_k, hist_v)  # fmt: skip
+
+
+def device_shard(cfg: DraftConfig, rank: int, ranks: int, device, seed: int = 0) -> DraftWeights:
+    """One rank's shard drawn directly on the device at the same scales (timing runs at the public size: the unsharded
+    model is 9.8 GB and is never materialised; shards of different ranks are independent draws, the replicated tensors are
+    keyed by the seed alone)."""
+    g = torch.Generator(device=device).manual_seed(4000 + seed * 16 + rank)
+    gr = torch.Generator(device=device).manual_seed(5000 + seed)  # replicated tensors: the same on every rank
+    h, d = cfg.hidden, cfg.head_dim
+    q, kv, inter = cfg.q_rank(ranks), cfg.kv_rank(ranks), cfg.inter // ranks
+
+    def draw(gen, shape, std):
+        return (torch.randn(shape, generator=gen, device=device) * std).to(torch.bfloat16)
+
+    def near_one(n):
+        return (1 + draw(gr, (n,), 0.1).float()).to(torch.bfloat16)
+
+    def conv():
+        base = draw(gr, (2, cfg.conv_taps, h), 0.05)
+        base[:, 0] += 1
+        return ConvWeights(base, draw(gr, (cfg.coeffs, h), 0.01))
+
+    layers = [
+        LayerWeights(
+            input_norm=near_one(h), post_norm=near_one(h), q_norm=near_one(d), k_norm=near_one(d),
+            qkv=draw(g, ((q + 2 * kv) * d, h), h**-0.5), o=draw(g, (h, q * d), (cfg.q_heads * d) ** -0.5),
+            gate_up=draw(g, (2 * inter, h), h**-0.5), down=draw(g, (h, inter), cfg.inter**-0.5),
+            attn_conv=conv(), mlp_conv=conv(),
+        )
+        for _ in range(cfg.layers)
+    ]  # fmt: skip
+    return DraftWeights(
+        layers, fc=draw(g, (h // ranks, cfg.features * h), (cfg.features * h) ** -0.5), hidden_norm=near_one(h), norm=near_one(h),
+        pred_codebook=draw(gr, (cfg.vocab, cfg.selector_rank), 0.05), succ_codebook=draw(gr, (cfg.vocab, cfg.selector_rank), 0.05),
+        hidden_proj=draw(gr, (cfg.selector_rank, h), 0.01),
+    )  # fmt: skip
