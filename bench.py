@@ -47,6 +47,7 @@ def parse():
                     help="dense stages: 0 item-engine GEMM kernels, 1 two persistent segment kernels, 2 cluster split-K GEMMs")
     ap.add_argument("--decode-layers", type=int, default=62, help="layers of the whole-step leg (0: skip it)")
     ap.add_argument("--decode-steps", type=int, default=24)
+    ap.add_argument("--no-draft", action="store_true", help="whole-step leg without the DFlash2 draft (ids from the host)")
     ap.add_argument("--accept", type=int, default=5, help="forced accept length of the whole-step leg (5 drafts + the bonus = 6 tokens a step)")
     return ap.parse_args()
 
@@ -213,6 +214,20 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
                  accept_override=forced, wait_budget=1 << 25)  # fmt: skip
     peers = S.connect_world(st) if world > 1 else st.bind()
     s = stream.cuda_stream
+    # the DFlash2 draft at its public size (this rank's TP slice, synthetic weights drawn on the device): with it the step
+    # is the whole fused iteration - draft, verify, accept - and needs no ids from the host
+    it = None
+    if not args.no_draft:
+        from sgl_muse_mega_b200.muse_spark.b200.dflash import synthetic as dsyn
+        from sgl_muse_mega_b200.muse_spark.b200.dflash.iteration import Iteration
+        from sgl_muse_mega_b200.muse_spark.b200.dflash.weights import DraftConfig
+
+        dcfg = DraftConfig()
+        capture = list(dcfg.capture) if n_layers == cfg.layers else [min(n_layers - 1, i * n_layers // 5) for i in range(5)]
+        dw = dsyn.device_shard(dcfg, tp_rank, cfg.tp, device, args.seed)
+        kw = dict(capture=capture, pool_rows=4096, rope_rows=kv_rows + rows, wait_budget=1 << 25)
+        it = Iteration.connect(st, peers, dcfg, dw, **kw) if world > 1 else Iteration(st, dcfg, dw, **kw)
+    step = it.step if it is not None else st.step
 
     def barrier():
         torch.cuda.synchronize()
@@ -230,23 +245,27 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
     gen = torch.Generator().manual_seed(args.seed)
     h_tokens = torch.randint(0, model.vocab, (rows,), generator=gen).pin_memory()
     h_words = torch.zeros(8, dtype=torch.int64).pin_memory()
+    h_forced = torch.tensor([args.accept], dtype=torch.int32).pin_memory()
     with torch.cuda.stream(stream):
         st.tokens.copy_(h_tokens)
         st.feeds.launch(s)
     barrier()
     with torch.cuda.stream(stream):
-        st.capture(pdl=True, warmup=True)
+        if it is not None:
+            it.capture_graph(pdl=True, warmup=True)
+        else:
+            st.capture(pdl=True, warmup=True)
     barrier()
     # ---- graph replays, inputs resident ----
     with torch.cuda.stream(stream):
         for _ in range(W):
-            st.step()
+            step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         e0.record(stream)
         for _ in range(K):
-            st.step()
+            step()
         e1.record(stream)
     barrier()
     step_ms = max_over_ranks(e0.elapsed_time(e1) / K)
@@ -264,11 +283,30 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
         e1.record(stream)
     barrier()
     layer_us = max_over_ranks(e0.elapsed_time(e1) / (reps * n_layers) * 1e3)
+    # ---- the draft alone (its launch list under programmatic dependent launch) ----
+    draft = None
+    if it is not None:
+        with torch.cuda.stream(stream):
+            it.draft.launch_all(s, True)
+        barrier()
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(reps):
+                it.draft.launch_all(s, True)
+            e1.record(stream)
+        barrier()
+        draft_us = max_over_ranks(e0.elapsed_time(e1) / reps * 1e3)
+        dbytes = draft_bytes(it.draft.cfg, cfg.tp, rows)
+        draft = {"us_per_step": draft_us, "kernels": it.draft.kernels(), "bytes": dbytes,
+                 "roofline_frac": dbytes / (draft_us * 1e-6) / 1e9 / peaks()[0], "config": "DFlash2 public config, TP8 slice"}
     # ---- end to end: ids from pinned host memory, step words back ----
     def e2e_step():
         with torch.cuda.stream(stream):
-            st.tokens.copy_(h_tokens, non_blocking=True)
-            st.step()
+            if it is None:
+                st.tokens.copy_(h_tokens, non_blocking=True)
+            else:  # the ids come from the draft; the host's per-step input is the accept control word
+                forced.copy_(h_forced, non_blocking=True)
+            step()
             h_words.copy_(st.accept.words, non_blocking=True)
         stream.synchronize()
 
@@ -292,14 +330,28 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
     out = {
         "layers": n_layers, "accept_len": args.accept, "tokens_per_step": commit, "ms_per_step": step_ms,
         "tok_s": commit / (step_ms * 1e-3), "e2e_ms_per_step": e2e_ms, "e2e_tok_s": commit / (e2e_ms * 1e-3),
-        "h2d_bytes_per_step": h_tokens.numel() * 8, "d2h_bytes_per_step": 64,
-        "layer_only_us": layer_us, "kernels_per_step": st.kernels,
+        "h2d_bytes_per_step": h_tokens.numel() * 8 if it is None else 4, "d2h_bytes_per_step": 64,
+        "layer_only_us": layer_us, "kernels_per_step": it.kernels if it is not None else st.kernels,
         "bytes_per_step": int(sum(b["total"] for b in byts)), "mean_distinct_experts": sum(d_list) / len(d_list),
         "present_ranks": world if world > 1 else 1, "model_ranks": cfg.tp,
-        "draft": "not in the step: the draft model's kernels are not built yet; ids come from the host",
+        "draft": draft if draft is not None else "not in the step (--no-draft): ids come from the host",
     }  # fmt: skip
+    if it is not None:
+        bad = it.statuses()
+        assert bad == [], f"device status of the draft: {bad}"
     del peers
     return out, st
+
+
+def draft_bytes(dcfg, ranks: int, rows: int) -> int:
+    """Algorithmic HBM bytes of one draft step on one rank: every weight once (bf16), the attention window's K / V."""
+    h, d = dcfg.hidden, dcfg.head_dim
+    qh, kvh, inter = dcfg.q_heads // ranks, dcfg.kv_heads // ranks, dcfg.inter // ranks
+    per_layer = 2 * dcfg.coeffs * h + (qh + 2 * kvh) * d * h + h * qh * d + 2 * inter * h + h * inter
+    kv = dcfg.layers * 2 * (dcfg.window_left + rows) * kvh * d
+    head = (dcfg.vocab // ranks) * h + dcfg.selector_rank * h + (rows - 1) * dcfg.vocab * 2  # lm_head shard, W_P, the f32 logits written + read (x2 bytes/2)
+    entry = (h // ranks) * dcfg.features * h + dcfg.layers * 2 * kvh * d * h
+    return 2 * (dcfg.layers * per_layer + kv + head + entry)
 
 
 # ---- GPU leg ----------------------------------------------------------------------------------------------------------

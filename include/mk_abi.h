@@ -282,6 +282,8 @@ typedef struct MkLmHeadBind {
     uint64_t status;               // i32 [16] or 0: a weight copy that never landed is recorded here (code 3), not trapped
     uint64_t flags;                // this rank's flag block and the peers' (as MkLayerBind); 0: no signalling
     uint64_t flags_peer[MKH_RANKS];
+    uint64_t ws;                   // 0, or ws_bytes of private scratch zeroed once: with hidden a multiple of 512 the GEMM then
+    int64_t ws_bytes;              // runs on the item engine (needs (hidden / 512) x 16 x n_out x 4 + 512 bytes)
 } MkLmHeadBind;
 int mk_lm_head_bind(MkModule* module, const MkLmHeadBind* bind, MkLaunch** out);
 

@@ -61,19 +61,43 @@ __global__ void __launch_bounds__(kRowThreads) dfeats_kernel(const DFeatsArgs a)
 }
 
 // ---- norm rows -------------------------------------------------------------------------------------------------------------
-// The all-reduced value of (row, ch): the ranks' bf16 partials summed in rank order in f32, rounded to bf16.
-__device__ __forceinline__ float ar_value(const DNormArgs& a, int row, int ch) {
-    float acc = __bfloat162float(a.ar[(size_t)row * a.H + ch]);
-    for (int r = 1; r < a.ranks; ++r) acc = __fadd_rn(acc, __bfloat162float(a.ar[((size_t)r * 16 + row) * a.H + ch]));
-    return bf16_round(acc);
+// One CTA per row, one thread per 8 consecutive channels (16-byte loads; H / 8 threads). A conv group spans a multiple of 8
+// channels, so a thread's channels share their dynamic coefficients.
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
+    const uint4 u = *(const uint4*)p;
+    const __nv_bfloat162* h = (const __nv_bfloat162*)&u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __low2float(h[i]);
+        v[2 * i + 1] = __high2float(h[i]);
+    }
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
+    uint4 u;
+    __nv_bfloat162* h = (__nv_bfloat162*)&u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *(uint4*)p = u;
+}
+// The all-reduced values of 8 channels of a row: the ranks' bf16 partials summed in rank order in f32, rounded to bf16.
+__device__ __forceinline__ void ar8(const DNormArgs& a, int row, int ch0, float (&x)[8]) {
+    load8(a.ar + (size_t)row * a.H + ch0, x);
+    for (int r = 1; r < a.ranks; ++r) {
+        float p[8];
+        load8(a.ar + ((size_t)r * 16 + row) * a.H + ch0, p);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = __fadd_rn(x[i], p[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = bf16_round(x[i]);
 }
 
-__global__ void __launch_bounds__(kRowThreads) dnorm_kernel(const DNormArgs a) {
+__global__ void __launch_bounds__(1024) dnorm_kernel(const DNormArgs a) {
     __shared__ double red[33];
     __shared__ long long s_tok;
     griddep_wait();
     xchg_wait(a.wait);
-    const int row = blockIdx.x, tid = threadIdx.x;
+    const int row = blockIdx.x, tid = threadIdx.x, ch0 = tid * 8;
     const bf16* src = a.x ? a.x + (size_t)row * a.H : nullptr;
     if (a.emb_ranks > 0) {
         if (tid == 0) {
@@ -88,61 +112,68 @@ __global__ void __launch_bounds__(kRowThreads) dnorm_kernel(const DNormArgs a) {
         __syncthreads();
         src = a.embed[s_tok / a.shard_rows] + (size_t)(s_tok % a.shard_rows) * a.H;
     }
-    constexpr int kPer = 8192 / kRowThreads;  // H <= 8192
-    float s[kPer];
-    double sq = 0.0;
-    const int per = a.H / kRowThreads;
-    const int taps_stride = a.groups;  // coeff row: [side][tap][group]
-#pragma unroll
-    for (int j = 0; j < kPer; ++j) {
-        if (j >= per) break;
-        const int ch = tid + j * kRowThreads;
-        float x;
-        if (a.ar != nullptr) {
-            x = ar_value(a, row, ch);
-            if (a.coeff != nullptr) {  // the conv's side 1 over the all-reduced rows
-                const int g = ch / (a.H / a.groups);
-                const bf16* c = a.coeff + (size_t)row * 4 * a.groups + 2 * taps_stride;
-                const bf16* b1 = a.base + (size_t)2 * a.H;
-                float out = __fmul_rn(__fadd_rn(__bfloat162float(b1[ch]), __bfloat162float(c[g])), x);
-                if (row > 0) {
-                    const float xp = ar_value(a, row - 1, ch);
-                    out = __fadd_rn(out, __fmul_rn(__fadd_rn(__bfloat162float(b1[a.H + ch]), __bfloat162float(c[taps_stride + g])), xp));
-                }
-                x = bf16_round(out);
+    float x[8];
+    if (a.ar != nullptr) {
+        ar8(a, row, ch0, x);
+        if (a.coeff != nullptr) {  // the conv's side 1 over the all-reduced rows; coeff row: [side][tap][group]
+            const int g = ch0 / (a.H / a.groups);
+            const bf16* c = a.coeff + (size_t)row * 4 * a.groups + 2 * a.groups;
+            const float d0 = __bfloat162float(c[g]), d1 = __bfloat162float(c[a.groups + g]);
+            float b0[8], b1[8], xp[8];
+            load8(a.base + (size_t)2 * a.H + ch0, b0);
+            if (row > 0) {
+                load8(a.base + (size_t)3 * a.H + ch0, b1);
+                ar8(a, row - 1, ch0, xp);
             }
-        } else {
-            x = __bfloat162float(src[ch]);
-        }
-        if (a.x_out != nullptr) a.x_out[(size_t)row * a.H + ch] = __float2bfloat16_rn(x);
-        const float v = a.residual ? __fadd_rn(x, __bfloat162float(a.residual[(size_t)row * a.H + ch])) : x;
-        s[j] = v;
-        sq += (double)v * (double)v;
-    }
-    const float ms = (float)(block_sum_d(sq, red) / (double)a.H);
-    const float r = rsqrt_exact(__fadd_rn(ms, a.eps));
 #pragma unroll
-    for (int j = 0; j < kPer; ++j) {
-        if (j >= per) break;
-        const int ch = tid + j * kRowThreads;
-        a.h[(size_t)row * a.H + ch] = __float2bfloat16_rn(__fmul_rn(__fmul_rn(s[j], r), __bfloat162float(a.w[ch])));
-        if (a.res_out != nullptr) a.res_out[(size_t)row * a.H + ch] = __float2bfloat16_rn(s[j]);
+            for (int i = 0; i < 8; ++i) {
+                float out = __fmul_rn(__fadd_rn(b0[i], d0), x[i]);
+                if (row > 0) out = __fadd_rn(out, __fmul_rn(__fadd_rn(b1[i], d1), xp[i]));
+                x[i] = bf16_round(out);
+            }
+        }
+    } else {
+        load8(src + ch0, x);
     }
+    if (a.x_out != nullptr) store8(a.x_out + (size_t)row * a.H + ch0, x);
+    double sq = 0.0;
+    if (a.residual != nullptr) {
+        float r[8];
+        load8(a.residual + (size_t)row * a.H + ch0, r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = __fadd_rn(x[i], r[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sq += (double)x[i] * (double)x[i];
+    const float ms = (float)(block_sum_d(sq, red) / (double)a.H);
+    const float rs = rsqrt_exact(__fadd_rn(ms, a.eps));
+    float w[8], h[8];
+    load8(a.w + ch0, w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) h[i] = __fmul_rn(__fmul_rn(x[i], rs), w[i]);
+    store8(a.h + (size_t)row * a.H + ch0, h);
+    if (a.res_out != nullptr) store8(a.res_out + (size_t)row * a.H + ch0, x);
 }
 
 // ---- grouped conv, side 0 -----------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kRowThreads) dconv_kernel(const DConvArgs a) {
+__global__ void __launch_bounds__(1024) dconv_kernel(const DConvArgs a) {
     griddep_wait();
-    const int row = blockIdx.x, per_group = a.H / a.groups;
+    const int row = blockIdx.x, ch0 = threadIdx.x * 8, g = ch0 / (a.H / a.groups);
     const bf16* c = a.coeff + (size_t)row * 4 * a.groups;  // side 0: taps at [0, groups) and [groups, 2 groups)
-    for (int ch = threadIdx.x; ch < a.H; ch += kRowThreads) {
-        const int g = ch / per_group;
-        float out = __fmul_rn(__fadd_rn(__bfloat162float(a.base[ch]), __bfloat162float(c[g])), __bfloat162float(a.h[(size_t)row * a.H + ch]));
-        if (row > 0)
-            out = __fadd_rn(out, __fmul_rn(__fadd_rn(__bfloat162float(a.base[a.H + ch]), __bfloat162float(c[a.groups + g])),
-                                           __bfloat162float(a.h[(size_t)(row - 1) * a.H + ch])));
-        a.out[(size_t)row * a.H + ch] = __float2bfloat16_rn(out);
+    const float d0 = __bfloat162float(c[g]), d1 = __bfloat162float(c[a.groups + g]);
+    float b0[8], b1[8], x[8], xp[8], out[8];
+    load8(a.base + ch0, b0);
+    load8(a.h + (size_t)row * a.H + ch0, x);
+    if (row > 0) {
+        load8(a.base + a.H + ch0, b1);
+        load8(a.h + (size_t)(row - 1) * a.H + ch0, xp);
     }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        out[i] = __fmul_rn(__fadd_rn(b0[i], d0), x[i]);
+        if (row > 0) out[i] = __fadd_rn(out[i], __fmul_rn(__fadd_rn(b1[i], d1), xp[i]));
+    }
+    store8(a.out + (size_t)row * a.H + ch0, out);
 }
 
 // ---- head norm + neox RoPE -----------------------------------------------------------------------------------------------------
@@ -223,22 +254,21 @@ __global__ void __launch_bounds__(kRowThreads) dctx_kv_kernel(const DCtxKvArgs a
 }
 
 // ---- non-causal sliding-window attention, head dim 128 -----------------------------------------------------------------------------
-// grid (nsplit, kvh): a CTA scores the M x G query rows of one kv head against one block of 64 key positions and leaves
-// (max, sum, unnormalised output) per row; the merge kernel combines the blocks. f32 FMAs from shared memory: the block is
-// 2 x 128 x 64 x 128 multiply-adds, and at most 34 blocks x kv heads run side by side.
-constexpr int kAQ = 128;        // query rows per kv head (M x G <= 128)
+// grid (nsplit, kvh): a CTA scores the M x G query rows of one kv head (at most 128; 16 per warp) against one block of 64
+// key positions and leaves (max, sum, unnormalised output) per row; the merge kernel combines the blocks. Tensor cores
+// through mma.sync m16n8k16 (bf16, f32 accumulate): S = Q K^T with K row-major as the column operand, then the
+// probabilities, rounded to bf16, re-used in registers as the row operand of P V with V transposed in shared memory.
+// Rows are padded by 8 elements so that a fragment load's 32 lanes fall into 32 distinct banks.
+constexpr int kAQ = 128;  // query rows per kv head (M x G <= 128)
 constexpr int kAKeys = kDraftKeysPerSplit;
-constexpr int kAKt = kAKeys + 4;  // padded row of the transposed key tile
-constexpr size_t kAttnSmem = ((size_t)kAQ * 128 + 128 * kAKt + (size_t)kAKeys * 128 + (size_t)kAQ * kAKeys + 2 * kAQ) * 4;
+constexpr int kAQs = 128 + 8, kAVs = kAKeys + 8;  // row strides (elements) of Q / K and of V^T
+constexpr size_t kAttnSmem = ((size_t)kAQ * kAQs + (size_t)kAKeys * kAQs + (size_t)128 * kAVs) * 2;
 
 __global__ void __launch_bounds__(256, 1) dattn_split_kernel(const DAttnArgs a) {
-    extern __shared__ __align__(16) float sm[];
-    float* Qs = sm;                     // [128][128]
-    float* Kt = Qs + kAQ * 128;         // [128 d][68]
-    float* Vs = Kt + 128 * kAKt;        // [64][128]
-    float* Ps = Vs + kAKeys * 128;      // [128][64]
-    float* ms = Ps + kAQ * kAKeys;      // [128]
-    float* ls = ms + kAQ;
+    extern __shared__ __align__(16) unsigned char sm_raw[];
+    bf16* Qs = (bf16*)sm_raw;           // [128][136]
+    bf16* Ks = Qs + kAQ * kAQs;         // [64][136]
+    bf16* Vt = Ks + kAKeys * kAQs;      // [128 d][72]
     griddep_wait();
     const int tid = threadIdx.x, split = blockIdx.x, h = blockIdx.y;
     const int G = a.qh / a.kvh, R = a.M * G;
@@ -253,113 +283,122 @@ __global__ void __launch_bounds__(256, 1) dattn_split_kernel(const DAttnArgs a) 
         }
         return;
     }
-    // Q rows r = b G + g of this kv head
-    for (int i = tid; i < kAQ * 64; i += 256) {
-        const int r = i >> 6, d2 = i & 63;
-        float2 v = make_float2(0.f, 0.f);
+    // Q rows r = b G + g of this kv head (rows past R are zero), 16 bytes a thread
+    for (int i = tid; i < kAQ * 16; i += 256) {
+        const int r = i >> 4, c = i & 15;
+        uint4 v = make_uint4(0, 0, 0, 0);
         if (r < R) {
             const int b = r / G, g = r - b * G;
-            const __nv_bfloat162 q = *(const __nv_bfloat162*)(a.q + ((size_t)b * a.qh + h * G + g) * 128 + 2 * d2);
-            v = make_float2(__low2float(q), __high2float(q));
+            v = *(const uint4*)(a.q + ((size_t)b * a.qh + h * G + g) * 128 + c * 8);
         }
-        *(float2*)(Qs + r * 128 + 2 * d2) = v;
+        *(uint4*)(Qs + r * kAQs + c * 8) = v;
     }
-    for (int i = tid; i < kAKeys * 64; i += 256) {
-        const int kk = i >> 6, d2 = i & 63;
+    for (int i = tid; i < kAKeys * 16; i += 256) {
+        const int kk = i >> 4, c = i & 15;
         const long long pk = key0 + kk;
-        float2 kf = make_float2(0.f, 0.f), vf = make_float2(0.f, 0.f);
+        uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
         if (pk <= hi) {
             const size_t slot = (size_t)(pk % a.pool_rows);
-            const __nv_bfloat162 k2 = *(const __nv_bfloat162*)(a.k_pool + (slot * a.kvh + h) * 128 + 2 * d2);
-            const __nv_bfloat162 v2 = *(const __nv_bfloat162*)(a.v_pool + (slot * a.kvh + h) * 128 + 2 * d2);
-            kf = make_float2(__low2float(k2), __high2float(k2));
-            vf = make_float2(__low2float(v2), __high2float(v2));
+            kv = *(const uint4*)(a.k_pool + (slot * a.kvh + h) * 128 + c * 8);
+            vv = *(const uint4*)(a.v_pool + (slot * a.kvh + h) * 128 + c * 8);
         }
-        Kt[(2 * d2) * kAKt + kk] = kf.x;
-        Kt[(2 * d2 + 1) * kAKt + kk] = kf.y;
-        *(float2*)(Vs + kk * 128 + 2 * d2) = vf;
+        *(uint4*)(Ks + kk * kAQs + c * 8) = kv;
+        const bf16* ve = (const bf16*)&vv;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) Vt[(c * 8 + e) * kAVs + kk] = ve[e];
     }
     __syncthreads();
-    const int ty = tid >> 4, tx = tid & 15;
-    {
-        float acc[8][4];
+    const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int r0 = warp * 16 + g, r1 = r0 + 8;
+    // S = Q K^T: 8 key tiles of 8, 8 steps of 16 over the head dimension
+    float sc[8][4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+    for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-        for (int d = 0; d < 128; ++d) {
-            const float4 k4 = *(const float4*)(Kt + d * kAKt + tx * 4);
+        for (int i = 0; i < 4; ++i) sc[nt][i] = 0.f;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float q = Qs[(ty * 8 + i) * 128 + d];
-                acc[i][0] = fmaf(q, k4.x, acc[i][0]);
-                acc[i][1] = fmaf(q, k4.y, acc[i][1]);
-                acc[i][2] = fmaf(q, k4.z, acc[i][2]);
-                acc[i][3] = fmaf(q, k4.w, acc[i][3]);
-            }
-        }
-        const float scale = 0.08838834764831845f;  // 128^-0.5
+    for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t a0 = *(const uint32_t*)(Qs + r0 * kAQs + ks * 16 + 2 * t), a1 = *(const uint32_t*)(Qs + r1 * kAQs + ks * 16 + 2 * t);
+        const uint32_t a2 = *(const uint32_t*)(Qs + r0 * kAQs + ks * 16 + 8 + 2 * t), a3 = *(const uint32_t*)(Qs + r1 * kAQs + ks * 16 + 8 + 2 * t);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int r = ty * 8 + i;
-            const long long pq = P + r / G;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const long long pk = key0 + tx * 4 + j;
-                const bool seen = r < R && pk <= hi && pk >= pq - a.left && pk <= pq + a.left;
-                Ps[r * kAKeys + tx * 4 + j] = seen ? acc[i][j] * scale : -INFINITY;
-            }
+        for (int nt = 0; nt < 8; ++nt) {
+            const uint32_t b0 = *(const uint32_t*)(Ks + (nt * 8 + g) * kAQs + ks * 16 + 2 * t);
+            const uint32_t b1 = *(const uint32_t*)(Ks + (nt * 8 + g) * kAQs + ks * 16 + 8 + 2 * t);
+            mma_bf16_16816(sc[nt], a0, a1, a2, a3, b0, b1);
         }
     }
-    __syncthreads();
-    {
-        const int warp = tid >> 5, lane = tid & 31;
-        for (int r = warp; r < kAQ; r += 8) {
-            const float s0 = Ps[r * kAKeys + lane], s1 = Ps[r * kAKeys + 32 + lane];
-            const float m = warp_max(fmaxf(s0, s1));
-            const float p0 = m == -INFINITY ? 0.f : expf(s0 - m), p1 = m == -INFINITY ? 0.f : expf(s1 - m);
-            const float l = warp_sum(p0 + p1);
-            Ps[r * kAKeys + lane] = p0;
-            Ps[r * kAKeys + 32 + lane] = p1;
-            if (lane == 0) {
-                ms[r] = m;
-                ls[r] = l;
+    // mask, row max, probabilities (a row's 64 scores sit in the 4 lanes of its quad)
+    const float scale = 0.08838834764831845f;  // 128^-0.5
+    const long long pq0 = P + r0 / G, pq1 = P + r1 / G;
+    float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const long long pk = key0 + nt * 8 + 2 * t + (i & 1);
+            const bool top = i < 2;
+            const long long pq = top ? pq0 : pq1;
+            const bool seen = (top ? r0 : r1) < R && pk <= hi && pk >= pq - a.left && pk <= pq + a.left;
+            const float v = seen ? sc[nt][i] * scale : -INFINITY;
+            sc[nt][i] = v;
+            if (top) m0 = fmaxf(m0, v);
+            else m1 = fmaxf(m1, v);
+        }
+    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 1));
+    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
+    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 1));
+    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
+    float l0 = 0.f, l1 = 0.f;
+    uint32_t pa[8][2];  // probabilities as bf16 pairs: [key tile][row r0 | row r1]
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+        const float p0 = m0 == -INFINITY ? 0.f : expf(sc[nt][0] - m0), p1 = m0 == -INFINITY ? 0.f : expf(sc[nt][1] - m0);
+        const float p2 = m1 == -INFINITY ? 0.f : expf(sc[nt][2] - m1), p3 = m1 == -INFINITY ? 0.f : expf(sc[nt][3] - m1);
+        const __nv_bfloat162 q0 = __floats2bfloat162_rn(p0, p1), q1 = __floats2bfloat162_rn(p2, p3);
+        // the sums run over the rounded probabilities, the values the output is built from
+        l0 += __low2float(q0) + __high2float(q0);
+        l1 += __low2float(q1) + __high2float(q1);
+        pa[nt][0] = *(const uint32_t*)&q0;
+        pa[nt][1] = *(const uint32_t*)&q1;
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    // O = P V: 4 steps of 16 keys, 16 tiles of 8 over the head dimension, in two halves to bound the registers
+    float* o0 = wsb + (size_t)r0 * 132;
+    float* o1 = wsb + (size_t)r1 * 132;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        float oc[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) oc[nt][i] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                const int d = (half * 8 + nt) * 8 + g;
+                const uint32_t b0 = *(const uint32_t*)(Vt + d * kAVs + j * 16 + 2 * t), b1 = *(const uint32_t*)(Vt + d * kAVs + j * 16 + 8 + 2 * t);
+                mma_bf16_16816(oc[nt], pa[2 * j][0], pa[2 * j][1], pa[2 * j + 1][0], pa[2 * j + 1][1], b0, b1);
             }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            const int d = (half * 8 + nt) * 8 + 2 * t;
+            if (r0 < R) *(float2*)(o0 + 4 + d) = make_float2(oc[nt][0], oc[nt][1]);
+            if (r1 < R) *(float2*)(o1 + 4 + d) = make_float2(oc[nt][2], oc[nt][3]);
         }
     }
-    __syncthreads();
-    {
-        float acc[8][8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
-        for (int kk = 0; kk < kAKeys; ++kk) {
-            const float4 va = *(const float4*)(Vs + kk * 128 + tx * 4), vb = *(const float4*)(Vs + kk * 128 + 64 + tx * 4);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float p = Ps[(ty * 8 + i) * kAKeys + kk];
-                acc[i][0] = fmaf(p, va.x, acc[i][0]);
-                acc[i][1] = fmaf(p, va.y, acc[i][1]);
-                acc[i][2] = fmaf(p, va.z, acc[i][2]);
-                acc[i][3] = fmaf(p, va.w, acc[i][3]);
-                acc[i][4] = fmaf(p, vb.x, acc[i][4]);
-                acc[i][5] = fmaf(p, vb.y, acc[i][5]);
-                acc[i][6] = fmaf(p, vb.z, acc[i][6]);
-                acc[i][7] = fmaf(p, vb.w, acc[i][7]);
-            }
+    if (t == 0) {
+        if (r0 < R) {
+            o0[0] = m0;
+            o0[1] = l0;
         }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int r = ty * 8 + i;
-            if (r >= R) continue;
-            float* o = wsb + (size_t)r * 132;
-            if (tx == 0) {
-                o[0] = ms[r];
-                o[1] = ls[r];
-            }
-            *(float4*)(o + 4 + tx * 4) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-            *(float4*)(o + 4 + 64 + tx * 4) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+        if (r1 < R) {
+            o1[0] = m1;
+            o1[1] = l1;
         }
     }
 }
@@ -409,9 +448,11 @@ __device__ __forceinline__ float key_value(unsigned long long k) {
 }
 __device__ __forceinline__ unsigned key_id(unsigned long long k) { return 0xFFFFFFFFu - (unsigned)(k & 0xFFFFFFFFull); }
 
-// 16 rounds of block arg-max over the threads' register-held keys (PER per thread; 0 = empty). out[round] = the key.
+// The 16 largest of the block's register-held keys (PER per thread; 0 = empty) -> out[0..16), descending. Each warp
+// selects its own 16 with shuffles only, then warp 0 selects among the 8 x 16 survivors: two block barriers in all.
+// `wl` holds 128 keys of shared memory.
 template <int PER>
-__device__ __forceinline__ void block_top16(unsigned long long (&k)[PER], unsigned long long* out, unsigned long long* red) {
+__device__ __forceinline__ void block_top16(unsigned long long (&k)[PER], unsigned long long* out, unsigned long long* wl) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int round = 0; round < kDraftTopK; ++round) {
         unsigned long long best = 0;
@@ -422,24 +463,40 @@ __device__ __forceinline__ void block_top16(unsigned long long (&k)[PER], unsign
             const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
             best = other > best ? other : best;
         }
-        __syncthreads();
-        if (lane == 0) red[warp] = best;
-        __syncthreads();
-        unsigned long long win = 0;
-#pragma unroll
-        for (int w = 0; w < kRowThreads / 32; ++w) win = red[w] > win ? red[w] : win;
-        if (win != 0) {
+        if (best != 0) {
 #pragma unroll
             for (int j = 0; j < PER; ++j)
-                if (k[j] == win) k[j] = 0;
+                if (k[j] == best) k[j] = 0;
         }
-        if (threadIdx.x == 0) out[round] = win;
+        if (lane == 0) wl[warp * kDraftTopK + round] = best;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        unsigned long long m[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) m[j] = wl[lane + 32 * j];
+        for (int round = 0; round < kDraftTopK; ++round) {
+            unsigned long long best = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) best = m[j] > best ? m[j] : best;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+                best = other > best ? other : best;
+            }
+            if (best != 0) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (m[j] == best) m[j] = 0;
+            }
+            if (lane == 0) out[round] = best;
+        }
     }
     __syncthreads();
 }
 
 __global__ void __launch_bounds__(kRowThreads) dtopk_kernel(const DTopkArgs a) {
-    __shared__ unsigned long long red[kRowThreads / 32];
+    __shared__ unsigned long long red[(kRowThreads / 32) * kDraftTopK];
     griddep_wait();
     xchg_wait(a.wait);
     const int chunk = blockIdx.x, row = blockIdx.y;
@@ -471,9 +528,11 @@ __device__ __forceinline__ void merge_row(const unsigned long long* keys, int nc
 }
 
 __global__ void __launch_bounds__(kRowThreads) dlattice_kernel(const DLatticeArgs a) {
-    __shared__ unsigned long long red[kRowThreads / 32];
+    __shared__ unsigned long long red[(kRowThreads / 32) * kDraftTopK];
     __shared__ unsigned long long s_cur[kDraftTopK], s_prev[kDraftTopK];
     __shared__ float s_hid[512];
+    __shared__ unsigned s_A[kDraftTopK][257], s_S[kDraftTopK][257];  // codebook rows as bf16 pairs, padded against bank conflicts
+    __shared__ long long s_pred[kDraftTopK];
     __shared__ float s_unary[kDraftTopK];
     __shared__ unsigned s_last;
     griddep_wait();
@@ -489,20 +548,32 @@ __global__ void __launch_bounds__(kRowThreads) dlattice_kernel(const DLatticeArg
         a.unary[(size_t)e * kDraftTopK + tid] = u;
     }
     __syncthreads();
-    {
-        const int p = tid >> 4, c = tid & 15;
-        long long pred = e == 0 ? a.words[kWordAnchor] : (long long)key_id(s_prev[p]);
+    if (tid < kDraftTopK) {
+        long long pred = e == 0 ? a.words[kWordAnchor] : (long long)key_id(s_prev[tid]);
         if (pred < 0 || pred >= a.vocab) {
             record_clamp(a.status, 430, pred);
             pred = pred < 0 ? 0 : a.vocab - 1;
         }
-        const bf16* A = a.pred + (size_t)pred * a.R;
-        const bf16* S = a.succ + (size_t)key_id(s_cur[c]) * a.R;
+        s_pred[tid] = pred;
+    }
+    __syncthreads();
+    {  // the 16 predecessor rows of A and the 16 candidate rows of S, coalesced
+        const int words = a.R / 2;
+        for (int i = tid; i < kDraftTopK * words; i += kRowThreads) {
+            const int r = i / words, w = i - r * words;
+            s_A[r][w] = ((const unsigned*)(a.pred + (size_t)s_pred[r] * a.R))[w];
+            s_S[r][w] = ((const unsigned*)(a.succ + (size_t)key_id(s_cur[r]) * a.R))[w];
+        }
+    }
+    __syncthreads();
+    {
+        const int p = tid >> 4, c = tid & 15;
         double dot = 0.0;
-        for (int r = 0; r < a.R; r += 2) {
-            const __nv_bfloat162 av = *(const __nv_bfloat162*)(A + r), sv = *(const __nv_bfloat162*)(S + r);
+        for (int w = 0; w < a.R / 2; ++w) {
+            const unsigned au = s_A[p][w], su = s_S[c][w];
+            const __nv_bfloat162 av = *(const __nv_bfloat162*)&au, sv = *(const __nv_bfloat162*)&su;
             // the product A x hid is exact in f32 (two bf16 factors) and rounded to bf16 as the reference stores it
-            const float p0 = bf16_round(__fmul_rn(__low2float(av), s_hid[r])), p1 = bf16_round(__fmul_rn(__high2float(av), s_hid[r + 1]));
+            const float p0 = bf16_round(__fmul_rn(__low2float(av), s_hid[2 * w])), p1 = bf16_round(__fmul_rn(__high2float(av), s_hid[2 * w + 1]));
             dot += (double)p0 * (double)__low2float(sv) + (double)p1 * (double)__high2float(sv);
         }
         a.scores[((size_t)e * kDraftTopK + p) * kDraftTopK + c] = __fadd_rn(s_unary[c], __bfloat162float(__double2bfloat16(dot)));
@@ -603,10 +674,10 @@ cudaError_t dfeats_launch(const DFeatsArgs& a, cudaStream_t s, bool pdl) {
     return launch_d(dfeats_kernel, dim3(a.rows * a.n_cap), dim3(kRowThreads), 0, s, pdl, a);
 }
 cudaError_t dnorm_launch(const DNormArgs& a, cudaStream_t s, bool pdl) {
-    return launch_d(dnorm_kernel, dim3(a.M), dim3(kRowThreads), 0, s, pdl, a);
+    return launch_d(dnorm_kernel, dim3(a.M), dim3(a.H / 8), 0, s, pdl, a);
 }
 cudaError_t dconv_launch(const DConvArgs& a, cudaStream_t s, bool pdl) {
-    return launch_d(dconv_kernel, dim3(a.M), dim3(kRowThreads), 0, s, pdl, a);
+    return launch_d(dconv_kernel, dim3(a.M), dim3(a.H / 8), 0, s, pdl, a);
 }
 cudaError_t dqkv_rows_launch(const DQkvRowsArgs& a, cudaStream_t s, bool pdl) {
     const int warps = a.M * (a.qh + 2 * a.kvh);

@@ -783,6 +783,8 @@ static void logits_wait(XchgWait& w, uint64_t flags, int64_t contributors, int64
     w.stage = 100 + XP_LOGITS;
 }
 
+static int lm_head_on_engine(MkModule* module, const MkLmHeadBind* b, MkLaunch** out);  // draft_host.inc
+
 static MkLaunch* new_op_launch(MkModule* module, int kind) {
     MkLaunch* L = new (std::nothrow) MkLaunch();
     if (L == nullptr) return nullptr;
@@ -847,6 +849,7 @@ int mk_lm_head_bind(MkModule* module, const MkLmHeadBind* b, MkLaunch** out) {
     MK_REQUIRE(b->rank >= 0 && b->rank < MKH_RANKS && b->out_peer[b->rank] != 0, "out_peer[rank] (this rank's logits) is 0");
     MK_REQUIRE(b->n_out >= 1 && b->col0 >= 0 && b->col0 + b->n_out <= b->v_total, "columns [%lld, %lld) outside %lld", (long long)b->col0,
                (long long)(b->col0 + b->n_out), (long long)b->v_total);
+    if (b->ws != 0 && b->hidden % 512 == 0) return lm_head_on_engine(module, b, out);
     MkLaunch* L = new_op_launch(module, OP_GEMM_BF16);
     MK_REQUIRE(L != nullptr, "out of host memory");
     GemmArgs& g = L->op_gemm;

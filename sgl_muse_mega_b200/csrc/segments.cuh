@@ -281,6 +281,19 @@ __device__ __forceinline__ void seg_finish_silu(const SegGemm& g, bf16* const* o
     }
 }
 
+// out[m, off0 + n] = sum_ks part[ks][m][n] as f32 into every destination (the lm_head's gathered logits); all CTAs share the
+// work.
+__device__ __forceinline__ void seg_finish_f32_push(const SegGemm& g, bf16* const* out, int n_out, long long ldo, long long off0) {
+    const int nsplit = g.K / kChunkK;
+    const long long total = (long long)g.M * g.N;
+    for (long long i = (long long)blockIdx.x * kSegThreads + threadIdx.x; i < total; i += (long long)gridDim.x * kSegThreads) {
+        const int m = (int)(i / g.N), n = (int)(i - (long long)m * g.N);
+        float v = 0.f;
+        for (int ks = 0; ks < nsplit; ++ks) v += g.part[((size_t)ks * 16 + m) * g.N + n];
+        for (int d = 0; d < n_out; ++d) ((float*)out[d])[off0 + (long long)m * ldo + n] = v;
+    }
+}
+
 // logits[m, n] = sum_ks part[ks][m][n] (f32), by one CTA.
 __device__ __forceinline__ void seg_finish_f32_cta(const SegGemm& g, float* out) {
     const int nsplit = g.K / kChunkK;
@@ -510,6 +523,8 @@ __global__ void __launch_bounds__(kSegThreads, 1) seg_gemm_kernel(const SegGemmA
         seg_finish_qkv(a.g[0], a.epi);
     } else if (a.finish == 3) {
         seg_finish_silu(a.g[0], a.out, a.n_out, a.ldo, a.off0);
+    } else if (a.finish == 4) {
+        seg_finish_f32_push(a.g[0], a.out, a.n_out, a.ldo, a.off0);
     } else {
         seg_finish_bf16(a.g[0], a.out, a.n_out, a.ldo, a.off0);
         if (a.finish == 1) {

@@ -280,7 +280,7 @@ struct SegGemmArgs {  // one GEMM stage (or pooler + router) as a kernel of its 
     SegGemm g[2];
     int n_gemm;
     int finish;                 // 0: bf16 push of g[0]; 1: the same plus f32 logits and routing scores of g[1]; 2: qkv row ops;
-                                // 3: SwiGLU of g[0]'s [gate | up] columns
+                                // 3: SwiGLU of g[0]'s [gate | up] columns; 4: f32 push of g[0] (out holds float pointers)
     bf16* out[kMaxRanks];
     int n_out;
     long long ldo, off0;

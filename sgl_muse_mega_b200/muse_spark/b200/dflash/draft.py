@@ -224,3 +224,53 @@ class DraftWorld:
                         l.step(s, k, 1)
             if after is not None:
                 after(li)
+
+
+# ---- a world of one process per GPU -------------------------------------------------------------------------------------
+
+EXCHANGE = ("flags", "ctx_raw", "ar_attn", "ar_mlp", "gathered")
+
+
+def exchange_layout(cfg: DraftConfig, ranks: int, rows: int):
+    """The draft's exchange arena of one rank (depends on the model and the block only: every rank carves the same)."""
+    from ....common import symm
+
+    lay = symm.Layout()
+    lay.add("flags", (64,), torch.int32)
+    lay.add("ctx_raw", (rows, cfg.hidden), BF)
+    lay.add("ar_attn", (ranks, 16, cfg.hidden), BF)
+    lay.add("ar_mlp", (ranks, 16, cfg.hidden), BF)
+    lay.add("gathered", (rows - 1, cfg.vocab), torch.float32)
+    return lay
+
+
+class ArenaExchange:
+    """This rank's exchange buffers inside its arena (tensors), plus its embedding shard (the target stack's)."""
+
+    def __init__(self, arena, embed):
+        self.arena, self.embed = arena, embed
+        for name in EXCHANGE:
+            setattr(self, name, arena.tensor(name))
+
+
+class PeerExchange:
+    """A peer's exchange buffers by device address (its arena, mapped) and the address of its embedding shard."""
+
+    def __init__(self, arena, embed_ptr: int):
+        self.arena, self.embed = arena, embed_ptr
+        for name in EXCHANGE:
+            setattr(self, name, arena.ptr(name))
+
+
+def connect_exchange(arena, embed, peer_embed_ptrs: Sequence[Optional[int]], rank: int, ranks: int, group=None) -> tuple:
+    """Swaps the draft arenas' handles over ``torch.distributed`` -> (own ``ArenaExchange``, the peer list for
+    ``DraftRank.bind``: own entry included, None for ranks beyond the present world)."""
+    import torch.distributed as dist
+
+    from ....common import symm
+
+    n = dist.get_world_size(group)
+    arenas = symm.connect(arena, rank, n, group)
+    own = ArenaExchange(arena, embed)
+    peers = [own if i == rank else PeerExchange(a, peer_embed_ptrs[i]) for i, a in enumerate(arenas)] + [None] * (ranks - n)
+    return own, peers

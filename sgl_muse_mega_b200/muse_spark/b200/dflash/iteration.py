@@ -47,6 +47,21 @@ class Iteration:
         self.draft.bind(peers)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
 
+    @classmethod
+    def connect(cls, stack: Stack, stack_peers: Sequence, dcfg: DraftConfig, dw: DraftWeights, group=None, **kw) -> "Iteration":
+        """A world of one process per GPU: ``stack_peers`` is what ``stack.connect_world`` returned (the peers' arenas hold
+        their embedding shards); the draft's own exchange arena is allocated, swapped and mapped here."""
+        from ....common import symm
+        from . import draft as DR
+
+        ranks = stack.case.cfg.tp
+        arena = symm.Arena(stack.lib, DR.exchange_layout(dcfg, ranks, stack.case.rows), stack.device)
+        embeds = [None if p is None or p is stack else p.view.embed for p in stack_peers]
+        own, peers = DR.connect_exchange(arena, stack.embed, embeds, stack.rank, ranks, group)
+        it = cls(stack, dcfg, dw, peers=peers, exchange=own, **kw)
+        it.peers = peers  # the mappings live as long as the iteration launches
+        return it
+
     @property
     def kernels(self) -> int:
         return self.draft.kernels() + self.stack.kernels

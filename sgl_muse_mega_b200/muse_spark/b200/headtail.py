@@ -80,7 +80,7 @@ class LmHead:
     gathered logits (``gathered[r]`` is rank r's [rows, v_total] buffer; absent ranks are None)."""
 
     def __init__(self, lib: host.Library, module, *, w, x, gathered: Sequence[Optional[torch.Tensor]], rank: int,
-                 flags=None, flags_peer: Sequence = (), v_total: Optional[int] = None):  # fmt: skip
+                 flags=None, flags_peer: Sequence = (), v_total: Optional[int] = None, engine: bool = True):  # fmt: skip
         """``gathered``: tensors, or device addresses (then ``v_total`` is their row length). ``flags`` /
         ``flags_peer``: this rank's flag block and the peers' (present exactly where ``gathered`` is): the GEMM then
         signals the logits exchange on every rank it stored to."""
@@ -88,10 +88,15 @@ class LmHead:
         if v_total is None:
             v_total = gathered[rank].shape[1]
         self.status = _z(16, dtype=torch.int32, device=x.device)
+        # private scratch of the item engine (partial sums per 512-k chunk and its barrier word); shapes it does not tile
+        # run on the cluster split-K GEMM without scratch
+        ws_bytes = (hidden // 512) * 16 * n_out * 4 + 512 if engine and hidden % 512 == 0 else 0
+        self.ws = _z(ws_bytes, dtype=torch.uint8, device=x.device) if ws_bytes else None
         self.keep = (w, x, list(gathered))
         self.bind = host.make(
             "MkLmHeadBind", w=w, x=x, out_peer=list(gathered), rank=rank, v_total=v_total, col0=rank * n_out,
             n_out=n_out, hidden=hidden, rows=x.shape[0], status=self.status, flags=flags, flags_peer=list(flags_peer),
+            ws=self.ws, ws_bytes=ws_bytes,
         )  # fmt: skip
         self.launch = lib.bind("mk_lm_head_bind", module, self.bind)
 

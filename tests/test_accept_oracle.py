@@ -95,8 +95,11 @@ def test_bind_argument_checks():
     _expect("mk_entry_bind", host.make("MkEntryBind", **{**e, "hidden": 1000}), "hidden 1000")
     _expect("mk_entry_bind", host.make("MkEntryBind", **{**e, "ranks": 3}), r"embed_peer\[2\]")
     h = dict(w=p, x=p, out_peer=[p], rank=0, v_total=1000, col0=0, n_out=250, hidden=1024, rows=16, status=0, flags=0,
-             flags_peer=[])
+             flags_peer=[], ws=0, ws_bytes=0)
     assert _lib().bind("mk_lm_head_bind", None, host.make("MkLmHeadBind", **h)).info().kernels == 1
+    need = (1024 // 512) * 16 * 250 * 4 + 512  # with scratch the GEMM runs on the item engine
+    assert _lib().bind("mk_lm_head_bind", None, host.make("MkLmHeadBind", **{**h, "ws": 4096, "ws_bytes": need})).info().kernels == 1
+    _expect("mk_lm_head_bind", host.make("MkLmHeadBind", **{**h, "ws": 4096, "ws_bytes": need - 16}), "ws_bytes")
     _expect("mk_lm_head_bind", host.make("MkLmHeadBind", **{**h, "col0": 800}), "columns")
     _expect("mk_lm_head_bind", host.make("MkLmHeadBind", **{**h, "rank": 1}), "out_peer")
     a = dict(logits=p, vocab=1000, rows=16, b_live=16, scale=1.0, cap=20.0, tokens=p, accept_override=0, n_override=0,

@@ -72,3 +72,44 @@ def test_conv_row_zero_has_no_second_tap():
     out = D.grouped_conv(x, delta, base)
     want0 = ((base[0].float() + delta[0, 0].float().repeat_interleave(16)) * x[0].float()).to(torch.bfloat16)
     assert torch.equal(out[0], want0)
+
+
+def test_draft_binds_validate_without_a_gpu():
+    """Pack-only binds (no module): operand checks and kernel counts of the draft's launch records."""
+    from sgl_muse_mega_b200.common import host
+
+    lib = host.library()
+    P = 1 << 20  # any aligned non-null address: a pack-only record never launches
+    shape = dict(rows=16, hidden=512, layers=2, q_heads=4, kv_heads=2, inter=512, features=5, ranks=2, rank=1, window_left=23,
+                 conv_groups=32, vocab=2048, selector_rank=64)  # fmt: skip
+    sh = host.make("MkDflashShape", **shape)
+    c = lib.dflash_constants(sh)
+    assert (c.coeffs, c.qkv_row, c.kv_rows_n, c.attn_splits, c.topk_chunks) == (128, 1024, 1024, 2, 1)
+    assert c.ws_bytes >= (5 * 512 // 512) * 16 * 256 * 4 + 512
+    common = dict(ws=P, flags=0, flags_peer=[], status=P, wait_budget=0, eps=1e-5)
+    entry = dict(cap=[P] * 5, words=P, embed_peer=[P, P], shard_rows=1024, mask_id=2002, w_fc=P, hid_norm=P, in_norm=P, w_kv=P,
+                 k_norm=[P, P], k_pool=[P, P], v_pool=[P, P], pool_rows=64, rope=P, rope_rows=64, feats=P, ctx_raw_peer=[0, P], ctx=P,
+                 kv=P, x=P, h=P, **common)  # fmt: skip
+    assert lib.dflash_bind("mk_dflash_entry_bind", None, sh, host.make("MkDflashEntryBind", **entry)).info().kernels == 6
+    with pytest.raises(RuntimeError, match="pool_rows"):
+        lib.dflash_bind("mk_dflash_entry_bind", None, sh, host.make("MkDflashEntryBind", **{**entry, "pool_rows": 30}))
+    with pytest.raises(RuntimeError, match="ctx_raw_peer"):
+        lib.dflash_bind("mk_dflash_entry_bind", None, sh, host.make("MkDflashEntryBind", **{**entry, "ctx_raw_peer": [P, 0]}))
+    layer = dict(h_in=P, res_in=P, words=P, attn_proj=P, attn_base=P, mlp_proj=P, mlp_base=P, w_qkv=P, q_norm=P, k_norm=P, w_o=P,
+                 post_norm=P, w_gate_up=P, w_down=P, next_norm=P, k_pool=P, v_pool=P, pool_rows=64, rope=P, rope_rows=64, c_att=P,
+                 xa=P, qkv=P, q=P, attn_ws=P, o=P, ar_attn_peer=[P, P], a=0, h_post=P, res_post=P, c_mlp=P, xm=P, m=P,
+                 ar_mlp_peer=[P, P], x_out=0, h_out=P, res_out=0, **common)  # fmt: skip
+    assert lib.dflash_bind("mk_dflash_layer_bind", None, sh, host.make("MkDflashLayerBind", **layer)).info().kernels == 13
+    with pytest.raises(RuntimeError, match="w_down"):
+        lib.dflash_bind("mk_dflash_layer_bind", None, sh, host.make("MkDflashLayerBind", **{**layer, "w_down": 0}))
+    head = dict(y=P, w_hproj=P, hid=P, logits=P, pred_codebook=P, succ_codebook=P, words=P, keys=P, cand=P, unary=P, scores=P,
+                pick=P, drafts=P, verify_ids=P, mult=0.17, cap=20.0, ws=P, flags=0, contributors=0, status=P, wait_budget=0)  # fmt: skip
+    assert lib.dflash_bind("mk_dflash_draft_head_bind", None, sh, host.make("MkDflashDraftHeadBind", **head)).info().kernels == 3
+    for bad, why in ((dict(q_heads=3), "heads"), (dict(hidden=768), "hidden"), (dict(inter=300), "inter"), (dict(rows=17), "rows"),
+                     (dict(conv_groups=128), "conv_groups"), (dict(selector_rank=600), "selector_rank")):  # fmt: skip
+        with pytest.raises(RuntimeError, match=why):
+            lib.dflash_constants(host.make("MkDflashShape", **{**shape, **bad}))
+    sync = dict(words=P, window=P, state=P, ring=P, pool=P, n_buf=10, row_bytes=256, ring_rows=4096, lag=1, status=P)
+    assert lib.bind("mk_dflash_kv_sync_bind", None, host.make("MkDflashKvSyncBind", **sync)).info().kernels == 1
+    with pytest.raises(RuntimeError, match="row_bytes"):
+        lib.bind("mk_dflash_kv_sync_bind", None, host.make("MkDflashKvSyncBind", **{**sync, "row_bytes": 100}))
