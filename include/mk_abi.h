@@ -283,7 +283,7 @@ typedef struct MkLmHeadBind {
     uint64_t flags;                // this rank's flag block and the peers' (as MkLayerBind); 0: no signalling
     uint64_t flags_peer[MKH_RANKS];
     uint64_t ws;                   // 0, or ws_bytes of private scratch zeroed once: with hidden a multiple of 512 the GEMM then
-    int64_t ws_bytes;              // runs on the item engine (needs (hidden / 512) x 16 x n_out x 4 + 512 bytes)
+    int64_t ws_bytes;              // runs on the item engine (needs (hidden / 256) x 16 x n_out x 4 + 512 bytes)
 } MkLmHeadBind;
 int mk_lm_head_bind(MkModule* module, const MkLmHeadBind* bind, MkLaunch** out);
 

@@ -159,7 +159,7 @@ static void fill_constants(const MkLayerShape& s, MkLayerConstants* c) {
     off += align_up((size_t)s.kv_heads * c->attn_splits * R * 66 * 4, 256);
     int64_t nmax = c->qkv_row;
     if (s.hidden > nmax) nmax = s.hidden;
-    off += align_up((size_t)16 * 16 * nmax * 4, 256);  // up to 16 K chunks of [16, N] f32
+    off += align_up((size_t)32 * 16 * nmax * 4, 256);  // up to 32 K chunks (256 k each) of [16, N] f32
     off += align_up((size_t)1024 * 4, 256);
     off += align_up(sizeof(RouteTables), 256);
     off += align_up((size_t)slots * s.inter / 16, 256);
@@ -316,7 +316,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     off += align_up((size_t)kvh * c.attn_splits * R * 66 * 4, 256);
     float* gpart = (float*)(ws + off);
     int64_t nmax = c.qkv_row > s.hidden ? c.qkv_row : s.hidden;
-    off += align_up((size_t)16 * 16 * nmax * 4, 256);
+    off += align_up((size_t)32 * 16 * nmax * 4, 256);
     unsigned* gcnt = (unsigned*)(ws + off);
     off += align_up((size_t)1024 * 4, 256);
     L->rt = (RouteTables*)(ws + off);
@@ -377,7 +377,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     L->router.out_f32 = 1;
     // the routing's selection scores come out of this GEMM's epilogue (a thread per logit); they live in the last
     // 16 x 1024 floats of the partial-sum scratch (the partial sums never reach that far: checked with the GEMM tiling)
-    float* const scores = gpart + (size_t)256 * nmax - 16 * 1024;
+    float* const scores = gpart + (size_t)512 * nmax - 16 * 1024;
     L->router.score = scores;
     L->router.score_bias = (const float*)b->expert_bias;
     L->router.score_mult = b->router_mult;
@@ -492,11 +492,11 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     // GPU steps the per-stage kernels (mk_launch_step) instead. Shapes outside its tiling keep the per-stage kernels.
     L->use_segments = false;
     L->seg_gemms = false;
-    const size_t part_cap = (size_t)256 * nmax - 16 * 1024;  // floats of partial-sum scratch below the routing scores
+    const size_t part_cap = (size_t)512 * nmax - 16 * 1024;  // floats of partial-sum scratch below the routing scores
     const bool seg_shapes = (qh * kHeadDim) % 512 == 0 && H % 512 == 0 && P % 512 == 0 && H <= 8192 && P <= 4096 &&
-                            (size_t)(H / 512) * 16 * (P / nr + E) <= part_cap &&
-                            (size_t)(qh * kHeadDim / 512) * 16 * H <= part_cap && (size_t)(P / 512) * 16 * (H / nr) <= part_cap &&
-                            (size_t)(H / 512) * 16 * c.qkv_row <= part_cap;
+                            (size_t)(H / 256) * 16 * (P / nr + E) <= part_cap &&
+                            (size_t)(qh * kHeadDim / 256) * 16 * H <= part_cap && (size_t)(P / 256) * 16 * (H / nr) <= part_cap &&
+                            (size_t)(H / 256) * 16 * c.qkv_row <= part_cap;
     auto seg_gemm = [&](SegGemm& g, const GemmArgs& src, bool f32, float* part) {
         const int es = f32 ? 4 : 2;
         g.w = (const unsigned char*)src.w;
@@ -526,7 +526,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
         };
         stage(L->sg_oproj, L->oproj, 0);
         stage(L->sg_pool, L->pooler, 1);
-        seg_gemm(L->sg_pool.g[1], L->router, true, gpart + (size_t)(H / 512) * 16 * (P / nr));
+        seg_gemm(L->sg_pool.g[1], L->router, true, gpart + (size_t)(H / 256) * 16 * (P / nr));
         L->sg_pool.n_gemm = 2;
         L->sg_pool.f32_out = (float*)b->logits;
         L->sg_pool.score = scores;
@@ -546,7 +546,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
         memset(&A, 0, sizeof A);
         seg_gemm(A.oproj, L->oproj, false, gpart);
         seg_gemm(A.pooler, L->pooler, false, gpart);
-        seg_gemm(A.router, L->router, true, gpart + (size_t)(H / 512) * 16 * (P / nr));
+        seg_gemm(A.router, L->router, true, gpart + (size_t)(H / 256) * 16 * (P / nr));
         for (int i = 0; i < L->oproj.n_out; ++i) A.ar_out[i] = (bf16*)L->oproj.out[i];
         A.n_ar = L->oproj.n_out;
         A.ar_off = 0;  // the destinations already point at this rank's slot

@@ -238,7 +238,8 @@ struct SegGemm {
     long long ldw, ldx;      // row strides in bytes
     int N, K, M;
     int f32;                 // 1: f32 weights through tf32 (tile 16 rows), 0: bf16 (tile 64 rows)
-    float* part;             // [K / 512][16][N] f32 partial sums
+    float* part;             // [K / 256][16][N] f32 partial sums (a slot per K chunk; few of them are written, see segments.cuh)
+    int item0, per;          // set on the device: the GEMM's first item within its stage, items per CTA
 };
 struct GridBarrier {
     unsigned long long* count;  // starts at a multiple of the grid size and only grows

@@ -90,7 +90,7 @@ class LmHead:
         self.status = _z(16, dtype=torch.int32, device=x.device)
         # private scratch of the item engine (partial sums per 512-k chunk and its barrier word); shapes it does not tile
         # run on the cluster split-K GEMM without scratch
-        ws_bytes = (hidden // 512) * 16 * n_out * 4 + 512 if engine and hidden % 512 == 0 else 0
+        ws_bytes = (hidden // 256) * 16 * n_out * 4 + 512 if engine and hidden % 512 == 0 else 0
         self.ws = _z(ws_bytes, dtype=torch.uint8, device=x.device) if ws_bytes else None
         self.keep = (w, x, list(gathered))
         self.bind = host.make(

@@ -97,7 +97,7 @@ def test_bind_argument_checks():
     h = dict(w=p, x=p, out_peer=[p], rank=0, v_total=1000, col0=0, n_out=250, hidden=1024, rows=16, status=0, flags=0,
              flags_peer=[], ws=0, ws_bytes=0)
     assert _lib().bind("mk_lm_head_bind", None, host.make("MkLmHeadBind", **h)).info().kernels == 1
-    need = (1024 // 512) * 16 * 250 * 4 + 512  # with scratch the GEMM runs on the item engine
+    need = (1024 // 256) * 16 * 250 * 4 + 512  # with scratch the GEMM runs on the item engine
     assert _lib().bind("mk_lm_head_bind", None, host.make("MkLmHeadBind", **{**h, "ws": 4096, "ws_bytes": need})).info().kernels == 1
     _expect("mk_lm_head_bind", host.make("MkLmHeadBind", **{**h, "ws": 4096, "ws_bytes": need - 16}), "ws_bytes")
     _expect("mk_lm_head_bind", host.make("MkLmHeadBind", **{**h, "col0": 800}), "columns")

@@ -85,7 +85,7 @@ def test_draft_binds_validate_without_a_gpu():
     sh = host.make("MkDflashShape", **shape)
     c = lib.dflash_constants(sh)
     assert (c.coeffs, c.qkv_row, c.kv_rows_n, c.attn_splits, c.topk_chunks) == (128, 1024, 1024, 2, 1)
-    assert c.ws_bytes >= (5 * 512 // 512) * 16 * 256 * 4 + 512
+    assert c.ws_bytes >= (5 * 512 // 256) * 16 * 256 * 4 + 512
     common = dict(ws=P, flags=0, flags_peer=[], status=P, wait_budget=0, eps=1e-5)
     entry = dict(cap=[P] * 5, words=P, embed_peer=[P, P], shard_rows=1024, mask_id=2002, w_fc=P, hid_norm=P, in_norm=P, w_kv=P,
                  k_norm=[P, P], k_pool=[P, P], v_pool=[P, P], pool_rows=64, rope=P, rope_rows=64, feats=P, ctx_raw_peer=[0, P], ctx=P,
