@@ -211,7 +211,7 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
     forced = torch.tensor([args.accept], dtype=torch.int32, device=device)
     arena = symm.Arena(lib, S.exchange_layout(model, rows), device) if world > 1 else None
     st = S.Stack(case, tp_rank, device, lib, module, arena=arena, kv_rows=kv_rows, keep_plain_experts=False,
-                 accept_override=forced, wait_budget=1 << 25)  # fmt: skip
+                 accept_override=forced, wait_budget=1 << 25, packed=True)  # fmt: skip
     peers = S.connect_world(st) if world > 1 else st.bind()
     s = stream.cuda_stream
     # the DFlash2 draft at its public size (this rank's TP slice, synthetic weights drawn on the device): with it the step
@@ -390,7 +390,8 @@ def run_ours(args) -> None:
         glob = i % 4 == 3
         case = synthetic.layer_case(cfg, rows=args.rows, ctx=args.ctx, global_attn=glob, next_global=(i + 1) % 4 == 3,
                                     band="baseline", seed=args.seed, layer=2 + i, only_ranks=[tp_rank])  # fmt: skip
-        lr = L.LayerRank(lib, module, case, tp_rank, device, tensors=case.ranks[0], keep_plain_experts=False)
+        lr = L.LayerRank(lib, module, case, tp_rank, device, tensors=case.ranks[0], keep_plain_experts=False,
+                         packed=args.form != 2)
         assert lr.tensor_cores, "the full shape runs its experts on the tcgen05 kernels"
         # the absent ranks' contributions: values of the right kind already in the exchange buffers
         g = torch.Generator(device=device).manual_seed(1000 + i)

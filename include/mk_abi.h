@@ -217,6 +217,11 @@ typedef struct MkLayerBind {
     //   2  one launch per stage with the cluster split-K GEMMs: 14 kernels a layer.
     // mk_launch_info.kernels tells which form was bound.
     int64_t fused;
+    // 1: w_o, w_p, w_r, w_up and w_qkv are item images of the item engine instead of row-major matrices (forms 0 and 1
+    // only): [ceil(N / 64)][K / 256][64 rows][256 k + 32 pad] bf16 ([N / 16][K / 256][16 rows][256 k + 16 pad] f32 for
+    // w_r), rows past N zero; w_p and w_up then hold this rank's node block only (P / node_ranks and H / node_ranks
+    // rows). One bulk copy brings an item in, instead of one per weight row.
+    int64_t dense_packed;
 } MkLayerBind;
 int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind* bind, MkLaunch** out);
 
@@ -284,6 +289,7 @@ typedef struct MkLmHeadBind {
     uint64_t flags_peer[MKH_RANKS];
     uint64_t ws;                   // 0, or ws_bytes of private scratch zeroed once: with hidden a multiple of 512 the GEMM then
     int64_t ws_bytes;              // runs on the item engine (needs (hidden / 256) x 16 x n_out x 4 + 512 bytes)
+    int64_t w_packed;              // 1: w holds item images (as MkLayerBind.dense_packed; needs ws)
 } MkLmHeadBind;
 int mk_lm_head_bind(MkModule* module, const MkLmHeadBind* bind, MkLaunch** out);
 
@@ -463,6 +469,7 @@ typedef struct MkDflashEntryBind {
     uint64_t status;
     int64_t wait_budget;
     double eps;
+    int64_t packed;         // 1: w_fc and w_kv are item images (as MkLayerBind.dense_packed)
 } MkDflashEntryBind;
 int mk_dflash_entry_bind(MkModule* module, const MkDflashShape* shape, const MkDflashEntryBind* bind, MkLaunch** out);
 
@@ -514,6 +521,7 @@ typedef struct MkDflashLayerBind {
     uint64_t status;
     int64_t wait_budget;
     double eps;
+    int64_t packed;         // 1: attn_proj, mlp_proj, w_qkv, w_o, w_gate_up, w_down are item images
 } MkDflashLayerBind;
 int mk_dflash_layer_bind(MkModule* module, const MkDflashShape* shape, const MkDflashLayerBind* bind, MkLaunch** out);
 
@@ -543,6 +551,7 @@ typedef struct MkDflashDraftHeadBind {
     int64_t contributors;
     uint64_t status;
     int64_t wait_budget;
+    int64_t packed;         // 1: w_hproj is an item image
 } MkDflashDraftHeadBind;
 int mk_dflash_draft_head_bind(MkModule* module, const MkDflashShape* shape, const MkDflashDraftHeadBind* bind, MkLaunch** out);
 

@@ -364,7 +364,8 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
         signal_to(L->oproj.sig, XP_AR, 0, all);
     }
     // pooler: the node block of rows [j P/nr, (j+1) P/nr) -> the node's gather rows
-    if (gemm(L->pooler, 0, false, b->w_p + (uint64_t)jnode * (P / nr) * H * 2, b->h3, P / nr, H, H)) return -1;
+    // (item images hold this rank's node block only; row-major matrices are replicated and offset here)
+    if (gemm(L->pooler, 0, false, b->dense_packed ? b->w_p : b->w_p + (uint64_t)jnode * (P / nr) * H * 2, b->h3, P / nr, H, H)) return -1;
     L->pooler.n_out = peers(b->pool_ag_peer, b->pool_ag, L->pooler.out, node0, nr);
     L->pooler.ldo = P;
     L->pooler.col0 = jnode * (P / nr);
@@ -382,7 +383,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     L->router.score_bias = (const float*)b->expert_bias;
     L->router.score_mult = b->router_mult;
     // unpooler: node block of [H, P]
-    if (gemm(L->unpool, 0, false, b->w_up + (uint64_t)jnode * (H / nr) * P * 2, b->y, H / nr, P, P)) return -1;
+    if (gemm(L->unpool, 0, false, b->dense_packed ? b->w_up : b->w_up + (uint64_t)jnode * (H / nr) * P * 2, b->y, H / nr, P, P)) return -1;
     L->unpool.n_out = peers(b->unpool_ag_peer, b->unpool_ag, L->unpool.out, node0, nr);
     L->unpool.ldo = H;
     L->unpool.col0 = jnode * (H / nr);
@@ -505,9 +506,11 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
         g.ldx = (long long)src.ldx * es;
         g.N = src.N; g.K = src.K; g.M = src.M; g.f32 = f32 ? 1 : 0;
         g.part = part;
+        g.packed = b->dense_packed ? 1 : 0;
     };
     // fused 0 (default): the per-stage launch list with its GEMMs on the item engine of segments.cuh where the shapes tile
     // (pooler and router share a launch); fused 2: the cluster split-K GEMMs of gemm.cu everywhere; fused 1: two segments
+    MK_REQUIRE(!b->dense_packed || (b->fused != 2 && seg_shapes), "dense_packed needs the item engine (fused 0 or 1 and shapes it tiles)");
     if (b->fused != 2 && seg_shapes) {
         L->seg_gemms = true;
         const GridBarrier gb{(unsigned long long*)gcnt, budget, L->status};
@@ -849,6 +852,7 @@ int mk_lm_head_bind(MkModule* module, const MkLmHeadBind* b, MkLaunch** out) {
     MK_REQUIRE(b->rank >= 0 && b->rank < MKH_RANKS && b->out_peer[b->rank] != 0, "out_peer[rank] (this rank's logits) is 0");
     MK_REQUIRE(b->n_out >= 1 && b->col0 >= 0 && b->col0 + b->n_out <= b->v_total, "columns [%lld, %lld) outside %lld", (long long)b->col0,
                (long long)(b->col0 + b->n_out), (long long)b->v_total);
+    MK_REQUIRE(!b->w_packed || (b->ws != 0 && b->hidden % 512 == 0), "w_packed needs the item engine (ws and hidden a multiple of 512)");
     if (b->ws != 0 && b->hidden % 512 == 0) return lm_head_on_engine(module, b, out);
     MkLaunch* L = new_op_launch(module, OP_GEMM_BF16);
     MK_REQUIRE(L != nullptr, "out of host memory");

@@ -80,6 +80,14 @@ __device__ __forceinline__ void seg_issue_w(const SegGemm& g, int item, SegPipe&
     const int bn = seg_bn(g), es = g.f32 ? 4 : 2, rowb = seg_row_bytes(g);
     const int valid = min(bn, g.N - nb * bn);
     const int tid = threadIdx.x;
+    if (g.packed) {  // the item's image is contiguous, padded rows included: one copy
+        const uint32_t img = (uint32_t)(bn * rowb);
+        if (tid == 0) {
+            umma::bulk_g2s(p.buf[b], g.w + (size_t)item * img, img, &p.bar[b]);
+            umma::mbar_arrive_expect_tx(&p.bar[b], img);
+        }
+        return;
+    }
     if (tid < valid)
         umma::bulk_g2s(p.buf[b] + tid * rowb, g.w + (size_t)(nb * bn + tid) * g.ldw + (size_t)ks * kChunkK * es, kChunkK * es,
                        &p.bar[b]);
@@ -120,6 +128,9 @@ __device__ __forceinline__ void seg_mma(const SegGemm& g, int item, SegPipe& p, 
     const unsigned char* xs0 = p.buf[b] + (BN + gq) * rowb + (wk * kw) * ES + t * 16;
     const unsigned char* xs1 = xs0 + 8 * rowb;
     const bool two = g.M > 8;
+#ifdef SEG_NO_MMA  // timing experiments only: the stream without the arithmetic
+    if (p.buf[b] == nullptr)
+#endif
 #pragma unroll
     for (int s = 0; s < nsteps; ++s) {
         uint4 wa = *(const uint4*)(wa0 + s * 64), wb = *(const uint4*)(wa1 + s * 64);

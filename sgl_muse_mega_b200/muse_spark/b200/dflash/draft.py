@@ -23,6 +23,7 @@ import torch
 
 from ....common import host
 from .. import headtail as HT
+from .. import weights as W
 from .weights import DraftConfig, DraftWeights, TargetShared, rope_table
 
 BF = torch.bfloat16
@@ -55,8 +56,13 @@ class DraftRank:
     def __init__(self, cfg: DraftConfig, w: DraftWeights, t: TargetShared, rank: int, ranks: int, device, *, rows: int,
                  pool_rows: int, rope_rows: int, lib: Optional[host.Library] = None, module=None, words: Optional[torch.Tensor] = None,
                  caps: Optional[Sequence[torch.Tensor]] = None, verify_ids: Optional[torch.Tensor] = None, exchange=None,
-                 flags: bool = False, wait_budget: int = 0):  # fmt: skip
+                 flags: bool = False, wait_budget: int = 0, packed: bool = False, lm_head_packed: Optional[bool] = None):  # fmt: skip
+        """``packed``: upload the draft's GEMM weights as item images (``weights.pack_items``: one bulk copy per item).
+        ``lm_head_packed``: ``t.lm_head`` already is one (a target stack built with ``packed``); default: pack it too."""
         self.cfg, self.rank, self.ranks, self.rows, self.device = cfg, rank, ranks, rows, device
+        self.packed = bool(packed)
+        pk = W.pack_items if self.packed else (lambda x: x)
+        self.lm_head_packed = self.packed or bool(lm_head_packed)
         self.lib = lib or host.library()
         self.module = module or self.lib.load()
         self.shape = shape_of(cfg, ranks, rank, rows)
@@ -69,14 +75,15 @@ class DraftRank:
         kvh, qh = cfg.kv_rank(ranks), cfg.q_rank(ranks)
         # weights
         self.w = dict(
-            fc=d(w.fc), hid_norm=d(w.hidden_norm), norm=d(w.norm), pred=d(w.pred_codebook), succ=d(w.succ_codebook),
-            hproj=d(w.hidden_proj), lm_head=d(t.lm_head),
-            w_kv=d(torch.cat([lw.qkv[qh * cfg.head_dim :] for lw in w.layers])),
+            fc=pk(d(w.fc)), hid_norm=d(w.hidden_norm), norm=d(w.norm), pred=d(w.pred_codebook), succ=d(w.succ_codebook),
+            hproj=pk(d(w.hidden_proj)),
+            lm_head=W.pack_items(d(t.lm_head)) if self.packed and not lm_head_packed else d(t.lm_head),
+            w_kv=pk(d(torch.cat([lw.qkv[qh * cfg.head_dim :] for lw in w.layers]))),
         )  # fmt: skip
         self.lw = [
-            dict(in_norm=d(lw.input_norm), post_norm=d(lw.post_norm), q_norm=d(lw.q_norm), k_norm=d(lw.k_norm), qkv=d(lw.qkv), o=d(lw.o),
-                 gate_up=d(lw.gate_up), down=d(lw.down), attn_proj=d(lw.attn_conv.proj), attn_base=d(lw.attn_conv.base),
-                 mlp_proj=d(lw.mlp_conv.proj), mlp_base=d(lw.mlp_conv.base))
+            dict(in_norm=d(lw.input_norm), post_norm=d(lw.post_norm), q_norm=d(lw.q_norm), k_norm=d(lw.k_norm), qkv=pk(d(lw.qkv)),
+                 o=pk(d(lw.o)), gate_up=pk(d(lw.gate_up)), down=pk(d(lw.down)), attn_proj=pk(d(lw.attn_conv.proj)),
+                 attn_base=d(lw.attn_conv.base), mlp_proj=pk(d(lw.mlp_conv.proj)), mlp_base=d(lw.mlp_conv.base))
             for lw in w.layers
         ]  # fmt: skip
         self.rope = d(rope_table(rope_rows, cfg.head_dim, cfg.rope_theta))
@@ -122,7 +129,8 @@ class DraftRank:
         fpeer = of("flags") if flags is not None else []
         # a slice of a larger world (absent ranks): an id owned by an absent rank reads this rank's shard instead
         embed = [self.x.embed if e is None else e for e in of("embed")]
-        common = dict(ws=self.ws, flags=flags, flags_peer=fpeer, status=self.status, wait_budget=self.wait_budget, eps=cfg.rms_eps)
+        common = dict(ws=self.ws, flags=flags, flags_peer=fpeer, status=self.status, wait_budget=self.wait_budget, eps=cfg.rms_eps,
+                      packed=int(self.packed))
         entry = host.make(
             "MkDflashEntryBind", cap=self.caps, words=self.words, embed_peer=embed, shard_rows=cfg.vocab // self.ranks,
             mask_id=cfg.mask_id, w_fc=self.w["fc"], hid_norm=self.w["hid_norm"], in_norm=self.lw[0]["in_norm"], w_kv=self.w["w_kv"],
@@ -148,13 +156,14 @@ class DraftRank:
             self.layers.append(lib.dflash_bind("mk_dflash_layer_bind", mod, self.shape, b))
         present = sum(p is not None for p in peers)
         self.lm_head = HT.LmHead(lib, mod, w=self.w["lm_head"], x=self.y[1:], gathered=of("gathered"), rank=r, flags=flags,
-                                 flags_peer=fpeer, v_total=cfg.vocab)  # fmt: skip
+                                 flags_peer=fpeer, v_total=cfg.vocab, w_packed=self.lm_head_packed, n_out=cfg.vocab // self.ranks,
+                                 hidden=cfg.hidden)  # fmt: skip
         head = host.make(
             "MkDflashDraftHeadBind", y=self.y, w_hproj=self.w["hproj"], hid=self.hid, logits=self.x.gathered,
             pred_codebook=self.w["pred"], succ_codebook=self.w["succ"], words=self.words, keys=self.keys, cand=self.cand,
             unary=self.unary, scores=self.scores, pick=self.pick, drafts=self.drafts, verify_ids=self.verify_ids,
             mult=cfg.output_multiplier, cap=cfg.softcap, ws=self.ws, flags=flags, contributors=present if flags is not None else 0,
-            status=self.status, wait_budget=self.wait_budget,
+            status=self.status, wait_budget=self.wait_budget, packed=int(self.packed),
         )  # fmt: skip
         self.head = lib.dflash_bind("mk_dflash_draft_head_bind", mod, self.shape, head)
         self.launches = [self.entry, *self.layers, self.lm_head.launch, self.head]
@@ -231,8 +240,10 @@ class DraftWorld:
 EXCHANGE = ("flags", "ctx_raw", "ar_attn", "ar_mlp", "gathered")
 
 
-def exchange_layout(cfg: DraftConfig, ranks: int, rows: int):
-    """The draft's exchange arena of one rank (depends on the model and the block only: every rank carves the same)."""
+def exchange_layout(cfg: DraftConfig, ranks: int, rows: int, with_embed: bool = False):
+    """The draft's exchange arena of one rank (depends on the model and the block only: every rank carves the same).
+    ``with_embed``: room for the rank's vocab shard of the embedding too (a draft that runs without a target stack, whose
+    arena otherwise holds it)."""
     from ....common import symm
 
     lay = symm.Layout()
@@ -241,6 +252,8 @@ def exchange_layout(cfg: DraftConfig, ranks: int, rows: int):
     lay.add("ar_attn", (ranks, 16, cfg.hidden), BF)
     lay.add("ar_mlp", (ranks, 16, cfg.hidden), BF)
     lay.add("gathered", (rows - 1, cfg.vocab), torch.float32)
+    if with_embed:
+        lay.add("embed", (cfg.vocab // ranks, cfg.hidden), BF)
     return lay
 
 
@@ -251,18 +264,21 @@ class ArenaExchange:
         self.arena, self.embed = arena, embed
         for name in EXCHANGE:
             setattr(self, name, arena.tensor(name))
+        if "embed" in arena.layout.items:  # the shard moves into the arena, where the peers can read it
+            self.embed = arena.tensor("embed")
+            self.embed.copy_(embed)
 
 
 class PeerExchange:
     """A peer's exchange buffers by device address (its arena, mapped) and the address of its embedding shard."""
 
-    def __init__(self, arena, embed_ptr: int):
-        self.arena, self.embed = arena, embed_ptr
+    def __init__(self, arena, embed_ptr: Optional[int]):
+        self.arena, self.embed = arena, embed_ptr if embed_ptr is not None else arena.ptr("embed")
         for name in EXCHANGE:
             setattr(self, name, arena.ptr(name))
 
 
-def connect_exchange(arena, embed, peer_embed_ptrs: Sequence[Optional[int]], rank: int, ranks: int, group=None) -> tuple:
+def connect_exchange(arena, embed, peer_embed_ptrs: Optional[Sequence[Optional[int]]], rank: int, ranks: int, group=None) -> tuple:
     """Swaps the draft arenas' handles over ``torch.distributed`` -> (own ``ArenaExchange``, the peer list for
     ``DraftRank.bind``: own entry included, None for ranks beyond the present world)."""
     import torch.distributed as dist
@@ -272,5 +288,6 @@ def connect_exchange(arena, embed, peer_embed_ptrs: Sequence[Optional[int]], ran
     n = dist.get_world_size(group)
     arenas = symm.connect(arena, rank, n, group)
     own = ArenaExchange(arena, embed)
-    peers = [own if i == rank else PeerExchange(a, peer_embed_ptrs[i]) for i, a in enumerate(arenas)] + [None] * (ranks - n)
+    ptrs = peer_embed_ptrs if peer_embed_ptrs is not None else [None] * n
+    peers = [own if i == rank else PeerExchange(a, ptrs[i]) for i, a in enumerate(arenas)] + [None] * (ranks - n)
     return own, peers

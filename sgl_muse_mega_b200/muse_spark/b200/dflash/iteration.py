@@ -25,7 +25,7 @@ from .weights import DraftConfig, DraftWeights, TargetShared
 class Iteration:
     def __init__(self, stack: Stack, dcfg: DraftConfig, dw: DraftWeights, *, capture: Optional[Sequence[int]] = None,
                  pool_rows: int = 4096, rope_rows: Optional[int] = None, peers: Optional[Sequence] = None, exchange=None,
-                 wait_budget: int = 0):  # fmt: skip
+                 wait_budget: int = 0, packed: Optional[bool] = None):  # fmt: skip
         """``stack``: the bound target stack of this rank (greedy tail). ``capture``: indices into ``stack.layers`` whose
         output residual feeds the draft (default: ``dcfg.capture`` relative to the stack's first layer). ``peers`` /
         ``exchange``: the draft's exchange buffers of a world of several processes (``DraftRank.bind``)."""
@@ -42,7 +42,7 @@ class Iteration:
         self.draft = DraftRank(
             dcfg, dw, t, stack.rank, cfg.tp, stack.device, rows=stack.case.rows, pool_rows=pool_rows, rope_rows=rope_rows,
             lib=stack.lib, module=stack.module, words=stack.accept.words, caps=caps, verify_ids=stack.tokens, exchange=exchange,
-            wait_budget=wait_budget,
+            wait_budget=wait_budget, packed=stack.packed if packed is None else packed, lm_head_packed=stack.packed,
         )  # fmt: skip
         self.draft.bind(peers)
         self.graph: Optional[torch.cuda.CUDAGraph] = None

@@ -80,11 +80,15 @@ class LmHead:
     gathered logits (``gathered[r]`` is rank r's [rows, v_total] buffer; absent ranks are None)."""
 
     def __init__(self, lib: host.Library, module, *, w, x, gathered: Sequence[Optional[torch.Tensor]], rank: int,
-                 flags=None, flags_peer: Sequence = (), v_total: Optional[int] = None, engine: bool = True):  # fmt: skip
+                 flags=None, flags_peer: Sequence = (), v_total: Optional[int] = None, engine: bool = True,
+                 w_packed: bool = False, n_out: Optional[int] = None, hidden: Optional[int] = None):  # fmt: skip
         """``gathered``: tensors, or device addresses (then ``v_total`` is their row length). ``flags`` /
         ``flags_peer``: this rank's flag block and the peers' (present exactly where ``gathered`` is): the GEMM then
         signals the logits exchange on every rank it stored to."""
-        n_out, hidden = w.shape
+        if w_packed:  # item images (weights.pack_items): the matrix shape comes from the caller
+            assert n_out is not None and hidden is not None and engine
+        else:
+            n_out, hidden = w.shape
         if v_total is None:
             v_total = gathered[rank].shape[1]
         self.status = _z(16, dtype=torch.int32, device=x.device)
@@ -96,7 +100,7 @@ class LmHead:
         self.bind = host.make(
             "MkLmHeadBind", w=w, x=x, out_peer=list(gathered), rank=rank, v_total=v_total, col0=rank * n_out,
             n_out=n_out, hidden=hidden, rows=x.shape[0], status=self.status, flags=flags, flags_peer=list(flags_peer),
-            ws=self.ws, ws_bytes=ws_bytes,
+            ws=self.ws, ws_bytes=ws_bytes, w_packed=int(w_packed),
         )  # fmt: skip
         self.launch = lib.bind("mk_lm_head_bind", module, self.bind)
 

@@ -43,7 +43,8 @@ class LayerRank:
     """One rank's weights (moved to the device), buffers and bound launch of one layer."""
 
     def __init__(self, lib: host.Library, module, case, rank: int, device, kv_rows: Optional[int] = None, tensors=None,
-                 tensor_cores: bool = True, keep_plain_experts: bool = True, io: Optional[dict] = None):  # fmt: skip
+                 tensor_cores: bool = True, keep_plain_experts: bool = True, io: Optional[dict] = None,
+                 packed: bool = False):  # fmt: skip
         """``io`` replaces buffers this layer would allocate with ones it shares with its neighbours in a stack: inputs
         ``qkv_in`` / ``stream_in`` (the predecessor's outputs), ``k_cache`` / ``v_cache`` (the pools the predecessor
         appended to), the step's feeds ``page_table`` / ``kv_len`` / ``cache_loc`` / ``next_cos_sin`` and the
@@ -77,6 +78,18 @@ class LayerRank:
             if not keep_plain_experts:
                 for k in ("gate_q", "gate_sf", "up_q", "up_sf", "w2_q", "w2_sf"):
                     w[k] = None
+        # the dense weights as item images of the item engine (one bulk copy an item instead of one per weight row); the
+        # pooler and the unpooler keep this rank's node block only. Not for the cluster split-K form (fused 2).
+        self.packed = bool(packed)
+        if self.packed:
+            w, nr = self.w, cfg.node_ranks
+            j = rank % nr
+            w["o_proj"] = weights.pack_items(w["o_proj"])
+            w["pooler"] = weights.pack_items(w["pooler"][j * (P // nr) : (j + 1) * (P // nr)])
+            w["router"] = weights.pack_items(w["router"])
+            w["unpooler"] = weights.pack_items(w["unpooler"][j * (H // nr) : (j + 1) * (H // nr)])
+            if w.get("next_qkv") is not None:
+                w["next_qkv"] = weights.pack_items(w["next_qkv"])
         bf, f32, u8, i32 = torch.bfloat16, torch.float32, torch.uint8, torch.int32
 
         def z(shape, dtype):
@@ -178,7 +191,7 @@ class LayerRank:
             c_post_w=w["cross_post_w"], c_stream_out=o["stream_out"], h3q=o["h3_next"], w_qkv=w["next_qkv"],
             qkv_out=o["qkv_next"], cos_sin=w["next_cos_sin"], cache_loc=self.cache_loc, next_k_cache=self.next_k,
             next_v_cache=self.next_v, next_kv_rows=self.next_kv_rows, q_scale=cfg.q_scale, qkv_eps=cfg.rms_eps,
-            flags=self.flags, flags_peer=peer("flags"), ws=self.ws, status=self.status, b_live=b_live, wait_budget=wait_budget, fused=fused,
+            flags=self.flags, flags_peer=peer("flags"), ws=self.ws, status=self.status, b_live=b_live, wait_budget=wait_budget, fused=fused, dense_packed=int(self.packed),
         )  # fmt: skip
         self.launch_record = self.lib.layer_bind(self.module, self.shape, bind)
         return self.launch_record
@@ -217,13 +230,13 @@ class LayerWorld:
     """Every rank of the world on one device, exchange buffers wired as peers (see the module docstring)."""
 
     def __init__(self, case, device, lib: Optional[host.Library] = None, ranks: Optional[list] = None, b_live: int = 0,
-                 tensor_cores: bool = True):  # fmt: skip
+                 tensor_cores: bool = True, packed: bool = False):  # fmt: skip
         self.lib = lib or host.library()
         self.case, self.device = case, device
         with torch.cuda.device(device):
             self.module = self.lib.load()
         n = case.cfg.tp
-        self.ranks = [LayerRank(self.lib, self.module, case, r, device, tensor_cores=tensor_cores) for r in range(n)]
+        self.ranks = [LayerRank(self.lib, self.module, case, r, device, tensor_cores=tensor_cores, packed=packed) for r in range(n)]
         for r in self.ranks:
             r.bind(self.ranks, b_live)
 

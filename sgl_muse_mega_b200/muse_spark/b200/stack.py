@@ -67,7 +67,7 @@ class Stack:
                  kv_rows: Optional[int] = None, tensor_cores: bool = True, keep_plain_experts: bool = True,
                  greedy: bool = True, accept_override: Optional[torch.Tensor] = None, ring: int = 64,
                  b_live: int = 0, wait_budget: int = 0, fused: bool = False, frame: Optional[dict] = None,
-                 pools: Optional[list] = None):  # fmt: skip
+                 pools: Optional[list] = None, packed: bool = False):  # fmt: skip
         """``case``: a ``synthetic.StackCase``; ``rank`` must be one of ``case.ranks``. ``arena``: the rank's exchange
         memory carved by ``exchange_layout`` (default: ordinary tensors, for a world inside one process). ``greedy``
         False ends the step with the soft cap (the logits go to ``self.logits_out``) instead of the accept."""
@@ -113,7 +113,12 @@ class Stack:
         self.embed.copy_(case.embed[slot])
         self.pre_w0 = dev(case.pre_w0)
         self.qkv0 = dev(case.qkv0[slot])
+        self.packed = bool(packed)  # the dense weights and the lm_head as item images (weights.pack_items)
         self.lm_head_w = dev(case.lm_head[slot])
+        if self.packed:
+            from . import weights as W
+
+            self.lm_head_w = W.pack_items(self.lm_head_w)
         self.gathered = self.arena.tensor("gathered")
         self.logits_out = None if greedy else torch.zeros(M, cfg.vocab, dtype=torch.float32, device=device)
         self.greedy, self.accept_override, self.ring = greedy, accept_override, ring
@@ -152,7 +157,7 @@ class Stack:
             if not (lc.tail or lc.next_global):
                 io["next_cos_sin"] = f.cos_sin
             lr = LayerRank(self.lib, module, lc, rank, device, tensors=t, tensor_cores=tensor_cores,
-                           keep_plain_experts=keep_plain_experts, io=io)  # fmt: skip
+                           keep_plain_experts=keep_plain_experts, io=io, packed=self.packed)  # fmt: skip
             if not keep_plain_experts:
                 lr.case = dataclasses.replace(lc, ranks=[])  # the device copies live in lr.w
             del lc, t
@@ -187,7 +192,7 @@ class Stack:
         self.lm_head = HT.LmHead(self.lib, self.module, w=self.lm_head_w, x=self.hidden,
                                  gathered=[None if v is None else v.gathered for v in views], rank=self.rank,
                                  flags=flags, flags_peer=[None if v is None else v.flags for v in views],
-                                 v_total=cfg.vocab)  # fmt: skip
+                                 v_total=cfg.vocab, w_packed=self.packed, n_out=cfg.vocab_rank, hidden=cfg.hidden)  # fmt: skip
         if self.greedy:
             self.accept = HT.Accept(
                 self.lib, self.module, logits=self.gathered, tokens=self.tokens, b_live=self.b_live,

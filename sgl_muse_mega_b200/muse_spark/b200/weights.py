@@ -112,3 +112,23 @@ def unpack_w2_fp4(pack: torch.Tensor):
     rows, kb, ks = nb * TILE_ROWS, kc * 128, kc * 16
     t, s = pack.split((TILE_BYTES, SF_BYTES), dim=-1)
     return _untiles(t, rows, kb), _unsf_images(s, rows, ks)
+
+
+def pack_items(w: torch.Tensor) -> torch.Tensor:
+    """A row-major GEMM weight [N, K] (bf16, or f32 for the router) -> the item images the item engine streams:
+    [ceil(N / bn)][K / 256][bn rows][256 k + 64 bytes of padding], bn = 64 (bf16) or 16 (f32), rows past N zero. An item
+    (one N block x one K chunk) is then contiguous and arrives by one bulk copy with its rows already at the padded stride
+    the kernel's shared-memory reads want. K must be a multiple of 256."""
+    n, k = w.shape
+    f32 = w.dtype == torch.float32
+    bn, kc, pad = (16, 256, 16) if f32 else (64, 256, 32)
+    if k % kc:
+        raise ValueError(f"K {k} is not a multiple of {kc}")
+    nb = (n + bn - 1) // bn
+    out = torch.zeros(nb, k // kc, bn, kc + pad, dtype=w.dtype, device=w.device)
+    full = n // bn
+    if full:
+        out[:full, :, :, :kc] = w[: full * bn].view(full, bn, k // kc, kc).permute(0, 2, 1, 3)
+    if n % bn:
+        out[full, :, : n % bn, :kc] = w[full * bn :].view(n % bn, k // kc, kc).permute(1, 0, 2)
+    return out

@@ -95,7 +95,7 @@ def test_bind_argument_checks():
     _expect("mk_entry_bind", host.make("MkEntryBind", **{**e, "hidden": 1000}), "hidden 1000")
     _expect("mk_entry_bind", host.make("MkEntryBind", **{**e, "ranks": 3}), r"embed_peer\[2\]")
     h = dict(w=p, x=p, out_peer=[p], rank=0, v_total=1000, col0=0, n_out=250, hidden=1024, rows=16, status=0, flags=0,
-             flags_peer=[], ws=0, ws_bytes=0)
+             flags_peer=[], ws=0, ws_bytes=0, w_packed=0)
     assert _lib().bind("mk_lm_head_bind", None, host.make("MkLmHeadBind", **h)).info().kernels == 1
     need = (1024 // 256) * 16 * 250 * 4 + 512  # with scratch the GEMM runs on the item engine
     assert _lib().bind("mk_lm_head_bind", None, host.make("MkLmHeadBind", **{**h, "ws": 4096, "ws_bytes": need})).info().kernels == 1

@@ -192,6 +192,22 @@ def test_draft_stagewise_and_end_to_end(ranks, rows, pos, commit):
     assert float(d.max()) < 3e-2, d
 
 
+def test_draft_item_images_give_the_same_bits():
+    """The draft's GEMM weights as item images: bit-identical results to row-major weights."""
+    case = synthetic.draft_case(CFG, 2, 16, 40, 7, 11)
+    a, b = DR.DraftWorld(case, DEV), DR.DraftWorld(case, DEV, packed=True)
+    a.run_interleaved()
+    b.run_interleaved()
+    torch.cuda.synchronize()
+    for ra, rb in zip(a.ranks, b.ranks):
+        assert ra.statuses() == [] and rb.statuses() == []
+        for k in ("y", "scores", "verify_ids", "cand", "unary", "hid", "kv", "ctx"):
+            assert torch.equal(getattr(ra, k), getattr(rb, k)), k
+        assert torch.equal(ra.x.gathered, rb.x.gathered)
+        for li in range(CFG.layers):
+            assert torch.equal(ra.k_pool[li], rb.k_pool[li]) and torch.equal(ra.v_pool[li], rb.v_pool[li])
+
+
 def test_draft_step_replays_as_a_graph():
     """A lone rank: the whole launch list under programmatic dependent launch, eager and as one CUDA graph, gives the
     stagewise run's results bit for bit; a second replay after new step words moves the block."""

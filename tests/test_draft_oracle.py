@@ -86,7 +86,7 @@ def test_draft_binds_validate_without_a_gpu():
     c = lib.dflash_constants(sh)
     assert (c.coeffs, c.qkv_row, c.kv_rows_n, c.attn_splits, c.topk_chunks) == (128, 1024, 1024, 2, 1)
     assert c.ws_bytes >= (5 * 512 // 256) * 16 * 256 * 4 + 512
-    common = dict(ws=P, flags=0, flags_peer=[], status=P, wait_budget=0, eps=1e-5)
+    common = dict(ws=P, flags=0, flags_peer=[], status=P, wait_budget=0, eps=1e-5, packed=0)
     entry = dict(cap=[P] * 5, words=P, embed_peer=[P, P], shard_rows=1024, mask_id=2002, w_fc=P, hid_norm=P, in_norm=P, w_kv=P,
                  k_norm=[P, P], k_pool=[P, P], v_pool=[P, P], pool_rows=64, rope=P, rope_rows=64, feats=P, ctx_raw_peer=[0, P], ctx=P,
                  kv=P, x=P, h=P, **common)  # fmt: skip
@@ -103,7 +103,7 @@ def test_draft_binds_validate_without_a_gpu():
     with pytest.raises(RuntimeError, match="w_down"):
         lib.dflash_bind("mk_dflash_layer_bind", None, sh, host.make("MkDflashLayerBind", **{**layer, "w_down": 0}))
     head = dict(y=P, w_hproj=P, hid=P, logits=P, pred_codebook=P, succ_codebook=P, words=P, keys=P, cand=P, unary=P, scores=P,
-                pick=P, drafts=P, verify_ids=P, mult=0.17, cap=20.0, ws=P, flags=0, contributors=0, status=P, wait_budget=0)  # fmt: skip
+                pick=P, drafts=P, verify_ids=P, mult=0.17, cap=20.0, ws=P, flags=0, contributors=0, status=P, wait_budget=0, packed=1)  # fmt: skip
     assert lib.dflash_bind("mk_dflash_draft_head_bind", None, sh, host.make("MkDflashDraftHeadBind", **head)).info().kernels == 3
     for bad, why in ((dict(q_heads=3), "heads"), (dict(hidden=768), "hidden"), (dict(inter=300), "inter"), (dict(rows=17), "rows"),
                      (dict(conv_groups=128), "conv_groups"), (dict(selector_rank=600), "selector_rank")):  # fmt: skip
@@ -113,3 +113,20 @@ def test_draft_binds_validate_without_a_gpu():
     assert lib.bind("mk_dflash_kv_sync_bind", None, host.make("MkDflashKvSyncBind", **sync)).info().kernels == 1
     with pytest.raises(RuntimeError, match="row_bytes"):
         lib.bind("mk_dflash_kv_sync_bind", None, host.make("MkDflashKvSyncBind", **{**sync, "row_bytes": 100}))
+
+
+def test_item_images_hold_the_matrix():
+    from sgl_muse_mega_b200.muse_spark.b200 import weights as W
+
+    g = torch.Generator().manual_seed(0)
+    for dtype, bn, pad in ((torch.bfloat16, 64, 32), (torch.float32, 16, 16)):
+        w = torch.randn(150, 512, generator=g).to(dtype)
+        img = W.pack_items(w)
+        nb = (150 + bn - 1) // bn
+        assert img.shape == (nb, 2, bn, 256 + pad) and img.is_contiguous()
+        for n, k in ((0, 0), (63, 255), (64, 256), (149, 511), (100, 300)):
+            assert img[n // bn, k // 256, n % bn, k % 256] == w[n, k]
+        assert float(img[..., 256:].abs().sum()) == 0  # the row padding
+        assert float(img[nb - 1, :, 150 - (nb - 1) * bn :].abs().sum()) == 0  # rows past N
+    with pytest.raises(ValueError):
+        W.pack_items(torch.zeros(64, 300, dtype=torch.bfloat16))

@@ -186,3 +186,21 @@ def _module(device):
         with torch.cuda.device(device):
             _MOD[device] = host_lib().load()
     return _MOD[device]
+
+
+@pytest.mark.parametrize("name", ["small_fp4_swa_tp2", "small_bf16_tail_tp4"])
+def test_item_images_give_the_same_bits(name, device):
+    """The dense weights as item images (one bulk copy an item) against row-major weights (one copy a row): the same
+    arithmetic in the same order, so every output of the layer is bit-identical."""
+    cfg, kw = CASES[name]
+    case = synthetic.layer_case(cfg, **kw)
+    a, b = L.LayerWorld(case, device), L.LayerWorld(case, device, packed=True)
+    a.run_interleaved()
+    b.run_interleaved()
+    torch.cuda.synchronize()
+    for ra, rb in zip(a.ranks, b.ranks):
+        assert ra.launch_record.status(torch.cuda.current_stream().cuda_stream).code == 0
+        assert rb.launch_record.status(torch.cuda.current_stream().cuda_stream).code == 0
+        for k, v in ra.o.items():
+            if torch.is_tensor(v):
+                assert torch.equal(v, rb.o[k]), k

@@ -130,3 +130,88 @@ def test_two_gpu_world_matches_the_emulated_world(graph, fused):
     for i in range(STEPS):  # every rank of the real world holds the same gathered logits and words, bit for bit
         for k in ("words", "top1", "logits"):
             assert torch.equal(got[0]["res"][i][k], got[1]["res"][i][k]), (i, k)
+
+
+# ---- the DFlash2 draft across two GPUs ------------------------------------------------------------------------------------
+
+
+def _draft_case():
+    from sgl_muse_mega_b200.muse_spark.b200.dflash import synthetic as dsyn
+    from sgl_muse_mega_b200.muse_spark.b200.dflash.weights import DraftConfig
+
+    cfg = DraftConfig(hidden=512, layers=2, q_heads=8, kv_heads=4, head_dim=128, inter=1024, vocab=2048, sliding_window=24,
+                      mask_id=2002, selector_rank=64, top_k=16)  # fmt: skip
+    return dsyn.draft_case(cfg, 2, 16, 40, 7, 13)
+
+
+def _draft_rank_main(rank, world, port, out):
+    import torch.distributed as dist
+
+    from sgl_muse_mega_b200.common import host, symm
+    from sgl_muse_mega_b200.muse_spark.b200.dflash import draft as DR
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    device = torch.device(f"cuda:{rank}")
+    torch.cuda.set_device(device)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        case = _draft_case()
+        cfg = case.cfg
+        lib = host.library()
+        module = lib.load()
+        arena = symm.Arena(lib, DR.exchange_layout(cfg, world, case.rows, with_embed=True), device)
+        w, t = case.shards[rank]
+        own, peers = DR.connect_exchange(arena, t.embed.to(device), None, rank, world)
+        dr = DR.DraftRank(cfg, w, t, rank, world, device, rows=case.rows, pool_rows=72, rope_rows=72, lib=lib, module=module,
+                          exchange=own, wait_budget=1 << 24)  # fmt: skip
+        dr.bind(peers)
+        dr.set_state(case.pos, case.anchor, case.commit, case.caps)
+        dr.load_history(case.hist_k, case.hist_v)
+        torch.cuda.synchronize()
+        dist.barrier()
+        s = torch.cuda.current_stream().cuda_stream
+        res = []
+        for step in range(2):  # eager with programmatic dependent launch, then the same step again (the words did not move)
+            dr.launch_all(s, pdl=True)
+            torch.cuda.synchronize()
+            res.append(dict(y=dr.y.cpu().clone(), ids=dr.verify_ids.cpu().clone(), scores=dr.scores.cpu().clone(),
+                            logits=dr.x.gathered.cpu().clone()))  # fmt: skip
+        dist.barrier()
+        out[rank] = dict(res=res, status=dr.statuses())
+        del peers
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_draft_matches_the_emulated_world():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from sgl_muse_mega_b200.muse_spark.b200.dflash import draft as DR
+
+    world = 2
+    case = _draft_case()
+    emu = DR.DraftWorld(case, torch.device("cuda:0"), pool_rows=72)
+    emu.run_interleaved()
+    torch.cuda.synchronize()
+    ref = [dict(y=dr.y.cpu(), ids=dr.verify_ids.cpu(), scores=dr.scores.cpu(), logits=dr.x.gathered.cpu()) for dr in emu.ranks]
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as m:
+        out = m.dict()
+        port = 29700 + os.getpid() % 200
+        procs = [ctx.Process(target=_draft_rank_main, args=(r, world, port, out)) for r in range(world)]
+        for p in procs:
+            p.start()
+        try:
+            for p in procs:
+                p.join(600)
+                assert p.exitcode == 0, f"rank process exit code {p.exitcode}"
+        finally:
+            for p in procs:  # only the processes started above, by handle
+                if p.is_alive():
+                    p.kill()
+        got = dict(out)
+    for r in range(world):
+        assert got[r]["status"] == [], got[r]["status"]
+        for step in range(2):
+            for k in ("y", "ids", "scores", "logits"):
+                assert torch.equal(got[r]["res"][step][k], ref[r][k]), (r, step, k)
