@@ -218,7 +218,7 @@ typedef struct MkLayerBind {
     // mk_launch_info.kernels tells which form was bound.
     int64_t fused;
     // 1: w_o, w_p, w_r, w_up and w_qkv are item images of the item engine instead of row-major matrices (forms 0 and 1
-    // only): [ceil(N / 64)][K / 256][64 rows][256 k + 32 pad] bf16 ([N / 16][K / 256][16 rows][256 k + 16 pad] f32 for
+    // only): [ceil(N / 64)][K / 512][64 rows][512 k + 32 pad] bf16 ([N / 16][K / 512][16 rows][512 k + 16 pad] f32 for
     // w_r), rows past N zero; w_p and w_up then hold this rank's node block only (P / node_ranks and H / node_ranks
     // rows). One bulk copy brings an item in, instead of one per weight row.
     int64_t dense_packed;

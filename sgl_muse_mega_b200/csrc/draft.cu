@@ -531,7 +531,8 @@ __global__ void __launch_bounds__(kRowThreads) dlattice_kernel(const DLatticeArg
     __shared__ unsigned long long red[(kRowThreads / 32) * kDraftTopK];
     __shared__ unsigned long long s_cur[kDraftTopK], s_prev[kDraftTopK];
     __shared__ float s_hid[512];
-    __shared__ unsigned s_A[kDraftTopK][257], s_S[kDraftTopK][257];  // codebook rows as bf16 pairs, padded against bank conflicts
+    __shared__ __align__(16) unsigned s_A[kDraftTopK][257];  // codebook rows as bf16 pairs, padded against bank conflicts
+    __shared__ __align__(16) unsigned s_S[kDraftTopK][257];
     __shared__ long long s_pred[kDraftTopK];
     __shared__ float s_unary[kDraftTopK];
     __shared__ unsigned s_last;
@@ -585,12 +586,18 @@ __global__ void __launch_bounds__(kRowThreads) dlattice_kernel(const DLatticeArg
     __syncthreads();
     if (s_last == 0) return;
     __threadfence();
+    // the whole lattice (gamma x 16 x 16 scores, 15 KB) and the candidates into shared memory, then one thread walks it
+    float* s_sc = (float*)&s_A[0][0];             // 16 x 257 words hold gamma x 256 scores (gamma <= 15)
+    long long* s_cd = (long long*)&s_S[0][0];     // gamma x 16 candidates
+    for (int i = tid; i < a.gamma * kDraftTopK * kDraftTopK; i += kRowThreads) s_sc[i] = __ldcg(a.scores + i);
+    for (int i = tid; i < a.gamma * kDraftTopK; i += kRowThreads) s_cd[i] = __ldcg(a.cand + i);
+    __syncthreads();
     if (tid == 0) {
         *a.counter = 0;
         int prev = 0;
         a.verify_ids[0] = a.words[kWordAnchor];
         for (int s = 0; s < a.gamma; ++s) {
-            const volatile float* row = a.scores + ((size_t)s * kDraftTopK + prev) * kDraftTopK;
+            const float* row = s_sc + (s * kDraftTopK + prev) * kDraftTopK;
             int idx = -1;
             for (int c = 0; c < kDraftTopK && idx < 0; ++c)
                 if (row[c] != row[c]) idx = c;  // the first NaN wins
@@ -603,7 +610,7 @@ __global__ void __launch_bounds__(kRowThreads) dlattice_kernel(const DLatticeArg
                         idx = c;
                     }
             }
-            const long long tok = ((const volatile long long*)a.cand)[(size_t)s * kDraftTopK + idx];
+            const long long tok = s_cd[s * kDraftTopK + idx];
             a.drafts[s] = tok;
             a.verify_ids[1 + s] = tok;
             a.pick[s] = idx;

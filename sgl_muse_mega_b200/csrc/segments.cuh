@@ -30,11 +30,11 @@ namespace mk {
 
 constexpr int kSegThreads = 512;
 constexpr int kSegWarps = kSegThreads / 32;
-constexpr int kChunkK = 256;                          // k per GEMM item
-constexpr int kSegBufs = 4;                           // items in flight per CTA
+constexpr int kChunkK = 512;                          // k per GEMM item
+constexpr int kSegPieces = 8;                         // bulk copies per packed item image (69,632 or 33,792 bytes)
 constexpr int kSegBufBytes = 80 * (kChunkK * 2 + 64); // 64 weight + 16 activation rows of bf16 (f32: 16 + 16 rows fit too)
 constexpr int kSegRedFloats = kSegWarps * 8 * 32;     // per-warp accumulator exchange
-constexpr size_t kSegSmem = kSegBufs * (size_t)kSegBufBytes + kSegRedFloats * 4 + 1024;
+constexpr size_t kSegSmem = 2 * (size_t)kSegBufBytes + kSegRedFloats * 4 + 1024;
 
 __host__ __device__ inline int seg_bn(const SegGemm& g) { return g.f32 ? 16 : 64; }
 __host__ __device__ inline int seg_items(const SegGemm& g) { return ((g.N + seg_bn(g) - 1) / seg_bn(g)) * (g.K / kChunkK); }
@@ -62,14 +62,16 @@ __device__ __forceinline__ void grid_barrier(const GridBarrier& gb, int site) {
     __syncthreads();
 }
 
-// The CTA's streaming state: the buffers, their copy barriers and phases.
+// The CTA's streaming state: two buffers, their copy barriers and phases.
 struct SegPipe {
-    unsigned char* buf[kSegBufs];
+    unsigned char* buf[2];
     float* red;
-    uint64_t* bar;  // [kSegBufs], each initialised with count 2: the weight request and the activation request
+    uint64_t* bar;  // [2]; a phase completes with the weight request's arrival and bytes and one arrival per thread for its
+                    // share of the activation rows
     int* abort;
-    uint32_t phase[kSegBufs];
+    uint32_t phase[2];
     int* status;
+    int tn;  // item-trace cursor (SEG_TRACE_ITEMS builds only)
 };
 
 __device__ __forceinline__ int seg_row_bytes(const SegGemm& g) { return kChunkK * (g.f32 ? 4 : 2) + 64; }
@@ -80,12 +82,10 @@ __device__ __forceinline__ void seg_issue_w(const SegGemm& g, int item, SegPipe&
     const int bn = seg_bn(g), es = g.f32 ? 4 : 2, rowb = seg_row_bytes(g);
     const int valid = min(bn, g.N - nb * bn);
     const int tid = threadIdx.x;
-    if (g.packed) {  // the item's image is contiguous, padded rows included: one copy
-        const uint32_t img = (uint32_t)(bn * rowb);
-        if (tid == 0) {
-            umma::bulk_g2s(p.buf[b], g.w + (size_t)item * img, img, &p.bar[b]);
-            umma::mbar_arrive_expect_tx(&p.bar[b], img);
-        }
+    if (g.packed) {  // the item's image is contiguous, padded rows included: a few large copies instead of one per row
+        const uint32_t img = (uint32_t)(bn * rowb), piece = img / kSegPieces;
+        if (tid == 0) umma::mbar_arrive_expect_tx(&p.bar[b], img);
+        if (tid < kSegPieces) umma::bulk_g2s(p.buf[b] + tid * piece, g.w + (size_t)item * img + tid * piece, piece, &p.bar[b]);
         return;
     }
     if (tid < valid)
@@ -94,26 +94,32 @@ __device__ __forceinline__ void seg_issue_w(const SegGemm& g, int item, SegPipe&
     if (tid == 0) umma::mbar_arrive_expect_tx(&p.bar[b], (uint32_t)(valid * kChunkK * es));
 }
 
-// Requests item `item`'s activation slice into buffer b (after whatever guards the activations). Rows past the window
-// and weight rows past N keep whatever the buffer held: an MMA output depends on its own weight row and its own window
-// row only, and outputs outside [0, M) x [0, N) are never stored.
+// Requests item `item`'s activation slice (M rows x one K chunk, at most 16 KB of bf16) into buffer b: every thread copies
+// 32 bytes (64 for the f32 router) with cp.async and hands their completion to the buffer's barrier, which therefore
+// counts one arrival per thread besides the weight request. (Sixteen small bulk copies per item kept the copy engine
+// busier than the item's weights did.) Rows past the window and weight rows past N keep whatever the buffer held: an MMA
+// output depends on its own weight row and its own window row only, and outputs outside [0, M) x [0, N) are never stored.
 __device__ __forceinline__ void seg_issue_x(const SegGemm& g, int item, SegPipe& p, int b) {
     const int nsplit = g.K / kChunkK, ks = item % nsplit;
-    const int bn = seg_bn(g), es = g.f32 ? 4 : 2, rowb = seg_row_bytes(g);
-    const int tid = threadIdx.x;
-    if (tid < g.M)
-        umma::bulk_g2s(p.buf[b] + (bn + tid) * rowb, g.x + (size_t)tid * g.ldx + (size_t)ks * kChunkK * es, kChunkK * es, &p.bar[b]);
-    if (tid == 0) umma::mbar_arrive_expect_tx(&p.bar[b], (uint32_t)(g.M * kChunkK * es));
+    const int bn = seg_bn(g), es = g.f32 ? 4 : 2, rowb = seg_row_bytes(g), per_row = kChunkK * es / 16;
+    const int n = g.f32 ? 4 : 2;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (j >= n) break;
+        const int piece = threadIdx.x + j * kSegThreads, m = piece / per_row, c = piece - m * per_row;
+        if (m < g.M) cp_async16(p.buf[b] + (bn + m) * rowb + c * 16, g.x + (size_t)m * g.ldx + (size_t)ks * kChunkK * es + c * 16, true);
+    }
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(umma::smem_u32(&p.bar[b])) : "memory");
 }
 
-// Waits for the item in buffer b and adds its products to the warp's accumulators (row group wn = warp % WN, k slice
-// wk = warp / WN of the chunk). All threads.
+// Multiplies the item in buffer b and stores its partial sums. All threads.
 template <bool WF32>
-__device__ __forceinline__ void seg_mma(const SegGemm& g, int item, SegPipe& p, int b, float (&acc0)[4], float (&acc1)[4]) {
+__device__ __forceinline__ void seg_compute(const SegGemm& g, int item, SegPipe& p, int b) {
     constexpr int WN = WF32 ? 1 : 4, WK = kSegWarps / WN, ES = WF32 ? 4 : 2, KSTEP = 64 / ES, BN = 16 * WN;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t = lane & 3;
     const int wn = warp % WN, wk = warp / WN;
-    constexpr int rowb = kChunkK * ES + 64;
+    const int nsplit = g.K / kChunkK, nb = item / nsplit, ks = item - nb * nsplit;
+    const int rowb = kChunkK * ES + 64;
     if (!umma::mbar_wait(&p.bar[b], p.phase[b], p.abort)) {
         if (atomicExch(p.abort, 1) == 0 && p.status != nullptr && atomicCAS(p.status, 0, 3) == 0) {
             p.status[1] = 210;
@@ -122,15 +128,16 @@ __device__ __forceinline__ void seg_mma(const SegGemm& g, int item, SegPipe& p, 
         }
     }
     p.phase[b] ^= 1u;
+#ifdef SEG_TRACE_ITEMS
+    if (blockIdx.x == 0 && threadIdx.x == 0 && p.status && p.tn < 62) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); ((unsigned long long*)(p.status + 64))[32 + p.tn++] = t; }
+#endif
     constexpr int kw = kChunkK / WK, nsteps = kw / KSTEP;
     const unsigned char* wa0 = p.buf[b] + (wn * 16 + gq) * rowb + (wk * kw) * ES + t * 16;
     const unsigned char* wa1 = wa0 + 8 * rowb;
     const unsigned char* xs0 = p.buf[b] + (BN + gq) * rowb + (wk * kw) * ES + t * 16;
     const unsigned char* xs1 = xs0 + 8 * rowb;
+    float acc0[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0};
     const bool two = g.M > 8;
-#ifdef SEG_NO_MMA  // timing experiments only: the stream without the arithmetic
-    if (p.buf[b] == nullptr)
-#endif
 #pragma unroll
     for (int s = 0; s < nsteps; ++s) {
         uint4 wa = *(const uint4*)(wa0 + s * 64), wb = *(const uint4*)(wa1 + s * 64);
@@ -155,28 +162,18 @@ __device__ __forceinline__ void seg_mma(const SegGemm& g, int item, SegPipe& p, 
             }
         }
     }
-}
-
-// Ends a run of consecutive K chunks of one N block: the k-slice warps of a row group meet in shared memory, in warp order,
-// and the run's partial sums go to slot `slot` (the run's first chunk) of the scratch; the accumulators restart at 0.
-template <bool WF32>
-__device__ __forceinline__ void seg_flush(const SegGemm& g, int nb, int slot, SegPipe& p, float (&acc0)[4], float (&acc1)[4]) {
-    constexpr int WN = WF32 ? 1 : 4, WK = kSegWarps / WN, BN = 16 * WN;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int wn = warp % WN, wk = warp / WN;
+    // the K warps of a row group meet in shared memory, in warp order
     {
         float* r = p.red + ((wk * WN + wn) * 8) * 32 + lane;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             r[i * 32] = acc0[i];
             r[(4 + i) * 32] = acc1[i];
-            acc0[i] = 0.f;
-            acc1[i] = 0.f;
         }
     }
     __syncthreads();
     // accumulator register i of lane ln of row group rn holds (row ln/4 + 8 (i/2 % 2), window row 8 (i/4) + 2 (ln%4) + i%2)
-    float* part = g.part + (size_t)slot * 16 * g.N;
+    float* part = g.part + (size_t)ks * 16 * g.N;
     for (int e = tid; e < WN * 256; e += kSegThreads) {
         const int rn = e >> 8, i = (e >> 5) & 7, ln = e & 31;
         float v = 0.f;
@@ -186,36 +183,46 @@ __device__ __forceinline__ void seg_flush(const SegGemm& g, int nb, int slot, Se
         const int m = (i >> 2) * 8 + 2 * (ln & 3) + (i & 1);
         if (m < g.M && n < g.N) part[(size_t)m * g.N + n] = v;
     }
-    __syncthreads();  // the exchange area is free again
+    __syncthreads();  // the buffer and the exchange area are free again
+#ifdef SEG_TRACE_ITEMS
+    if (blockIdx.x == 0 && threadIdx.x == 0 && p.status && p.tn < 62) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); ((unsigned long long*)(p.status + 64))[32 + p.tn++] = t; }
+#endif
 }
 
-// A stage made of up to two GEMMs: items [0, n0) belong to g[0], the rest to g[1]; items of a GEMM are ordered N block by
-// N block, K chunk by K chunk. CTA c owns the contiguous items [c per, (c + 1) per): consecutive chunks of an N block
-// accumulate in registers, so a block's partial sums exist only for its first chunk and for every chunk at which a CTA's
-// range begins (seg_next_slot enumerates them for the finishes).
+// One GEMM stage: this CTA's items (cta, cta + grid, ...). `w_issued` items (0, 1 or 2) already have their weights on the
+// way (seg_prefetch_w before the barrier that guards the activations).
+__device__ __forceinline__ void seg_prefetch_w(const SegGemm& g, SegPipe& p, int first_item, int stride, int total) {
+    if (first_item < total) seg_issue_w(g, first_item, p, 0);
+    if (first_item + stride < total) seg_issue_w(g, first_item + stride, p, 1);
+}
+
+__device__ __forceinline__ void seg_gemm_stage(const SegGemm& g, SegPipe& p, int first_item, int stride, int total, bool w_issued) {
+    int it0 = first_item, it1 = first_item + stride;
+    if (it0 < total) {
+        if (!w_issued) seg_issue_w(g, it0, p, 0);
+        seg_issue_x(g, it0, p, 0);
+    }
+    if (it1 < total) {
+        if (!w_issued) seg_issue_w(g, it1, p, 1);
+        seg_issue_x(g, it1, p, 1);
+    }
+    int b = 0;
+    for (int it = first_item; it < total; it += stride, b ^= 1) {
+        if (g.f32) seg_compute<true>(g, it, p, b);
+        else seg_compute<false>(g, it, p, b);
+        const int nxt = it + 2 * stride;
+        if (nxt < total) {
+            seg_issue_w(g, nxt, p, b);
+            seg_issue_x(g, nxt, p, b);
+        }
+    }
+}
+
+// A stage made of up to two GEMMs: items [0, n0) belong to g[0], the rest to g[1].
 struct SegStage {
     SegGemm g[2];
-    int n0, total, per;
+    int n0, total;
 };
-__device__ __forceinline__ SegStage seg_stage(const SegGemm& a, const SegGemm* b) {
-    SegStage s;
-    s.g[0] = a;
-    s.g[1] = b != nullptr ? *b : a;
-    s.n0 = seg_items(a);
-    s.total = s.n0 + (b != nullptr ? seg_items(*b) : 0);
-    s.per = (s.total + (int)gridDim.x - 1) / (int)gridDim.x;
-    if (s.per < 1) s.per = 1;
-    s.g[0].item0 = 0;
-    s.g[1].item0 = s.n0;
-    s.g[0].per = s.g[1].per = s.per;
-    return s;
-}
-// The next chunk slot after `ks` that holds partial sums, for the N block whose chunk 0 is stage item `base`.
-__device__ __forceinline__ int seg_next_slot(int base, int ks, int per) { return ((base + ks) / per + 1) * per - base; }
-#define SEG_FOR_SLOTS(g, nb, ks)                                                                     \
-    for (int ks = 0, base_ = (g).item0 + (nb) * ((g).K / kChunkK), nsplit_ = (g).K / kChunkK; ks < nsplit_; \
-         ks = seg_next_slot(base_, ks, (g).per))
-
 __device__ __forceinline__ void seg_stage_issue_w(const SegStage& s, int item, SegPipe& p, int b) {
     if (item < s.n0) seg_issue_w(s.g[0], item, p, b);
     else seg_issue_w(s.g[1], item - s.n0, p, b);
@@ -224,39 +231,27 @@ __device__ __forceinline__ void seg_stage_issue_x(const SegStage& s, int item, S
     if (item < s.n0) seg_issue_x(s.g[0], item, p, b);
     else seg_issue_x(s.g[1], item - s.n0, p, b);
 }
-// Requests the weights of this CTA's first items (they never depend on a predecessor). Every buffer must be free.
 __device__ __forceinline__ void seg_stage_prefetch_w(const SegStage& s, SegPipe& p) {
-    const int lo = blockIdx.x * s.per, hi = min(s.total, lo + s.per);
-#pragma unroll
-    for (int j = 0; j < kSegBufs; ++j)
-        if (lo + j < hi) seg_stage_issue_w(s, lo + j, p, j);
+    const int first = blockIdx.x, stride = gridDim.x;
+    if (first < s.total) seg_stage_issue_w(s, first, p, 0);
+    if (first + stride < s.total) seg_stage_issue_w(s, first + stride, p, 1);
 }
-// Runs the stage's items of this CTA; the weights of its first items are already requested (seg_stage_prefetch_w).
+// Runs the stage's items of this CTA; the weights of its first two items are already requested (seg_stage_prefetch_w).
 __device__ __forceinline__ void seg_stage_run(const SegStage& s, SegPipe& p) {
-    const int lo = blockIdx.x * s.per, hi = min(s.total, lo + s.per);
-#pragma unroll
-    for (int j = 0; j < kSegBufs; ++j)
-        if (lo + j < hi) seg_stage_issue_x(s, lo + j, p, j);
-    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
-    int run_slot = -1;
-    for (int it = lo; it < hi; ++it) {
-        const int b = (it - lo) & (kSegBufs - 1);
+    const int first = blockIdx.x, stride = gridDim.x;
+    if (first < s.total) seg_stage_issue_x(s, first, p, 0);
+    if (first + stride < s.total) seg_stage_issue_x(s, first + stride, p, 1);
+    int b = 0;
+    for (int it = first; it < s.total; it += stride, b ^= 1) {
         const bool second = it >= s.n0;
         const SegGemm& g = s.g[second ? 1 : 0];
         const int local = second ? it - s.n0 : it;
-        const int nsplit = g.K / kChunkK, nb = local / nsplit, ks = local - nb * nsplit;
-        if (run_slot < 0) run_slot = ks;
-        if (g.f32) seg_mma<true>(g, local, p, b, acc0, acc1);
-        else seg_mma<false>(g, local, p, b, acc0, acc1);
-        __syncthreads();  // every warp has read buffer b
-        if (it + kSegBufs < hi) {
-            seg_stage_issue_w(s, it + kSegBufs, p, b);
-            seg_stage_issue_x(s, it + kSegBufs, p, b);
-        }
-        if (ks == nsplit - 1 || it + 1 == hi) {  // the N block, or this CTA's range, ends here
-            if (g.f32) seg_flush<true>(g, nb, run_slot, p, acc0, acc1);
-            else seg_flush<false>(g, nb, run_slot, p, acc0, acc1);
-            run_slot = -1;
+        if (g.f32) seg_compute<true>(g, local, p, b);
+        else seg_compute<false>(g, local, p, b);
+        const int nxt = it + 2 * stride;
+        if (nxt < s.total) {
+            seg_stage_issue_w(s, nxt, p, b);
+            seg_stage_issue_x(s, nxt, p, b);
         }
     }
 }
@@ -265,11 +260,12 @@ __device__ __forceinline__ void seg_stage_run(const SegStage& s, SegPipe& p) {
 
 // out[m, col0 + n] = bf16(sum_ks part[ks][m][n]) into every destination (own buffer and peers'); all CTAs share the work.
 __device__ __forceinline__ void seg_finish_bf16(const SegGemm& g, bf16* const* out, int n_out, long long ldo, long long off0) {
+    const int nsplit = g.K / kChunkK;
     const long long total = (long long)g.M * g.N;
     for (long long i = (long long)blockIdx.x * kSegThreads + threadIdx.x; i < total; i += (long long)gridDim.x * kSegThreads) {
         const int m = (int)(i / g.N), n = (int)(i - (long long)m * g.N);
         float v = 0.f;
-        SEG_FOR_SLOTS(g, n / seg_bn(g), ks) v += g.part[((size_t)ks * 16 + m) * g.N + n];
+        for (int ks = 0; ks < nsplit; ++ks) v += g.part[((size_t)ks * 16 + m) * g.N + n];
         const bf16 b = __float2bfloat16_rn(v);
         for (int d = 0; d < n_out; ++d) out[d][off0 + (long long)m * ldo + n] = b;
     }
@@ -278,13 +274,16 @@ __device__ __forceinline__ void seg_finish_bf16(const SegGemm& g, bf16* const* o
 // SwiGLU over a [gate rows | up rows] GEMM: out[m, n] = bf16(silu(bf16(gate[m, n])) x bf16(up[m, n])), n < N / 2; f32 steps
 // in the order gate / (1 + exp(-gate)) x up.
 __device__ __forceinline__ void seg_finish_silu(const SegGemm& g, bf16* const* out, int n_out, long long ldo, long long off0) {
-    const int half = g.N / 2;
+    const int nsplit = g.K / kChunkK, half = g.N / 2;
     const long long total = (long long)g.M * half;
     for (long long i = (long long)blockIdx.x * kSegThreads + threadIdx.x; i < total; i += (long long)gridDim.x * kSegThreads) {
         const int m = (int)(i / half), n = (int)(i - (long long)m * half);
         float gate = 0.f, up = 0.f;
-        SEG_FOR_SLOTS(g, n / seg_bn(g), ks) gate += g.part[((size_t)ks * 16 + m) * g.N + n];
-        SEG_FOR_SLOTS(g, (half + n) / seg_bn(g), ks) up += g.part[((size_t)ks * 16 + m) * g.N + half + n];
+        for (int ks = 0; ks < nsplit; ++ks) {
+            const float* row = g.part + ((size_t)ks * 16 + m) * g.N;
+            gate += row[n];
+            up += row[half + n];
+        }
         gate = bf16_round(gate);
         up = bf16_round(up);
         const bf16 b = __float2bfloat16_rn(__fmul_rn(__fdiv_rn(gate, __fadd_rn(1.0f, expf(-gate))), up));
@@ -295,21 +294,23 @@ __device__ __forceinline__ void seg_finish_silu(const SegGemm& g, bf16* const* o
 // out[m, off0 + n] = sum_ks part[ks][m][n] as f32 into every destination (the lm_head's gathered logits); all CTAs share the
 // work.
 __device__ __forceinline__ void seg_finish_f32_push(const SegGemm& g, bf16* const* out, int n_out, long long ldo, long long off0) {
+    const int nsplit = g.K / kChunkK;
     const long long total = (long long)g.M * g.N;
     for (long long i = (long long)blockIdx.x * kSegThreads + threadIdx.x; i < total; i += (long long)gridDim.x * kSegThreads) {
         const int m = (int)(i / g.N), n = (int)(i - (long long)m * g.N);
         float v = 0.f;
-        SEG_FOR_SLOTS(g, n / seg_bn(g), ks) v += g.part[((size_t)ks * 16 + m) * g.N + n];
+        for (int ks = 0; ks < nsplit; ++ks) v += g.part[((size_t)ks * 16 + m) * g.N + n];
         for (int d = 0; d < n_out; ++d) ((float*)out[d])[off0 + (long long)m * ldo + n] = v;
     }
 }
 
 // logits[m, n] = sum_ks part[ks][m][n] (f32), by one CTA.
 __device__ __forceinline__ void seg_finish_f32_cta(const SegGemm& g, float* out) {
+    const int nsplit = g.K / kChunkK;
     for (int i = threadIdx.x; i < g.M * g.N; i += kSegThreads) {
         const int m = i / g.N, n = i - m * g.N;
         float v = 0.f;
-        SEG_FOR_SLOTS(g, n / seg_bn(g), ks) v += g.part[((size_t)ks * 16 + m) * g.N + n];
+        for (int ks = 0; ks < nsplit; ++ks) v += g.part[((size_t)ks * 16 + m) * g.N + n];
         out[(size_t)m * g.N + n] = v;
     }
 }
@@ -317,12 +318,12 @@ __device__ __forceinline__ void seg_finish_f32_cta(const SegGemm& g, float* out)
 // The qkv epilogue (as gemm.cu mode 1): one warp per (row, head); bf16(acc), per-head qk norm (q scaled), interleaved-pair
 // RoPE, K and V rows appended to the successor's pool.
 __device__ __forceinline__ void seg_finish_qkv(const SegGemm& g, const GemmArgs& e) {
-    const int heads = g.N / kHeadDim;
+    const int nsplit = g.K / kChunkK, heads = g.N / kHeadDim;
     const int lane = threadIdx.x & 31;
     for (int w = blockIdx.x * kSegWarps + (threadIdx.x >> 5); w < g.M * heads; w += gridDim.x * kSegWarps) {
         const int m = w / heads, head = w - m * heads;
         float y0 = 0.f, y1 = 0.f;
-        SEG_FOR_SLOTS(g, head * kHeadDim / seg_bn(g), ks) {
+        for (int ks = 0; ks < nsplit; ++ks) {
             const float2 v = *(const float2*)(g.part + ((size_t)ks * 16 + m) * g.N + head * kHeadDim + 2 * lane);
             y0 += v.x;
             y1 += v.y;
@@ -486,7 +487,7 @@ __device__ __forceinline__ void seg_trace(int* status, int slot) {
 }
 
 struct SegShared {
-    uint64_t bar[kSegBufs];
+    uint64_t bar[2];
     int abort;
     float red[33];
     float redk[kMaxTopk][kSegWarps + 1];
@@ -497,17 +498,18 @@ struct SegShared {
 };
 
 __device__ __forceinline__ void seg_setup(SegPipe& p, SegShared& sh, unsigned char* dyn, int* status) {
-    for (int j = 0; j < kSegBufs; ++j) {
-        p.buf[j] = dyn + (size_t)j * kSegBufBytes;
-        p.phase[j] = 0;
-    }
-    p.red = (float*)(dyn + (size_t)kSegBufs * kSegBufBytes);
+    p.buf[0] = dyn;
+    p.buf[1] = dyn + kSegBufBytes;
+    p.red = (float*)(dyn + 2 * kSegBufBytes);
     p.bar = sh.bar;
     p.abort = &sh.abort;
+    p.phase[0] = p.phase[1] = 0;
     p.status = status;
+    p.tn = 0;
     if (threadIdx.x == 0) {
         sh.abort = 0;
-        for (int j = 0; j < kSegBufs; ++j) umma::mbar_init(&sh.bar[j], 2);
+        umma::mbar_init(&sh.bar[0], 1 + kSegThreads);
+        umma::mbar_init(&sh.bar[1], 1 + kSegThreads);
         umma::mbar_fence_init();
     }
     __syncthreads();
@@ -522,27 +524,28 @@ __global__ void __launch_bounds__(kSegThreads, 1) seg_gemm_kernel(const SegGemmA
     __shared__ SegShared sh;
     SegPipe p;
     seg_setup(p, sh, dyn, a.status);
-    const SegStage st = seg_stage(a.g[0], a.n_gemm > 1 ? &a.g[1] : nullptr);
+    SegStage st{{a.g[0], a.g[a.n_gemm > 1 ? 1 : 0]}, seg_items(a.g[0]), seg_items(a.g[0]) + (a.n_gemm > 1 ? seg_items(a.g[1]) : 0)};
     seg_stage_prefetch_w(st, p);  // static weights: requested while the predecessor still runs
     griddep_wait();
     seg_stage_run(st, p);
     grid_barrier(a.gb, 30 + a.finish);
     if (a.finish == 2) {
-        seg_finish_qkv(st.g[0], a.epi);
+        seg_finish_qkv(a.g[0], a.epi);
     } else if (a.finish == 3) {
-        seg_finish_silu(st.g[0], a.out, a.n_out, a.ldo, a.off0);
+        seg_finish_silu(a.g[0], a.out, a.n_out, a.ldo, a.off0);
     } else if (a.finish == 4) {
-        seg_finish_f32_push(st.g[0], a.out, a.n_out, a.ldo, a.off0);
+        seg_finish_f32_push(a.g[0], a.out, a.n_out, a.ldo, a.off0);
     } else {
-        seg_finish_bf16(st.g[0], a.out, a.n_out, a.ldo, a.off0);
+        seg_finish_bf16(a.g[0], a.out, a.n_out, a.ldo, a.off0);
         if (a.finish == 1) {
             // the router: f32 logits and, a thread per logit, the routing's selection scores (sigmoid in f64 rounded to
             // f32, plus the expert's bias)
-            const SegGemm& g = st.g[1];
+            const SegGemm& g = a.g[1];
+            const int nsplit = g.K / kChunkK;
             for (int i = blockIdx.x * kSegThreads + threadIdx.x; i < g.M * g.N; i += gridDim.x * kSegThreads) {
                 const int m = i / g.N, n = i - m * g.N;
                 float v = 0.f;
-                SEG_FOR_SLOTS(g, n / seg_bn(g), ks) v += g.part[((size_t)ks * 16 + m) * g.N + n];
+                for (int ks = 0; ks < nsplit; ++ks) v += g.part[((size_t)ks * 16 + m) * g.N + n];
                 a.f32_out[i] = v;
                 if (a.score != nullptr) a.score[i] = (float)(1.0 / (1.0 + exp(-((double)v * a.score_mult)))) + a.score_bias[n];
             }
@@ -558,7 +561,8 @@ __global__ void __launch_bounds__(kSegThreads, 1) segment_a_kernel(const SegAArg
     SegPipe p;
     seg_setup(p, sh, dyn, a.status);
     const int cta = blockIdx.x;
-    const SegStage s1 = seg_stage(a.oproj, nullptr), s3 = seg_stage(a.pooler, &a.router);
+    SegStage s1{{a.oproj, a.oproj}, seg_items(a.oproj), seg_items(a.oproj)};
+    SegStage s3{{a.pooler, a.router}, seg_items(a.pooler), seg_items(a.pooler) + seg_items(a.router)};
     seg_trace(a.status, 0);
     seg_stage_prefetch_w(s1, p);  // static weights: on their way while the attention still runs
     griddep_wait();
@@ -571,7 +575,7 @@ __global__ void __launch_bounds__(kSegThreads, 1) segment_a_kernel(const SegAArg
     grid_barrier(a.gb, 1);
     seg_trace(a.status, 3);
     // this rank's bf16 partial of the all-reduce, pushed into every present rank's workspace
-    seg_finish_bf16(s1.g[0], a.ar_out, a.n_ar, a.oproj.N, a.ar_off);
+    seg_finish_bf16(a.oproj, a.ar_out, a.n_ar, a.oproj.N, a.ar_off);
     xchg_signal(a.sig_ar);
     seg_trace(a.status, 4);
     if (cta < a.post_norm.M) {
@@ -585,11 +589,11 @@ __global__ void __launch_bounds__(kSegThreads, 1) segment_a_kernel(const SegAArg
     seg_trace(a.status, 7);
     grid_barrier(a.gb, 3);
     seg_trace(a.status, 8);
-    seg_finish_bf16(s3.g[0], a.pool_out, a.n_pool, a.pool_ld, a.pool_col0);
+    seg_finish_bf16(a.pooler, a.pool_out, a.n_pool, a.pool_ld, a.pool_col0);
     xchg_signal(a.sig_pool);
     seg_trace(a.status, 9);
     if (cta == (int)gridDim.x - 1) {
-        seg_finish_f32_cta(s3.g[1], a.logits);
+        seg_finish_f32_cta(a.router, a.logits);
         __syncthreads();
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         for (int row = warp; row < a.topk.M; row += kSegWarps) topk_row(a.topk, row, lane, sh.s_ids);
@@ -609,7 +613,7 @@ __global__ void __launch_bounds__(kSegThreads, 1) segment_b_kernel(const SegBArg
     SegPipe p;
     seg_setup(p, sh, dyn, a.status);
     const int cta = blockIdx.x;
-    const SegStage s2 = seg_stage(a.unpool, nullptr);
+    SegStage s2{{a.unpool, a.unpool}, seg_items(a.unpool), seg_items(a.unpool)};
     seg_trace(a.status, 16);
     seg_stage_prefetch_w(s2, p);
     griddep_wait();
@@ -624,11 +628,14 @@ __global__ void __launch_bounds__(kSegThreads, 1) segment_b_kernel(const SegBArg
     seg_trace(a.status, 19);
     seg_stage_run(s2, p);
     seg_trace(a.status, 20);
-    const SegStage s4 = seg_stage(a.qkv, nullptr);
-    if (!a.tail) seg_stage_prefetch_w(s4, p);
+    SegStage s4{{a.qkv, a.qkv}, 0, 0};
+    if (!a.tail) {
+        s4.n0 = s4.total = seg_items(a.qkv);
+        seg_stage_prefetch_w(s4, p);
+    }
     grid_barrier(a.gb, 12);
     seg_trace(a.status, 21);
-    seg_finish_bf16(s2.g[0], a.unpool_out, a.n_unpool, a.unpool_ld, a.unpool_col0);
+    seg_finish_bf16(a.unpool, a.unpool_out, a.n_unpool, a.unpool_ld, a.unpool_col0);
     xchg_signal(a.sig_unpool);
     if (cta < a.M) {
         xchg_wait_epoch(a.cross_norm.wait, e_unpool);
@@ -642,7 +649,7 @@ __global__ void __launch_bounds__(kSegThreads, 1) segment_b_kernel(const SegBArg
     seg_trace(a.status, 24);
     grid_barrier(a.gb, 14);
     seg_trace(a.status, 25);
-    seg_finish_qkv(s4.g[0], a.qkv_epi);
+    seg_finish_qkv(a.qkv, a.qkv_epi);
     seg_trace(a.status, 26);
 }
 

@@ -240,7 +240,7 @@ struct SegGemm {
     int f32;                 // 1: f32 weights through tf32 (tile 16 rows), 0: bf16 (tile 64 rows)
     float* part;             // [K / 256][16][N] f32 partial sums (a slot per K chunk; few of them are written, see segments.cuh)
     int item0, per;          // set on the device: the GEMM's first item within its stage, items per CTA
-    int packed;              // 1: w holds item images [N block][K chunk][rows][256 k + 64 bytes] (one bulk copy per item)
+    int packed;              // 1: w holds item images [N block][K chunk][rows][512 k + 64 bytes] (a few bulk copies per item)
 };
 struct GridBarrier {
     unsigned long long* count;  // starts at a multiple of the grid size and only grows

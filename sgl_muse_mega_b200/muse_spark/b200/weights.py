@@ -116,12 +116,12 @@ def unpack_w2_fp4(pack: torch.Tensor):
 
 def pack_items(w: torch.Tensor) -> torch.Tensor:
     """A row-major GEMM weight [N, K] (bf16, or f32 for the router) -> the item images the item engine streams:
-    [ceil(N / bn)][K / 256][bn rows][256 k + 64 bytes of padding], bn = 64 (bf16) or 16 (f32), rows past N zero. An item
-    (one N block x one K chunk) is then contiguous and arrives by one bulk copy with its rows already at the padded stride
-    the kernel's shared-memory reads want. K must be a multiple of 256."""
+    [ceil(N / bn)][K / 512][bn rows][512 k + 64 bytes of padding], bn = 64 (bf16) or 16 (f32), rows past N zero. An item
+    (one N block x one K chunk) is then contiguous and arrives by a few large bulk copies with its rows already at the
+    padded stride the kernel's shared-memory reads want. K must be a multiple of 512."""
     n, k = w.shape
     f32 = w.dtype == torch.float32
-    bn, kc, pad = (16, 256, 16) if f32 else (64, 256, 32)
+    bn, kc, pad = (16, 512, 16) if f32 else (64, 512, 32)
     if k % kc:
         raise ValueError(f"K {k} is not a multiple of {kc}")
     nb = (n + bn - 1) // bn

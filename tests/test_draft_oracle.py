@@ -120,13 +120,13 @@ def test_item_images_hold_the_matrix():
 
     g = torch.Generator().manual_seed(0)
     for dtype, bn, pad in ((torch.bfloat16, 64, 32), (torch.float32, 16, 16)):
-        w = torch.randn(150, 512, generator=g).to(dtype)
+        w = torch.randn(150, 1024, generator=g).to(dtype)
         img = W.pack_items(w)
         nb = (150 + bn - 1) // bn
-        assert img.shape == (nb, 2, bn, 256 + pad) and img.is_contiguous()
-        for n, k in ((0, 0), (63, 255), (64, 256), (149, 511), (100, 300)):
-            assert img[n // bn, k // 256, n % bn, k % 256] == w[n, k]
-        assert float(img[..., 256:].abs().sum()) == 0  # the row padding
+        assert img.shape == (nb, 2, bn, 512 + pad) and img.is_contiguous()
+        for n, k in ((0, 0), (63, 511), (64, 512), (149, 1023), (100, 600)):
+            assert img[n // bn, k // 512, n % bn, k % 512] == w[n, k]
+        assert float(img[..., 512:].abs().sum()) == 0  # the row padding
         assert float(img[nb - 1, :, 150 - (nb - 1) * bn :].abs().sum()) == 0  # rows past N
     with pytest.raises(ValueError):
         W.pack_items(torch.zeros(64, 300, dtype=torch.bfloat16))
