@@ -403,27 +403,32 @@ __global__ void __launch_bounds__(256, 1) dattn_split_kernel(const DAttnArgs a) 
     }
 }
 
-// One warp per (window row, q head): the blocks' partials combined in block order.
+// One warp per (window row, q head): the blocks' partials combined in block order. The blocks' (max, sum) pairs are read
+// lane-parallel (two blocks a lane, at most 64 blocks), the rescaled outputs accumulated with the loads of several blocks
+// in flight.
 __global__ void __launch_bounds__(kRowThreads) dattn_merge_kernel(const DAttnArgs a) {
     griddep_wait();
     const int lane = threadIdx.x & 31, G = a.qh / a.kvh, R = a.M * G;
     for (int w = blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5); w < a.M * a.qh; w += gridDim.x * (kRowThreads / 32)) {
         const int b = w / a.qh, head = w - b * a.qh, h = head / G, r = b * G + (head - h * G);
         const float* base = a.ws + ((size_t)h * a.nsplit * R + r) * 132;
-        float mx = -INFINITY;
-        for (int s = 0; s < a.nsplit; ++s) mx = fmaxf(mx, base[(size_t)s * R * 132]);
-        float l = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
+        const size_t stride = (size_t)R * 132;
+        const float ma = lane < a.nsplit ? base[lane * stride] : -INFINITY, mb = lane + 32 < a.nsplit ? base[(lane + 32) * stride] : -INFINITY;
+        const float la = lane < a.nsplit ? base[lane * stride + 1] : 0.f, lb = lane + 32 < a.nsplit ? base[(lane + 32) * stride + 1] : 0.f;
+        const float mx = warp_max(fmaxf(ma, mb));
+        const float fa = ma == -INFINITY ? 0.f : expf(ma - mx), fb = mb == -INFINITY ? 0.f : expf(mb - mx);
+        const float l = warp_sum(la * fa + lb * fb);
+        float o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
         for (int s = 0; s < a.nsplit; ++s) {
-            const float* p = base + (size_t)s * R * 132;
-            const float m = p[0];
-            if (m == -INFINITY) continue;
-            const float f = expf(m - mx);
-            l += p[1] * f;
+            const float f = __shfl_sync(0xffffffffu, s < 32 ? fa : fb, s & 31);
+            if (f == 0.f) continue;  // an empty block: its output words were never written
+            const float* p = base + s * stride;
             const float2 v0 = *(const float2*)(p + 4 + 2 * lane), v1 = *(const float2*)(p + 4 + 64 + 2 * lane);
-            o[0] += v0.x * f;
-            o[1] += v0.y * f;
-            o[2] += v1.x * f;
-            o[3] += v1.y * f;
+            o[0] = fmaf(v0.x, f, o[0]);
+            o[1] = fmaf(v0.y, f, o[1]);
+            o[2] = fmaf(v1.x, f, o[2]);
+            o[3] = fmaf(v1.y, f, o[3]);
         }
         const float inv = l > 0.f ? 1.f / l : 0.f;
         bf16* out = a.o + ((size_t)b * a.qh + head) * 128;
