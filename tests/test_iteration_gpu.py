@@ -98,3 +98,26 @@ def test_iteration_replays_as_one_graph():
         prev_bonus = w[HT.WORDS["ANCHOR"]]
     assert it2.statuses() == []
     assert st2.accept.out_ring.cpu()[:12].count_nonzero() > 0
+
+
+def test_eight_row_window_iteration():
+    """DFlash block 8 (1 anchor + 7 drafts): the same launch lists with an 8-row window, three graph replays."""
+    rows = 8
+    case = synthetic.stack_case(CFG, n_layers=4, rows=rows, ctx=CTX, seed=10)
+    forced = torch.tensor([2], dtype=torch.int32, device=DEV)
+    st = S.Stack(case, 0, DEV, accept_override=forced, packed=True)
+    st.bind()
+    dw, dt = dsyn.draft_weights(DCFG, 4), dsyn.target_shared(DCFG, 4)
+    w0, _ = shard(DCFG, dw, dt, 0, 1)
+    it = Iteration(st, DCFG, w0, capture=list(DCFG.capture), pool_rows=64, rope_rows=128)
+    st.feeds.launch(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    it.capture_graph(warmup=False)
+    for i in range(3):
+        it.step()
+        torch.cuda.synchronize()
+        w = st.accept.words.cpu().tolist()
+        assert w[HT.WORDS["P"]] == CTX + 3 * (i + 1) and w[HT.WORDS["COMMIT"]] == 3 and w[HT.WORDS["ITER"]] == i + 1
+        assert st.tokens.shape[0] == rows and it.draft.drafts.shape[0] == rows - 1
+        assert st.tokens.cpu()[1:].tolist() == it.draft.drafts.cpu().tolist()
+    assert it.statuses() == []
