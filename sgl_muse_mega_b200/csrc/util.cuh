@@ -17,6 +17,8 @@ typedef __nv_bfloat16 bf16;
 // comes after the wait, a successor's prologue may read anything written two or more kernels back, but nothing of its
 // immediate predecessor before its own wait. Both are no-ops without the launch attribute.
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// (Measured the other way round, trigger first: the successors' CTAs then sit on the SMs while this grid still runs, and
+// the layer takes 224 us instead of 215.)
 __device__ __forceinline__ void griddep_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     griddep_launch();
