@@ -476,7 +476,8 @@ int mk_dflash_entry_bind(MkModule* module, const MkDflashShape* shape, const MkD
 // one draft layer from its normed input (reference mk_dflash_qkv_bind + mk_dflash_layer_bind, abi.h:353-491): conv
 // projection, conv, qkv, head norm + RoPE + K/V append, attention, o_proj partial pushed to every rank, all-reduce + conv
 // finish + post norm, conv projection, conv, gate_up with SwiGLU, down partial pushed, all-reduce + conv finish + the
-// successor's norm (the next layer's input norm, or the final norm). 13 kernels.
+// successor's norm (the next layer's input norm, or the final norm). 10 kernels: the conv rides its projection's finish, the
+// head norm + RoPE + K/V append the qkv GEMM's.
 typedef struct MkDflashLayerBind {
     uint64_t h_in;          // bf16 [rows][hidden]
     uint64_t res_in;

@@ -8,7 +8,7 @@
 //
 // Every kernel waits for its predecessor with griddepcontrol.wait before its first dependent read; exchange waits are
 // bounded (params.h). Nothing here traps: an index outside its table is clamped and recorded in the status block (code 4).
-#include "draft.h"
+#include "draft_rows.cuh"
 
 namespace mk {
 
@@ -16,11 +16,6 @@ namespace {
 
 constexpr int kRowThreads = 256;
 
-__device__ __forceinline__ double warp_sum_d(double v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
 // Block-wide f64 sum; `red` holds 33 doubles of shared memory.
 __device__ __forceinline__ double block_sum_d(double v, double* red) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
@@ -36,17 +31,6 @@ __device__ __forceinline__ double block_sum_d(double v, double* red) {
     __syncthreads();
     return red[32];
 }
-// 1 / sqrt(x) as two correctly rounded f32 operations
-__device__ __forceinline__ float rsqrt_exact(float x) { return __fdiv_rn(1.0f, __fsqrt_rn(x)); }
-
-__device__ __forceinline__ void record_clamp(int* status, int site, long long v) {
-    if (status != nullptr && atomicCAS(status, 0, 4) == 0) {
-        status[1] = site;
-        status[2] = (int)blockIdx.x;
-        status[3] = (int)v;
-    }
-}
-
 // ---- captured residuals -> fc's input rows ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kRowThreads) dfeats_kernel(const DFeatsArgs a) {
     griddep_wait();
@@ -63,22 +47,6 @@ __global__ void __launch_bounds__(kRowThreads) dfeats_kernel(const DFeatsArgs a)
 // ---- norm rows -------------------------------------------------------------------------------------------------------------
 // One CTA per row, one thread per 8 consecutive channels (16-byte loads; H / 8 threads). A conv group spans a multiple of 8
 // channels, so a thread's channels share their dynamic coefficients.
-__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
-    const uint4 u = *(const uint4*)p;
-    const __nv_bfloat162* h = (const __nv_bfloat162*)&u;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        v[2 * i] = __low2float(h[i]);
-        v[2 * i + 1] = __high2float(h[i]);
-    }
-}
-__device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
-    uint4 u;
-    __nv_bfloat162* h = (__nv_bfloat162*)&u;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-    *(uint4*)p = u;
-}
 // The all-reduced values of 8 channels of a row: the ranks' bf16 partials summed in rank order in f32, rounded to bf16.
 __device__ __forceinline__ void ar8(const DNormArgs& a, int row, int ch0, float (&x)[8]) {
     load8(a.ar + (size_t)row * a.H + ch0, x);
@@ -176,40 +144,6 @@ __global__ void __launch_bounds__(1024) dconv_kernel(const DConvArgs a) {
     store8(a.out + (size_t)row * a.H + ch0, out);
 }
 
-// ---- head norm + neox RoPE -----------------------------------------------------------------------------------------------------
-// One warp per 128-wide head: lane l holds elements 2l, 2l + 1 of the low half and of the high half. `round_normed`: the
-// block's q / k round the normed head to bf16 before the rotation, the context K does not.
-__device__ __forceinline__ void head_norm_rope(const bf16* x, const bf16* w, float eps, const float* cos_sin, bool round_normed,
-                                               bf16* out, int lane) {
-    const __nv_bfloat162 xl = *(const __nv_bfloat162*)(x + 2 * lane), xh = *(const __nv_bfloat162*)(x + 64 + 2 * lane);
-    float v[4] = {__low2float(xl), __high2float(xl), __low2float(xh), __high2float(xh)};
-    double sq = 0.0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) sq += (double)v[i] * (double)v[i];
-    const float ms = (float)(warp_sum_d(sq) / 128.0);
-    const float r = rsqrt_exact(__fadd_rn(ms, eps));
-    const __nv_bfloat162 wl = *(const __nv_bfloat162*)(w + 2 * lane), wh = *(const __nv_bfloat162*)(w + 64 + 2 * lane);
-    const float wv[4] = {__low2float(wl), __high2float(wl), __low2float(wh), __high2float(wh)};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        v[i] = __fmul_rn(__fmul_rn(v[i], r), wv[i]);
-        if (round_normed) v[i] = bf16_round(v[i]);
-    }
-    const float2 c = *(const float2*)(cos_sin + 2 * lane), s = *(const float2*)(cos_sin + 64 + 2 * lane);
-    const float lo0 = __fsub_rn(__fmul_rn(v[0], c.x), __fmul_rn(v[2], s.x)), lo1 = __fsub_rn(__fmul_rn(v[1], c.y), __fmul_rn(v[3], s.y));
-    const float hi0 = __fadd_rn(__fmul_rn(v[2], c.x), __fmul_rn(v[0], s.x)), hi1 = __fadd_rn(__fmul_rn(v[3], c.y), __fmul_rn(v[1], s.y));
-    *(__nv_bfloat162*)(out + 2 * lane) = __floats2bfloat162_rn(lo0, lo1);
-    *(__nv_bfloat162*)(out + 64 + 2 * lane) = __floats2bfloat162_rn(hi0, hi1);
-}
-
-__device__ __forceinline__ long long clamp_pos(long long p, long long rows, int* status, int site) {
-    if (p < 0 || p >= rows) {
-        record_clamp(status, site, p);
-        p = p < 0 ? 0 : rows - 1;
-    }
-    return p;
-}
-
 __global__ void __launch_bounds__(kRowThreads) dqkv_rows_kernel(const DQkvRowsArgs a) {
     griddep_wait();
     const int lane = threadIdx.x & 31, heads = a.qh + 2 * a.kvh;
@@ -217,17 +151,9 @@ __global__ void __launch_bounds__(kRowThreads) dqkv_rows_kernel(const DQkvRowsAr
     for (int w = blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5); w < a.M * heads; w += gridDim.x * (kRowThreads / 32)) {
         const int m = w / heads, head = w - m * heads;
         const bf16* x = a.qkv + ((size_t)m * heads + head) * kDraftHeadDim;
-        const long long pos = clamp_pos(P + m, a.rope_rows, a.status, 410);
-        const size_t slot = (size_t)((P + m) % a.pool_rows + a.pool_rows) % a.pool_rows;
-        if (head < a.qh) {
-            head_norm_rope(x, a.q_norm, a.eps, a.rope + pos * kDraftHeadDim, true, a.q_out + ((size_t)m * a.qh + head) * kDraftHeadDim, lane);
-        } else if (head < a.qh + a.kvh) {
-            head_norm_rope(x, a.k_norm, a.eps, a.rope + pos * kDraftHeadDim, true,
-                           a.k_pool + (slot * a.kvh + (head - a.qh)) * kDraftHeadDim, lane);
-        } else {
-            uint2* dst = (uint2*)(a.v_pool + (slot * a.kvh + (head - a.qh - a.kvh)) * kDraftHeadDim);
-            dst[lane] = ((const uint2*)x)[lane];
-        }
+        const __nv_bfloat162 xl = *(const __nv_bfloat162*)(x + 2 * lane), xh = *(const __nv_bfloat162*)(x + 64 + 2 * lane);
+        float v[4] = {__low2float(xl), __high2float(xl), __low2float(xh), __high2float(xh)};
+        dqkv_head(a, m, head, v, P, lane);
     }
 }
 

@@ -60,22 +60,6 @@ struct DConvArgs {  // side 0: out[n] = (b0 + d[n][0]) h[n] + (b1 + d[n][1]) h[n
     int M, H, groups;
 };
 
-struct DQkvRowsArgs {
-    const bf16* qkv;  // [M][(qh + 2 kvh) x 128]
-    int M, qh, kvh;
-    const bf16* q_norm;
-    const bf16* k_norm;
-    float eps;
-    const float* rope;  // [rope_rows][128]: cos | sin
-    long long rope_rows;
-    const long long* words;
-    bf16* q_out;        // [M][qh x 128]
-    bf16* k_pool;       // [pool_rows][kvh][128], slot = position % pool_rows
-    bf16* v_pool;
-    long long pool_rows;
-    int* status;
-};
-
 struct DCtxKvArgs {
     const bf16* kv;  // [M][layers x 2 x kvh x 128]: per layer the k heads, then the v heads
     int M, layers, kvh;

@@ -24,6 +24,7 @@
 // This file is compiled as part of rows.cu: the segments reuse its row functions (top-k, route tables, quantisation).
 #pragma once
 
+#include "draft_rows.cuh"
 #include "umma.cuh"
 
 namespace mk {
@@ -304,6 +305,76 @@ __device__ __forceinline__ void seg_finish_f32_push(const SegGemm& g, bf16* cons
     }
 }
 
+// A conv projection (N = 2 sides x 2 taps x groups coefficient columns): the bf16 coefficients into c_out, then the conv's
+// side 0 over the rows the projection was computed from, a thread per (row, group):
+//   xa[m, ch] = (base[0, ch] + c[m, side 0, tap 0, g]) h[m, ch] + (base[1, ch] + c[m, side 0, tap 1, g]) h[m - 1, ch]
+// in f32 with separately rounded products, as the stand-alone conv kernel.
+__device__ __forceinline__ void seg_finish_conv(const SegGemm& g, bf16* c_out, long long ldo, const SegConv& cv) {
+    const int nsplit = g.K / kChunkK;
+    const long long total = (long long)g.M * g.N;
+    for (long long i = (long long)blockIdx.x * kSegThreads + threadIdx.x; i < total; i += (long long)gridDim.x * kSegThreads) {
+        const int m = (int)(i / g.N), n = (int)(i - (long long)m * g.N);
+        float v = 0.f;
+        for (int ks = 0; ks < nsplit; ++ks) v += g.part[((size_t)ks * 16 + m) * g.N + n];
+        c_out[(long long)m * ldo + n] = __float2bfloat16_rn(v);
+    }
+    const int per_group = cv.H / cv.groups, pairs = g.M * cv.groups;
+    for (int i = blockIdx.x * kSegThreads + threadIdx.x; i < pairs; i += gridDim.x * kSegThreads) {
+        const int m = i / cv.groups, gi = i - m * cv.groups;
+        float d0 = 0.f, d1 = 0.f;
+        for (int ks = 0; ks < nsplit; ++ks) {
+            const float* row = g.part + ((size_t)ks * 16 + m) * g.N;
+            d0 += row[gi];
+            d1 += row[cv.groups + gi];
+        }
+        d0 = bf16_round(d0);
+        d1 = bf16_round(d1);
+        for (int c0 = gi * per_group; c0 < (gi + 1) * per_group; c0 += 8) {
+            float b0[8], b1[8], x[8], xp[8], out[8];
+            load8(cv.base + c0, b0);
+            load8(cv.h + (size_t)m * cv.H + c0, x);
+            if (m > 0) {
+                load8(cv.base + cv.H + c0, b1);
+                load8(cv.h + (size_t)(m - 1) * cv.H + c0, xp);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                out[j] = __fmul_rn(__fadd_rn(b0[j], d0), x[j]);
+                if (m > 0) out[j] = __fadd_rn(out[j], __fmul_rn(__fadd_rn(b1[j], d1), xp[j]));
+            }
+            store8(cv.xa + (size_t)m * cv.H + c0, out);
+        }
+    }
+}
+
+// The draft's qkv: a warp per (row, 128-wide head) sums its partial sums, rounds them to bf16 (the stored qkv row), then
+// head norm, neox RoPE and the K / V append (dqkv_head).
+__device__ __forceinline__ void seg_finish_dqkv(const SegGemm& g, bf16* qkv_out, long long ldo, const DQkvRowsArgs& a) {
+    const int nsplit = g.K / kChunkK, heads = a.qh + 2 * a.kvh, lane = threadIdx.x & 31;
+    const long long P = a.words[kWordP];
+    for (int w = blockIdx.x * kSegWarps + (threadIdx.x >> 5); w < g.M * heads; w += gridDim.x * kSegWarps) {
+        const int m = w / heads, head = w - m * heads;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int ks = 0; ks < nsplit; ++ks) {
+            const float* row = g.part + ((size_t)ks * 16 + m) * g.N + head * kDraftHeadDim;
+            const float2 lo = *(const float2*)(row + 2 * lane), hi = *(const float2*)(row + 64 + 2 * lane);
+            v[0] += lo.x;
+            v[1] += lo.y;
+            v[2] += hi.x;
+            v[3] += hi.y;
+        }
+        const __nv_bfloat162 ql = __floats2bfloat162_rn(v[0], v[1]), qh = __floats2bfloat162_rn(v[2], v[3]);
+        bf16* orow = qkv_out + (long long)m * ldo + head * kDraftHeadDim;
+        *(__nv_bfloat162*)(orow + 2 * lane) = ql;
+        *(__nv_bfloat162*)(orow + 64 + 2 * lane) = qh;
+        v[0] = __low2float(ql);
+        v[1] = __high2float(ql);
+        v[2] = __low2float(qh);
+        v[3] = __high2float(qh);
+        dqkv_head(a, m, head, v, P, lane);
+    }
+}
+
 // logits[m, n] = sum_ks part[ks][m][n] (f32), by one CTA.
 __device__ __forceinline__ void seg_finish_f32_cta(const SegGemm& g, float* out) {
     const int nsplit = g.K / kChunkK;
@@ -535,6 +606,10 @@ __global__ void __launch_bounds__(kSegThreads, 1) seg_gemm_kernel(const SegGemmA
         seg_finish_silu(a.g[0], a.out, a.n_out, a.ldo, a.off0);
     } else if (a.finish == 4) {
         seg_finish_f32_push(a.g[0], a.out, a.n_out, a.ldo, a.off0);
+    } else if (a.finish == 5) {
+        seg_finish_conv(a.g[0], a.out[0], a.ldo, a.conv);
+    } else if (a.finish == 6) {
+        seg_finish_dqkv(a.g[0], a.out[0], a.ldo, a.rows);
     } else {
         seg_finish_bf16(a.g[0], a.out, a.n_out, a.ldo, a.off0);
         if (a.finish == 1) {

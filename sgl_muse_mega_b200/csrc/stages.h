@@ -278,11 +278,35 @@ struct SegBArgs {  // combine .. successor's qkv head
     GridBarrier gb;
     int* status;
 };
+// The DFlash2 draft's row work that rides the finishes of its GEMMs (draft.h holds the rest of the draft's records).
+struct DQkvRowsArgs {
+    const bf16* qkv;  // [M][(qh + 2 kvh) x 128]
+    int M, qh, kvh;
+    const bf16* q_norm;
+    const bf16* k_norm;
+    float eps;
+    const float* rope;  // [rope_rows][128]: cos | sin
+    long long rope_rows;
+    const long long* words;
+    bf16* q_out;        // [M][qh x 128]
+    bf16* k_pool;       // [pool_rows][kvh][128], slot = position % pool_rows
+    bf16* v_pool;
+    long long pool_rows;
+    int* status;
+};
+
+struct SegConv {  // the grouped conv's side 0 over the rows the projection was computed from
+    const bf16* h;     // [M][H]
+    const bf16* base;  // [2 sides][2 taps][H]
+    bf16* xa;          // [M][H]
+    int H, groups;
+};
 struct SegGemmArgs {  // one GEMM stage (or pooler + router) as a kernel of its own
     SegGemm g[2];
     int n_gemm;
     int finish;                 // 0: bf16 push of g[0]; 1: the same plus f32 logits and routing scores of g[1]; 2: qkv row ops;
-                                // 3: SwiGLU of g[0]'s [gate | up] columns; 4: f32 push of g[0] (out holds float pointers)
+                                // 3: SwiGLU of g[0]'s [gate | up] columns; 4: f32 push of g[0] (out holds float pointers);
+                                // 5: conv projection + conv; 6: the draft's qkv + row work
     bf16* out[kMaxRanks];
     int n_out;
     long long ldo, off0;
@@ -292,6 +316,8 @@ struct SegGemmArgs {  // one GEMM stage (or pooler + router) as a kernel of its 
     const float* score_bias;
     double score_mult;
     GemmArgs epi;               // finish 2: the qkv head's epilogue operands
+    SegConv conv;               // finish 5: g[0] is a conv projection; bf16 coefficients to out[0], then the conv's side 0
+    DQkvRowsArgs rows;          // finish 6: g[0] is the draft's qkv; bf16 rows to out[0], head norm, neox RoPE, K / V append
     GridBarrier gb;
     int* status;
 };

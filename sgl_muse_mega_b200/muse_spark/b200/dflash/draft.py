@@ -5,7 +5,7 @@ layers, draft_head) and ``sm103/dflash/head.py`` / ``layer.py`` binds with this 
 
     mk_dflash_entry_bind        feats, fc (gathered), ctx norm, context k / v rows, their head norm + RoPE into the pools,
                                 the block's embedding rows + layer 0's input norm                              6 kernels
-    mk_dflash_layer_bind x L    conv, qkv, attention, o_proj + all-reduce, conv, SwiGLU MLP + all-reduce       13 kernels
+    mk_dflash_layer_bind x L    conv, qkv, attention, o_proj + all-reduce, conv, SwiGLU MLP + all-reduce       10 kernels
     mk_lm_head_bind             the target lm_head over y rows 1.., f32 logits gathered on every rank           1 kernel
     mk_dflash_draft_head_bind   W_P y, top-16, lattice, walk, the verify window's ids                           3 kernels
 

@@ -218,7 +218,7 @@ def test_draft_step_replays_as_a_graph():
     torch.cuda.synchronize()
     want = dict(y=dr.y.cpu().clone(), ids=dr.verify_ids.cpu().clone(), scores=dr.scores.cpu().clone(), k=dr.k_pool[1].cpu().clone())
     s = torch.cuda.current_stream().cuda_stream
-    assert dr.kernels() == 6 + 13 * CFG.layers + 1 + 3
+    assert dr.kernels() == 6 + 10 * CFG.layers + 1 + 3
     dr.launch_all(s, pdl=True)
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()

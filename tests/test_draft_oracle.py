@@ -99,7 +99,7 @@ def test_draft_binds_validate_without_a_gpu():
                  post_norm=P, w_gate_up=P, w_down=P, next_norm=P, k_pool=P, v_pool=P, pool_rows=64, rope=P, rope_rows=64, c_att=P,
                  xa=P, qkv=P, q=P, attn_ws=P, o=P, ar_attn_peer=[P, P], a=0, h_post=P, res_post=P, c_mlp=P, xm=P, m=P,
                  ar_mlp_peer=[P, P], x_out=0, h_out=P, res_out=0, **common)  # fmt: skip
-    assert lib.dflash_bind("mk_dflash_layer_bind", None, sh, host.make("MkDflashLayerBind", **layer)).info().kernels == 13
+    assert lib.dflash_bind("mk_dflash_layer_bind", None, sh, host.make("MkDflashLayerBind", **layer)).info().kernels == 10
     with pytest.raises(RuntimeError, match="w_down"):
         lib.dflash_bind("mk_dflash_layer_bind", None, sh, host.make("MkDflashLayerBind", **{**layer, "w_down": 0}))
     head = dict(y=P, w_hproj=P, hid=P, logits=P, pred_codebook=P, succ_codebook=P, words=P, keys=P, cand=P, unary=P, scores=P,
