@@ -204,3 +204,22 @@ def test_item_images_give_the_same_bits(name, device):
         for k, v in ra.o.items():
             if torch.is_tensor(v):
                 assert torch.equal(v, rb.o[k]), k
+
+
+@pytest.mark.parametrize("rows", [1, 4, 8, 16])
+@pytest.mark.parametrize("tp", [1, 2])
+def test_window_rows_sweep(rows, tp, device):
+    """The verify window of M = 1, 4, 8 and 16 rows (the expert-block sweep of the benchmark configurations) through the
+    whole layer, every stage against the oracle fed the kernels' own inputs; tensor-core experts, dense weights as item
+    images."""
+    from golden_cases import small_cfg
+
+    cfg = small_cfg(tp)
+    case = synthetic.layer_case(cfg, rows=rows, ctx=29, band="baseline", seed=40 + rows)
+    world = L.LayerWorld(case, device, packed=True)
+    world.run_interleaved()
+    torch.cuda.synchronize()
+    for r in world.ranks:
+        assert r.tensor_cores
+        assert r.launch_record.status(torch.cuda.current_stream().cuda_stream).code == 0
+    check_world(world, list(range(tp)))
