@@ -553,6 +553,11 @@ typedef struct MkDflashDraftHeadBind {
     uint64_t status;
     int64_t wait_budget;
     int64_t packed;         // 1: w_hproj is an item image
+    // the sampled walk (reference abi.h:537-540, kernels/dflash/sample.cuh walk): samp = i64 [4] sampling words (seed,
+    // stream, top_k, f32 temperature bits | f32 top_p bits << 32) or 0 for the greedy walk; slot e then draws its candidate
+    // from softmax(score row / T) with the Philox4x32-10 uniform e of {words[4] (iteration), stream, purpose 0}
+    uint64_t samp;
+    uint64_t walk_q;        // f32 [rows - 1][16] or 0: each slot's probabilities over its candidates
 } MkDflashDraftHeadBind;
 int mk_dflash_draft_head_bind(MkModule* module, const MkDflashShape* shape, const MkDflashDraftHeadBind* bind, MkLaunch** out);
 

@@ -302,6 +302,49 @@ def walk(cand: torch.Tensor, scores: torch.Tensor):
     return torch.tensor(toks, dtype=torch.int64), torch.tensor(picks, dtype=torch.int64)
 
 
+# ---- the sampled walk (temperature > 0): dflash2.py:663-700 (Philox4x32-10 uniforms), :609-640 (selector_walk) ----------
+
+PHILOX_M = (0xD2511F53, 0xCD9E8D57)
+PHILOX_W = (0x9E3779B9, 0xBB67AE85)
+PURPOSE_WALK, PURPOSE_ACCEPT = 0, 1
+_M32 = 0xFFFFFFFF
+
+
+def philox(counter, key):
+    """Philox4x32-10 (Salmon et al., SC'11): 4 counter words, 2 key words -> 4 output words."""
+    c0, c1, c2, c3 = counter
+    k0, k1 = key
+    for _ in range(10):
+        p0, p1 = PHILOX_M[0] * c0, PHILOX_M[1] * c2
+        c0, c1, c2, c3 = (p1 >> 32) ^ c1 ^ k0, p1 & _M32, (p0 >> 32) ^ c3 ^ k1, p0 & _M32
+        k0, k1 = (k0 + PHILOX_W[0]) & _M32, (k1 + PHILOX_W[1]) & _M32
+    return c0, c1, c2, c3
+
+
+def uniforms(seed: int, stream: int, iteration: int, purpose: int) -> torch.Tensor:
+    """u_i in [0, 1), i < 16: the top 24 bits of word i % 4 of philox({iteration, stream, purpose, i / 4}, seed)."""
+    seed &= 2**64 - 1
+    key = (seed & _M32, seed >> 32)
+    out = [(philox((iteration & _M32, stream & _M32, purpose, i // 4), key)[i % 4] >> 8) * 2.0**-24 for i in range(16)]
+    return torch.tensor(out, dtype=torch.float32)
+
+
+def walk_sampled(cand: torch.Tensor, scores: torch.Tensor, u: torch.Tensor, temperature: float):
+    """Slot e draws from softmax(score row of slot e - 1's pick / T): index = #{c : u_e >= cumsum(q)_c}, clamped to
+    K - 1. -> (tokens, picks, q [gamma, K] f32)."""
+    slots, k = cand.shape
+    toks, picks, prev = [], [], 0
+    q = torch.empty(slots, k, dtype=torch.float32)
+    for e in range(slots):
+        scaled = scores[e, prev].float() / temperature
+        ex = torch.exp(scaled - scaled.max())
+        q[e] = ex / ex.sum()
+        idx = min(int((u[e] >= torch.cumsum(q[e], 0)).sum()), k - 1)
+        toks.append(int(cand[e, idx])), picks.append(idx)
+        prev = idx
+    return torch.tensor(toks, dtype=torch.int64), torch.tensor(picks, dtype=torch.int64), q
+
+
 def draft_step(cfg: DraftConfig, shards: list, kv: DraftKV, caps: torch.Tensor, anchor: int, pos: int, commit: int, rows: int) -> dict:
     """(A) + (B) + (C). caps f32 [features, n >= commit, H]: the last verify's captured residuals, row i at position
     pos - commit + i; the first ``commit`` context rows are written to the KV."""

@@ -443,6 +443,18 @@ __global__ void __launch_bounds__(kRowThreads) dtopk_kernel(const DTopkArgs a) {
     block_top16<PER>(k, a.keys + ((size_t)row * a.nchunk + chunk) * kDraftTopK, red);
 }
 
+// Philox4x32-10 (Salmon et al., SC'11)
+__device__ __forceinline__ uint4 philox4x32(uint4 c, uint2 k) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const unsigned long long p0 = (unsigned long long)0xD2511F53u * c.x, p1 = (unsigned long long)0xCD9E8D57u * c.z;
+        c = make_uint4((unsigned)(p1 >> 32) ^ c.y ^ k.x, (unsigned)p1, (unsigned)(p0 >> 32) ^ c.w ^ k.y, (unsigned)p0);
+        k.x += 0x9E3779B9u;
+        k.y += 0xBB67AE85u;
+    }
+    return c;
+}
+
 // ---- lattice and walk ---------------------------------------------------------------------------------------------------------------
 constexpr int kMaxMergePer = kMaxMergeChunks * kDraftTopK / kRowThreads;
 
@@ -530,7 +542,35 @@ __global__ void __launch_bounds__(kRowThreads) dlattice_kernel(const DLatticeArg
         for (int s = 0; s < a.gamma; ++s) {
             const float* row = s_sc + (s * kDraftTopK + prev) * kDraftTopK;
             int idx = -1;
-            for (int c = 0; c < kDraftTopK && idx < 0; ++c)
+            if (a.samp != nullptr) {
+                // sampled: q = softmax(row / T) in f32 (T clamped at 1e-5), index = #{c : u >= cumsum(q)_c} clamped to 15;
+                // u = the top 24 bits of word s % 4 of Philox4x32-10({iteration, stream, purpose 0, s / 4}, seed)
+                const float T = fmaxf(__uint_as_float((unsigned)((unsigned long long)a.samp[3] & 0xFFFFFFFFull)), 1e-5f);
+                float sc[kDraftTopK], mx = -INFINITY, sum = 0.f;
+                for (int c = 0; c < kDraftTopK; ++c) {
+                    sc[c] = __fdiv_rn(row[c], T);
+                    mx = fmaxf(mx, sc[c]);
+                }
+                for (int c = 0; c < kDraftTopK; ++c) {
+                    sc[c] = expf(__fsub_rn(sc[c], mx));
+                    sum = __fadd_rn(sum, sc[c]);
+                }
+                const unsigned long long seed = (unsigned long long)a.samp[0];
+                const uint4 r4 = philox4x32(make_uint4((unsigned)a.words[kWordIter], (unsigned)a.samp[1], 0u, (unsigned)s / 4),
+                                            make_uint2((unsigned)seed, (unsigned)(seed >> 32)));
+                const unsigned rw[4] = {r4.x, r4.y, r4.z, r4.w};
+                const float u = (float)(rw[s & 3] >> 8) * 0x1p-24f;
+                float cum = 0.f;
+                idx = 0;
+                for (int c = 0; c < kDraftTopK; ++c) {
+                    const float q = __fdiv_rn(sc[c], sum);
+                    cum = __fadd_rn(cum, q);
+                    idx += u >= cum;
+                    if (a.walk_q != nullptr) a.walk_q[s * kDraftTopK + c] = q;
+                }
+                idx = min(idx, kDraftTopK - 1);
+            }
+            for (int c = 0; a.samp == nullptr && c < kDraftTopK && idx < 0; ++c)
                 if (row[c] != row[c]) idx = c;  // the first NaN wins
             if (idx < 0) {
                 idx = 0;

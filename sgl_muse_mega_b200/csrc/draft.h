@@ -15,7 +15,7 @@ constexpr int kDraftKeysPerSplit = 64;
 constexpr int kDraftTopkChunk = 4096;  // vocabulary entries one top-k CTA scans
 constexpr int kMaxMergeChunks = 128;    // chunk lists the merge holds in registers (256 threads x 8 keys)
 // step words (i64): the draft reads the position, the anchor and the last commit
-constexpr int kWordP = 0, kWordAnchor = 1, kWordCommit = 3;
+constexpr int kWordP = 0, kWordAnchor = 1, kWordCommit = 3, kWordIter = 4;
 // exchange points of the draft's own flag block
 enum DraftXchg { DXP_CTX = 0, DXP_ATTN, DXP_MLP, DXP_LOGITS = 5 };
 
@@ -111,6 +111,9 @@ struct DLatticeArgs {
     long long* verify_ids;  // [gamma + 1]: the anchor, then the drafts
     unsigned* counter;
     int* status;
+    // the sampled walk (temperature > 0), or samp null: the greedy walk
+    const long long* samp;  // i64 [4]: seed, stream, top_k, f32 temperature bits | f32 top_p bits << 32
+    float* walk_q;          // [gamma][16]: each slot's probabilities over its candidates
 };
 
 struct DKvSyncArgs {

@@ -56,7 +56,8 @@ class DraftRank:
     def __init__(self, cfg: DraftConfig, w: DraftWeights, t: TargetShared, rank: int, ranks: int, device, *, rows: int,
                  pool_rows: int, rope_rows: int, lib: Optional[host.Library] = None, module=None, words: Optional[torch.Tensor] = None,
                  caps: Optional[Sequence[torch.Tensor]] = None, verify_ids: Optional[torch.Tensor] = None, exchange=None,
-                 flags: bool = False, wait_budget: int = 0, packed: bool = False, lm_head_packed: Optional[bool] = None):  # fmt: skip
+                 flags: bool = False, wait_budget: int = 0, packed: bool = False, lm_head_packed: Optional[bool] = None,
+                 samp: Optional[torch.Tensor] = None):  # fmt: skip
         """``packed``: upload the draft's GEMM weights as item images (``weights.pack_items``: one bulk copy per item).
         ``lm_head_packed``: ``t.lm_head`` already is one (a target stack built with ``packed``); default: pack it too."""
         self.cfg, self.rank, self.ranks, self.rows, self.device = cfg, rank, ranks, rows, device
@@ -111,6 +112,8 @@ class DraftRank:
         self.pick = z(gamma, dt=torch.int32)
         self.drafts = z(gamma, dt=torch.int64)
         self.verify_ids = verify_ids if verify_ids is not None else z(rows, dt=torch.int64)
+        self.samp = samp  # i64 [4] sampling words on the device (``sampling_words``), or None: the greedy walk
+        self.walk_q = z(gamma, 16, dt=torch.float32)
         self.status = z(16, dt=torch.int32)
         self.launches: list = []
 
@@ -163,7 +166,8 @@ class DraftRank:
             pred_codebook=self.w["pred"], succ_codebook=self.w["succ"], words=self.words, keys=self.keys, cand=self.cand,
             unary=self.unary, scores=self.scores, pick=self.pick, drafts=self.drafts, verify_ids=self.verify_ids,
             mult=cfg.output_multiplier, cap=cfg.softcap, ws=self.ws, flags=flags, contributors=present if flags is not None else 0,
-            status=self.status, wait_budget=self.wait_budget, packed=int(self.packed),
+            status=self.status, wait_budget=self.wait_budget, packed=int(self.packed), samp=self.samp,
+            walk_q=self.walk_q if self.samp is not None else None,
         )  # fmt: skip
         self.head = lib.dflash_bind("mk_dflash_draft_head_bind", mod, self.shape, head)
         self.launches = [self.entry, *self.layers, self.lm_head.launch, self.head]
@@ -197,6 +201,17 @@ class DraftRank:
         out = [("draft", st.code, st.stage, st.observed)] if st.code else []
         st = self.lm_head.launch.status(torch.cuda.current_stream(self.device).cuda_stream)
         return out + ([("draft_lm_head", st.code, st.stage, st.observed)] if st.code else [])
+
+
+def sampling_words(seed: int, stream: int, temperature: float, top_k: int = 1 << 30, top_p: float = 1.0) -> torch.Tensor:
+    """The sampled step's words (reference ``sm103/dflash/head.py:56-59``): seed, stream, top_k, f32 temperature bits |
+    f32 top_p bits << 32, as i64 [4] on the host."""
+    import struct
+
+    t = struct.unpack("<I", struct.pack("<f", temperature))[0]
+    p = struct.unpack("<I", struct.pack("<f", top_p))[0]
+    seed &= 2**64 - 1
+    return torch.tensor([seed - 2**64 if seed >= 2**63 else seed, stream, top_k, t | (p << 32)], dtype=torch.int64)
 
 
 class DraftWorld:

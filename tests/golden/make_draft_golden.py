@@ -25,6 +25,10 @@ REF = Path(os.environ.get("MUSE_REFERENCE", "/root/reference"))
 CASES = [("tp2_b16", 2, 16, 40, 7, 1), ("tp1_b8", 1, 8, 12, 3, 2), ("tp4_b16", 4, 16, 33, 16, 3)]
 
 
+PHILOX_CASES = [((0, 0, 0, 0), (0, 0)), ((1, 2, 3, 4), (5, 6)), ((0xFFFFFFFF, 0x12345678, 1, 3), (0xDEADBEEF, 0x0BADF00D))]
+SAMPLE_SEED, SAMPLE_TEMP = 0x1234567887654321, 0.7
+
+
 def small_cfg():
     from sgl_muse_mega_b200.muse_spark.b200.dflash.weights import DraftConfig
 
@@ -71,6 +75,13 @@ def main() -> None:
                                   cand=res[0]["cand"], unary=res[0]["unary"], scores=res[0]["scores"],
                                   per_rank=[{k: r[k] for k in ("ctx_k", "ctx_v", "kv_k", "kv_v")} for r in res])  # fmt: skip
         print(name, "tokens", res[0]["tokens"].tolist())
+    # the sampled walk: Philox known answers, the step's uniforms, and the walk over each case's lattice
+    out["philox"] = [dict(counter=c, key=k, out=R2.philox(c, k)) for c, k in PHILOX_CASES]
+    out["sampled"] = {}
+    for name, g in out["cases"].items():
+        u = R2.uniforms(SAMPLE_SEED, g["pos"], 3, R2.PURPOSE_WALK)
+        toks, q = R2.selector_walk(g["cand"], g["scores"], greedy=False, uniforms=u, temperature=SAMPLE_TEMP)
+        out["sampled"][name] = dict(u=u, tokens=toks, q=q)
     torch.save(out, HERE / "draft.pt")
     print("wrote", HERE / "draft.pt", (HERE / "draft.pt").stat().st_size, "bytes")
 

@@ -208,6 +208,40 @@ def test_draft_item_images_give_the_same_bits():
             assert torch.equal(ra.k_pool[li], rb.k_pool[li]) and torch.equal(ra.v_pool[li], rb.v_pool[li])
 
 
+def test_sampled_walk_matches_the_oracle():
+    """Temperature > 0: the head walks the lattice by sampling with the step's Philox uniforms. Uniforms, picks and tokens
+    exactly as the oracle's walk over the kernel's own lattice, probabilities to f32 rounding."""
+    seed, stream, temp = 0x1234567887654321, 40, 0.7
+    case = synthetic.draft_case(CFG, 1, 16, 40, 7, 11)
+    samp = DR.sampling_words(seed, stream, temp).to(DEV)
+    world = DR.DraftWorld(case, DEV, samp=samp)
+    dr = world.ranks[0]
+    for iteration in (0, 5):
+        dr.words[4] = iteration  # the step counter keys the uniforms
+        world.run_interleaved()
+        torch.cuda.synchronize()
+        assert dr.statuses() == []
+        u = D.uniforms(seed, stream, iteration, D.PURPOSE_WALK)
+        toks, picks, q = D.walk_sampled(dr.cand.cpu(), dr.scores.cpu(), u, temp)
+        got_q = dr.walk_q.cpu()
+        # the walk conditions slot e on slot e - 1's pick: compare slot by slot along the kernel's own path
+        prev = 0
+        for e in range(case.rows - 1):
+            row = dr.scores[e, prev].cpu() / temp
+            ref_q = torch.softmax(row, 0)
+            assert torch.allclose(got_q[e], ref_q, rtol=0, atol=2e-6), (iteration, e)
+            cum = torch.cumsum(got_q[e], 0)
+            idx = min(int((u[e] >= cum).sum()), 15)
+            if float((cum - u[e]).abs().min()) > 1e-5:  # away from a boundary of the CDF the draw is unambiguous
+                assert int(dr.pick[e]) == idx, (iteration, e)
+            prev = int(dr.pick[e])
+            assert int(dr.drafts[e]) == int(dr.cand[e, prev]) == int(dr.verify_ids[1 + e])
+        if torch.equal(dr.pick.cpu().long(), picks):
+            assert torch.equal(dr.drafts.cpu(), toks)
+    # another iteration count draws other uniforms
+    assert not torch.equal(D.uniforms(seed, stream, 0, 0), D.uniforms(seed, stream, 5, 0))
+
+
 def test_draft_step_replays_as_a_graph():
     """A lone rank: the whole launch list under programmatic dependent launch, eager and as one CUDA graph, gives the
     stagewise run's results bit for bit; a second replay after new step words moves the block."""

@@ -103,7 +103,7 @@ def test_draft_binds_validate_without_a_gpu():
     with pytest.raises(RuntimeError, match="w_down"):
         lib.dflash_bind("mk_dflash_layer_bind", None, sh, host.make("MkDflashLayerBind", **{**layer, "w_down": 0}))
     head = dict(y=P, w_hproj=P, hid=P, logits=P, pred_codebook=P, succ_codebook=P, words=P, keys=P, cand=P, unary=P, scores=P,
-                pick=P, drafts=P, verify_ids=P, mult=0.17, cap=20.0, ws=P, flags=0, contributors=0, status=P, wait_budget=0, packed=1)  # fmt: skip
+                pick=P, drafts=P, verify_ids=P, mult=0.17, cap=20.0, ws=P, flags=0, contributors=0, status=P, wait_budget=0, packed=1, samp=0, walk_q=0)  # fmt: skip
     assert lib.dflash_bind("mk_dflash_draft_head_bind", None, sh, host.make("MkDflashDraftHeadBind", **head)).info().kernels == 3
     for bad, why in ((dict(q_heads=3), "heads"), (dict(hidden=768), "hidden"), (dict(inter=300), "inter"), (dict(rows=17), "rows"),
                      (dict(conv_groups=128), "conv_groups"), (dict(selector_rank=600), "selector_rank")):  # fmt: skip
@@ -130,3 +130,18 @@ def test_item_images_hold_the_matrix():
         assert float(img[nb - 1, :, 150 - (nb - 1) * bn :].abs().sum()) == 0  # rows past N
     with pytest.raises(ValueError):
         W.pack_items(torch.zeros(64, 300, dtype=torch.bfloat16))
+
+
+def test_philox_and_sampled_walk_match_the_reference():
+    """Philox4x32-10 known answers, the step's uniforms and the sampled walk (softmax of the score row / T, inverse CDF)
+    against the reference's own outputs."""
+    for k in GOLD["philox"]:
+        assert tuple(D.philox(tuple(k["counter"]), tuple(k["key"]))) == tuple(k["out"])
+    seed, temp = 0x1234567887654321, 0.7
+    for name, s in GOLD["sampled"].items():
+        g = GOLD["cases"][name]
+        u = D.uniforms(seed, g["pos"], 3, D.PURPOSE_WALK)
+        assert torch.equal(u, s["u"]) and float(u.min()) >= 0 and float(u.max()) < 1
+        toks, picks, q = D.walk_sampled(g["cand"], g["scores"], u, temp)
+        assert torch.equal(toks, s["tokens"]) and torch.equal(q, s["q"])
+        assert torch.equal(g["cand"].gather(1, picks[:, None])[:, 0], toks)
