@@ -538,7 +538,7 @@ typedef struct MkDflashDraftHeadBind {
     uint64_t pred_codebook;
     uint64_t succ_codebook;  // bf16 [vocab][selector_rank]
     uint64_t words;
-    uint64_t keys;          // u64 [rows - 1][topk_chunks][16]
+    uint64_t keys;          // u64 [rows - 1][topk_chunks + 1][16]: the chunks' candidate lists, then the row's merged 16
     uint64_t cand;          // i64 [rows - 1][16]
     uint64_t unary;         // f32 [rows - 1][16]
     uint64_t scores;        // f32 [rows - 1][16][16]

@@ -345,16 +345,26 @@ __global__ void __launch_bounds__(kRowThreads) dattn_merge_kernel(const DAttnArg
         const float fa = ma == -INFINITY ? 0.f : expf(ma - mx), fb = mb == -INFINITY ? 0.f : expf(mb - mx);
         const float l = warp_sum(la * fa + lb * fb);
         float o[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-        for (int s = 0; s < a.nsplit; ++s) {
-            const float f = __shfl_sync(0xffffffffu, s < 32 ? fa : fb, s & 31);
-            if (f == 0.f) continue;  // an empty block: its output words were never written
-            const float* p = base + s * stride;
-            const float2 v0 = *(const float2*)(p + 4 + 2 * lane), v1 = *(const float2*)(p + 4 + 64 + 2 * lane);
-            o[0] = fmaf(v0.x, f, o[0]);
-            o[1] = fmaf(v0.y, f, o[1]);
-            o[2] = fmaf(v1.x, f, o[2]);
-            o[3] = fmaf(v1.y, f, o[3]);
+        // eight blocks' rows are requested before the first is used: the loop is one L2 round trip per eight blocks
+        for (int s0 = 0; s0 < a.nsplit; s0 += 8) {
+            float2 v0[8], v1[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float* p = base + (size_t)min(s0 + j, a.nsplit - 1) * stride;
+                v0[j] = *(const float2*)(p + 4 + 2 * lane);
+                v1[j] = *(const float2*)(p + 4 + 64 + 2 * lane);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int s = s0 + j;
+                float f = __shfl_sync(0xffffffffu, s < 32 ? fa : fb, s & 31);
+                if (s >= a.nsplit) f = 0.f;
+                // an empty block has f = 0 and output words that were never written: select, do not multiply
+                o[0] += f == 0.f ? 0.f : v0[j].x * f;
+                o[1] += f == 0.f ? 0.f : v0[j].y * f;
+                o[2] += f == 0.f ? 0.f : v1[j].x * f;
+                o[3] += f == 0.f ? 0.f : v1[j].y * f;
+            }
         }
         const float inv = l > 0.f ? 1.f / l : 0.f;
         bf16* out = a.o + ((size_t)b * a.qh + head) * 128;
@@ -382,16 +392,16 @@ __device__ __forceinline__ unsigned key_id(unsigned long long k) { return 0xFFFF
 // The 16 largest of the block's register-held keys (PER per thread; 0 = empty) -> out[0..16), descending. Each warp
 // selects its own 16 with shuffles only, then warp 0 selects among the 8 x 16 survivors: two block barriers in all.
 // `wl` holds 128 keys of shared memory.
-template <int PER>
-__device__ __forceinline__ void block_top16(unsigned long long (&k)[PER], unsigned long long* out, unsigned long long* wl) {
+template <int PER, typename KEY>
+__device__ __forceinline__ void block_top16(KEY (&k)[PER], KEY* out, KEY* wl) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int round = 0; round < kDraftTopK; ++round) {
-        unsigned long long best = 0;
+        KEY best = 0;
 #pragma unroll
         for (int j = 0; j < PER; ++j) best = k[j] > best ? k[j] : best;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
-            const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+            const KEY other = __shfl_xor_sync(0xffffffffu, best, o);
             best = other > best ? other : best;
         }
         if (best != 0) {
@@ -403,16 +413,16 @@ __device__ __forceinline__ void block_top16(unsigned long long (&k)[PER], unsign
     }
     __syncthreads();
     if (warp == 0) {
-        unsigned long long m[4];
+        KEY m[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) m[j] = wl[lane + 32 * j];
         for (int round = 0; round < kDraftTopK; ++round) {
-            unsigned long long best = 0;
+            KEY best = 0;
 #pragma unroll
             for (int j = 0; j < 4; ++j) best = m[j] > best ? m[j] : best;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
-                const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+                const KEY other = __shfl_xor_sync(0xffffffffu, best, o);
                 best = other > best ? other : best;
             }
             if (best != 0) {
@@ -426,21 +436,60 @@ __device__ __forceinline__ void block_top16(unsigned long long (&k)[PER], unsign
     __syncthreads();
 }
 
+// Inside a chunk of 4096 ids a 32-bit key orders (value descending, id ascending): the bf16 value as a sortable 16-bit
+// pattern above the complemented 12-bit position; the selection then runs on single registers.
+__device__ __forceinline__ unsigned chunk_key(float logit, unsigned pos) {
+    unsigned h = __float_as_uint(bf16_round(logit)) >> 16;
+    if (logit != logit) h = 0xFFFFu;  // NaN sorts above every number
+    else h = (h & 0x8000u) ? (~h & 0xFFFFu) : (h | 0x8000u);
+    return (h << 12) | (4095u - pos);
+}
+__device__ __forceinline__ unsigned long long chunk_key_global(unsigned k, unsigned chunk) {
+    if (k == 0) return 0ull;
+    const unsigned h = k >> 12, pos = 4095u - (k & 4095u);
+    // the 32-bit pattern topk_key makes of the same value (its low 16 bits are zeros, complemented for negatives)
+    const unsigned u = h == 0xFFFFu ? 0xFFFFFFFFu : (h & 0x8000u) ? (h << 16) : ((h << 16) | 0xFFFFu);
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (chunk * (unsigned)kDraftTopkChunk + pos));
+}
+
+constexpr int kMaxMergePer = kMaxMergeChunks * kDraftTopK / kRowThreads;
+
+// grid (chunks, rows): every CTA leaves its chunk's 16 best; the last CTA of a row to finish merges the row's lists into
+// the row's slot `nchunk` of the key buffer (the 16 candidates, descending).
 __global__ void __launch_bounds__(kRowThreads) dtopk_kernel(const DTopkArgs a) {
     __shared__ unsigned long long red[(kRowThreads / 32) * kDraftTopK];
+    __shared__ unsigned s_win[kDraftTopK];
+    __shared__ unsigned s_last;
     griddep_wait();
     xchg_wait(a.wait);
     const int chunk = blockIdx.x, row = blockIdx.y;
     constexpr int PER = kDraftTopkChunk / kRowThreads;
-    unsigned long long k[PER];
+    unsigned k[PER];
     const long long start = (long long)chunk * kDraftTopkChunk;
     const float* src = a.logits + (size_t)row * a.V;
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
-        const long long id = start + threadIdx.x + (long long)j * kRowThreads;
-        k[j] = id < a.V ? topk_key(src[id], (unsigned)id) : 0ull;
+        const unsigned pos = threadIdx.x + j * kRowThreads;
+        k[j] = start + pos < a.V ? chunk_key(src[start + pos], pos) : 0u;
     }
-    block_top16<PER>(k, a.keys + ((size_t)row * a.nchunk + chunk) * kDraftTopK, red);
+    block_top16<PER, unsigned>(k, s_win, (unsigned*)red);
+    unsigned long long* row_keys = a.keys + (size_t)row * (a.nchunk + 1) * kDraftTopK;
+    if (threadIdx.x < kDraftTopK) row_keys[chunk * kDraftTopK + threadIdx.x] = chunk_key_global(s_win[threadIdx.x], (unsigned)chunk);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(a.row_count + row, 1u) == (unsigned)a.nchunk - 1 ? 1u : 0u;
+    __syncthreads();
+    if (s_last == 0) return;
+    __threadfence();
+    if (threadIdx.x == 0) a.row_count[row] = 0;
+    unsigned long long m[kMaxMergePer];
+    const int n = a.nchunk * kDraftTopK;
+#pragma unroll
+    for (int j = 0; j < kMaxMergePer; ++j) {
+        const int i = threadIdx.x + j * kRowThreads;
+        m[j] = i < n ? __ldcg(row_keys + i) : 0ull;
+    }
+    block_top16<kMaxMergePer, unsigned long long>(m, row_keys + (size_t)a.nchunk * kDraftTopK, red);
 }
 
 // Philox4x32-10 (Salmon et al., SC'11)
@@ -456,22 +505,7 @@ __device__ __forceinline__ uint4 philox4x32(uint4 c, uint2 k) {
 }
 
 // ---- lattice and walk ---------------------------------------------------------------------------------------------------------------
-constexpr int kMaxMergePer = kMaxMergeChunks * kDraftTopK / kRowThreads;
-
-// The global top-16 of a row from its chunks' lists -> s_out[16] keys.
-__device__ __forceinline__ void merge_row(const unsigned long long* keys, int nchunk, unsigned long long* s_out, unsigned long long* red) {
-    unsigned long long k[kMaxMergePer];
-    const int n = nchunk * kDraftTopK;
-#pragma unroll
-    for (int j = 0; j < kMaxMergePer; ++j) {
-        const int i = threadIdx.x + j * kRowThreads;
-        k[j] = i < n ? keys[i] : 0ull;
-    }
-    block_top16<kMaxMergePer>(k, s_out, red);
-}
-
 __global__ void __launch_bounds__(kRowThreads) dlattice_kernel(const DLatticeArgs a) {
-    __shared__ unsigned long long red[(kRowThreads / 32) * kDraftTopK];
     __shared__ unsigned long long s_cur[kDraftTopK], s_prev[kDraftTopK];
     __shared__ float s_hid[512];
     __shared__ __align__(16) unsigned s_A[kDraftTopK][257];  // codebook rows as bf16 pairs, padded against bank conflicts
@@ -481,8 +515,12 @@ __global__ void __launch_bounds__(kRowThreads) dlattice_kernel(const DLatticeArg
     __shared__ unsigned s_last;
     griddep_wait();
     const int e = blockIdx.x, tid = threadIdx.x;
-    merge_row(a.keys + (size_t)e * a.nchunk * kDraftTopK, a.nchunk, s_cur, red);
-    if (e > 0) merge_row(a.keys + (size_t)(e - 1) * a.nchunk * kDraftTopK, a.nchunk, s_prev, red);
+    // the rows' 16 candidates, merged by the top-k kernel (slot nchunk of a row's key lists)
+    if (tid < kDraftTopK) {
+        s_cur[tid] = a.keys[((size_t)e * (a.nchunk + 1) + a.nchunk) * kDraftTopK + tid];
+        if (e > 0) s_prev[tid] = a.keys[((size_t)(e - 1) * (a.nchunk + 1) + a.nchunk) * kDraftTopK + tid];
+    }
+    __syncthreads();
     for (int i = tid; i < a.R; i += kRowThreads) s_hid[i] = __bfloat162float(a.hid[(size_t)e * a.R + i]);
     if (tid < kDraftTopK) {
         const float v = key_value(s_cur[tid]);

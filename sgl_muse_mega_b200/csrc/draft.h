@@ -89,7 +89,8 @@ struct DTopkArgs {
     const float* logits;  // [gamma][V] f32 (rounded to bf16 before the comparison)
     long long V;
     int gamma, nchunk;
-    unsigned long long* keys;  // [gamma][nchunk][16]
+    unsigned long long* keys;  // [gamma][nchunk + 1][16]: the chunks' lists, then the row's merged 16
+    unsigned* row_count;       // [gamma] arrival counters of the rows' chunk CTAs (self-resetting)
     XchgWait wait;
 };
 

@@ -105,7 +105,7 @@ class DraftRank:
                       a=z(rows, H), h_post=z(rows, H), res_post=z(rows, H), c_mlp=z(rows, c.coeffs), xm=z(rows, H),
                       m=z(rows, cfg.inter // ranks), x_out=z(rows, H))  # fmt: skip
         self.hid = z(gamma, cfg.selector_rank)
-        self.keys = torch.zeros(gamma, c.topk_chunks, 16, dtype=torch.int64, device=dev)
+        self.keys = torch.zeros(gamma, c.topk_chunks + 1, 16, dtype=torch.int64, device=dev)
         self.cand = torch.zeros(gamma, 16, dtype=torch.int64, device=dev)
         self.unary = z(gamma, 16, dt=torch.float32)
         self.scores = z(gamma, 16, 16, dt=torch.float32)
