@@ -4,7 +4,7 @@
 // no fused multiply-add where it has a separate multiply and add, one bf16 rounding where it rounds):
 //   rms_norm / add_rms_norm :245-266   head_norm_rope :275-294   grouped_conv :297-316   attention :338-361
 //   topk_low_id :391-399   lattice :587-606   selector_walk :609-640   all_reduce :214-222
-// Sums of squares accumulate in f64 (the reference's mean is an f64 mean rounded to f32).
+// Sums of squares are held to about 2^-45 in two f32 words (the reference's mean is an f64 mean rounded to f32).
 //
 // Every kernel waits for its predecessor with griddepcontrol.wait before its first dependent read; exchange waits are
 // bounded (params.h). Nothing here traps: an index outside its table is clamped and recorded in the status block (code 4).
@@ -16,20 +16,19 @@ namespace {
 
 constexpr int kRowThreads = 256;
 
-// Block-wide f64 sum; `red` holds 33 doubles of shared memory.
-__device__ __forceinline__ double block_sum_d(double v, double* red) {
+// Block-wide sum of two-word sums; `red` holds 33 of them in shared memory.
+__device__ __forceinline__ double block_sum_f2(F2 v, F2* red) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
-    v = warp_sum_d(v);
-    __syncthreads();
+    v = warp_sum_f2(v);
     if (lane == 0) red[warp] = v;
     __syncthreads();
     if (warp == 0) {
-        double s = lane < nw ? red[lane] : 0.0;
-        s = warp_sum_d(s);
+        F2 s = lane < nw ? red[lane] : F2{0.f, 0.f};
+        s = warp_sum_f2(s);
         if (lane == 0) red[32] = s;
     }
     __syncthreads();
-    return red[32];
+    return f2_value(red[32]);
 }
 // ---- captured residuals -> fc's input rows ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kRowThreads) dfeats_kernel(const DFeatsArgs a) {
@@ -61,7 +60,7 @@ __device__ __forceinline__ void ar8(const DNormArgs& a, int row, int ch0, float 
 }
 
 __global__ void __launch_bounds__(1024) dnorm_kernel(const DNormArgs a) {
-    __shared__ double red[33];
+    __shared__ F2 red[33];
     __shared__ long long s_tok;
     griddep_wait();
     xchg_wait(a.wait);
@@ -104,7 +103,7 @@ __global__ void __launch_bounds__(1024) dnorm_kernel(const DNormArgs a) {
         load8(src + ch0, x);
     }
     if (a.x_out != nullptr) store8(a.x_out + (size_t)row * a.H + ch0, x);
-    double sq = 0.0;
+    F2 sq = {0.f, 0.f};
     if (a.residual != nullptr) {
         float r[8];
         load8(a.residual + (size_t)row * a.H + ch0, r);
@@ -112,8 +111,8 @@ __global__ void __launch_bounds__(1024) dnorm_kernel(const DNormArgs a) {
         for (int i = 0; i < 8; ++i) x[i] = __fadd_rn(x[i], r[i]);
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) sq += (double)x[i] * (double)x[i];
-    const float ms = (float)(block_sum_d(sq, red) / (double)a.H);
+    for (int i = 0; i < 8; ++i) f2_add_sq(sq, x[i]);
+    const float ms = (float)(block_sum_f2(sq, red) / (double)a.H);
     const float rs = rsqrt_exact(__fadd_rn(ms, a.eps));
     float w[8], h[8];
     load8(a.w + ch0, w);

@@ -11,6 +11,37 @@ __device__ __forceinline__ double warp_sum_d(double v) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
+// Sums of squares to about 2^-45 without f64 arithmetic (scarce on this part): a square is split exactly into its rounded
+// value and the rounding error (fma), the running sum keeps the exact error of every addition in a second word (two-sum).
+struct F2 {
+    float hi, lo;
+};
+__device__ __forceinline__ void f2_add(F2& s, float x) {
+    const float t = __fadd_rn(s.hi, x), bb = __fsub_rn(t, s.hi);
+    s.lo = __fadd_rn(s.lo, __fadd_rn(__fsub_rn(s.hi, __fsub_rn(t, bb)), __fsub_rn(x, bb)));
+    s.hi = t;
+}
+__device__ __forceinline__ void f2_add_sq(F2& s, float x) {
+    const float p = __fmul_rn(x, x);
+    f2_add(s, p);
+    s.lo = __fadd_rn(s.lo, __fmaf_rn(x, x, -p));
+}
+__device__ __forceinline__ void f2_merge(F2& s, const F2& o) {
+    f2_add(s, o.hi);
+    s.lo = __fadd_rn(s.lo, o.lo);
+}
+__device__ __forceinline__ F2 warp_sum_f2(F2 v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        F2 other;
+        other.hi = __shfl_xor_sync(0xffffffffu, v.hi, o);
+        other.lo = __shfl_xor_sync(0xffffffffu, v.lo, o);
+        f2_merge(v, other);
+    }
+    return v;
+}
+__device__ __forceinline__ double f2_value(const F2& s) { return (double)s.hi + (double)s.lo; }
+
 // 1 / sqrt(x) as two correctly rounded f32 operations
 __device__ __forceinline__ float rsqrt_exact(float x) { return __fdiv_rn(1.0f, __fsqrt_rn(x)); }
 
@@ -43,10 +74,10 @@ __device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
 // block's q / k round the normed head to bf16 before the rotation, the context K does not.
 __device__ __forceinline__ void head_norm_rope_vals(float (&v)[4], const bf16* w, float eps, const float* cos_sin, bool round_normed,
                                                     bf16* out, int lane) {
-    double sq = 0.0;
+    F2 sq = {0.f, 0.f};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) sq += (double)v[i] * (double)v[i];
-    const float ms = (float)(warp_sum_d(sq) / 128.0);
+    for (int i = 0; i < 4; ++i) f2_add_sq(sq, v[i]);
+    const float ms = (float)(f2_value(warp_sum_f2(sq)) / 128.0);
     const float r = rsqrt_exact(__fadd_rn(ms, eps));
     const __nv_bfloat162 wl = *(const __nv_bfloat162*)(w + 2 * lane), wh = *(const __nv_bfloat162*)(w + 64 + 2 * lane);
     const float wv[4] = {__low2float(wl), __high2float(wl), __low2float(wh), __high2float(wh)};
