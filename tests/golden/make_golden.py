@@ -1,7 +1,7 @@
 """Generates the golden fixtures of ``tests/golden/*.pt`` from the REFERENCE's own torch oracle.
 
-Run once, in a container where the reference checkout is mounted (default ``/root/reference``; override with
-``MUSE_REFERENCE``):
+Run once, in a container where the reference checkout is mounted (its location: ``REF`` below, or the environment
+variable ``MUSE_REFERENCE``):
 
     python tests/golden/make_golden.py
 
