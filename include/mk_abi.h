@@ -222,6 +222,14 @@ typedef struct MkLayerBind {
     // w_r), rows past N zero; w_p and w_up then hold this rank's node block only (P / node_ranks and H / node_ranks
     // rows). One bulk copy brings an item in, instead of one per weight row.
     int64_t dense_packed;
+    // Expert parallelism of the expert block (whole experts per rank instead of the reference's tensor-parallel slices):
+    // with expert_hi > expert_lo this launch's route tables keep only the routed (row, slot) pairs whose expert id lies
+    // in [expert_lo, expert_hi), so g1, g2 and their zb rows cover this rank's experts alone; the other pairs' zb rows
+    // are the other ranks' to write (into the same zb buffer) before combine reads them. The expert arrays are still
+    // indexed by the global id: a rank that holds only its experts passes base pointers moved back by expert_lo experts.
+    // 0 / 0: every expert (the reference's layout).
+    int64_t expert_lo;
+    int64_t expert_hi;
 } MkLayerBind;
 int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind* bind, MkLaunch** out);
 

@@ -181,14 +181,18 @@ static __device__ void topk_row(const TopkArgs& a, int row, int lane, int* s_ids
     else topk_row_t<kTopkPer>(a, row, lane, s_ids);
 }
 
-static __device__ void route_tables(const int* s_ids, int E, int S, RouteTables* rt, int* cnt, int* first) {
+// e_hi > e_lo: only the slots routed to an expert in [e_lo, e_hi) enter the tables (this rank's whole experts); the
+// other slots belong to other ranks.
+static __device__ void route_tables(const int* s_ids, int E, int S, RouteTables* rt, int* cnt, int* first, int e_lo = 0,
+                                    int e_hi = 0) {
     const int tid = threadIdx.x, nt = blockDim.x;
     for (int e = tid; e < E; e += nt) cnt[e] = 0;
     __syncthreads();
     int my_e = -1;
     if (tid < S) {
         my_e = s_ids[tid];
-        atomicAdd(&cnt[my_e], 1);
+        if (e_hi > e_lo && (my_e < e_lo || my_e >= e_hi)) my_e = -1;
+        if (my_e >= 0) atomicAdd(&cnt[my_e], 1);
     }
     __syncthreads();
     if (tid < 32) {
@@ -218,7 +222,7 @@ static __device__ void route_tables(const int* s_ids, int E, int S, RouteTables*
         }
     }
     __syncthreads();
-    if (tid < S) {
+    if (tid < S && my_e >= 0) {
         int before = 0;
         for (int s = 0; s < tid; ++s) before += (s_ids[s] == my_e);
         rt->slot[first[my_e] + before] = tid;
@@ -305,7 +309,7 @@ __global__ void __launch_bounds__(512) route_nq_kernel(const RouteNqArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (warp < a.topk.M) topk_row(a.topk, warp, lane, s_ids);
     __syncthreads();
-    route_tables(s_ids, a.topk.E, a.b_live * a.topk.k, a.rt, cnt, first);
+    route_tables(s_ids, a.topk.E, a.b_live * a.topk.k, a.rt, cnt, first, a.topk.e_lo, a.topk.e_hi);
 }
 
 // ---- h row view: scales moved to the row's largest exponent ---------------------------------------------------------------

@@ -233,6 +233,9 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     const int I_s = (int)c.inter_rank, H_s = (int)c.hidden_rank, slots = (int)c.slots;
     const int b_live = b->b_live > 0 ? (int)b->b_live : M;
     MK_REQUIRE(b_live <= M, "b_live %d exceeds rows %d", b_live, M);
+    MK_REQUIRE((b->expert_lo == 0 && b->expert_hi == 0) || (b->expert_lo >= 0 && b->expert_lo < b->expert_hi && b->expert_hi <= E),
+               "expert range [%lld, %lld) of %d experts", (long long)b->expert_lo, (long long)b->expert_hi, E);
+    MK_REQUIRE(b->expert_hi == 0 || s.ranks == 1, "an expert range takes whole experts (ranks 1), got ranks %lld", (long long)s.ranks);
     const bool fp4 = !s.bf16, tail = s.tail != 0;
 
     NEED(qkv_in); NEED(k_cache); NEED(v_cache); NEED(page_table); NEED(kv_len); NEED(x_attn);
@@ -415,7 +418,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     wait_for(L->post_norm.wait, XP_AR, 0, all, ST_POST_NORM);
     wait_for(L->cross_norm.wait, XP_UNPOOL, node0, nr, ST_CROSS_NORM);
     L->topk = TopkArgs{(const float*)b->logits, (const float*)b->expert_bias, (int*)b->topk_idx32, (float*)b->topk_w,
-                       b->router_mult, (float)b->route_scale, E, K, M, (int*)b->status, scores};
+                       b->router_mult, (float)b->route_scale, E, K, M, (int*)b->status, scores, (int)b->expert_lo, (int)b->expert_hi};
     L->nq = NqArgs{(const bf16*)b->pool_ag, (const bf16*)b->gamma, (unsigned char*)b->q, (unsigned char*)b->sf,
                    (float*)b->x_scale, (float)b->eps, P, (int)s.bf16};
     L->combine = CombineArgs{(const bf16*)b->zb, (const float*)b->topk_w, (const bf16*)b->gamma_p1, (bf16*)b->y, P, K, b_live};

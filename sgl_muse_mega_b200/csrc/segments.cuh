@@ -673,7 +673,7 @@ __global__ void __launch_bounds__(kSegThreads, 1) segment_a_kernel(const SegAArg
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         for (int row = warp; row < a.topk.M; row += kSegWarps) topk_row(a.topk, row, lane, sh.s_ids);
         __syncthreads();
-        route_tables(sh.s_ids, a.topk.E, a.b_live * a.topk.k, a.rt, sh.cnt, sh.first);
+        route_tables(sh.s_ids, a.topk.E, a.b_live * a.topk.k, a.rt, sh.cnt, sh.first, a.topk.e_lo, a.topk.e_hi);
     } else if (cta < a.topk.M) {
         xchg_wait_epoch(a.nq.wait, e_pool);
         nq_row(a.nq, cta, sh.red);

@@ -40,6 +40,7 @@ struct TopkArgs {
     int E, k, M;
     int* status;  // a row with NaN scores is recorded here (code 6); may be null
     const float* score;  // [M, E] selection scores from the router GEMM's epilogue, or null: computed here from the logits
+    int e_lo, e_hi;      // e_hi > e_lo: the route tables keep the experts in [e_lo, e_hi) only (expert parallelism)
 };
 struct NqArgs {
     const bf16* pooled;

@@ -23,6 +23,7 @@ from . import weights
 
 # stage groups between which every rank must have finished before any rank continues (the exchanges)
 STAGE_GROUPS = ((0, 3), (3, 2), (5, 5), (10, 2), (12, 2), (14, 3))
+EXPERT_FIELDS = ("gate_q", "gate_sf", "up_q", "up_sf", "w2_q", "w2_sf", "g1_alphas", "g1_scale_c", "g2_alphas", "gate", "up", "w2")
 STAGE_NAMES = (
     "attn_split", "attn_combine", "o_proj", "post_norm", "pooler", "router", "topk", "nq", "route_tables", "g1",
     "h_row", "g2", "combine", "unpooler", "cross_norm", "qkv", "rowops",
@@ -44,7 +45,7 @@ class LayerRank:
 
     def __init__(self, lib: host.Library, module, case, rank: int, device, kv_rows: Optional[int] = None, tensors=None,
                  tensor_cores: bool = True, keep_plain_experts: bool = True, io: Optional[dict] = None,
-                 packed: bool = False):  # fmt: skip
+                 packed: bool = False, expert_range: Optional[tuple] = None):  # fmt: skip
         """``io`` replaces buffers this layer would allocate with ones it shares with its neighbours in a stack: inputs
         ``qkv_in`` / ``stream_in`` (the predecessor's outputs), ``k_cache`` / ``v_cache`` (the pools the predecessor
         appended to), the step's feeds ``page_table`` / ``kv_len`` / ``cache_loc`` / ``next_cos_sin`` and the
@@ -53,7 +54,10 @@ class LayerRank:
         ``flags``).
         ``tensor_cores``: bind the packed NVFP4 images when the shape has whole 128-row tiles (the tcgen05 expert
         kernels); otherwise, or when False, the experts run on the general CUDA-core kernels from the plain tensors.
-        ``keep_plain_experts`` False drops the plain expert tensors once the images exist (halves the expert memory)."""
+        ``keep_plain_experts`` False drops the plain expert tensors once the images exist (halves the expert memory).
+        ``expert_range`` (lo, hi): expert parallelism of a lone-rank shape (``MkLayerBind.expert_lo`` / ``expert_hi``):
+        this object keeps and packs the experts [lo, hi) only and runs the routed slots that fall on them; the ranks of
+        such a world share ``zb`` (``io``) and any one of them runs combine once all have run their experts."""
         cfg = case.cfg
         self.lib, self.case, self.rank, self.device = lib, case, rank, device
         self.shape = layer_shape(cfg, case, rank)
@@ -62,7 +66,9 @@ class LayerRank:
         dev = lambda x: None if x is None else x.to(device).contiguous()  # noqa: E731
         io = dict(io or {})
         skip = set(io) | ({"k_ctx", "v_ctx"} if "k_cache" in io else set())
-        self.w = {k: (None if k in skip else dev(v)) for k, v in vars(t).items()}
+        self.expert_lo, self.expert_hi = expert_range or (0, 0)
+        per_expert = lambda k, v: v if v is None or not self.expert_hi or k not in EXPERT_FIELDS else v[self.expert_lo : self.expert_hi]  # noqa: E731
+        self.w = {k: (None if k in skip else dev(per_expert(k, v))) for k, v in vars(t).items()}
         for k in ("qkv_in", "stream_in", "next_cos_sin"):
             if k in io:
                 self.w[k] = io[k]
@@ -171,6 +177,13 @@ class LayerRank:
             return [getattr(p, attr) if p is not None else None for p in peers]
 
         fp4 = not case.bf16
+
+        def ex(t):
+            """A per-expert array's address as the kernels index it (by the global expert id)."""
+            if t is None or not self.expert_hi:
+                return t
+            return t.data_ptr() - self.expert_lo * t[0].numel() * t.element_size()
+
         bind = host.make(
             "MkLayerBind",
             qkv_in=w["qkv_in"], k_cache=self.k_cache, v_cache=self.v_cache, kv_rows=self.kv_rows,
@@ -181,10 +194,10 @@ class LayerRank:
             w_r=w["router"], logits=o["logits"], router_mult=case.router_mult, expert_bias=w["expert_bias"],
             topk_idx32=o["ids"], topk_w=o["w"], route_scale=cfg.route_scale, gamma=w["pre_gamma"], eps=case.pre_eps,
             q=o["xq"], sf=o["x_sf"], x_scale=o["x_scale"],
-            w1_gate=w["gate_q"] if fp4 else w["gate"], w1_gate_sf=w["gate_sf"], w1_up=w["up_q"] if fp4 else w["up"],
-            w1_up_sf=w["up_sf"], w2=w["w2_q"] if fp4 else w["w2"], w2_sf=w["w2_sf"], w1_pack=self.w1_pack,
-            w2_pack=self.w2_pack, g1_alphas=w["g1_alphas"],
-            g1_scale_c=w["g1_scale_c"], g2_alphas=w["g2_alphas"], z=self.z, z_sf=self.z_sf, z_ex=self.z_ex, zb=self.zb,
+            w1_gate=ex(w["gate_q"] if fp4 else w["gate"]), w1_gate_sf=ex(w["gate_sf"]),
+            w1_up=ex(w["up_q"] if fp4 else w["up"]), w1_up_sf=ex(w["up_sf"]), w2=ex(w["w2_q"] if fp4 else w["w2"]),
+            w2_sf=ex(w["w2_sf"]), w1_pack=ex(self.w1_pack), w2_pack=ex(self.w2_pack), g1_alphas=ex(w["g1_alphas"]),
+            g1_scale_c=ex(w["g1_scale_c"]), g2_alphas=ex(w["g2_alphas"]), z=self.z, z_sf=self.z_sf, z_ex=self.z_ex, zb=self.zb,
             z_peer=peer(self.z_name), zsf_peer=peer("z_sf"), zex_peer=peer("z_ex"), zb_peer=peer("zb"),
             gamma_p1=w["gamma_p1"], y=o["y"], w_up=w["unpooler"], unpool_ag=self.unpool_ag,
             unpool_ag_peer=peer("unpool_ag"), c_alpha=w["cross_alpha"], c_beta=w["cross_beta"], c_pre_w=w["cross_pre_w"],
@@ -192,6 +205,7 @@ class LayerRank:
             qkv_out=o["qkv_next"], cos_sin=w["next_cos_sin"], cache_loc=self.cache_loc, next_k_cache=self.next_k,
             next_v_cache=self.next_v, next_kv_rows=self.next_kv_rows, q_scale=cfg.q_scale, qkv_eps=cfg.rms_eps,
             flags=self.flags, flags_peer=peer("flags"), ws=self.ws, status=self.status, b_live=b_live, wait_budget=wait_budget, fused=fused, dense_packed=int(self.packed),
+            expert_lo=self.expert_lo, expert_hi=self.expert_hi,
         )  # fmt: skip
         self.launch_record = self.lib.layer_bind(self.module, self.shape, bind)
         return self.launch_record

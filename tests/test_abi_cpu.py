@@ -7,7 +7,7 @@ import re
 import pytest
 import torch
 
-from golden_cases import CASES
+from golden_cases import CASES, small_cfg
 from sgl_muse_mega_b200.common import host
 from sgl_muse_mega_b200.muse_spark.b200 import layer as L
 from sgl_muse_mega_b200.muse_spark.b200 import synthetic
@@ -84,6 +84,27 @@ def test_pack_only_bind_and_refusals(lib):
     rank.w["o_proj"] = None
     with pytest.raises(RuntimeError, match="w_o"):
         rank.bind()
+
+
+def test_expert_range_binds_whole_experts_only(lib):
+    """Expert parallelism of the expert block: a lone-rank shape keeps its experts [lo, hi) (sliced and packed on their
+    own, bound by pointers moved back by lo experts); bad ranges and tensor-parallel shapes are refused."""
+    from sgl_muse_mega_b200.muse_spark.b200 import expert_block as X
+
+    cfg = X.block_config(experts=16, moe_hidden=1024, moe_inter=1024)
+    case = synthetic.layer_case(cfg, rows=4, ctx=8, seed=5)
+    rank = L.LayerRank(lib, None, case, 0, torch.device("cpu"), expert_range=(4, 8))
+    assert rank.w["gate_q"].shape[0] == 4 and rank.w1_pack.shape[0] == 4 and rank.w["expert_bias"].shape[0] == 16
+    rec = rank.bind()
+    assert rec.info().kernels == 13
+    for lo, hi in ((4, 4), (8, 4), (0, 17), (-1, 4)):
+        rank.expert_lo, rank.expert_hi = lo, hi
+        with pytest.raises(RuntimeError, match="expert range"):
+            rank.bind()
+    tp2 = synthetic.layer_case(small_cfg(2), rows=4, ctx=8, seed=6)
+    r2 = L.LayerRank(lib, None, tp2, 0, torch.device("cpu"), expert_range=(0, 8))
+    with pytest.raises(RuntimeError, match="whole experts"):
+        r2.bind()
 
 
 def test_module_load_needs_builtin_image(lib):
