@@ -1,5 +1,5 @@
 """Times one skinny GEMM of the item engine in isolation: ``out[16, N] = x[16, K] W[N, K]^T`` through ``mk_lm_head_bind``
-(f32 outputs), weights as item images or row-major, L2 flushed between launches.
+(f32 outputs), weights as item images or row-major, L2 flushed between launches (or left warm).
 
     python -m sgl_muse_mega_b200.muse_spark.b200.gemm_probe --n 25256 --k 8192 [--plain] [--reps 5]
 
@@ -24,6 +24,7 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=16)
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--plain", action="store_true", help="row-major weights (one bulk copy per weight row)")
+    ap.add_argument("--warm", action="store_true", help="no L2 flush between launches: weights that fit L2 are read from it")
     args = ap.parse_args()
     dev = torch.device("cuda:0")
     lib = host.library()
@@ -37,7 +38,8 @@ def main() -> None:
     s = torch.cuda.current_stream().cuda_stream
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     for _ in range(args.reps):
-        flush.zero_()
+        if not args.warm:
+            flush.zero_()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         lm.launch(s, False)
