@@ -351,6 +351,17 @@ typedef struct MkAcceptBind {
     uint64_t status;
     int64_t pool_rows;         // rows of the KV pools behind loc_full / loc_swa (identity slots): a next window that would
                                // not fit is clamped to the last rows and recorded (code 4); 0 = unchecked
+    // The sampled accept (reference kernels/dflash/sample.cuh sample_accept; arithmetic test/reference/dflash2.py:703-791)
+    // instead of the greedy one when samp is bound: the rows' sampling distributions (temperature, exact top-k and top-p
+    // sets), block verification (block_verify 1) or the token-by-token test against the draft walk's probabilities, the
+    // bonus token from the residual by inverse CDF in vocabulary order. Same launch, same outputs (top1 is not written).
+    uint64_t samp;             // i64 [4] as MkDflashDraftHeadBind.samp (seed, stream, top_k, temperature | top_p bits), or 0
+    uint64_t cand;             // i64 [b_live - 1, 16]: the draft slots' candidates (MkDflashDraftHeadBind.cand)
+    uint64_t walk_q;           // f32 [b_live - 1, 16]: the walk's probabilities over them (MkDflashDraftHeadBind.walk_q)
+    int64_t block_verify;
+    uint64_t sample_ws;        // scratch of sample_ws_bytes >= rows x vocab x 12 + 256, 256-byte aligned
+    int64_t sample_ws_bytes;
+    uint64_t sample_out;       // out f64 [2] or 0: the residual's scale and the mass of the bonus distribution
 } MkAcceptBind;
 int mk_accept_bind(MkModule* module, const MkAcceptBind* bind, MkLaunch** out);
 

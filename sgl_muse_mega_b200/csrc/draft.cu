@@ -491,18 +491,6 @@ __global__ void __launch_bounds__(kRowThreads) dtopk_kernel(const DTopkArgs a) {
     block_top16<kMaxMergePer, unsigned long long>(m, row_keys + (size_t)a.nchunk * kDraftTopK, red);
 }
 
-// Philox4x32-10 (Salmon et al., SC'11)
-__device__ __forceinline__ uint4 philox4x32(uint4 c, uint2 k) {
-#pragma unroll
-    for (int r = 0; r < 10; ++r) {
-        const unsigned long long p0 = (unsigned long long)0xD2511F53u * c.x, p1 = (unsigned long long)0xCD9E8D57u * c.z;
-        c = make_uint4((unsigned)(p1 >> 32) ^ c.y ^ k.x, (unsigned)p1, (unsigned)(p0 >> 32) ^ c.w ^ k.y, (unsigned)p0);
-        k.x += 0x9E3779B9u;
-        k.y += 0xBB67AE85u;
-    }
-    return c;
-}
-
 // ---- lattice and walk ---------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kRowThreads) dlattice_kernel(const DLatticeArgs a) {
     __shared__ unsigned long long s_cur[kDraftTopK], s_prev[kDraftTopK];

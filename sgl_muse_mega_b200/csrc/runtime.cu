@@ -906,7 +906,8 @@ int mk_softcap_bind(MkModule* module, const MkSoftcapBind* b, MkLaunch** out) {
 
 int mk_accept_bind(MkModule* module, const MkAcceptBind* b, MkLaunch** out) {
     MK_REQUIRE(out != nullptr && b != nullptr, "bind or out is NULL");
-    NEED(logits); NEED(tokens); NEED(words); NEED(out_ring); NEED(top1); NEED(counter);
+    NEED(logits); NEED(tokens); NEED(words); NEED(out_ring); NEED(counter);
+    MK_REQUIRE(b->samp != 0 || b->top1 != 0, "top1 is not bound");
     MK_REQUIRE(b->rows >= 1 && b->rows <= kMaxRows && b->b_live >= 1 && b->b_live <= b->rows, "rows %lld / b_live %lld", (long long)b->rows,
                (long long)b->b_live);
     MK_REQUIRE(b->vocab >= 1 && b->ring >= b->rows && b->cap > 0, "vocab %lld / ring %lld / cap %g", (long long)b->vocab, (long long)b->ring, b->cap);
@@ -914,6 +915,14 @@ int mk_accept_bind(MkModule* module, const MkAcceptBind* b, MkLaunch** out) {
     MK_REQUIRE(b->cos_sin == 0 || (b->cos_sin_cache != 0 && b->cos_sin_rows >= 1), "cos_sin without its cache");
     MK_REQUIRE(b->dslot == 0 || (b->dkv_len != 0 && b->dring >= 1), "dslot without dkv_len / dring");
     MK_REQUIRE(b->dcos_sin == 0 || (b->dslot != 0 && b->dcos_sin_cache != 0 && b->dcos_sin_rows >= 1), "dcos_sin without dslot or its cache");
+    const int64_t cells = b->rows * b->vocab, ys_bytes = (cells * 4 + 255) / 256 * 256;
+    if (b->samp != 0) {
+        NEED(cand); NEED(walk_q); NEED(sample_ws);
+        MK_REQUIRE(b->b_live >= 2, "the sampled accept needs at least one draft row");
+        MK_REQUIRE(b->sample_ws_bytes >= ys_bytes + cells * 8 + 256, "sample_ws_bytes %lld below the %lld the sampled accept needs",
+                   (long long)b->sample_ws_bytes, (long long)(ys_bytes + cells * 8 + 256));
+        MK_REQUIRE((b->sample_ws & 255) == 0, "sample_ws is not 256-byte aligned");
+    }
     MkLaunch* L = new_op_launch(module, OP_ACCEPT);
     MK_REQUIRE(L != nullptr, "out of host memory");
     L->accept = AcceptArgs{(const float*)b->logits, (int)b->vocab, (int)b->rows, (int)b->b_live, (float)b->scale, (float)b->cap,
@@ -925,6 +934,16 @@ int mk_accept_bind(MkModule* module, const MkAcceptBind* b, MkLaunch** out) {
     logits_wait(L->accept.wait, b->flags, b->contributors, b->wait_budget, b->status);
     L->accept.pool_rows = b->pool_rows;
     L->accept.status = (int*)b->status;
+    if (b->samp != 0) {
+        L->accept.samp = (const long long*)b->samp;
+        L->accept.cand = (const long long*)b->cand;
+        L->accept.walk_q = (const float*)b->walk_q;
+        L->accept.block_verify = b->block_verify != 0;
+        L->accept.ys = (float*)b->sample_ws;
+        L->accept.es = (double*)(b->sample_ws + (uint64_t)ys_bytes);
+        L->accept.row_z = (double*)(b->sample_ws + (uint64_t)ys_bytes + (uint64_t)cells * 8);
+        L->accept.sample_out = (double*)b->sample_out;
+    }
     L->status = (int*)b->status;
     *out = L;
     return 0;

@@ -226,6 +226,15 @@ struct AcceptArgs {
     XchgWait wait;                    // the lm_head shards of every rank
     long long pool_rows;              // 0: unchecked
     int* status;
+    // the sampled accept (samp non-null) instead of the greedy one
+    const long long* samp;            // i64 [4]: seed, stream, top_k, f32 temperature bits | f32 top_p bits << 32
+    const long long* cand;            // i64 [b_live - 1][16] the draft slots' candidates
+    const float* walk_q;              // f32 [b_live - 1][16] the walk's probabilities over them
+    int block_verify;                 // 1: block verification, 0: token by token
+    float* ys;                        // scratch f32 [rows][vocab]: soft-capped logits / T
+    double* es;                       // scratch f64 [rows][vocab]: exp(y - max) of the kept entries, 0 elsewhere
+    double* row_z;                    // scratch f64 [rows]: the kept mass
+    double* sample_out;               // out f64 [2] or null: the residual's scale and the bonus distribution's mass
 };
 cudaError_t feeds_launch(const FeedsArgs& a, cudaStream_t s, bool pdl);
 cudaError_t entry_launch(const EntryArgs& a, cudaStream_t s, bool pdl);

@@ -134,4 +134,22 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N));
 }
 
+// Philox4x32-10 (Salmon et al., SC'11): the sampled step's uniforms are the top 24 bits of word i % 4 of
+// philox({iteration, stream, purpose, i / 4}, seed); purpose 0 the draft walk, 1 the accept.
+__device__ __forceinline__ uint4 philox4x32(uint4 c, uint2 k) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const unsigned long long p0 = (unsigned long long)0xD2511F53u * c.x, p1 = (unsigned long long)0xCD9E8D57u * c.z;
+        c = make_uint4((unsigned)(p1 >> 32) ^ c.y ^ k.x, (unsigned)p1, (unsigned)(p0 >> 32) ^ c.w ^ k.y, (unsigned)p0);
+        k.x += 0x9E3779B9u;
+        k.y += 0xBB67AE85u;
+    }
+    return c;
+}
+__device__ __forceinline__ float philox_uniform(unsigned long long seed, unsigned stream, unsigned iter, unsigned purpose, int i) {
+    const uint4 r = philox4x32(make_uint4(iter, stream, purpose, (unsigned)i / 4), make_uint2((unsigned)seed, (unsigned)(seed >> 32)));
+    const unsigned w = (i & 3) == 0 ? r.x : (i & 3) == 1 ? r.y : (i & 3) == 2 ? r.z : r.w;
+    return (float)(w >> 8) * 0x1p-24f;
+}
+
 }  // namespace mk

@@ -57,8 +57,11 @@ class DraftRank:
                  pool_rows: int, rope_rows: int, lib: Optional[host.Library] = None, module=None, words: Optional[torch.Tensor] = None,
                  caps: Optional[Sequence[torch.Tensor]] = None, verify_ids: Optional[torch.Tensor] = None, exchange=None,
                  flags: bool = False, wait_budget: int = 0, packed: bool = False, lm_head_packed: Optional[bool] = None,
-                 samp: Optional[torch.Tensor] = None):  # fmt: skip
-        """``packed``: upload the draft's GEMM weights as item images (``weights.pack_items``: one bulk copy per item).
+                 samp: Optional[torch.Tensor] = None, cand: Optional[torch.Tensor] = None,
+                 walk_q: Optional[torch.Tensor] = None):  # fmt: skip
+        """``samp`` (the sampling words on the device) selects the sampled walk; ``cand`` / ``walk_q``: buffers a sampled
+        accept was bound to (default: allocated here).
+        ``packed``: upload the draft's GEMM weights as item images (``weights.pack_items``: one bulk copy per item).
         ``lm_head_packed``: ``t.lm_head`` already is one (a target stack built with ``packed``); default: pack it too."""
         self.cfg, self.rank, self.ranks, self.rows, self.device = cfg, rank, ranks, rows, device
         self.packed = bool(packed)
@@ -106,14 +109,14 @@ class DraftRank:
                       m=z(rows, cfg.inter // ranks), x_out=z(rows, H))  # fmt: skip
         self.hid = z(gamma, cfg.selector_rank)
         self.keys = torch.zeros(gamma, c.topk_chunks + 1, 16, dtype=torch.int64, device=dev)
-        self.cand = torch.zeros(gamma, 16, dtype=torch.int64, device=dev)
+        self.cand = cand if cand is not None else torch.zeros(gamma, 16, dtype=torch.int64, device=dev)
         self.unary = z(gamma, 16, dt=torch.float32)
         self.scores = z(gamma, 16, 16, dt=torch.float32)
         self.pick = z(gamma, dt=torch.int32)
         self.drafts = z(gamma, dt=torch.int64)
         self.verify_ids = verify_ids if verify_ids is not None else z(rows, dt=torch.int64)
         self.samp = samp  # i64 [4] sampling words on the device (``sampling_words``), or None: the greedy walk
-        self.walk_q = z(gamma, 16, dt=torch.float32)
+        self.walk_q = walk_q if walk_q is not None else z(gamma, 16, dt=torch.float32)
         self.status = z(16, dt=torch.int32)
         self.launches: list = []
 

@@ -29,7 +29,7 @@ class Iteration:
         """``stack``: the bound target stack of this rank (greedy tail). ``capture``: indices into ``stack.layers`` whose
         output residual feeds the draft (default: ``dcfg.capture`` relative to the stack's first layer). ``peers`` /
         ``exchange``: the draft's exchange buffers of a world of several processes (``DraftRank.bind``)."""
-        assert stack.bound and stack.greedy, "the iteration ends with the greedy accept of a bound stack"
+        assert stack.bound and stack.greedy, "the iteration ends with the accept (greedy or sampled) of a bound stack"
         cfg = stack.case.cfg
         assert (dcfg.hidden, dcfg.vocab) == (cfg.hidden, cfg.vocab), "the draft borrows the target's embedding and lm_head"
         first = stack.case.first_layer
@@ -43,6 +43,7 @@ class Iteration:
             dcfg, dw, t, stack.rank, cfg.tp, stack.device, rows=stack.case.rows, pool_rows=pool_rows, rope_rows=rope_rows,
             lib=stack.lib, module=stack.module, words=stack.accept.words, caps=caps, verify_ids=stack.tokens, exchange=exchange,
             wait_budget=wait_budget, packed=stack.packed if packed is None else packed, lm_head_packed=stack.packed,
+            samp=stack.samp, cand=stack.draft_cand, walk_q=stack.draft_walk_q,
         )  # fmt: skip
         self.draft.bind(peers)
         self.graph: Optional[torch.cuda.CUDAGraph] = None

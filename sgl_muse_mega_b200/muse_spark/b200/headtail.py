@@ -125,9 +125,16 @@ class Accept:
     def __init__(self, lib: host.Library, module, *, logits, tokens, b_live: int, scale: float, cap: float, ring: int = 64,
                  accept_override: Optional[torch.Tensor] = None, cos_sin_cache=None, cos_sin=None, loc_full=None,
                  loc_swa=None, kv_len=None, dcos_sin_cache=None, dring: int = 0, flags=None, contributors: int = 0,
-                 wait_budget: int = 0, pool_rows: int = 0):  # fmt: skip
+                 wait_budget: int = 0, pool_rows: int = 0, samp=None, cand=None, walk_q=None, block_verify: bool = True):  # fmt: skip
+        """``samp`` (the sampling words on the device, ``dflash.draft.sampling_words``) with the draft head's ``cand`` and
+        ``walk_q`` binds the sampled accept instead of the greedy one (``sample_out``: the residual's scale and mass)."""
         dev = logits.device
         rows, vocab = logits.shape
+        self.sample_ws = self.sample_out = None
+        if samp is not None:
+            ys = (rows * vocab * 4 + 255) // 256 * 256
+            self.sample_ws = _z(ys + rows * vocab * 8 + 256, dtype=torch.uint8, device=dev)
+            self.sample_out = _z(2, dtype=torch.float64, device=dev)
         self.words = _z(N_WORDS, dtype=torch.int64, device=dev)
         self.out_ring = _z(ring, dtype=torch.int32, device=dev)
         self.top1 = _z(rows, dtype=torch.int32, device=dev)
@@ -137,7 +144,7 @@ class Accept:
         self.dcos_sin = _z(2 * b_live, 128, dtype=torch.float32, device=dev) if draft else None
         self.dslot = _z(2 * b_live, dtype=torch.int32, device=dev) if draft else None
         self.dkv_len = _z(1, dtype=torch.int32, device=dev) if draft else None
-        self.keep = (logits, tokens, accept_override, cos_sin_cache, cos_sin, loc_full, loc_swa, kv_len, dcos_sin_cache)
+        self.keep = (logits, tokens, accept_override, cos_sin_cache, cos_sin, loc_full, loc_swa, kv_len, dcos_sin_cache, samp, cand, walk_q)
         self.bind = host.make(
             "MkAcceptBind", logits=logits, vocab=vocab, rows=rows, b_live=b_live, scale=scale, cap=cap, tokens=tokens,
             accept_override=accept_override, n_override=0 if accept_override is None else accept_override.numel(),
@@ -146,6 +153,8 @@ class Accept:
             cos_sin=cos_sin, loc_full=loc_full, loc_swa=loc_swa, kv_len=kv_len, dcos_sin_cache=dcos_sin_cache,
             dcos_sin_rows=0 if dcos_sin_cache is None else dcos_sin_cache.shape[0], dcos_sin=self.dcos_sin,
             dslot=self.dslot, dkv_len=self.dkv_len, dring=dring, flags=flags, contributors=contributors,
-            wait_budget=wait_budget, status=self.status, pool_rows=pool_rows,
+            wait_budget=wait_budget, status=self.status, pool_rows=pool_rows, samp=samp, cand=cand, walk_q=walk_q,
+            block_verify=int(block_verify), sample_ws=self.sample_ws,
+            sample_ws_bytes=0 if self.sample_ws is None else self.sample_ws.numel(), sample_out=self.sample_out,
         )  # fmt: skip
         self.launch = lib.bind("mk_accept_bind", module, self.bind)

@@ -67,8 +67,12 @@ class Stack:
                  kv_rows: Optional[int] = None, tensor_cores: bool = True, keep_plain_experts: bool = True,
                  greedy: bool = True, accept_override: Optional[torch.Tensor] = None, ring: int = 64,
                  b_live: int = 0, wait_budget: int = 0, fused: bool = False, frame: Optional[dict] = None,
-                 pools: Optional[list] = None, packed: bool = False):  # fmt: skip
-        """``case``: a ``synthetic.StackCase``; ``rank`` must be one of ``case.ranks``. ``arena``: the rank's exchange
+                 pools: Optional[list] = None, packed: bool = False, sampling: Optional[torch.Tensor] = None,
+                 block_verify: bool = True):  # fmt: skip
+        """``sampling``: the sampled step's words (``dflash.draft.sampling_words``): the step then ends with the sampled
+        accept over the draft head's candidates and walk probabilities (``self.draft_cand`` / ``self.draft_walk_q``, which
+        the draft of the iteration writes), block verification or token by token.
+        ``case``: a ``synthetic.StackCase``; ``rank`` must be one of ``case.ranks``. ``arena``: the rank's exchange
         memory carved by ``exchange_layout`` (default: ordinary tensors, for a world inside one process). ``greedy``
         False ends the step with the soft cap (the logits go to ``self.logits_out``) instead of the accept."""
         self.lib = lib or host.library()
@@ -78,6 +82,12 @@ class Stack:
         self.module, self.case, self.rank, self.device = module, case, rank, device
         cfg, M = case.cfg, case.rows
         self.b_live, self.wait_budget, self.fused = b_live or M, wait_budget, fused
+        self.samp = None if sampling is None else sampling.to(device)
+        self.block_verify = block_verify
+        self.draft_cand = self.draft_walk_q = None
+        if self.samp is not None:
+            self.draft_cand = torch.zeros(M - 1, 16, dtype=torch.int64, device=device)
+            self.draft_walk_q = torch.zeros(M - 1, 16, dtype=torch.float32, device=device)
         slot = case.ranks.index(rank)
         dev = lambda t: t.to(device).contiguous()  # noqa: E731
         i64, i32, bf = torch.int64, torch.int32, torch.bfloat16
@@ -199,7 +209,8 @@ class Stack:
                 scale=cfg.output_multiplier, cap=cfg.softcap, ring=self.ring, accept_override=self.accept_override,
                 cos_sin_cache=self.cos_sin_cache, cos_sin=f.cos_sin, loc_full=f.loc_full, loc_swa=f.loc_swa,
                 kv_len=f.kv_len, flags=flags, contributors=present, wait_budget=self.wait_budget,
-                pool_rows=self.kv_rows,
+                pool_rows=self.kv_rows, samp=self.samp, cand=self.draft_cand, walk_q=self.draft_walk_q,
+                block_verify=self.block_verify,
             )  # fmt: skip
             self.accept.words[HT.WORDS["P"]] = case.ctx
             self.tail = self.accept

@@ -105,8 +105,17 @@ def test_bind_argument_checks():
     a = dict(logits=p, vocab=1000, rows=16, b_live=16, scale=1.0, cap=20.0, tokens=p, accept_override=0, n_override=0,
              words=p, out_ring=p, ring=64, top1=p, counter=p, cos_sin_cache=0, cos_sin_rows=0, cos_sin=0, loc_full=0,
              loc_swa=0, kv_len=0, dcos_sin_cache=0, dcos_sin_rows=0, dcos_sin=0, dslot=0, dkv_len=0, dring=0, flags=0,
-             contributors=0, wait_budget=0, status=0, pool_rows=0)  # fmt: skip
+             contributors=0, wait_budget=0, status=0, pool_rows=0, samp=0, cand=0, walk_q=0, block_verify=0, sample_ws=0,
+             sample_ws_bytes=0, sample_out=0)  # fmt: skip
     assert _lib().bind("mk_accept_bind", None, host.make("MkAcceptBind", **a)).info().kernels == 1
+    # the sampled accept: its operands and scratch (rows x vocab x 12 bytes + 256, 256-byte aligned)
+    need = 16 * 1000 * 12 + 256
+    smp = {**a, "samp": p, "cand": p, "walk_q": p, "sample_ws": 4096, "sample_ws_bytes": need, "top1": 0}
+    assert _lib().bind("mk_accept_bind", None, host.make("MkAcceptBind", **smp)).info().kernels == 1
+    _expect("mk_accept_bind", host.make("MkAcceptBind", **{**smp, "sample_ws_bytes": need - 1}), "sample_ws_bytes")
+    _expect("mk_accept_bind", host.make("MkAcceptBind", **{**smp, "cand": 0}), "cand")
+    _expect("mk_accept_bind", host.make("MkAcceptBind", **{**smp, "sample_ws": 4100}), "aligned")
+    _expect("mk_accept_bind", host.make("MkAcceptBind", **{**a, "top1": 0}), "top1")
     _expect("mk_accept_bind", host.make("MkAcceptBind", **{**a, "b_live": 17}), "b_live")
     _expect("mk_accept_bind", host.make("MkAcceptBind", **{**a, "ring": 8}), "ring")
     _expect("mk_accept_bind", host.make("MkAcceptBind", **{**a, "dslot": p}), "dslot")

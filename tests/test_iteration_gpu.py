@@ -121,3 +121,37 @@ def test_eight_row_window_iteration():
         assert st.tokens.shape[0] == rows and it.draft.drafts.shape[0] == rows - 1
         assert st.tokens.cpu()[1:].tolist() == it.draft.drafts.cpu().tolist()
     assert it.statuses() == []
+
+
+def test_sampled_iteration_matches_the_oracle_on_its_own_tensors():
+    """Temperature > 0: the draft head walks by Philox uniforms (purpose 0), the verify ends with the sampled accept
+    (purpose 1) over the draft's candidates and walk probabilities; three graph replays, each checked against the oracle
+    fed the step's own gathered logits, candidates, probabilities and ids."""
+    from oracle import dflash_sample as SM
+    from sgl_muse_mega_b200.muse_spark.b200.dflash.draft import sampling_words
+
+    seed, strm, temp, top_k, top_p = 0x1122334455667788, 2, 0.9, 64, 0.95
+    case = synthetic.stack_case(CFG, n_layers=4, rows=ROWS, ctx=CTX, seed=11)
+    st = S.Stack(case, 0, DEV, packed=True, sampling=sampling_words(seed, strm, temp, top_k, top_p))
+    st.bind()
+    dw, dt = dsyn.draft_weights(DCFG, 4), dsyn.target_shared(DCFG, 4)
+    w0, _ = shard(DCFG, dw, dt, 0, 1)
+    it = Iteration(st, DCFG, w0, capture=list(DCFG.capture), pool_rows=64, rope_rows=128)
+    assert it.draft.cand.data_ptr() == st.draft_cand.data_ptr() and it.draft.samp is st.samp
+    st.feeds.launch(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    it.capture_graph(warmup=False)
+    pos = CTX
+    for i in range(3):
+        it.step()
+        torch.cuda.synchronize()
+        assert it.statuses() == []
+        tokens, cand, q = st.tokens.cpu(), st.draft_cand.cpu(), st.draft_walk_q.cpu()
+        assert tokens[1:].tolist() == it.draft.drafts.cpu().tolist()
+        y = capped(st) / torch.tensor(temp, dtype=torch.float32)
+        probs = SM.target_probs(y, 1.0, top_k, float(torch.tensor(top_p, dtype=torch.float32)))
+        ref = SM.sampled_accept(tokens, probs, cand, q, D.uniforms(seed, strm, i, SM.PURPOSE_ACCEPT), True)
+        w = st.accept.words.cpu().tolist()
+        pos += ref.accept_len + 1
+        assert (w[HT.WORDS["ACCEPT"]], w[HT.WORDS["ANCHOR"]], w[HT.WORDS["P"]], w[HT.WORDS["ITER"]]) == (
+            ref.accept_len, ref.bonus, pos, i + 1)  # fmt: skip
