@@ -361,7 +361,8 @@ typedef struct MkAcceptBind {
     int64_t block_verify;
     uint64_t sample_ws;        // scratch of sample_ws_bytes >= rows x vocab x 12 + 256, 256-byte aligned
     int64_t sample_ws_bytes;
-    uint64_t sample_out;       // out f64 [2] or 0: the residual's scale and the mass of the bonus distribution
+    uint64_t sample_out;       // out f64 [16] or 0: [0] the residual's scale, [1] the mass of the bonus distribution
+                               // (the rest is written by trace builds only)
 } MkAcceptBind;
 int mk_accept_bind(MkModule* module, const MkAcceptBind* bind, MkLaunch** out);
 

@@ -248,6 +248,17 @@ __global__ void __launch_bounds__(1024) accept_kernel(const AcceptArgs a) {
 // after a full accept) by inverse CDF in vocabulary order. Uniforms: Philox, purpose 1, coin e - 1 for prefix e, 15 for
 // the bonus. Sums are f64; the selections are exact bisections over the order-preserving 32-bit image of the f32 values.
 constexpr int kTopCand = 16;  // candidates per draft slot
+#ifdef SAMPLE_TRACE
+// trace builds: the global timer at the stages of the sampled accept, as f64 nanoseconds in sample_out[2 + slot]
+#define SAMPLE_STAMP(a, slot, who)                                                  \
+    if ((who) && threadIdx.x == 0 && (a).sample_out != nullptr) {                    \
+        unsigned long long t_;                                                      \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                      \
+        (a).sample_out[2 + (slot)] = (double)t_;                                    \
+    }
+#else
+#define SAMPLE_STAMP(a, slot, who)
+#endif
 __device__ __forceinline__ unsigned ord_key(float v) {
     const unsigned b = __float_as_uint(v);
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
@@ -270,16 +281,212 @@ __device__ __forceinline__ double block_sum_d(double v, double* red) {
     return red[32];
 }
 
+// The last CTA of a sampled accept, all 1024 threads: verification by one thread, the bonus by inverse CDF over the
+// accepted row's distribution (a contiguous run of ids per thread), then the step words and the feeds.
+__device__ __noinline__ void sample_tail(const AcceptArgs& a) {
+    __shared__ double s_scan[1024];
+    __shared__ double s_pc[kMaxRows][kTopCand];  // P_e at slot e's candidates
+    __shared__ float s_qc[kMaxRows][kTopCand];   // the walk's probabilities
+    __shared__ long long s_cd[kMaxRows][kTopCand];
+    __shared__ double s_pd[kMaxRows], s_z[kMaxRows];
+    __shared__ long long s_tok[kMaxRows + 1];
+    __shared__ float s_u[16];
+    __shared__ double s_w[32];
+    __shared__ int s_acc, s_hit, s_hitw;
+    __shared__ long long s_bonus;
+    __shared__ double s_scale, s_mass, s_target;
+    const int tid = threadIdx.x, V = a.vocab;
+    const int gamma = a.b_live - 1;
+    SAMPLE_STAMP(a, 5, true)
+    // ---- everything the verification reads, fetched by many threads at once ----
+    if (tid < a.b_live) {
+        s_z[tid] = __ldcg(a.row_z + tid);
+        s_tok[tid] = a.tokens[tid];
+    }
+    if (tid < 16)
+        s_u[tid] = philox_uniform((unsigned long long)a.samp[0], (unsigned)a.samp[1], (unsigned)a.words[4], 1u, tid);
+    __syncthreads();
+    if (tid < gamma * kTopCand) {
+        const int e = tid / kTopCand, c = tid % kTopCand;
+        const long long id = a.cand[tid];
+        s_cd[e][c] = id;
+        s_qc[e][c] = a.walk_q[tid];
+        s_pc[e][c] = id >= 0 && id < V ? __ldcg(a.es + (size_t)e * V + id) / s_z[e] : 0.0;
+    } else if (tid >= 512 && tid < 512 + gamma) {
+        const int e = tid - 512;
+        const long long d = s_tok[e + 1];
+        s_pd[e] = d >= 0 && d < V ? __ldcg(a.es + (size_t)e * V + d) / s_z[e] : 0.0;
+    }
+    __syncthreads();
+    // ---- verification (one thread, shared memory only) ----
+    if (tid == 0) {
+        double q_d[kMaxRows], ratio[kMaxRows + 1];
+        for (int e = 0; e < gamma; ++e) {
+            double q = 0.0;
+            for (int c = 0; c < kTopCand; ++c)
+                if (s_cd[e][c] == s_tok[e + 1]) q += (double)s_qc[e][c];
+            q_d[e] = q;
+        }
+        int acc = 0;
+        double scale = 1.0, mass = -1.0;
+        if (a.block_verify) {
+            ratio[0] = 1.0;
+            for (int e = 0; e < gamma; ++e)
+                ratio[e + 1] = (q_d[e] > 0.0 && q_d[e] <= 1.0) ? fmin(ratio[e] * s_pd[e] / q_d[e], 1.0) : 0.0;
+            for (int e = gamma; e > 0; --e) {
+                const double coin = (double)s_u[e - 1];
+                if (!(coin < ratio[e])) continue;
+                double bar = ratio[e], m = -1.0;
+                if (e < gamma && ratio[e] > 0.0 && ratio[e] < 1.0) {
+                    // mass of max(r P_e - Q_e, 0): Q_e lives on the slot's candidates only
+                    double pc = 0.0, over = 0.0;
+                    for (int c = 0; c < kTopCand; ++c) {
+                        pc += s_pc[e][c];
+                        over += fmax(ratio[e] * s_pc[e][c] - (double)s_qc[e][c], 0.0);
+                    }
+                    m = ratio[e] * fmax(1.0 - pc, 0.0) + over;
+                    bar = m / (m + 1.0 - ratio[e]);
+                }
+                if (coin < bar) {
+                    acc = e;
+                    scale = ratio[e];
+                    mass = m;
+                    break;
+                }
+            }
+        } else {
+            while (acc < gamma && q_d[acc] > 0.0 && q_d[acc] <= 1.0 && (double)s_u[acc] * q_d[acc] < s_pd[acc]) ++acc;
+        }
+        if (a.accept_override != nullptr) {
+            const int f = a.accept_override[a.words[4] % a.n_override];
+            acc = f < 0 ? 0 : min(f, gamma);
+            scale = 1.0;
+            mass = -1.0;
+        }
+        s_acc = acc;
+        s_scale = scale;
+        s_mass = mass;
+    }
+    __syncthreads();
+    SAMPLE_STAMP(a, 6, true)
+    // ---- the bonus: inverse CDF of max(s P_a - Q_a, 0) in vocabulary order; every thread sums a contiguous run of ids
+    // (the candidates' share taken off afterwards: max(sP - q, 0) = sP - min(q, sP)) ----
+    const int acc = s_acc;
+    const bool resid = acc < gamma;
+    const double mul = s_scale / s_z[acc];
+    const double* es = a.es + (size_t)acc * V;
+    const int lane = tid & 31, warp = tid >> 5;
+    auto dist = [&](int id) {
+        double v = s_scale * (__ldcg(es + id) / s_z[acc]);
+        if (resid) {
+            for (int c = 0; c < kTopCand; ++c)
+                if (s_cd[acc][c] == (long long)id) v -= (double)s_qc[acc][c];
+            v = fmax(v, 0.0);
+        }
+        return v;
+    };
+    // level 1: a contiguous run of ids per warp, lanes interleaved (coalesced); the candidates' share is taken off the
+    // run's total afterwards: max(sP - q, 0) = sP - min(q, sP)
+    const int R = (V + 31) / 32, lo1 = min(warp * R, V), hi1 = min(lo1 + R, V);
+    {
+        double m[8] = {0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+        for (int jb = lo1 + lane; jb < hi1; jb += 256) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int jj = jb + 32 * u;
+                if (jj < hi1) m[u] += __ldcg(es + jj);
+            }
+        }
+        double tot = ((m[0] + m[1]) + (m[2] + m[3])) + ((m[4] + m[5]) + (m[6] + m[7]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+        tot *= mul;
+        if (resid)
+            for (int c = 0; c < kTopCand; ++c) {
+                const long long id = s_cd[acc][c];
+                if (id >= lo1 && id < hi1) tot -= fmin((double)s_qc[acc][c], s_scale * s_pc[acc][c]);
+            }
+        if (lane == 0) s_w[warp] = fmax(tot, 0.0);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        double incl = s_w[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const double t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        const double total = __shfl_sync(0xffffffffu, incl, 31);
+        const double mass = s_mass >= 0.0 ? s_mass : total;
+        const double target = (double)s_u[15] * mass;
+        const unsigned past = __ballot_sync(0xffffffffu, incl > target);
+        s_w[lane] = incl;
+        if (lane == 0) {
+            s_mass = mass;
+            s_target = target;
+            s_bonus = V - 1;
+            s_hitw = past ? __ffs(past) - 1 : 32;
+            s_hit = 1024;
+        }
+    }
+    __syncthreads();
+    const double target = s_target;
+    if (s_hitw < 32) {
+        // level 2: the run that holds the target, a short contiguous piece per thread
+        const int hw = s_hitw, lo = min(hw * R, V), hi = min(lo + R, V);
+        const double base = hw > 0 ? s_w[hw - 1] : 0.0;
+        const int per = (hi - lo + 1023) / 1024, j0 = min(lo + tid * per, hi), j1 = min(j0 + per, hi);
+        double mine = 0.0;
+        for (int jj = j0; jj < j1; ++jj) mine += dist(jj);
+        s_scan[tid] = mine;
+        __syncthreads();
+        if (tid < 32) {  // running sums of the 1024 pieces: 32 per lane, then across the lanes
+            double run = 0.0;
+            for (int t = 0; t < 32; ++t) {
+                run += s_scan[tid * 32 + t];
+                s_scan[tid * 32 + t] = run;
+            }
+            double incl = run;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const double t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (tid >= o) incl += t;
+            }
+            const double before = base + incl - run;
+            for (int t = 0; t < 32; ++t) s_scan[tid * 32 + t] += before;
+        }
+        __syncthreads();
+        if (s_scan[tid] > target && (tid == 0 ? !(base > target) : !(s_scan[tid - 1] > target))) s_hit = tid;
+        __syncthreads();
+        if (s_hit == 1024 && tid == 0) s_bonus = hi - 1;  // rounding left the target just past the run's own sums
+        if (s_hit == tid) {
+            double run = tid > 0 ? s_scan[tid - 1] : base;
+            long long id = j1 - 1;
+            for (int jj = j0; jj < j1; ++jj) {
+                run += dist(jj);
+                if (run > target) {
+                    id = jj;
+                    break;
+                }
+            }
+            s_bonus = id;
+        }
+    }
+    __syncthreads();
+    if (tid == 0 && a.sample_out != nullptr) {
+        a.sample_out[0] = s_scale;
+        a.sample_out[1] = s_mass;
+    }
+    SAMPLE_STAMP(a, 7, true)
+    commit_and_feed(a, acc, s_bonus);
+    SAMPLE_STAMP(a, 8, true)
+}
+
 // grid = window rows, 1024 threads: every live row's distribution; the last CTA to finish verifies and draws the bonus.
 __global__ void __launch_bounds__(1024) sample_accept_kernel(const AcceptArgs a) {
     __shared__ double red[33];
     __shared__ float s_mx[32];
-    __shared__ double s_scan[1024];
-    __shared__ int s_last, s_acc, s_hit;
-    __shared__ long long s_bonus;
-    __shared__ double s_scale, s_mass;
-    __shared__ long long s_cand[kTopCand];
-    __shared__ float s_q[kTopCand];
+    __shared__ int s_last;
     griddep_wait();
     xchg_wait(a.wait);
     const int row = blockIdx.x, tid = threadIdx.x, V = a.vocab;
@@ -356,125 +563,218 @@ __global__ void __launch_bounds__(1024) sample_accept_kernel(const AcceptArgs a)
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // ---- verification (one thread) ----
-    const int gamma = a.b_live - 1;
-    if (tid == 0) {
-        const unsigned long long seed = (unsigned long long)a.samp[0];
-        const unsigned stream = (unsigned)a.samp[1], iter = (unsigned)a.words[4];
-        double p_d[kMaxRows], q_d[kMaxRows], ratio[kMaxRows + 1];
-        for (int e = 0; e < gamma; ++e) {
-            const long long d = a.tokens[e + 1];
-            p_d[e] = d >= 0 && d < V ? __ldcg(a.es + (size_t)e * V + d) / __ldcg(a.row_z + e) : 0.0;
-            double q = 0.0;
-            for (int c = 0; c < kTopCand; ++c)
-                if (a.cand[e * kTopCand + c] == d) q += (double)a.walk_q[e * kTopCand + c];
-            q_d[e] = q;
+    sample_tail(a);
+}
+
+// ---- the rows' distributions on clusters --------------------------------------------------------------------------------------
+// The same arithmetic as sample_accept_kernel with a row spread over a cluster of kSampleCluster CTAs (four: sixteen
+// clusters of eight did not all fit the GPU at once, and the second wave doubled the time) (one vocabulary
+// slice each, its keys in shared memory): the sums and counts meet through distributed shared memory, the two selections
+// are 8-way section searches (about 11 passes over the slice instead of 32).
+constexpr int kSampleCluster = 4;
+constexpr size_t kSampleMaxSlice = 204 * 1024;  // bytes of keys a CTA holds; larger vocabularies take the one-CTA-per-row kernel
+constexpr int kSampleWays = 7;  // thresholds per search pass
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ double ld_cluster_f64(const double* local, unsigned rank) {
+    unsigned addr = (unsigned)__cvta_generic_to_shared(local), remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    double v;
+    asm volatile("ld.shared::cluster.f64 %0, [%1];" : "=d"(v) : "r"(remote) : "memory");
+    return v;
+}
+// The cluster's totals of N values per thread (or maxima), identical in every thread of every CTA: CTA totals in a slot
+// set that alternates between calls, one cluster barrier, then every CTA adds the slots in rank order.
+struct ClusterRed {
+    double warp[32][kSampleWays];
+    double slot[2][kSampleWays];
+    double total[kSampleWays];
+    int parity;
+};
+template <int N, bool MAX>
+__device__ __forceinline__ void cluster_reduce(double (&v)[N], ClusterRed& r) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const double t = __shfl_xor_sync(0xffffffffu, v[i], o);
+            v[i] = MAX ? fmax(v[i], t) : v[i] + t;
         }
-        int acc = 0;
-        double scale = 1.0, mass = -1.0;
-        if (a.block_verify) {
-            ratio[0] = 1.0;
-            for (int e = 0; e < gamma; ++e)
-                ratio[e + 1] = (q_d[e] > 0.0 && q_d[e] <= 1.0) ? fmin(ratio[e] * p_d[e] / q_d[e], 1.0) : 0.0;
-            for (int e = gamma; e > 0; --e) {
-                const double coin = (double)philox_uniform(seed, stream, iter, 1u, e - 1);
-                if (!(coin < ratio[e])) continue;
-                double bar = ratio[e], m = -1.0;
-                if (e < gamma && ratio[e] > 0.0 && ratio[e] < 1.0) {
-                    // mass of max(r P_e - Q_e, 0): Q_e lives on the slot's candidates only
-                    double pc = 0.0, over = 0.0;
-                    for (int c = 0; c < kTopCand; ++c) {
-                        const long long id = a.cand[e * kTopCand + c];
-                        const double pe = id >= 0 && id < V ? __ldcg(a.es + (size_t)e * V + id) / __ldcg(a.row_z + e) : 0.0;
-                        pc += pe;
-                        over += fmax(ratio[e] * pe - (double)a.walk_q[e * kTopCand + c], 0.0);
-                    }
-                    m = ratio[e] * fmax(1.0 - pc, 0.0) + over;
-                    bar = m / (m + 1.0 - ratio[e]);
-                }
-                if (coin < bar) {
-                    acc = e;
-                    scale = ratio[e];
-                    mass = m;
-                    break;
-                }
-            }
+    __syncthreads();  // the previous call's totals have been read
+    if (lane == 0)
+        for (int i = 0; i < N; ++i) r.warp[warp][i] = v[i];
+    __syncthreads();
+    const int par = r.parity;
+    if (threadIdx.x < N) {
+        double t = r.warp[0][threadIdx.x];
+        for (int w = 1; w < 32; ++w) t = MAX ? fmax(t, r.warp[w][threadIdx.x]) : t + r.warp[w][threadIdx.x];
+        r.slot[par][threadIdx.x] = t;
+    }
+    cluster_sync_all();
+    if (threadIdx.x < N) {
+        double t = ld_cluster_f64(&r.slot[par][threadIdx.x], 0);
+        for (unsigned c = 1; c < (unsigned)kSampleCluster; ++c) {
+            const double o = ld_cluster_f64(&r.slot[par][threadIdx.x], c);
+            t = MAX ? fmax(t, o) : t + o;
+        }
+        r.total[threadIdx.x] = t;
+    }
+    if (threadIdx.x == 0) r.parity = par ^ 1;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < N; ++i) v[i] = r.total[i];
+}
+
+// The smallest 32-bit t in [lo, hi] for which `below(t)` holds, given that it holds at hi and is monotone; `measure` fills
+// the cluster's totals for up to kSampleWays thresholds at once.
+template <typename Measure, typename Below>
+__device__ __forceinline__ unsigned section_search(unsigned lo, unsigned hi, Measure measure, Below below) {
+    while (lo < hi) {
+        unsigned t[kSampleWays];
+        const unsigned span = hi - lo;
+        int n;
+        if (span <= (unsigned)kSampleWays) {
+            n = (int)span;
+            for (int i = 0; i < kSampleWays; ++i) t[i] = lo + (unsigned)min(i, n - 1);
         } else {
-            while (acc < gamma && q_d[acc] > 0.0 && q_d[acc] <= 1.0 &&
-                   (double)philox_uniform(seed, stream, iter, 1u, acc) * q_d[acc] < p_d[acc])
-                ++acc;
+            n = kSampleWays;
+            const unsigned step = span / (unsigned)(kSampleWays + 1);
+            for (int i = 0; i < kSampleWays; ++i) t[i] = lo + step * (unsigned)(i + 1);
         }
-        if (a.accept_override != nullptr) {
-            const int f = a.accept_override[a.words[4] % a.n_override];
-            acc = f < 0 ? 0 : min(f, gamma);
-            scale = 1.0;
-            mass = -1.0;
+        double m[kSampleWays];
+        measure(t, m);
+        int first = n;
+        for (int i = n - 1; i >= 0; --i)
+            if (below(m[i])) first = i;
+        if (first < n) {
+            hi = t[first];
+            lo = first == 0 ? lo : t[first - 1] + 1u;
+        } else {
+            lo = t[n - 1] + 1u;
         }
-        s_acc = acc;
-        s_scale = scale;
-        s_mass = mass;
     }
+    return lo;
+}
+
+// grid = (kSampleCluster, window rows), clusters of kSampleCluster along x, 1024 threads, dynamic shared memory = one
+// slice of keys (4 bytes per vocabulary entry of the slice).
+__global__ void __launch_bounds__(1024) sample_accept_cluster_kernel(const AcceptArgs a) {
+    extern __shared__ __align__(16) unsigned char dyn_keys[];
+    __shared__ ClusterRed cr;
+    __shared__ int s_last;
+    unsigned* keys = (unsigned*)dyn_keys;
+    griddep_wait();
+    xchg_wait(a.wait);
+    const int row = blockIdx.y, tid = threadIdx.x, V = a.vocab;
+    const int slice = (V + kSampleCluster - 1) / kSampleCluster, j0 = min((int)blockIdx.x * slice, V), n = min(slice, V - j0);
+    const float T = fmaxf(__uint_as_float((unsigned)((unsigned long long)a.samp[3] & 0xFFFFFFFFull)), 1e-5f);
+    const float top_p = __uint_as_float((unsigned)((unsigned long long)a.samp[3] >> 32));
+    const long long top_k = a.samp[2];
+    if (tid == 0) cr.parity = 0;
     __syncthreads();
-    // ---- the bonus: inverse CDF of max(s P_a - Q_a, 0) in vocabulary order (all threads, a contiguous run of ids each) ----
-    const int acc = s_acc;
-    const double scale = s_scale, zr = __ldcg(a.row_z + acc);
-    const bool resid = acc < gamma;
-    if (tid < kTopCand) {
-        s_cand[tid] = resid ? a.cand[acc * kTopCand + tid] : -1;
-        s_q[tid] = resid ? a.walk_q[acc * kTopCand + tid] : 0.f;
-    }
-    __syncthreads();
-    const double* es = a.es + (size_t)acc * V;
-    const int per = (V + 1023) / 1024, j0 = min(tid * per, V), j1 = min(j0 + per, V);
-    auto dist = [&](int j) {
-        double v = scale * (__ldcg(es + j) / zr);
-        if (resid) {
-            for (int c = 0; c < kTopCand; ++c)
-                if (s_cand[c] == (long long)j) v -= (double)s_q[c];
-            v = fmax(v, 0.0);
-        }
-        return v;
-    };
-    double mine = 0.0;
-    for (int j = j0; j < j1; ++j) mine += dist(j);
-    s_scan[tid] = mine;
-    __syncthreads();
-    if (tid == 0) {  // running sums of the 1024 runs, in order
-        double run = 0.0;
-        for (int t = 0; t < 1024; ++t) {
-            run += s_scan[t];
-            s_scan[t] = run;
-        }
-        const double total = run, mass = s_mass >= 0.0 ? s_mass : total;
-        const double target = (double)philox_uniform((unsigned long long)a.samp[0], (unsigned)a.samp[1], (unsigned)a.words[4], 1u, 15) * mass;
-        int hit = -1;
-        for (int t = 0; t < 1024 && hit < 0; ++t)
-            if (s_scan[t] > target) hit = t;
-        s_hit = hit;
-        s_mass = mass;
-        red[0] = target;
-        s_bonus = V - 1;
-    }
-    __syncthreads();
-    if (s_hit == tid) {
-        double run = tid > 0 ? s_scan[tid - 1] : 0.0;
-        const double target = red[0];
-        long long id = j1 - 1;
-        for (int j = j0; j < j1; ++j) {
-            run += dist(j);
-            if (run > target) {
-                id = j;
-                break;
+    const bool first = blockIdx.x == 0 && blockIdx.y == 0;
+    SAMPLE_STAMP(a, 0, first)
+    if (row < a.b_live) {  // uniform over the cluster
+        const float* x = a.logits + (size_t)row * V + j0;
+        float* ys = a.ys + (size_t)row * V + j0;
+        double* es = a.es + (size_t)row * V + j0;
+        double mxd[1] = {-INFINITY};
+        for (int i = tid; i < n; i += 4096) {  // four loads in flight
+            float v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = i + u * 1024 < n ? __ldg(x + i + u * 1024) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int ii = i + u * 1024;
+                if (ii < n) {
+                    const float y = __fdiv_rn(tanhf((v[u] * a.scale) / a.cap) * a.cap, T);
+                    ys[ii] = y;
+                    keys[ii] = ord_key(y);
+                    mxd[0] = fmax(mxd[0], (double)y);
+                }
             }
         }
-        s_bonus = id;
+        cluster_reduce<1, true>(mxd, cr);
+        const double mx = mxd[0];
+        SAMPLE_STAMP(a, 1, first)
+        unsigned floor_key = 0u;
+        if (top_k < (long long)V) {
+            floor_key = section_search(
+                0u, 0xFFFFFFFFu,
+                [&](const unsigned (&t)[kSampleWays], double (&m)[kSampleWays]) {
+                    int c[kSampleWays] = {};
+                    for (int i = tid; i < n; i += 1024) {
+                        const unsigned k = keys[i];
+#pragma unroll
+                        for (int w = 0; w < kSampleWays; ++w) c[w] += k > t[w];
+                    }
+#pragma unroll
+                    for (int w = 0; w < kSampleWays; ++w) m[w] = (double)c[w];
+                    cluster_reduce<kSampleWays, false>(m, cr);
+                },
+                [&](double count) { return count < (double)top_k; });
+        }
+        SAMPLE_STAMP(a, 2, first)
+        double zz[1] = {0.0};
+        for (int i = tid; i < n; i += 1024) {
+            const unsigned k = keys[i];
+            const double e = k >= floor_key ? exp((double)ys[i] - mx) : 0.0;
+            es[i] = e;
+            zz[0] += e;
+        }
+        cluster_reduce<1, false>(zz, cr);
+        double z = zz[0];
+        SAMPLE_STAMP(a, 3, first)
+        if (top_p < 1.0f) {
+            const double tau = (double)top_p * z;
+            const unsigned thr = section_search(
+                floor_key, ord_key((float)mx),
+                [&](const unsigned (&t)[kSampleWays], double (&m)[kSampleWays]) {
+#pragma unroll
+                    for (int w = 0; w < kSampleWays; ++w) m[w] = 0.0;
+                    for (int i = tid; i < n; i += 4096) {  // four loads in flight
+                        double e[4];
+                        unsigned k[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int ii = i + u * 1024;
+                            e[u] = ii < n ? es[ii] : 0.0;
+                            k[u] = ii < n ? keys[ii] : 0u;
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+#pragma unroll
+                            for (int w = 0; w < kSampleWays; ++w) m[w] += k[u] > t[w] ? e[u] : 0.0;
+                    }
+                    cluster_reduce<kSampleWays, false>(m, cr);
+                },
+                [&](double mass) { return mass < tau; });
+            zz[0] = 0.0;
+            for (int i = tid; i < n; i += 1024) {
+                const double e = keys[i] >= thr ? es[i] : 0.0;
+                es[i] = e;
+                zz[0] += e;
+            }
+            cluster_reduce<1, false>(zz, cr);
+            z = zz[0];
+        }
+        if (tid == 0 && blockIdx.x == 0) a.row_z[row] = z;
+        SAMPLE_STAMP(a, 4, first)
+    }
+    cluster_sync_all();  // no CTA leaves while a peer may still read its slots
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        const unsigned old = atomicAdd(a.counter, 1u);
+        s_last = old == (unsigned)(gridDim.x * gridDim.y - 1);
+        if (s_last) *a.counter = 0;
     }
     __syncthreads();
-    if (tid == 0 && a.sample_out != nullptr) {
-        a.sample_out[0] = s_scale;
-        a.sample_out[1] = s_mass;
-    }
-    commit_and_feed(a, acc, s_bonus);
+    if (!s_last) return;
+    __threadfence();
+    sample_tail(a);
 }
 
 // ---- launchers ------------------------------------------------------------------------------------------------------------
@@ -504,8 +804,29 @@ cudaError_t softcap_launch(const SoftcapArgs& a, cudaStream_t s, bool pdl) {
     if (blocks > 148 * 8) blocks = 148 * 8;
     return launch_ht(softcap_kernel, dim3((unsigned)blocks), dim3(256), s, pdl, a);
 }
+cudaError_t headtail_prepare() {
+    return cudaFuncSetAttribute(sample_accept_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSampleMaxSlice);
+}
 cudaError_t accept_launch(const AcceptArgs& a, cudaStream_t s, bool pdl) {
-    if (a.samp != nullptr) return launch_ht(sample_accept_kernel, dim3(a.rows), dim3(1024), s, pdl, a);
+    if (a.samp != nullptr) {
+        const size_t slice_bytes = ((size_t)a.vocab + kSampleCluster - 1) / kSampleCluster * 4;
+        if (slice_bytes > kSampleMaxSlice) return launch_ht(sample_accept_kernel, dim3(a.rows), dim3(1024), s, pdl, a);
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = kSampleCluster;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(kSampleCluster, a.rows);
+        cfg.blockDim = dim3(1024);
+        cfg.dynamicSmemBytes = slice_bytes;
+        cfg.stream = s;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl ? 2 : 1;
+        return cudaLaunchKernelEx(&cfg, sample_accept_cluster_kernel, a);
+    }
     return launch_ht(accept_kernel, dim3(a.rows), dim3(1024), s, pdl, a);
 }
 

@@ -190,6 +190,8 @@ int mk_module_load(const void* image, uint64_t bytes, const char* code_prefetch_
     if (e != cudaSuccess) return cuda_fail(e, "experts_prepare");
     e = experts_umma_prepare();
     if (e != cudaSuccess) return cuda_fail(e, "experts_umma_prepare");
+    e = headtail_prepare();
+    if (e != cudaSuccess) return cuda_fail(e, "headtail_prepare");
     e = segments_prepare();
     if (e != cudaSuccess) return cuda_fail(e, "segments_prepare");
     e = draft_prepare();

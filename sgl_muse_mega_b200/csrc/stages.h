@@ -240,6 +240,7 @@ cudaError_t feeds_launch(const FeedsArgs& a, cudaStream_t s, bool pdl);
 cudaError_t entry_launch(const EntryArgs& a, cudaStream_t s, bool pdl);
 cudaError_t softcap_launch(const SoftcapArgs& a, cudaStream_t s, bool pdl);
 cudaError_t accept_launch(const AcceptArgs& a, cudaStream_t s, bool pdl);
+cudaError_t headtail_prepare();
 
 // segments.cuh (compiled with rows.cu): the dense GEMMs and the row work between them as two persistent kernels
 struct SegGemm {

@@ -134,7 +134,7 @@ class Accept:
         if samp is not None:
             ys = (rows * vocab * 4 + 255) // 256 * 256
             self.sample_ws = _z(ys + rows * vocab * 8 + 256, dtype=torch.uint8, device=dev)
-            self.sample_out = _z(2, dtype=torch.float64, device=dev)
+            self.sample_out = _z(16, dtype=torch.float64, device=dev)  # [0:2] scale, mass; the rest: trace builds
         self.words = _z(N_WORDS, dtype=torch.int64, device=dev)
         self.out_ring = _z(ring, dtype=torch.int32, device=dev)
         self.top1 = _z(rows, dtype=torch.int32, device=dev)

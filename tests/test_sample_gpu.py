@@ -90,7 +90,7 @@ def test_sampled_accept(vocab, rows, temp, top_k, top_p, block, boost, grid, see
     ref = S.sampled_accept(tokens, probs, cand, q, u, block)
     w = acc.words.cpu()
     assert (int(w[A.WORDS["ACCEPT"]]), int(w[A.WORDS["ANCHOR"]])) == (ref.accept_len, ref.bonus)
-    scale, mass = acc.sample_out.cpu().tolist()
+    scale, mass = acc.sample_out.cpu()[:2].tolist()
     assert scale == pytest.approx(ref.scale, rel=1e-9) and mass == pytest.approx(ref.norm, rel=1e-9)
     step = A.Accept(ref.accept_len, ref.accept_len + 1, ref.bonus, None, 100 + ref.accept_len + 1)
     words, ring = A.step_words(words, ring, step, tokens)
