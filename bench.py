@@ -48,6 +48,11 @@ def parse():
     ap.add_argument("--decode-layers", type=int, default=62, help="layers of the whole-step leg (0: skip it)")
     ap.add_argument("--decode-steps", type=int, default=24)
     ap.add_argument("--no-draft", action="store_true", help="whole-step leg without the DFlash2 draft (ids from the host)")
+    ap.add_argument("--temperature", type=float, default=0.0,
+                    help="> 0: the whole-step leg runs the sampled step (sampled draft walk, sampled accept with --top-k / --top-p; "
+                         "the accept length stays forced)")
+    ap.add_argument("--top-k", type=int, default=1 << 30)
+    ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--accept", type=int, default=5, help="forced accept length of the whole-step leg (5 drafts + the bonus = 6 tokens a step)")
     return ap.parse_args()
 
@@ -210,8 +215,14 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
                                 max_pos=kv_rows + rows, lazy=True)  # fmt: skip
     forced = torch.tensor([args.accept], dtype=torch.int32, device=device)
     arena = symm.Arena(lib, S.exchange_layout(model, rows), device) if world > 1 else None
+    sampling = None
+    if args.temperature > 0:
+        from sgl_muse_mega_b200.muse_spark.b200.dflash.draft import sampling_words
+
+        assert not args.no_draft, "the sampled accept reads the draft head's candidates"
+        sampling = sampling_words(args.seed, 0, args.temperature, args.top_k, args.top_p)
     st = S.Stack(case, tp_rank, device, lib, module, arena=arena, kv_rows=kv_rows, keep_plain_experts=False,
-                 accept_override=forced, wait_budget=1 << 25, packed=True)  # fmt: skip
+                 accept_override=forced, wait_budget=1 << 25, packed=True, sampling=sampling)  # fmt: skip
     peers = S.connect_world(st) if world > 1 else st.bind()
     s = stream.cuda_stream
     # the DFlash2 draft at its public size (this rank's TP slice, synthetic weights drawn on the device): with it the step
@@ -335,6 +346,7 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
         "bytes_per_step": int(sum(b["total"] for b in byts)), "mean_distinct_experts": sum(d_list) / len(d_list),
         "present_ranks": world if world > 1 else 1, "model_ranks": cfg.tp,
         "draft": draft if draft is not None else "not in the step (--no-draft): ids come from the host",
+        "sampling": "greedy" if sampling is None else {"temperature": args.temperature, "top_k": args.top_k, "top_p": args.top_p},
     }  # fmt: skip
     if it is not None:
         bad = it.statuses()
