@@ -55,6 +55,9 @@ CASES = [
     (512, 16, 0.8, 1 << 30, 1.0, True, 25.0, 0.0, 22),
     (25256, 16, 1.0, 64, 0.95, True, 32.0, 0.0, 24),
     (202048, 16, 0.8, 1 << 30, 1.0, True, 40.0, 0.0, 30),
+    # a vocabulary whose quarter does not fit a CTA's shared memory: one CTA per row, plain bisections
+    (262144, 8, 1.0, 64, 0.9, True, 40.0, 0.0, 11),
+    (262144, 8, 0.8, 1 << 30, 1.0, False, 40.0, 0.0, 12),
 ]
 
 

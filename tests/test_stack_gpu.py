@@ -50,7 +50,7 @@ def run_world(tp, rows, ctx, seed, **kw):
     return cfg, case, world, tokens
 
 
-@pytest.mark.parametrize("tp,rows,ctx", [(2, 16, 24), (1, 5, 40)])
+@pytest.mark.parametrize("tp,rows,ctx", [(2, 16, 24), (1, 5, 40), (4, 8, 30)])
 def test_stack_stagewise_and_end_to_end(tp, rows, ctx):
     cfg, case, world, tokens = run_world(tp, rows, ctx, 21)
     # snapshot each layer's view right after the run (the accept rewrites the feeds for the next step)
