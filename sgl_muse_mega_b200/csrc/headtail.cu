@@ -570,10 +570,12 @@ __global__ void __launch_bounds__(1024) sample_accept_kernel(const AcceptArgs a)
 // The same arithmetic as sample_accept_kernel with a row spread over a cluster of kSampleCluster CTAs (four: sixteen
 // clusters of eight did not all fit the GPU at once, and the second wave doubled the time) (one vocabulary
 // slice each, its keys in shared memory): the sums and counts meet through distributed shared memory, the two selections
-// are 8-way section searches (about 11 passes over the slice instead of 32).
+// are 8-way section searches: 12 passes over the slice instead of 32.
 constexpr int kSampleCluster = 4;
 constexpr size_t kSampleMaxSlice = 204 * 1024;  // bytes of keys a CTA holds; larger vocabularies take the one-CTA-per-row kernel
-constexpr int kSampleWays = 7;  // thresholds per search pass
+constexpr int kCountWays = 7;   // thresholds per pass of the top-k search (15 measured slower: 9 passes of 17.7 us against 12 of 9.7)
+constexpr int kMassWays = 7;    // thresholds per pass of the top-p search (f64 masses)
+constexpr int kSampleWays = kCountWays;  // slots of a cluster reduction
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -628,22 +630,22 @@ __device__ __forceinline__ void cluster_reduce(double (&v)[N], ClusterRed& r) {
 }
 
 // The smallest 32-bit t in [lo, hi] for which `below(t)` holds, given that it holds at hi and is monotone; `measure` fills
-// the cluster's totals for up to kSampleWays thresholds at once.
-template <typename Measure, typename Below>
+// the cluster's totals for up to W thresholds at once.
+template <int W, typename Measure, typename Below>
 __device__ __forceinline__ unsigned section_search(unsigned lo, unsigned hi, Measure measure, Below below) {
     while (lo < hi) {
-        unsigned t[kSampleWays];
+        unsigned t[W];
         const unsigned span = hi - lo;
         int n;
-        if (span <= (unsigned)kSampleWays) {
+        if (span <= (unsigned)W) {
             n = (int)span;
-            for (int i = 0; i < kSampleWays; ++i) t[i] = lo + (unsigned)min(i, n - 1);
+            for (int i = 0; i < W; ++i) t[i] = lo + (unsigned)min(i, n - 1);
         } else {
-            n = kSampleWays;
-            const unsigned step = span / (unsigned)(kSampleWays + 1);
-            for (int i = 0; i < kSampleWays; ++i) t[i] = lo + step * (unsigned)(i + 1);
+            n = W;
+            const unsigned step = span / (unsigned)(W + 1);
+            for (int i = 0; i < W; ++i) t[i] = lo + step * (unsigned)(i + 1);
         }
-        double m[kSampleWays];
+        double m[W];
         measure(t, m);
         int first = n;
         for (int i = n - 1; i >= 0; --i)
@@ -701,18 +703,18 @@ __global__ void __launch_bounds__(1024) sample_accept_cluster_kernel(const Accep
         SAMPLE_STAMP(a, 1, first)
         unsigned floor_key = 0u;
         if (top_k < (long long)V) {
-            floor_key = section_search(
+            floor_key = section_search<kCountWays>(
                 0u, 0xFFFFFFFFu,
-                [&](const unsigned (&t)[kSampleWays], double (&m)[kSampleWays]) {
-                    int c[kSampleWays] = {};
+                [&](const unsigned (&t)[kCountWays], double (&m)[kCountWays]) {
+                    int c[kCountWays] = {};
                     for (int i = tid; i < n; i += 1024) {
                         const unsigned k = keys[i];
 #pragma unroll
-                        for (int w = 0; w < kSampleWays; ++w) c[w] += k > t[w];
+                        for (int w = 0; w < kCountWays; ++w) c[w] += k > t[w];
                     }
 #pragma unroll
-                    for (int w = 0; w < kSampleWays; ++w) m[w] = (double)c[w];
-                    cluster_reduce<kSampleWays, false>(m, cr);
+                    for (int w = 0; w < kCountWays; ++w) m[w] = (double)c[w];
+                    cluster_reduce<kCountWays, false>(m, cr);
                 },
                 [&](double count) { return count < (double)top_k; });
         }
@@ -729,11 +731,11 @@ __global__ void __launch_bounds__(1024) sample_accept_cluster_kernel(const Accep
         SAMPLE_STAMP(a, 3, first)
         if (top_p < 1.0f) {
             const double tau = (double)top_p * z;
-            const unsigned thr = section_search(
+            const unsigned thr = section_search<kMassWays>(
                 floor_key, ord_key((float)mx),
-                [&](const unsigned (&t)[kSampleWays], double (&m)[kSampleWays]) {
+                [&](const unsigned (&t)[kMassWays], double (&m)[kMassWays]) {
 #pragma unroll
-                    for (int w = 0; w < kSampleWays; ++w) m[w] = 0.0;
+                    for (int w = 0; w < kMassWays; ++w) m[w] = 0.0;
                     for (int i = tid; i < n; i += 4096) {  // four loads in flight
                         double e[4];
                         unsigned k[4];
@@ -746,9 +748,9 @@ __global__ void __launch_bounds__(1024) sample_accept_cluster_kernel(const Accep
 #pragma unroll
                         for (int u = 0; u < 4; ++u)
 #pragma unroll
-                            for (int w = 0; w < kSampleWays; ++w) m[w] += k[u] > t[w] ? e[u] : 0.0;
+                            for (int w = 0; w < kMassWays; ++w) m[w] += k[u] > t[w] ? e[u] : 0.0;
                     }
-                    cluster_reduce<kSampleWays, false>(m, cr);
+                    cluster_reduce<kMassWays, false>(m, cr);
                 },
                 [&](double mass) { return mass < tau; });
             zz[0] = 0.0;
