@@ -186,13 +186,17 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs a) {
     }
 }
 
-// One warp per (token, query head): merge the splits in split order, normalise, RMS norm, sigmoid gate.
+// Four warps per (token, query head), two pairs per CTA: each warp merges a contiguous quarter of the splits in split
+// order, the quarters meet in shared memory in order; then normalise, RMS norm, sigmoid gate. (One warp per pair walked
+// up to 16 dependent batches of loads; the quarter walks at most 4.)
 __global__ void __launch_bounds__(256) attn_combine_kernel(const AttnArgs a) {
+    __shared__ float s_o[2][4][64];
     griddep_wait();
     griddep_launch();
-    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (w >= a.M * a.qh) return;
-    const int tok = w / a.qh, head = w % a.qh;
+    const int pc = threadIdx.x >> 7, wq = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31;
+    const int w = blockIdx.x * 2 + pc;
+    const bool valid = w < a.M * a.qh;
+    const int tok = valid ? w / a.qh : 0, head = valid ? w % a.qh : 0;
     const int kvhead = head / a.G, r = tok * a.G + head % a.G;
     const float* base = a.ws + ((size_t)kvhead * a.splits * a.R + r) * 66;
     const size_t stride = (size_t)a.R * 66;
@@ -205,7 +209,7 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const AttnArgs a) {
         const int s = lane + 32 * i;
         ms_[i] = -1e30f;
         ls_[i] = 0.f;
-        if (s < a.splits) {
+        if (valid && s < a.splits) {
             const float2 ml = *(const float2*)(base + s * stride + 64);
             ms_[i] = ml.x;
             ls_[i] = ml.y;
@@ -220,9 +224,10 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const AttnArgs a) {
         L += ls_[i] * ms_[i];
     }
     L = warp_sum(L);
-    // O = sum over the splits, in split order, of O_s x scale_s: 8 independent loads per batch
+    // this warp's quarter: O = sum over its splits, in split order, of O_s x scale_s: 8 independent loads per batch
+    const int quarter = ((a.splits + 3) / 4 + 7) / 8 * 8, q0 = wq * quarter, q1 = min(q0 + quarter, a.splits);
     float o0 = 0.f, o1 = 0.f;
-    for (int s0 = 0; s0 < a.splits; s0 += 8) {
+    for (int s0 = q0; s0 < q1; s0 += 8) {
         float2 v[8];
         float sc[8];
 #pragma unroll
@@ -234,7 +239,7 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const AttnArgs a) {
                 const float t = __shfl_sync(0xffffffffu, ms_[i], s & 31);
                 if (i == (s >> 5)) scj = t;
             }
-            sc[j] = s < a.splits ? scj : 0.f;
+            sc[j] = s < q1 ? scj : 0.f;
             v[j] = sc[j] != 0.f ? *(const float2*)(base + s * stride + 2 * lane) : make_float2(0.f, 0.f);
         }
 #pragma unroll
@@ -243,6 +248,12 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const AttnArgs a) {
             o1 += v[j].y * sc[j];
         }
     }
+    s_o[pc][wq][2 * lane] = o0;
+    s_o[pc][wq][2 * lane + 1] = o1;
+    __syncthreads();
+    if (wq != 0 || !valid) return;
+    o0 = ((s_o[pc][0][2 * lane] + s_o[pc][1][2 * lane]) + s_o[pc][2][2 * lane]) + s_o[pc][3][2 * lane];
+    o1 = ((s_o[pc][0][2 * lane + 1] + s_o[pc][1][2 * lane + 1]) + s_o[pc][2][2 * lane + 1]) + s_o[pc][3][2 * lane + 1];
     const float inv = 1.0f / L;
     const float x0 = o0 * inv, x1 = o1 * inv;
     const float ms = warp_sum(x0 * x0 + x1 * x1) * (1.0f / 64.0f);
@@ -276,8 +287,8 @@ cudaError_t attn_combine_launch(const AttnArgs& a, cudaStream_t stream, bool pdl
     cudaLaunchAttribute attr[1];
     cudaLaunchConfig_t cfg;
     attn_cfg(cfg, attr, stream, pdl);
-    const int warps = a.M * a.qh;
-    cfg.gridDim = dim3((warps + 7) / 8, 1, 1);
+    const int pairs = a.M * a.qh;  // two (token, head) pairs per CTA, four warps each
+    cfg.gridDim = dim3((pairs + 1) / 2, 1, 1);
     cfg.blockDim = dim3(256, 1, 1);
     return cudaLaunchKernelEx(&cfg, attn_combine_kernel, a);
 }
