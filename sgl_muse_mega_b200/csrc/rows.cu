@@ -32,11 +32,19 @@ static __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 // One CTA per row, H / 8 threads, 8 consecutive columns per thread.
 __global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
     __shared__ float red[33];
-    griddep_wait();
-    griddep_launch();
-    xchg_wait(a.wait);  // the all-reduce partials (mode 0) or the unpooler gather (mode 1) of every contributing rank
     const int row = blockIdx.x, c0 = threadIdx.x * 8;
     const size_t off = (size_t)row * a.H + c0;
+    // the layer's own weights are in flight while the predecessor still runs, the residual stream while the peers' rows
+    // are still on their way
+    const float4 al0 = *(const float4*)(a.alpha + c0), al1 = *(const float4*)(a.alpha + c0 + 4);
+    const float4 be0 = *(const float4*)(a.beta + c0), be1 = *(const float4*)(a.beta + c0 + 4);
+    const uint4 pw_raw = *(const uint4*)(a.pre_w + c0);
+    uint4 post_raw = make_uint4(0, 0, 0, 0);
+    if (a.mode != 0) post_raw = *(const uint4*)(a.post_w + c0);
+    griddep_wait();
+    griddep_launch();
+    const float4 s0 = *(const float4*)(a.stream_in + off), s1 = *(const float4*)(a.stream_in + off + 4);
+    xchg_wait(a.wait);  // the all-reduce partials (mode 0) or the unpooler gather (mode 1) of every contributing rank
     float v[8];
     if (a.mode == 0) {
         uint4 part[kMaxRanks];
@@ -58,15 +66,12 @@ __global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
     } else {
         float w[8];
         unpack8(*(const uint4*)(a.src + off), v);
-        unpack8(*(const uint4*)(a.post_w + c0), w);
+        unpack8(post_raw, w);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] *= w[i];
     }
-    const float4 s0 = *(const float4*)(a.stream_in + off), s1 = *(const float4*)(a.stream_in + off + 4);
-    const float4 al0 = *(const float4*)(a.alpha + c0), al1 = *(const float4*)(a.alpha + c0 + 4);
-    const float4 be0 = *(const float4*)(a.beta + c0), be1 = *(const float4*)(a.beta + c0 + 4);
     float pw[8];
-    unpack8(*(const uint4*)(a.pre_w + c0), pw);
+    unpack8(pw_raw, pw);
     const float st[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
     const float al[8] = {al0.x, al0.y, al0.z, al0.w, al1.x, al1.y, al1.z, al1.w};
     const float be[8] = {be0.x, be0.y, be0.z, be0.w, be1.x, be1.y, be1.z, be1.w};
@@ -352,17 +357,18 @@ constexpr int kMaxTopk = 8;
 __global__ void __launch_bounds__(512) combine_kernel(const CombineArgs a) {
     __shared__ float red[kMaxTopk][17];
     __shared__ float sc[kMaxTopk];
-    griddep_wait();
-    griddep_launch();
     const int row = blockIdx.x, tid = threadIdx.x, c0 = tid * 8, warp = tid >> 5, lane = tid & 31;
     const int nw = blockDim.x >> 5;
+    const uint4 gp_raw = *(const uint4*)(a.gamma_p1 + c0);  // a weight: in flight while the predecessor still runs
+    griddep_wait();
+    griddep_launch();
     xchg_wait(a.wait);  // every rank's column band of the expert outputs
     if (row >= a.b_live) {
         *(uint4*)(a.y + (size_t)row * a.P + c0) = make_uint4(0, 0, 0, 0);
         return;
     }
     float gp[8];
-    unpack8(*(const uint4*)(a.gamma_p1 + c0), gp);
+    unpack8(gp_raw, gp);
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int j0 = 0; j0 < a.k; j0 += kMaxTopk) {
         const int kk = min(kMaxTopk, a.k - j0);
