@@ -194,6 +194,8 @@ int mk_module_load(const void* image, uint64_t bytes, const char* code_prefetch_
     if (e != cudaSuccess) return cuda_fail(e, "headtail_prepare");
     e = segments_prepare();
     if (e != cudaSuccess) return cuda_fail(e, "segments_prepare");
+    e = dense_prepare();
+    if (e != cudaSuccess) return cuda_fail(e, "dense_prepare");
     e = draft_prepare();
     if (e != cudaSuccess) return cuda_fail(e, "draft_prepare");
     MkModule* m = new (std::nothrow) MkModule{dev, prop.multiProcessorCount};
@@ -226,6 +228,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     } guard{L};
     L->pack_only = module == nullptr;
     L->device = module ? module->device : -1;
+    L->sms = module ? module->sms : 148;
     L->shape = s;
     L->bind = *b;
     fill_constants(s, &L->consts);
@@ -511,12 +514,18 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
         g.ldx = (long long)src.ldx * es;
         g.N = src.N; g.K = src.K; g.M = src.M; g.f32 = f32 ? 1 : 0;
         g.part = part;
-        g.packed = b->dense_packed ? 1 : 0;
+        g.packed = (int)b->dense_packed;
     };
     // fused 0 (default): the per-stage launch list with its GEMMs on the item engine of segments.cuh where the shapes tile
     // (pooler and router share a launch); fused 2: the cluster split-K GEMMs of gemm.cu everywhere; fused 1: two segments
-    MK_REQUIRE(!b->dense_packed || (b->fused != 2 && seg_shapes), "dense_packed needs the item engine (fused 0 or 1 and shapes it tiles)");
-    if (b->fused != 2 && seg_shapes) {
+    // dense_packed 2: tile images of the tcgen05 engine (dense.cu): every K a whole number of 256-byte stages
+    const bool umma_images = b->dense_packed == 2;
+    const bool umma_shapes = (qh * kHeadDim) % 128 == 0 && H % 128 == 0 && P % 128 == 0;
+    MK_REQUIRE(b->dense_packed >= 0 && b->dense_packed <= 2, "dense_packed %lld is not 0, 1 or 2", (long long)b->dense_packed);
+    MK_REQUIRE(b->dense_packed != 1 || (b->fused != 2 && seg_shapes), "dense_packed 1 needs the item engine (fused 0 or 1 and shapes it tiles)");
+    MK_REQUIRE(!umma_images || (b->fused == 0 && umma_shapes),
+               "dense_packed 2 needs the per-stage launch list (fused 0) and K dimensions that are multiples of 128");
+    if (umma_images || (b->fused != 2 && seg_shapes)) {
         L->seg_gemms = true;
         const GridBarrier gb{(unsigned long long*)gcnt, budget, L->status};
         auto stage = [&](SegGemmArgs& g, const GemmArgs& src, int finish) {
@@ -546,6 +555,14 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
             L->sg_qkv.epi = L->qkv;
         }
         L->stage_on[ST_ROUTER] = false;  // rides the pooler's launch
+        if (umma_images) {
+            // stream-K partial sums below the routing scores, tickets behind the grid-barrier word
+            unsigned* const tickets = gcnt + 64;
+            SegGemmArgs* all4[4] = {&L->sg_oproj, &L->sg_pool, &L->sg_unpool, tail ? nullptr : &L->sg_qkv};
+            for (SegGemmArgs* g : all4)
+                MK_REQUIRE(g == nullptr || dense_setup(*g, L->sms, gpart, part_cap, tickets, 1024 - 64),
+                           "a dense GEMM of this shape does not fit the tensor-core engine's scratch");
+        }
     }
     if (b->fused == 1 && seg_shapes) {
         L->use_segments = true;
@@ -857,8 +874,10 @@ int mk_lm_head_bind(MkModule* module, const MkLmHeadBind* b, MkLaunch** out) {
     MK_REQUIRE(b->rank >= 0 && b->rank < MKH_RANKS && b->out_peer[b->rank] != 0, "out_peer[rank] (this rank's logits) is 0");
     MK_REQUIRE(b->n_out >= 1 && b->col0 >= 0 && b->col0 + b->n_out <= b->v_total, "columns [%lld, %lld) outside %lld", (long long)b->col0,
                (long long)(b->col0 + b->n_out), (long long)b->v_total);
-    MK_REQUIRE(!b->w_packed || (b->ws != 0 && b->hidden % 512 == 0), "w_packed needs the item engine (ws and hidden a multiple of 512)");
-    if (b->ws != 0 && b->hidden % 512 == 0) return lm_head_on_engine(module, b, out);
+    MK_REQUIRE(b->w_packed != 1 || (b->ws != 0 && b->hidden % 512 == 0), "w_packed 1 needs the item engine (ws and hidden a multiple of 512)");
+    MK_REQUIRE(b->w_packed != 2 || (b->ws != 0 && b->hidden % 128 == 0), "w_packed 2 needs the tensor-core engine (ws and hidden a multiple of 128)");
+    MK_REQUIRE(b->w_packed >= 0 && b->w_packed <= 2, "w_packed %lld is not 0, 1 or 2", (long long)b->w_packed);
+    if (b->w_packed == 2 || (b->ws != 0 && b->hidden % 512 == 0)) return lm_head_on_engine(module, b, out);
     MkLaunch* L = new_op_launch(module, OP_GEMM_BF16);
     MK_REQUIRE(L != nullptr, "out of host memory");
     GemmArgs& g = L->op_gemm;

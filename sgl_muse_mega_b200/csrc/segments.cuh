@@ -752,7 +752,10 @@ static cudaError_t seg_launch(void (*kern)(const Args), const Args& a, int grid,
     cfg.numAttrs = pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, a);
 }
-cudaError_t seg_gemm_launch(const SegGemmArgs& a, int grid, cudaStream_t s, bool pdl) { return seg_launch(seg_gemm_kernel, a, grid, s, pdl); }
+cudaError_t seg_gemm_launch(const SegGemmArgs& a, int grid, cudaStream_t s, bool pdl) {
+    if (a.g[0].packed == 2) return dense_launch(a, grid, s, pdl);  // tile images: the tcgen05 engine of dense.cu
+    return seg_launch(seg_gemm_kernel, a, grid, s, pdl);
+}
 cudaError_t seg_a_launch(const SegAArgs& a, int grid, cudaStream_t s, bool pdl) { return seg_launch(segment_a_kernel, a, grid, s, pdl); }
 cudaError_t seg_b_launch(const SegBArgs& a, int grid, cudaStream_t s, bool pdl) { return seg_launch(segment_b_kernel, a, grid, s, pdl); }
 

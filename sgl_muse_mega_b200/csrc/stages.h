@@ -251,7 +251,12 @@ struct SegGemm {
     int f32;                 // 1: f32 weights through tf32 (tile 16 rows), 0: bf16 (tile 64 rows)
     float* part;             // [K / 256][16][N] f32 partial sums (a slot per K chunk; few of them are written, see segments.cuh)
     int item0, per;          // set on the device: the GEMM's first item within its stage, items per CTA
-    int packed;              // 1: w holds item images [N block][K chunk][rows][512 k + 64 bytes] (a few bulk copies per item)
+    int packed;              // 1: w holds item images [N block][K chunk][rows][512 k + 64 bytes] (a few bulk copies per item);
+                             // 2: w holds the tensor-core tile images of dense.cu ([tile][K stage][2 atoms][128 rows][128 B],
+                             // 128-byte swizzle) and the GEMM runs on tcgen05 (dense_umma_kernel)
+    // dense.cu only: stream-K partial sums [tiles][maxc][16][128] f32 live in `part`; one self-resetting ticket per tile
+    int maxc;                // partial-sum slots per tile (an upper bound of the CTAs that share a tile's K range)
+    unsigned* ticket;        // [tiles], zero between launches
 };
 struct GridBarrier {
     unsigned long long* count;  // starts at a multiple of the grid size and only grows
@@ -332,8 +337,16 @@ struct SegGemmArgs {  // one GEMM stage (or pooler + router) as a kernel of its 
     GridBarrier gb;
     int* status;
 };
+// Launches the GEMM stage on the engine its weights are packed for (g[0].packed == 2: dense.cu's tcgen05 kernel).
 cudaError_t seg_gemm_launch(const SegGemmArgs& a, int grid, cudaStream_t s, bool pdl);
 size_t segments_smem();
+// dense.cu: the tcgen05 stream-K GEMM kernel over tile images (SegGemm.packed == 2)
+size_t dense_smem();
+cudaError_t dense_prepare();
+int dense_grid(const SegGemmArgs& a, int sms);
+size_t dense_part_bound(long long N);  // floats of partial-sum scratch that any K and any grid leave sufficient for N rows
+bool dense_setup(SegGemmArgs& a, int sms, float* part, size_t part_floats, unsigned* ticket, size_t ticket_words);
+cudaError_t dense_launch(const SegGemmArgs& a, int sms, cudaStream_t s, bool pdl);
 cudaError_t segments_prepare();
 cudaError_t seg_a_launch(const SegAArgs& a, int grid, cudaStream_t s, bool pdl);
 cudaError_t seg_b_launch(const SegBArgs& a, int grid, cudaStream_t s, bool pdl);

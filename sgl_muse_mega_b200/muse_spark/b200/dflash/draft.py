@@ -56,17 +56,20 @@ class DraftRank:
     def __init__(self, cfg: DraftConfig, w: DraftWeights, t: TargetShared, rank: int, ranks: int, device, *, rows: int,
                  pool_rows: int, rope_rows: int, lib: Optional[host.Library] = None, module=None, words: Optional[torch.Tensor] = None,
                  caps: Optional[Sequence[torch.Tensor]] = None, verify_ids: Optional[torch.Tensor] = None, exchange=None,
-                 flags: bool = False, wait_budget: int = 0, packed: bool = False, lm_head_packed: Optional[bool] = None,
+                 flags: bool = False, wait_budget: int = 0, packed: Optional[int] = None, lm_head_packed: Optional[int] = None,
                  samp: Optional[torch.Tensor] = None, cand: Optional[torch.Tensor] = None,
-                 walk_q: Optional[torch.Tensor] = None):  # fmt: skip
+                 walk_q: Optional[torch.Tensor] = None, sample_too: bool = False):  # fmt: skip
         """``samp`` (the sampling words on the device) selects the sampled walk; ``cand`` / ``walk_q``: buffers a sampled
-        accept was bound to (default: allocated here).
-        ``packed``: upload the draft's GEMM weights as item images (``weights.pack_items``: one bulk copy per item).
-        ``lm_head_packed``: ``t.lm_head`` already is one (a target stack built with ``packed``); default: pack it too."""
+        accept was bound to (default: allocated here). ``sample_too``: the greedy head stays bound beside the sampled one
+        (``launch_all(sample=False)`` runs it), for a server that takes greedy and sampled requests.
+        ``packed``: the layout the draft's GEMM weights are uploaded in (``weights.pack_dense``): 2 tile images for the
+        tensor-core engine (the default where the shapes tile), 1 / True item images, 0 / False row-major.
+        ``lm_head_packed``: the layout ``t.lm_head`` already has (a target stack's packed lm_head); default: packed here."""
         self.cfg, self.rank, self.ranks, self.rows, self.device = cfg, rank, ranks, rows, device
-        self.packed = bool(packed)
-        pk = W.pack_items if self.packed else (lambda x: x)
-        self.lm_head_packed = self.packed or bool(lm_head_packed)
+        tiles_ok = cfg.conv_groups % 32 == 0 and (cfg.inter // ranks) % 64 == 0 and cfg.hidden % 128 == 0
+        self.packed = (2 if tiles_ok else 0) if packed is None else int(packed)
+        pk = lambda x, perm=None: W.pack_dense(x, self.packed, perm)  # noqa: E731
+        self.lm_head_packed = int(lm_head_packed or 0) or self.packed
         self.lib = lib or host.library()
         self.module = module or self.lib.load()
         self.shape = shape_of(cfg, ranks, rank, rows)
@@ -81,13 +84,14 @@ class DraftRank:
         self.w = dict(
             fc=pk(d(w.fc)), hid_norm=d(w.hidden_norm), norm=d(w.norm), pred=d(w.pred_codebook), succ=d(w.succ_codebook),
             hproj=pk(d(w.hidden_proj)),
-            lm_head=W.pack_items(d(t.lm_head)) if self.packed and not lm_head_packed else d(t.lm_head),
+            lm_head=d(t.lm_head) if lm_head_packed else pk(d(t.lm_head)),
             w_kv=pk(d(torch.cat([lw.qkv[qh * cfg.head_dim :] for lw in w.layers]))),
         )  # fmt: skip
         self.lw = [
             dict(in_norm=d(lw.input_norm), post_norm=d(lw.post_norm), q_norm=d(lw.q_norm), k_norm=d(lw.k_norm), qkv=pk(d(lw.qkv)),
-                 o=pk(d(lw.o)), gate_up=pk(d(lw.gate_up)), down=pk(d(lw.down)), attn_proj=pk(d(lw.attn_conv.proj)),
-                 attn_base=d(lw.attn_conv.base), mlp_proj=pk(d(lw.mlp_conv.proj)), mlp_base=d(lw.mlp_conv.base))
+                 o=pk(d(lw.o)), gate_up=pk(d(lw.gate_up), W.silu_perm(cfg.inter // ranks)), down=pk(d(lw.down)),
+                 attn_proj=pk(d(lw.attn_conv.proj), W.conv_perm(cfg.conv_groups)), attn_base=d(lw.attn_conv.base),
+                 mlp_proj=pk(d(lw.mlp_conv.proj), W.conv_perm(cfg.conv_groups)), mlp_base=d(lw.mlp_conv.base))
             for lw in w.layers
         ]  # fmt: skip
         self.rope = d(rope_table(rope_rows, cfg.head_dim, cfg.rope_theta))
@@ -116,6 +120,7 @@ class DraftRank:
         self.drafts = z(gamma, dt=torch.int64)
         self.verify_ids = verify_ids if verify_ids is not None else z(rows, dt=torch.int64)
         self.samp = samp  # i64 [4] sampling words on the device (``sampling_words``), or None: the greedy walk
+        self.sample_too = sample_too and samp is not None
         self.walk_q = walk_q if walk_q is not None else z(gamma, 16, dt=torch.float32)
         self.status = z(16, dt=torch.int32)
         self.launches: list = []
@@ -164,22 +169,29 @@ class DraftRank:
         self.lm_head = HT.LmHead(lib, mod, w=self.w["lm_head"], x=self.y[1:], gathered=of("gathered"), rank=r, flags=flags,
                                  flags_peer=fpeer, v_total=cfg.vocab, w_packed=self.lm_head_packed, n_out=cfg.vocab // self.ranks,
                                  hidden=cfg.hidden)  # fmt: skip
-        head = host.make(
-            "MkDflashDraftHeadBind", y=self.y, w_hproj=self.w["hproj"], hid=self.hid, logits=self.x.gathered,
-            pred_codebook=self.w["pred"], succ_codebook=self.w["succ"], words=self.words, keys=self.keys, cand=self.cand,
-            unary=self.unary, scores=self.scores, pick=self.pick, drafts=self.drafts, verify_ids=self.verify_ids,
-            mult=cfg.output_multiplier, cap=cfg.softcap, ws=self.ws, flags=flags, contributors=present if flags is not None else 0,
-            status=self.status, wait_budget=self.wait_budget, packed=int(self.packed), samp=self.samp,
-            walk_q=self.walk_q if self.samp is not None else None,
-        )  # fmt: skip
-        self.head = lib.dflash_bind("mk_dflash_draft_head_bind", mod, self.shape, head)
+        def head_bind(samp):
+            return host.make(
+                "MkDflashDraftHeadBind", y=self.y, w_hproj=self.w["hproj"], hid=self.hid, logits=self.x.gathered,
+                pred_codebook=self.w["pred"], succ_codebook=self.w["succ"], words=self.words, keys=self.keys, cand=self.cand,
+                unary=self.unary, scores=self.scores, pick=self.pick, drafts=self.drafts, verify_ids=self.verify_ids,
+                mult=cfg.output_multiplier, cap=cfg.softcap, ws=self.ws, flags=flags, contributors=present if flags is not None else 0,
+                status=self.status, wait_budget=self.wait_budget, packed=int(self.packed), samp=samp,
+                walk_q=self.walk_q if samp is not None else None,
+            )  # fmt: skip
+
+        self.head = lib.dflash_bind("mk_dflash_draft_head_bind", mod, self.shape, head_bind(self.samp))
         self.launches = [self.entry, *self.layers, self.lm_head.launch, self.head]
+        self.launches_greedy = self.launches
+        if self.sample_too:
+            self.head_greedy = lib.dflash_bind("mk_dflash_draft_head_bind", mod, self.shape, head_bind(None))
+            self.launches_greedy = [*self.launches[:-1], self.head_greedy]
 
     def kernels(self) -> int:
         return sum(l.info().kernels for l in self.launches)
 
-    def launch_all(self, s: int, pdl: bool = True) -> None:
-        for l in self.launches:
+    def launch_all(self, s: int, pdl: bool = True, sample: Optional[bool] = None) -> None:
+        """``sample`` False: the greedy walk of a rank bound with ``sample_too``; default: the walk the rank was built for."""
+        for l in self.launches_greedy if sample is False else self.launches:
             l(s, pdl)
 
     def set_state(self, pos: int, anchor: int, commit: int, caps: Optional[torch.Tensor] = None) -> None:

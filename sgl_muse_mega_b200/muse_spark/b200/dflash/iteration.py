@@ -25,11 +25,11 @@ from .weights import DraftConfig, DraftWeights, TargetShared
 class Iteration:
     def __init__(self, stack: Stack, dcfg: DraftConfig, dw: DraftWeights, *, capture: Optional[Sequence[int]] = None,
                  pool_rows: int = 4096, rope_rows: Optional[int] = None, peers: Optional[Sequence] = None, exchange=None,
-                 wait_budget: int = 0, packed: Optional[bool] = None):  # fmt: skip
+                 wait_budget: int = 0, packed: Optional[int] = None):  # fmt: skip
         """``stack``: the bound target stack of this rank (greedy tail). ``capture``: indices into ``stack.layers`` whose
         output residual feeds the draft (default: ``dcfg.capture`` relative to the stack's first layer). ``peers`` /
         ``exchange``: the draft's exchange buffers of a world of several processes (``DraftRank.bind``)."""
-        assert stack.bound and stack.greedy, "the iteration ends with the accept (greedy or sampled) of a bound stack"
+        assert stack.bound and stack.accept is not None, "the iteration ends with the accept (greedy or sampled) of a bound stack"
         cfg = stack.case.cfg
         assert (dcfg.hidden, dcfg.vocab) == (cfg.hidden, cfg.vocab), "the draft borrows the target's embedding and lm_head"
         first = stack.case.first_layer
@@ -42,8 +42,8 @@ class Iteration:
         self.draft = DraftRank(
             dcfg, dw, t, stack.rank, cfg.tp, stack.device, rows=stack.case.rows, pool_rows=pool_rows, rope_rows=rope_rows,
             lib=stack.lib, module=stack.module, words=stack.accept.words, caps=caps, verify_ids=stack.tokens, exchange=exchange,
-            wait_budget=wait_budget, packed=stack.packed if packed is None else packed, lm_head_packed=stack.packed,
-            samp=stack.samp, cand=stack.draft_cand, walk_q=stack.draft_walk_q,
+            wait_budget=wait_budget, packed=packed, lm_head_packed=stack.packed,
+            samp=stack.samp, cand=stack.draft_cand, walk_q=stack.draft_walk_q, sample_too=stack.sample_too,
         )  # fmt: skip
         self.draft.bind(peers)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -67,23 +67,34 @@ class Iteration:
     def kernels(self) -> int:
         return self.draft.kernels() + self.stack.kernels
 
-    def launch_all(self, s: int, pdl: bool = True) -> None:
-        self.draft.launch_all(s, pdl)
-        self.stack.launch_all(s, pdl)
+    def launch_all(self, s: int, pdl: bool = True, sample: Optional[bool] = None, feeds: bool = False) -> None:
+        """``sample``: which of a dual-bound iteration's two forms runs (False the greedy walk and accept, True the sampled
+        ones); default: the form the stack was built for. ``feeds``: the window feeds' kernel first (a serving framework's
+        batch tensors changed since the last step)."""
+        if feeds:
+            self.stack.feeds.launch(s, False)
+        self.draft.launch_all(s, pdl, sample)
+        self.stack.launch_all(s, pdl, tail=None if sample is None else ("sample" if sample else "greedy"))
 
-    def capture_graph(self, pdl: bool = True, warmup: bool = True) -> torch.cuda.CUDAGraph:
+    def capture_graph(self, pdl: bool = True, warmup: bool = True, sample: Optional[bool] = None, feeds: bool = False,
+                      after=None) -> torch.cuda.CUDAGraph:  # fmt: skip
+        """One CUDA graph of the iteration on a side stream. ``after()``: torch work captured behind the launches (the
+        export of the step's results). The default form's graph is kept as ``self.graph`` (``step`` replays it)."""
         dev = self.stack.device
         g = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream(dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
             if warmup:
-                self.launch_all(side.cuda_stream, pdl)
+                self.launch_all(side.cuda_stream, pdl, sample, feeds)
                 side.synchronize()
             with torch.cuda.graph(g, stream=side):
-                self.launch_all(torch.cuda.current_stream(dev).cuda_stream, pdl)
+                self.launch_all(torch.cuda.current_stream(dev).cuda_stream, pdl, sample, feeds)
+                if after is not None:
+                    after()
         torch.cuda.current_stream(dev).wait_stream(side)
-        self.graph = g
+        if sample is None:
+            self.graph = g
         return g
 
     def step(self) -> None:

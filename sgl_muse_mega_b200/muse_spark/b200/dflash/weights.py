@@ -65,6 +65,31 @@ class DraftConfig:
     def qkv_row(self, ranks: int) -> int:
         return (self.q_rank(ranks) + 2 * self.kv_rank(ranks)) * self.head_dim
 
+    @classmethod
+    def from_hf(cls, cfg: dict) -> "DraftConfig":
+        """From a DFlash2 ``config.json`` (a dict). Raises ValueError for the variants the kernels do not implement (another
+        architecture, causal or non-sliding layers, an activation other than silu, attention bias, a scaled rope), KeyError
+        for a config without the DFlash2 keys; same refusals as the reference's ``sm103/dflash/weights.py:64-110``."""
+        d = cfg["dflash_config"]
+        checks = {
+            f"architectures {cfg['architectures']}": cfg["architectures"] == ["DFlash2DraftModel"],
+            "a causal or non-sliding layer": cfg["is_causal"] is False and set(cfg["layer_types"]) == {"sliding_attention"},
+            "an activation other than silu, or attention bias": cfg["hidden_act"] == "silu" and not cfg["attention_bias"],
+            "a rope type other than default": cfg["rope_parameters"]["rope_type"] == "default",
+        }
+        for what, ok in checks.items():
+            if not ok:
+                raise ValueError(what)
+        return cls(
+            hidden=cfg["hidden_size"], layers=cfg["num_hidden_layers"], q_heads=cfg["num_attention_heads"],
+            kv_heads=cfg["num_key_value_heads"], head_dim=cfg["head_dim"], inter=cfg["intermediate_size"],
+            vocab=cfg["vocab_size"], sliding_window=cfg["sliding_window"],
+            rope_theta=float(cfg["rope_parameters"]["rope_theta"]), rms_eps=cfg["rms_norm_eps"],
+            conv_taps=d["conv_kernel_size"], conv_group=d["conv_group_size"], capture=tuple(d["target_layer_ids"]),
+            mask_id=d["mask_token_id"], selector_rank=d["selector_rank"], top_k=d["selector_top_k"],
+            output_multiplier=d["output_multiplier"], softcap=float(d["final_logit_softcapping"]),
+        )  # fmt: skip
+
 
 @dataclass
 class ConvWeights:
@@ -144,3 +169,51 @@ def rope_table(rows: int, dim: int, theta: float) -> torch.Tensor:
     """[rows, dim] f32: cos in the first half of a row, sin in the second (what the draft's kernels gather by position)."""
     c, s = rope_cos_sin(torch.arange(rows), dim, theta)
     return torch.cat([c, s], 1).contiguous()
+
+
+# ---- a DFlash2 checkpoint -> one rank's weights ---------------------------------------------------------------------------------
+
+DRAFT_FILE = "model.safetensors"  # the published draft's single weight file in its directory
+
+
+def safetensors_reader(path: str):
+    """``read(names) -> {name: tensor}`` over a safetensors file (only a real checkpoint needs the package)."""
+
+    def read(names):
+        from safetensors import safe_open
+
+        with safe_open(path, framework="pt") as f:
+            return {n: f.get_tensor(n) for n in names}
+
+    return read
+
+
+def load_shard(read, rank: int, ranks: int, cfg: DraftConfig = DraftConfig()) -> DraftWeights:
+    """Rank ``rank``'s shard of a DFlash2 checkpoint. ``read(names)`` returns the named bf16 tensors (``safetensors_reader``
+    or a test's dict lookup); the entry names are the checkpoint's (reference ``sm103/dflash/weights.py:185-243``): per
+    layer the q / k / v / o and gate / up / down projections, four norms and the two grouped convs' base kernels and
+    kernel projections; globally fc, two norms and the candidate selector's codebooks and projection. Row-parallel shards
+    are copied so that the unsharded tensors can be freed."""
+    layers = []
+    for i in range(cfg.layers):
+        p, a = f"layers.{i}.", f"layers.{i}.self_attn."
+        norms = [p + "input_layernorm.weight", p + "post_attention_layernorm.weight", a + "q_norm.weight", a + "k_norm.weight"]
+        convs = [f"{p}{c}.{n}" for c in ("attention_conv", "mlp_conv") for n in ("base_kernel", "kernel_projection.weight")]
+        proj = [f"{a}{n}_proj.weight" for n in "qkvo"] + [f"{p}mlp.{n}_proj.weight" for n in ("gate", "up", "down")]
+        t = read(norms + convs + proj)
+        for n, x in t.items():
+            if x.dtype != torch.bfloat16:
+                raise ValueError(f"{n} is {x.dtype}, not bfloat16")
+        whole = LayerWeights(
+            *(t[n] for n in norms),
+            qkv=torch.cat([t[f"{a}{n}_proj.weight"] for n in "qkv"]), o=t[a + "o_proj.weight"],
+            gate_up=torch.cat([t[p + "mlp.gate_proj.weight"], t[p + "mlp.up_proj.weight"]]), down=t[p + "mlp.down_proj.weight"],
+            attn_conv=ConvWeights(t[convs[0]], t[convs[1]]), mlp_conv=ConvWeights(t[convs[2]], t[convs[3]]),
+        )  # fmt: skip
+        layers.append(shard_layer(cfg, whole, rank, ranks))
+    sel = "candidate_selector."
+    names = ["fc.weight", "hidden_norm.weight", "norm.weight", sel + "predecessor_codebook", sel + "successor_codebook",
+             sel + "hidden_projection.weight"]  # fmt: skip
+    g = read(names)
+    return DraftWeights(layers, fc=block(g[names[0]], rank, ranks).clone(), hidden_norm=g[names[1]], norm=g[names[2]],
+                        pred_codebook=g[names[3]], succ_codebook=g[names[4]], hidden_proj=g[names[5]])  # fmt: skip

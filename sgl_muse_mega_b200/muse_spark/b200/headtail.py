@@ -81,11 +81,12 @@ class LmHead:
 
     def __init__(self, lib: host.Library, module, *, w, x, gathered: Sequence[Optional[torch.Tensor]], rank: int,
                  flags=None, flags_peer: Sequence = (), v_total: Optional[int] = None, engine: bool = True,
-                 w_packed: bool = False, n_out: Optional[int] = None, hidden: Optional[int] = None):  # fmt: skip
+                 w_packed: int = 0, n_out: Optional[int] = None, hidden: Optional[int] = None):  # fmt: skip
         """``gathered``: tensors, or device addresses (then ``v_total`` is their row length). ``flags`` /
         ``flags_peer``: this rank's flag block and the peers' (present exactly where ``gathered`` is): the GEMM then
         signals the logits exchange on every rank it stored to."""
-        if w_packed:  # item images (weights.pack_items): the matrix shape comes from the caller
+        w_packed = int(w_packed)
+        if w_packed:  # item images (1, weights.pack_items) or tile images (2, weights.pack_umma): the shape comes from the caller
             assert n_out is not None and hidden is not None and engine
         else:
             n_out, hidden = w.shape
@@ -95,6 +96,9 @@ class LmHead:
         # private scratch of the item engine (partial sums per 512-k chunk and its barrier word); shapes it does not tile
         # run on the cluster split-K GEMM without scratch
         ws_bytes = (hidden // 256) * 16 * n_out * 4 + 512 if engine and hidden % 512 == 0 else 0
+        if w_packed == 2:  # the tensor-core engine: stream-K partial sums and one ticket per 128-row tile
+            tiles = (n_out + 127) // 128
+            ws_bytes = max(ws_bytes, (2 * 148 + 2 * tiles) * 2048 * 4 + (tiles * 4 + 255) // 256 * 256 + 512)
         self.ws = _z(ws_bytes, dtype=torch.uint8, device=x.device) if ws_bytes else None
         self.keep = (w, x, list(gathered))
         self.bind = host.make(
@@ -125,9 +129,12 @@ class Accept:
     def __init__(self, lib: host.Library, module, *, logits, tokens, b_live: int, scale: float, cap: float, ring: int = 64,
                  accept_override: Optional[torch.Tensor] = None, cos_sin_cache=None, cos_sin=None, loc_full=None,
                  loc_swa=None, kv_len=None, dcos_sin_cache=None, dring: int = 0, flags=None, contributors: int = 0,
-                 wait_budget: int = 0, pool_rows: int = 0, samp=None, cand=None, walk_q=None, block_verify: bool = True):  # fmt: skip
+                 wait_budget: int = 0, pool_rows: int = 0, samp=None, cand=None, walk_q=None, block_verify: bool = True,
+                 share: Optional["Accept"] = None):  # fmt: skip
         """``samp`` (the sampling words on the device, ``dflash.draft.sampling_words``) with the draft head's ``cand`` and
-        ``walk_q`` binds the sampled accept instead of the greedy one (``sample_out``: the residual's scale and mass)."""
+        ``walk_q`` binds the sampled accept instead of the greedy one (``sample_out``: the residual's scale and mass).
+        ``share``: another accept of the same step (the greedy one beside the sampled one) whose step words, token ring,
+        counter and draft feeds this one advances too: a request may then alternate between the two launches."""
         dev = logits.device
         rows, vocab = logits.shape
         self.sample_ws = self.sample_out = None
@@ -135,15 +142,20 @@ class Accept:
             ys = (rows * vocab * 4 + 255) // 256 * 256
             self.sample_ws = _z(ys + rows * vocab * 8 + 256, dtype=torch.uint8, device=dev)
             self.sample_out = _z(16, dtype=torch.float64, device=dev)  # [0:2] scale, mass; the rest: trace builds
-        self.words = _z(N_WORDS, dtype=torch.int64, device=dev)
-        self.out_ring = _z(ring, dtype=torch.int32, device=dev)
-        self.top1 = _z(rows, dtype=torch.int32, device=dev)
-        self.counter = _z(1, dtype=torch.int32, device=dev)
-        self.status = _z(16, dtype=torch.int32, device=dev)
         draft = dcos_sin_cache is not None
-        self.dcos_sin = _z(2 * b_live, 128, dtype=torch.float32, device=dev) if draft else None
-        self.dslot = _z(2 * b_live, dtype=torch.int32, device=dev) if draft else None
-        self.dkv_len = _z(1, dtype=torch.int32, device=dev) if draft else None
+        if share is not None:
+            assert share.out_ring.numel() == ring, "accepts that share their state have one token ring"
+            self.words, self.out_ring, self.top1, self.counter = share.words, share.out_ring, share.top1, share.counter
+            self.dcos_sin, self.dslot, self.dkv_len = share.dcos_sin, share.dslot, share.dkv_len
+        else:
+            self.words = _z(N_WORDS, dtype=torch.int64, device=dev)
+            self.out_ring = _z(ring, dtype=torch.int32, device=dev)
+            self.top1 = _z(rows, dtype=torch.int32, device=dev)
+            self.counter = _z(1, dtype=torch.int32, device=dev)
+            self.dcos_sin = _z(2 * b_live, 128, dtype=torch.float32, device=dev) if draft else None
+            self.dslot = _z(2 * b_live, dtype=torch.int32, device=dev) if draft else None
+            self.dkv_len = _z(1, dtype=torch.int32, device=dev) if draft else None
+        self.status = _z(16, dtype=torch.int32, device=dev)
         self.keep = (logits, tokens, accept_override, cos_sin_cache, cos_sin, loc_full, loc_swa, kv_len, dcos_sin_cache, samp, cand, walk_q)
         self.bind = host.make(
             "MkAcceptBind", logits=logits, vocab=vocab, rows=rows, b_live=b_live, scale=scale, cap=cap, tokens=tokens,

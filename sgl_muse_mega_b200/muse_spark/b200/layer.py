@@ -45,13 +45,13 @@ class LayerRank:
 
     def __init__(self, lib: host.Library, module, case, rank: int, device, kv_rows: Optional[int] = None, tensors=None,
                  tensor_cores: bool = True, keep_plain_experts: bool = True, io: Optional[dict] = None,
-                 packed: bool = False, expert_range: Optional[tuple] = None):  # fmt: skip
+                 packed: Optional[int] = None, expert_range: Optional[tuple] = None):  # fmt: skip
         """``io`` replaces buffers this layer would allocate with ones it shares with its neighbours in a stack: inputs
         ``qkv_in`` / ``stream_in`` (the predecessor's outputs), ``k_cache`` / ``v_cache`` (the pools the predecessor
         appended to), the step's feeds ``page_table`` / ``kv_len`` / ``cache_loc`` / ``next_cos_sin`` and the
         successor's pools ``next_k`` / ``next_v``, and the exchange buffers one rank's layers share (``ar``, ``z``,
         ``z_sf``, ``z_ex``, ``zb``: byte tensors at least as large as this layer needs; ``pool_ag``, ``unpool_ag``,
-        ``flags``).
+        ``flags``), and ``status`` (one status block shared by the launches of a stack).
         ``tensor_cores``: bind the packed NVFP4 images when the shape has whole 128-row tiles (the tcgen05 expert
         kernels); otherwise, or when False, the experts run on the general CUDA-core kernels from the plain tensors.
         ``keep_plain_experts`` False drops the plain expert tensors once the images exist (halves the expert memory).
@@ -84,18 +84,22 @@ class LayerRank:
             if not keep_plain_experts:
                 for k in ("gate_q", "gate_sf", "up_q", "up_sf", "w2_q", "w2_sf"):
                     w[k] = None
-        # the dense weights as item images of the item engine (one bulk copy an item instead of one per weight row); the
-        # pooler and the unpooler keep this rank's node block only. Not for the cluster split-K form (fused 2).
-        self.packed = bool(packed)
+        # the dense weights in the layout of the dense engine (``MkLayerBind.dense_packed``): 2 (the default where every K is
+        # a multiple of 128) the tile images of the tensor-core engine, 1 / True the item images of the mma.sync item
+        # engine, 0 / False row-major (item engine with one copy per weight row, or the cluster split-K GEMMs with
+        # ``bind(fused=2)``). Packed forms keep this rank's node block of the pooler and the unpooler only.
+        tiles_ok = cfg.oproj_k % 128 == 0 and H % 128 == 0 and P % 128 == 0
+        self.packed = (2 if tiles_ok else 0) if packed is None else int(packed)
         if self.packed:
             w, nr = self.w, cfg.node_ranks
             j = rank % nr
-            w["o_proj"] = weights.pack_items(w["o_proj"])
-            w["pooler"] = weights.pack_items(w["pooler"][j * (P // nr) : (j + 1) * (P // nr)])
-            w["router"] = weights.pack_items(w["router"])
-            w["unpooler"] = weights.pack_items(w["unpooler"][j * (H // nr) : (j + 1) * (H // nr)])
+            pk = lambda t: weights.pack_dense(t, self.packed)  # noqa: E731
+            w["o_proj"] = pk(w["o_proj"])
+            w["pooler"] = pk(w["pooler"][j * (P // nr) : (j + 1) * (P // nr)])
+            w["router"] = pk(w["router"])
+            w["unpooler"] = pk(w["unpooler"][j * (H // nr) : (j + 1) * (H // nr)])
             if w.get("next_qkv") is not None:
-                w["next_qkv"] = weights.pack_items(w["next_qkv"])
+                w["next_qkv"] = pk(w["next_qkv"])
         bf, f32, u8, i32 = torch.bfloat16, torch.float32, torch.uint8, torch.int32
 
         def z(shape, dtype):
@@ -155,7 +159,7 @@ class LayerRank:
         self.z_ex, self.zb = shared("z_ex", c.z_ex_bytes), shared("zb", c.zb_bytes)
         self.flags = io["flags"] if "flags" in io else z((c.flag_words,), i32)
         self.ws = raw(c.ws_bytes)
-        self.status = raw(c.status_bytes)
+        self.status = io["status"] if "status" in io else raw(c.status_bytes)
         self.module = module
         self.launch_record = None
 
@@ -164,10 +168,13 @@ class LayerRank:
         ``z_sf``, ``z_ex``, ``zb``, ``flags`` are that rank's exchange buffers (tensors, or device addresses of buffers
         mapped from another process): every rank's ``LayerRank`` (own included), or None for a lone rank.
         ``fused``: the form of the dense stages (``MkLayerBind.fused``): 0 / False / None = one launch per stage with
-        the GEMMs on the persistent item engine (13 kernels a layer), 1 / True = two persistent segment kernels (7 kernels;
+        the GEMMs on the engine the weights are packed for (13 kernels a layer), 1 / True = two persistent segment kernels
+        (item engine only: ``packed`` 0 or 1; 7 kernels;
         measured slower on the full shape, and never for peers launched one after the other on one GPU: its exchange
         waits poll for ranks that run at the same time), 2 = one launch per stage with the cluster split-K GEMMs (14)."""
         fused = int(fused or 0)
+        if fused and self.packed == 2:
+            raise RuntimeError("dense_packed 2 (tile images) binds the per-stage launch list only: build the rank with packed=0 or 1 for fused forms")
         cfg, case, w, o = self.case.cfg, self.case, self.w, self.o
         n = cfg.tp
 
@@ -244,7 +251,7 @@ class LayerWorld:
     """Every rank of the world on one device, exchange buffers wired as peers (see the module docstring)."""
 
     def __init__(self, case, device, lib: Optional[host.Library] = None, ranks: Optional[list] = None, b_live: int = 0,
-                 tensor_cores: bool = True, packed: bool = False):  # fmt: skip
+                 tensor_cores: bool = True, packed: Optional[int] = None):  # fmt: skip
         self.lib = lib or host.library()
         self.case, self.device = case, device
         with torch.cuda.device(device):

@@ -67,9 +67,17 @@ class Stack:
                  kv_rows: Optional[int] = None, tensor_cores: bool = True, keep_plain_experts: bool = True,
                  greedy: bool = True, accept_override: Optional[torch.Tensor] = None, ring: int = 64,
                  b_live: int = 0, wait_budget: int = 0, fused: bool = False, frame: Optional[dict] = None,
-                 pools: Optional[list] = None, packed: bool = False, sampling: Optional[torch.Tensor] = None,
-                 block_verify: bool = True):  # fmt: skip
-        """``sampling``: the sampled step's words (``dflash.draft.sampling_words``): the step then ends with the sampled
+                 pools: Optional[list] = None, packed: Optional[int] = None, sampling: Optional[torch.Tensor] = None,
+                 block_verify: bool = True, shared_status: bool = False, accept_too: bool = False,
+                 sample_too: bool = False):  # fmt: skip
+        """``accept_too``: a stack whose step ends with the soft cap (``greedy`` False) binds the accept as well
+        (``self.accept``), for a fused iteration on the same buffers; ``launch_all(tail=...)`` picks the tail.
+        ``sample_too`` (with ``sampling``): the greedy accept stays bound beside the sampled one (``self.accept`` and
+        ``self.accept_sampled``, one set of step words), so that greedy and sampled requests share the stack.
+        ``shared_status``: every layer launch of the stack records into ONE status block (``self.shared_status``) instead
+        of one per layer: a wait that gave up then makes every later wait of the step give up at once (they see the
+        recorded failure) instead of each spending its own budget, and a host reads one block per step.
+        ``sampling``: the sampled step's words (``dflash.draft.sampling_words``): the step then ends with the sampled
         accept over the draft head's candidates and walk probabilities (``self.draft_cand`` / ``self.draft_walk_q``, which
         the draft of the iteration writes), block verification or token by token.
         ``case``: a ``synthetic.StackCase``; ``rank`` must be one of ``case.ranks``. ``arena``: the rank's exchange
@@ -123,15 +131,20 @@ class Stack:
         self.embed.copy_(case.embed[slot])
         self.pre_w0 = dev(case.pre_w0)
         self.qkv0 = dev(case.qkv0[slot])
-        self.packed = bool(packed)  # the dense weights and the lm_head as item images (weights.pack_items)
+        # the dense weights and the lm_head in the dense engine's layout (``LayerRank``): 2 tile images (tensor cores; the
+        # default where every K is a multiple of 128), 1 item images, 0 row-major
+        tiles_ok = cfg.oproj_k % 128 == 0 and cfg.hidden % 128 == 0 and cfg.moe_hidden % 128 == 0
+        self.packed = (2 if tiles_ok and not fused else 0) if packed is None else int(packed)  # the fused form: item engine
         self.lm_head_w = dev(case.lm_head[slot])
         if self.packed:
             from . import weights as W
 
-            self.lm_head_w = W.pack_items(self.lm_head_w)
+            self.lm_head_w = W.pack_dense(self.lm_head_w, self.packed)
         self.gathered = self.arena.tensor("gathered")
         self.logits_out = None if greedy else torch.zeros(M, cfg.vocab, dtype=torch.float32, device=device)
         self.greedy, self.accept_override, self.ring = greedy, accept_override, ring
+        self.accept_too, self.sample_too = accept_too, sample_too
+        self.accept = self.accept_sampled = self.softcap = None
         # ---- the KV pools: one pair per layer; context rows from the case ----
         n = len(case.layers)
         self.pools = pools
@@ -152,6 +165,9 @@ class Stack:
         # weights at a time: ``case.layers`` may draw them on demand, and without ``keep_plain_experts`` nothing of a
         # layer but its packed images and dense weights stays on the device ----
         shared = {k: self.arena.tensor(k) for k in ("ar", "pool_ag", "unpool_ag", "z", "z16", "z_sf", "z_ex", "zb", "flags")}
+        self.shared_status = torch.zeros(4096, dtype=torch.uint8, device=device) if shared_status else None
+        if shared_status:
+            shared["status"] = self.shared_status
         self.layers: list[LayerRank] = []
         qkv_in, stream_in = self.qkv_head.out, self.residual0
         for j in range(n):
@@ -203,21 +219,30 @@ class Stack:
                                  gathered=[None if v is None else v.gathered for v in views], rank=self.rank,
                                  flags=flags, flags_peer=[None if v is None else v.flags for v in views],
                                  v_total=cfg.vocab, w_packed=self.packed, n_out=cfg.vocab_rank, hidden=cfg.hidden)  # fmt: skip
-        if self.greedy:
-            self.accept = HT.Accept(
-                self.lib, self.module, logits=self.gathered, tokens=self.tokens, b_live=self.b_live,
-                scale=cfg.output_multiplier, cap=cfg.softcap, ring=self.ring, accept_override=self.accept_override,
-                cos_sin_cache=self.cos_sin_cache, cos_sin=f.cos_sin, loc_full=f.loc_full, loc_swa=f.loc_swa,
-                kv_len=f.kv_len, flags=flags, contributors=present, wait_budget=self.wait_budget,
-                pool_rows=self.kv_rows, samp=self.samp, cand=self.draft_cand, walk_q=self.draft_walk_q,
-                block_verify=self.block_verify,
+        self.tails = {}
+        if self.greedy or self.accept_too:
+            common = dict(
+                logits=self.gathered, tokens=self.tokens, b_live=self.b_live, scale=cfg.output_multiplier, cap=cfg.softcap,
+                ring=self.ring, accept_override=self.accept_override, cos_sin_cache=self.cos_sin_cache, cos_sin=f.cos_sin,
+                loc_full=f.loc_full, loc_swa=f.loc_swa, kv_len=f.kv_len, flags=flags, contributors=present,
+                wait_budget=self.wait_budget, pool_rows=self.kv_rows,
             )  # fmt: skip
+            sampled = dict(samp=self.samp, cand=self.draft_cand, walk_q=self.draft_walk_q, block_verify=self.block_verify)
+            if self.samp is None or self.sample_too:
+                self.accept = HT.Accept(self.lib, self.module, **common)
+                self.tails["greedy"] = self.accept
+            if self.samp is not None:
+                self.accept_sampled = HT.Accept(self.lib, self.module, **common, **sampled, share=self.accept)
+                self.tails["sample"] = self.accept_sampled
+                if self.accept is None:  # a sampled-only stack: ``accept`` names its one accept, as before
+                    self.accept = self.accept_sampled
             self.accept.words[HT.WORDS["P"]] = case.ctx
-            self.tail = self.accept
-        else:
-            self.tail = HT.Softcap(self.lib, self.module, x=self.gathered, out=self.logits_out,
-                                   scale=cfg.output_multiplier, cap=cfg.softcap, flags=flags, contributors=present,
-                                   wait_budget=self.wait_budget)  # fmt: skip
+        if not self.greedy:
+            self.softcap = HT.Softcap(self.lib, self.module, x=self.gathered, out=self.logits_out,
+                                      scale=cfg.output_multiplier, cap=cfg.softcap, flags=flags, contributors=present,
+                                      wait_budget=self.wait_budget)  # fmt: skip
+            self.tails["softcap"] = self.softcap
+        self.tail = self.softcap if not self.greedy else (self.accept_sampled if self.samp is not None and not self.sample_too else self.accept)
         self.bound = True
 
     # ---- launching ----
@@ -231,14 +256,15 @@ class Stack:
         self.entry.launch(s, False)
         self.qkv_head.launch(s, pdl)
 
-    def launch_all(self, s: int, pdl: bool = True, feeds: bool = False) -> None:
+    def launch_all(self, s: int, pdl: bool = True, feeds: bool = False, tail: Optional[str] = None) -> None:
+        """``tail``: "softcap", "greedy" or "sample" (one of the bound tails); default: the stack's own."""
         if feeds:
             self.feeds.launch(s, False)
         self.launch_head(s, pdl)
         for lr in self.layers:
             lr.launch(s, pdl)
         self.lm_head.launch(s, pdl)
-        self.tail.launch(s, pdl)
+        (self.tail if tail is None else self.tails[tail]).launch(s, pdl)
 
     def capture(self, pdl: bool = True, warmup: bool = True) -> torch.cuda.CUDAGraph:
         """One CUDA graph of the whole step on a side stream; ``step`` replays it. ``warmup`` runs the step once before
@@ -275,7 +301,8 @@ class Stack:
     def statuses(self) -> list:
         """(launch name, code, stage, observed) of every launch whose device status word is non-zero."""
         s = torch.cuda.current_stream(self.device).cuda_stream
-        recs = [("feeds", self.feeds.launch), ("lm_head", self.lm_head.launch), ("tail", self.tail.launch)]
+        recs = [("feeds", self.feeds.launch), ("lm_head", self.lm_head.launch)]
+        recs += [(f"tail:{k}", t.launch) for k, t in self.tails.items()]
         recs += [(f"layer{j}", lr.launch_record) for j, lr in enumerate(self.layers)]
         bad = []
         for name, rec in recs:

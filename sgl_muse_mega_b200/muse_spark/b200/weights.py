@@ -132,3 +132,66 @@ def pack_items(w: torch.Tensor) -> torch.Tensor:
     if n % bn:
         out[full, :, : n % bn, :kc] = w[full * bn :].view(n % bn, k // kc, kc).permute(1, 0, 2)
     return out
+
+
+# ---- tile images of the tensor-core dense engine (csrc/dense.cu) ---------------------------------------------------------------
+
+UMMA_ROWS = 128  # weight rows per tile (the M operand of tcgen05.mma)
+UMMA_STAGE_BYTES = 256  # bytes of K per stage and row: two 128-byte swizzle atoms
+
+
+def pack_umma(w: torch.Tensor, perm: torch.Tensor | None = None) -> torch.Tensor:
+    """A row-major GEMM weight [N, K] (bf16, or f32 for the router) -> the tile images the tensor-core dense engine streams:
+    u8 [ceil(N / 128)][K bytes / 256][2 atoms][128 rows][128 bytes], the 16-byte chunk j of row r of an atom stored at chunk
+    j ^ (r % 8) (K-major 128-byte swizzle), rows past N zero. One (tile, K stage) is 32 KiB and arrives by two bulk copies.
+    ``perm``: tile row i of the image holds row ``perm[i]`` of ``w`` (the epilogues that pair rows: SwiGLU, conv).
+    f32 weights lose their low 13 mantissa bits here (the tf32 operand the reference's router defines, R1:123-125)."""
+    if w.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError(f"dtype {w.dtype} is not bf16 / f32")
+    if perm is not None:
+        w = w[perm.to(w.device)]
+    n, k = w.shape
+    row_bytes = k * w.element_size()
+    if row_bytes % UMMA_STAGE_BYTES:
+        raise ValueError(f"K {k} ({row_bytes} bytes) is not a whole number of {UMMA_STAGE_BYTES}-byte stages")
+    if w.dtype == torch.float32:
+        w = (w.contiguous().view(torch.int32) & ~0x1FFF).view(torch.float32)
+    tiles, ks = (n + UMMA_ROWS - 1) // UMMA_ROWS, row_bytes // UMMA_STAGE_BYTES
+    b = torch.zeros(tiles * UMMA_ROWS, row_bytes, dtype=torch.uint8, device=w.device)
+    b[:n] = w.contiguous().view(torch.uint8).view(n, row_bytes)
+    v = b.view(tiles, 16, 8, ks, 2, 8, 16).permute(0, 3, 4, 1, 2, 5, 6)  # [tile, stage, atom, group, row8, chunk, 16]
+    idx = _swizzle_index(w.device)[None, None, None, None, :, :, None].expand(tiles, ks, 2, 16, 8, 8, 16)
+    return torch.gather(v, 5, idx).reshape(tiles, ks, 2, UMMA_ROWS, 128).contiguous()
+
+
+def unpack_umma(img: torch.Tensor, n: int, dtype: torch.dtype) -> torch.Tensor:
+    """Exact inverse of ``pack_umma`` without ``perm`` (up to the router's cleared mantissa bits): -> [n, K]."""
+    tiles, ks = img.shape[:2]
+    v = img.reshape(tiles, ks, 2, 16, 8, 8, 16)
+    idx = _swizzle_index(img.device)[None, None, None, None, :, :, None].expand(tiles, ks, 2, 16, 8, 8, 16)
+    v = torch.gather(v, 5, idx).permute(0, 3, 4, 1, 2, 5, 6).reshape(tiles * UMMA_ROWS, ks * UMMA_STAGE_BYTES)
+    return v[:n].contiguous().view(dtype)
+
+
+def silu_perm(inter: int) -> torch.Tensor:
+    """Row order of a [gate rows | up rows] weight ([2 inter, K]) for the SwiGLU epilogue: tile t holds gate rows
+    64 t .. 64 t + 63, then the same features' up rows."""
+    t = torch.arange(inter // 64)[:, None] * 64 + torch.arange(64)[None, :]
+    return torch.cat((t, t + inter), 1).reshape(-1)
+
+
+def conv_perm(groups: int) -> torch.Tensor:
+    """Row order of a conv projection ([4 groups, K], rows kind x groups + group) for the conv epilogue: tile t holds the four
+    kinds' coefficients of groups 32 t .. 32 t + 31 (tile row kind 32 + group)."""
+    t = torch.arange(groups // 32)[:, None, None] * 32
+    kind = torch.arange(4)[None, :, None] * groups
+    g = torch.arange(32)[None, None, :]
+    return (t + kind + g).reshape(-1)
+
+
+def pack_dense(w: torch.Tensor, packed: int, perm: torch.Tensor | None = None) -> torch.Tensor:
+    """The weight in the layout of the dense engine ``packed`` names: 0 row-major, 1 item images, 2 tile images."""
+    packed = int(packed)
+    if packed == 2:
+        return pack_umma(w, perm)
+    return pack_items(w) if packed == 1 else w

@@ -21,8 +21,10 @@ from .config import Config
 
 INDEX = "model.safetensors.index.json"  # the checkpoint index the expert reader walks (reference runtime/build.py)
 DRAFT_FILE = "model.safetensors"  # the DFlash2 draft's single weight file (reference sm103/dflash/weights.py)
-# the longest bounded device wait, seconds: every wait gives up after 2^20 polls and returns a status instead of
-# trapping, well inside one second; SGLang's watchdog only has to exceed that
+# The longest a step can take when a peer never signals, seconds: an exchange wait gives up after the bind's poll budget
+# (runtime.executor.WAIT_BUDGET polls of ~64 ns: a quarter of a second) and records a status instead of trapping; once
+# a launch's status block holds a failure, its later waits give up after 1024 polls, and the executor raises on the status
+# at the next step. SGLang's watchdog only has to exceed the first wait plus a step.
 LONGEST_WAIT_S = 1.0
 
 
@@ -74,9 +76,13 @@ def config_disable_reasons(cfg, hf_config) -> list:
 def model_disable_reasons(model, hf_config) -> list:
     """Refusals that need the loaded model: every tensor the build aliases in place must have the per-rank shape and
     dtype the kernels read (reference spec.py:125-140 via runtime/build.alias_reasons)."""
+    from .runtime import shim
     from .runtime.build import alias_reasons
 
-    return alias_reasons(model, Config())
+    # the serving world's degree and this process's rank in it: the per-rank shapes (and the vocab shard's first row)
+    # depend on both, so every rank checks its own tensors and all ranks reach the same verdict
+    tp = shim.tp_group()
+    return alias_reasons(model, Config().with_tp(tp.world_size), tp.rank_in_group)
 
 
 def build(model, hf_config, ctx):

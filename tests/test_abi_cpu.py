@@ -71,7 +71,7 @@ def test_pack_only_bind_and_refusals(lib):
     """A bind without a module validates every operand and yields a record that reports its geometry but cannot launch."""
     cfg, kw = CASES["small_fp4_swa_tp2"]
     case = synthetic.layer_case(cfg, **kw)
-    rank = L.LayerRank(lib, None, case, 0, torch.device("cpu"))
+    rank = L.LayerRank(lib, None, case, 0, torch.device("cpu"), packed=0)
     rec = rank.bind(fused=2)
     info = rec.info()
     assert info.kernels == 14 and info.grid > 0 and info.smem > 0  # 17 stage slots; top-k + tables + nq share a launch, the row ops ride the qkv GEMM
@@ -84,6 +84,19 @@ def test_pack_only_bind_and_refusals(lib):
     rank.w["o_proj"] = None
     with pytest.raises(RuntimeError, match="w_o"):
         rank.bind()
+
+
+def test_tile_images_bind_on_the_tensor_core_engine_only(lib):
+    """The default layout of the dense weights is the tile image of the tensor-core engine (dense_packed 2): it binds the
+    per-stage launch list (13 kernels) and refuses the other forms, and a K that is not whole 256-byte stages is refused."""
+    cfg, kw = CASES["small_fp4_swa_tp2"]
+    case = synthetic.layer_case(cfg, **kw)
+    rank = L.LayerRank(lib, None, case, 0, torch.device("cpu"))
+    assert rank.packed == 2 and rank.w["o_proj"].dtype == torch.uint8 and rank.w["o_proj"].shape[2:] == (2, 128, 128)
+    assert rank.bind().info().kernels == 13
+    for form in (1, 2):
+        with pytest.raises(RuntimeError, match="dense_packed 2"):
+            rank.bind(fused=form)
 
 
 def test_expert_range_binds_whole_experts_only(lib):
@@ -116,7 +129,7 @@ def test_module_load_needs_builtin_image(lib):
 def test_tail_and_bf16_variants_drop_stages(lib):
     cfg, kw = CASES["small_bf16_tail_tp4"]
     case = synthetic.layer_case(cfg, **kw)
-    rank = L.LayerRank(lib, None, case, 1, torch.device("cpu"))
+    rank = L.LayerRank(lib, None, case, 1, torch.device("cpu"), packed=0)
     assert rank.bind(fused=2).info().kernels == 14 - 2  # no h-row view (bf16), no successor qkv (tail)
     assert rank.bind(fused=0).info().kernels == 13 - 2
     assert rank.bind(fused=1).info().kernels == 7 - 1  # the fused form: no h-row view either

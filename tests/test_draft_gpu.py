@@ -68,7 +68,8 @@ class Checker:
                 ctx_raw = dr.x.ctx_raw.cpu()
             assert torch.equal(dr.x.ctx_raw.cpu(), ctx_raw)  # every rank gathered the same rows
             close_rows(dr.ctx, D.rms_norm(ctx_raw, w.hidden_norm, cfg.rms_eps), "ctx")
-            self.gemm(dr.kv, dr.ctx, dr.w["w_kv"], "ctx_kv")
+            w_kv = torch.cat([lw.qkv[cfg.q_rank(case.ranks) * cfg.head_dim :] for lw in w.layers])  # dr.w holds the packed image
+            self.gemm(dr.kv, dr.ctx, w_kv, "ctx_kv")
             cos, sin = rope_cos_sin(pos0 + torch.arange(case.rows), cfg.head_dim, cfg.rope_theta)
             kvh = cfg.kv_rank(case.ranks)
             kv = dr.kv.cpu().view(case.rows, cfg.layers, 2, kvh, cfg.head_dim)
@@ -195,7 +196,7 @@ def test_draft_stagewise_and_end_to_end(ranks, rows, pos, commit):
 def test_draft_item_images_give_the_same_bits():
     """The draft's GEMM weights as item images: bit-identical results to row-major weights."""
     case = synthetic.draft_case(CFG, 2, 16, 40, 7, 11)
-    a, b = DR.DraftWorld(case, DEV), DR.DraftWorld(case, DEV, packed=True)
+    a, b = DR.DraftWorld(case, DEV, packed=0), DR.DraftWorld(case, DEV, packed=1)
     a.run_interleaved()
     b.run_interleaved()
     torch.cuda.synchronize()

@@ -105,7 +105,7 @@ def test_eight_row_window_iteration():
     rows = 8
     case = synthetic.stack_case(CFG, n_layers=4, rows=rows, ctx=CTX, seed=10)
     forced = torch.tensor([2], dtype=torch.int32, device=DEV)
-    st = S.Stack(case, 0, DEV, accept_override=forced, packed=True)
+    st = S.Stack(case, 0, DEV, accept_override=forced)
     st.bind()
     dw, dt = dsyn.draft_weights(DCFG, 4), dsyn.target_shared(DCFG, 4)
     w0, _ = shard(DCFG, dw, dt, 0, 1)
@@ -132,7 +132,7 @@ def test_sampled_iteration_matches_the_oracle_on_its_own_tensors():
 
     seed, strm, temp, top_k, top_p = 0x1122334455667788, 2, 0.9, 64, 0.95
     case = synthetic.stack_case(CFG, n_layers=4, rows=ROWS, ctx=CTX, seed=11)
-    st = S.Stack(case, 0, DEV, packed=True, sampling=sampling_words(seed, strm, temp, top_k, top_p))
+    st = S.Stack(case, 0, DEV, sampling=sampling_words(seed, strm, temp, top_k, top_p))
     st.bind()
     dw, dt = dsyn.draft_weights(DCFG, 4), dsyn.target_shared(DCFG, 4)
     w0, _ = shard(DCFG, dw, dt, 0, 1)

@@ -134,7 +134,7 @@ def test_fused_layer_parity(name, device):
     against the oracle like the per-stage kernels."""
     cfg, kw = CASES[name]
     case = synthetic.layer_case(cfg, **kw)
-    world = L.LayerWorld(case, device)
+    world = L.LayerWorld(case, device, packed=0)
     rank = world.ranks[0]
     rank.bind(world.ranks, fused=True)
     assert rank.launch_record.info().kernels == 7
@@ -154,7 +154,7 @@ def test_fused_matches_per_stage_kernels_on_a_lone_rank(name, device):
     outs = []
     drop = (1 if case.bf16 else 0) + (1 if case.tail else 0)  # no h-row view, no successor qkv
     for form in (2, 0, 1):
-        rank = L.LayerRank(host_lib(), _module(device), case, 1, device)
+        rank = L.LayerRank(host_lib(), _module(device), case, 1, device, packed=0)
         rank.bind(None, fused=form)
         assert rank.launch_record.info().kernels == {2: 14 - drop, 0: 13 - drop, 1: 7 - (1 if case.bf16 else 0)}[form]
         rank.launch(torch.cuda.current_stream().cuda_stream, pdl=True)
@@ -194,7 +194,7 @@ def test_item_images_give_the_same_bits(name, device):
     arithmetic in the same order, so every output of the layer is bit-identical."""
     cfg, kw = CASES[name]
     case = synthetic.layer_case(cfg, **kw)
-    a, b = L.LayerWorld(case, device), L.LayerWorld(case, device, packed=True)
+    a, b = L.LayerWorld(case, device, packed=0), L.LayerWorld(case, device, packed=1)
     a.run_interleaved()
     b.run_interleaved()
     torch.cuda.synchronize()
@@ -210,16 +210,42 @@ def test_item_images_give_the_same_bits(name, device):
 @pytest.mark.parametrize("tp", [1, 2])
 def test_window_rows_sweep(rows, tp, device):
     """The verify window of M = 1, 4, 8 and 16 rows (the expert-block sweep of the benchmark configurations) through the
-    whole layer, every stage against the oracle fed the kernels' own inputs; tensor-core experts, dense weights as item
-    images."""
+    whole layer, every stage against the oracle fed the kernels' own inputs; tensor-core experts, dense weights as tile
+    images on the tensor-core engine."""
     from golden_cases import small_cfg
 
     cfg = small_cfg(tp)
     case = synthetic.layer_case(cfg, rows=rows, ctx=29, band="baseline", seed=40 + rows)
-    world = L.LayerWorld(case, device, packed=True)
+    world = L.LayerWorld(case, device)
     world.run_interleaved()
     torch.cuda.synchronize()
     for r in world.ranks:
-        assert r.tensor_cores
+        assert r.tensor_cores and r.packed == 2
         assert r.launch_record.status(torch.cuda.current_stream().cuda_stream).code == 0
     check_world(world, list(range(tp)))
+
+
+@pytest.mark.parametrize("name", ["small_fp4_swa_tp8", "small_fp4_swa_tp1_m5", "small_bf16_tail_tp4", "downscaled_m1"])
+def test_dense_engines_agree(name, device, golden_dir):
+    """The dense GEMMs on the tensor-core engine (tile images, tcgen05 with the whole K accumulated in tensor memory) against
+    the item engine (mma.sync, partial sums per K chunk): the same routing, the same values up to f32 summation order, and
+    each engine within the per-stage bounds of the oracle."""
+    cfg, kw = CASES[name]
+    case = synthetic.layer_case(cfg, **kw)
+    outs = []
+    for packed in (2, 1):
+        world = L.LayerWorld(case, device, packed=packed)
+        assert all(r.packed == packed for r in world.ranks)
+        world.run_interleaved()
+        torch.cuda.synchronize()
+        for r in world.ranks:
+            st = r.launch_record.status(torch.cuda.current_stream().cuda_stream)
+            assert st.code == 0, (packed, r.rank, st.code, st.stage, st.block, st.observed)
+        check_world(world, [0])
+        outs.append({k: v.clone() for k, v in world.ranks[0].values().items()})
+    a, b = outs
+    assert torch.equal(a["ids"], b["ids"])
+    for k in ("branch", "h3", "pooled", "logits", "ffn_out", "qkv_next"):
+        if k in a:
+            x, y = a[k].float(), b[k].float()
+            assert ((x - y).norm() / y.norm().clamp_min(1e-20)).item() < 4e-3, k

@@ -59,8 +59,52 @@ def test_alias_reasons_accept_the_model_and_name_what_is_wrong(case1):
     # a model without the expected modules is one reason, not an exception
     del lm.layers[0].mlp.pre_expert_proj
     assert B.alias_reasons(model, cfg, 0)[0].startswith("the loaded model lacks a tensor the kernels read")
-    # the full-size spec refuses this small model through the same hook
-    assert len(SP.model_disable_reasons(fake_model(case1), None)) > 10
+
+
+@pytest.mark.parametrize("tp", [1, 2, 4, 8])
+def test_model_disable_reasons_use_the_serving_world(tp):
+    """The spec's model hook checks every rank's tensors against the per-rank shapes of the SERVING world (its TP degree
+    and this process's rank in it): a valid full-width model of any supported world passes on every rank, and all ranks
+    reach the same verdict. The tensors here are zero-stride views of the right shapes (the hook reads shapes, dtypes
+    and the vocab shard's first row only)."""
+    from sgl_muse_mega_b200.muse_spark.config import Config as C
+
+    cfg = C().with_tp(tp)
+    for rank in sorted({0, tp - 1}):
+        shim.install()
+        shim.install(tp_group=shim.Parallel(rank, tp))
+        model = shaped_model(cfg, rank)
+        assert SP.model_disable_reasons(model, None) == [], (tp, rank)
+    # a model sharded for another world is refused, with the offending tensors named
+    shim.install(tp_group=shim.Parallel(0, tp))
+    other = shaped_model(C().with_tp(8 if tp != 8 else 4), 0)
+    assert any("qkv0 is" in r for r in SP.model_disable_reasons(other, None))
+    shim.install()
+
+
+def shaped_model(cfg, rank: int):
+    """A model whose tensors have the per-rank shapes of ``cfg`` without their memory (expanded scalars made 'contiguous'
+    is impossible, so each tensor is an empty meta tensor: shape, dtype and contiguity are all the hook reads)."""
+    bf, f32 = torch.bfloat16, torch.float32
+    m = lambda shape, dt=bf: torch.empty(shape, dtype=dt, device="meta")  # noqa: E731
+    h, mh = cfg.hidden, cfg.moe_hidden
+    norm = lambda n: NS(_frozen_weight=m((n,)))  # noqa: E731
+    layers = []
+    for _ in range(cfg.layers):
+        layers.append(NS(
+            input_layernorm=norm(h),
+            self_attn=NS(qkv_proj=NS(weight=m((cfg.qkv_row, h))), o_proj=NS(weight=m((h, cfg.oproj_k))),
+                         rotary_emb=NS(cos_sin_cache=m((64, cfg.head_dim), f32))),
+            mlp=NS(pre_expert_proj=NS(weight=m((mh, h))), post_expert_proj=NS(weight=m((h, mh))),
+                   gate=NS(weight=m((cfg.experts, h), f32), e_score_correction_bias=m((cfg.experts,), f32)),
+                   pre_expert_norm=norm(mh), experts=NS(post_expert_norm=norm(mh))),
+            post_attention_residual_gate=NS(_alpha=m((h,), f32), _beta=m((h,), f32)),
+            post_feedforward_residual_gate=NS(_alpha=m((h,), f32), _beta=m((h,), f32)),
+            pre_feedforward_layernorm=norm(h), post_feedforward_layernorm=norm(h),
+        ))  # fmt: skip
+    shard = NS(org_vocab_start_index=rank * cfg.vocab_rank)
+    lm = NS(layers=layers, norm=norm(h), embed_tokens=NS(weight=m((cfg.vocab_rank, h)), shard_indices=shard))
+    return NS(model=NS(language_model=lm), lm_head=NS(weight=m((cfg.vocab_rank, h)), shard_indices=shard))
 
 
 def test_vocab_shard_must_be_this_ranks_rows():
@@ -110,6 +154,8 @@ def test_model_case_aliases_the_models_tensors(case1):
 
 
 def test_plan_takes_only_the_batch_1_verify_step_of_one_block(case1):
+    shim.install()
+    shim.install(capture_mode=True)
     v = X.Verify(case1.cfg, 16, case1, None, None, None, None, 0, "cpu", None, "test build")
     assert v.widths == (16,) and v.summary() == "test build" and v.draft_sampler is None
     fb = lambda mode, bs: shim.ForwardBatch(shim.ForwardMode(mode), bs, torch.tensor([40]), torch.tensor([0]), torch.arange(16))  # noqa: E731
@@ -120,5 +166,8 @@ def test_plan_takes_only_the_batch_1_verify_step_of_one_block(case1):
     assert v.plan(ids, fb("decode", 1)) is None
     assert v.plan(ids, fb("target_verify", 2)) is None
     assert v.plan(ids[:8], fb("target_verify", 1)) is None
+    shim.install(capture_mode=False)  # outside SGLang's decode-graph capture the step is SGLang's own
+    assert v.plan(ids, fb("target_verify", 1), view=NS()) is None
+    shim.install()
     with pytest.raises(RuntimeError, match="plan"):
         v.forward(None, None, ids, None, fb("target_verify", 1))

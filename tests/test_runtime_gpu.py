@@ -53,7 +53,10 @@ def test_verify_forward_on_scattered_slots_equals_the_identity_stack():
     view = type("View", (), {})()
     view.kv_pool, view.req_to_token_pool = pool, shim.ReqToTokenPool(r2t.to(DEV))
     # ---- build and step ----
+    shim.install()
+    shim.install(capture_mode=True, tp_group=shim.Parallel(0, 1))
     model = fake_model(case, device=DEV)
+    model.model.language_model.layers_to_capture = [2, 4]  # the inputs of layers 2 and 4 = the outputs of layers 1 and 3
     assert B.alias_reasons(model, cfg, 0) == []
     verify = B.build(model, None, shim.Context(rows), parallel=shim.Parallel(0, 1), experts=experts_of(case, device=DEV), cfg=cfg)
     assert isinstance(verify, X.Verify) and verify.widths == (rows,) and "block 16" in verify.summary()
@@ -66,7 +69,10 @@ def test_verify_forward_on_scattered_slots_equals_the_identity_stack():
     torch.cuda.synchronize()
     assert verify.stack.statuses() == []
     assert torch.equal(out.next_token_logits, ref.logits_out)
-    assert torch.equal(out.hidden_states, ref.hidden)
+    # hidden_states: the capture layers' output residuals in capture order, bf16 (what the draft's fc reads)
+    want = torch.cat([ref.layers[c].o["stream_out"].to(torch.bfloat16) for c in (1, 3)], 1)
+    assert out.hidden_states.shape == (rows, 2 * cfg.hidden) and torch.equal(out.hidden_states, want)
+    verify.check_status()  # clean: nothing raised
     # the window's rows landed where the batch said: layer 1 is global (full pool), layer 2 sliding-window (swa pool)
     for j, lc in enumerate(case.layers):
         where = pos_to_full[ctx:] if lc.global_attn else full_to_swa[pos_to_full[ctx:]]
