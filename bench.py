@@ -43,9 +43,10 @@ def parse():
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--cpu-sample-experts", type=int, default=24)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--form", type=int, default=0, choices=(0, 1, 2, 3),
+    ap.add_argument("--form", type=int, default=0, choices=(0, 1, 2, 3, 4),
                     help="dense stages: 0 tcgen05 stream-K GEMM kernels over tile images (default), 1 two persistent segment "
-                         "kernels (mma.sync item engine), 2 cluster split-K GEMMs, 3 item-engine GEMM kernels")
+                         "kernels (mma.sync item engine), 2 cluster split-K GEMMs, 3 item-engine GEMM kernels, 4 two fused "
+                         "tcgen05 kernels (GEMM stages and the row work between them)")
     ap.add_argument("--decode-layers", type=int, default=62, help="layers of the whole-step leg (0: skip it)")
     ap.add_argument("--decode-steps", type=int, default=24)
     ap.add_argument("--no-draft", action="store_true", help="whole-step leg without the DFlash2 draft (ids from the host)")
@@ -223,7 +224,7 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
         assert not args.no_draft, "the sampled accept reads the draft head's candidates"
         sampling = sampling_words(args.seed, 0, args.temperature, args.top_k, args.top_p)
     st = S.Stack(case, tp_rank, device, lib, module, arena=arena, kv_rows=kv_rows, keep_plain_experts=False,
-                 accept_override=forced, wait_budget=1 << 25, sampling=sampling)  # fmt: skip
+                 accept_override=forced, wait_budget=1 << 25, sampling=sampling, fused=args.form == 4)  # fmt: skip
     peers = S.connect_world(st) if world > 1 else st.bind()
     s = stream.cuda_stream
     # the DFlash2 draft at its public size (this rank's TP slice, synthetic weights drawn on the device): with it the step
@@ -404,7 +405,7 @@ def run_ours(args) -> None:
         case = synthetic.layer_case(cfg, rows=args.rows, ctx=args.ctx, global_attn=glob, next_global=(i + 1) % 4 == 3,
                                     band="baseline", seed=args.seed, layer=2 + i, only_ranks=[tp_rank])  # fmt: skip
         lr = L.LayerRank(lib, module, case, tp_rank, device, tensors=case.ranks[0], keep_plain_experts=False,
-                         packed={0: 2, 1: 1, 2: 0, 3: 1}[args.form])
+                         packed={0: 2, 1: 1, 2: 0, 3: 1, 4: 2}[args.form])
         assert lr.tensor_cores, "the full shape runs its experts on the tcgen05 kernels"
         # the absent ranks' contributions: values of the right kind already in the exchange buffers
         g = torch.Generator(device=device).manual_seed(1000 + i)
@@ -415,7 +416,7 @@ def run_ours(args) -> None:
         lr.z_sf.copy_(torch.randint(0x30, 0x40, lr.z_sf.shape, generator=g, device=device, dtype=torch.uint8))
         lr.z_ex.copy_(torch.randint(0, 3, lr.z_ex.shape, generator=g, device=device, dtype=torch.uint8))
         lr.zb.view(torch.bfloat16).copy_(torch.randn(lr.zb.numel() // 2, generator=g, device=device))
-        lr.bind(None, fused={0: 0, 1: 1, 2: 2, 3: 0}[args.form])
+        lr.bind(None, fused={0: 0, 1: 1, 2: 2, 3: 0, 4: 1}[args.form])
         case.ranks = []  # the device copies live in lr.w
         ring.append(lr)
     torch.cuda.synchronize()

@@ -27,6 +27,10 @@ constexpr int kXchgPoints = 8;   // words [0, 8) of the flag block: exchange cou
 constexpr int kXchgEpoch = 8;    // words [8, 16): this rank's epoch per exchange (local)
 constexpr int kXchgDone = 16;    // words [16, 24): CTA arrival counters of the producers (local)
 constexpr int kXchgWords = 32;
+// The fused kernels (fused.cuh) feed and consume an exchange inside one kernel, one arrival per finished tile: they count in
+// words of their own, so that both protocols can serve launches on one flag block.
+constexpr int kFusedFlag = 32;   // words [32, 40): arrivals per exchange point (written by peers)
+constexpr int kFusedEpoch = 40;  // words [40, 48): completed launches that fed the exchange (local)
 
 struct XchgSignal {
     unsigned* flag[kMaxRanks];  // the exchange's word on every receiving rank

@@ -188,18 +188,19 @@ static __device__ void topk_row(const TopkArgs& a, int row, int lane, int* s_ids
 
 // e_hi > e_lo: only the slots routed to an expert in [e_lo, e_hi) enter the tables (this rank's whole experts); the
 // other slots belong to other ranks.
-static __device__ void route_tables(const int* s_ids, int E, int S, RouteTables* rt, int* cnt, int* first, int e_lo = 0,
-                                    int e_hi = 0) {
-    const int tid = threadIdx.x, nt = blockDim.x;
+// `grp`: the threads that build the tables (S <= grp.n): a whole block, or the epilogue warps of a fused kernel.
+static __device__ void route_tables(const int* s_ids, int E, int S, RouteTables* rt, int* cnt, int* first, int e_lo, int e_hi,
+                                    const Grp& grp) {
+    const int tid = grp.tid, nt = grp.n;
     for (int e = tid; e < E; e += nt) cnt[e] = 0;
-    __syncthreads();
+    grp_sync(grp);
     int my_e = -1;
     if (tid < S) {
         my_e = s_ids[tid];
         if (e_hi > e_lo && (my_e < e_lo || my_e >= e_hi)) my_e = -1;
         if (my_e >= 0) atomicAdd(&cnt[my_e], 1);
     }
-    __syncthreads();
+    grp_sync(grp);
     if (tid < 32) {
         // exclusive scan of the counts over the experts, 32 experts per step; compaction of the active ones
         int base = 0, nact = 0;
@@ -226,12 +227,16 @@ static __device__ void route_tables(const int* s_ids, int E, int S, RouteTables*
             rt->n_active = nact;
         }
     }
-    __syncthreads();
+    grp_sync(grp);
     if (tid < S && my_e >= 0) {
         int before = 0;
         for (int s = 0; s < tid; ++s) before += (s_ids[s] == my_e);
         rt->slot[first[my_e] + before] = tid;
     }
+}
+static __device__ void route_tables(const int* s_ids, int E, int S, RouteTables* rt, int* cnt, int* first, int e_lo = 0,
+                                    int e_hi = 0) {
+    route_tables(s_ids, E, S, rt, cnt, first, e_lo, e_hi, block_grp());
 }
 
 static __device__ void nq_row(const NqArgs& a, int row, float* red) {
@@ -444,6 +449,7 @@ __global__ void __launch_bounds__(256) rowops_kernel(const RowopsArgs a) {
 }  // namespace mk
 
 #include "segments.cuh"
+#include "fused.cuh"
 
 namespace mk {
 

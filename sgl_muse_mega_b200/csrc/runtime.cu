@@ -78,6 +78,9 @@ struct MkLaunch {
     mk::SegGemmArgs sg_oproj, sg_pool, sg_unpool, sg_qkv;
     mk::SegAArgs seg_a;
     mk::SegBArgs seg_b;
+    bool use_fused;     // mk_launch runs the dense stages as the two fused tensor-core kernels (fused.cuh)
+    mk::FusedArgs fused_a, fused_b;
+    int fused_grid_a, fused_grid_b;
     // stand-alone launches around the layers (feeds, entry, lm_head, soft cap, accept): n_ops > 0 replaces the stage list
     int n_ops;
     int op_kind[4];
@@ -196,6 +199,8 @@ int mk_module_load(const void* image, uint64_t bytes, const char* code_prefetch_
     if (e != cudaSuccess) return cuda_fail(e, "segments_prepare");
     e = dense_prepare();
     if (e != cudaSuccess) return cuda_fail(e, "dense_prepare");
+    e = fused_prepare();
+    if (e != cudaSuccess) return cuda_fail(e, "fused_prepare");
     e = draft_prepare();
     if (e != cudaSuccess) return cuda_fail(e, "draft_prepare");
     MkModule* m = new (std::nothrow) MkModule{dev, prop.multiProcessorCount};
@@ -315,7 +320,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
         w.status = (int*)b->status;
         w.stage = stage;
     };
-    const int all = (int)s.ranks;
+    const int all = (int)s.ranks, s_rank = (int)s.rank;
 
     // scratch carve (must follow fill_constants)
     unsigned char* ws = (unsigned char*)b->ws;
@@ -523,8 +528,10 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     const bool umma_shapes = (qh * kHeadDim) % 128 == 0 && H % 128 == 0 && P % 128 == 0;
     MK_REQUIRE(b->dense_packed >= 0 && b->dense_packed <= 2, "dense_packed %lld is not 0, 1 or 2", (long long)b->dense_packed);
     MK_REQUIRE(b->dense_packed != 1 || (b->fused != 2 && seg_shapes), "dense_packed 1 needs the item engine (fused 0 or 1 and shapes it tiles)");
-    MK_REQUIRE(!umma_images || (b->fused == 0 && umma_shapes),
-               "dense_packed 2 needs the per-stage launch list (fused 0) and K dimensions that are multiples of 128");
+    MK_REQUIRE(!umma_images || (b->fused != 2 && umma_shapes),
+               "dense_packed 2 needs fused 0 or 1 and K dimensions that are multiples of 128");
+    MK_REQUIRE(!(umma_images && b->fused == 1) || (H % 1024 == 0 && P <= 4096 && K <= 8),
+               "the fused tensor-core kernels need hidden a multiple of 1024, moe_hidden <= 4096 and topk <= 8");
     if (umma_images || (b->fused != 2 && seg_shapes)) {
         L->seg_gemms = true;
         const GridBarrier gb{(unsigned long long*)gcnt, budget, L->status};
@@ -560,11 +567,121 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
             unsigned* const tickets = gcnt + 64;
             SegGemmArgs* all4[4] = {&L->sg_oproj, &L->sg_pool, &L->sg_unpool, tail ? nullptr : &L->sg_qkv};
             for (SegGemmArgs* g : all4)
-                MK_REQUIRE(g == nullptr || dense_setup(*g, L->sms, gpart, part_cap, tickets, 1024 - 64),
+                MK_REQUIRE(g == nullptr || dense_setup(*g, L->sms, gpart, part_cap, tickets, 448 - 64),
                            "a dense GEMM of this shape does not fit the tensor-core engine's scratch");
         }
     }
-    if (b->fused == 1 && seg_shapes) {
+    L->use_fused = false;
+    if (b->fused == 1 && umma_images) {
+        // The fused form on the tensor-core engine (fused.cuh): kernel A = o_proj .. routing, kernel B = combine .. qkv head.
+        // Like the segment kernels its exchange waits poll for peers that run at the same time: a lone rank or one process
+        // per GPU; mk_launch_step still runs the per-stage kernels.
+        L->use_fused = true;
+        // the 1024 counter words: [0, 2) grid barrier, [16, 48) the two kernels' launch / dependency words, [64, 448) tile
+        // tickets, [448, 544) the row meetings' counters of kernels A and B; the meetings' partial sums take the last 2048
+        // floats of the partial-sum scratch
+        unsigned* const words = gcnt + 16;
+        unsigned* const tickets = gcnt + 64;
+        const size_t ticket_cap = 448 - 64;
+        const int norm_parts = H / 1024, combine_parts = (P + 1023) / 1024;
+        MK_REQUIRE(norm_parts <= 8 && combine_parts <= 4, "the fused kernels cut a row into at most 8 (hidden) / 4 (moe_hidden) parts");
+        auto units = [](const SegGemm& g) { return (long long)((g.N + 127) / 128) * (g.K * (g.f32 ? 4 : 2) / 256); };
+        auto grid_for = [&](const SegGemmArgs& x, const SegGemmArgs* y) {
+            long long G = L->sms < 148 ? L->sms : 148;
+            const long long t0 = units(x.g[0]) + (x.n_gemm > 1 ? units(x.g[1]) : 0);
+            if (t0 < G) G = t0;
+            if (y != nullptr) {
+                const long long t1 = units(y->g[0]) + (y->n_gemm > 1 ? units(y->g[1]) : 0);
+                if (t1 < G) G = t1;
+            }
+            return (int)G;
+        };
+        auto fused_wait = [&](FusedArgs& F, int s, int point, int first, int count, int tiles, int stage) {
+            F.wait_flag[s] = nullptr;
+            F.wait_epoch[s] = nullptr;
+            F.bump_epoch[s] = nullptr;
+            F.wait_contrib[s] = 0;
+            F.wait_stage[s] = stage;
+            XchgSignal& x = s == 0 ? F.sig0 : F.sig1;
+            memset(&x, 0, sizeof x);
+            if (flags == nullptr || point < 0) return;
+            unsigned present = 0;
+            for (int r = first; r < first + count; ++r)
+                if (flag_of(r)) {
+                    x.flag[x.n++] = flag_of(r) + kFusedFlag + point;
+                    x.remote |= r != s_rank;
+                    ++present;
+                }
+            F.wait_flag[s] = flags + kFusedFlag + point;
+            F.wait_epoch[s] = flags + kFusedEpoch + point;
+            F.bump_epoch[s] = flags + kFusedEpoch + point;
+            F.wait_contrib[s] = present * (unsigned)tiles;
+        };
+        FusedArgs& A = L->fused_a;
+        memset(&A, 0, sizeof A);
+        A.st[0] = L->sg_oproj;
+        A.st[1] = L->sg_pool;
+        A.st[0].sig = XchgSignal{};
+        A.st[1].sig = XchgSignal{};
+        A.st[1].score = nullptr;  // the top-k CTAs compute the selection scores (spread over their threads)
+        A.score_out = scores;
+        A.n_stages = 2;
+        A.row_kind[0] = 0; A.row_kind[1] = 1; A.row_kind[2] = 2;
+        A.M = M;
+        A.norm = L->post_norm;
+        A.topk = L->topk;
+        A.nq = L->nq;
+        A.rt = L->rt;
+        A.b_live = b_live;
+        A.launches = words; A.done = words + 1; A.dep = words + 2;
+        A.norm_parts = norm_parts; A.combine_parts = combine_parts;
+        const size_t fused_cap = part_cap - 2048;
+        A.meet_count = gcnt + 448; A.meet_part = gpart + fused_cap;
+        A.tiles0[0] = (H + 127) / 128;
+        A.tiles0[1] = (P / nr + 127) / 128;
+        A.router_tiles = (E + 127) / 128;
+        fused_wait(A, 0, XP_AR, 0, all, A.tiles0[0], ST_POST_NORM);
+        fused_wait(A, 1, XP_POOL, node0, nr, A.tiles0[1], ST_NQ);
+        A.budget = budget;
+        A.status = L->status;
+        L->fused_grid_a = grid_for(A.st[0], &A.st[1]);
+        MK_REQUIRE(L->fused_grid_a >= M * norm_parts && L->fused_grid_a > M,
+                   "the fused kernel A has %d CTAs for %d row parts and the routing", L->fused_grid_a, M * norm_parts);
+        MK_REQUIRE(dense_setup(A.st[0], L->sms, gpart, fused_cap, tickets, ticket_cap, L->fused_grid_a) &&
+                       dense_setup(A.st[1], L->sms, gpart, fused_cap, tickets, ticket_cap, L->fused_grid_a),
+                   "a dense GEMM of this shape does not fit the fused kernel's scratch");
+        FusedArgs& B = L->fused_b;
+        memset(&B, 0, sizeof B);
+        B.st[0] = L->sg_unpool;
+        B.st[0].sig = XchgSignal{};
+        B.n_stages = 1;
+        if (!tail) {
+            B.st[1] = L->sg_qkv;
+            B.st[1].sig = XchgSignal{};
+            B.n_stages = 2;
+        }
+        B.row_kind[0] = 3; B.row_kind[1] = 1; B.row_kind[2] = 0;
+        B.M = M;
+        B.norm = L->cross_norm;
+        B.combine = L->combine;
+        B.b_live = b_live;
+        B.launches = words + 8; B.done = words + 9; B.dep = words + 10;
+        B.norm_parts = norm_parts; B.combine_parts = combine_parts;
+        B.meet_count = gcnt + 496; B.meet_part = gpart + fused_cap + 1024;
+        B.tiles0[0] = (H / nr + 127) / 128;
+        B.tiles0[1] = tail ? 0 : ((int)c.qkv_row + 127) / 128;
+        fused_wait(B, 0, XP_UNPOOL, node0, nr, B.tiles0[0], ST_CROSS_NORM);
+        fused_wait(B, 1, -1, 0, 0, 0, 0);
+        B.budget = budget;
+        B.status = L->status;
+        L->fused_grid_b = grid_for(B.st[0], tail ? nullptr : &B.st[1]);
+        MK_REQUIRE(L->fused_grid_b >= M * norm_parts && L->fused_grid_b >= M * combine_parts,
+                   "the fused kernel B has %d CTAs for %d / %d row parts", L->fused_grid_b, M * norm_parts, M * combine_parts);
+        MK_REQUIRE(dense_setup(B.st[0], L->sms, gpart, fused_cap, tickets, ticket_cap, L->fused_grid_b) &&
+                       (tail || dense_setup(B.st[1], L->sms, gpart, fused_cap, tickets, ticket_cap, L->fused_grid_b)),
+                   "a dense GEMM of this shape does not fit the fused kernel's scratch");
+    }
+    if (b->fused == 1 && seg_shapes && !umma_images) {
         L->use_segments = true;
         const GridBarrier gb{(unsigned long long*)gcnt, budget, L->status};
         SegAArgs& A = L->seg_a;
@@ -715,6 +832,18 @@ int mk_launch(const MkLaunch* launch, uint64_t stream, int pdl) {
     MK_REQUIRE(!launch->pack_only, "a pack-only record (bound without a module) cannot launch");
     if (launch->n_dops > 0) return run_dops(launch, 0, launch->n_dops, (cudaStream_t)stream, pdl != 0);
     if (launch->n_ops > 0) return run_ops(launch, (cudaStream_t)stream, pdl != 0);
+    if (launch->use_fused) {
+        const MkLaunch* L = launch;
+        cudaStream_t s = (cudaStream_t)stream;
+        const bool p = pdl != 0;
+        if (run_stage(L, ST_ATTN_SPLIT, s, p) || run_stage(L, ST_ATTN_COMBINE, s, p)) return -1;
+        cudaError_t e = fused_launch(L->fused_a, L->fused_grid_a, s, p);
+        if (e != cudaSuccess) return fail("fused kernel A launch: %s", cudaGetErrorString(e));
+        if (run_stage(L, ST_G1, s, p) || run_stage(L, ST_HROW, s, p) || run_stage(L, ST_G2, s, p)) return -1;
+        e = fused_launch(L->fused_b, L->fused_grid_b, s, p);
+        if (e != cudaSuccess) return fail("fused kernel B launch: %s", cudaGetErrorString(e));
+        return 0;
+    }
     if (launch->use_segments) {
         const MkLaunch* L = launch;
         cudaStream_t s = (cudaStream_t)stream;
@@ -762,7 +891,7 @@ int mk_launch_info(const MkLaunch* launch, MkLaunchInfo* out) {
     }
     int kernels = 0;
     for (int i = 0; i < ST_COUNT; ++i) kernels += L->stage_on[i];
-    if (L->use_segments) kernels = 6 + (L->stage_on[ST_HROW] ? 1 : 0);  // attention x 2, segment A, g1, [h row], g2, segment B
+    if (L->use_segments || L->use_fused) kernels = 6 + (L->stage_on[ST_HROW] ? 1 : 0);  // attention x 2, A, g1, [h row], g2, B
     int64_t grid = 0, smem = 0;
     auto gg = [&](const GemmArgs& g, bool f32) {
         const int64_t n = gemm_grid(g);

@@ -345,11 +345,52 @@ size_t dense_smem();
 cudaError_t dense_prepare();
 int dense_grid(const SegGemmArgs& a, int sms);
 size_t dense_part_bound(long long N);  // floats of partial-sum scratch that any K and any grid leave sufficient for N rows
-bool dense_setup(SegGemmArgs& a, int sms, float* part, size_t part_floats, unsigned* ticket, size_t ticket_words);
+// `force_grid` > 0: the kernel that runs the stage has that many CTAs (a fused kernel: one grid for all its stages)
+bool dense_setup(SegGemmArgs& a, int sms, float* part, size_t part_floats, unsigned* ticket, size_t ticket_words, int force_grid = 0);
 cudaError_t dense_launch(const SegGemmArgs& a, int sms, cudaStream_t s, bool pdl);
 cudaError_t segments_prepare();
 cudaError_t seg_a_launch(const SegAArgs& a, int grid, cudaStream_t s, bool pdl);
 cudaError_t seg_b_launch(const SegBArgs& a, int grid, cudaStream_t s, bool pdl);
+
+// fused.cuh (compiled with rows.cu): two GEMM stages on the tensor-core engine and the row work around them in one kernel
+struct FusedArgs {
+    SegGemmArgs st[2];          // the GEMM stages (tile images, dense_setup done with the kernel's grid)
+    int n_stages;               // 1 or 2
+    int row_kind[3];            // the row stage before stage 0 / between the stages / behind the last: 0 none, 1 norm rows,
+                                // 2 routing + pre-expert norm and quantisation rows, 3 combine rows
+    int M;                      // window rows
+    NormArgs norm;
+    TopkArgs topk;
+    float* score_out;           // [M, E] the routing's selection scores (topk.score reads them), written by the top-k CTAs
+    NqArgs nq;
+    RouteTables* rt;
+    int b_live;
+    CombineArgs combine;
+    // words of this kernel in the layer's private scratch (zero once, they only grow)
+    unsigned* launches;         // launches completed
+    unsigned* done;             // CTAs out of the current launch
+    unsigned* dep;              // [6]: parts of row stage 0 / 1 done, router tiles finished, first-GEMM tiles of stage 0 / 1 finished,
+                                // top-k rows done
+    int norm_parts, combine_parts;  // 1024-column parts a norm row (H / 1024) / a combine row (ceil(P / 1024)) is cut into
+    float* meet_part;           // partial sums of the rows' parts: 2 norm meetings x [16 rows][8 parts], then the combine's
+                                // [16 rows][4 parts][8 slots]
+    unsigned* meet_count;       // [3][16] arrivals per row of the three meetings, only grow
+    int tiles0[2];              // tiles of each stage's first GEMM
+    int router_tiles;
+    // exchanges fed per finished tile: stage 0's first GEMM (sig0), stage 1's first GEMM (sig1); flag words of the fused
+    // protocol in every receiving rank's flag block
+    XchgSignal sig0, sig1;
+    const unsigned* wait_flag[2];   // this rank's word of the exchange stage s feeds (null: no exchange)
+    const unsigned* wait_epoch[2];  // the flag block's count of completed launches that fed it
+    unsigned wait_contrib[2];       // arrivals per launch: present ranks x tiles
+    int wait_stage[2];              // recorded with a wait that ran out
+    unsigned* bump_epoch[2];        // the counts the last CTA out advances (null: none)
+    long long budget;
+    int* status;
+};
+size_t fused_smem();
+cudaError_t fused_prepare();
+cudaError_t fused_launch(const FusedArgs& a, int grid, cudaStream_t s, bool pdl);
 
 size_t experts_umma_smem(bool g2);
 cudaError_t experts_umma_prepare();

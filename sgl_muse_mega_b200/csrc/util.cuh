@@ -75,6 +75,46 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return red[32];
 }
 
+// A group of threads that works on one row together: the whole block (bar 0: __syncthreads) or the `n` threads of a
+// warp-specialised kernel's epilogue warps that share named barrier `bar` (tid counts from the group's first thread).
+struct Grp {
+    int tid, n, bar;
+};
+__device__ __forceinline__ Grp block_grp() { return Grp{(int)threadIdx.x, (int)blockDim.x, 0}; }
+__device__ __forceinline__ void grp_sync(const Grp& g) {
+    if (g.bar == 0) __syncthreads();
+    else asm volatile("bar.sync %0, %1;" ::"r"(g.bar), "r"(g.n) : "memory");
+}
+// Group-wide sum / max; `red` holds 33 floats of shared memory; every thread of the group gets the result.
+__device__ __forceinline__ float grp_sum(float v, float* red, const Grp& g) {
+    const int lane = g.tid & 31, warp = g.tid >> 5, nw = (g.n + 31) >> 5;
+    v = warp_sum(v);
+    grp_sync(g);
+    if (lane == 0) red[warp] = v;
+    grp_sync(g);
+    if (warp == 0) {
+        float s = lane < nw ? red[lane] : 0.f;
+        s = warp_sum(s);
+        if (lane == 0) red[32] = s;
+    }
+    grp_sync(g);
+    return red[32];
+}
+__device__ __forceinline__ float grp_max(float v, float* red, const Grp& g) {
+    const int lane = g.tid & 31, warp = g.tid >> 5, nw = (g.n + 31) >> 5;
+    v = warp_max(v);
+    grp_sync(g);
+    if (lane == 0) red[warp] = v;
+    grp_sync(g);
+    if (warp == 0) {
+        float s = lane < nw ? red[lane] : -INFINITY;
+        s = warp_max(s);
+        if (lane == 0) red[32] = s;
+    }
+    grp_sync(g);
+    return red[32];
+}
+
 // ---- e2m1 / e4m3 ----
 
 // 4-bit e2m1 code -> float: bit 3 sign, {0,.5,1,1.5,2,3,4,6}

@@ -168,13 +168,14 @@ class LayerRank:
         ``z_sf``, ``z_ex``, ``zb``, ``flags`` are that rank's exchange buffers (tensors, or device addresses of buffers
         mapped from another process): every rank's ``LayerRank`` (own included), or None for a lone rank.
         ``fused``: the form of the dense stages (``MkLayerBind.fused``): 0 / False / None = one launch per stage with
-        the GEMMs on the engine the weights are packed for (13 kernels a layer), 1 / True = two persistent segment kernels
-        (item engine only: ``packed`` 0 or 1; 7 kernels;
+        the GEMMs on the engine the weights are packed for (13 kernels a layer), 1 / True = two persistent kernels around the
+        experts (7 kernels a layer): on tile images (``packed`` 2) the fused tensor-core kernels, on ``packed`` 0 or 1 the
+        segment kernels of the item engine (
         measured slower on the full shape, and never for peers launched one after the other on one GPU: its exchange
         waits poll for ranks that run at the same time), 2 = one launch per stage with the cluster split-K GEMMs (14)."""
         fused = int(fused or 0)
-        if fused and self.packed == 2:
-            raise RuntimeError("dense_packed 2 (tile images) binds the per-stage launch list only: build the rank with packed=0 or 1 for fused forms")
+        if fused == 2 and self.packed == 2:
+            raise RuntimeError("dense_packed 2 (tile images) has no cluster split-K form: build the rank with packed=0 for fused=2")
         cfg, case, w, o = self.case.cfg, self.case, self.w, self.o
         n = cfg.tp
 

@@ -69,8 +69,11 @@ class Stack:
                  b_live: int = 0, wait_budget: int = 0, fused: bool = False, frame: Optional[dict] = None,
                  pools: Optional[list] = None, packed: Optional[int] = None, sampling: Optional[torch.Tensor] = None,
                  block_verify: bool = True, shared_status: bool = False, accept_too: bool = False,
-                 sample_too: bool = False):  # fmt: skip
-        """``accept_too``: a stack whose step ends with the soft cap (``greedy`` False) binds the accept as well
+                 sample_too: bool = False, identity_slots: bool = True):  # fmt: skip
+        """``identity_slots`` False (a serving framework's pools: position p does not live in pool row p): the accept writes
+        no feeds for the next window (it can only write identity slots); the window feeds' kernel must run before every
+        step (``launch_all(feeds=True)``) on the framework's batch tensors.
+        ``accept_too``: a stack whose step ends with the soft cap (``greedy`` False) binds the accept as well
         (``self.accept``), for a fused iteration on the same buffers; ``launch_all(tail=...)`` picks the tail.
         ``sample_too`` (with ``sampling``): the greedy accept stays bound beside the sampled one (``self.accept`` and
         ``self.accept_sampled``, one set of step words), so that greedy and sampled requests share the stack.
@@ -134,7 +137,7 @@ class Stack:
         # the dense weights and the lm_head in the dense engine's layout (``LayerRank``): 2 tile images (tensor cores; the
         # default where every K is a multiple of 128), 1 item images, 0 row-major
         tiles_ok = cfg.oproj_k % 128 == 0 and cfg.hidden % 128 == 0 and cfg.moe_hidden % 128 == 0
-        self.packed = (2 if tiles_ok and not fused else 0) if packed is None else int(packed)  # the fused form: item engine
+        self.packed = (2 if tiles_ok else 0) if packed is None else int(packed)
         self.lm_head_w = dev(case.lm_head[slot])
         if self.packed:
             from . import weights as W
@@ -143,7 +146,7 @@ class Stack:
         self.gathered = self.arena.tensor("gathered")
         self.logits_out = None if greedy else torch.zeros(M, cfg.vocab, dtype=torch.float32, device=device)
         self.greedy, self.accept_override, self.ring = greedy, accept_override, ring
-        self.accept_too, self.sample_too = accept_too, sample_too
+        self.accept_too, self.sample_too, self.identity_slots = accept_too, sample_too, identity_slots
         self.accept = self.accept_sampled = self.softcap = None
         # ---- the KV pools: one pair per layer; context rows from the case ----
         n = len(case.layers)
@@ -223,10 +226,12 @@ class Stack:
         if self.greedy or self.accept_too:
             common = dict(
                 logits=self.gathered, tokens=self.tokens, b_live=self.b_live, scale=cfg.output_multiplier, cap=cfg.softcap,
-                ring=self.ring, accept_override=self.accept_override, cos_sin_cache=self.cos_sin_cache, cos_sin=f.cos_sin,
-                loc_full=f.loc_full, loc_swa=f.loc_swa, kv_len=f.kv_len, flags=flags, contributors=present,
-                wait_budget=self.wait_budget, pool_rows=self.kv_rows,
+                ring=self.ring, accept_override=self.accept_override, flags=flags, contributors=present,
+                wait_budget=self.wait_budget,
             )  # fmt: skip
+            if self.identity_slots:
+                common.update(cos_sin_cache=self.cos_sin_cache, cos_sin=f.cos_sin, loc_full=f.loc_full, loc_swa=f.loc_swa,
+                              kv_len=f.kv_len, pool_rows=self.kv_rows)  # fmt: skip
             sampled = dict(samp=self.samp, cand=self.draft_cand, walk_q=self.draft_walk_q, block_verify=self.block_verify)
             if self.samp is None or self.sample_too:
                 self.accept = HT.Accept(self.lib, self.module, **common)

@@ -88,15 +88,15 @@ def test_pack_only_bind_and_refusals(lib):
 
 def test_tile_images_bind_on_the_tensor_core_engine_only(lib):
     """The default layout of the dense weights is the tile image of the tensor-core engine (dense_packed 2): it binds the
-    per-stage launch list (13 kernels) and refuses the other forms, and a K that is not whole 256-byte stages is refused."""
+    per-stage launch list (13 kernels) or the two fused kernels (7), and refuses the cluster split-K form."""
     cfg, kw = CASES["small_fp4_swa_tp2"]
     case = synthetic.layer_case(cfg, **kw)
     rank = L.LayerRank(lib, None, case, 0, torch.device("cpu"))
     assert rank.packed == 2 and rank.w["o_proj"].dtype == torch.uint8 and rank.w["o_proj"].shape[2:] == (2, 128, 128)
     assert rank.bind().info().kernels == 13
-    for form in (1, 2):
-        with pytest.raises(RuntimeError, match="dense_packed 2"):
-            rank.bind(fused=form)
+    assert rank.bind(fused=1).info().kernels == 7  # the two fused tensor-core kernels around the experts
+    with pytest.raises(RuntimeError, match="dense_packed 2"):
+        rank.bind(fused=2)
 
 
 def test_expert_range_binds_whole_experts_only(lib):

@@ -97,9 +97,14 @@ def test_lm_head_softcap_golden():
     assert all(int(h.status[0]) == 0 for h in heads)
 
 
-def test_lm_head_full_shard_ragged_tile():
-    """The 816B model's shard: 25256 vocab rows (not a multiple of the 64-row tile) x 8192, 16 rows, one of eight ranks,
-    against an f32 matmul of the same bf16 operands; columns outside the shard stay untouched."""
+@pytest.mark.parametrize("packed", [0, 2])
+def test_lm_head_full_shard_ragged_tile(packed):
+    """The 816B model's shard: 25256 vocab rows (not a multiple of the 64- or 128-row tile) x 8192, 16 rows, one of eight
+    ranks, against an f32 matmul of the same bf16 operands; columns outside the shard stay untouched. ``packed`` 2: tile
+    images on the tensor-core engine (198 tiles over 148 CTAs: tiles shared by two CTAs meet through the ticketed partial
+    sums), 0: row-major weights on the item engine."""
+    from sgl_muse_mega_b200.muse_spark.b200 import weights as W
+
     lib, module = ctx()
     gen = torch.Generator(device=DEV).manual_seed(5)
     n, k, vt = 25256, 8192, 25256 * 8
@@ -108,7 +113,7 @@ def test_lm_head_full_shard_ragged_tile():
     own = torch.full((16, vt), 7.0, dtype=torch.float32, device=DEV)
     gathered = [None] * 8
     gathered[3] = own
-    h = HT.LmHead(lib, module, w=w, x=x, gathered=gathered, rank=3)
+    h = HT.LmHead(lib, module, w=W.pack_dense(w, packed), x=x, gathered=gathered, rank=3, w_packed=packed, n_out=n, hidden=k)
     h.launch(stream())
     torch.cuda.synchronize()
     ref = x.float() @ w.float().T
@@ -232,3 +237,41 @@ def test_accept_full_vocab_argmax():
     ref = A.first_argmax(torch.tanh((lg * MULT) / CAP) * CAP)
     assert torch.equal(acc.top1.cpu().long(), ref)
     assert ref[4] == 777 and ref[9] == 201000 and ref[12] == 202047
+
+
+@pytest.mark.parametrize("n,k,rows", [(8192, 1024, 16), (2304, 8192, 16), (1000, 512, 5), (25256, 8192, 16)])
+def test_tensor_core_gemm_replays_with_alternating_weights(n, k, rows):
+    """The tensor-core dense engine launched back to back with programmatic dependent launch on ONE output, partial-sum
+    scratch and ticket block, alternating between two weight images: every launch's result must be its own image's (a
+    launch that overtook its predecessor's epilogue, or a ticket left out of step, would mix the two), and the tickets
+    are back at zero after every launch."""
+    from sgl_muse_mega_b200.common import host
+    from sgl_muse_mega_b200.muse_spark.b200 import weights as W
+
+    lib, module = ctx()
+    gen = torch.Generator(device=DEV).manual_seed(n + k)
+    ws = [(torch.randn(n, k, generator=gen, device=DEV) * k**-0.5).bfloat16() for _ in range(2)]
+    x = torch.randn(rows, k, generator=gen, device=DEV).bfloat16()
+    refs = [x.float() @ w.float().T for w in ws]
+    out = torch.zeros(rows, n, dtype=torch.float32, device=DEV)
+    tiles = (n + 127) // 128
+    ticket_bytes = (tiles * 4 + 255) // 256 * 256
+    ws_bytes = (2 * 148 + 2 * tiles) * 2048 * 4 + ticket_bytes + 512
+    scratch = torch.zeros(ws_bytes, dtype=torch.uint8, device=DEV)
+    status = torch.zeros(16, dtype=torch.int32, device=DEV)
+    launches = []
+    images = [W.pack_umma(w) for w in ws]  # kept alive: the binds hold their addresses
+    for img in images:
+        bind = host.make("MkLmHeadBind", w=img, x=x, out_peer=[out], rank=0, v_total=n, col0=0, n_out=n, hidden=k,
+                         rows=rows, status=status, flags=None, flags_peer=[], ws=scratch, ws_bytes=ws_bytes, w_packed=2)  # fmt: skip
+        launches.append((lib.bind("mk_lm_head_bind", module, bind), bind))
+    for count, pdl in ((1, False), (4, True), (7, True), (2, False)):
+        for i in range(count):
+            launches[i % 2][0](stream(), pdl)
+        torch.cuda.synchronize()
+        ref = refs[(count - 1) % 2]
+        rel = ((out - ref).norm(dim=1) / ref.norm(dim=1)).max().item()
+        assert rel < 1e-4, (count, pdl, rel)
+        tickets = scratch[ws_bytes - 512 - ticket_bytes : ws_bytes - 512].view(torch.int32)
+        assert not bool(tickets.any()), "a tile's ticket did not wrap back to zero"
+    assert int(status[0]) == 0

@@ -249,3 +249,66 @@ def test_dense_engines_agree(name, device, golden_dir):
         if k in a:
             x, y = a[k].float(), b[k].float()
             assert ((x - y).norm() / y.norm().clamp_min(1e-20)).item() < 4e-3, k
+
+
+@pytest.mark.parametrize("name", ["small_fp4_swa_tp1_m5", "downscaled_m1"])
+def test_fused_tensor_core_layer_parity(name, device):
+    """The fused form on the tensor-core engine (kernel A: o_proj .. routing, kernel B: combine .. qkv head, the row work
+    on the epilogue warps between the GEMM stages) through one mk_launch: stage by stage against the oracle like the
+    per-stage kernels, twice in a row (the dependency words only grow), then as a CUDA graph, bit for bit the same."""
+    cfg, kw = CASES[name]
+    case = synthetic.layer_case(cfg, **kw)
+    world = L.LayerWorld(case, device)
+    rank = world.ranks[0]
+    assert rank.packed == 2
+    rank.bind(world.ranks, fused=True)
+    assert rank.launch_record.info().kernels == 7
+    s = torch.cuda.current_stream().cuda_stream
+    rank.launch(s, pdl=True)
+    torch.cuda.synchronize()
+    st = rank.launch_record.status(s)
+    assert st.code == 0, (st.code, st.stage, st.block, st.observed, st.expected)
+    check_world(world, [0])
+    first = {k: v.clone() for k, v in rank.values().items()}
+    for v in rank.o.values():
+        v.zero_()
+    rank.launch(s, pdl=False)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream(device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        rank.launch(torch.cuda.current_stream().cuda_stream, pdl=True)
+    for rep in range(2):
+        for v in rank.o.values():
+            v.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        for k, v in rank.values().items():
+            assert torch.equal(first[k].view(torch.uint8), v.view(torch.uint8)), (rep, k)
+    assert rank.launch_record.status(s).code == 0
+
+
+@pytest.mark.parametrize("name", ["small_fp4_swa_tp8", "small_bf16_tail_tp4", "small_fp4_global_tp8_baseline"])
+def test_fused_tensor_core_matches_per_stage_on_a_lone_rank(name, device):
+    """One rank of a larger world alone (its peers' contributions absent in both runs): the fused tensor-core kernels
+    against the per-stage kernels on the same tile images: the same routing and the same values up to f32 summation order
+    (the fused kernel cuts its GEMM stages over one grid, the row stages sum on 128 threads)."""
+    cfg, kw = CASES[name]
+    case = synthetic.layer_case(cfg, **kw)
+    outs = []
+    for form in (0, 1):
+        rank = L.LayerRank(host_lib(), _module(device), case, 1, device)
+        rank.bind(None, fused=form)
+        rank.launch(torch.cuda.current_stream().cuda_stream, pdl=True)
+        torch.cuda.synchronize()
+        st = rank.launch_record.status(torch.cuda.current_stream().cuda_stream)
+        assert st.code == 0, (form, st.code, st.stage, st.block, st.observed, st.expected)
+        outs.append({k: v.clone() for k, v in rank.values().items()})
+    b, a = outs
+    assert torch.equal(a["ids"], b["ids"])
+    for k in a:
+        if a[k].dtype in (torch.int32, torch.uint8):
+            continue
+        x, y = a[k].float(), b[k].float()
+        rel = ((x - y).norm() / y.norm().clamp_min(1e-20)).item()
+        assert rel < 2e-2, (k, rel)
