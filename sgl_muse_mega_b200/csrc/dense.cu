@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(kDThreads, 1) dense_umma_kernel(const __grid_c
     const DenseCtx c = dense_setup_cta<kRing>(dense_smem_raw, a.status);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const Plan pl = plan_of(a);
-    const TileSignals none = {{nullptr, nullptr}, {nullptr, nullptr}};
+    const TileSignals none = {{nullptr, nullptr}, {nullptr, nullptr}, false};
     if (warp == 0) {
         // weights do not depend on the predecessor: streamed before the programmatic launch wait
         if (lane == 0) {

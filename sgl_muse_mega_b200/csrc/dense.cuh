@@ -93,19 +93,6 @@ __device__ __forceinline__ void mma_tf32(uint32_t d, uint64_t ad, uint64_t bd, u
         : "memory");
 }
 
-// weights are read once: evict-first in L2, so that the activations, partial sums and exchange buffers stay resident
-__device__ __forceinline__ uint64_t policy_evict_first() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-__device__ __forceinline__ void bulk_g2s_hint(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar, uint64_t policy) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
-                     smem_u32(smem_dst)),
-                 "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
-                 : "memory");
-}
-
 __device__ __forceinline__ uint4 pack8f(const float* f) {
     uint4 v;
     __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
@@ -461,6 +448,8 @@ __device__ __forceinline__ bool dense_stage_x(const SegGemmArgs& a, const DenseC
 struct TileSignals {
     const XchgSignal* tile_sig[2];
     unsigned* dep[2];
+    bool defer1;  // the second GEMM's tiles are not finished here: every contributor stores its partial and arrives on
+                  // dep[1]; whoever waits for all contributions sums them in slot order (the router's rows, fused.cuh)
 };
 
 // warps 4-7 (te = 0..127, q = warp - 4): accumulators out of tensor memory, the stream-K meeting of a shared tile, the
@@ -488,7 +477,15 @@ __device__ __forceinline__ bool dense_epilogue(const SegGemmArgs& a, const Dense
 #pragma unroll
         for (int m = 0; m < 16; ++m) v[m] = __uint_as_float(r[m]);
         bool finish = true;
-        if (u.n > 1) {
+        if (u.gi == 1 && sg.defer1) {
+            float* mine = g.part + ((size_t)u.tile * g.maxc + u.slot) * 2048 + te;
+#pragma unroll
+            for (int m = 0; m < 16; ++m) __stcg(mine + m * 128, v[m]);
+            __threadfence();
+            bar_sync(2, 128);
+            if (te == 0) atomicAdd(sg.dep[1], 1u);
+            finish = false;
+        } else if (u.n > 1) {
             // this CTA's partial of the tile, then a ticket: the last contributor sums all of them in slot order
             float* mine = g.part + ((size_t)u.tile * g.maxc + u.slot) * 2048 + te;
 #pragma unroll

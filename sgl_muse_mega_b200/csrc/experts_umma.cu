@@ -54,6 +54,7 @@ struct UnitMeta {
     int slot[kMaxRows];   // route slot (token x topk + k)
     float s[kMaxRows];    // g1: alpha x x_scale[token]; g2: 2^e_row[slot]
     float c;              // g1: scale_c; g2: alpha
+    int erow[kMaxRows];   // g2 without an h-row kernel: each routed slot's row exponent (the largest of its group exponents)
 };
 
 __device__ __forceinline__ void record_abort(int* status, volatile int* abort, int code, int where, int observed) {
@@ -137,8 +138,10 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    griddep_wait();
-    // one round trip for the route tables every unit looks up
+    // One round trip for the route tables every unit looks up. g2's predecessor is g1: the tables were written two or more
+    // kernels back, so g2 copies them and starts streaming its first weights under g1's tail; the roles that touch what g1
+    // wrote wait below.
+    if (!G2) griddep_wait();
     for (int i = tid; i < (int)(sizeof(RouteTables) / 4); i += 256) ((int*)rt)[i] = ((const int*)a.rt)[i];
     __syncthreads();
     const int NB = a.NB, KCH = a.K / 256;
@@ -147,6 +150,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
     if (warp == 0) {
         // ---- weight producer ----
         if (lane == 0) {
+            const uint64_t policy = policy_evict_first();  // expert weights are read once a step
             uint32_t it = 0;
             for (int u = blockIdx.x; u < n_units && !*abort; u += gridDim.x) {
                 const int e = rt->act_e[u / NB], blk = u % NB;
@@ -161,7 +165,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
                     unsigned char* dst = stages + s * STAGE;
                     const unsigned char* g = src + (size_t)kc * STAGE;
 #pragma unroll
-                    for (uint32_t off = 0; off < STAGE; off += 9216) bulk_g2s(dst + off, g + off, 9216, &full[s]);
+                    for (uint32_t off = 0; off < STAGE; off += 9216) bulk_g2s_hint(dst + off, g + off, 9216, &full[s], policy);
                 }
             }
         }
@@ -214,6 +218,10 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
     } else if (warp < 4) {
         // ---- stager: the B operand of unit j into buffer j & 1, two units ahead of the MMAs ----
         const int ts = tid - 64;  // 0..63
+        if (G2) {
+            griddep_wait();
+            xchg_wait_role(a.wait, ts, 64, 3);  // without an h-row kernel in front: every rank's column band of the h planes
+        }
         int j = 0;
         for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++j) {
             const int buf = j & 1;
@@ -234,10 +242,11 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
             if (ts < n_tok) {
                 slot = rt->slot[s0 + ts];
                 row = G2 ? slot : slot / a.topk;
-                sc = G2 ? a.rowscale[slot] : a.g1_alphas[e] * a.x_scale[row];
+                sc = G2 ? (a.bex != nullptr ? 0.f : a.rowscale[slot]) : a.g1_alphas[e] * a.x_scale[row];
             }
             if (ts == 0) cc = G2 ? a.g2_alphas[e] : a.g1_scale_c[e];
-            uint4 wv[4];
+            const bool view = G2 && a.bex != nullptr;  // this kernel forms the h-row view itself (no h-row kernel ran)
+            uint4 wv[4], xv[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 const int idx = k * 64 + ts;  // 16 rows x 16 uint4 at most
@@ -245,6 +254,48 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
                     const int tk = idx / wq, c = idx - tk * wq;
                     const int sl = rt->slot[s0 + tk];
                     wv[k] = *(const uint4*)(a.bsf + (size_t)(G2 ? sl : sl / a.topk) * (a.K / 16) + c * 16);
+                    if (view) xv[k] = *(const uint4*)(a.bex + (size_t)sl * (a.K / 16) + c * 16);
+                }
+            }
+            if (view) {
+                // the row exponent of each routed slot = the largest of its K / 16 group exponents: four threads share a
+                // slot (a quarter of its exponent bytes each; tokens 0..7 on the first stager warp, 8..15 on the second)
+                const int tk = ts >> 2, qd = ts & 3, gb = a.K / 16;
+                int er = -128;
+                if (tk < n_tok) {
+                    const signed char* ex = a.bex + (size_t)rt->slot[s0 + tk] * gb;
+                    for (int i = qd * 16; i < gb; i += 64) {
+                        const uint4 v4 = *(const uint4*)(ex + i);
+                        const uint32_t w4[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) er = max(er, (int)(signed char)(w4[j] >> (8 * b)));
+                    }
+                }
+                er = max(er, __shfl_xor_sync(0xffffffffu, er, 1));
+                er = max(er, __shfl_xor_sync(0xffffffffu, er, 2));
+                if (qd == 0 && tk < n_tok) m.erow[tk] = er;
+                bar_sync(3, 64);
+                if (ts < n_tok) sc = __uint_as_float((uint32_t)(m.erow[ts] + 127) << 23);  // 2^e_row
+                // every scale byte moved to its row's exponent (scale x 2^-(e_row - e_group))
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int idx = k * 64 + ts;
+                    if (idx < wtotal) {
+                        const int e_row = m.erow[idx / wq];
+                        const uint32_t sw[4] = {wv[k].x, wv[k].y, wv[k].z, wv[k].w};
+                        const uint32_t ew[4] = {xv[k].x, xv[k].y, xv[k].z, xv[k].w};
+                        uint32_t o[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            o[j] = 0;
+#pragma unroll
+                            for (int b = 0; b < 4; ++b)
+                                o[j] |= scale_down_byte((sw[j] >> (8 * b)) & 0xFFu, e_row - (int)(signed char)(ew[j] >> (8 * b))) << (8 * b);
+                        }
+                        wv[k] = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
                 }
             }
             for (int base = 0; base < total; base += 64 * 8) {
@@ -291,6 +342,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
         }
     } else {
         // ---- scale words -> tensor memory, epilogue out ----
+        if (G2) griddep_wait();
         const int q = warp - 4, te = tid - 128;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
 

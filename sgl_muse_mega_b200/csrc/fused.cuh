@@ -40,8 +40,8 @@ struct FusedShared {  // behind the engine's shared memory
     float redk[kMaxTopk][5];
     float total[kMaxTopk];
     int s_ids[kMaxSlots];
-    int cnt[1024];
-    int first[1024];
+    int cnt[1024];   // route tables; the top-k CTAs keep their row's selection scores here (as floats)
+    int first[1024]; // route tables; the top-k CTAs keep the experts' biases here (as floats)
 };
 
 // ---- bounded waits on words that only grow -------------------------------------------------------------------------------------
@@ -230,8 +230,18 @@ __device__ __forceinline__ void norm_part_g(const NormArgs& a, int row, int part
         *(uint2*)(a.q + (size_t)row * (a.P / 2) + (gi) * 8) = make_uint2(l_, h_);                    \
         a.sf[(size_t)row * groups + (gi)] = (unsigned char)sfb_;                                     \
     }
+#ifdef FUSED_TRACE
+#define NQ_T(slot)                                                                   \
+    if (g.tid == 0 && blockIdx.x == 0 && trace != nullptr) {                         \
+        unsigned long long t_;                                                       \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                      \
+        ((unsigned long long*)trace)[32 + (slot)] = t_;                              \
+    }
+#else
+#define NQ_T(slot)
+#endif
 // Up to two groups per thread (P <= 4096): group t and group t + 128.
-__device__ __forceinline__ void nq_row_g(const NqArgs& a, int row, float* red, const Grp& g) {
+__device__ __forceinline__ void nq_row_g(const NqArgs& a, int row, float* red, const Grp& g, int* trace = nullptr) {
     const int t = g.tid, groups = a.P / 16;
     const bf16* x = a.pooled + (size_t)row * a.P;
     const bool on0 = t < groups, on1 = t + 128 < groups;
@@ -258,7 +268,9 @@ __device__ __forceinline__ void nq_row_g(const NqArgs& a, int row, float* red, c
 #pragma unroll
         for (int i = 0; i < 8; ++i) ss += hi1[i] * hi1[i];
     }
+    NQ_T(12)
     const float rstd = inv_sqrt(grp_sum(ss, red, g) / (float)a.P + a.eps);
+    NQ_T(13)
     float gmax0 = 0.f, gmax1 = 0.f;
     if (on0) {
         MK_NQ_NORM8(lo0, g0a, gmax0)
@@ -281,7 +293,9 @@ __device__ __forceinline__ void nq_row_g(const NqArgs& a, int row, float* red, c
         }
         return;
     }
+    NQ_T(16)
     const float amax = grp_max(fmaxf(gmax0, gmax1), red, g);
+    NQ_T(17)
     const float kSixth = 1.0f / 6.0f, kInv2688 = 1.0f / 2688.0f;
     const float x_scale = fmaxf(amax, 1e-10f) * kInv2688;
     const float inv_x = 1.0f / x_scale;
@@ -426,16 +440,42 @@ __global__ void __launch_bounds__(kDThreads, 1) fused_dense_kernel(const __grid_
                 const bool apart = G >= 2 * a.M + 1;
                 const int topk_row_of = apart ? cta - a.M : cta;
                 if (topk_row_of >= 0 && topk_row_of < a.M) {
-                    grp_wait_word(a.dep + 2, (e + 1) * (unsigned)a.router_tiles, false, a.budget, a.status, 2, 620, g);
-                    // the row's selection scores (sigmoid in f64 rounded to f32, plus the expert's bias) on all 128 threads:
-                    // f64 arithmetic is scarce, a tile's epilogue would spend 16 of them per thread
+                    // The router's tiles are not finished by their contributors (a tile is shared by some twenty CTAs: one
+                    // of them summing all partials was the longest chain of the kernel): every top-k CTA sums its own row's
+                    // partial logits in slot order, computes the selection scores (sigmoid in f64 rounded to f32, plus the
+                    // expert's bias) on all 128 threads and keeps them in shared memory for the selection.
+                    const SegGemm& rg = a.st[1].g[1];
+                    const Plan rp = plan_of(a.st[1]);
+                    float* scores = (float*)sh.cnt;
+                    float* bias = (float*)sh.first;
+                    for (int ex = te; ex < a.topk.E; ex += 128) bias[ex] = a.topk.bias[ex];  // in flight during the wait
+                    grp_wait_word(a.dep + 2, (e + 1) * (unsigned)a.router_contribs, false, a.budget, a.status, 2, 620, g);
+                    const int KSr = stages_of(rg);
                     for (int ex = te; ex < a.topk.E; ex += 128) {
-                        const float v = __ldcg(a.topk.logits + (size_t)topk_row_of * a.topk.E + ex);
-                        a.score_out[(size_t)topk_row_of * a.topk.E + ex] =
-                            (float)(1.0 / (1.0 + exp(-((double)v * a.topk.mult)))) + a.topk.bias[ex];
+                        const int rt_tile = ex >> 7, col = ex & 127;
+                        const uint32_t first = rp.T0 + (uint32_t)rt_tile * KSr;
+                        const int n = cta_of(first + KSr - 1, rp.T, rp.G) - cta_of(first, rp.T, rp.G) + 1;
+                        const float* src = rg.part + (size_t)rt_tile * rg.maxc * 2048 + topk_row_of * 128 + col;
+                        float v = 0.f;
+                        int sl = 0;
+                        for (; sl + 8 <= n; sl += 8) {
+                            float t8[8];
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) t8[k] = __ldcg(src + (size_t)(sl + k) * 2048);
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) v += t8[k];
+                        }
+                        for (; sl < n; ++sl) v += __ldcg(src + (size_t)sl * 2048);
+                        a.st[1].f32_out[(size_t)topk_row_of * a.topk.E + ex] = v;
+                        scores[ex] = (float)(1.0 / (1.0 + exp(-((double)v * a.topk.mult)))) + bias[ex];
                     }
                     grp_sync(g);
-                    if (q == 0) topk_row(a.topk, topk_row_of, lane, sh.s_ids);
+                    if (q == 0) {
+                        TopkArgs tk = a.topk;  // the selection reads this row's scores and the biases from shared memory
+                        tk.score = scores - (size_t)topk_row_of * a.topk.E;
+                        tk.bias = bias;
+                        topk_row(tk, topk_row_of, lane, sh.s_ids);
+                    }
                     grp_arrive(a.dep + 5, g);
                 }
                 if (cta == G - 1) {
@@ -452,7 +492,7 @@ __global__ void __launch_bounds__(kDThreads, 1) fused_dense_kernel(const __grid_
                     if (a.wait_flag[1] != nullptr)
                         grp_wait_word(a.wait_flag[1], (ex1 + 1) * a.wait_contrib[1], true, a.budget, a.status, 1, a.wait_stage[1], g);
                     if (te == 0) { FT(2 + 4 * s) }
-                    nq_row_g(a.nq, cta, sh.red, g);
+                    nq_row_g(a.nq, cta, sh.red, g, a.status);
                 }
             }
             if (te == 0) { FT(3 + 4 * s) }
@@ -463,6 +503,7 @@ __global__ void __launch_bounds__(kDThreads, 1) fused_dense_kernel(const __grid_
             sg.tile_sig[1] = nullptr;
             sg.dep[0] = a.dep + 3 + s;
             sg.dep[1] = a.dep + 2;
+            sg.defer1 = a.row_kind[2] == 2;  // kernel A: the router's rows are summed by their top-k CTAs
             ok = dense_epilogue<kFRing>(a.st[s], c, plan_of(a.st[s]), i, q, te, lane, sg);
             if (te == 0) { FT(4 + 4 * s) }
         }

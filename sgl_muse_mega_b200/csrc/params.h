@@ -120,6 +120,33 @@ __device__ __forceinline__ void xchg_wait_epoch(const XchgWait& w, unsigned epoc
 }
 __device__ __forceinline__ void xchg_wait(const XchgWait& w) { xchg_wait_epoch(w, xchg_epoch(w)); }
 
+// The same wait for one role of a warp-specialised kernel: the `n` threads that share named barrier `bar` (tid counts from
+// the role's first thread); the other roles carry on.
+__device__ __forceinline__ void xchg_wait_role(const XchgWait& w, int tid, int n, int bar) {
+    if (w.flag == nullptr) return;
+    if (tid == 0) {
+        const unsigned want = xchg_epoch(w) * w.contributors;
+        long long polls = 0;
+        for (;;) {
+            unsigned seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(w.flag) : "memory");
+            if ((int)(seen - want) >= 0) break;
+            if ((polls & 1023) == 1023 && w.status != nullptr && *(volatile int*)w.status != 0) break;
+            if (++polls > w.budget) {
+                if (w.status != nullptr && atomicCAS(w.status, 0, 1) == 0) {
+                    w.status[1] = w.stage;
+                    w.status[2] = (int)blockIdx.x;
+                    w.status[3] = (int)seen;
+                    w.status[4] = (int)want;
+                }
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+    asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(n) : "memory");
+}
+
 // Route tables in the private scratch, written by the routing kernel each launch.
 struct RouteTables {
     int n_active;                   // distinct routed experts

@@ -325,16 +325,6 @@ __global__ void __launch_bounds__(512) route_nq_kernel(const RouteNqArgs a) {
 // ---- h row view: scales moved to the row's largest exponent ---------------------------------------------------------------
 // e_row = max over the full row's group exponents; sf' = sf x 2^-(e_row - e): exponent-field move while normal, round half
 // up on the subnormal grid                                                                 (muse_spark.py:447-491)
-__device__ __forceinline__ uint32_t scale_down_byte(uint32_t byte, int delta) {
-    const int ef = (int)(byte >> 3);
-    if (ef > delta) return byte - ((uint32_t)delta << 3);
-    const uint32_t sig = (byte & 7u) | (ef != 0 ? 8u : 0u);
-    int sh = delta - ef + (ef != 0 ? 1 : 0);
-    sh = min(max(sh, 0), 8);
-    const uint32_t half = sh > 0 ? (1u << (sh - 1)) : 0u;
-    return (sig + half) >> sh;
-}
-
 __global__ void __launch_bounds__(256) hrow_kernel(const unsigned char* z_sf, const signed char* z_ex, int groups, int slots_live,
                                                    unsigned char* z_sfd, float* rowscale, const XchgWait wait) {
     __shared__ float red[33];

@@ -484,7 +484,10 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
             u.P = P; u.I = I; u.I_s = I_s; u.H_s = H_s; u.rank = (int)s.rank; u.topk = K;
             u.wpack = (const unsigned char*)(g2 ? b->w2_pack : b->w1_pack);
             u.bq = g2 ? (const unsigned char*)b->z : (const unsigned char*)b->q;
-            u.bsf = g2 ? L->z_sfd : (const unsigned char*)b->sf;
+            // g2 forms the h-row view in its own stager (row exponents, moved scale bytes, row scales): no h-row kernel
+            u.bsf = g2 ? (const unsigned char*)b->z_sf : (const unsigned char*)b->sf;
+            u.bex = g2 ? (const signed char*)b->z_ex : nullptr;
+            if (g2) u.wait = L->hrow_wait;
             u.x_scale = (const float*)b->x_scale;
             u.g1_alphas = (const float*)b->g1_alphas;
             u.g1_scale_c = (const float*)b->g1_scale_c;
@@ -500,6 +503,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
             u.status = L->status;
             u.sig = g2 ? ex.sig_g2 : ex.sig_g1;
         }
+        L->stage_on[ST_HROW] = false;
     }
     // The fused form of the dense stages (segments.cuh): two persistent kernels with grid barriers. Its exchange waits
     // poll for peers that run at the same time, so it serves a lone rank or one process per GPU; a world emulated on one
@@ -650,6 +654,16 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
         MK_REQUIRE(dense_setup(A.st[0], L->sms, gpart, fused_cap, tickets, ticket_cap, L->fused_grid_a) &&
                        dense_setup(A.st[1], L->sms, gpart, fused_cap, tickets, ticket_cap, L->fused_grid_a),
                    "a dense GEMM of this shape does not fit the fused kernel's scratch");
+        {
+            // the CTAs that hold a K range of a router tile (the kernel's own cut: unit s belongs to the largest c with
+            // floor(c T / G) <= s)
+            const long long T0 = units(A.st[1].g[0]), T = T0 + units(A.st[1].g[1]), G = L->fused_grid_a;
+            const long long KS = (long long)H * 4 / 256;
+            auto cta_of = [&](long long u) { return ((u + 1) * G + T - 1) / T - 1; };
+            long long total = 0;
+            for (int t = 0; t < A.router_tiles; ++t) total += cta_of(T0 + (t + 1) * KS - 1) - cta_of(T0 + t * KS) + 1;
+            A.router_contribs = (int)total;
+        }
         FusedArgs& B = L->fused_b;
         memset(&B, 0, sizeof B);
         B.st[0] = L->sg_unpool;

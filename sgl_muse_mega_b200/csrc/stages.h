@@ -145,7 +145,11 @@ struct UmmaArgs {
     int P, I, I_s, H_s, rank, topk;
     const unsigned char* wpack;  // [E][NB][K / 256][stage bytes] packed weight image
     const unsigned char* bq;     // B rows: g1 xq [M, P/2]; g2 z [slots, I/2]
-    const unsigned char* bsf;    // their e4m3 scales: g1 x_sf [M, P/16]; g2 z_sfd [slots, I/16]
+    const unsigned char* bsf;    // their e4m3 scales: g1 x_sf [M, P/16]; g2 z_sfd [slots, I/16], or with `bex` the raw z_sf
+    const signed char* bex;      // g2: the h planes' group exponents z_ex [slots, I/16]: the stager then forms the row view
+                                 // itself (row exponent = the largest of the slot's exponents, every scale byte moved to it,
+                                 // row scale 2^e_row) and no h-row kernel runs; null: bsf / rowscale hold the view
+    XchgWait wait;               // g2 with bex: the h planes of every rank
     const float* x_scale;        // g1
     const float* g1_alphas;
     const float* g1_scale_c;
@@ -377,6 +381,7 @@ struct FusedArgs {
     unsigned* meet_count;       // [3][16] arrivals per row of the three meetings, only grow
     int tiles0[2];              // tiles of each stage's first GEMM
     int router_tiles;
+    int router_contribs;        // CTAs that hold a K range of a router tile, over all its tiles (each arrives once per launch)
     // exchanges fed per finished tile: stage 0's first GEMM (sig0), stage 1's first GEMM (sig1); flag words of the fused
     // protocol in every receiving rank's flag block
     XchgSignal sig0, sig1;

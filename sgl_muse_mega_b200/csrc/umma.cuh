@@ -61,6 +61,20 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
                  : "memory");
 }
 
+// The same with an L2 cache policy. Weights are read once per step: streamed evict-first, they do not push the activations,
+// partial sums, exchange buffers and the kernels' own instructions out of L2.
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void bulk_g2s_hint(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+                 : "memory");
+}
+
 // ---- tensor memory ----
 // One full warp allocates `cols` columns (power of two >= 32) and writes the base address to shared memory.
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {

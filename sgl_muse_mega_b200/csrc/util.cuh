@@ -139,6 +139,19 @@ __device__ __forceinline__ uint32_t float_to_e4m3(float x) {
     return (uint32_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
 }
 
+// An e4m3 scale byte times 2^-delta (delta >= 0): exponent-field move while the result stays normal, round half up on the
+// subnormal grid (the h-row view of the experts' second GEMM: every group's scale is moved to the row's largest exponent;
+// test/reference/muse_spark.py:447-491).
+__device__ __forceinline__ uint32_t scale_down_byte(uint32_t byte, int delta) {
+    const int ef = (int)(byte >> 3);
+    if (ef > delta) return byte - ((uint32_t)delta << 3);
+    const uint32_t sig = (byte & 7u) | (ef != 0 ? 8u : 0u);
+    int sh = delta - ef + (ef != 0 ? 1 : 0);
+    sh = min(max(sh, 0), 8);
+    const uint32_t half = sh > 0 ? (1u << (sh - 1)) : 0u;
+    return (sig + half) >> sh;
+}
+
 // ---- mma.sync ----
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,

@@ -74,10 +74,13 @@ def test_pack_only_bind_and_refusals(lib):
     rank = L.LayerRank(lib, None, case, 0, torch.device("cpu"), packed=0)
     rec = rank.bind(fused=2)
     info = rec.info()
-    assert info.kernels == 14 and info.grid > 0 and info.smem > 0  # 17 stage slots; top-k + tables + nq share a launch, the row ops ride the qkv GEMM
+    # 17 stage slots; top-k + tables + nq share a launch, the row ops ride the qkv GEMM, the h-row view the tensor-core g2
+    assert info.kernels == 13 and info.grid > 0 and info.smem > 0
     # the fused form on request: attention x 2, segment A, g1, h row, g2, segment B
     # default: the GEMMs on the item engine, pooler + router in one launch
-    assert rank.bind().info().kernels == 13 and rank.bind(fused=1).info().kernels == 7
+    assert rank.bind().info().kernels == 12 and rank.bind(fused=1).info().kernels == 6
+    plain = L.LayerRank(lib, None, case, 0, torch.device("cpu"), packed=0, tensor_cores=False)
+    assert plain.bind().info().kernels == 13  # CUDA-core experts keep the h-row kernel
     with pytest.raises(RuntimeError, match="pack-only"):
         rec(0, False)
     # a missing operand is named
@@ -88,13 +91,13 @@ def test_pack_only_bind_and_refusals(lib):
 
 def test_tile_images_bind_on_the_tensor_core_engine_only(lib):
     """The default layout of the dense weights is the tile image of the tensor-core engine (dense_packed 2): it binds the
-    per-stage launch list (13 kernels) or the two fused kernels (7), and refuses the cluster split-K form."""
+    per-stage launch list (12 kernels) or the two fused kernels (6), and refuses the cluster split-K form."""
     cfg, kw = CASES["small_fp4_swa_tp2"]
     case = synthetic.layer_case(cfg, **kw)
     rank = L.LayerRank(lib, None, case, 0, torch.device("cpu"))
     assert rank.packed == 2 and rank.w["o_proj"].dtype == torch.uint8 and rank.w["o_proj"].shape[2:] == (2, 128, 128)
-    assert rank.bind().info().kernels == 13
-    assert rank.bind(fused=1).info().kernels == 7  # the two fused tensor-core kernels around the experts
+    assert rank.bind().info().kernels == 12
+    assert rank.bind(fused=1).info().kernels == 6  # the two fused tensor-core kernels around the experts
     with pytest.raises(RuntimeError, match="dense_packed 2"):
         rank.bind(fused=2)
 
@@ -109,7 +112,7 @@ def test_expert_range_binds_whole_experts_only(lib):
     rank = L.LayerRank(lib, None, case, 0, torch.device("cpu"), expert_range=(4, 8))
     assert rank.w["gate_q"].shape[0] == 4 and rank.w1_pack.shape[0] == 4 and rank.w["expert_bias"].shape[0] == 16
     rec = rank.bind()
-    assert rec.info().kernels == 13
+    assert rec.info().kernels == 12
     for lo, hi in ((4, 4), (8, 4), (0, 17), (-1, 4)):
         rank.expert_lo, rank.expert_hi = lo, hi
         with pytest.raises(RuntimeError, match="expert range"):

@@ -137,7 +137,7 @@ def test_fused_layer_parity(name, device):
     world = L.LayerWorld(case, device, packed=0)
     rank = world.ranks[0]
     rank.bind(world.ranks, fused=True)
-    assert rank.launch_record.info().kernels == 7
+    assert rank.launch_record.info().kernels == 7 - int(rank.tensor_cores)  # the tensor-core g2 forms the h-row view itself
     rank.launch(torch.cuda.current_stream().cuda_stream, pdl=True)
     torch.cuda.synchronize()
     assert rank.launch_record.status(torch.cuda.current_stream().cuda_stream).code == 0
@@ -156,7 +156,9 @@ def test_fused_matches_per_stage_kernels_on_a_lone_rank(name, device):
     for form in (2, 0, 1):
         rank = L.LayerRank(host_lib(), _module(device), case, 1, device, packed=0)
         rank.bind(None, fused=form)
-        assert rank.launch_record.info().kernels == {2: 14 - drop, 0: 13 - drop, 1: 7 - (1 if case.bf16 else 0)}[form]
+        hrow = 0 if case.bf16 or rank.tensor_cores else 1  # the h-row kernel: CUDA-core NVFP4 experts only
+        assert rank.launch_record.info().kernels == {2: 13 + hrow - (1 if case.tail else 0), 0: 12 + hrow - (1 if case.tail else 0),
+                                                     1: 6 + hrow}[form]
         rank.launch(torch.cuda.current_stream().cuda_stream, pdl=True)
         torch.cuda.synchronize()
         assert rank.launch_record.status(torch.cuda.current_stream().cuda_stream).code == 0
@@ -262,7 +264,7 @@ def test_fused_tensor_core_layer_parity(name, device):
     rank = world.ranks[0]
     assert rank.packed == 2
     rank.bind(world.ranks, fused=True)
-    assert rank.launch_record.info().kernels == 7
+    assert rank.launch_record.info().kernels == 6
     s = torch.cuda.current_stream().cuda_stream
     rank.launch(s, pdl=True)
     torch.cuda.synchronize()
