@@ -37,8 +37,12 @@ def parse():
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--config", type=int, default=1, choices=(1, 2, 3, 4),
+                    help="BASELINE.json configuration: 1 (default) one full-shape layer, M=16, ctx 8192, plus the whole-step leg; "
+                         "2 the isolated NVFP4 expert block, M in {1,4,8,16} x EP in {1,2,4,8}; 3 the whole model at a 200-token "
+                         "context generating 256 tokens; 4 the same at a 131072-token context generating 64 tokens")
     ap.add_argument("--ring", type=int, default=8, help="distinct layers in the ring")
-    ap.add_argument("--ctx", type=int, default=8192)
+    ap.add_argument("--ctx", type=int, default=None, help="context length (default: the configuration's)")
     ap.add_argument("--rows", type=int, default=16)
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--cpu-sample-experts", type=int, default=24)
@@ -56,7 +60,13 @@ def parse():
     ap.add_argument("--top-k", type=int, default=1 << 30)
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--accept", type=int, default=5, help="forced accept length of the whole-step leg (5 drafts + the bonus = 6 tokens a step)")
-    return ap.parse_args()
+    args = ap.parse_args()
+    if args.ctx is None:
+        args.ctx = {1: 8192, 2: 16, 3: 200, 4: 131072}[args.config]
+    if args.config in (3, 4):  # generated tokens / committed tokens per step, rounded up
+        commit = args.accept + 1
+        args.decode_steps = -(-(256 if args.config == 3 else 64) // commit)
+    return args
 
 
 # DRAM traffic of the g1 expert kernel from its ncu capture (profiles/experts_umma_kernel_config1_full.md): 238.46 MB read +
@@ -158,11 +168,12 @@ def cpu_layer_sample(args, threads: int, repeats: int = 1) -> dict:
     times = []
     for _ in range(repeats):
         t0 = time.perf_counter()
-        O.run_layer(layers, cfg.node_ranks)
+        out = O.run_layer(layers, cfg.node_ranks)
         times.append(time.perf_counter() - t0)
     wall = statistics.median(times)
     return {
         "wall_s": wall,
+        "distinct_experts": int(torch.unique(out[0]["ids"]).numel()),
         "us_per_rank_layer": wall / cfg.tp * 1e6,
         "sample": f"1 full-shape layer, all {cfg.tp} rank slices of the TP8 world, M={args.rows}, ctx={args.ctx}, routing "
         f"confined to {args.cpu_sample_experts} experts; value = wall / {cfg.tp} ranks; median of {repeats}",
@@ -181,7 +192,11 @@ def run_reference(args) -> None:
         "impl": "reference", "metric": METRIC, "value": v, "unit": "us", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": v / 1e3, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
         "dtype": "nvfp4 weights x nvfp4/bf16 activations, f64 accumulate (CPU oracle)", "data": "synthetic",
-        "config": {"workload": WORKLOAD},
+        "config": {"workload": WORKLOAD, "rows": args.rows, "ctx": args.ctx, "distinct_experts_per_layer": [r["distinct_experts"]],
+                   "note": "the CPU arm confines routing to a hot subset of experts (its weights must fit host memory and the run a "
+                           "few seconds): it does LESS expert work than the GPU arm's ~100 distinct experts, so the GPU / CPU "
+                           "ratio is a lower bound; the port is bit-exact against the reference's test/reference/muse_spark.py "
+                           "on the committed golden cases"},
         "cpu_baseline": {"value": v, "unit": "us", "cores": threads, "kind": "port", "sample": r["sample"]},
         "e2e": {"value": v, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": time.perf_counter() - t0,
@@ -296,6 +311,35 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
         e1.record(stream)
     barrier()
     layer_us = max_over_ranks(e0.elapsed_time(e1) / (reps * n_layers) * 1e3)
+    # ---- per attention type: every layer between its own events (one pass), and a global layer's attention stages alone ----
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_layers + 1)]
+    with torch.cuda.stream(stream):
+        evs[0].record(stream)
+        for j, lr in enumerate(st.layers):
+            lr.launch(s, True)
+            evs[j + 1].record(stream)
+    barrier()
+    per_layer = [evs[j].elapsed_time(evs[j + 1]) * 1e3 for j in range(n_layers)]
+    kinds = {"swa_nvfp4": [t for t, lr in zip(per_layer, st.layers) if not lr.case.global_attn and not lr.case.bf16],
+             "global_nvfp4": [t for t, lr in zip(per_layer, st.layers) if lr.case.global_attn and not lr.case.bf16],
+             "bf16_experts": [t for t, lr in zip(per_layer, st.layers) if lr.case.bf16]}
+    layer_kinds = {k: round(max_over_ranks(sum(v) / len(v)), 1) for k, v in kinds.items() if v}
+    attn = None
+    glob = [lr for lr in st.layers if lr.case.global_attn and not lr.case.bf16][:8]
+    if glob and world == 1:  # stage stepping is for one process: the exchanges of a world need every rank in step
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in glob]
+        with torch.cuda.stream(stream):
+            for lr, (a, b) in zip(glob, pairs):
+                a.record(stream)
+                lr.launch_record.step(s, 0, 2)  # split + merge
+                b.record(stream)
+        barrier()
+        us = sum(a.elapsed_time(b) for a, b in pairs) / len(pairs) * 1e3
+        keys = int(st.feeds.kv_len.item())
+        kv_bytes = 2 * keys * cfg.kv_row_bytes
+        attn = {"us": round(us, 1), "keys": keys, "kv_bytes": kv_bytes, "gb_s": round(kv_bytes / (us * 1e-6) / 1e9, 1),
+                "frac_of_hbm": round(kv_bytes / (us * 1e-6) / 1e9 / peaks()[0], 3),
+                "note": "attention split + merge of a global layer between events (includes two event records, ~5 us)"}
     # ---- the draft alone (its launch list under programmatic dependent launch) ----
     draft = None
     if it is not None:
@@ -341,10 +385,11 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
             scale = 2.0 / 0.5625
             b["total"] += int((b["g1"] + b["g2"]) * (scale - 1))
     out = {
-        "layers": n_layers, "accept_len": args.accept, "tokens_per_step": commit, "ms_per_step": step_ms,
+        "layers": n_layers, "steps": K, "accept_len": args.accept, "tokens_per_step": commit, "ms_per_step": step_ms,
         "tok_s": commit / (step_ms * 1e-3), "e2e_ms_per_step": e2e_ms, "e2e_tok_s": commit / (e2e_ms * 1e-3),
         "h2d_bytes_per_step": h_tokens.numel() * 8 if it is None else 4, "d2h_bytes_per_step": 64,
-        "layer_only_us": layer_us, "kernels_per_step": it.kernels if it is not None else st.kernels,
+        "layer_only_us": layer_us, "layer_us_by_kind": layer_kinds, "global_attention": attn, "ctx": args.ctx,
+        "kernels_per_step": it.kernels if it is not None else st.kernels,
         "bytes_per_step": int(sum(b["total"] for b in byts)), "mean_distinct_experts": sum(d_list) / len(d_list),
         "present_ranks": world if world > 1 else 1, "model_ranks": cfg.tp,
         "draft": draft if draft is not None else "not in the step (--no-draft): ids come from the host",
@@ -355,6 +400,30 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
         assert bad == [], f"device status of the draft: {bad}"
     del peers
     return out, st
+
+
+def decode_line(args, cfg, dec: dict, world: int, clocks) -> dict:
+    """The JSON line of configs[3] / configs[4]: decode tokens per second of the whole fused iteration at the forced accept
+    length, the model's TP8 slice per GPU (ranks 0 .. world - 1 of the TP8 world present)."""
+    peak, peak_kind = peaks()
+    n_layers = dec["layers"]
+    gen = 256 if args.config == 3 else 64
+    what = (f"configs[{args.config}]: full-shape 62-layer model + DFlash2 draft, TP8 slice per GPU on {world} B200(s), "
+            f"{args.ctx}-token context (KV filled directly: no prefill path here), {gen} generated tokens, block 16, "
+            f"forced accept {args.accept} (commit {args.accept + 1} a step)")
+    layer_gbs = dec["bytes_per_step"] / (dec["layer_only_us"] * n_layers * 1e-6) / 1e9
+    return {
+        "metric": "batch-1 decode tok/s at fixed accept len", "value": dec["tok_s"], "unit": "tok/s", "n_gpus": world,
+        "steps": dec["steps"], "warmup": 3, "ms_per_step": dec["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "nvfp4 experts (e2m1 x e4m3 block scales), bf16 dense, f32 accumulate", "data": "synthetic",
+        "config": {"workload": what, "rows": args.rows, "ctx": args.ctx, "l2": "inputs larger than L2 (every layer of the model is distinct)",
+                   "kernels_per_step": dec["kernels_per_step"]},
+        "roofline": {"bound": "hbm", "kernel": "whole step's layers", "achieved": layer_gbs, "peak": peak, "unit": "GB/s",
+                     "frac": layer_gbs / peak, "traffic": None, "peak_kind": peak_kind},
+        "e2e": {"value": dec["e2e_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": dec["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": dec["d2h_bytes_per_step"]},
+        "gpu_launches": dec["kernels_per_step"] * (2 * dec["steps"] + 7), "decode": dec, "clocks": clocks, "cpu_baseline": None,
+    }  # fmt: skip
 
 
 def draft_bytes(dcfg, ranks: int, rows: int) -> int:
@@ -395,6 +464,12 @@ def run_ours(args) -> None:
     if world > 1:
         run_world(args, cfg, lib, module, device, rank, world, local)
         dist.destroy_process_group()
+        return
+    if args.config in (3, 4):
+        stream = torch.cuda.Stream(device)
+        sampler = ClockSampler(local)
+        dec, _st = decode_leg(args, cfg, lib, module, device, rank, world, stream)
+        print(json.dumps(decode_line(args, cfg, dec, world, sampler.stop())), flush=True)
         return
     # a ring of distinct layers: global iff i % 4 == 3 here (3 swa : 1 global). Each GPU holds the slice of TP rank
     # `rank % 8`; with N GPUs the ranks are independent replicas of the per-GPU work (no exchange partner is waited for).
@@ -591,6 +666,11 @@ def run_world(args, cfg, lib, module, device, rank: int, world: int, local: int)
     sampler = ClockSampler(local) if rank == 0 else None
     assert args.decode_layers > 0, "the multi-GPU run times the layers of the whole-step leg"
     dec, st = decode_leg(args, cfg, lib, module, device, rank, world, stream)
+    if args.config in (3, 4):
+        clocks = sampler.stop() if sampler else None
+        if rank == 0:
+            print(json.dumps(decode_line(args, cfg, dec, world, clocks)), flush=True)
+        return
     n_layers = dec["layers"]
     peak, peak_kind = peaks()
     # the dominant kernel (g1) between events, every rank stepping the same stages in the same order
@@ -645,10 +725,69 @@ def run_world(args, cfg, lib, module, device, rank: int, world: int, local: int)
         print(json.dumps(line), flush=True)
 
 
+def run_expert_block(args) -> None:
+    """configs[2]: the isolated NVFP4 expert block at the full expert shape (256 experts x 28.31 MB), M in {1, 4, 8, 16}
+    rows, experts partitioned over EP in {1, 2, 4, 8} ranks. One GPU: the ranks' launches run one after the other on it (a
+    rank's time is what its GPU would take; the block's time is the slowest rank's). Reports the achieved HBM GB/s of the
+    routed experts' weight bytes, L2 flushed before every sample."""
+    import torch
+
+    from sgl_muse_mega_b200.common import host
+    from sgl_muse_mega_b200.muse_spark.b200 import expert_block as X
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device: there is no CPU fallback"
+    assert int(os.environ.get("WORLD_SIZE", "1")) == 1, "--config 2 emulates the expert-parallel ranks on one GPU"
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    lib = host.library()
+    module = lib.load()
+    sampler = ClockSampler(0)
+    cfg = X.block_config()
+    full = X.draw_case(cfg, 16, device, seed=args.seed)
+    peak, peak_kind = peaks()
+    sweep, launches = [], 0
+    iters = max(3, min(args.steps, 10))
+    for rows in (1, 4, 8, 16):
+        case = X.with_rows(full, rows)
+        for ep in (1, 2, 4, 8):
+            blk = X.ExpertBlock(case, device, ep=ep, lib=lib, module=module)
+            blk.run()
+            torch.cuda.synchronize()
+            assert not any(blk.statuses()), blk.statuses()
+            d = blk.local_experts()
+            us = blk.time_experts(iters)
+            launches += 2 * ep * (iters + 2)
+            slow = max(range(ep), key=lambda r: us[r])
+            sweep.append({"rows": rows, "ep": ep, "distinct_experts": d, "us": [round(t, 1) for t in us],
+                          "gb_s": [round(n * X.EXPERT_BYTES / (t * 1e-6) / 1e9, 1) if n else None for n, t in zip(d, us)],
+                          "block_us": round(us[slow], 1),
+                          "block_gb_s": round(sum(d) * X.EXPERT_BYTES / (us[slow] * 1e-6) / 1e9, 1)})  # fmt: skip
+            del blk
+            torch.cuda.empty_cache()
+    head = next(x for x in sweep if x["rows"] == 16 and x["ep"] == 1)
+    gbs = head["block_gb_s"]
+    line = {
+        "metric": "isolated NVFP4 expert block: achieved HBM GB/s of the routed experts' weight bytes", "value": gbs, "unit": "GB/s",
+        "n_gpus": 1, "steps": iters, "warmup": 2, "ms_per_step": head["block_us"] / 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "nvfp4 experts (e2m1 x e4m3 block scales), f32 accumulate", "data": "synthetic",
+        "config": {"workload": "configs[2]: isolated NVFP4 expert block, full expert shape, M in {1,4,8,16}, EP in {1,2,4,8} "
+                               "(ranks run one after the other on 1 B200)", "l2": "flushed before every sample (512 MB write)",
+                   "headline": "M=16, EP=1"},
+        "roofline": {"bound": "hbm", "kernel": "experts_umma_kernel<g1> + <g2>", "achieved": gbs, "peak": peak, "unit": "GB/s",
+                     "frac": gbs / peak, "traffic": None, "peak_kind": peak_kind},
+        "sweep": sweep, "gpu_launches": launches, "clocks": sampler.stop(), "cpu_baseline": None,
+        "e2e": {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "note": "the block has no host-facing call of its own: the layer launch of --config 1 is the end-to-end path"},
+    }  # fmt: skip
+    print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+    elif args.config == 2:
+        run_expert_block(args)
     else:
         run_ours(args)
 

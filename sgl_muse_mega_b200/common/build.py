@@ -80,22 +80,6 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
-def build_variant(name: str, defines: list) -> Path:
-    """A second library ``lib/libmk_<name>.so`` from the same sources with extra ``-D`` macros (the trace builds that
-    stamp the global timer at stage boundaries); the shipped library is untouched."""
-    LIB_DIR.mkdir(exist_ok=True)
-    out = LIB_DIR / f"libmk_{name}.so"
-    deps = list(CSRC.glob("*")) + list(INCLUDE.glob("*.h"))
-    if out.exists() and all(p.stat().st_mtime <= out.stat().st_mtime for p in deps):
-        return out
-    cmd = [nvcc(), "-shared", "--cudart", "static", *DEVICE_FLAGS, *[f"-D{d}" for d in defines], "-I", str(INCLUDE),
-           "-o", str(out), *map(str, sources())]  # fmt: skip
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if r.returncode != 0:
-        raise RuntimeError(f"nvcc failed:\n{r.stdout}\n{r.stderr}")
-    return out
-
-
 if __name__ == "__main__":
     import sys
 

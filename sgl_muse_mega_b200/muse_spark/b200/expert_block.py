@@ -11,15 +11,13 @@ pair is computed by exactly one rank with the same kernels, tiles and order.
 ``MkLayerBind.expert_lo`` / ``expert_hi``, each keeping and packing its own experts only, all writing the same ``zb``).
 The stages run through the C ABI by index: pooler + router (the block's inputs: h rows ~ N(0, 1) against N(0, 1 / H)
 weights give pooled rows and router logits ~ N(0, 1)), routing + pre-expert norm + input quantisation, g1, h-row view,
-g2 on every rank, then one combine. Run as a module it times the expert kernels (g1, h-row, g2) of each rank between CUDA
-events with L2 flushed before every sample and prints one JSON line per (rows, ep).
+g2 on every rank, then one combine. ``time_experts`` times the expert kernels (g1, g2) of each rank between CUDA events with
+L2 flushed before every sample (``bench.py --config 2`` prints the sweep over rows and ranks).
 """
 
 from __future__ import annotations
 
-import argparse
 import dataclasses
-import json
 from typing import Optional
 
 import torch
@@ -100,7 +98,7 @@ class ExpertBlock:
         return [int(torch.unique(ids[(ids >= r * per) & (ids < (r + 1) * per)]).numel()) for r in range(self.ep)]
 
     def time_experts(self, iters: int = 10, flush_mb: int = 512) -> list:
-        """Median microseconds of g1 + h-row view + g2 per rank, L2 flushed before each sample."""
+        """Median microseconds of g1 + g2 (the h-row view rides g2's staging) per rank, L2 flushed before each sample."""
         s = torch.cuda.current_stream(self.device)
         flush = torch.empty(flush_mb << 20, dtype=torch.uint8, device=self.device)
         out = []
@@ -116,36 +114,3 @@ class ExpertBlock:
                 ts.append(a.elapsed_time(b) * 1e3)
             out.append(sorted(ts[2:])[len(ts[2:]) // 2])
         return out
-
-
-def main() -> None:
-    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("--rows", type=int, nargs="+", default=[1, 4, 8, 16])
-    ap.add_argument("--ep", type=int, nargs="+", default=[1, 2, 4, 8])
-    ap.add_argument("--iters", type=int, default=10)
-    args = ap.parse_args()
-    device = torch.device("cuda:0")
-    torch.cuda.set_device(device)
-    lib = host.library()
-    module = lib.load()
-    cfg = block_config()
-    full = draw_case(cfg, max(args.rows), device)
-    for rows in args.rows:
-        case = with_rows(full, rows)
-        for ep in args.ep:
-            blk = ExpertBlock(case, device, ep=ep, lib=lib, module=module)
-            blk.run()
-            torch.cuda.synchronize()
-            assert not any(blk.statuses()), blk.statuses()
-            d = blk.local_experts()
-            us = blk.time_experts(args.iters)
-            gbs = [round(n * EXPERT_BYTES / (t * 1e-6) / 1e9, 1) if n else None for n, t in zip(d, us)]
-            slow = max(range(ep), key=lambda r: us[r])
-            print(json.dumps({"rows": rows, "ep": ep, "distinct_experts": d, "us": [round(t, 1) for t in us], "gb_s": gbs,
-                              "block_us": round(us[slow], 1), "block_gb_s": round(sum(d) * EXPERT_BYTES / (us[slow] * 1e-6) / 1e9, 1)}))  # fmt: skip
-            del blk
-            torch.cuda.empty_cache()
-
-
-if __name__ == "__main__":
-    main()

@@ -17,7 +17,14 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REF = Path(os.environ.get("MUSE_REFERENCE", "/root/reference"))
+
+
+def reference_checkout() -> Path:
+    """The reference checkout this script imports read-only: named by the environment, never assumed."""
+    if "MUSE_REFERENCE" not in os.environ:
+        raise SystemExit("set MUSE_REFERENCE to the reference checkout (this script imports its oracle read-only)")
+    return Path(os.environ["MUSE_REFERENCE"])
+
 
 SEED, ROWS, VOCAB, CASES = 4242, 16, 1000, 12
 
@@ -41,6 +48,7 @@ def draw_case(i: int):
 
 
 def main() -> None:
+    REF = reference_checkout()
     sys.path[:0] = [str(REPO), str(REF), str(REF / "test")]
     from reference import dflash2 as R2  # the reference's DFlash2 oracle
 

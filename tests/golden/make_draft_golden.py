@@ -19,7 +19,14 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REF = Path(os.environ.get("MUSE_REFERENCE", "/root/reference"))
+
+
+def reference_checkout() -> Path:
+    """The reference checkout this script imports read-only: named by the environment, never assumed."""
+    if "MUSE_REFERENCE" not in os.environ:
+        raise SystemExit("set MUSE_REFERENCE to the reference checkout (this script imports its oracle read-only)")
+    return Path(os.environ["MUSE_REFERENCE"])
+
 
 # (name, ranks, rows, pos, commit, seed): a window that clips the history (pos > sliding window) and one that does not
 CASES = [("tp2_b16", 2, 16, 40, 7, 1), ("tp1_b8", 1, 8, 12, 3, 2), ("tp4_b16", 4, 16, 33, 16, 3)]
@@ -37,6 +44,7 @@ def small_cfg():
 
 
 def main() -> None:
+    REF = reference_checkout()
     sys.path[:0] = [str(REPO), str(REF), str(REF / "test")]
     from reference import dflash2 as R2  # the reference's DFlash2 oracle
 

@@ -1,9 +1,8 @@
 """Generates the golden fixtures of ``tests/golden/*.pt`` from the REFERENCE's own torch oracle.
 
-Run once, in a container where the reference checkout is mounted (its location: ``REF`` below, or the environment
-variable ``MUSE_REFERENCE``):
+Run once, in a container where the reference checkout is mounted (the environment variable ``MUSE_REFERENCE`` names it):
 
-    python tests/golden/make_golden.py
+    MUSE_REFERENCE=<checkout> python tests/golden/make_golden.py
 
 It imports the reference's ``test/reference/muse_spark.py`` read-only, draws the seeded synthetic layer cases of
 ``sgl_muse_mega_b200.muse_spark.b200.synthetic``, repacks their plain tensors into the reference's kernel layouts with the
@@ -22,7 +21,15 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REF = Path(os.environ.get("MUSE_REFERENCE", "/root/reference"))
+
+
+def reference_checkout() -> Path:
+    """The reference checkout this script imports read-only: named by the environment, never assumed."""
+    if "MUSE_REFERENCE" not in os.environ:
+        raise SystemExit("set MUSE_REFERENCE to the reference checkout (this script imports its oracle read-only)")
+    return Path(os.environ["MUSE_REFERENCE"])
+
+REF = reference_checkout()
 sys.path[:0] = [str(REPO), str(REF), str(REF / "test")]
 
 from reference import muse_spark as R  # noqa: E402  (the reference's oracle)

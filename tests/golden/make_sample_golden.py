@@ -19,7 +19,14 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REF = Path(os.environ.get("MUSE_REFERENCE", "/root/reference"))
+
+
+def reference_checkout() -> Path:
+    """The reference checkout this script imports read-only: named by the environment, never assumed."""
+    if "MUSE_REFERENCE" not in os.environ:
+        raise SystemExit("set MUSE_REFERENCE to the reference checkout (this script imports its oracle read-only)")
+    return Path(os.environ["MUSE_REFERENCE"])
+
 
 VOCAB, ROWS, CANDS = 512, 16, 16
 # (name, temperature, top_k, top_p, block, boost of the drafted token's target logit, logit grid or 0, seed)
@@ -53,6 +60,7 @@ def draw(seed: int, boost: float, grid: float):
 
 
 def main() -> None:
+    REF = reference_checkout()
     sys.path[:0] = [str(REPO), str(REF), str(REF / "test")]
     from reference import dflash2 as R2  # the reference's DFlash2 oracle
 
