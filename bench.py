@@ -398,8 +398,105 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
     if it is not None:
         bad = it.statuses()
         assert bad == [], f"device status of the draft: {bad}"
+    if world > 1:
+        # every present rank ends the run with the same step state, bit for bit: the gathered logits, the arg-max, the step
+        # words, the window's ids and the residuals the draft captured
+        state = {"logits": st.gathered, "top1": st.accept.top1, "words": st.accept.words, "tokens": st.tokens}
+        if it is not None:
+            state["capture_residuals"] = torch.stack([st.layers[c].o["stream_out"] for c in it.capture])
+        out["ranks_equal"] = ranks_equal(state, world)
     del peers
     return out, st
+
+
+def ranks_equal(state: dict, world: int) -> dict:
+    """All-gathers the named tensors and compares every rank's copy with rank 0's bit for bit: name -> equal."""
+    import torch
+    import torch.distributed as dist
+
+    res = {}
+    for name, t in state.items():
+        t = t.contiguous()
+        got = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(got, t)
+        res[name] = all(torch.equal(g.view(torch.uint8), got[0].view(torch.uint8)) for g in got[1:])
+    return res
+
+
+def parity_world(args, lib, module, device, rank: int, world: int) -> dict:
+    """The world of ``world`` processes against the same world emulated on one GPU (every rank's launches interleaved in
+    one process, rank 0's GPU), on a 4-layer model of tensor-parallel width ``world``: three verify steps as CUDA graph
+    replays, after each the step words, the arg-max and the gathered logits of every rank all-gathered and compared bit
+    for bit with the emulated ranks' (the fused form's GEMMs sum in another fixed order: its logits are held to a relative
+    distance instead, its ranks to each other bit for bit)."""
+    import torch
+    import torch.distributed as dist
+
+    from sgl_muse_mega_b200.common import symm
+    from sgl_muse_mega_b200.muse_spark.b200 import stack as S
+    from sgl_muse_mega_b200.muse_spark.b200 import synthetic
+    from sgl_muse_mega_b200.muse_spark.config import Config
+
+    cfg = Config(hidden=1024, q_heads=64, kv_heads=8, experts=16, topk=8, moe_hidden=1024, moe_inter=1024, swa_window=7,
+                 vocab=4096, layers=4, bf16_moe_layers=(0,), tp=world, node_ranks=min(4, world))  # fmt: skip
+    rows, ctx, steps, accept = 16, 24, 3, 6
+    fused = args.form == 4
+    gen = torch.Generator().manual_seed(31)
+    ids = [torch.randint(0, cfg.vocab, (rows,), generator=gen) for _ in range(steps)]
+    case = synthetic.stack_case(cfg, n_layers=4, rows=rows, ctx=ctx, seed=21, only_ranks=[rank])
+    forced = torch.tensor([accept], dtype=torch.int32, device=device)
+    arena = symm.Arena(lib, S.exchange_layout(cfg, rows), device)
+    st = S.Stack(case, rank, device, lib, module, arena=arena, accept_override=forced, wait_budget=1 << 25, fused=fused)
+    peers = S.connect_world(st)
+    st.feeds.launch(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    st.capture(warmup=False)
+    names = ("words", "top1", "logits")
+    got = []  # per step: name -> every rank's copy
+    for t in ids:
+        st.tokens.copy_(t)
+        st.step()
+        torch.cuda.synchronize()
+        mine = {"words": st.accept.words, "top1": st.accept.top1, "logits": st.gathered}
+        step = {}
+        for k in names:
+            every = [torch.empty_like(mine[k]) for _ in range(world)]
+            dist.all_gather(every, mine[k].contiguous())
+            step[k] = [e.cpu() for e in every]
+        got.append(step)
+    status = st.statuses()
+    dist.barrier()
+    del peers
+    res = None
+    if rank == 0:
+        whole = synthetic.stack_case(cfg, n_layers=4, rows=rows, ctx=ctx, seed=21)
+        w = S.StackWorld(whole, device, lib, accept_override=forced)
+        mismatch, worst = [], 0.0
+        for i, t in enumerate(ids):
+            for e in w.ranks:
+                e.tokens.copy_(t)
+            w.run_interleaved(feeds=i == 0)
+            torch.cuda.synchronize()
+            for r, e in enumerate(w.ranks):
+                ref = {"words": e.accept.words.cpu(), "top1": e.accept.top1.cpu(), "logits": e.gathered.cpu()}
+                for k in names:
+                    a = got[i][k][r]
+                    if not torch.equal(a, got[i][k][0]):
+                        mismatch.append(f"step {i}: rank {r}'s {k} differ from rank 0's")
+                    if fused:
+                        if k == "logits":
+                            worst = max(worst, float((a - ref[k]).norm() / ref[k].norm()))
+                    elif not torch.equal(a, ref[k]):
+                        mismatch.append(f"step {i}: rank {r}'s {k} differ from the emulated world's")
+        emu_status = [x for e in w.ranks for x in e.statuses()]
+        res = {"model": "4 layers (one with bf16 experts), hidden 1024, 16 experts, vocab 4096, tensor-parallel over the ranks",
+               "steps": steps, "compared": list(names), "bit_equal": not mismatch and not fused, "mismatch": mismatch[:8],
+               "status": [str(x) for x in status + emu_status]}  # fmt: skip
+        if fused:
+            res["ranks_bit_equal"] = not mismatch
+            res["logits_rel_to_per_stage_world"] = worst
+            res["note"] = "the fused form sums its GEMMs in another fixed order than the emulated world's per-stage kernels"
+    return res
 
 
 def decode_line(args, cfg, dec: dict, world: int, clocks) -> dict:
@@ -624,24 +721,43 @@ def run_ours(args) -> None:
         r = cpu_layer_sample(args, threads, repeats=3)
         cpu = {"value": r["us_per_rank_layer"], "unit": "us", "cores": threads, "kind": "port", "sample": r["sample"]}
     if rank == 0:
+        # The line's value is the same quantity at every N: the mean layer of the whole-step leg's 62-layer model (60 NVFP4
+        # layers, 3 sliding-window : 1 global, and the two bf16-expert layers), eager launches with programmatic dependent
+        # launch. The ring of eight NVFP4 layers above stays in the line as ``ring_layer_us`` (and is the value when the
+        # whole-step leg is skipped).
+        value, timed = us_layer, f"a ring of {args.ring} distinct NVFP4 layers, eager with programmatic dependent launch"
+        value_gbs, value_bytes = layer_gbs, int(total_bytes / args.steps)
+        e2e = {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+        if dec is not None:
+            n_dec = dec["layers"]
+            value, timed = dec["layer_only_us"], "the layer launches of the whole-step leg, eager with programmatic dependent launch"
+            value_bytes = dec["bytes_per_step"] // n_dec
+            value_gbs = value_bytes / (value * 1e-6) / 1e9
+            e2e = {"value": dec["e2e_ms_per_step"] * 1e3 / n_dec, "unit": "us", "h2d_bytes_per_step": dec["h2d_bytes_per_step"],
+                   "d2h_bytes_per_step": dec["d2h_bytes_per_step"],
+                   "note": "whole fused iteration through the CUDA graph with the host's control word in and the step words out, divided by its layers",
+                   "layer_call": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                                  "note": "one layer launch through the C-ABI with its host rows in and out"}}  # fmt: skip
         line = {
-            "metric": METRIC, "value": us_layer, "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": us_layer / 1e3, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "metric": METRIC, "value": value, "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": value / 1e3, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
             "dtype": "nvfp4 experts (e2m1 x e4m3 block scales), bf16 dense, f32 accumulate", "data": "synthetic",
             "config": {
                 "workload": WORKLOAD, "rows": args.rows, "ctx": args.ctx, "ring_layers": args.ring,
-                "ring_bytes": int(sum(b["total"] for b in byt)), "l2": "inputs larger than L2 (ring of distinct layers)",
+                "ring_bytes": int(sum(b["total"] for b in byt)), "l2": "inputs larger than L2 (every layer of the model is distinct)",
                 "distinct_experts_per_layer": d_list, "multi_gpu": "independent replicas of the per-GPU slice" if world > 1 else "1 GPU",
-                "kernels_per_step": int(info.kernels),
+                "kernels_per_step": int(info.kernels), "timed": timed,
             },
-            "layer_roofline": {"bound": "hbm", "achieved": layer_gbs, "peak": peak, "unit": "GB/s", "frac": layer_gbs / peak,
-                               "bytes_per_layer": int(total_bytes / args.steps), "peak_kind": peak_kind},
+            "ring_layer_us": us_layer,
+            "ring_roofline": {"achieved": layer_gbs, "frac": layer_gbs / peak, "bytes_per_layer": int(total_bytes / args.steps)},
+            "layer_roofline": {"bound": "hbm", "achieved": value_gbs, "peak": peak, "unit": "GB/s", "frac": value_gbs / peak,
+                               "bytes_per_layer": value_bytes, "peak_kind": peak_kind},
             "roofline": {"bound": "hbm", "kernel": "experts_umma_kernel<g1>", "achieved": g1_gbs, "peak": peak, "unit": "GB/s",
                          "frac": g1_gbs / peak, "traffic": G1_TRAFFIC_RATIO * g1_bytes / len(pairs), "traffic_note": G1_TRAFFIC_NOTE,
                          "peak_kind": peak_kind,
                          "us_per_launch": sum(g1_ms) / k_steps * 1e3},
-            "e2e": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": int(info.kernels) * args.steps,
+            "e2e": e2e,
+            "gpu_launches": int(info.kernels) * args.steps + (dec["kernels_per_step"] * (2 * args.decode_steps + 7) if dec else 0),
             "stage_us_serialised": stage_us,
             "decode": dec,
             "segment_trace_us": seg_trace,
@@ -668,8 +784,13 @@ def run_world(args, cfg, lib, module, device, rank: int, world: int, local: int)
     dec, st = decode_leg(args, cfg, lib, module, device, rank, world, stream)
     if args.config in (3, 4):
         clocks = sampler.stop() if sampler else None
+        del st
+        torch.cuda.empty_cache()
+        emu = parity_world(args, lib, module, device, rank, world)
         if rank == 0:
-            print(json.dumps(decode_line(args, cfg, dec, world, clocks)), flush=True)
+            line = decode_line(args, cfg, dec, world, clocks)
+            line["parity_n"] = parity_n(world, dec, emu)
+            print(json.dumps(line), flush=True)
         return
     n_layers = dec["layers"]
     peak, peak_kind = peaks()
@@ -693,6 +814,9 @@ def run_world(args, cfg, lib, module, device, rank: int, world: int, local: int)
     g1_gbs = g1_bytes / (float(t.item()) * 1e-3) / 1e9
     assert st.statuses() == []
     clocks = sampler.stop() if sampler else None
+    del st, fp4, lr
+    torch.cuda.empty_cache()
+    emu = parity_world(args, lib, module, device, rank, world)
     if rank == 0:
         us_layer = dec["layer_only_us"]
         layer_gbs = dec["bytes_per_step"] / (us_layer * n_layers * 1e-6) / 1e9
@@ -718,11 +842,20 @@ def run_world(args, cfg, lib, module, device, rank: int, world: int, local: int)
                     "h2d_bytes_per_step": dec["h2d_bytes_per_step"], "d2h_bytes_per_step": dec["d2h_bytes_per_step"],
                     "note": "whole verify step through the CUDA graph with host ids in and step words out, divided by its layers"},
             "gpu_launches": dec["kernels_per_step"] * (2 * args.decode_steps + 7),
+            "parity_n": parity_n(world, dec, emu),
             "decode": dec,
             "clocks": clocks,
             "cpu_baseline": None,
         }  # fmt: skip
         print(json.dumps(line), flush=True)
+
+
+def parity_n(world: int, dec: dict, emu: dict) -> dict:
+    """The multi-GPU run's parity record: the timed model's end state equal on every rank, and the small model's world
+    equal to the same world emulated on one GPU."""
+    same = dec.get("ranks_equal") or {}
+    ok = bool(same) and all(same.values()) and bool(emu) and (emu["bit_equal"] or emu.get("ranks_bit_equal", False)) and not emu["status"]
+    return {"ranks": world, "bit_equal": ok, "timed_model_ranks_equal": same, "emulated_world": emu}
 
 
 def run_expert_block(args) -> None:

@@ -29,6 +29,9 @@ from .executor import Verify
 
 INDEX = "model.safetensors.index.json"
 BF16, F32 = torch.bfloat16, torch.float32
+# the target's built object of this process: the draft spec's build (``muse_spark/draft.py``) leaves the draft's weights
+# on it, the worker hooks (``runtime/iteration.py``) find it through the model (reference build.py ``TARGET``)
+TARGET: Optional[Verify] = None
 
 
 def alias_specs(model, cfg: Config) -> dict:
@@ -201,4 +204,13 @@ def build(model, hf_config, ctx, *, parallel=None, experts: Optional[Callable[[i
     arena = symm.Arena(lib, layout, device) if world > 1 else symm.LocalArena(layout, device)
     case = model_case(model, cfg, rank, device, block, experts)
     summary = f"TP{cfg.tp}, block {block}, sm_100a library {lib.path.name}; built in {time.perf_counter() - t0:.1f} s"
-    return Verify(cfg, block, case, lib, module, arena, model, rank, device, getattr(parallel, "device_group", None), summary)
+    global TARGET
+    TARGET = Verify(cfg, block, case, lib, module, arena, model, rank, device, getattr(parallel, "device_group", None), summary)
+    try:
+        model.built_megakernel = TARGET  # where the hooks of an SGLang without the binding module look it up
+    except AttributeError:
+        pass
+    from . import iteration  # the two hooks on SGLang's DFlash2 worker, before SGLang builds the worker
+
+    iteration.install()
+    return TARGET

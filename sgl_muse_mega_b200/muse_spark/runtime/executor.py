@@ -133,9 +133,20 @@ class Verify:
         self.kv_bound = _addresses(pools)
         r2t = getattr(view, "req_to_token_pool", None) or shim.req_to_token_pool()
         frame = dict(self.frame, req_to_token=r2t.req_to_token, full_to_swa=pool.full_to_swa_index_mapping)
+        # With the DFlash2 draft built, the stack also binds the accepts of the fused iteration (greedy and sampled, one set
+        # of step words) beside the soft cap of the plain verify step; SGLang's simulated acceptance becomes the accept's
+        # forced table.
+        extra = {}
+        if self.draft is not None:
+            from .iteration import simulated_accepts
+
+            table = simulated_accepts(self.block)
+            extra = dict(accept_too=True, sample_too=True, sampling=torch.zeros(4, dtype=torch.int64),
+                         accept_override=None if table is None else table.to(self.device), ring=4096,
+                         block_verify=bool(getattr(shim.server_spec(), "speculative_use_block_verification", True)))  # fmt: skip
         self.stack = S.Stack(self.case, self.rank, self.device, self.lib, self.module, arena=self.arena, greedy=False,
                              keep_plain_experts=False, frame=frame, pools=pools, wait_budget=WAIT_BUDGET,
-                             shared_status=True)  # fmt: skip
+                             shared_status=True, identity_slots=False, **extra)  # fmt: skip
         if cfg.tp > 1:
             self.peers = S.connect_world(self.stack, self.group)
         else:

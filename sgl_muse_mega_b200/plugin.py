@@ -7,6 +7,7 @@ serves its architecture. No model code is imported here.
 
 SPECS = {
     "MuseSparkForConditionalGeneration": "sgl_muse_mega_b200.muse_spark.spec:SPEC",
+    "DFlash2DraftModel": "sgl_muse_mega_b200.muse_spark.draft:SPEC",
 }
 
 

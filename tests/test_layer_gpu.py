@@ -342,3 +342,28 @@ def test_a_missing_peer_runs_the_wait_out_and_is_recorded(device):
     torch.cuda.synchronize()
     assert clean.ranks[0].launch_record.status(s).code == 0
     check_world(clean, [0])
+
+
+@pytest.mark.parametrize("global_attn", [False, True])
+def test_full_shape_layer_parity(global_attn, device):
+    """The benchmark's own configuration as a whole layer: the full-shape model's TP8 world (hidden 8192, 16 query / 2 kv
+    heads a rank, 256 experts top-8, expert width 4096) on one device, M = 16 rows over an 8192-token context, one
+    sliding-window and one global layer, NVFP4 experts on the tensor cores, dense GEMMs on tile images. Every stage of
+    ranks 0 and 7 against the oracle fed the kernels' own inputs, routing ids exact. The routing is confined to 24 hot
+    experts (a +1 bias on them, as the reference's real-dims CPU test does) so that the CPU oracle holds the weights."""
+    from sgl_muse_mega_b200.muse_spark.config import Config
+
+    cfg = Config()
+    hot = torch.randperm(cfg.experts, generator=torch.Generator().manual_seed(1))[:24]
+    case = synthetic.layer_case(cfg, rows=16, ctx=8192, global_attn=global_attn, band="baseline", seed=1, experts_subset=hot)
+    world = L.LayerWorld(case, device)
+    assert all(r.tensor_cores and r.packed == 2 for r in world.ranks)
+    world.run_interleaved()
+    torch.cuda.synchronize()
+    for r in world.ranks:
+        st = r.launch_record.status(torch.cuda.current_stream().cuda_stream)
+        assert st.code == 0, f"rank {r.rank}: device status {st.code} at {st.stage} (block {st.block}, observed {st.observed})"
+    report = check_world(world, [0, cfg.tp - 1])
+    ids = world.ranks[0].o["ids"].cpu()
+    assert set(ids.flatten().tolist()) <= set(hot.tolist())
+    print({k[1]: f"{v:.1e}" for k, v in report.items() if k[0] == 0})

@@ -171,3 +171,187 @@ def test_plan_takes_only_the_batch_1_verify_step_of_one_block(case1):
     shim.install()
     with pytest.raises(RuntimeError, match="plan"):
         v.forward(None, None, ids, None, fb("target_verify", 1))
+
+
+# ---- the DFlash2 draft's spec and the fused iteration's host side ----------------------------------------------------------------
+
+
+def test_plugin_registers_the_draft_spec_too():
+    from sgl_muse_mega_b200.muse_spark import draft as DS
+
+    plugin.register()
+    found, why = sglang_api.find_spec(architectures=["DFlash2DraftModel"], isa="sm_100")
+    assert found is DS.SPEC and why is None
+    assert DS.SPEC.max_rows == 0 and DS.Draft().widths == () and DS.SPEC.requires.tp_sizes == frozenset({1, 2, 4, 8})
+
+
+def test_draft_spec_refuses_other_drafts_and_a_missing_target(monkeypatch):
+    from fake_sglang import draft_hf_config
+    from sgl_muse_mega_b200.muse_spark import draft as DS
+    from sgl_muse_mega_b200.muse_spark.b200.dflash.weights import DraftConfig
+
+    hf = lambda d: NS(to_dict=lambda: d)  # noqa: E731
+    good = draft_hf_config(DraftConfig())
+    assert DraftConfig.from_hf(good) == DraftConfig()
+    monkeypatch.setattr(B, "TARGET", object())
+    assert DS.model_disable_reasons(None, hf(good)) == []
+    monkeypatch.setattr(B, "TARGET", None)
+    assert DS.model_disable_reasons(None, hf(good)) == ["the target's megakernel is not built in this process"]
+    monkeypatch.setattr(B, "TARGET", object())
+    other = dict(good, num_hidden_layers=good["num_hidden_layers"] + 1, layer_types=good["layer_types"] + ["sliding_attention"])
+    assert any(r.startswith("layers ") for r in DS.model_disable_reasons(None, hf(other)))
+    causal = dict(good, is_causal=True)
+    assert "a causal or non-sliding layer" in DS.model_disable_reasons(None, hf(causal))[0]
+    assert "KeyError" in DS.model_disable_reasons(None, hf({"architectures": ["DFlash2DraftModel"]}))[0]
+    with pytest.raises(RuntimeError, match="not built"):
+        monkeypatch.setattr(B, "TARGET", None)
+        DS.build(None, hf(good), None)
+
+
+@pytest.mark.parametrize("ranks", [1, 2])
+def test_draft_build_reads_this_ranks_shard_onto_the_target(monkeypatch, ranks):
+    from fake_sglang import draft_checkpoint, draft_hf_config
+    from sgl_muse_mega_b200.muse_spark import draft as DS
+    from sgl_muse_mega_b200.muse_spark.b200.dflash import synthetic as dsyn
+    from sgl_muse_mega_b200.muse_spark.b200.dflash.weights import DraftConfig, load_shard, shard
+
+    dcfg = DraftConfig(hidden=256, layers=2, q_heads=4, kv_heads=2, head_dim=64, inter=256, vocab=512, sliding_window=24,
+                       mask_id=500, selector_rank=16, top_k=8, capture=(0, 1))  # fmt: skip
+    w, t = dsyn.draft_weights(dcfg, 3), dsyn.target_shared(dcfg, 3)
+    entries = draft_checkpoint(dcfg, w)
+    read = lambda names: {n: entries[n] for n in names}  # noqa: E731
+    for rank in range(ranks):
+        target = NS(draft=None, draft_cfg=None, device="cpu")
+        monkeypatch.setattr(B, "TARGET", target)
+        shim.install()
+        shim.install(tp_group=shim.Parallel(rank, ranks))
+        built = DS.build(None, NS(to_dict=lambda: draft_hf_config(dcfg)), None, read=read, cfg=dcfg)
+        assert built.widths == () and target.draft_cfg is dcfg
+        want, _ = shard(dcfg, w, t, rank, ranks)
+        assert torch.equal(target.draft.fc, want.fc) and torch.equal(target.draft.pred_codebook, w.pred_codebook)
+        for got, ref in zip(target.draft.layers, want.layers):
+            for name in ("input_norm", "post_norm", "q_norm", "k_norm", "qkv", "o", "gate_up", "down"):
+                assert torch.equal(getattr(got, name), getattr(ref, name)), name
+            assert torch.equal(got.attn_conv.base, ref.attn_conv.base) and torch.equal(got.mlp_conv.proj, ref.mlp_conv.proj)
+    shim.install()
+    with pytest.raises(ValueError, match="not bfloat16"):
+        load_shard(lambda names: {n: entries[n].float() for n in names}, 0, 1, dcfg)
+
+
+def test_simulated_accepts_meet_the_expected_length(monkeypatch):
+    from sgl_muse_mega_b200.muse_spark.runtime import iteration as IT
+
+    monkeypatch.delenv("SGLANG_SIMULATE_ACC_LEN", raising=False)
+    assert IT.simulated_accepts(16) is None and IT.fixed_token() is None
+    monkeypatch.setenv("SGLANG_SIMULATE_ACC_LEN", "3.3")
+    monkeypatch.setenv("SGLANG_SIMULATE_ACC_METHOD", "match-expected")
+    t = IT.simulated_accepts(16)
+    assert t.dtype == torch.int32 and t.shape == (IT.SIMULATED_STEPS,) and set(t.tolist()) == {2, 3}
+    commits = (t + 1).double()
+    assert abs(float(commits.mean()) - 3.3) < 1e-2
+    # any run of consecutive steps stays within a few commits of the expected total
+    run = commits.cumsum(0)
+    for lo in (0, 100, 1777):
+        for n in (10, 64, 500):
+            assert abs(float(run[lo + n] - run[lo]) - 3.3 * n) < 2.0, (lo, n)
+    monkeypatch.setenv("SGLANG_SIMULATE_ACC_METHOD", "multinomial")
+    m = IT.simulated_accepts(16) + 1
+    assert int(m.min()) >= 1 and int(m.max()) <= 16 and abs(float(m.double().mean()) - 3.3) < 0.1
+    monkeypatch.setenv("SGLANG_SIMULATE_ACC_LEN", "40")
+    assert set(IT.simulated_accepts(16).tolist()) == {15}  # clamped to the block
+    monkeypatch.setenv("SGLANG_SIMULATE_ACC_METHOD", "other")
+    with pytest.raises(ValueError, match="simulate_acc_method"):
+        IT.simulated_accepts(16)
+    monkeypatch.setenv("SGLANG_SIMULATE_ACC_METHOD", "multinomial")
+    monkeypatch.setenv("SGLANG_SIMULATE_ACC_TOKEN_MODE", "fixed")
+    shim.install(fixed_token_id=7)
+    assert IT.fixed_token() == 7
+    shim.install()
+
+
+def test_fused_mode_takes_only_the_steps_its_graphs_serve():
+    from fake_sglang import FakeRequest, decode_batch, plain_sampling_info
+    from sgl_muse_mega_b200.muse_spark.runtime import iteration as IT
+
+    f = IT.Fused.__new__(IT.Fused)  # mode() reads only ``sample``
+    f.sample = True
+    spec = shim.DraftInput(bonus_tokens=torch.tensor([5]))
+    greedy, sampled = FakeRequest("a"), FakeRequest("b", temperature=0.7, top_k=40, top_p=0.9)
+    assert f.mode(decode_batch([greedy], spec), needs_logits=False) == "greedy"
+    assert f.mode(decode_batch([greedy], spec), needs_logits=True) is None  # logprobs and the like read the logits
+    assert f.mode(decode_batch([greedy], spec, sampling_info=None), needs_logits=False) == "greedy"
+    assert f.mode(decode_batch([sampled], spec), needs_logits=True) == "sample"
+    assert f.mode(decode_batch([greedy, sampled], spec), needs_logits=False) is None
+    assert f.mode(decode_batch([greedy], spec, mode="extend"), needs_logits=False) is None
+    assert f.mode(decode_batch([greedy], spec, mode="idle"), needs_logits=False) is None
+    assert f.mode(decode_batch([greedy], spec, is_extend_in_batch=True), needs_logits=False) is None
+    assert f.mode(decode_batch([greedy], object()), needs_logits=False) is None  # not the DFlash2 draft's input
+    for edit in (dict(need_min_p_sampling=True), dict(has_custom_logit_processor=True), dict(grammar_mask=torch.ones(1)),
+                 dict(logit_bias=torch.ones(1)), dict(sampling_mask_batch_indices=torch.ones(1)),
+                 dict(penalizer_orchestrator=NS(is_required=True))):  # fmt: skip
+        assert f.mode(decode_batch([sampled], spec, sampling_info=plain_sampling_info(**edit)), needs_logits=True) is None, edit
+    assert f.mode(decode_batch([sampled], spec, sampling_info=plain_sampling_info(penalizer_orchestrator=NS(is_required=False))),
+                  needs_logits=True) == "sample"  # fmt: skip
+    assert f.mode(decode_batch([sampled], spec, has_grammar=True), needs_logits=True) is None
+    assert f.mode(decode_batch([sampled], spec, return_logprob=True), needs_logits=True) is None
+    f.sample = False  # a simulated accept length: sampled steps are SGLang's
+    assert f.mode(decode_batch([sampled], spec), needs_logits=True) is None
+
+
+def test_request_seed_is_the_same_on_every_rank():
+    from fake_sglang import FakeRequest
+    from sgl_muse_mega_b200.muse_spark.runtime import iteration as IT
+
+    assert IT.request_seed(FakeRequest("r", seed=12345)) == 12345
+    assert IT.request_seed(FakeRequest("r", seed=2**64 - 1)) == -1  # wrapped into a signed 64-bit word
+    a, b = IT.request_seed(FakeRequest("req-1")), IT.request_seed(FakeRequest("req-1"))
+    assert a == b and -(2**63) <= a < 2**63 and a != IT.request_seed(FakeRequest("req-2"))
+
+
+def test_hooks_wrap_the_worker_and_fall_back_to_its_own_step(monkeypatch):
+    import sys
+    import types
+
+    from sgl_muse_mega_b200.muse_spark.runtime import iteration as IT
+
+    calls = []
+
+    class Worker:
+        def __init__(self, model):
+            self.target_worker = NS(model_runner=NS(model=model))
+            self.draft_model, self.draft_model_runner = "draft", NS(token_to_kv_pool="pool")
+
+        def init_cuda_graphs(self):
+            calls.append("graphs")
+            return "ok"
+
+        def forward_batch_generation(self, batch, on_publish=None):
+            calls.append(("own", batch))
+            return "own step"
+
+        def _can_skip_verify_logits(self, batch, info):
+            return True
+
+    mod = types.ModuleType("sglang.srt.speculative.dflash_worker_v2")
+    mod.DFlashWorkerV2 = Worker
+    for name in ("sglang", "sglang.srt", "sglang.srt.speculative"):
+        monkeypatch.setitem(sys.modules, name, types.ModuleType(name))
+    monkeypatch.setitem(sys.modules, "sglang.srt.speculative.dflash_worker_v2", mod)
+    IT.install()
+
+    class Target(X.Verify):
+        def __init__(self):
+            self.block, self.fused = 16, None
+
+        def dflash_iteration(self, *, block_size, draft_model, draft_kv_pool):
+            calls.append(("bind", block_size, draft_model, draft_kv_pool))
+            return lambda batch, needs_logits, on_publish: None if batch.kind == "prefill" else f"fused {batch.kind} {needs_logits}"
+
+    w = Worker(NS(built_megakernel=Target()))
+    assert w.init_cuda_graphs() == "ok" and calls == ["graphs", ("bind", 16, "draft", "pool")]
+    decode, prefill = NS(kind="decode", sampling_info=None), NS(kind="prefill", sampling_info=None)
+    assert w.forward_batch_generation(decode) == "fused decode False"
+    assert w.forward_batch_generation(prefill) == "own step" and calls[-1] == ("own", prefill)
+    # a worker whose target model has no megakernel build keeps its own step
+    plain = Worker(NS())
+    assert plain.init_cuda_graphs() == "ok" and plain.forward_batch_generation(decode) == "own step"
