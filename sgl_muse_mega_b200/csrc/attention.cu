@@ -36,7 +36,9 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs a) {
     __shared__ __align__(128) unsigned char Vs[2][kKeyBlock * 128];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, kvhead = blockIdx.y;
+    RT(5, 0)
     griddep_wait();
+    RT(5, 1)
     const int kv_len = *a.kv_len;
     const int n_ctx = kv_len - a.M;
     const int lo = a.window > 0 ? max(0, n_ctx - a.window) : 0;
@@ -184,6 +186,7 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs a) {
         if (r0 < a.R) { w0[64] = m0; w0[65] = l0; }
         if (r1 < a.R) { w1[64] = m1; w1[65] = l1; }
     }
+    RT(5, 2)
 }
 
 // Four warps per (token, query head), two pairs per CTA: each warp merges a contiguous quarter of the splits in split
@@ -191,8 +194,10 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs a) {
 // up to 16 dependent batches of loads; the quarter walks at most 4.)
 __global__ void __launch_bounds__(256) attn_combine_kernel(const AttnArgs a) {
     __shared__ float s_o[2][4][64];
+    RT(6, 0)
     griddep_wait();
     griddep_launch();
+    RT(6, 1)
     const int pc = threadIdx.x >> 7, wq = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31;
     const int w = blockIdx.x * 2 + pc;
     const bool valid = w < a.M * a.qh;
@@ -263,6 +268,7 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const AttnArgs a) {
     const float s0 = 1.0f / (1.0f + expf(-g0)), s1 = 1.0f / (1.0f + expf(-g1));
     __nv_bfloat162 out = __floats2bfloat162_rn(x0 * rstd * s0, x1 * rstd * s1);
     *(__nv_bfloat162*)(a.x_attn + (size_t)tok * a.qh * kHeadDim + head * kHeadDim + 2 * lane) = out;
+    RT(6, 2)
 }
 
 static void attn_cfg(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, cudaStream_t stream, bool pdl) {
@@ -294,3 +300,5 @@ cudaError_t attn_combine_launch(const AttnArgs& a, cudaStream_t stream, bool pdl
 }
 
 }  // namespace mk
+
+RT_READ(mk_attn_trace_read)

@@ -41,10 +41,23 @@ namespace {
 constexpr int kRing = 6;
 }  // namespace
 
+
 __global__ void __launch_bounds__(kDThreads, 1) dense_umma_kernel(const __grid_constant__ SegGemmArgs a) {
     extern __shared__ unsigned char dense_smem_raw[];
-    const DenseCtx c = dense_setup_cta<kRing>(dense_smem_raw, a.status);
+#ifdef DENSE_TRACE
+    unsigned long long t_entry;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_entry));
+#endif
+    DenseCtx c = dense_setup_cta<kRing>(dense_smem_raw, a.status);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef DENSE_TRACE
+    // o_proj 0, pooler + router 1, unpooler 2, qkv 3, anything else 4 + finish % 4
+    c.trace_id = a.finish == 1 ? 1 : a.finish == 2 ? 3 : a.finish == 0 ? (a.g[0].K > 1024 ? 2 : 0) : 4 + (a.finish & 3);
+    if (tid == 0) {
+        g_dense_trace[c.trace_id][blockIdx.x][0] = t_entry;
+        DT(1)
+    }
+#endif
     const Plan pl = plan_of(a);
     const TileSignals none = {{nullptr, nullptr}, {nullptr, nullptr}, false};
     if (warp == 0) {
@@ -61,6 +74,7 @@ __global__ void __launch_bounds__(kDThreads, 1) dense_umma_kernel(const __grid_c
         }
     } else if (warp < 4) {
         griddep_wait();
+        if (tid == 64) { DT(3) }
         uint32_t it = 0;
         dense_stage_x<kRing>(a, c, pl, it, tid - 64);
     } else {
@@ -69,8 +83,20 @@ __global__ void __launch_bounds__(kDThreads, 1) dense_umma_kernel(const __grid_c
         dense_epilogue<kRing>(a, c, pl, i, warp - 4, tid - 128, lane, none);
     }
     dense_teardown_cta(c);
+    if (tid == 0) { DT(9) }
     xchg_signal(a.sig);
 }
+
+#ifdef DENSE_TRACE
+}  // namespace mk
+// trace builds: copies the dense launches' stamps to `dst` (8 x 160 x 16 words) and clears them
+extern "C" int mk_dense_trace_read(void* dst) {
+    if (cudaMemcpyFromSymbol(dst, mk::g_dense_trace, sizeof(unsigned long long) * 8 * 160 * 16) != cudaSuccess) return -1;
+    static unsigned long long zero[8 * 160 * 16];
+    return cudaMemcpyToSymbol(mk::g_dense_trace, zero, sizeof zero) == cudaSuccess ? 0 : -1;
+}
+namespace mk {
+#endif
 
 size_t dense_smem() { return DenseLayout<kRing>::kBytes; }
 

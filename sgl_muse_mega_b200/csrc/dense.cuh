@@ -7,6 +7,24 @@
 #include "draft_rows.cuh"
 #include "umma.cuh"
 
+// Trace builds (-DDENSE_TRACE): every CTA of a stand-alone dense launch stamps its milestones (global timer, 16 words a
+// CTA) into a device array: 0 entry, 1 set up, 2 last weight stage issued, 3 programmatic wait returned (stager), 4 first
+// rows staged, 5 first stage landed, 6 last MMA committed, 7 first accumulators complete, 8 epilogues done, 9 torn down,
+// 10 first finish started.
+#ifdef DENSE_TRACE
+namespace mk {
+static __device__ unsigned long long g_dense_trace[8][160][16];  // one copy per translation unit: dense.cu's is read
+}
+#define DT(slot)                                                                       \
+    {                                                                                  \
+        unsigned long long t_;                                                         \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                         \
+        if (c.trace_id >= 0) mk::g_dense_trace[c.trace_id][blockIdx.x][(slot)] = t_;  \
+    }
+#else
+#define DT(slot)
+#endif
+
 namespace mk {
 
 using namespace umma;
@@ -280,6 +298,7 @@ struct DenseCtx {
     unsigned char* extra;  // first byte behind the engine's shared memory
     uint32_t tmem;
     int* status;
+    int trace_id;  // trace builds: the launch's row of the trace array (-1: none)
 };
 
 // Carves the dynamic shared memory, initialises the barriers and allocates the tensor memory; ends with a block-wide
@@ -302,6 +321,7 @@ __device__ __forceinline__ DenseCtx dense_setup_cta(unsigned char* raw, int* sta
     c.is_last = (volatile int*)(c.tmem_slot + 2);
     c.extra = (unsigned char*)bars + DenseLayout<RING>::kBarBytes;
     c.status = status;
+    c.trace_id = -1;
     if (threadIdx.x == 0) {
         for (int i = 0; i < RING; ++i) {
             mbar_init(&c.full_w[i], 1);
@@ -356,6 +376,7 @@ __device__ __forceinline__ bool dense_produce(const SegGemmArgs& a, const DenseC
         }
         p += u.k1 - u.k0;
     }
+    DT(2)
     return true;
 }
 
@@ -380,6 +401,7 @@ __device__ __forceinline__ bool dense_mma(const SegGemmArgs& a, const DenseCtx& 
                 return false;
             }
             tc_fence_after();
+            if (p == pl.lo && ks == u.k0) { DT(5) }
             const uint32_t wb = smem_u32(c.wring + s * kStageW), xb = smem_u32(c.xring + s * kStageX);
 #pragma unroll
             for (int at = 0; at < 2; ++at)
@@ -393,6 +415,7 @@ __device__ __forceinline__ bool dense_mma(const SegGemmArgs& a, const DenseCtx& 
             tc_commit(&c.empty[s]);
         }
         tc_commit(&c.acc_full[buf]);
+        DT(6)
         p += u.k1 - u.k0;
     }
     return true;
@@ -430,6 +453,7 @@ __device__ __forceinline__ bool dense_stage_x(const SegGemmArgs& a, const DenseC
                 cp_async_wait<kXDepth - 1>();
                 fence_proxy_async_smem();
                 mbar_arrive(&c.full_x[arrived % RING]);
+                if (arrived == it0 && ts == 0) { DT(4) }
                 ++arrived;
             }
         }
@@ -468,6 +492,7 @@ __device__ __forceinline__ bool dense_epilogue(const SegGemmArgs& a, const Dense
             return false;
         }
         tc_fence_after();
+        if (p == pl.lo && te == 0) { DT(7) }
         uint32_t r[16];
         tmem_ld16(c.tmem + lane_base + buf * 16, r);
         tmem_ld_wait();
@@ -519,6 +544,7 @@ __device__ __forceinline__ bool dense_epilogue(const SegGemmArgs& a, const Dense
             }
         }
         if (finish) {
+            if (te == 0) { DT(10) }
 #pragma unroll
             for (int m = 0; m < 16; ++m) tile[m * kTileLd + te] = v[m];
             bar_sync(2, 128);
@@ -551,6 +577,7 @@ __device__ __forceinline__ bool dense_epilogue(const SegGemmArgs& a, const Dense
         bar_sync(2, 128);  // the tile and the ticket flag are free again
         p += u.k1 - u.k0;
     }
+    if (te == 0) { DT(8) }
     return true;
 }
 

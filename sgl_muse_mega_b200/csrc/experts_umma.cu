@@ -87,8 +87,19 @@ __device__ __forceinline__ int prov_exp_u(float amax) {
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                    \
         ((unsigned long long*)(a.status + 64 + 128 * G2))[(slot)] = t_;                           \
     }
+// and every CTA stamps its own milestones (16 words each) into a device array: 0 entry, 1 set up, 2 tables copied,
+// 3 last weight stage issued, 4 first operands ready, 5 first weight stage landed, 6 last MMA committed, 7 first
+// accumulators complete, 8 epilogues done, 9 torn down, 11 first rows staged
+static __device__ unsigned long long g_umma_trace[2][160][16];
+#define CT(slot)                                                       \
+    {                                                                  \
+        unsigned long long t_;                                         \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));         \
+        g_umma_trace[G2][blockIdx.x][(slot)] = t_;                     \
+    }
 #else
 #define UT(slot)
+#define CT(slot)
 #endif
 
 template <bool G2>
@@ -118,6 +129,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
+        CT(0)
         for (int i = 0; i < S; ++i) {
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], 1);
@@ -137,6 +149,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    if (tid == 0) { CT(1) }
 
     // One round trip for the route tables every unit looks up. g2's predecessor is g1: the tables were written two or more
     // kernels back, so g2 copies them and starts streaming its first weights under g1's tail; the roles that touch what g1
@@ -146,6 +159,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
     __syncthreads();
     const int NB = a.NB, KCH = a.K / 256;
     const int n_units = rt->n_active * NB;
+    if (tid == 0) { CT(2) }
 
     if (warp == 0) {
         // ---- weight producer ----
@@ -168,6 +182,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
                     for (uint32_t off = 0; off < STAGE; off += 9216) bulk_g2s_hint(dst + off, g + off, 9216, &full[s], policy);
                 }
             }
+            CT(3)
         }
     } else if (warp == 1) {
         // ---- scale copies + MMA issue ----
@@ -183,6 +198,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
                 }
                 tc_fence_after();
                 UT(4 * i + 0)
+                if (i == 0) { CT(4) }
                 const uint32_t xs_addr = smem_u32(xs + buf * kXsBytes);
                 bool ok = true;
                 for (int kc = 0; kc < KCH; ++kc, ++it) {
@@ -193,6 +209,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
                         break;
                     }
                     tc_fence_after();
+                    if (it == 0) { CT(5) }
                     const uint32_t sbase = smem_u32(stages + s * STAGE);
 #pragma unroll
                     for (int t = 0; t < TILES; ++t)
@@ -213,6 +230,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
                 if (!ok) break;
                 UT(4 * i + 1)
                 tc_commit(&acc_full[buf]);
+                CT(6)
             }
         }
     } else if (warp < 4) {
@@ -236,7 +254,16 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
             uint32_t* wb = sfw + buf * (kMaxRows * 64);
             const int ai = u / NB, s0 = rt->act_off[ai], n_tok = rt->act_off[ai + 1] - s0, e = rt->act_e[ai];
             const int row_bytes = a.K / 2, per_row = KCH * 8, total = n_tok * per_row, wq = KCH, wtotal = n_tok * wq;
-            // every global load of the unit is issued before the first store: one memory round trip
+            // the rows' codes go straight to their swizzled places (16-byte asynchronous copies, all in flight at once);
+            // every other global load of the unit is issued before the first store: one memory round trip
+            for (int idx = ts; idx < total; idx += 64) {
+                const int tk = idx / per_row, rem = idx - tk * per_row, kc = rem >> 3, jj = rem & 7;
+                const int sl = rt->slot[s0 + tk];
+                // only live rows are written: a stale row feeds accumulator columns that no epilogue reads
+                cp_async16(xb + kc * 2048 + (tk >> 3) * 1024 + (tk & 7) * 128 + ((jj ^ (tk & 7)) << 4),
+                           a.bq + (size_t)(G2 ? sl : sl / a.topk) * row_bytes + rem * 16, true);
+            }
+            cp_async_commit();
             int slot = 0, row = 0;
             float sc = 0.f, cc = 0.f;
             if (ts < n_tok) {
@@ -264,9 +291,15 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
                 int er = -128;
                 if (tk < n_tok) {
                     const signed char* ex = a.bex + (size_t)rt->slot[s0 + tk] * gb;
-                    for (int i = qd * 16; i < gb; i += 64) {
-                        const uint4 v4 = *(const uint4*)(ex + i);
-                        const uint32_t w4[4] = {v4.x, v4.y, v4.z, v4.w};
+                    uint4 v4[kMaxKChunks / 4];  // K <= 4096: at most 256 exponent bytes a slot, 64 a thread, loaded at once
+#pragma unroll
+                    for (int r = 0; r < kMaxKChunks / 4; ++r) {
+                        const int i = qd * 16 + r * 64;
+                        v4[r] = i < gb ? *(const uint4*)(ex + i) : make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
+                    }
+#pragma unroll
+                    for (int r = 0; r < kMaxKChunks / 4; ++r) {
+                        const uint32_t w4[4] = {v4[r].x, v4[r].y, v4[r].z, v4[r].w};
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
 #pragma unroll
@@ -298,27 +331,6 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
                     }
                 }
             }
-            for (int base = 0; base < total; base += 64 * 8) {
-                uint4 v[8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const int idx = base + k * 64 + ts;
-                    if (idx < total) {
-                        const int tk = idx / per_row, rem = idx - tk * per_row;
-                        const int sl = rt->slot[s0 + tk];
-                        v[k] = *(const uint4*)(a.bq + (size_t)(G2 ? sl : sl / a.topk) * row_bytes + rem * 16);
-                    }
-                }
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const int idx = base + k * 64 + ts;
-                    if (idx < total) {
-                        const int tk = idx / per_row, rem = idx - tk * per_row, kc = rem >> 3, jj = rem & 7;
-                        // only live rows are written: a stale row feeds accumulator columns that no epilogue reads
-                        *(uint4*)(xb + kc * 2048 + (tk >> 3) * 1024 + (tk & 7) * 128 + ((jj ^ (tk & 7)) << 4)) = v[k];
-                    }
-                }
-            }
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 const int idx = k * 64 + ts;
@@ -337,8 +349,10 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
                     m.c = cc;
                 }
             }
+            cp_async_wait<0>();
             fence_proxy_async_smem();
             mbar_arrive(&staged[buf]);
+            if (j == 0 && ts == 0) { CT(11) }
         }
     } else {
         // ---- scale words -> tensor memory, epilogue out ----
@@ -373,6 +387,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
             if (!bar_all(2, 128, mbar_wait(&acc_full[buf], (i >> 1) & 1, abort))) break;
             tc_fence_after();
             if (te == 0) { UT(4 * i + 2) }
+            if (te == 0 && i == 0) { CT(7) }
             if (u + stride < n_units && !publish(i + 1)) break;
             if (te == 0) { UT(4 * i + 3) }
             const UnitMeta& m = meta[buf];
@@ -431,10 +446,12 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
             mbar_arrive(&buf_free[buf]);
         }
         if (te == 0 && *abort == 0 && i * stride + u0 < n_units) record_abort(a.status, abort, 3, 130 + G2, i);
+        if (te == 0) { CT(8) }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 2) tmem_dealloc(tmem, kTmemCols);
+    if (tid == 0) { CT(9) }
     xchg_signal(a.sig);  // every CTA arrives, also one that had no unit
 }
 
@@ -451,6 +468,15 @@ cudaError_t experts_umma_prepare() {
     if (e != cudaSuccess) return e;
     return cudaFuncSetAttribute(experts_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)experts_umma_smem(true));
 }
+
+#ifdef UMMA_TRACE
+}  // namespace mk
+// trace builds: copies the experts' per-CTA stamps to `dst` (2 x 160 x 16 words)
+extern "C" int mk_umma_trace_read(void* dst) {
+    return cudaMemcpyFromSymbol(dst, mk::g_umma_trace, sizeof(unsigned long long) * 2 * 160 * 16) == cudaSuccess ? 0 : -1;
+}
+namespace mk {
+#endif
 
 cudaError_t experts_umma_launch(const UmmaArgs& a, bool g2, int grid, cudaStream_t s, bool pdl) {
     cudaLaunchAttribute attr[1];

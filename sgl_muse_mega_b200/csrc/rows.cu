@@ -41,8 +41,10 @@ __global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
     const uint4 pw_raw = *(const uint4*)(a.pre_w + c0);
     uint4 post_raw = make_uint4(0, 0, 0, 0);
     if (a.mode != 0) post_raw = *(const uint4*)(a.post_w + c0);
+    RT(a.mode != 0, 0)
     griddep_wait();
     griddep_launch();
+    RT(a.mode != 0, 1)
     const float4 s0 = *(const float4*)(a.stream_in + off), s1 = *(const float4*)(a.stream_in + off + 4);
     xchg_wait(a.wait);  // the all-reduce partials (mode 0) or the unpooler gather (mode 1) of every contributing rank
     float v[8];
@@ -100,6 +102,7 @@ __global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
         *(float4*)(a.normed_f32 + off) = make_float4(h[0], h[1], h[2], h[3]);
         *(float4*)(a.normed_f32 + off + 4) = make_float4(h[4], h[5], h[6], h[7]);
     }
+    RT(a.mode != 0, 2)
 }
 
 // ---- routing (top-k + route tables) and pre-expert norm + quantisation in one launch ---------------------------------------
@@ -302,24 +305,69 @@ struct RouteNqArgs {
     NqArgs nq;
     RouteTables* rt;
     int b_live;
+    unsigned* ticket;  // zero between launches: the routing rows' arrivals
 };
 
+// Blocks 0 .. M - 1: the routing of one row each - a thread per expert forms the selection score (the f64 sigmoid is the
+// long pole: one per thread instead of a row's worth per lane), warp 0 selects the top-k from shared memory, and the row
+// takes a ticket; the last row to arrive builds the route tables from every row's ids. Blocks M .. 2 M - 1: the pre-expert
+// norm + quantisation of one row each.
 __global__ void __launch_bounds__(512) route_nq_kernel(const RouteNqArgs a) {
     __shared__ float red[33];
     __shared__ int s_ids[kMaxSlots];
     __shared__ int cnt[1024];
     __shared__ int first[1024];
+    __shared__ float s_sel[1024];
+    __shared__ int s_last;
+    const int M = a.topk.M, E = a.topk.E, tid = threadIdx.x;
+    // the biases do not depend on the predecessor
+    float bias[2] = {0.f, 0.f};
+    if ((int)blockIdx.x < M) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+            if (tid + 512 * r < E) bias[r] = a.topk.bias[tid + 512 * r];
+    }
+    RT(2, 0)
     griddep_wait();
     griddep_launch();
-    if (blockIdx.x > 0) {
+    RT(2, 1)
+    if ((int)blockIdx.x >= M) {
         xchg_wait(a.nq.wait);  // the pooler gather of the node's ranks
-        nq_row(a.nq, blockIdx.x - 1, red);
+        nq_row(a.nq, blockIdx.x - M, red);
+        RT(2, 2)
         return;
     }
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (warp < a.topk.M) topk_row(a.topk, warp, lane, s_ids);
+    const int row = blockIdx.x;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int e = tid + 512 * r;
+        if (e < E) {
+            if (a.topk.score != nullptr) {
+                s_sel[e] = a.topk.score[(size_t)row * E + e];
+            } else {
+                const double z = (double)a.topk.logits[(size_t)row * E + e] * a.topk.mult;
+                s_sel[e] = (float)(1.0 / (1.0 + exp(-z))) + bias[r];
+            }
+        }
+    }
     __syncthreads();
-    route_tables(s_ids, a.topk.E, a.b_live * a.topk.k, a.rt, cnt, first, a.topk.e_lo, a.topk.e_hi);
+    if (tid < 32) {
+        TopkArgs tk = a.topk;
+        tk.score = s_sel - (size_t)row * E;
+        topk_row(tk, row, tid, s_ids);
+        __threadfence();  // the row's ids and weights, then its arrival
+        __syncwarp();
+        if (tid == 0) s_last = atomicInc(a.ticket, (unsigned)(M - 1)) == (unsigned)(M - 1);
+    }
+    __syncthreads();
+    RT(2, 2)
+    if (!s_last) return;
+    __threadfence();
+    const int S = M * a.topk.k;
+    for (int i = tid; i < S; i += 512) s_ids[i] = __ldcg(a.topk.ids + i);
+    __syncthreads();
+    route_tables(s_ids, E, a.b_live * a.topk.k, a.rt, cnt, first, a.topk.e_lo, a.topk.e_hi);
+    RT(2, 3)
 }
 
 // ---- h row view: scales moved to the row's largest exponent ---------------------------------------------------------------
@@ -355,8 +403,10 @@ __global__ void __launch_bounds__(512) combine_kernel(const CombineArgs a) {
     const int row = blockIdx.x, tid = threadIdx.x, c0 = tid * 8, warp = tid >> 5, lane = tid & 31;
     const int nw = blockDim.x >> 5;
     const uint4 gp_raw = *(const uint4*)(a.gamma_p1 + c0);  // a weight: in flight while the predecessor still runs
+    RT(4, 0)
     griddep_wait();
     griddep_launch();
+    RT(4, 1)
     xchg_wait(a.wait);  // every rank's column band of the expert outputs
     if (row >= a.b_live) {
         *(uint4*)(a.y + (size_t)row * a.P + c0) = make_uint4(0, 0, 0, 0);
@@ -402,6 +452,7 @@ __global__ void __launch_bounds__(512) combine_kernel(const CombineArgs a) {
         __syncthreads();
     }
     *(uint4*)(a.y + (size_t)row * a.P + c0) = pack8(acc);
+    RT(4, 2)
 }
 
 // ---- qkv row ops: qk norm, q scale, interleaved-pair RoPE, KV append -----------------------------------------------------------
@@ -462,9 +513,10 @@ static cudaError_t launch1(void (*kern)(KArgs...), dim3 grid, dim3 block, cudaSt
 cudaError_t resid_norm_launch(const NormArgs& a, cudaStream_t s, bool pdl) {
     return launch1(resid_norm_kernel, dim3(a.M), dim3(a.H / 8), s, pdl, a);
 }
-cudaError_t route_nq_launch(const TopkArgs& t, const NqArgs& n, RouteTables* rt, int b_live, cudaStream_t s, bool pdl) {
-    RouteNqArgs a{t, n, rt, b_live};
-    return launch1(route_nq_kernel, dim3(1 + t.M), dim3(512), s, pdl, a);
+cudaError_t route_nq_launch(const TopkArgs& t, const NqArgs& n, RouteTables* rt, int b_live, unsigned* ticket, cudaStream_t s,
+                            bool pdl) {
+    RouteNqArgs a{t, n, rt, b_live, ticket};
+    return launch1(route_nq_kernel, dim3(2 * t.M), dim3(512), s, pdl, a);
 }
 cudaError_t hrow_launch(const unsigned char* z_sf, const signed char* z_ex, int groups, int slots_live, int slots,
                         unsigned char* z_sfd, float* rowscale, const XchgWait& wait, cudaStream_t s, bool pdl) {
@@ -479,3 +531,5 @@ cudaError_t rowops_launch(const RowopsArgs& a, cudaStream_t s, bool pdl) {
 }
 
 }  // namespace mk
+
+RT_READ(mk_rows_trace_read)

@@ -64,6 +64,7 @@ struct MkLaunch {
     mk::RowopsArgs rowops;
     mk::ExpertArgs ex;
     mk::RouteTables* rt;
+    unsigned* route_ticket;  // the routing rows' arrivals (route_nq_kernel)
     unsigned char* z_sfd;
     float* rowscale;
     int* status;
@@ -334,6 +335,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     off += align_up((size_t)1024 * 4, 256);
     L->rt = (RouteTables*)(ws + off);
     off += align_up(sizeof(RouteTables), 256);
+    L->route_ticket = gcnt + 560;  // behind the fused kernels' meeting counters
     L->z_sfd = ws + off;
     off += align_up((size_t)slots * I / 16, 256);
     L->rowscale = (float*)(ws + off);
@@ -557,7 +559,10 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
         seg_gemm(L->sg_pool.g[1], L->router, true, gpart + (size_t)(H / 256) * 16 * (P / nr));
         L->sg_pool.n_gemm = 2;
         L->sg_pool.f32_out = (float*)b->logits;
-        L->sg_pool.score = scores;
+        // tile images: the routing kernel forms the selection scores itself (a thread per logit) instead of the CTA that
+        // finishes a router tile (a row's worth of f64 sigmoids per thread at the tail of the GEMM)
+        L->sg_pool.score = umma_images ? nullptr : scores;
+        if (umma_images) L->topk.score = nullptr;
         L->sg_pool.score_bias = (const float*)b->expert_bias;
         L->sg_pool.score_mult = b->router_mult;
         stage(L->sg_unpool, L->unpool, 0);
@@ -756,7 +761,7 @@ static int run_stage(const MkLaunch* L, int st, cudaStream_t s, bool pdl) {
         case ST_POOLER: e = L->seg_gemms ? seg_gemm_launch(L->sg_pool, L->sms, s, pdl) : gemm_launch(L->pooler, false, s, pdl); break;
         case ST_ROUTER: e = gemm_launch(L->router, true, s, pdl); break;
         case ST_TOPK:  // top-k, route tables and the pre-expert norm + quantisation share one launch
-            e = route_nq_launch(L->topk, L->nq, L->rt, L->combine.b_live, s, pdl);
+            e = route_nq_launch(L->topk, L->nq, L->rt, L->combine.b_live, L->route_ticket, s, pdl);
             break;
         case ST_NQ:
         case ST_TABLES:

@@ -126,7 +126,8 @@ cudaError_t attn_split_launch(const AttnArgs& a, cudaStream_t stream, bool pdl);
 cudaError_t attn_combine_launch(const AttnArgs& a, cudaStream_t stream, bool pdl);
 cudaError_t resid_norm_launch(const NormArgs& a, cudaStream_t s, bool pdl);
 // one launch: block 0 routes (top-k + route tables), blocks 1..M run the pre-expert norm + quantisation of one row each
-cudaError_t route_nq_launch(const TopkArgs& t, const NqArgs& n, RouteTables* rt, int b_live, cudaStream_t s, bool pdl);
+// `ticket`: a device word, zero between launches (the routing rows' arrivals)
+cudaError_t route_nq_launch(const TopkArgs& t, const NqArgs& n, RouteTables* rt, int b_live, unsigned* ticket, cudaStream_t s, bool pdl);
 cudaError_t hrow_launch(const unsigned char* z_sf, const signed char* z_ex, int groups, int slots_live, int slots,
                         unsigned char* z_sfd, float* rowscale, const XchgWait& wait, cudaStream_t s, bool pdl);
 cudaError_t combine_launch(const CombineArgs& a, int M, cudaStream_t s, bool pdl);

@@ -205,4 +205,24 @@ __device__ __forceinline__ float philox_uniform(unsigned long long seed, unsigne
     return (float)(w >> 8) * 0x1p-24f;
 }
 
+// Trace builds (-DROWS_TRACE): thread 0 of every CTA of a row or attention kernel stamps entry (0), programmatic wait
+// returned (1) and end (2) into a per-translation-unit device array [kernel][CTA][4]; RT_READ defines the C function
+// that copies it out.
+#ifdef ROWS_TRACE
+static __device__ unsigned long long g_rows_trace[8][160][4];
+#define RT(kid, slot)                                                           \
+    if (threadIdx.x == 0 && threadIdx.y == 0 && blockIdx.y == 0) {              \
+        unsigned long long t_;                                                  \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                  \
+        if (blockIdx.x < 160) g_rows_trace[(kid)][blockIdx.x][(slot)] = t_;     \
+    }
+#define RT_READ(name)                                                                                                   \
+    extern "C" int name(void* dst) {                                                                                    \
+        return cudaMemcpyFromSymbol(dst, mk::g_rows_trace, sizeof(unsigned long long) * 8 * 160 * 4) == cudaSuccess ? 0 : -1; \
+    }
+#else
+#define RT(kid, slot)
+#define RT_READ(name)
+#endif
+
 }  // namespace mk
