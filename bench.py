@@ -47,6 +47,9 @@ def parse():
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--cpu-sample-experts", type=int, default=24)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--timeline", action="store_true",
+                    help="one layer's timeline from the trace build (per kernel: first CTA in, programmatic wait returned, last CTA "
+                         "out) instead of the bench line")
     ap.add_argument("--form", type=int, default=0, choices=(0, 1, 2, 3, 4),
                     help="dense stages: 0 tcgen05 stream-K GEMM kernels over tile images (default), 1 two persistent segment "
                          "kernels (mma.sync item engine), 2 cluster split-K GEMMs, 3 item-engine GEMM kernels, 4 two fused "
@@ -858,6 +861,91 @@ def parity_n(world: int, dec: dict, emu: dict) -> dict:
     return {"ranks": world, "bit_equal": ok, "timed_model_ranks_equal": same, "emulated_world": emu}
 
 
+def run_timeline(args) -> None:
+    """One full-shape NVFP4 layer of the ring under programmatic dependent launch on the trace build of the library
+    (``common/build.py`` ``trace=True``): every kernel's CTAs stamp %globaltimer at entry, when their programmatic wait
+    returns and when they leave. Prints per kernel, in launch order: first entry, wait returned (first CTA), end (last
+    CTA), body = end - wait returned, and the boundary = wait returned - the predecessor's end. The stamps cost a few
+    hundred nanoseconds a kernel: read the proportions, not the sum."""
+    import ctypes
+
+    import torch
+
+    from sgl_muse_mega_b200.common import build, host
+    from sgl_muse_mega_b200.muse_spark.b200 import layer as L
+    from sgl_muse_mega_b200.muse_spark.b200 import synthetic
+    from sgl_muse_mega_b200.muse_spark.config import Config
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device: there is no CPU fallback"
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    lib = host.Library(build.build(trace=True))
+    module = lib.load()
+    synthetic.set_device(device)
+    cfg = Config()
+    ring = []
+    for i in range(3):
+        case = synthetic.layer_case(cfg, rows=args.rows, ctx=args.ctx, global_attn=False, next_global=False, band="baseline",
+                                    seed=args.seed, layer=2 + i, only_ranks=[0])  # fmt: skip
+        lr = L.LayerRank(lib, module, case, 0, device, tensors=case.ranks[0], keep_plain_experts=False)
+        g = torch.Generator(device=device).manual_seed(1000 + i)
+        lr.ar.view(torch.bfloat16).copy_(torch.randn(lr.ar.numel() // 2, generator=g, device=device) * 0.3)
+        lr.pool_ag.copy_(torch.randn(lr.pool_ag.shape, generator=g, device=device))
+        lr.unpool_ag.copy_(torch.randn(lr.unpool_ag.shape, generator=g, device=device))
+        lr.zb.view(torch.bfloat16).copy_(torch.randn(lr.zb.numel() // 2, generator=g, device=device))
+        lr.bind(None, fused=0)
+        case.ranks = []
+        ring.append(lr)
+    stream = torch.cuda.Stream(device)
+    s = stream.cuda_stream
+    for rep in range(12):
+        ring[rep % 3].launch(s, True)
+    stream.synchronize()
+    st = ring[2].launch_record.status(s)
+    assert st.code == 0, f"device status {st.code} at stage {st.stage}"
+
+    def read(fn: str, shape) -> "torch.Tensor":
+        n = 1
+        for d in shape:
+            n *= d
+        buf = (ctypes.c_ulonglong * n)()
+        assert getattr(lib.dll, fn)(buf) == 0, fn
+        return torch.tensor(list(buf), dtype=torch.int64).view(*shape)
+
+    dense = read("mk_dense_trace_read", (8, 160, 16))  # [o_proj, pooler + router, unpooler, qkv][CTA]: 0 entry, 3 wait, 9 out
+    umma = read("mk_umma_trace_read", (2, 160, 16))  # [g1, g2][CTA]: 0 entry, 2 tables copied, 9 out
+    rows = read("mk_rows_trace_read", (8, 160, 4))  # [post norm, cross norm, routing, -, combine][CTA]: entry, wait, out, tables
+    attn = read("mk_attn_trace_read", (8, 160, 4))  # [5 split, 6 combine][CTA]
+    kernels = [
+        ("attn_split", attn[5, :, 0], attn[5, :, 1], attn[5, :, 2]), ("attn_combine", attn[6, :, 0], attn[6, :, 1], attn[6, :, 2]),
+        ("o_proj", dense[0, :, 0], dense[0, :, 3], dense[0, :, 9]), ("post_norm", rows[0, :, 0], rows[0, :, 1], rows[0, :, 2]),
+        ("pooler+router", dense[1, :, 0], dense[1, :, 3], dense[1, :, 9]),
+        ("routing+quantisation", rows[2, :, 0], rows[2, :, 1], torch.maximum(rows[2, :, 2], rows[2, :, 3])),
+        ("g1", umma[0, :, 0], umma[0, :, 2], umma[0, :, 9]), ("g2", umma[1, :, 0], umma[1, :, 2], umma[1, :, 9]),
+        ("combine", rows[4, :, 0], rows[4, :, 1], rows[4, :, 2]), ("unpooler", dense[2, :, 0], dense[2, :, 3], dense[2, :, 9]),
+        ("cross_norm", rows[1, :, 0], rows[1, :, 1], rows[1, :, 2]), ("qkv", dense[3, :, 0], dense[3, :, 3], dense[3, :, 9]),
+    ]  # fmt: skip
+    ev = []
+    for name, entry, wait, end in kernels:
+        entry, wait, end = entry[entry > 0], wait[wait > 0], end[end > 0]
+        if entry.numel() and wait.numel() and end.numel():
+            ev.append((name, int(entry.min()), int(wait.min()), int(end.max())))
+    ev.sort(key=lambda e: e[1])  # each kernel's stamps are its last launch's; the ring's launches follow one another
+    t0, prev = ev[0][1], None
+    out = []
+    for name, entry, wait, end in ev:
+        rec = {"kernel": name, "entry_us": round((entry - t0) / 1e3, 2), "wait_returned_us": round((wait - t0) / 1e3, 2),
+               "end_us": round((end - t0) / 1e3, 2), "body_us": round((end - wait) / 1e3, 2),
+               "boundary_us": None if prev is None else round((wait - prev) / 1e3, 2)}  # fmt: skip
+        # g2 copies its route tables before g1 has finished: its "wait" stamp is not a wait on g1
+        if name == "g2":
+            rec["boundary_us"], rec["body_us"] = None, round((end - prev) / 1e3, 2)
+            rec["note"] = "body counted from g1's end (the roles that read g1's output wait inside the kernel)"
+        out.append(rec)
+        prev = end
+    print(json.dumps({"timeline": out, "workload": WORKLOAD, "note": "trace build, one layer under programmatic dependent launch"}))
+
+
 def run_expert_block(args) -> None:
     """configs[2]: the isolated NVFP4 expert block at the full expert shape (256 experts x 28.31 MB), M in {1, 4, 8, 16}
     rows, experts partitioned over EP in {1, 2, 4, 8} ranks. One GPU: the ranks' launches run one after the other on it (a
@@ -919,6 +1007,8 @@ def main() -> None:
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+    elif args.timeline:
+        run_timeline(args)
     elif args.config == 2:
         run_expert_block(args)
     else:
