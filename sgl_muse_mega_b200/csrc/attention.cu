@@ -31,6 +31,21 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// The key blocks the window's rows see, and the splits that share them: a launch has `a.splits` CTAs per kv head (sized for
+// the longest context), of which the first min(splits, blocks) take a contiguous share of the blocks each; the others
+// leave at once and the merge does not read their partials. Both kernels derive the same numbers from kv_len.
+struct AttnSpan {
+    int lo, nblk, eff;
+};
+__device__ __forceinline__ AttnSpan attn_span(const AttnArgs& a, int kv_len) {
+    AttnSpan sp;
+    const int n_ctx = kv_len - a.M;
+    sp.lo = a.window > 0 ? max(0, n_ctx - a.window) : 0;
+    sp.nblk = (kv_len - sp.lo + kKeyBlock - 1) / kKeyBlock;
+    sp.eff = min(a.splits, max(sp.nblk, 1));
+    return sp;
+}
+
 __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs a) {
     __shared__ __align__(128) unsigned char Ks[2][kKeyBlock * 128];
     __shared__ __align__(128) unsigned char Vs[2][kKeyBlock * 128];
@@ -41,9 +56,10 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs a) {
     RT(5, 1)
     const int kv_len = *a.kv_len;
     const int n_ctx = kv_len - a.M;
-    const int lo = a.window > 0 ? max(0, n_ctx - a.window) : 0;
-    const int nblk = (kv_len - lo + kKeyBlock - 1) / kKeyBlock;
-    const int b0 = (int)((long long)split * nblk / a.splits), b1 = (int)((long long)(split + 1) * nblk / a.splits);
+    const AttnSpan span = attn_span(a, kv_len);
+    if (split >= span.eff) return;  // more splits than key blocks: the merge reads the first `eff` partials only
+    const int lo = span.lo, nblk = span.nblk;
+    const int b0 = (int)((long long)split * nblk / span.eff), b1 = (int)((long long)(split + 1) * nblk / span.eff);
 
     // Q fragments of this warp's 16 rows (rows >= R are zero)
     const int r0 = warp * 16 + g, r1 = r0 + 8;
@@ -206,7 +222,8 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const AttnArgs a) {
     const float* base = a.ws + ((size_t)kvhead * a.splits * a.R + r) * 66;
     const size_t stride = (size_t)a.R * 66;
     // the (m, l) pairs of the splits live in the lanes (split s in lane s % 32, register s / 32): all loads independent
-    constexpr int kPer = 4;  // splits <= 128
+    constexpr int kPer = 8;  // splits <= 256
+    const int n_splits = attn_span(a, *a.kv_len).eff;
     float ms_[kPer], ls_[kPer];
     float mx = -1e30f;
 #pragma unroll
@@ -214,7 +231,7 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const AttnArgs a) {
         const int s = lane + 32 * i;
         ms_[i] = -1e30f;
         ls_[i] = 0.f;
-        if (valid && s < a.splits) {
+        if (valid && s < n_splits) {
             const float2 ml = *(const float2*)(base + s * stride + 64);
             ms_[i] = ml.x;
             ls_[i] = ml.y;
@@ -230,7 +247,7 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const AttnArgs a) {
     }
     L = warp_sum(L);
     // this warp's quarter: O = sum over its splits, in split order, of O_s x scale_s: 8 independent loads per batch
-    const int quarter = ((a.splits + 3) / 4 + 7) / 8 * 8, q0 = wq * quarter, q1 = min(q0 + quarter, a.splits);
+    const int quarter = ((n_splits + 3) / 4 + 7) / 8 * 8, q0 = wq * quarter, q1 = min(q0 + quarter, n_splits);
     float o0 = 0.f, o1 = 0.f;
     for (int s0 = q0; s0 < q1; s0 += 8) {
         float2 v[8];

@@ -72,6 +72,8 @@ struct MkLaunch {
     bool use_umma;  // experts on tcgen05 (packed images bound) instead of CUDA cores
     int sms;
     mk::UmmaArgs umma_g1, umma_g2;
+    mk::Bf16UmmaArgs bf16_g1, bf16_g2;
+    bool use_bf16_umma;  // a bf16 layer's experts on tcgen05 (tile images bound)
     bool stage_on[ST_COUNT];
     mk::XchgWait hrow_wait;
     bool use_segments;  // mk_launch runs the dense stages as the two persistent segment kernels
@@ -104,11 +106,12 @@ using namespace mk;
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 static int attn_splits_for(const MkLayerShape& s) {
-    int sp = 144 / (int)s.kv_heads;
+    // Global attention: two 256-thread CTAs fit an SM (128 registers a thread), so 288 CTAs over the kv heads; at run time
+    // only as many splits as the context has 64-key blocks take part (attention.cu attn_span). The merge holds up to 256.
+    int sp = 288 / (int)s.kv_heads;
     if (sp < 1) sp = 1;
-    if (sp > 72) sp = 72;
-    // a sliding-window layer never sees more than window + rows keys: more splits than 64-key blocks would only add empty
-    // partials for the merge to read
+    if (sp > 256) sp = 256;
+    // a sliding-window layer never sees more than window + rows keys
     if (s.window > 0) {
         const int blocks = (int)((s.window + s.rows + 63) / 64) + 1;
         if (sp > blocks) sp = blocks;
@@ -168,6 +171,7 @@ static void fill_constants(const MkLayerShape& s, MkLayerConstants* c) {
     off += align_up(sizeof(RouteTables), 256);
     off += align_up((size_t)slots * s.inter / 16, 256);
     off += align_up((size_t)slots * 4, 256);
+    if (s.bf16) off += align_up(kBf16UmmaScratchBytes, 256);  // the grouped tensor-core experts' pieces and tickets
     c->ws_bytes = (int64_t)off;
 }
 
@@ -194,6 +198,8 @@ int mk_module_load(const void* image, uint64_t bytes, const char* code_prefetch_
     if (e != cudaSuccess) return cuda_fail(e, "experts_prepare");
     e = experts_umma_prepare();
     if (e != cudaSuccess) return cuda_fail(e, "experts_umma_prepare");
+    e = experts_bf16_umma_prepare();
+    if (e != cudaSuccess) return cuda_fail(e, "experts_bf16_umma_prepare");
     e = headtail_prepare();
     if (e != cudaSuccess) return cuda_fail(e, "headtail_prepare");
     e = segments_prepare();
@@ -254,15 +260,21 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     NEED(w_p); NEED(pool_ag); NEED(w_r); NEED(logits); NEED(expert_bias); NEED(topk_idx32); NEED(topk_w); NEED(gamma); NEED(q);
     NEED(z); NEED(zb); NEED(gamma_p1); NEED(y);
     MK_REQUIRE((b->w1_pack == 0) == (b->w2_pack == 0), "w1_pack and w2_pack must be bound together");
-    const bool use_umma = b->w1_pack != 0;
-    if (use_umma) {
-        MK_REQUIRE(fp4, "the packed tensor-core images are NVFP4: a bf16 layer cannot bind them");
+    // packed images: NVFP4 stages on an NVFP4 layer, bf16 tile images (one image per expert, weights.py pack_umma) on a
+    // bf16 layer
+    const bool use_umma = b->w1_pack != 0 && fp4, use_bf16_umma = b->w1_pack != 0 && !fp4;
+    if (use_bf16_umma) {
+        MK_REQUIRE(I_s % 64 == 0 && H_s % 128 == 0 && P % 128 == 0 && I % 128 == 0,
+                   "the tensor-core bf16 experts need I/ranks a multiple of 64, P/ranks, P and I multiples of 128");
+        ALIGNED16(w1_pack); ALIGNED16(w2_pack);
+    } else if (use_umma) {
         MK_REQUIRE(I_s % 128 == 0 && H_s % 128 == 0 && P % 256 == 0 && I % 256 == 0 && P <= 4096 && I <= 4096,
                    "the tensor-core expert path needs I/ranks and P/ranks multiples of 128 and P, I multiples of 256 up to 4096");
         ALIGNED16(w1_pack); ALIGNED16(w2_pack);
     } else {
         NEED(w1_gate); NEED(w1_up); NEED(w2);
     }
+    L->use_bf16_umma = use_bf16_umma;
     NEED(w_up); NEED(unpool_ag); NEED(c_alpha); NEED(c_beta); NEED(c_pre_w); NEED(c_post_w); NEED(c_stream_out); NEED(h3q);
     NEED(ws); NEED(status);
     if (fp4) {
@@ -340,6 +352,8 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     off += align_up((size_t)slots * I / 16, 256);
     L->rowscale = (float*)(ws + off);
     off += align_up((size_t)slots * 4, 256);
+    unsigned char* const bf16_scratch = ws + off;
+    if (s.bf16) off += align_up(kBf16UmmaScratchBytes, 256);
     MK_REQUIRE((int64_t)off == c.ws_bytes, "internal: scratch carve %zu != %lld", off, (long long)c.ws_bytes);
     L->status = (int*)b->status;
     L->max_active = slots < E ? slots : E;
@@ -476,6 +490,30 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     MK_REQUIRE(g1_smem(P) <= 200 * 1024 && g2_smem(I) <= 200 * 1024, "expert rows exceed shared memory");
     L->use_umma = use_umma;
     L->sms = module ? module->sms : 148;
+    if (use_bf16_umma) {
+        MK_REQUIRE(L->sms <= kBf16UmmaMaxGrid, "%d CTAs exceed the grouped experts' scratch", L->sms);
+        for (int g2 = 0; g2 < 2; ++g2) {
+            Bf16UmmaArgs& u = g2 ? L->bf16_g2 : L->bf16_g1;
+            memset(&u, 0, sizeof u);
+            u.rt = L->rt;
+            u.w = (const unsigned char*)(g2 ? b->w2_pack : b->w1_pack);
+            u.x = (const bf16*)(g2 ? b->z : b->q);
+            u.K = g2 ? I : P;
+            u.NB = g2 ? H_s / 128 : 2 * I_s / 128;
+            u.topk = K;
+            u.by_token = !g2;
+            u.g2 = g2;
+            for (int i = 0; i < ex.n_peer; ++i) u.out[i] = g2 ? ex.zb_peer[i] : (bf16*)ex.z_peer[i];
+            u.n_out = ex.n_peer;
+            u.ldo = g2 ? P : I;
+            u.col0 = (long long)s.rank * (g2 ? H_s : I_s);
+            u.part = (float*)bf16_scratch;
+            u.ticket = (unsigned*)(bf16_scratch + (size_t)2 * kBf16UmmaMaxGrid * 2048 * 4) + (g2 ? kBf16UmmaMaxGrid : 0);
+            if (g2) u.wait = ex.wait_g2;
+            u.sig = g2 ? ex.sig_g2 : ex.sig_g1;
+            u.status = L->status;
+        }
+    }
     if (use_umma) {
         for (int g2 = 0; g2 < 2; ++g2) {
             UmmaArgs& u = g2 ? L->umma_g2 : L->umma_g1;
@@ -767,14 +805,18 @@ static int run_stage(const MkLaunch* L, int st, cudaStream_t s, bool pdl) {
         case ST_TABLES:
             break;  // folded into ST_TOPK's launch (the slots stay in the stage list: stage indices are ABI)
         case ST_G1:
-            e = L->use_umma ? experts_umma_launch(L->umma_g1, false, L->sms, s, pdl) : g1_launch(L->ex, L->max_active, s, pdl);
+            e = L->use_umma        ? experts_umma_launch(L->umma_g1, false, L->sms, s, pdl)
+                : L->use_bf16_umma ? experts_bf16_umma_launch(L->bf16_g1, L->sms, s, pdl)
+                                   : g1_launch(L->ex, L->max_active, s, pdl);
             break;
         case ST_HROW:
             e = hrow_launch((const unsigned char*)L->bind.z_sf, (const signed char*)L->bind.z_ex, (int)L->shape.inter / 16,
                             L->slots_live, (int)L->consts.slots, L->z_sfd, L->rowscale, L->hrow_wait, s, pdl);
             break;
         case ST_G2:
-            e = L->use_umma ? experts_umma_launch(L->umma_g2, true, L->sms, s, pdl) : g2_launch(L->ex, L->max_active, s, pdl);
+            e = L->use_umma        ? experts_umma_launch(L->umma_g2, true, L->sms, s, pdl)
+                : L->use_bf16_umma ? experts_bf16_umma_launch(L->bf16_g2, L->sms, s, pdl)
+                                   : g2_launch(L->ex, L->max_active, s, pdl);
             break;
         case ST_COMBINE: e = combine_launch(L->combine, (int)L->shape.rows, s, pdl); break;
         case ST_UNPOOL: e = L->seg_gemms ? seg_gemm_launch(L->sg_unpool, L->sms, s, pdl) : gemm_launch(L->unpool, false, s, pdl); break;

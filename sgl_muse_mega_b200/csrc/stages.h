@@ -399,6 +399,29 @@ cudaError_t fused_prepare();
 cudaError_t fused_launch(const FusedArgs& a, int grid, cudaStream_t s, bool pdl);
 
 size_t experts_umma_smem(bool g2);
+// experts_bf16_umma.cu: the bf16 experts as a grouped GEMM on the tcgen05 dense pipeline (tile images per expert)
+struct Bf16UmmaArgs {
+    const RouteTables* rt;
+    const unsigned char* w;  // [E][NB][K bytes / 256][32768] tile images (g1: [gate | up] rows in silu_perm order)
+    const bf16* x;           // g1: the normed pooled rows [M, K] (row = slot / topk); g2: the gathered h rows [slots, K]
+    int K;                   // contraction length in elements (a multiple of 128)
+    int NB;                  // 128-row tiles per expert: 2 I_s / 128 (g1) or H_s / 128 (g2)
+    int topk, by_token, g2;
+    bf16* out[kMaxRanks];    // g1: every rank's h rows [slots, ldo], g2: every rank's expert outputs [slots, ldo]
+    int n_out;
+    long long ldo, col0;     // this rank's column band starts at col0; a tile covers 64 (g1) or 128 (g2) columns of it
+    float* part;             // [2 x grid][16][128] f32: the accumulators of the unit pieces a CTA shares with its neighbours
+    unsigned* ticket;        // [grid] arrivals at a shared unit, zero between launches
+    XchgWait wait;           // g2: the h rows of every rank
+    XchgSignal sig;
+    int* status;
+};
+size_t experts_bf16_umma_smem();
+cudaError_t experts_bf16_umma_prepare();
+cudaError_t experts_bf16_umma_launch(const Bf16UmmaArgs& a, int grid, cudaStream_t s, bool pdl);
+constexpr int kBf16UmmaMaxGrid = 160;
+constexpr size_t kBf16UmmaScratchBytes = (size_t)2 * kBf16UmmaMaxGrid * 2048 * 4 + 2 * kBf16UmmaMaxGrid * 4;  // pieces, then g1's and g2's tickets
+
 cudaError_t experts_umma_prepare();
 cudaError_t experts_umma_launch(const UmmaArgs& a, bool g2, int grid, cudaStream_t s, bool pdl);
 

@@ -76,7 +76,16 @@ class LayerRank:
         whole_tiles = (cfg.inter_rank % 128 == 0 and cfg.moe_hidden_rank % 128 == 0 and P % 256 == 0
                        and cfg.moe_inter % 256 == 0 and P <= 4096 and cfg.moe_inter <= 4096)  # fmt: skip
         self.tensor_cores = bool(tensor_cores and not case.bf16 and whole_tiles)
+        # a bf16 layer's experts as a grouped GEMM on the tensor-core dense pipeline (one tile image per expert)
+        self.tensor_cores_bf16 = bool(tensor_cores and case.bf16 and cfg.inter_rank % 64 == 0 and cfg.moe_hidden_rank % 128 == 0
+                                      and P % 128 == 0 and cfg.moe_inter % 128 == 0 and self.w["gate"] is not None)  # fmt: skip
         self.w1_pack = self.w2_pack = None
+        if self.tensor_cores_bf16:
+            w = self.w
+            self.w1_pack, self.w2_pack = weights.pack_bf16_experts(w["gate"], w["up"], w["w2"])
+            if not keep_plain_experts:
+                for k in ("gate", "up", "w2"):
+                    w[k] = None
         if self.tensor_cores:
             w = self.w
             self.w1_pack = weights.pack_w1_fp4(w["gate_q"], w["gate_sf"], w["up_q"], w["up_sf"])

@@ -226,11 +226,15 @@ def layer_case(
             next_cos_sin=cos_sin,
         )
         if bf16:
-            t.update(
-                gate=normal((E, i_s, P), P**-0.5, bf, seed, "gate", layer, r),
-                up=normal((E, i_s, P), P**-0.5, bf, seed, "up", layer, r),
-                w2=normal((E, h_s, I), I**-0.5, bf, seed, "w2", layer, r),
-            )
+
+            def rows16(name, nrows, k):
+                if experts_subset is None:
+                    return normal((E, nrows, k), k**-0.5, bf, seed, name, layer, r)
+                w = torch.zeros(E, nrows, k, dtype=bf, device=_DEVICE)
+                w[experts_subset.long()] = normal((len(experts_subset), nrows, k), k**-0.5, bf, seed, name, layer, r)
+                return w
+
+            t.update(gate=rows16("gate", i_s, P), up=rows16("up", i_s, P), w2=rows16("w2", h_s, I))
         else:
 
             def fp4(name, nrows, k):

@@ -180,6 +180,23 @@ def silu_perm(inter: int) -> torch.Tensor:
     return torch.cat((t, t + inter), 1).reshape(-1)
 
 
+def pack_bf16_experts(gate: torch.Tensor, up: torch.Tensor, w2: torch.Tensor) -> tuple:
+    """A bf16 layer's experts (this rank's shards: gate, up [E, I_s, P], w2 [E, H_s, I]) -> the tile images of the grouped
+    tensor-core GEMM (``csrc/experts_bf16_umma.cu``): (w1 image, w2 image), each u8
+    [E x tiles per expert][K bytes / 256][2][128][128]. w1's tiles hold 64 gate rows and the same features' up rows
+    (``silu_perm`` inside every expert), w2's its rows in order. I_s must be a multiple of 64, H_s of 128."""
+    e, i_s, p = gate.shape
+    h_s = w2.shape[1]
+    if i_s % 64 or h_s % 128:
+        raise ValueError(f"I_s {i_s} is not a multiple of 64 or H_s {h_s} not of 128")
+    perm = silu_perm(i_s).to(gate.device)
+    w1 = torch.cat((gate, up), 1)[:, perm]  # [E, 2 I_s, P]: per expert, tile t = gate rows 64 t .., then up rows 64 t ..
+    img1 = pack_umma(w1.reshape(e * 2 * i_s, p))
+    del w1
+    img2 = pack_umma(w2.reshape(e * h_s, w2.shape[2]))
+    return img1, img2
+
+
 def conv_perm(groups: int) -> torch.Tensor:
     """Row order of a conv projection ([4 groups, K], rows kind x groups + group) for the conv epilogue: tile t holds the four
     kinds' coefficients of groups 32 t .. 32 t + 31 (tile row kind 32 + group)."""

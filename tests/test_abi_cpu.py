@@ -138,6 +138,27 @@ def test_tail_and_bf16_variants_drop_stages(lib):
     assert rank.bind(fused=1).info().kernels == 7 - 1  # the fused form: no h-row view either
 
 
+def test_bf16_layers_bind_tile_images_of_their_experts(lib):
+    """A bf16 layer with whole tiles packs one tile image per expert (gate and up rows of a feature block in one tile) and
+    binds the grouped tensor-core GEMM; the image inverts to the shards."""
+    from sgl_muse_mega_b200.muse_spark.b200 import weights as W
+
+    cfg, kw = CASES["small_bf16_global_tp8"]
+    case = synthetic.layer_case(cfg, **kw)
+    rank = L.LayerRank(lib, None, case, 3, torch.device("cpu"))
+    assert rank.tensor_cores_bf16 and not rank.tensor_cores
+    e, i_s, p = rank.w["gate"].shape
+    h_s, inter = rank.w["w2"].shape[1:]
+    assert rank.w1_pack.shape == (e * 2 * i_s // 128, p * 2 // 256, 2, 128, 128)
+    assert rank.w2_pack.shape == (e * h_s // 128, inter * 2 // 256, 2, 128, 128)
+    w1 = W.unpack_umma(rank.w1_pack, e * 2 * i_s, torch.bfloat16).view(e, 2 * i_s // 128, 2, 64, p)
+    assert torch.equal(w1[:, :, 0].reshape(e, i_s, p), rank.w["gate"]) and torch.equal(w1[:, :, 1].reshape(e, i_s, p), rank.w["up"])
+    assert torch.equal(W.unpack_umma(rank.w2_pack, e * h_s, torch.bfloat16).view(e, h_s, inter), rank.w["w2"])
+    assert rank.bind().info().kernels == 12  # a bf16 layer has no h-row view on either expert path
+    plain = L.LayerRank(lib, None, case, 3, torch.device("cpu"), tensor_cores=False)
+    assert not plain.tensor_cores_bf16 and plain.w1_pack is None and plain.bind().info().kernels == 12
+
+
 def test_weight_images_round_trip_and_layout():
     """The tensor-core weight images invert exactly, and a byte lands where the kernel's descriptors expect it."""
     from sgl_muse_mega_b200.muse_spark.b200 import weights as W

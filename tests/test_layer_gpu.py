@@ -19,13 +19,12 @@ def device():
 
 
 def _paths():
-    """Every golden case on the default expert path (tcgen05 for NVFP4 shapes with whole 128-row tiles) and the NVFP4
-    cases again on the general CUDA-core expert kernels."""
+    """Every golden case on the default expert path (tcgen05: block-scaled NVFP4 stages, or the grouped bf16 GEMM of the
+    bf16 layers, for shapes with whole tiles) and again on the general CUDA-core expert kernels."""
     out = []
-    for name, (_, kw) in CASES.items():
+    for name in CASES:
         out.append((name, True))
-        if not kw.get("bf16"):
-            out.append((name, False))
+        out.append((name, False))
     return out
 
 
@@ -34,8 +33,8 @@ def test_layer_parity(name, tensor_cores, device, golden_dir):
     cfg, kw = CASES[name]
     case = synthetic.layer_case(cfg, **kw)
     world = L.LayerWorld(case, device, tensor_cores=tensor_cores)
-    if not kw.get("bf16"):
-        assert all(r.tensor_cores == tensor_cores for r in world.ranks), "the case did not take the expert path under test"
+    taken = [r.tensor_cores_bf16 if kw.get("bf16") else r.tensor_cores for r in world.ranks]
+    assert all(t == tensor_cores for t in taken), "the case did not take the expert path under test"
     world.run_interleaved()
     torch.cuda.synchronize()
     for r in world.ranks:
@@ -63,6 +62,29 @@ def test_expert_paths_agree_to_rounding(device):
             assert (pa == pb).float().mean() > 0.999
         za, zb = ra.zb.view(torch.bfloat16).float(), rb.zb.view(torch.bfloat16).float()
         assert ((za - zb).norm() / za.norm()).item() < 2e-3
+
+
+def test_bf16_expert_paths_agree_to_rounding(device):
+    """A bf16 layer's experts as the grouped tensor-core GEMM and on the CUDA-core kernels, from bit-identical routed rows:
+    both round the gate and up sums to bf16 before the SwiGLU, so the h rows differ only where an f32 sum in another order
+    crosses a bf16 rounding boundary (one ulp, on well under 1 % of the elements), and zb agrees to 4e-3."""
+    cfg, kw = CASES["small_bf16_global_tp8"]
+    case = synthetic.layer_case(cfg, **kw)
+    a = L.LayerWorld(case, device, tensor_cores=False)
+    b = L.LayerWorld(case, device, tensor_cores=True)
+    assert all(r.tensor_cores_bf16 for r in b.ranks) and not any(r.tensor_cores_bf16 for r in a.ranks)
+    for w in (a, b):
+        w.run_interleaved()
+    torch.cuda.synchronize()
+    for ra, rb in zip(a.ranks, b.ranks):
+        for r in (ra, rb):
+            st = r.launch_record.status(torch.cuda.current_stream().cuda_stream)
+            assert st.code == 0, (st.code, st.stage)
+        assert torch.equal(ra.o["ids"], rb.o["ids"]) and torch.equal(ra.o["xq"], rb.o["xq"])
+        ha, hb = ra.z.view(torch.bfloat16).float(), rb.z.view(torch.bfloat16).float()
+        assert (ha != hb).float().mean() < 0.01 and ((ha - hb).norm() / ha.norm()).item() < 2e-3
+        za, zb = ra.zb.view(torch.bfloat16).float(), rb.zb.view(torch.bfloat16).float()
+        assert ((za - zb).norm() / za.norm()).item() < 4e-3
 
 
 def test_b_live_pads(device, golden_dir):
@@ -344,20 +366,22 @@ def test_a_missing_peer_runs_the_wait_out_and_is_recorded(device):
     check_world(clean, [0])
 
 
-@pytest.mark.parametrize("global_attn", [False, True])
-def test_full_shape_layer_parity(global_attn, device):
+@pytest.mark.parametrize("global_attn,bf16", [(False, False), (True, False), (True, True)])
+def test_full_shape_layer_parity(global_attn, bf16, device):
     """The benchmark's own configuration as a whole layer: the full-shape model's TP8 world (hidden 8192, 16 query / 2 kv
     heads a rank, 256 experts top-8, expert width 4096) on one device, M = 16 rows over an 8192-token context, one
-    sliding-window and one global layer, NVFP4 experts on the tensor cores, dense GEMMs on tile images. Every stage of
+    sliding-window and one global layer, NVFP4 experts on the tensor cores (and a bf16-expert layer on the grouped
+    tensor-core GEMM), dense GEMMs on tile images. Every stage of
     ranks 0 and 7 against the oracle fed the kernels' own inputs, routing ids exact. The routing is confined to 24 hot
     experts (a +1 bias on them, as the reference's real-dims CPU test does) so that the CPU oracle holds the weights."""
     from sgl_muse_mega_b200.muse_spark.config import Config
 
     cfg = Config()
     hot = torch.randperm(cfg.experts, generator=torch.Generator().manual_seed(1))[:24]
-    case = synthetic.layer_case(cfg, rows=16, ctx=8192, global_attn=global_attn, band="baseline", seed=1, experts_subset=hot)
+    case = synthetic.layer_case(cfg, rows=16, ctx=8192, global_attn=global_attn, band="baseline", seed=1, experts_subset=hot,
+                                bf16=bf16)  # fmt: skip
     world = L.LayerWorld(case, device)
-    assert all(r.tensor_cores and r.packed == 2 for r in world.ranks)
+    assert all((r.tensor_cores_bf16 if bf16 else r.tensor_cores) and r.packed == 2 for r in world.ranks)
     world.run_interleaved()
     torch.cuda.synchronize()
     for r in world.ranks:
