@@ -124,7 +124,8 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
     uint64_t* acc_empty = bars + 2 * S + 4;  // [2]
     uint64_t* staged = bars + 2 * S + 6;     // [2] stager -> epilogue warps: rows, words and metadata of a unit are in place
     uint64_t* buf_free = bars + 2 * S + 8;   // [2] epilogue warps -> stager: the unit that used the buffer is finished
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * S + 10);
+    uint64_t* rows_first = bars + 2 * S + 10;  // stager -> producer (g1): the first unit's row loads are on their way
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * S + 11);
     volatile int* abort = (volatile int*)(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -141,6 +142,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
             mbar_init(&staged[i], 64);
             mbar_init(&buf_free[i], 128);
         }
+        mbar_init(rows_first, 64);
         *abort = 0;
         mbar_fence_init();
     }
@@ -166,6 +168,9 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
         if (lane == 0) {
             const uint64_t policy = policy_evict_first();  // expert weights are read once a step
             uint32_t it = 0;
+            // g1 starts everything at once behind the routing kernel: the first unit's rows (32 KB) are requested before the
+            // weight stream fills the memory system's queues with 21 MB, or they arrive behind it (4 us instead of 1)
+            if (!G2 && blockIdx.x < n_units) mbar_wait(rows_first, 0, abort);
             for (int u = blockIdx.x; u < n_units && !*abort; u += gridDim.x) {
                 const int e = rt->act_e[u / NB], blk = u % NB;
                 const unsigned char* src = a.wpack + ((size_t)(e * NB + blk) * KCH) * STAGE;
@@ -284,6 +289,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
                     if (view) xv[k] = *(const uint4*)(a.bex + (size_t)sl * (a.K / 16) + c * 16);
                 }
             }
+            if (j == 0) mbar_arrive(rows_first);  // the first unit's loads are issued: the weight stream may start (g1)
             if (view) {
                 // the row exponent of each routed slot = the largest of its K / 16 group exponents: four threads share a
                 // slot (a quarter of its exponent bytes each; tokens 0..7 on the first stager warp, 8..15 on the second)
@@ -459,7 +465,7 @@ size_t experts_umma_smem(bool g2) {
     const size_t stage = (g2 ? 1 : 2) * (size_t)(kTileBytes + kSfBytes);
     const int S = g2 ? 8 : 4;
     return 1024 + S * stage + 2 * kXsBytes + 2 * kMaxRows * 64 * 4 + 2 * sizeof(UnitMeta) + sizeof(RouteTables) + 16 +
-           (2 * S + 10) * 8 + 16;
+           (2 * S + 11) * 8 + 16;
 }
 
 cudaError_t experts_umma_prepare() {

@@ -53,9 +53,13 @@ __device__ __forceinline__ void xchg_signal(const XchgSignal& x) {
     if (x.n == 0) return;
     __syncthreads();
     if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
-        // Every CTA publishes its stores at device scope and arrives; the last one to arrive has thereby observed all of
-        // them and alone pays the system-scope fence (microseconds) that orders them before the peers' flag words.
-        __threadfence();
+        // Every CTA publishes its own stores at the scope of the receivers and arrives. With a peer among them that is a
+        // system-scope fence per CTA: the CTAs pay it one by one as they finish, under the kernel's tail; the last CTA to
+        // arrive has observed all of them and fences once more (nothing of its own is outstanding by then) before the
+        // flag words. (A device-scope fence per CTA and one system-scope fence in the last CTA put the whole cost of
+        // flushing the grid's peer stores behind the kernel's end.)
+        if (x.remote) __threadfence_system();
+        else __threadfence();
         const unsigned total = gridDim.x * gridDim.y * gridDim.z;
         if (atomicAdd(x.done, 1u) == total - 1) {
             *x.done = 0;
