@@ -422,7 +422,9 @@ def ranks_equal(state: dict, world: int) -> dict:
         t = t.contiguous()
         got = [torch.empty_like(t) for _ in range(world)]
         dist.all_gather(got, t)
-        res[name] = all(torch.equal(g.view(torch.uint8), got[0].view(torch.uint8)) for g in got[1:])
+        same = all(torch.equal(g.view(torch.uint8), got[0].view(torch.uint8)) for g in got[1:])
+        # equal, or how many elements of the worst rank differ from rank 0's
+        res[name] = True if same else {"differing_elements": max(int((g != got[0]).sum()) for g in got[1:]), "of": t.numel()}
     return res
 
 
@@ -857,7 +859,7 @@ def parity_n(world: int, dec: dict, emu: dict) -> dict:
     """The multi-GPU run's parity record: the timed model's end state equal on every rank, and the small model's world
     equal to the same world emulated on one GPU."""
     same = dec.get("ranks_equal") or {}
-    ok = bool(same) and all(same.values()) and bool(emu) and (emu["bit_equal"] or emu.get("ranks_bit_equal", False)) and not emu["status"]
+    ok = bool(same) and all(v is True for v in same.values()) and bool(emu) and (emu["bit_equal"] or emu.get("ranks_bit_equal", False)) and not emu["status"]
     return {"ranks": world, "bit_equal": ok, "timed_model_ranks_equal": same, "emulated_world": emu}
 
 

@@ -332,7 +332,7 @@ typedef struct MkAcceptBind {
     uint64_t out_ring;         // i32 [ring]
     int64_t ring;
     uint64_t top1;             // out i32 [rows]
-    uint64_t counter;          // u32 [1], zeroed once by the caller
+    uint64_t counter;          // u32 [512], zeroed once by the caller (arrival counters and the row chunks' winners)
     uint64_t cos_sin_cache;    // f32 [cos_sin_rows, 64]
     int64_t cos_sin_rows;
     uint64_t cos_sin;          // out: next target feeds (each may be 0)

@@ -138,8 +138,11 @@ class DraftRank:
         of = lambda name: [None if p is None else getattr(p, name) for p in peers]  # noqa: E731
         flags = self.x.flags
         fpeer = of("flags") if flags is not None else []
-        # a slice of a larger world (absent ranks): an id owned by an absent rank reads this rank's shard instead
-        embed = [self.x.embed if e is None else e for e in of("embed")]
+        # a slice of a larger world (absent ranks): an id owned by an absent rank reads a present rank's shard instead, the
+        # same one on every present rank (present rank number r mod present)
+        shards = of("embed")
+        here = [i for i, e in enumerate(shards) if e is not None]
+        embed = [shards[here[i % len(here)]] if e is None else e for i, e in enumerate(shards)]
         common = dict(ws=self.ws, flags=flags, flags_peer=fpeer, status=self.status, wait_budget=self.wait_budget, eps=cfg.rms_eps,
                       packed=int(self.packed))
         entry = host.make(

@@ -151,7 +151,7 @@ class Accept:
             self.words = _z(N_WORDS, dtype=torch.int64, device=dev)
             self.out_ring = _z(ring, dtype=torch.int32, device=dev)
             self.top1 = _z(rows, dtype=torch.int32, device=dev)
-            self.counter = _z(1, dtype=torch.int32, device=dev)
+            self.counter = _z(512, dtype=torch.int32, device=dev)  # arrival counters and the row chunks' winners
             self.dcos_sin = _z(2 * b_live, 128, dtype=torch.float32, device=dev) if draft else None
             self.dslot = _z(2 * b_live, dtype=torch.int32, device=dev) if draft else None
             self.dkv_len = _z(1, dtype=torch.int32, device=dev) if draft else None

@@ -209,8 +209,11 @@ class Stack:
         # the fused segment kernels only on request, and never for peers that live in this process (they are launched one
         # after the other on this GPU, and a segment's exchange waits poll for ranks that run at the same time)
         fused = self.fused and not any(isinstance(p, Stack) and p is not self for p in peers)
-        # the entry reads the owner rank's shard; an absent rank's rows read this rank's shard (a lone-rank timing run)
-        shards = [(v.embed if v is not None else self.view.embed) for v in views]
+        # the entry reads the owner rank's shard; in a slice of a larger world an absent rank's rows read a present rank's
+        # shard, the same one on every present rank (present rank number r mod present): the ranks must embed the same rows
+        # or their residual streams part ways
+        here = [i for i, v in enumerate(views) if v is not None]
+        shards = [(v.embed if v is not None else views[here[i % len(here)]].embed) for i, v in enumerate(views)]
         self.entry = HT.Entry(self.lib, self.module, ids=self.tokens, embed_shards=shards, pre_w=self.pre_w0,
                               eps_embed=cfg.rms_eps, eps_pre=cfg.rms_eps, shard_rows=cfg.vocab_rank, hidden=cfg.hidden,
                               residual=self.residual0, normed=self.normed0)  # fmt: skip
