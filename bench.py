@@ -959,7 +959,8 @@ def run_expert_block(args) -> None:
     from sgl_muse_mega_b200.muse_spark.b200 import expert_block as X
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device: there is no CPU fallback"
-    assert int(os.environ.get("WORLD_SIZE", "1")) == 1, "--config 2 emulates the expert-parallel ranks on one GPU"
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        return run_expert_block_world(args)
     device = torch.device("cuda:0")
     torch.cuda.set_device(device)
     lib = host.library()
@@ -1003,6 +1004,96 @@ def run_expert_block(args) -> None:
                 "note": "the block has no host-facing call of its own: the layer launch of --config 1 is the end-to-end path"},
     }  # fmt: skip
     print(json.dumps(line), flush=True)
+
+
+def run_expert_block_world(args) -> None:
+    """configs[2] on N GPUs, one process each: an expert-parallel world of N ranks with E / N whole experts a rank; g2 stores
+    its zb rows into every rank's zb, every rank's combine waits for all ranks. Per M in {1, 4, 8, 16}: g1 + g2 + combine
+    between CUDA events on every rank (L2 flushed and the ranks aligned before each sample), the block's time = the slowest
+    rank's median; the combined rows of every rank are compared bit for bit with rank 0's and with the same world emulated
+    on rank 0's GPU."""
+    import torch
+    import torch.distributed as dist
+
+    from sgl_muse_mega_b200.common import host
+    from sgl_muse_mega_b200.muse_spark.b200 import expert_block as X
+
+    world, rank, local = int(os.environ["WORLD_SIZE"]), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", device_id=device)
+    lib = host.library()
+    module = lib.load()
+    sampler = ClockSampler(local) if rank == 0 else None
+    cfg = X.block_config()
+    full = X.draw_case(cfg, 16, device, seed=args.seed)
+    peak, peak_kind = peaks()
+    iters = max(3, min(args.steps, 10))
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=device)
+    stream = torch.cuda.current_stream(device)
+    sweep, launches, equal = [], 0, True
+    for rows in (1, 4, 8, 16):
+        case = X.with_rows(full, rows)
+        blk = X.ExpertBlockRank(case, device, rank, world, lib=lib, module=module)
+        blk.run()
+        torch.cuda.synchronize()
+        dist.barrier()
+        assert blk.status() == 0, blk.status()
+        ys = [torch.empty_like(blk.y) for _ in range(world)]
+        dist.all_gather(ys, blk.y.contiguous())
+        same = all(torch.equal(y.view(torch.int16), ys[0].view(torch.int16)) for y in ys[1:])
+        emu_same = None
+        if rank == 0:
+            emu = X.ExpertBlock(case, device, ep=world, lib=lib, module=module)
+            emu.run()
+            torch.cuda.synchronize()
+            emu_same = bool(torch.equal(emu.ranks[0].o["y"], blk.y))
+            del emu
+            torch.cuda.empty_cache()
+        ts = []
+        for _ in range(iters + 2):
+            flush.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            blk.run_experts(stream.cuda_stream)
+            b.record(stream)
+            b.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3)
+        launches += 3 * (iters + 2)
+        mine = torch.tensor([sorted(ts[2:])[len(ts[2:]) // 2], float(blk.local_experts())], device=device)
+        every = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        us, d = [float(e[0]) for e in every], [int(e[1]) for e in every]
+        equal = equal and same and emu_same is not False
+        sweep.append({"rows": rows, "ep": world, "distinct_experts": d, "us": [round(t, 1) for t in us], "block_us": round(max(us), 1),
+                      "block_gb_s": round(sum(d) * X.EXPERT_BYTES / (max(us) * 1e-6) / 1e9, 1), "y_equal_on_every_rank": same,
+                      "y_equal_to_the_emulated_world": emu_same})  # fmt: skip
+        del blk
+        torch.cuda.empty_cache()
+        dist.barrier()
+    clocks = sampler.stop() if sampler else None
+    if rank == 0:
+        head = sweep[-1]
+        line = {
+            "metric": "isolated NVFP4 expert block: achieved HBM GB/s of the routed experts' weight bytes", "value": head["block_gb_s"],
+            "unit": "GB/s", "n_gpus": world, "steps": iters, "warmup": 2, "ms_per_step": head["block_us"] / 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 experts (e2m1 x e4m3 block scales), f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"configs[2]: isolated NVFP4 expert block, full expert shape, M in {{1,4,8,16}}, EP = {world} ranks on "
+                                   f"{world} B200s (whole experts per rank, zb rows exchanged through peer memory)",
+                       "l2": "flushed before every sample (512 MB write)", "headline": f"M=16, EP={world}",
+                       "timed": "g1 + g2 + combine (the combine waits for every rank's zb rows)"},
+            "roofline": {"bound": "hbm", "kernel": "experts_umma_kernel<g1> + <g2>", "achieved": head["block_gb_s"] / world,
+                         "peak": peak, "unit": "GB/s", "frac": head["block_gb_s"] / world / peak, "traffic": None, "peak_kind": peak_kind,
+                         "note": "per GPU: the block's bytes over the slowest rank's time, divided by the ranks"},
+            "parity_n": {"ranks": world, "bit_equal": equal},
+            "sweep": sweep, "gpu_launches": launches, "clocks": clocks, "cpu_baseline": None,
+            "e2e": {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                    "note": "the block has no host-facing call of its own: the layer launch of --config 1 is the end-to-end path"},
+        }  # fmt: skip
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
 
 
 def main() -> None:

@@ -230,6 +230,13 @@ typedef struct MkLayerBind {
     // 0 / 0: every expert (the reference's layout).
     int64_t expert_lo;
     int64_t expert_hi;
+    // An expert-parallel world of one process per GPU (ep_world > 1, with an expert range on a ranks = 1 shape and the packed
+    // NVFP4 images): this launch is rank ep_rank of ep_world; g2 stores its zb rows into every rank's zb (zb_peer[r], r <
+    // ep_world; zb_peer[ep_rank] may be 0 = zb) and signals the expert-output exchange in every rank's flag block
+    // (flags_peer[r]); combine waits for all ep_world ranks. 0 / 0: no such world (the ranks of an expert-parallel world
+    // emulated on one GPU share zb and run one after the other).
+    int64_t ep_rank;
+    int64_t ep_world;
 } MkLayerBind;
 int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind* bind, MkLaunch** out);
 

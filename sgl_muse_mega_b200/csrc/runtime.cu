@@ -253,6 +253,11 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     MK_REQUIRE((b->expert_lo == 0 && b->expert_hi == 0) || (b->expert_lo >= 0 && b->expert_lo < b->expert_hi && b->expert_hi <= E),
                "expert range [%lld, %lld) of %d experts", (long long)b->expert_lo, (long long)b->expert_hi, E);
     MK_REQUIRE(b->expert_hi == 0 || s.ranks == 1, "an expert range takes whole experts (ranks 1), got ranks %lld", (long long)s.ranks);
+    const int ep_world = (int)b->ep_world, ep_rank = (int)b->ep_rank;
+    MK_REQUIRE(ep_world == 0 || (ep_world >= 2 && ep_world <= kMaxRanks && ep_rank >= 0 && ep_rank < ep_world && b->expert_hi > 0 &&
+                                 b->flags != 0 && b->w1_pack != 0 && !s.bf16),
+               "an expert-parallel world needs 2..8 ranks, a rank inside it, an expert range, a flag block and the packed NVFP4 "
+               "images (ep_rank %lld, ep_world %lld)", (long long)b->ep_rank, (long long)b->ep_world);
     const bool fp4 = !s.bf16, tail = s.tail != 0;
 
     NEED(qkv_in); NEED(k_cache); NEED(v_cache); NEED(page_table); NEED(kv_len); NEED(x_attn);
@@ -542,6 +547,30 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
             u.n_peer = ex.n_peer;
             u.status = L->status;
             u.sig = g2 ? ex.sig_g2 : ex.sig_g1;
+        }
+        if (ep_world > 1) {
+            // whole experts per rank, one process per GPU: the h planes stay local, the zb rows of this rank's (row, slot)
+            // pairs go to every rank of the expert-parallel world, whose combines wait for all of them
+            UmmaArgs& u = L->umma_g2;
+            u.n_peer = 0;
+            memset(&u.sig, 0, sizeof u.sig);
+            for (int r = 0; r < ep_world; ++r) {
+                const uint64_t zb = r == ep_rank ? b->zb : b->zb_peer[r], fl = r == ep_rank ? b->flags : b->flags_peer[r];
+                MK_REQUIRE(zb != 0 && fl != 0, "zb_peer[%d] or flags_peer[%d] of the expert-parallel world is 0", r, r);
+                u.zb_peer[u.n_peer++] = (bf16*)zb;
+                u.sig.flag[u.sig.n++] = (unsigned*)fl + XP_ZB;
+                u.sig.remote |= r != ep_rank;
+            }
+            u.sig.done = flags + kXchgDone + XP_ZB;
+            u.sig.epoch = flags + kXchgEpoch + XP_ZB;
+            XchgWait& w = L->combine.wait;
+            memset(&w, 0, sizeof w);
+            w.flag = flags + XP_ZB;
+            w.epoch = flags + kXchgEpoch + XP_ZB;
+            w.contributors = (unsigned)ep_world;
+            w.budget = budget;
+            w.status = (int*)b->status;
+            w.stage = ST_COMBINE;
         }
         L->stage_on[ST_HROW] = false;
     }

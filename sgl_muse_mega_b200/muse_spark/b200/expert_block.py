@@ -9,6 +9,9 @@ pair is computed by exactly one rank with the same kernels, tiles and order.
 
 ``ExpertBlock`` holds the ``ep`` ranks of such a world on ONE device (``LayerRank`` objects of a lone-rank shape bound with
 ``MkLayerBind.expert_lo`` / ``expert_hi``, each keeping and packing its own experts only, all writing the same ``zb``).
+``ExpertBlockRank`` is one rank of the same world with one process per GPU: its zb rows and its flag block live in an
+arena the peers map (``common/symm.py``), g2 stores the zb rows of its (row, slot) pairs into every rank's zb and signals
+the expert-output exchange, and every rank's combine waits for all ranks (``MkLayerBind.ep_rank`` / ``ep_world``).
 The stages run through the C ABI by index: pooler + router (the block's inputs: h rows ~ N(0, 1) against N(0, 1 / H)
 weights give pooled rows and router logits ~ N(0, 1)), routing + pre-expert norm + input quantisation, g1, h-row view,
 g2 on every rank, then one combine. ``time_experts`` times the expert kernels (g1, g2) of each rank between CUDA events with
@@ -22,7 +25,7 @@ from typing import Optional
 
 import torch
 
-from ...common import host
+from ...common import host, symm
 from ..config import Config
 from . import layer as L
 from . import synthetic
@@ -114,3 +117,72 @@ class ExpertBlock:
                 ts.append(a.elapsed_time(b) * 1e3)
             out.append(sorted(ts[2:])[len(ts[2:]) // 2])
         return out
+
+
+def ep_layout(zb_bytes: int) -> symm.Layout:
+    """The arena of one rank of an expert-parallel world: its flag block and its zb rows."""
+    lay = symm.Layout()
+    lay.add("flags", (64,), torch.int32)
+    lay.add("zb", (zb_bytes,), torch.uint8)
+    return lay
+
+
+class _EpPeer:
+    """A peer's zb rows and flag block by device address (its arena, mapped)."""
+
+    def __init__(self, arena):
+        self.arena, self.zb, self.flags = arena, arena.ptr("zb"), arena.ptr("flags")
+
+
+class ExpertBlockRank:
+    """Rank ``rank`` of an expert-parallel world of ``world`` processes, one per GPU (``torch.distributed`` initialised: it
+    only swaps the arenas' handles). Every rank draws the same case (same seed) and keeps its experts
+    [rank E / world, (rank + 1) E / world); the block's input rows are the same on every rank, so every rank routes alike.
+    ``run`` enqueues pooler + router, routing, g1, g2 and the combine; afterwards ``y`` holds the combined rows on every
+    rank."""
+
+    def __init__(self, case, device, rank: int, world: int, lib: Optional[host.Library] = None, module=None, seed: int = 0,
+                 group=None, wait_budget: int = 1 << 24):  # fmt: skip
+        cfg = case.cfg
+        assert cfg.tp == 1 and cfg.experts % world == 0 and world >= 2
+        self.lib = lib or host.library()
+        self.case, self.device, self.rank, self.world, self.rows = case, device, rank, world, case.rows
+        with torch.cuda.device(device):
+            self.module = module or self.lib.load()
+        c = self.lib.layer_constants(L.layer_shape(cfg, case, 0))
+        self.arena = symm.Arena(self.lib, ep_layout(int(c.zb_bytes)), device)
+        per = cfg.experts // world
+        self.lr = L.LayerRank(self.lib, self.module, case, 0, device, tensors=case.ranks[0], keep_plain_experts=False,
+                              io={"zb": self.arena.tensor("zb"), "flags": self.arena.tensor("flags")},
+                              expert_range=(rank * per, (rank + 1) * per))  # fmt: skip
+        arenas = symm.connect(self.arena, rank, world, group, self.lib)
+        self.peers = [None if r == rank else _EpPeer(a) for r, a in enumerate(arenas)]  # the mappings live with this object
+        self.lr.bind(ep_peers=self.peers, ep_rank=rank, wait_budget=wait_budget)
+        g = torch.Generator(device=device)
+        g.manual_seed(1000 + seed)
+        h = torch.randn(case.rows, cfg.hidden, generator=g, device=device).to(torch.bfloat16)
+        self.lr.o["h3"].copy_(h)
+        self.lr.o["h3f"].copy_(h.float())
+        import torch.distributed as dist
+
+        dist.barrier(group)  # every rank is bound before any rank launches (a launch stores into the peers' zb)
+
+    @property
+    def y(self) -> torch.Tensor:
+        return self.lr.o["y"]
+
+    def run(self, stream: Optional[int] = None) -> None:
+        s = torch.cuda.current_stream(self.device).cuda_stream if stream is None else stream
+        self.lr.launch_record.step(s, ST_POOLER, ST_COMBINE - ST_POOLER + 1)
+
+    def run_experts(self, stream: int) -> None:
+        """g1, g2 and the combine (which waits for every rank's zb rows): what ``time_block`` times."""
+        self.lr.launch_record.step(stream, ST_G1, ST_COMBINE - ST_G1 + 1)
+
+    def status(self) -> int:
+        return self.lr.launch_record.status(torch.cuda.current_stream(self.device).cuda_stream).code
+
+    def local_experts(self) -> int:
+        ids = self.lr.o["ids"][: self.rows].flatten().cpu()
+        per = self.case.cfg.experts // self.world
+        return int(torch.unique(ids[(ids >= self.rank * per) & (ids < (self.rank + 1) * per)]).numel())

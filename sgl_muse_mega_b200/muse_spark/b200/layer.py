@@ -172,7 +172,8 @@ class LayerRank:
         self.module = module
         self.launch_record = None
 
-    def bind(self, peers: Optional[list] = None, b_live: int = 0, wait_budget: int = 0, fused: Optional[bool] = None):
+    def bind(self, peers: Optional[list] = None, b_live: int = 0, wait_budget: int = 0, fused: Optional[bool] = None,
+             ep_peers: Optional[list] = None, ep_rank: int = 0):
         """Binds the launch; ``peers`` = per rank an object whose attributes ``ar``, ``pool_ag``, ``unpool_ag``, ``z``,
         ``z_sf``, ``z_ex``, ``zb``, ``flags`` are that rank's exchange buffers (tensors, or device addresses of buffers
         mapped from another process): every rank's ``LayerRank`` (own included), or None for a lone rank.
@@ -181,7 +182,10 @@ class LayerRank:
         experts (7 kernels a layer): on tile images (``packed`` 2) the fused tensor-core kernels, on ``packed`` 0 or 1 the
         segment kernels of the item engine (
         measured slower on the full shape, and never for peers launched one after the other on one GPU: its exchange
-        waits poll for ranks that run at the same time), 2 = one launch per stage with the cluster split-K GEMMs (14)."""
+        waits poll for ranks that run at the same time), 2 = one launch per stage with the cluster split-K GEMMs (14).
+        ``ep_peers`` / ``ep_rank``: an expert-parallel world of one process per GPU (``expert_range`` given): per rank an
+        object with ``zb`` and ``flags`` (this rank's own entry may be None); g2 writes its zb rows into every rank's zb
+        and the combine waits for all ranks."""
         fused = int(fused or 0)
         if fused == 2 and self.packed == 2:
             raise RuntimeError("dense_packed 2 (tile images) has no cluster split-K form: build the rank with packed=0 for fused=2")
@@ -194,6 +198,12 @@ class LayerRank:
             return [getattr(p, attr) if p is not None else None for p in peers]
 
         fp4 = not case.bf16
+        zb_peer, flags_peer, ep_world = peer("zb"), peer("flags"), 0
+        if ep_peers is not None:
+            assert self.expert_hi and peers is None, "an expert-parallel world binds a lone-rank shape with an expert range"
+            ep_world = len(ep_peers)
+            zb_peer = [self.zb if r == ep_rank else getattr(ep_peers[r], "zb") for r in range(ep_world)]
+            flags_peer = [self.flags if r == ep_rank else getattr(ep_peers[r], "flags") for r in range(ep_world)]
 
         def ex(t):
             """A per-expert array's address as the kernels index it (by the global expert id)."""
@@ -215,14 +225,14 @@ class LayerRank:
             w1_up=ex(w["up_q"] if fp4 else w["up"]), w1_up_sf=ex(w["up_sf"]), w2=ex(w["w2_q"] if fp4 else w["w2"]),
             w2_sf=ex(w["w2_sf"]), w1_pack=ex(self.w1_pack), w2_pack=ex(self.w2_pack), g1_alphas=ex(w["g1_alphas"]),
             g1_scale_c=ex(w["g1_scale_c"]), g2_alphas=ex(w["g2_alphas"]), z=self.z, z_sf=self.z_sf, z_ex=self.z_ex, zb=self.zb,
-            z_peer=peer(self.z_name), zsf_peer=peer("z_sf"), zex_peer=peer("z_ex"), zb_peer=peer("zb"),
+            z_peer=peer(self.z_name), zsf_peer=peer("z_sf"), zex_peer=peer("z_ex"), zb_peer=zb_peer,
             gamma_p1=w["gamma_p1"], y=o["y"], w_up=w["unpooler"], unpool_ag=self.unpool_ag,
             unpool_ag_peer=peer("unpool_ag"), c_alpha=w["cross_alpha"], c_beta=w["cross_beta"], c_pre_w=w["cross_pre_w"],
             c_post_w=w["cross_post_w"], c_stream_out=o["stream_out"], h3q=o["h3_next"], w_qkv=w["next_qkv"],
             qkv_out=o["qkv_next"], cos_sin=w["next_cos_sin"], cache_loc=self.cache_loc, next_k_cache=self.next_k,
             next_v_cache=self.next_v, next_kv_rows=self.next_kv_rows, q_scale=cfg.q_scale, qkv_eps=cfg.rms_eps,
-            flags=self.flags, flags_peer=peer("flags"), ws=self.ws, status=self.status, b_live=b_live, wait_budget=wait_budget, fused=fused, dense_packed=int(self.packed),
-            expert_lo=self.expert_lo, expert_hi=self.expert_hi,
+            flags=self.flags, flags_peer=flags_peer, ws=self.ws, status=self.status, b_live=b_live, wait_budget=wait_budget, fused=fused, dense_packed=int(self.packed),
+            expert_lo=self.expert_lo, expert_hi=self.expert_hi, ep_rank=ep_rank if ep_world else 0, ep_world=ep_world,
         )  # fmt: skip
         self.launch_record = self.lib.layer_bind(self.module, self.shape, bind)
         return self.launch_record

@@ -215,3 +215,74 @@ def test_two_gpu_draft_matches_the_emulated_world():
         for step in range(2):
             for k in ("y", "ids", "scores", "logits"):
                 assert torch.equal(got[r]["res"][step][k], ref[r][k]), (r, step, k)
+
+
+# ---- the expert block with whole experts per rank across two GPUs ------------------------------------------------------------
+
+
+def _ep_case(device):
+    from sgl_muse_mega_b200.muse_spark.b200 import expert_block as X
+
+    return X.draw_case(X.block_config(experts=16, moe_hidden=1024, moe_inter=1024), 16, device, seed=4)
+
+
+def _ep_rank_main(rank, world, port, out):
+    import torch.distributed as dist
+
+    from sgl_muse_mega_b200.muse_spark.b200 import expert_block as X
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    device = torch.device(f"cuda:{rank}")
+    torch.cuda.set_device(device)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        blk = X.ExpertBlockRank(_ep_case(device), device, rank, world, seed=2)
+        res = []
+        for _ in range(2):  # a second run on the same buffers: the exchange's epochs advance, the values stay
+            blk.run()
+            torch.cuda.synchronize()
+            dist.barrier()  # no rank starts the next run (stores into the peers' zb) while a peer's combine still reads
+            res.append(dict(y=blk.y.cpu().clone(), zb=blk.lr.zb.cpu().clone(), ids=blk.lr.o["ids"].cpu().clone()))
+        out[rank] = dict(res=res, status=blk.status(), local=blk.local_experts())
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_expert_parallel_block_matches_the_emulated_world():
+    """Whole experts per rank, one process per GPU: each rank's g2 stores the zb rows of its (row, slot) pairs into both
+    ranks' zb and both combines wait for both ranks; y and zb on either GPU are bit-identical to the same world with its
+    ranks launched one after the other on one GPU (and so to the lone rank that holds every expert)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from sgl_muse_mega_b200.muse_spark.b200 import expert_block as X
+
+    world = 2
+    dev = torch.device("cuda:0")
+    emu = X.ExpertBlock(_ep_case(dev), dev, ep=world, seed=2)
+    emu.run()
+    torch.cuda.synchronize()
+    assert emu.statuses() == [0, 0]
+    ref = dict(y=emu.ranks[0].o["y"].cpu(), zb=emu.zb.cpu(), ids=emu.ranks[0].o["ids"].cpu())
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as m:
+        out = m.dict()
+        port = 29400 + os.getpid() % 200
+        procs = [ctx.Process(target=_ep_rank_main, args=(r, world, port, out)) for r in range(world)]
+        for p in procs:
+            p.start()
+        try:
+            for p in procs:
+                p.join(600)
+                assert p.exitcode == 0, f"rank process exit code {p.exitcode}"
+        finally:
+            for p in procs:  # only the processes started above, by handle
+                if p.is_alive():
+                    p.kill()
+        got = dict(out)
+    assert [got[r]["local"] for r in range(world)] == emu.local_experts()
+    for r in range(world):
+        assert got[r]["status"] == 0, got[r]["status"]
+        for i in range(2):
+            for k in ("ids", "zb", "y"):
+                assert torch.equal(got[r]["res"][i][k], ref[k]), (r, i, k)
