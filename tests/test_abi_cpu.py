@@ -123,6 +123,30 @@ def test_expert_range_binds_whole_experts_only(lib):
         r2.bind()
 
 
+def test_expert_parallel_world_binds_every_ranks_zb_and_flags(lib):
+    """One process per GPU with whole experts per rank: the bind takes every rank's zb rows and flag block (here: device
+    addresses of a peer's mapped arena) and refuses a world with a missing peer, without an expert range or without the
+    packed images."""
+    from types import SimpleNamespace as NS
+
+    from sgl_muse_mega_b200.muse_spark.b200 import expert_block as X
+
+    cfg = X.block_config(experts=16, moe_hidden=1024, moe_inter=1024)
+    case = synthetic.layer_case(cfg, rows=4, ctx=8, seed=5)
+    rank = L.LayerRank(lib, None, case, 0, torch.device("cpu"), expert_range=(8, 16))
+    peer = NS(zb=0x7F0000001000, flags=0x7F0000002000)
+    assert rank.bind(ep_peers=[peer, None], ep_rank=1).info().kernels == 12
+    with pytest.raises(RuntimeError, match="zb_peer\\[0\\] or flags_peer\\[0\\]"):
+        rank.bind(ep_peers=[NS(zb=0, flags=0), None], ep_rank=1)
+    with pytest.raises(ValueError, match="exceed 8"):
+        rank.bind(ep_peers=[peer] * 9, ep_rank=1)
+    plain = L.LayerRank(lib, None, case, 0, torch.device("cpu"), expert_range=(8, 16), tensor_cores=False)
+    with pytest.raises(RuntimeError, match="expert-parallel world needs"):
+        plain.bind(ep_peers=[peer, None], ep_rank=1)
+    lay = X.ep_layout(4096)
+    assert lay.offset("flags") == 0 and lay.offset("zb") >= 256
+
+
 def test_module_load_needs_builtin_image(lib):
     out = ctypes.c_void_p()
     assert lib.dll.mk_module_load(b"xx", 2, None, ctypes.byref(out)) == -1
