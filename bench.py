@@ -62,6 +62,9 @@ def parse():
                          "the accept length stays forced)")
     ap.add_argument("--top-k", type=int, default=1 << 30)
     ap.add_argument("--top-p", type=float, default=1.0)
+    ap.add_argument("--tree", action="store_true",
+                    help="whole-step leg with the DFlash2 token tree (tree walk, ancestor-masked attention, tree accept, "
+                         "compaction); --accept then names the forced leaf ROW, the accept length is its depth")
     ap.add_argument("--accept", type=int, default=5, help="forced accept length of the whole-step leg (5 drafts + the bonus = 6 tokens a step)")
     args = ap.parse_args()
     if args.ctx is None:
@@ -242,7 +245,7 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
         assert not args.no_draft, "the sampled accept reads the draft head's candidates"
         sampling = sampling_words(args.seed, 0, args.temperature, args.top_k, args.top_p)
     st = S.Stack(case, tp_rank, device, lib, module, arena=arena, kv_rows=kv_rows, keep_plain_experts=False,
-                 accept_override=forced, wait_budget=1 << 25, sampling=sampling, fused=args.form == 4)  # fmt: skip
+                 accept_override=forced, wait_budget=1 << 25, sampling=sampling, fused=args.form == 4, tree=args.tree)  # fmt: skip
     peers = S.connect_world(st) if world > 1 else st.bind()
     s = stream.cuda_stream
     # the DFlash2 draft at its public size (this rank's TP slice, synthetic weights drawn on the device): with it the step
@@ -293,6 +296,7 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
             step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    pos0 = int(st.accept.words[0].item())
     with torch.cuda.stream(stream):
         e0.record(stream)
         for _ in range(K):
@@ -300,6 +304,8 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
         e1.record(stream)
     barrier()
     step_ms = max_over_ranks(e0.elapsed_time(e1) / K)
+    # tokens a step as the position word counts them (a tree's forced leaf row has the depth its lattice gives it)
+    committed = (int(st.accept.words[0].item()) - pos0) / K
     # ---- the layers alone (eager launches with programmatic dependent launch), same exchange partners ----
     with torch.cuda.stream(stream):
         for lr in st.layers:
@@ -380,7 +386,11 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
     e2e_ms = max_over_ranks((time.perf_counter() - t0) / K * 1e3)
     bad = st.statuses()
     assert bad == [], f"device status after the whole-step leg: {bad}"
-    assert int(h_words[2]) == args.accept and int(h_words[3]) == commit, h_words.tolist()
+    if args.tree:
+        assert 0 <= int(h_words[2]) <= args.accept and int(h_words[3]) == int(h_words[2]) + 1, h_words.tolist()
+        commit = committed
+    else:
+        assert int(h_words[2]) == args.accept and int(h_words[3]) == commit and committed == commit, h_words.tolist()
     d_list = [int(torch.unique(lr.o["ids"]).numel()) for lr in st.layers]
     byts = [layer_bytes(cfg, d, int(h_words[0]), rows, lr.case.global_attn) for d, lr in zip(d_list, st.layers)]
     for b, lr in zip(byts, st.layers):
@@ -397,6 +407,7 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
         "present_ranks": world if world > 1 else 1, "model_ranks": cfg.tp,
         "draft": draft if draft is not None else "not in the step (--no-draft): ids come from the host",
         "sampling": "greedy" if sampling is None else {"temperature": args.temperature, "top_k": args.top_k, "top_p": args.top_p},
+        "window": "token tree (forced leaf row %d)" % args.accept if args.tree else "chain",
     }  # fmt: skip
     if it is not None:
         bad = it.statuses()

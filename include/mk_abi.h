@@ -237,6 +237,11 @@ typedef struct MkLayerBind {
     // emulated on one GPU share zb and run one after the other).
     int64_t ep_rank;
     int64_t ep_world;
+    // A token-tree window (0: a chain): the table mk_dflash_tree_bind's launch writes (i32 [96]). The attention then places
+    // row r at position context + depth[r] and lets it see, of the window's own rows, the rows of its ancestor mask (every
+    // context key is its past); the K / V rows are still appended at the window's slots in row order (the compaction moves
+    // the accepted path's rows afterwards), and cos_sin must hold the rows' rotations by depth (the tree's launch writes them).
+    uint64_t tree;
 } MkLayerBind;
 int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind* bind, MkLaunch** out);
 
@@ -370,6 +375,11 @@ typedef struct MkAcceptBind {
     int64_t sample_ws_bytes;
     uint64_t sample_out;       // out f64 [16] or 0: [0] the residual's scale, [1] the mass of the bonus distribution
                                // (the rest is written by trace builds only)
+    // The token tree (greedy accept only): the table mk_dflash_tree_bind's launch wrote (i32 [96]), or 0 for a chain. The
+    // accept then takes the deepest row whose token and all of whose ancestors' tokens equal the target's arg-max at their
+    // parents (accept_override names the leaf row instead), commits the path's tokens and the bonus, and writes the path
+    // into the table ([48] the accept length, [48 + i] the window row at depth i) for mk_dflash_tree_compact_bind.
+    uint64_t tree;
 } MkAcceptBind;
 int mk_accept_bind(MkModule* module, const MkAcceptBind* bind, MkLaunch** out);
 
@@ -592,6 +602,41 @@ int mk_dflash_draft_head_bind(MkModule* module, const MkDflashShape* shape, cons
 // pools into the serving engine's draft pool at the slots it allocated. state i64 [17]: the position the pool is complete
 // to, then the slots of the next positions. A pool and ring that disagree by more than 16 rows copy nothing and record
 // status code 4 (the reference traps).
+// The token tree (reference kernels/dflash/tree.cuh). mk_dflash_tree_bind: the draft head's tree walk, after its lattice:
+// the window's 16 rows as a tree over the candidates (best-first by path log-probability, four successors a row, preorder),
+// table i32 [96] = parent[16] (-1 for the anchor), depth[16], ancestor mask[16], path[16] (the accept's), the window rows'
+// slots in the full and the sliding-window pools (copied from loc_full / loc_swa when given); verify_ids = the rows' tokens;
+// cos_sin = the target's rotation feeds of the window rewritten by depth.
+typedef struct MkDflashTreeBind {
+    uint64_t cand;        // i64 [rows - 1][16]
+    uint64_t scores;      // f32 [rows - 1][16][16]
+    uint64_t words;       // the step words (the anchor)
+    uint64_t table;       // out i32 [96]
+    uint64_t verify_ids;  // out i64 [rows]
+    uint64_t loc_full;    // i32 [rows] or 0
+    uint64_t loc_swa;     // i32 [rows] or 0
+    int64_t rows;         // 16
+    uint64_t cos_sin_cache;  // f32 [cos_sin_rows][64] or 0
+    int64_t cos_sin_rows;
+    uint64_t cos_sin;        // out f32 [rows][64] or 0: the target's rotation rows of the window, row r at P + depth(r)
+} MkDflashTreeBind;
+int mk_dflash_tree_bind(MkModule* module, const MkDflashTreeBind* bind, MkLaunch** out);
+
+// mk_dflash_tree_compact_bind (reference abi.h mk_dflash_tree_compact, tree.cuh:251-298): after the tree accept, the row at
+// depth i (1 .. accept) of every K / V pool and capture buffer takes the bytes of the accepted path's row. rows: a device
+// array of base pointers, the sliding-window pools first (rows addressed through the table's sliding-window slots), then
+// the full pools, then the capture buffers (rows addressed by window row).
+typedef struct MkDflashTreeCompactBind {
+    uint64_t table;
+    uint64_t rows;          // u64 [n_swa + n_full + n_cap]
+    int64_t n_swa;
+    int64_t n_full;
+    int64_t n_cap;
+    int64_t kv_row_bytes;   // multiple of 16
+    int64_t cap_row_bytes;  // multiple of 16
+} MkDflashTreeCompactBind;
+int mk_dflash_tree_compact_bind(MkModule* module, const MkDflashTreeCompactBind* bind, MkLaunch** out);
+
 typedef struct MkDflashKvSyncBind {
     uint64_t words;
     uint64_t window;   // i64 [16]

@@ -81,7 +81,8 @@ EXPORTS = (
     "mk_launch_info", "mk_launch_status", "mk_layer_constants", "mk_layer_bind", "mk_qkv_constants", "mk_qkv_bind",
     "mk_qkv_launch_static", "mk_feeds_bind", "mk_entry_bind", "mk_lm_head_bind", "mk_softcap_bind", "mk_accept_bind",
     "mk_symm_alloc", "mk_symm_open", "mk_symm_close", "mk_symm_free", "mk_dflash_constants", "mk_dflash_entry_bind",
-    "mk_dflash_layer_bind", "mk_dflash_draft_head_bind", "mk_dflash_kv_sync_bind",
+    "mk_dflash_layer_bind", "mk_dflash_draft_head_bind", "mk_dflash_kv_sync_bind", "mk_dflash_tree_bind",
+    "mk_dflash_tree_compact_bind",
 )  # fmt: skip
 
 
@@ -117,6 +118,8 @@ class Library:
                        ("mk_dflash_draft_head_bind", "MkDflashDraftHeadBind")):  # fmt: skip
             getattr(d, fn).argtypes = [vp, P(STRUCTS["MkDflashShape"]), P(STRUCTS[st]), P(vp)]
         d.mk_dflash_kv_sync_bind.argtypes = [vp, P(STRUCTS["MkDflashKvSyncBind"]), P(vp)]
+        d.mk_dflash_tree_bind.argtypes = [vp, P(STRUCTS["MkDflashTreeBind"]), P(vp)]
+        d.mk_dflash_tree_compact_bind.argtypes = [vp, P(STRUCTS["MkDflashTreeCompactBind"]), P(vp)]
         d.mk_symm_alloc.argtypes = [ctypes.c_int64, P(ctypes.c_uint64), ctypes.c_char_p]
         d.mk_symm_open.argtypes = [ctypes.c_char_p, P(ctypes.c_uint64)]
         d.mk_symm_close.argtypes = [ctypes.c_uint64]

@@ -48,7 +48,7 @@ __device__ __forceinline__ AttnSpan attn_span(const AttnArgs& a, int kv_len) {
     return sp;
 }
 
-__global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs a) {
+__global__ void __launch_bounds__(256, 2) attn_split_kernel(const AttnArgs a) {
     __shared__ __align__(128) unsigned char Ks[2][kKeyBlock * 128];
     __shared__ __align__(128) unsigned char Vs[2][kKeyBlock * 128];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -78,7 +78,12 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs a) {
             qa[kk][3] = r1 < a.R ? *(const uint32_t*)(q1 + 16 * kk + 8 + 2 * t) : 0u;
         }
     }
-    const int posq0 = n_ctx + r0 / a.G, posq1 = n_ctx + r1 / a.G;
+    // a row's position and, for a token-tree window (draft.h: the table's depth and ancestor-mask words), the window rows it
+    // sees: a chain's row t sits at n_ctx + t and sees every earlier row; a tree's row sits at n_ctx + its depth and sees
+    // its ancestors
+    const int tq0 = min(r0 / a.G, a.M - 1), tq1 = min(r1 / a.G, a.M - 1);
+    const int posq0 = n_ctx + (a.tree != nullptr ? a.tree[16 + tq0] : r0 / a.G), posq1 = n_ctx + (a.tree != nullptr ? a.tree[16 + tq1] : r1 / a.G);
+    const unsigned tmask0 = a.tree != nullptr ? (unsigned)a.tree[32 + tq0] : 0u, tmask1 = a.tree != nullptr ? (unsigned)a.tree[32 + tq1] : 0u;
 
     auto load_block = [&](int b, int st) {
         const int p0 = lo + b * kKeyBlock;
@@ -134,7 +139,8 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs a) {
             for (int c = 0; c < 4; ++c) {
                 const int p = pbase + 8 * j + 2 * t + (c & 1);
                 const int pq = (c & 2) ? posq1 : posq0;
-                const bool v = p <= pq && p < kv_len && (a.window <= 0 || p + a.window >= pq);
+                const bool own = a.tree == nullptr ? p <= pq : (p < n_ctx || ((((c & 2) ? tmask1 : tmask0) >> (p - n_ctx)) & 1u));
+                const bool v = own && p < kv_len && (a.window <= 0 || p + a.window >= pq);
                 vis[j][c] = v;
                 s[j][c] *= kScaleLog2e;
                 if (v) {

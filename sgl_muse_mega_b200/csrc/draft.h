@@ -129,10 +129,35 @@ struct DKvSyncArgs {
     int* status;
 };
 
+// tree.cu: the token tree. The table's words (i32): parent, depth, ancestor mask, accepted path ([0] the accept length,
+// [i] the window row at depth i), the window rows' slots in the full and the sliding-window pools.
+constexpr int kTreeRows = 16;
+constexpr int kTreeParent = 0, kTreeDepth = 16, kTreeMask = 32, kTreePath = 48, kTreeSlotFull = 64, kTreeSlotSwa = 80, kTreeWords = 96;
+constexpr int kCompactCapCtas = 4;
+struct DTreeArgs {
+    const long long* cand;   // [rows - 1][16]
+    const float* scores;     // [rows - 1][16][16]
+    const long long* words;  // the anchor
+    int* table;              // out [kTreeWords]
+    long long* verify_ids;   // out [rows]: the rows' tokens in preorder
+    const int* loc_full;     // [rows] the window rows' pool slots (or null)
+    const int* loc_swa;
+    int rows;
+    const float* cos_sin_cache;  // f32 [cos_sin_rows][64] or null
+    long long cos_sin_rows;
+    float* cos_sin;              // out [rows][64]: the target's rotation rows, row r at position P + depth(r)
+};
+struct DCompactArgs {
+    const int* table;                 // the path and the window's slots
+    const unsigned long long* rows;   // [n_swa + n_full + n_cap] base pointers: sliding-window pools, full pools, capture buffers
+    int n_swa, n_full, n_cap;
+    int kv_row_bytes, cap_row_bytes;  // multiples of 16
+};
+
 // One kernel of a draft launch record (the host walks an array of these).
 enum DraftOpKind {
     DOP_FEATS = 1, DOP_GEMM, DOP_NORM, DOP_CONV, DOP_QKV_ROWS, DOP_CTX_KV, DOP_ATTN_SPLIT, DOP_ATTN_MERGE, DOP_TOPK, DOP_LATTICE,
-    DOP_KV_SYNC
+    DOP_KV_SYNC, DOP_TREE, DOP_COMPACT
 };
 struct DraftOp {
     int kind;
@@ -147,6 +172,8 @@ struct DraftOp {
         DTopkArgs topk;
         DLatticeArgs lat;
         DKvSyncArgs sync;
+        DTreeArgs tree;
+        DCompactArgs compact;
     };
 };
 
@@ -160,6 +187,8 @@ cudaError_t dattn_merge_launch(const DAttnArgs& a, cudaStream_t s, bool pdl);
 cudaError_t dtopk_launch(const DTopkArgs& a, cudaStream_t s, bool pdl);
 cudaError_t dlattice_launch(const DLatticeArgs& a, cudaStream_t s, bool pdl);
 cudaError_t dkv_sync_launch(const DKvSyncArgs& a, cudaStream_t s, bool pdl);
+cudaError_t dtree_walk_launch(const DTreeArgs& a, cudaStream_t s, bool pdl);
+cudaError_t tree_compact_launch(const DCompactArgs& a, cudaStream_t s, bool pdl);
 cudaError_t draft_prepare();
 size_t dattn_smem();
 

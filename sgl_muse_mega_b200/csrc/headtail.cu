@@ -10,6 +10,7 @@
 //                  the committed-token ring and the next step's feeds
 //                  (reference kernels/dflash/verify_accept.cu:304-400, test/reference/dflash2.py:362-368,649-660)
 #include "stages.h"
+#include "draft.h"
 
 namespace mk {
 
@@ -133,7 +134,8 @@ __device__ __forceinline__ void commit_and_feed(const AcceptArgs& a, int acc, lo
     if (tid == 0) {
         const long long p = a.words[0], iter = a.words[4], cnt = a.words[5];
         const long long cc = acc + 1;
-        for (int j = 0; j < acc; ++j) a.out_ring[(cnt + j) % a.ring] = (int)a.tokens[j + 1];
+        // the accepted drafts: rows 1 .. acc of a chain, the accepted path's rows of a tree
+        for (int j = 0; j < acc; ++j) a.out_ring[(cnt + j) % a.ring] = (int)a.tokens[a.tree != nullptr ? a.tree[kTreePath + j + 1] : j + 1];
         a.out_ring[(cnt + acc) % a.ring] = (int)bonus;
         a.words[0] = p + cc;   // P: committed length
         a.words[1] = bonus;    // ANCHOR: next block's row 0
@@ -248,7 +250,29 @@ __global__ void __launch_bounds__(1024) accept_kernel(const AcceptArgs a) {
     if (!s_last) return;
     __threadfence();
     // ---- the accept (one thread), then the next iteration's feeds (all threads) ----
-    if (tid == 0) {
+    if (tid == 0 && a.tree != nullptr) {
+        // The token tree's accept (test/reference/dflash2.py:1375-1391): a row matches when its token is the target's
+        // arg-max at its parent; it is accepted when it and all its ancestors match; the rows are in preorder, so the
+        // accepted path's leaf is the largest accepted row. The forced table names the leaf row instead.
+        const long long iter = a.words[4];
+        unsigned match = 1u;
+        for (int r = 1; r < a.b_live; ++r)
+            if (a.tokens[r] == (long long)__ldcg(a.top1 + a.tree[kTreeParent + r])) match |= 1u << r;
+        int leaf = 0;
+        for (int r = 1; r < a.b_live; ++r)
+            if (((unsigned)a.tree[kTreeMask + r] & ~match) == 0u) leaf = r;
+        if (a.accept_override != nullptr) {
+            const int f = a.accept_override[iter % a.n_override];
+            leaf = f < 0 ? 0 : min(f, a.b_live - 1);
+        }
+        const unsigned on = (unsigned)a.tree[kTreeMask + leaf];
+        int n = 0;
+        for (int r = 1; r < a.b_live; ++r)
+            if ((on >> r) & 1u) a.tree[kTreePath + ++n] = r;  // the window rows at depths 1 .. n
+        a.tree[kTreePath] = n;
+        s_acc = n;
+        s_bonus = __ldcg(a.top1 + leaf);
+    } else if (tid == 0) {
         const long long iter = a.words[4];
         int acc = 0;
         while (acc + 1 < a.b_live && a.tokens[acc + 1] == (long long)__ldcg(a.top1 + acc)) ++acc;

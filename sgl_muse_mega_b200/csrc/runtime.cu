@@ -372,7 +372,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     // attention
     L->attn = AttnArgs{(const bf16*)b->qkv_in, (const unsigned char*)b->k_cache, (const unsigned char*)b->v_cache,
                        (const long long*)b->page_table, (const int*)b->kv_len, attn_ws, (bf16*)b->x_attn,
-                       M, qh, kvh, G, R, (int)c.qkv_row, (int)s.window, (int)c.attn_splits};
+                       M, qh, kvh, G, R, (int)c.qkv_row, (int)s.window, (int)c.attn_splits, (const int*)b->tree};
     // GEMMs
     (void)gpart;
     (void)gcnt;
@@ -878,6 +878,8 @@ static int run_dops(const MkLaunch* L, int first, int last, cudaStream_t s, bool
             case DOP_TOPK: e = dtopk_launch(op.topk, s, pdl); break;
             case DOP_LATTICE: e = dlattice_launch(op.lat, s, pdl); break;
             case DOP_KV_SYNC: e = dkv_sync_launch(op.sync, s, pdl); break;
+            case DOP_TREE: e = dtree_walk_launch(op.tree, s, pdl); break;
+            case DOP_COMPACT: e = tree_compact_launch(op.compact, s, pdl); break;
             default: return fail("draft kernel kind %d does not exist", op.kind);
         }
         if (e != cudaSuccess) return fail("draft kernel %d (kind %d) launch: %s", i, op.kind, cudaGetErrorString(e));
@@ -1184,6 +1186,8 @@ int mk_accept_bind(MkModule* module, const MkAcceptBind* b, MkLaunch** out) {
         L->accept.row_z = (double*)(b->sample_ws + (uint64_t)ys_bytes + (uint64_t)cells * 8);
         L->accept.sample_out = (double*)b->sample_out;
     }
+    MK_REQUIRE(b->tree == 0 || b->samp == 0, "the token tree's accept is greedy: samp and tree are exclusive");
+    L->accept.tree = (int*)b->tree;
     L->status = (int*)b->status;
     *out = L;
     return 0;

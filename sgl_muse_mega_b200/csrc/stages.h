@@ -14,6 +14,7 @@ struct AttnArgs {
     float* ws;
     bf16* x_attn;
     int M, qh, kvh, G, R, qkv_row, window, splits;
+    const int* tree;  // a token-tree window's table (draft.h kTree*: depth at [16 + row], ancestor mask at [32 + row]) or null
 };
 struct NormArgs {
     int mode, H, ranks;
@@ -240,6 +241,7 @@ struct AcceptArgs {
     double* es;                       // scratch f64 [rows][vocab]: exp(y - max) of the kept entries, 0 elsewhere
     double* row_z;                    // scratch f64 [rows]: the kept mass
     double* sample_out;               // out f64 [2] or null: the residual's scale and the bonus distribution's mass
+    int* tree;                        // the token tree's table (draft.h kTree*), or null: the window is a chain
 };
 cudaError_t feeds_launch(const FeedsArgs& a, cudaStream_t s, bool pdl);
 cudaError_t entry_launch(const EntryArgs& a, cudaStream_t s, bool pdl);

@@ -47,6 +47,21 @@ class Iteration:
         )  # fmt: skip
         self.draft.bind(peers)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        # a token-tree window (the stack was built with ``tree=True``): the tree walk over the head's lattice between the
+        # draft and the verify step (it rewrites the window's ids and its rotation feeds), the compaction of the accepted
+        # path's K / V and captured rows behind the accept
+        self.tree_walk = self.tree_compact = None
+        if stack.tree_table is not None:
+            from . import tree as TR
+
+            dr, f = self.draft, stack.feeds
+            self.tree_walk = TR.TreeWalk(stack.lib, stack.module, cand=dr.cand, scores=dr.scores, words=stack.accept.words,
+                                         verify_ids=stack.tokens, loc_full=f.loc_full, loc_swa=f.loc_swa, table=stack.tree_table,
+                                         cos_sin_cache=stack.cos_sin_cache, cos_sin=f.cos_sin)  # fmt: skip
+            swa = [t for lr, kv in zip(stack.layers, stack.pools) if not lr.case.global_attn for t in kv]
+            full = [t for lr, kv in zip(stack.layers, stack.pools) if lr.case.global_attn for t in kv]
+            self.tree_compact = TR.TreeCompact(stack.lib, stack.module, table=stack.tree_table, swa=swa, full=full,
+                                               caps=list(dict.fromkeys(caps)))  # fmt: skip
 
     @classmethod
     def connect(cls, stack: Stack, stack_peers: Sequence, dcfg: DraftConfig, dw: DraftWeights, group=None, **kw) -> "Iteration":
@@ -65,7 +80,7 @@ class Iteration:
 
     @property
     def kernels(self) -> int:
-        return self.draft.kernels() + self.stack.kernels
+        return self.draft.kernels() + self.stack.kernels + (2 if self.tree_walk is not None else 0)
 
     def launch_all(self, s: int, pdl: bool = True, sample: Optional[bool] = None, feeds: bool = False) -> None:
         """``sample``: which of a dual-bound iteration's two forms runs (False the greedy walk and accept, True the sampled
@@ -74,7 +89,11 @@ class Iteration:
         if feeds:
             self.stack.feeds.launch(s, False)
         self.draft.launch_all(s, pdl, sample)
+        if self.tree_walk is not None:
+            self.tree_walk.launch(s, pdl)
         self.stack.launch_all(s, pdl, tail=None if sample is None else ("sample" if sample else "greedy"))
+        if self.tree_compact is not None:
+            self.tree_compact.launch(s, pdl)
 
     def capture_graph(self, pdl: bool = True, warmup: bool = True, sample: Optional[bool] = None, feeds: bool = False,
                       after=None) -> torch.cuda.CUDAGraph:  # fmt: skip

@@ -130,11 +130,13 @@ class Accept:
                  accept_override: Optional[torch.Tensor] = None, cos_sin_cache=None, cos_sin=None, loc_full=None,
                  loc_swa=None, kv_len=None, dcos_sin_cache=None, dring: int = 0, flags=None, contributors: int = 0,
                  wait_budget: int = 0, pool_rows: int = 0, samp=None, cand=None, walk_q=None, block_verify: bool = True,
-                 share: Optional["Accept"] = None):  # fmt: skip
+                 share: Optional["Accept"] = None, tree: Optional[torch.Tensor] = None):  # fmt: skip
         """``samp`` (the sampling words on the device, ``dflash.draft.sampling_words``) with the draft head's ``cand`` and
         ``walk_q`` binds the sampled accept instead of the greedy one (``sample_out``: the residual's scale and mass).
         ``share``: another accept of the same step (the greedy one beside the sampled one) whose step words, token ring,
-        counter and draft feeds this one advances too: a request may then alternate between the two launches."""
+        counter and draft feeds this one advances too: a request may then alternate between the two launches.
+        ``tree``: the token tree's table (``dflash/tree.py`` ``TreeWalk.table``): the greedy accept then follows the
+        tree's matching path instead of the chain's prefix and leaves the path in the table."""
         dev = logits.device
         rows, vocab = logits.shape
         self.sample_ws = self.sample_out = None
@@ -167,6 +169,6 @@ class Accept:
             dslot=self.dslot, dkv_len=self.dkv_len, dring=dring, flags=flags, contributors=contributors,
             wait_budget=wait_budget, status=self.status, pool_rows=pool_rows, samp=samp, cand=cand, walk_q=walk_q,
             block_verify=int(block_verify), sample_ws=self.sample_ws,
-            sample_ws_bytes=0 if self.sample_ws is None else self.sample_ws.numel(), sample_out=self.sample_out,
+            sample_ws_bytes=0 if self.sample_ws is None else self.sample_ws.numel(), sample_out=self.sample_out, tree=tree,
         )  # fmt: skip
         self.launch = lib.bind("mk_accept_bind", module, self.bind)

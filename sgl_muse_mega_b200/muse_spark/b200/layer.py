@@ -173,7 +173,7 @@ class LayerRank:
         self.launch_record = None
 
     def bind(self, peers: Optional[list] = None, b_live: int = 0, wait_budget: int = 0, fused: Optional[bool] = None,
-             ep_peers: Optional[list] = None, ep_rank: int = 0):
+             ep_peers: Optional[list] = None, ep_rank: int = 0, tree: Optional[torch.Tensor] = None):
         """Binds the launch; ``peers`` = per rank an object whose attributes ``ar``, ``pool_ag``, ``unpool_ag``, ``z``,
         ``z_sf``, ``z_ex``, ``zb``, ``flags`` are that rank's exchange buffers (tensors, or device addresses of buffers
         mapped from another process): every rank's ``LayerRank`` (own included), or None for a lone rank.
@@ -185,7 +185,8 @@ class LayerRank:
         waits poll for ranks that run at the same time), 2 = one launch per stage with the cluster split-K GEMMs (14).
         ``ep_peers`` / ``ep_rank``: an expert-parallel world of one process per GPU (``expert_range`` given): per rank an
         object with ``zb`` and ``flags`` (this rank's own entry may be None); g2 writes its zb rows into every rank's zb
-        and the combine waits for all ranks."""
+        and the combine waits for all ranks. ``tree``: the token tree's table (``dflash/tree.py``): the attention masks
+        the window's own keys by the rows' ancestor masks and places the rows by depth."""
         fused = int(fused or 0)
         if fused == 2 and self.packed == 2:
             raise RuntimeError("dense_packed 2 (tile images) has no cluster split-K form: build the rank with packed=0 for fused=2")
@@ -232,7 +233,7 @@ class LayerRank:
             qkv_out=o["qkv_next"], cos_sin=w["next_cos_sin"], cache_loc=self.cache_loc, next_k_cache=self.next_k,
             next_v_cache=self.next_v, next_kv_rows=self.next_kv_rows, q_scale=cfg.q_scale, qkv_eps=cfg.rms_eps,
             flags=self.flags, flags_peer=flags_peer, ws=self.ws, status=self.status, b_live=b_live, wait_budget=wait_budget, fused=fused, dense_packed=int(self.packed),
-            expert_lo=self.expert_lo, expert_hi=self.expert_hi, ep_rank=ep_rank if ep_world else 0, ep_world=ep_world,
+            expert_lo=self.expert_lo, expert_hi=self.expert_hi, ep_rank=ep_rank if ep_world else 0, ep_world=ep_world, tree=tree,
         )  # fmt: skip
         self.launch_record = self.lib.layer_bind(self.module, self.shape, bind)
         return self.launch_record

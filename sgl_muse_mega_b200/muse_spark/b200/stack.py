@@ -69,7 +69,7 @@ class Stack:
                  b_live: int = 0, wait_budget: int = 0, fused: bool = False, frame: Optional[dict] = None,
                  pools: Optional[list] = None, packed: Optional[int] = None, sampling: Optional[torch.Tensor] = None,
                  block_verify: bool = True, shared_status: bool = False, accept_too: bool = False,
-                 sample_too: bool = False, identity_slots: bool = True):  # fmt: skip
+                 sample_too: bool = False, identity_slots: bool = True, tree: bool = False):  # fmt: skip
         """``identity_slots`` False (a serving framework's pools: position p does not live in pool row p): the accept writes
         no feeds for the next window (it can only write identity slots); the window feeds' kernel must run before every
         step (``launch_all(feeds=True)``) on the framework's batch tensors.
@@ -77,6 +77,9 @@ class Stack:
         (``self.accept``), for a fused iteration on the same buffers; ``launch_all(tail=...)`` picks the tail.
         ``sample_too`` (with ``sampling``): the greedy accept stays bound beside the sampled one (``self.accept`` and
         ``self.accept_sampled``, one set of step words), so that greedy and sampled requests share the stack.
+        ``tree``: the verify window is a token tree (``dflash/tree.py``): every layer's attention reads ``self.tree_table``
+        (rows placed by depth, window keys masked by ancestors) and the greedy accept follows the tree's matching path;
+        the iteration that owns the stack runs the tree walk before the step and the compaction after it.
         ``shared_status``: every layer launch of the stack records into ONE status block (``self.shared_status``) instead
         of one per layer: a wait that gave up then makes every later wait of the step give up at once (they see the
         recorded failure) instead of each spending its own budget, and a host reads one block per step.
@@ -95,6 +98,8 @@ class Stack:
         self.b_live, self.wait_budget, self.fused = b_live or M, wait_budget, fused
         self.samp = None if sampling is None else sampling.to(device)
         self.block_verify = block_verify
+        assert not (tree and sampling is not None), "the token tree's accept is greedy"
+        self.tree_table = torch.zeros(96, dtype=torch.int32, device=device) if tree else None
         self.draft_cand = self.draft_walk_q = None
         if self.samp is not None:
             self.draft_cand = torch.zeros(M - 1, 16, dtype=torch.int64, device=device)
@@ -219,7 +224,7 @@ class Stack:
                               residual=self.residual0, normed=self.normed0)  # fmt: skip
         live = self.b_live if self.b_live != M else 0
         for lr in self.layers:
-            lr.bind(views, live, self.wait_budget, fused=fused)
+            lr.bind(views, live, self.wait_budget, fused=fused, tree=self.tree_table)
         flags = self.arena.tensor("flags")
         self.lm_head = HT.LmHead(self.lib, self.module, w=self.lm_head_w, x=self.hidden,
                                  gathered=[None if v is None else v.gathered for v in views], rank=self.rank,
@@ -237,7 +242,7 @@ class Stack:
                               kv_len=f.kv_len, pool_rows=self.kv_rows)  # fmt: skip
             sampled = dict(samp=self.samp, cand=self.draft_cand, walk_q=self.draft_walk_q, block_verify=self.block_verify)
             if self.samp is None or self.sample_too:
-                self.accept = HT.Accept(self.lib, self.module, **common)
+                self.accept = HT.Accept(self.lib, self.module, **common, tree=self.tree_table)
                 self.tails["greedy"] = self.accept
             if self.samp is not None:
                 self.accept_sampled = HT.Accept(self.lib, self.module, **common, **sampled, share=self.accept)

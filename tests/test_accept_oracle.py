@@ -106,8 +106,18 @@ def test_bind_argument_checks():
              words=p, out_ring=p, ring=64, top1=p, counter=p, cos_sin_cache=0, cos_sin_rows=0, cos_sin=0, loc_full=0,
              loc_swa=0, kv_len=0, dcos_sin_cache=0, dcos_sin_rows=0, dcos_sin=0, dslot=0, dkv_len=0, dring=0, flags=0,
              contributors=0, wait_budget=0, status=0, pool_rows=0, samp=0, cand=0, walk_q=0, block_verify=0, sample_ws=0,
-             sample_ws_bytes=0, sample_out=0)  # fmt: skip
+             sample_ws_bytes=0, sample_out=0, tree=0)  # fmt: skip
     assert _lib().bind("mk_accept_bind", None, host.make("MkAcceptBind", **a)).info().kernels == 1
+    # the token tree: the greedy accept follows the table's tree; the tree's own launches check their operands
+    assert _lib().bind("mk_accept_bind", None, host.make("MkAcceptBind", **{**a, "tree": p})).info().kernels == 1
+    t = dict(cand=p, scores=p, words=p, table=p, verify_ids=p, loc_full=0, loc_swa=0, rows=16, cos_sin_cache=0, cos_sin_rows=0, cos_sin=0)
+    assert _lib().bind("mk_dflash_tree_bind", None, host.make("MkDflashTreeBind", **t)).info().kernels == 1
+    _expect("mk_dflash_tree_bind", host.make("MkDflashTreeBind", **{**t, "rows": 17}), "rows")
+    _expect("mk_dflash_tree_bind", host.make("MkDflashTreeBind", **{**t, "table": 0}), "table")
+    c = dict(table=p, rows=p, n_swa=3, n_full=1, n_cap=5, kv_row_bytes=256, cap_row_bytes=4096)
+    assert _lib().bind("mk_dflash_tree_compact_bind", None, host.make("MkDflashTreeCompactBind", **c)).info().kernels == 1
+    _expect("mk_dflash_tree_compact_bind", host.make("MkDflashTreeCompactBind", **{**c, "kv_row_bytes": 250}), "multiples of 16")
+    _expect("mk_dflash_tree_compact_bind", host.make("MkDflashTreeCompactBind", **{**c, "n_swa": 0, "n_full": 0, "n_cap": 0}), "no buffers")
     # the sampled accept: its operands and scratch (rows x vocab x 12 bytes + 256, 256-byte aligned)
     need = 16 * 1000 * 12 + 256
     smp = {**a, "samp": p, "cand": p, "walk_q": p, "sample_ws": 4096, "sample_ws_bytes": need, "top1": 0}
@@ -115,6 +125,7 @@ def test_bind_argument_checks():
     _expect("mk_accept_bind", host.make("MkAcceptBind", **{**smp, "sample_ws_bytes": need - 1}), "sample_ws_bytes")
     _expect("mk_accept_bind", host.make("MkAcceptBind", **{**smp, "cand": 0}), "cand")
     _expect("mk_accept_bind", host.make("MkAcceptBind", **{**smp, "sample_ws": 4100}), "aligned")
+    _expect("mk_accept_bind", host.make("MkAcceptBind", **{**smp, "tree": p}), "exclusive")
     _expect("mk_accept_bind", host.make("MkAcceptBind", **{**a, "top1": 0}), "top1")
     _expect("mk_accept_bind", host.make("MkAcceptBind", **{**a, "b_live": 17}), "b_live")
     _expect("mk_accept_bind", host.make("MkAcceptBind", **{**a, "ring": 8}), "ring")
