@@ -524,6 +524,10 @@ def decode_line(args, cfg, dec: dict, world: int, clocks) -> dict:
     what = (f"configs[{args.config}]: full-shape 62-layer model + DFlash2 draft, TP8 slice per GPU on {world} B200(s), "
             f"{args.ctx}-token context (KV filled directly: no prefill path here), {gen} generated tokens, block 16, "
             f"forced accept {args.accept} (commit {args.accept + 1} a step)")
+    if args.tree:
+        what = what.replace(f"forced accept {args.accept} (commit {args.accept + 1} a step)",
+                            f"token-tree window, forced leaf row {args.accept} (its depth + 1 = {dec['tokens_per_step']:.2f} tokens a step "
+                            "on synthetic lattices: the number shows the tree step's cost, not the tree's acceptance gain)")
     layer_gbs = dec["bytes_per_step"] / (dec["layer_only_us"] * n_layers * 1e-6) / 1e9
     return {
         "metric": "batch-1 decode tok/s at fixed accept len", "value": dec["tok_s"], "unit": "tok/s", "n_gpus": world,
