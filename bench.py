@@ -62,6 +62,9 @@ def parse():
                          "the accept length stays forced)")
     ap.add_argument("--top-k", type=int, default=1 << 30)
     ap.add_argument("--top-p", type=float, default=1.0)
+    ap.add_argument("--exchange", default="auto", choices=("auto", "packets", "flags"),
+                    help="the layers' bf16 exchanges of a world of several GPUs: rows that carry their own validity (packets, "
+                         "the default there) or counter words in the flag block (flags)")
     ap.add_argument("--tree", action="store_true",
                     help="whole-step leg with the DFlash2 token tree (tree walk, ancestor-masked attention, tree accept, "
                          "compaction); --accept then names the forced leaf ROW, the accept length is its depth")
@@ -245,7 +248,8 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
         assert not args.no_draft, "the sampled accept reads the draft head's candidates"
         sampling = sampling_words(args.seed, 0, args.temperature, args.top_k, args.top_p)
     st = S.Stack(case, tp_rank, device, lib, module, arena=arena, kv_rows=kv_rows, keep_plain_experts=False,
-                 accept_override=forced, wait_budget=1 << 25, sampling=sampling, fused=args.form == 4, tree=args.tree)  # fmt: skip
+                 accept_override=forced, wait_budget=1 << 25, sampling=sampling, fused=args.form == 4, tree=args.tree,
+                 packets=None if args.exchange == "auto" else args.exchange == "packets")  # fmt: skip
     peers = S.connect_world(st) if world > 1 else st.bind()
     s = stream.cuda_stream
     # the DFlash2 draft at its public size (this rank's TP slice, synthetic weights drawn on the device): with it the step
@@ -408,6 +412,8 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
         "draft": draft if draft is not None else "not in the step (--no-draft): ids come from the host",
         "sampling": "greedy" if sampling is None else {"temperature": args.temperature, "top_k": args.top_k, "top_p": args.top_p},
         "window": "token tree (forced leaf row %d)" % args.accept if args.tree else "chain",
+        "exchange": "stream order (one rank)" if world == 1 and not st.packets else
+                    "packets (bf16 rows with in-band validity; h planes and logits on counter words)" if st.packets else "counter words",
     }  # fmt: skip
     if it is not None:
         bad = it.statuses()
@@ -462,7 +468,8 @@ def parity_world(args, lib, module, device, rank: int, world: int) -> dict:
     case = synthetic.stack_case(cfg, n_layers=4, rows=rows, ctx=ctx, seed=21, only_ranks=[rank])
     forced = torch.tensor([accept], dtype=torch.int32, device=device)
     arena = symm.Arena(lib, S.exchange_layout(cfg, rows), device)
-    st = S.Stack(case, rank, device, lib, module, arena=arena, accept_override=forced, wait_budget=1 << 25, fused=fused)
+    st = S.Stack(case, rank, device, lib, module, arena=arena, accept_override=forced, wait_budget=1 << 25, fused=fused,
+                 packets=None if args.exchange == "auto" else args.exchange == "packets")  # fmt: skip
     peers = S.connect_world(st)
     st.feeds.launch(torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
@@ -507,6 +514,7 @@ def parity_world(args, lib, module, device, rank: int, world: int) -> dict:
         emu_status = [x for e in w.ranks for x in e.statuses()]
         res = {"model": "4 layers (one with bf16 experts), hidden 1024, 16 experts, vocab 4096, tensor-parallel over the ranks",
                "steps": steps, "compared": list(names), "bit_equal": not mismatch and not fused, "mismatch": mismatch[:8],
+               "exchange": "packets" if st.packets else "counter words",
                "status": [str(x) for x in status + emu_status]}  # fmt: skip
         if fused:
             res["ranks_bit_equal"] = not mismatch

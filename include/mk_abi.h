@@ -242,6 +242,15 @@ typedef struct MkLayerBind {
     // context key is its past); the K / V rows are still appended at the window's slots in row order (the compaction moves
     // the accepted path's rows afterwards), and cos_sin must hold the rows' rotations by depth (the tree's launch writes them).
     uint64_t tree;
+    // 1: the four bf16 exchanges of the layer (all-reduce partials, pooler gather, expert outputs, unpooler gather) carry
+    // their own validity instead of counting in the flag block: ar, pool_ag, zb and unpool_ag of every rank must be filled
+    // with 0xFF bytes once before the first launch (a bf16 of all ones marks "not arrived"; no kernel produces it). The
+    // producers then only store (no fence, no arrival, no flag), the consumers poll the 16-byte packets they use with the
+    // wait budget and put the mark back, so the buffers read as marks after a step: a caller that inspects ar / pool_ag /
+    // zb / unpool_ag between stages binds 0. The reference's counterpart: its packets with in-band validity
+    // (kernels/postattn.cuh:38-53, kernels/framework.cuh:1409-1482). Not with fused = 1. 0: counter words (flags) or, without
+    // a flag block, stream order.
+    int64_t packets;
 } MkLayerBind;
 int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind* bind, MkLaunch** out);
 

@@ -46,6 +46,10 @@ struct XchgWait {
     long long budget;           // polls before giving up
     int* status;
     int stage;                  // recorded with a wait that ran out
+    // packet mode (pkt_take below): the exchanged bf16 rows carry their own validity and there is no counter word
+    int packets;                // 1: on (flag is null then)
+    unsigned present;           // bit j: source j of the exchange is bound and writes its part (a part of an absent source is 0)
+    int band;                   // columns per source where the sources write column bands of one row (0: whole rows)
 };
 
 // Every thread of every CTA calls this after the kernel's last store to a peer.
@@ -149,6 +153,53 @@ __device__ __forceinline__ void xchg_wait_role(const XchgWait& w, int tid, int n
         }
     }
     asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(n) : "memory");
+}
+
+// ---- packet mode: bf16 exchanges that carry their own validity --------------------------------------------------------------
+// A bf16 whose 16 bits are all ones is a NaN that no float -> bf16 conversion produces (they give the canonical 0x7FFF), so an
+// exchange buffer filled with it says, 2 bytes at a time, what has not arrived yet. The producers store their results into
+// the peers' buffers as they finish a tile and do nothing else: no fence, no arrival count, no flag. A consumer thread polls
+// the 16-byte packet it is about to use until none of its eight halves is the mark (stores of any width >= 2 bytes may
+// complete it piecewise), takes the value and puts the mark back for the buffer's next use; that store is ordered before the
+// next use because the peers reach it only through a later exchange that needs this rank's later kernels, which start after
+// this one has ended. A poll that runs out of its budget records itself like a counter wait (code 1) and the kernel
+// carries on with the bytes it saw.
+constexpr unsigned kPktMark = 0xFFFFFFFFu;
+__device__ __forceinline__ bool pkt_word_ok(unsigned w) { return (w & 0xFFFFu) != 0xFFFFu && (w >> 16) != 0xFFFFu; }
+__device__ __forceinline__ bool pkt_ok(const uint4& v) {
+    return pkt_word_ok(v.x) && pkt_word_ok(v.y) && pkt_word_ok(v.z) && pkt_word_ok(v.w);
+}
+__device__ __forceinline__ uint4 pkt_peek(const void* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// `polls` counts over all the packets a thread takes in one launch (one budget a thread).
+__device__ __forceinline__ uint4 pkt_take(const void* p, const XchgWait& w, long long& polls) {
+    uint4 v = pkt_peek(p);
+    while (!pkt_ok(v)) {
+        if ((polls & 255) == 255 && w.status != nullptr && *(volatile int*)w.status != 0) break;  // a failure already on record
+        if (++polls > w.budget) {
+            if (w.status != nullptr && atomicCAS(w.status, 0, 1) == 0) {
+                w.status[1] = w.stage;
+                w.status[2] = (int)blockIdx.x;
+                w.status[3] = (int)threadIdx.x;
+                w.status[4] = -1;
+            }
+            break;
+        }
+        __nanosleep(32);
+        v = pkt_peek(p);
+    }
+    *(uint4*)const_cast<void*>(p) = make_uint4(kPktMark, kPktMark, kPktMark, kPktMark);
+    return v;
+}
+// the packet at column c of a row whose sources write bands of w.band columns (or whole rows): taken if its source is
+// present, zeros otherwise
+__device__ __forceinline__ uint4 pkt_take_col(const void* p, int c, const XchgWait& w, long long& polls) {
+    const int src = w.band > 0 ? c / w.band : 0;
+    if (w.band > 0 && !((w.present >> src) & 1u)) return make_uint4(0, 0, 0, 0);
+    return pkt_take(p, w, polls);
 }
 
 // Route tables in the private scratch, written by the routing kernel each launch.

@@ -48,11 +48,21 @@ __global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
     const float4 s0 = *(const float4*)(a.stream_in + off), s1 = *(const float4*)(a.stream_in + off + 4);
     xchg_wait(a.wait);  // the all-reduce partials (mode 0) or the unpooler gather (mode 1) of every contributing rank
     float v[8];
+    long long polls = 0;
     if (a.mode == 0) {
         uint4 part[kMaxRanks];
+        if (a.wait.packets) {  // every present rank's partial as it arrives; an absent rank's is 0
 #pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r)
-            if (r < a.ranks) part[r] = *(const uint4*)(a.src + ((size_t)r * a.M + row) * a.H + c0);
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < a.ranks) {
+                    part[r] = make_uint4(0, 0, 0, 0);
+                    if ((a.wait.present >> r) & 1u) part[r] = pkt_take(a.src + ((size_t)r * a.M + row) * a.H + c0, a.wait, polls);
+                }
+        } else {
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < a.ranks) part[r] = *(const uint4*)(a.src + ((size_t)r * a.M + row) * a.H + c0);
+        }
         unpack8(part[0], v);
 #pragma unroll
         for (int r = 1; r < kMaxRanks; ++r)
@@ -67,7 +77,7 @@ __global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
         unpack8(b, v);
     } else {
         float w[8];
-        unpack8(*(const uint4*)(a.src + off), v);
+        unpack8(a.wait.packets ? pkt_take_col(a.src + off, c0, a.wait, polls) : *(const uint4*)(a.src + off), v);
         unpack8(post_raw, w);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] *= w[i];
@@ -252,8 +262,14 @@ static __device__ void nq_row(const NqArgs& a, int row, float* red) {
     const bool own = tid < groups;
     if (own) {
         float g[16];
-        unpack8(*(const uint4*)(x + tid * 16), *(float(*)[8])g);
-        unpack8(*(const uint4*)(x + tid * 16 + 8), *(float(*)[8])(g + 8));
+        if (a.wait.packets) {
+            long long polls = 0;
+            unpack8(pkt_take_col(x + tid * 16, tid * 16, a.wait, polls), *(float(*)[8])g);
+            unpack8(pkt_take_col(x + tid * 16 + 8, tid * 16 + 8, a.wait, polls), *(float(*)[8])(g + 8));
+        } else {
+            unpack8(*(const uint4*)(x + tid * 16), *(float(*)[8])g);
+            unpack8(*(const uint4*)(x + tid * 16 + 8), *(float(*)[8])(g + 8));
+        }
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             n[i] = g[i];
@@ -418,9 +434,16 @@ __global__ void __launch_bounds__(512) combine_kernel(const CombineArgs a) {
     for (int j0 = 0; j0 < a.k; j0 += kMaxTopk) {
         const int kk = min(kMaxTopk, a.k - j0);
         uint4 raw[kMaxTopk];
+        if (a.wait.packets) {
+            long long polls = 0;
 #pragma unroll
-        for (int j = 0; j < kMaxTopk; ++j)
-            if (j < kk) raw[j] = *(const uint4*)(a.zb + ((size_t)row * a.k + j0 + j) * a.P + c0);
+            for (int j = 0; j < kMaxTopk; ++j)
+                if (j < kk) raw[j] = pkt_take_col(a.zb + ((size_t)row * a.k + j0 + j) * a.P + c0, c0, a.wait, polls);
+        } else {
+#pragma unroll
+            for (int j = 0; j < kMaxTopk; ++j)
+                if (j < kk) raw[j] = *(const uint4*)(a.zb + ((size_t)row * a.k + j0 + j) * a.P + c0);
+        }
         float xg[kMaxTopk][8];
 #pragma unroll
         for (int j = 0; j < kMaxTopk; ++j) {

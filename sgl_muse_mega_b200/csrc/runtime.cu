@@ -317,9 +317,13 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     unsigned* const flags = (unsigned*)b->flags;
     const long long budget = b->wait_budget > 0 ? b->wait_budget : kDefaultWaitBudget;
     auto flag_of = [&](int r) -> unsigned* { return (unsigned*)(r == s.rank ? b->flags : b->flags_peer[r]); };
+    // packet mode: the bf16 exchanges carry their own validity (params.h pkt_take); the h planes keep their counter word
+    const bool packets = b->packets != 0;
+    MK_REQUIRE(!packets || b->fused != 1, "packets is not available with the fused form (fused = 1)");
+    auto in_band = [&](int point) { return packets && (point == XP_AR || point == XP_POOL || point == XP_ZB || point == XP_UNPOOL); };
     auto signal_to = [&](XchgSignal& x, int point, int first, int count) {
         memset(&x, 0, sizeof x);
-        if (flags == nullptr) return;
+        if (flags == nullptr || in_band(point)) return;
         for (int r = first; r < first + count; ++r)
             if (flag_of(r)) {
                 x.flag[x.n++] = flag_of(r) + point;
@@ -330,6 +334,18 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     };
     auto wait_for = [&](XchgWait& w, int point, int first, int count, int stage) {
         memset(&w, 0, sizeof w);
+        if (in_band(point)) {
+            // the sources that are bound (own buffer and the peers' that were given) write their part; bit j: source first + j
+            const uint64_t* arr = point == XP_AR ? b->ar_peer : point == XP_POOL ? b->pool_ag_peer : point == XP_ZB ? b->zb_peer : b->unpool_ag_peer;
+            for (int r = first; r < first + count; ++r)
+                if (r == s.rank || arr[r] != 0) w.present |= 1u << (r - first);
+            w.band = point == XP_AR ? 0 : (int)((point == XP_UNPOOL ? s.hidden : s.moe_hidden) / count);
+            w.packets = 1;
+            w.budget = budget;
+            w.status = (int*)b->status;
+            w.stage = stage;
+            return;
+        }
         if (flags == nullptr) return;
         for (int r = first; r < first + count; ++r) w.contributors += flag_of(r) != nullptr;
         w.flag = flags + point;
@@ -556,7 +572,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
             memset(&u.sig, 0, sizeof u.sig);
             for (int r = 0; r < ep_world; ++r) {
                 const uint64_t zb = r == ep_rank ? b->zb : b->zb_peer[r], fl = r == ep_rank ? b->flags : b->flags_peer[r];
-                MK_REQUIRE(zb != 0 && fl != 0, "zb_peer[%d] or flags_peer[%d] of the expert-parallel world is 0", r, r);
+                MK_REQUIRE(zb != 0 && (packets || fl != 0), "zb_peer[%d] or flags_peer[%d] of the expert-parallel world is 0", r, r);
                 u.zb_peer[u.n_peer++] = (bf16*)zb;
                 u.sig.flag[u.sig.n++] = (unsigned*)fl + XP_ZB;
                 u.sig.remote |= r != ep_rank;
@@ -565,12 +581,19 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
             u.sig.epoch = flags + kXchgEpoch + XP_ZB;
             XchgWait& w = L->combine.wait;
             memset(&w, 0, sizeof w);
-            w.flag = flags + XP_ZB;
-            w.epoch = flags + kXchgEpoch + XP_ZB;
-            w.contributors = (unsigned)ep_world;
             w.budget = budget;
             w.status = (int*)b->status;
             w.stage = ST_COMBINE;
+            if (packets) {  // whole rows from whichever rank owns the slot's expert: every packet of a live row arrives
+                memset(&u.sig, 0, sizeof u.sig);
+                w.packets = 1;
+                w.present = (1u << ep_world) - 1;
+                w.band = 0;
+            } else {
+                w.flag = flags + XP_ZB;
+                w.epoch = flags + kXchgEpoch + XP_ZB;
+                w.contributors = (unsigned)ep_world;
+            }
         }
         L->stage_on[ST_HROW] = false;
     }

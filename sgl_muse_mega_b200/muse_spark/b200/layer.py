@@ -173,7 +173,7 @@ class LayerRank:
         self.launch_record = None
 
     def bind(self, peers: Optional[list] = None, b_live: int = 0, wait_budget: int = 0, fused: Optional[bool] = None,
-             ep_peers: Optional[list] = None, ep_rank: int = 0, tree: Optional[torch.Tensor] = None):
+             ep_peers: Optional[list] = None, ep_rank: int = 0, tree: Optional[torch.Tensor] = None, packets: bool = False):
         """Binds the launch; ``peers`` = per rank an object whose attributes ``ar``, ``pool_ag``, ``unpool_ag``, ``z``,
         ``z_sf``, ``z_ex``, ``zb``, ``flags`` are that rank's exchange buffers (tensors, or device addresses of buffers
         mapped from another process): every rank's ``LayerRank`` (own included), or None for a lone rank.
@@ -186,8 +186,16 @@ class LayerRank:
         ``ep_peers`` / ``ep_rank``: an expert-parallel world of one process per GPU (``expert_range`` given): per rank an
         object with ``zb`` and ``flags`` (this rank's own entry may be None); g2 writes its zb rows into every rank's zb
         and the combine waits for all ranks. ``tree``: the token tree's table (``dflash/tree.py``): the attention masks
-        the window's own keys by the rows' ancestor masks and places the rows by depth."""
+        the window's own keys by the rows' ancestor masks and places the rows by depth.
+        ``packets``: the four bf16 exchanges carry their own validity (``MkLayerBind.packets``): this rank's ``ar``,
+        ``pool_ag``, ``zb`` and ``unpool_ag`` are filled with the "not arrived" mark here, the consumers put it back after
+        every use, so these four read as marks after a launch (``values()`` of such a rank has no pooled / zb rows)."""
         fused = int(fused or 0)
+        if packets:
+            if fused == 1:
+                raise RuntimeError("packets is not available with the fused form")
+            for t in (self.ar, self.pool_ag, self.zb, self.unpool_ag):
+                t.view(torch.uint8).fill_(0xFF)
         if fused == 2 and self.packed == 2:
             raise RuntimeError("dense_packed 2 (tile images) has no cluster split-K form: build the rank with packed=0 for fused=2")
         cfg, case, w, o = self.case.cfg, self.case, self.w, self.o
@@ -233,7 +241,7 @@ class LayerRank:
             qkv_out=o["qkv_next"], cos_sin=w["next_cos_sin"], cache_loc=self.cache_loc, next_k_cache=self.next_k,
             next_v_cache=self.next_v, next_kv_rows=self.next_kv_rows, q_scale=cfg.q_scale, qkv_eps=cfg.rms_eps,
             flags=self.flags, flags_peer=flags_peer, ws=self.ws, status=self.status, b_live=b_live, wait_budget=wait_budget, fused=fused, dense_packed=int(self.packed),
-            expert_lo=self.expert_lo, expert_hi=self.expert_hi, ep_rank=ep_rank if ep_world else 0, ep_world=ep_world, tree=tree,
+            expert_lo=self.expert_lo, expert_hi=self.expert_hi, ep_rank=ep_rank if ep_world else 0, ep_world=ep_world, tree=tree, packets=int(packets),
         )  # fmt: skip
         self.launch_record = self.lib.layer_bind(self.module, self.shape, bind)
         return self.launch_record

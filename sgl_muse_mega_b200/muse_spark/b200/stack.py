@@ -69,7 +69,8 @@ class Stack:
                  b_live: int = 0, wait_budget: int = 0, fused: bool = False, frame: Optional[dict] = None,
                  pools: Optional[list] = None, packed: Optional[int] = None, sampling: Optional[torch.Tensor] = None,
                  block_verify: bool = True, shared_status: bool = False, accept_too: bool = False,
-                 sample_too: bool = False, identity_slots: bool = True, tree: bool = False):  # fmt: skip
+                 sample_too: bool = False, identity_slots: bool = True, tree: bool = False,
+                 packets: Optional[bool] = None):  # fmt: skip
         """``identity_slots`` False (a serving framework's pools: position p does not live in pool row p): the accept writes
         no feeds for the next window (it can only write identity slots); the window feeds' kernel must run before every
         step (``launch_all(feeds=True)``) on the framework's batch tensors.
@@ -80,6 +81,9 @@ class Stack:
         ``tree``: the verify window is a token tree (``dflash/tree.py``): every layer's attention reads ``self.tree_table``
         (rows placed by depth, window keys masked by ancestors) and the greedy accept follows the tree's matching path;
         the iteration that owns the stack runs the tree walk before the step and the compaction after it.
+        ``packets``: the layers' bf16 exchanges carry their own validity (``LayerRank.bind(packets=...)``) instead of counting
+        in the flag block; default: on for a world of several processes (peers over NVLink: it saves every producer's
+        system-scope fence and the flag's extra trip), off otherwise (a lone rank or an emulated world orders by stream).
         ``shared_status``: every layer launch of the stack records into ONE status block (``self.shared_status``) instead
         of one per layer: a wait that gave up then makes every later wait of the step give up at once (they see the
         recorded failure) instead of each spending its own budget, and a host reads one block per step.
@@ -98,6 +102,7 @@ class Stack:
         self.b_live, self.wait_budget, self.fused = b_live or M, wait_budget, fused
         self.samp = None if sampling is None else sampling.to(device)
         self.block_verify = block_verify
+        self.packets = packets
         assert not (tree and sampling is not None), "the token tree's accept is greedy"
         self.tree_table = torch.zeros(96, dtype=torch.int32, device=device) if tree else None
         self.draft_cand = self.draft_walk_q = None
@@ -223,8 +228,12 @@ class Stack:
                               eps_embed=cfg.rms_eps, eps_pre=cfg.rms_eps, shard_rows=cfg.vocab_rank, hidden=cfg.hidden,
                               residual=self.residual0, normed=self.normed0)  # fmt: skip
         live = self.b_live if self.b_live != M else 0
+        packets = self.packets
+        if packets is None:
+            packets = not fused and any(isinstance(p, PeerStack) for p in peers)
+        self.packets = bool(packets)
         for lr in self.layers:
-            lr.bind(views, live, self.wait_budget, fused=fused, tree=self.tree_table)
+            lr.bind(views, live, self.wait_budget, fused=fused, tree=self.tree_table, packets=self.packets)
         flags = self.arena.tensor("flags")
         self.lm_head = HT.LmHead(self.lib, self.module, w=self.lm_head_w, x=self.hidden,
                                  gathered=[None if v is None else v.gathered for v in views], rank=self.rank,

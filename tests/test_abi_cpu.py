@@ -147,6 +147,28 @@ def test_expert_parallel_world_binds_every_ranks_zb_and_flags(lib):
     assert lay.offset("flags") == 0 and lay.offset("zb") >= 256
 
 
+def test_packet_mode_binds_and_marks_the_exchange_rows(lib):
+    """``packets``: the bind fills this rank's four bf16 exchange buffers with the "not arrived" mark, keeps the kernel
+    count, and refuses the fused form; an expert-parallel world in packet mode needs no peer flag block."""
+    from types import SimpleNamespace as NS
+
+    from sgl_muse_mega_b200.muse_spark.b200 import expert_block as X
+
+    cfg, kw = CASES["small_fp4_swa_tp2"]
+    case = synthetic.layer_case(cfg, **kw)
+    rank = L.LayerRank(lib, None, case, 0, torch.device("cpu"))
+    assert not bool((rank.ar.view(torch.uint8) == 0xFF).any())
+    assert rank.bind(packets=True).info().kernels == rank.bind().info().kernels
+    for t in (rank.ar, rank.pool_ag, rank.zb, rank.unpool_ag):
+        assert bool((t.view(torch.uint8) == 0xFF).all())
+    with pytest.raises(RuntimeError, match="fused"):
+        rank.bind(fused=1, packets=True)
+    ecfg = X.block_config(experts=16, moe_hidden=1024, moe_inter=1024)
+    ecase = synthetic.layer_case(ecfg, rows=4, ctx=8, seed=5)
+    ep = L.LayerRank(lib, None, ecase, 0, torch.device("cpu"), expert_range=(8, 16))
+    assert ep.bind(ep_peers=[NS(zb=0x7F0000001000, flags=0), None], ep_rank=1, packets=True).info().kernels == 12
+
+
 def test_module_load_needs_builtin_image(lib):
     out = ctypes.c_void_p()
     assert lib.dll.mk_module_load(b"xx", 2, None, ctypes.byref(out)) == -1
