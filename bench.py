@@ -63,8 +63,9 @@ def parse():
     ap.add_argument("--top-k", type=int, default=1 << 30)
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--exchange", default="auto", choices=("auto", "packets", "flags"),
-                    help="the layers' bf16 exchanges of a world of several GPUs: rows that carry their own validity (packets, "
-                         "the default there) or counter words in the flag block (flags)")
+                    help="how a layer's bf16 rows reach their consumers, between GPUs and inside one: rows that carry their own "
+                         "validity (packets: the default, except with --form 4), or counter words in the flag block between "
+                         "GPUs and kernel completion inside one (flags)")
     ap.add_argument("--tree", action="store_true",
                     help="whole-step leg with the DFlash2 token tree (tree walk, ancestor-masked attention, tree accept, "
                          "compaction); --accept then names the forced leaf ROW, the accept length is its depth")
@@ -249,7 +250,7 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
         sampling = sampling_words(args.seed, 0, args.temperature, args.top_k, args.top_p)
     st = S.Stack(case, tp_rank, device, lib, module, arena=arena, kv_rows=kv_rows, keep_plain_experts=False,
                  accept_override=forced, wait_budget=1 << 25, sampling=sampling, fused=args.form == 4, tree=args.tree,
-                 packets=None if args.exchange == "auto" else args.exchange == "packets")  # fmt: skip
+                 packets=args.form != 4 if args.exchange == "auto" else args.exchange == "packets")  # fmt: skip
     peers = S.connect_world(st) if world > 1 else st.bind()
     s = stream.cuda_stream
     # the DFlash2 draft at its public size (this rank's TP slice, synthetic weights drawn on the device): with it the step
@@ -412,8 +413,9 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
         "draft": draft if draft is not None else "not in the step (--no-draft): ids come from the host",
         "sampling": "greedy" if sampling is None else {"temperature": args.temperature, "top_k": args.top_k, "top_p": args.top_p},
         "window": "token tree (forced leaf row %d)" % args.accept if args.tree else "chain",
-        "exchange": "stream order (one rank)" if world == 1 and not st.packets else
-                    "packets (bf16 rows with in-band validity; h planes and logits on counter words)" if st.packets else "counter words",
+        "exchange": "packets (bf16 rows and router logits with in-band validity, their consumers do not wait for the producing "
+                    "grid's end; h planes and vocabulary logits on counter words)" if st.packets else
+                    "kernel completion (one rank)" if world == 1 else "counter words",
     }  # fmt: skip
     if it is not None:
         bad = it.statuses()
@@ -616,7 +618,7 @@ def run_ours(args) -> None:
         lr.z_sf.copy_(torch.randint(0x30, 0x40, lr.z_sf.shape, generator=g, device=device, dtype=torch.uint8))
         lr.z_ex.copy_(torch.randint(0, 3, lr.z_ex.shape, generator=g, device=device, dtype=torch.uint8))
         lr.zb.view(torch.bfloat16).copy_(torch.randn(lr.zb.numel() // 2, generator=g, device=device))
-        lr.bind(None, fused={0: 0, 1: 1, 2: 2, 3: 0, 4: 1}[args.form])
+        lr.bind(None, fused={0: 0, 1: 1, 2: 2, 3: 0, 4: 1}[args.form], packets=args.form == 0 and args.exchange != "flags")
         case.ranks = []  # the device copies live in lr.w
         ring.append(lr)
     torch.cuda.synchronize()

@@ -247,7 +247,9 @@ typedef struct MkLayerBind {
     // with 0xFF bytes once before the first launch (a bf16 of all ones marks "not arrived"; no kernel produces it). The
     // producers then only store (no fence, no arrival, no flag), the consumers poll the 16-byte packets they use with the
     // wait budget and put the mark back, so the buffers read as marks after a step: a caller that inspects ar / pool_ag /
-    // zb / unpool_ag between stages binds 0. The reference's counterpart: its packets with in-band validity
+    // zb / unpool_ag between stages binds 0. With tile images (dense_packed 2) the router's f32 logits are handed to the
+    // routing rows the same way (fill logits with 0xFF bytes as well; they read as marks afterwards), and the row kernels
+    // that consume packets do not wait for the producing grid's end. The reference's counterpart: its packets with in-band validity
     // (kernels/postattn.cuh:38-53, kernels/framework.cuh:1409-1482). Not with fused = 1. 0: counter words (flags) or, without
     // a flag block, stream order.
     int64_t packets;

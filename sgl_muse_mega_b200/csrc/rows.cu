@@ -42,7 +42,9 @@ __global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
     uint4 post_raw = make_uint4(0, 0, 0, 0);
     if (a.mode != 0) post_raw = *(const uint4*)(a.post_w + c0);
     RT(a.mode != 0, 0)
-    griddep_wait();
+    // packet mode: the rows that arrive are their own dependency (pkt_take), everything else this kernel reads was complete
+    // before the producer of those rows passed its own wait, so the kernel does not wait for the producer's grid to end
+    if (!a.wait.packets) griddep_wait();
     griddep_launch();
     RT(a.mode != 0, 1)
     const float4 s0 = *(const float4*)(a.stream_in + off), s1 = *(const float4*)(a.stream_in + off + 4);
@@ -344,8 +346,10 @@ __global__ void __launch_bounds__(512) route_nq_kernel(const RouteNqArgs a) {
             if (tid + 512 * r < E) bias[r] = a.topk.bias[tid + 512 * r];
     }
     RT(2, 0)
-    griddep_wait();
-    griddep_launch();
+    // packet mode: the pooled rows and (where this kernel forms the scores) the router's f32 logits are their own dependency
+    const bool polled = a.nq.wait.packets && ((int)blockIdx.x >= M || a.topk.score == nullptr);
+    if (!polled) griddep_wait();
+    else griddep_launch();
     RT(2, 1)
     if ((int)blockIdx.x >= M) {
         xchg_wait(a.nq.wait);  // the pooler gather of the node's ranks
@@ -361,7 +365,32 @@ __global__ void __launch_bounds__(512) route_nq_kernel(const RouteNqArgs a) {
             if (a.topk.score != nullptr) {
                 s_sel[e] = a.topk.score[(size_t)row * E + e];
             } else {
-                const double z = (double)a.topk.logits[(size_t)row * E + e] * a.topk.mult;
+                float lg;
+                if (a.nq.wait.packets) {  // an f32 of all ones marks a logit that has not arrived (pkt_take's rule, 4 bytes)
+                    unsigned* p = (unsigned*)(a.topk.logits + (size_t)row * E + e);
+                    long long polls = 0;
+                    unsigned v;
+                    for (;;) {
+                        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+                        if (v != kPktMark) break;
+                        if ((polls & 255) == 255 && a.nq.wait.status != nullptr && *(volatile int*)a.nq.wait.status != 0) break;
+                        if (++polls > a.nq.wait.budget) {
+                            if (a.nq.wait.status != nullptr && atomicCAS(a.nq.wait.status, 0, 1) == 0) {
+                                a.nq.wait.status[1] = a.nq.wait.stage;
+                                a.nq.wait.status[2] = (int)blockIdx.x;
+                                a.nq.wait.status[3] = tid;
+                                a.nq.wait.status[4] = -2;
+                            }
+                            break;
+                        }
+                        __nanosleep(32);
+                    }
+                    *p = kPktMark;
+                    lg = __uint_as_float(v);
+                } else {
+                    lg = a.topk.logits[(size_t)row * E + e];
+                }
+                const double z = (double)lg * a.topk.mult;
                 s_sel[e] = (float)(1.0 / (1.0 + exp(-z))) + bias[r];
             }
         }
@@ -420,7 +449,7 @@ __global__ void __launch_bounds__(512) combine_kernel(const CombineArgs a) {
     const int nw = blockDim.x >> 5;
     const uint4 gp_raw = *(const uint4*)(a.gamma_p1 + c0);  // a weight: in flight while the predecessor still runs
     RT(4, 0)
-    griddep_wait();
+    if (!a.wait.packets) griddep_wait();
     griddep_launch();
     RT(4, 1)
     xchg_wait(a.wait);  // every rank's column band of the expert outputs

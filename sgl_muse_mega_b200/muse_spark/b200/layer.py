@@ -189,12 +189,14 @@ class LayerRank:
         the window's own keys by the rows' ancestor masks and places the rows by depth.
         ``packets``: the four bf16 exchanges carry their own validity (``MkLayerBind.packets``): this rank's ``ar``,
         ``pool_ag``, ``zb`` and ``unpool_ag`` are filled with the "not arrived" mark here, the consumers put it back after
-        every use, so these four read as marks after a launch (``values()`` of such a rank has no pooled / zb rows)."""
+        every use, so these four read as marks after a launch (``values()`` of such a rank has no pooled / zb rows). The
+        router's f32 logits travel the same way inside the rank (marked, polled by the routing rows, wiped), and the
+        consuming row kernels do not wait for the producing grid to end: they start on the rows as they arrive."""
         fused = int(fused or 0)
         if packets:
             if fused == 1:
                 raise RuntimeError("packets is not available with the fused form")
-            for t in (self.ar, self.pool_ag, self.zb, self.unpool_ag):
+            for t in (self.ar, self.pool_ag, self.zb, self.unpool_ag, self.o["logits"]):
                 t.view(torch.uint8).fill_(0xFF)
         if fused == 2 and self.packed == 2:
             raise RuntimeError("dense_packed 2 (tile images) has no cluster split-K form: build the rank with packed=0 for fused=2")

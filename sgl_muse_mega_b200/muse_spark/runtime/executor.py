@@ -146,7 +146,7 @@ class Verify:
                          block_verify=bool(getattr(shim.server_spec(), "speculative_use_block_verification", True)))  # fmt: skip
         self.stack = S.Stack(self.case, self.rank, self.device, self.lib, self.module, arena=self.arena, greedy=False,
                              keep_plain_experts=False, frame=frame, pools=pools, wait_budget=WAIT_BUDGET,
-                             shared_status=True, identity_slots=False, **extra)  # fmt: skip
+                             shared_status=True, identity_slots=False, packets=True, **extra)  # fmt: skip
         if cfg.tp > 1:
             self.peers = S.connect_world(self.stack, self.group)
         else:

@@ -12,7 +12,7 @@ from sgl_muse_mega_b200.muse_spark.b200 import synthetic
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
-OUTS = ("x_attn", "branch", "stream_mid", "h3", "logits", "ids", "w", "xq", "x_sf", "y", "stream_out", "h3_next", "qkv_next")
+OUTS = ("x_attn", "branch", "stream_mid", "h3", "ids", "w", "xq", "x_sf", "y", "stream_out", "h3_next", "qkv_next")
 
 
 def stream() -> int:
