@@ -920,7 +920,7 @@ def run_timeline(args) -> None:
         lr.pool_ag.copy_(torch.randn(lr.pool_ag.shape, generator=g, device=device))
         lr.unpool_ag.copy_(torch.randn(lr.unpool_ag.shape, generator=g, device=device))
         lr.zb.view(torch.bfloat16).copy_(torch.randn(lr.zb.numel() // 2, generator=g, device=device))
-        lr.bind(None, fused=0)
+        lr.bind(None, fused=0, packets=args.exchange != "flags")
         case.ranks = []
         ring.append(lr)
     stream = torch.cuda.Stream(device)

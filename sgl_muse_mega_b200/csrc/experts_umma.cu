@@ -156,7 +156,14 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
     // One round trip for the route tables every unit looks up. g2's predecessor is g1: the tables were written two or more
     // kernels back, so g2 copies them and starts streaming its first weights under g1's tail; the roles that touch what g1
     // wrote wait below.
-    if (!G2) griddep_wait();
+    if (!G2) {
+        griddep_wait_only();
+        if (a.sig.target != nullptr && blockIdx.x == 0) {  // g2 will not wait for this grid's end: leave it the epoch to wait for
+            if (tid == 0) xchg_announce(a.sig);
+            __syncthreads();
+        }
+        griddep_launch();
+    }
     for (int i = tid; i < (int)(sizeof(RouteTables) / 4); i += 256) ((int*)rt)[i] = ((const int*)a.rt)[i];
     __syncthreads();
     const int NB = a.NB, KCH = a.K / 256;
@@ -242,7 +249,10 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
         // ---- stager: the B operand of unit j into buffer j & 1, two units ahead of the MMAs ----
         const int ts = tid - 64;  // 0..63
         if (G2) {
-            griddep_wait();
+            // a.wait.packets: the h planes' counter word counts this rank's own g1 too, so it alone orders the stager
+            // behind g1's stores (its loads of the planes go through L2): no wait for g1's grid to end
+            if (a.wait.packets) griddep_launch();
+            else griddep_wait();
             xchg_wait_role(a.wait, ts, 64, 3);  // without an h-row kernel in front: every rank's column band of the h planes
         }
         int j = 0;
@@ -285,8 +295,8 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
                 if (idx < wtotal) {
                     const int tk = idx / wq, c = idx - tk * wq;
                     const int sl = rt->slot[s0 + tk];
-                    wv[k] = *(const uint4*)(a.bsf + (size_t)(G2 ? sl : sl / a.topk) * (a.K / 16) + c * 16);
-                    if (view) xv[k] = *(const uint4*)(a.bex + (size_t)sl * (a.K / 16) + c * 16);
+                    wv[k] = __ldcg((const uint4*)(a.bsf + (size_t)(G2 ? sl : sl / a.topk) * (a.K / 16) + c * 16));
+                    if (view) xv[k] = __ldcg((const uint4*)(a.bex + (size_t)sl * (a.K / 16) + c * 16));
                 }
             }
             if (j == 0) mbar_arrive(rows_first);  // the first unit's loads are issued: the weight stream may start (g1)
@@ -301,7 +311,7 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
 #pragma unroll
                     for (int r = 0; r < kMaxKChunks / 4; ++r) {
                         const int i = qd * 16 + r * 64;
-                        v4[r] = i < gb ? *(const uint4*)(ex + i) : make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
+                        v4[r] = i < gb ? __ldcg((const uint4*)(ex + i)) : make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
                     }
 #pragma unroll
                     for (int r = 0; r < kMaxKChunks / 4; ++r) {
@@ -362,7 +372,10 @@ __global__ void __launch_bounds__(256, 1) experts_umma_kernel(const UmmaArgs a) 
         }
     } else {
         // ---- scale words -> tensor memory, epilogue out ----
-        if (G2) griddep_wait();
+        if (G2) {  // nothing here reads what g1 wrote (the stager hands the rows over through shared memory)
+            if (a.wait.packets) griddep_launch();
+            else griddep_wait();
+        }
         const int q = warp - 4, te = tid - 128;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
 

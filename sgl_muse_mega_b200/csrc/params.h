@@ -26,6 +26,7 @@ constexpr int kHeadDim = 64;
 constexpr int kXchgPoints = 8;   // words [0, 8) of the flag block: exchange counters (written by peers)
 constexpr int kXchgEpoch = 8;    // words [8, 16): this rank's epoch per exchange (local)
 constexpr int kXchgDone = 16;    // words [16, 24): CTA arrival counters of the producers (local)
+constexpr int kXchgTarget = 24;  // words [24, 32): the epoch a producer launch of this rank is about to complete (local)
 constexpr int kXchgWords = 32;
 // The fused kernels (fused.cuh) feed and consume an exchange inside one kernel, one arrival per finished tile: they count in
 // words of their own, so that both protocols can serve launches on one flag block.
@@ -38,6 +39,7 @@ struct XchgSignal {
     int remote;                 // some receiver is another rank (system-scope ordering needed)
     unsigned* done;
     unsigned* epoch;
+    unsigned* target;           // xchg_announce: where the producer leaves epoch + 1 for a consumer that does not wait for its end
 };
 struct XchgWait {
     const unsigned* flag;       // this rank's word of the exchange; null: off
@@ -46,10 +48,11 @@ struct XchgWait {
     long long budget;           // polls before giving up
     int* status;
     int stage;                  // recorded with a wait that ran out
-    // packet mode (pkt_take below): the exchanged bf16 rows carry their own validity and there is no counter word
+    // packet mode (pkt_take_n below): the exchanged bf16 rows carry their own validity and there is no counter word
     int packets;                // 1: on (flag is null then)
     unsigned present;           // bit j: source j of the exchange is bound and writes its part (a part of an absent source is 0)
     int band;                   // columns per source where the sources write column bands of one row (0: whole rows)
+    const unsigned* target;     // the epoch to wait for, left by this rank's producer launch (xchg_announce); null: the epoch word
 };
 
 // Every thread of every CTA calls this after the kernel's last store to a peer.
@@ -77,6 +80,16 @@ __device__ __forceinline__ void xchg_signal(const XchgSignal& x) {
             }
         }
     }
+}
+
+// A consumer kernel that does not wait for its own rank's producer grid to end cannot read the epoch word (the producer's
+// last CTA advances it at some point while the consumer already runs). The producer's first CTA therefore leaves the epoch
+// its launch will complete in the target word, after its own programmatic-launch wait (every earlier signal is in by
+// then) and before it lets the dependent launch: thread 0 of CTA 0 calls this, the CTA synchronises, then triggers.
+__device__ __forceinline__ void xchg_announce(const XchgSignal& x) {
+    if (x.target == nullptr) return;
+    *(volatile unsigned*)x.target = *(volatile unsigned*)x.epoch + 1;
+    __threadfence();
 }
 
 // Every thread of every CTA calls this after griddep_wait() and before the first read of exchanged data.
@@ -133,7 +146,7 @@ __device__ __forceinline__ void xchg_wait(const XchgWait& w) { xchg_wait_epoch(w
 __device__ __forceinline__ void xchg_wait_role(const XchgWait& w, int tid, int n, int bar) {
     if (w.flag == nullptr) return;
     if (tid == 0) {
-        const unsigned want = xchg_epoch(w) * w.contributors;
+        const unsigned want = (w.target != nullptr ? *(volatile const unsigned*)w.target : xchg_epoch(w)) * w.contributors;
         long long polls = 0;
         for (;;) {
             unsigned seen;
@@ -174,32 +187,48 @@ __device__ __forceinline__ uint4 pkt_peek(const void* p) {
     asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
-// `polls` counts over all the packets a thread takes in one launch (one budget a thread).
-__device__ __forceinline__ uint4 pkt_take(const void* p, const XchgWait& w, long long& polls) {
-    uint4 v = pkt_peek(p);
-    while (!pkt_ok(v)) {
-        if ((polls & 255) == 255 && w.status != nullptr && *(volatile int*)w.status != 0) break;  // a failure already on record
-        if (++polls > w.budget) {
-            if (w.status != nullptr && atomicCAS(w.status, 0, 1) == 0) {
-                w.status[1] = w.stage;
-                w.status[2] = (int)blockIdx.x;
-                w.status[3] = (int)threadIdx.x;
-                w.status[4] = -1;
-            }
-            break;
+// One more poll of a thread: false when it has to give up (its budget ran out: recorded once per launch; or a failure is
+// already on record, so that a launch gives up once and not once per wait).
+__device__ __forceinline__ bool pkt_again(const XchgWait& w, long long& polls) {
+    if ((polls & 255) == 255 && w.status != nullptr && *(volatile int*)w.status != 0) return false;
+    if (++polls > w.budget) {
+        if (w.status != nullptr && atomicCAS(w.status, 0, 1) == 0) {
+            w.status[1] = w.stage;
+            w.status[2] = (int)blockIdx.x;
+            w.status[3] = (int)threadIdx.x;
+            w.status[4] = -1;
         }
-        __nanosleep(32);
-        v = pkt_peek(p);
+        return false;
     }
-    *(uint4*)const_cast<void*>(p) = make_uint4(kPktMark, kPktMark, kPktMark, kPktMark);
-    return v;
+    __nanosleep(32);
+    return true;
 }
-// the packet at column c of a row whose sources write bands of w.band columns (or whole rows): taken if its source is
-// present, zeros otherwise
-__device__ __forceinline__ uint4 pkt_take_col(const void* p, int c, const XchgWait& w, long long& polls) {
-    const int src = w.band > 0 ? c / w.band : 0;
-    if (w.band > 0 && !((w.present >> src) & 1u)) return make_uint4(0, 0, 0, 0);
-    return pkt_take(p, w, polls);
+// The thread's n <= N packets at addr(0) .. addr(n - 1), those whose bit in `need` is set (the others read as zeros): all
+// loads of a round are issued together (one memory round trip a round, not one a packet), the round repeats until every
+// packet is whole; then the marks go back.
+template <int N, class Addr>
+__device__ __forceinline__ void pkt_take_n(uint4 (&v)[N], int n, unsigned need, Addr addr, const XchgWait& w) {
+    long long polls = 0;
+    for (;;) {
+        bool ok = true;
+#pragma unroll
+        for (int j = 0; j < N; ++j)
+            if (j < n && ((need >> j) & 1u)) {
+                v[j] = pkt_peek(addr(j));
+                ok = ok && pkt_ok(v[j]);
+            }
+        if (ok || !pkt_again(w, polls)) break;
+    }
+#pragma unroll
+    for (int j = 0; j < N; ++j)
+        if (j < n) {
+            if ((need >> j) & 1u) *(uint4*)addr(j) = make_uint4(kPktMark, kPktMark, kPktMark, kPktMark);
+            else v[j] = make_uint4(0, 0, 0, 0);
+        }
+}
+// whether the source that writes column c of a row is present (bands of w.band columns a source; 0: whole rows, always)
+__device__ __forceinline__ bool pkt_col_present(const XchgWait& w, int c) {
+    return w.band <= 0 || ((w.present >> (c / w.band)) & 1u);
 }
 
 // Route tables in the private scratch, written by the routing kernel each launch.

@@ -29,7 +29,8 @@ static __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 // mode 0 (post-attention): branch = bf16(sum over ranks of the bf16 partials, rank order, f32); v = branch
 // mode 1 (cross-layer):    v = gathered unpooler row x post_w
 // stream' = fma(alpha, stream, scaled), normed = bf16((stream' rstd) pre_w)       (muse_spark.py:335-357)
-// One CTA per row, H / 8 threads, 8 consecutive columns per thread.
+// One CTA per row, H / 8 threads, 8 consecutive columns per thread. (Tried: a row on a cluster of eight CTAs, totals met
+// through distributed shared memory. No gain: the kernel is bound by the arrival of its rows, not by one SM's throughput.)
 __global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
     __shared__ float red[33];
     const int row = blockIdx.x, c0 = threadIdx.x * 8;
@@ -42,7 +43,7 @@ __global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
     uint4 post_raw = make_uint4(0, 0, 0, 0);
     if (a.mode != 0) post_raw = *(const uint4*)(a.post_w + c0);
     RT(a.mode != 0, 0)
-    // packet mode: the rows that arrive are their own dependency (pkt_take), everything else this kernel reads was complete
+    // packet mode: the rows that arrive are their own dependency (pkt_take_n), everything else this kernel reads was complete
     // before the producer of those rows passed its own wait, so the kernel does not wait for the producer's grid to end
     if (!a.wait.packets) griddep_wait();
     griddep_launch();
@@ -50,16 +51,10 @@ __global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
     const float4 s0 = *(const float4*)(a.stream_in + off), s1 = *(const float4*)(a.stream_in + off + 4);
     xchg_wait(a.wait);  // the all-reduce partials (mode 0) or the unpooler gather (mode 1) of every contributing rank
     float v[8];
-    long long polls = 0;
     if (a.mode == 0) {
         uint4 part[kMaxRanks];
         if (a.wait.packets) {  // every present rank's partial as it arrives; an absent rank's is 0
-#pragma unroll
-            for (int r = 0; r < kMaxRanks; ++r)
-                if (r < a.ranks) {
-                    part[r] = make_uint4(0, 0, 0, 0);
-                    if ((a.wait.present >> r) & 1u) part[r] = pkt_take(a.src + ((size_t)r * a.M + row) * a.H + c0, a.wait, polls);
-                }
+            pkt_take_n(part, a.ranks, a.wait.present, [&](int r) { return (void*)(a.src + ((size_t)r * a.M + row) * a.H + c0); }, a.wait);
         } else {
 #pragma unroll
             for (int r = 0; r < kMaxRanks; ++r)
@@ -79,7 +74,10 @@ __global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
         unpack8(b, v);
     } else {
         float w[8];
-        unpack8(a.wait.packets ? pkt_take_col(a.src + off, c0, a.wait, polls) : *(const uint4*)(a.src + off), v);
+        uint4 got[1];
+        if (a.wait.packets) pkt_take_n(got, 1, pkt_col_present(a.wait, c0) ? 1u : 0u, [&](int) { return (void*)(a.src + off); }, a.wait);
+        else got[0] = *(const uint4*)(a.src + off);
+        unpack8(got[0], v);
         unpack8(post_raw, w);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] *= w[i];
@@ -264,10 +262,11 @@ static __device__ void nq_row(const NqArgs& a, int row, float* red) {
     const bool own = tid < groups;
     if (own) {
         float g[16];
-        if (a.wait.packets) {
-            long long polls = 0;
-            unpack8(pkt_take_col(x + tid * 16, tid * 16, a.wait, polls), *(float(*)[8])g);
-            unpack8(pkt_take_col(x + tid * 16 + 8, tid * 16 + 8, a.wait, polls), *(float(*)[8])(g + 8));
+        if (a.wait.packets) {  // both packets of the group lie in one source's band (bands are multiples of 16 columns)
+            uint4 got[2];
+            pkt_take_n(got, 2, pkt_col_present(a.wait, tid * 16) ? 3u : 0u, [&](int j) { return (void*)(x + tid * 16 + 8 * j); }, a.wait);
+            unpack8(got[0], *(float(*)[8])g);
+            unpack8(got[1], *(float(*)[8])(g + 8));
         } else {
             unpack8(*(const uint4*)(x + tid * 16), *(float(*)[8])g);
             unpack8(*(const uint4*)(x + tid * 16 + 8), *(float(*)[8])(g + 8));
@@ -366,24 +365,13 @@ __global__ void __launch_bounds__(512) route_nq_kernel(const RouteNqArgs a) {
                 s_sel[e] = a.topk.score[(size_t)row * E + e];
             } else {
                 float lg;
-                if (a.nq.wait.packets) {  // an f32 of all ones marks a logit that has not arrived (pkt_take's rule, 4 bytes)
+                if (a.nq.wait.packets) {  // an f32 of all ones marks a logit that has not arrived (pkt_take_n's rule, 4 bytes)
                     unsigned* p = (unsigned*)(a.topk.logits + (size_t)row * E + e);
                     long long polls = 0;
                     unsigned v;
                     for (;;) {
                         asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-                        if (v != kPktMark) break;
-                        if ((polls & 255) == 255 && a.nq.wait.status != nullptr && *(volatile int*)a.nq.wait.status != 0) break;
-                        if (++polls > a.nq.wait.budget) {
-                            if (a.nq.wait.status != nullptr && atomicCAS(a.nq.wait.status, 0, 1) == 0) {
-                                a.nq.wait.status[1] = a.nq.wait.stage;
-                                a.nq.wait.status[2] = (int)blockIdx.x;
-                                a.nq.wait.status[3] = tid;
-                                a.nq.wait.status[4] = -2;
-                            }
-                            break;
-                        }
-                        __nanosleep(32);
+                        if (v != kPktMark || !pkt_again(a.nq.wait, polls)) break;
                     }
                     *p = kPktMark;
                     lg = __uint_as_float(v);
@@ -449,8 +437,10 @@ __global__ void __launch_bounds__(512) combine_kernel(const CombineArgs a) {
     const int nw = blockDim.x >> 5;
     const uint4 gp_raw = *(const uint4*)(a.gamma_p1 + c0);  // a weight: in flight while the predecessor still runs
     RT(4, 0)
-    if (!a.wait.packets) griddep_wait();
-    griddep_launch();
+    // (packet mode: unlike the norms and the routing rows this kernel keeps its wait for g2's grid. Measured without it: its
+    // CTAs sit on the first SMs g2 frees and poll through g2's last 10 us, and the slowest row then ends 12.6 us after g2
+    // instead of 8.8; the rows of its own rank are all there when the wait returns, a peer's are polled for.)
+    griddep_wait();
     RT(4, 1)
     xchg_wait(a.wait);  // every rank's column band of the expert outputs
     if (row >= a.b_live) {
@@ -464,10 +454,8 @@ __global__ void __launch_bounds__(512) combine_kernel(const CombineArgs a) {
         const int kk = min(kMaxTopk, a.k - j0);
         uint4 raw[kMaxTopk];
         if (a.wait.packets) {
-            long long polls = 0;
-#pragma unroll
-            for (int j = 0; j < kMaxTopk; ++j)
-                if (j < kk) raw[j] = pkt_take_col(a.zb + ((size_t)row * a.k + j0 + j) * a.P + c0, c0, a.wait, polls);
+            pkt_take_n(raw, kk, pkt_col_present(a.wait, c0) ? 0xFFu : 0u,
+                       [&](int j) { return (void*)(a.zb + ((size_t)row * a.k + j0 + j) * a.P + c0); }, a.wait);
         } else {
 #pragma unroll
             for (int j = 0; j < kMaxTopk; ++j)

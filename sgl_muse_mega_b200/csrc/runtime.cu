@@ -317,7 +317,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
     unsigned* const flags = (unsigned*)b->flags;
     const long long budget = b->wait_budget > 0 ? b->wait_budget : kDefaultWaitBudget;
     auto flag_of = [&](int r) -> unsigned* { return (unsigned*)(r == s.rank ? b->flags : b->flags_peer[r]); };
-    // packet mode: the bf16 exchanges carry their own validity (params.h pkt_take); the h planes keep their counter word
+    // packet mode: the bf16 exchanges carry their own validity (params.h pkt_take_n); the h planes keep their counter word
     const bool packets = b->packets != 0;
     MK_REQUIRE(!packets || b->fused != 1, "packets is not available with the fused form (fused = 1)");
     auto in_band = [&](int point) { return packets && (point == XP_AR || point == XP_POOL || point == XP_ZB || point == XP_UNPOOL); };
@@ -548,7 +548,12 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
             // g2 forms the h-row view in its own stager (row exponents, moved scale bytes, row scales): no h-row kernel
             u.bsf = g2 ? (const unsigned char*)b->z_sf : (const unsigned char*)b->sf;
             u.bex = g2 ? (const signed char*)b->z_ex : nullptr;
-            if (g2) u.wait = L->hrow_wait;
+            if (g2) {
+                u.wait = L->hrow_wait;
+                // packet mode: g2 orders itself behind g1 by the h planes' counter word alone (g1 announces the epoch)
+                u.wait.packets = packets && u.wait.flag != nullptr;
+                if (u.wait.packets) u.wait.target = flags + kXchgTarget + XP_Z;
+            }
             u.x_scale = (const float*)b->x_scale;
             u.g1_alphas = (const float*)b->g1_alphas;
             u.g1_scale_c = (const float*)b->g1_scale_c;
@@ -563,6 +568,7 @@ int mk_layer_bind(MkModule* module, const MkLayerShape* shape, const MkLayerBind
             u.n_peer = ex.n_peer;
             u.status = L->status;
             u.sig = g2 ? ex.sig_g2 : ex.sig_g1;
+            if (!g2 && packets && u.sig.n > 0) u.sig.target = flags + kXchgTarget + XP_Z;
         }
         if (ep_world > 1) {
             // whole experts per rank, one process per GPU: the h planes stay local, the zb rows of this rank's (row, slot)
