@@ -123,7 +123,7 @@ __device__ __forceinline__ void xchg_wait_epoch(const XchgWait& w, unsigned epoc
                 }
                 break;
             }
-            __nanosleep(64);
+            if (polls > 4096) __nanosleep(64);
         }
 #ifdef XCHG_TRACE
         // trace builds: nanoseconds CTA 0 spent in this wait and the number of waits, per recorded stage (words 256.. of
@@ -162,7 +162,7 @@ __device__ __forceinline__ void xchg_wait_role(const XchgWait& w, int tid, int n
                 }
                 break;
             }
-            __nanosleep(64);
+            if (polls > 4096) __nanosleep(64);
         }
     }
     asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(n) : "memory");
@@ -200,8 +200,7 @@ __device__ __forceinline__ bool pkt_again(const XchgWait& w, long long& polls) {
         }
         return false;
     }
-    __nanosleep(32);
-    return true;
+    return true;  // no sleep between rounds: a 32 ns sleep cost 1.3 us at the post norm, where the last rows decide
 }
 // The thread's n <= N packets at addr(0) .. addr(n - 1), those whose bit in `need` is set (the others read as zeros): all
 // loads of a round are issued together (one memory round trip a round, not one a packet), the round repeats until every
