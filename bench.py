@@ -62,6 +62,9 @@ def parse():
                          "the accept length stays forced)")
     ap.add_argument("--top-k", type=int, default=1 << 30)
     ap.add_argument("--top-p", type=float, default=1.0)
+    ap.add_argument("--tp", type=int, default=8, choices=(4, 8),
+                    help="tensor-parallel width of the model whose slice each GPU holds (8: the reference's two-node world; "
+                         "4 with --gpus 4: the whole model as the single-node TP4 world, configs[3] / [4] only)")
     ap.add_argument("--exchange", default="auto", choices=("auto", "packets", "flags"),
                     help="how a layer's bf16 rows reach their consumers, between GPUs and inside one: rows that carry their own "
                          "validity (packets: the default, except with --form 4), or counter words in the flag block between "
@@ -369,7 +372,7 @@ def decode_leg(args, cfg, lib, module, device, rank: int, world: int, stream) ->
         draft_us = max_over_ranks(e0.elapsed_time(e1) / reps * 1e3)
         dbytes = draft_bytes(it.draft.cfg, cfg.tp, rows)
         draft = {"us_per_step": draft_us, "kernels": it.draft.kernels(), "bytes": dbytes,
-                 "roofline_frac": dbytes / (draft_us * 1e-6) / 1e9 / peaks()[0], "config": "DFlash2 public config, TP8 slice"}
+                 "roofline_frac": dbytes / (draft_us * 1e-6) / 1e9 / peaks()[0], "config": f"DFlash2 public config, TP{cfg.tp} slice"}
     # ---- end to end: ids from pinned host memory, step words back ----
     def e2e_step():
         with torch.cuda.stream(stream):
@@ -531,7 +534,8 @@ def decode_line(args, cfg, dec: dict, world: int, clocks) -> dict:
     peak, peak_kind = peaks()
     n_layers = dec["layers"]
     gen = 256 if args.config == 3 else 64
-    what = (f"configs[{args.config}]: full-shape 62-layer model + DFlash2 draft, TP8 slice per GPU on {world} B200(s), "
+    what = (f"configs[{args.config}]: full-shape 62-layer model + DFlash2 draft, TP{cfg.tp} slice per GPU on {world} B200(s)"
+            f"{' (the whole world)' if world == cfg.tp else ''}, "
             f"{args.ctx}-token context (KV filled directly: no prefill path here), {gen} generated tokens, block 16, "
             f"forced accept {args.accept} (commit {args.accept + 1} a step)")
     if args.tree:
@@ -585,6 +589,9 @@ def run_ours(args) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     cfg = Config()
+    if args.tp != cfg.tp:
+        assert args.config in (3, 4), "--tp 4 serves the decode legs (--config 3 / 4)"
+        cfg = cfg.with_tp(args.tp)
     lib = host.library()
     module = lib.load()
     synthetic.set_device(device)
