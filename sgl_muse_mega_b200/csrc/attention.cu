@@ -54,14 +54,32 @@ __global__ void __launch_bounds__(256, 2) attn_split_kernel(const AttnArgs a) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, kvhead = blockIdx.y;
     RT(5, 0)
-    griddep_wait();
-    RT(5, 1)
+    // Everything up to the wait reads what earlier steps (or kernels two or more back) left: the window's length and page
+    // table, and the context's K / V rows. The first key block's context rows are requested here, under the predecessor's
+    // tail; only the window's own rows (appended by the predecessor) and the queries wait.
     const int kv_len = *a.kv_len;
     const int n_ctx = kv_len - a.M;
     const AttnSpan span = attn_span(a, kv_len);
     if (split >= span.eff) return;  // more splits than key blocks: the merge reads the first `eff` partials only
     const int lo = span.lo, nblk = span.nblk;
     const int b0 = (int)((long long)split * nblk / span.eff), b1 = (int)((long long)(split + 1) * nblk / span.eff);
+    // part 0: the whole block; 1: its context keys (p < n_ctx); 2: the rest (window keys, zero fill past kv_len)
+    auto load_block = [&](int b, int st, int part) {
+        const int p0 = lo + b * kKeyBlock;
+        for (int i = tid; i < kKeyBlock * 8; i += blockDim.x) {
+            const int key = i >> 3, c = i & 7, p = p0 + key;
+            if ((part == 1 && p >= n_ctx) || (part == 2 && p < n_ctx)) continue;
+            const bool ok = p < kv_len;
+            const long long off = ok ? a.page_table[p] + (long long)kvhead * 128 + c * 16 : 0;
+            const int d = key * 128 + ((c ^ (key & 7)) << 4);
+            cp_async16(&Ks[st][d], a.k_cache + off, ok);
+            cp_async16(&Vs[st][d], a.v_cache + off, ok);
+        }
+        cp_async_commit();
+    };
+    if (b0 < b1) load_block(b0, 0, 1);
+    griddep_wait();
+    RT(5, 1)
 
     // Q fragments of this warp's 16 rows (rows >= R are zero)
     const int r0 = warp * 16 + g, r1 = r0 + 8;
@@ -85,29 +103,16 @@ __global__ void __launch_bounds__(256, 2) attn_split_kernel(const AttnArgs a) {
     const int posq0 = n_ctx + (a.tree != nullptr ? a.tree[16 + tq0] : r0 / a.G), posq1 = n_ctx + (a.tree != nullptr ? a.tree[16 + tq1] : r1 / a.G);
     const unsigned tmask0 = a.tree != nullptr ? (unsigned)a.tree[32 + tq0] : 0u, tmask1 = a.tree != nullptr ? (unsigned)a.tree[32 + tq1] : 0u;
 
-    auto load_block = [&](int b, int st) {
-        const int p0 = lo + b * kKeyBlock;
-        for (int i = tid; i < kKeyBlock * 8; i += blockDim.x) {
-            const int key = i >> 3, c = i & 7, p = p0 + key;
-            const bool ok = p < kv_len;
-            const long long off = ok ? a.page_table[p] + (long long)kvhead * 128 + c * 16 : 0;
-            const int d = key * 128 + ((c ^ (key & 7)) << 4);
-            cp_async16(&Ks[st][d], a.k_cache + off, ok);
-            cp_async16(&Vs[st][d], a.v_cache + off, ok);
-        }
-        cp_async_commit();
-    };
-
     float o[8][4];
 #pragma unroll
     for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
     float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;
 
-    if (b0 < b1) load_block(b0, 0);
+    if (b0 < b1) load_block(b0, 0, 2);
     for (int b = b0; b < b1; ++b) {
         const int st = (b - b0) & 1;
         if (b + 1 < b1) {
-            load_block(b + 1, st ^ 1);
+            load_block(b + 1, st ^ 1, 0);
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
