@@ -78,6 +78,13 @@ __global__ void __launch_bounds__(kDThreads, 1) dense_umma_kernel(const __grid_c
         uint32_t it = 0;
         dense_stage_x<kRing>(a, c, pl, it, tid - 64);
     } else {
+        if (a.finish == 2 && tid - 128 < 33) {
+            // the qkv head's rotation rows and pool slots (feeds of the step, written kernels ago): into L1 / L2 now, not at
+            // the first tile's finish
+            const char* p = tid - 128 < 32 ? (a.epi.cos_sin ? (const char*)a.epi.cos_sin + (tid - 128) * 128 : nullptr)
+                                           : (const char*)a.epi.cache_loc;
+            if (p != nullptr && (tid - 128 == 32 || (tid - 128) * 32 < a.g[0].M * 64)) asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
+        }
         griddep_wait();
         int i = 0;
         dense_epilogue<kRing>(a, c, pl, i, warp - 4, tid - 128, lane, none);

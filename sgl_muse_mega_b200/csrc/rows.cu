@@ -452,6 +452,9 @@ __global__ void __launch_bounds__(512) combine_kernel(const CombineArgs a) {
     const int row = blockIdx.x, tid = threadIdx.x, c0 = tid * 8, warp = tid >> 5, lane = tid & 31;
     const int nw = blockDim.x >> 5;
     const uint4 gp_raw = *(const uint4*)(a.gamma_p1 + c0);  // a weight: in flight while the predecessor still runs
+    // the row's routing weights were written before g1 ran: requested here too (a pad row has none)
+    float w_pre = 0.f;
+    if (tid < kMaxTopk && tid < a.k && row < a.b_live) w_pre = a.w[(size_t)row * a.k + tid];
     RT(4, 0)
     // (packet mode, as the norms: no wait for g2's grid. With polls that slept 32 ns between rounds this lost 3.8 us: the
     // CTAs take the first SMs g2 frees and poll through g2's last 10 us, and a sleeping poll noticed the last rows late.)
@@ -496,7 +499,8 @@ __global__ void __launch_bounds__(512) combine_kernel(const CombineArgs a) {
         if (tid < kMaxTopk && tid < kk) {
             float s = 0.f;
             for (int w = 0; w < nw; ++w) s += red[tid][w];
-            sc[tid] = a.w[(size_t)row * a.k + j0 + tid] * (1.0f / sqrtf(s / (float)a.P + 1e-8f));
+            const float wj = j0 == 0 ? w_pre : a.w[(size_t)row * a.k + j0 + tid];
+            sc[tid] = wj * (1.0f / sqrtf(s / (float)a.P + 1e-8f));
         }
         __syncthreads();
 #pragma unroll
