@@ -224,13 +224,16 @@ __global__ void __launch_bounds__(256, 2) attn_split_kernel(const AttnArgs a) {
 __global__ void __launch_bounds__(256) attn_combine_kernel(const AttnArgs a) {
     __shared__ float s_o[2][4][64];
     RT(6, 0)
-    griddep_wait();
-    griddep_launch();
-    RT(6, 1)
     const int pc = threadIdx.x >> 7, wq = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31;
     const int w = blockIdx.x * 2 + pc;
     const bool valid = w < a.M * a.qh;
     const int tok = valid ? w / a.qh : 0, head = valid ? w % a.qh : 0;
+    // the gate values sit in the qkv row the split kernel already waited for: requested before this kernel's own wait
+    const bf16* og = a.qkv + (size_t)tok * a.qkv_row + (a.qh + 2 * a.kvh) * kHeadDim + head * kHeadDim + 2 * lane;
+    const __nv_bfloat162 og2 = *(const __nv_bfloat162*)og;
+    griddep_wait();
+    griddep_launch();
+    RT(6, 1)
     const int kvhead = head / a.G, r = tok * a.G + head % a.G;
     const float* base = a.ws + ((size_t)kvhead * a.splits * a.R + r) * 66;
     const size_t stride = (size_t)a.R * 66;
@@ -293,8 +296,7 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const AttnArgs a) {
     const float x0 = o0 * inv, x1 = o1 * inv;
     const float ms = warp_sum(x0 * x0 + x1 * x1) * (1.0f / 64.0f);
     const float rstd = 1.0f / sqrtf(ms + 1e-5f);
-    const bf16* og = a.qkv + (size_t)tok * a.qkv_row + (a.qh + 2 * a.kvh) * kHeadDim + head * kHeadDim + 2 * lane;
-    const float g0 = __bfloat162float(og[0]), g1 = __bfloat162float(og[1]);
+    const float g0 = __low2float(og2), g1 = __high2float(og2);
     const float s0 = 1.0f / (1.0f + expf(-g0)), s1 = 1.0f / (1.0f + expf(-g1));
     __nv_bfloat162 out = __floats2bfloat162_rn(x0 * rstd * s0, x1 * rstd * s1);
     *(__nv_bfloat162*)(a.x_attn + (size_t)tok * a.qh * kHeadDim + head * kHeadDim + 2 * lane) = out;
