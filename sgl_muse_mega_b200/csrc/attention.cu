@@ -137,20 +137,34 @@ __global__ void __launch_bounds__(256, 2) attn_split_kernel(const AttnArgs a) {
         // masks, running max
         const int pbase = lo + b * kKeyBlock;
         float mx0 = -1e30f, mx1 = -1e30f;
-        bool vis[8][4];
+        // a block of context keys that every row of the window sees whole (all of a global layer's but the last, all of a
+        // sliding window's but the first and the last) needs no per-element masks
+        const bool whole = pbase + kKeyBlock <= n_ctx && (a.window <= 0 || pbase + a.window >= n_ctx + a.M - 1);
+        unsigned vis = 0xFFFFFFFFu;  // bit 4 j + c
+        if (whole) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < 8; ++j) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int p = pbase + 8 * j + 2 * t + (c & 1);
-                const int pq = (c & 2) ? posq1 : posq0;
-                const bool own = a.tree == nullptr ? p <= pq : (p < n_ctx || ((((c & 2) ? tmask1 : tmask0) >> (p - n_ctx)) & 1u));
-                const bool v = own && p < kv_len && (a.window <= 0 || p + a.window >= pq);
-                vis[j][c] = v;
-                s[j][c] *= kScaleLog2e;
-                if (v) {
-                    if (c & 2) mx1 = fmaxf(mx1, s[j][c]);
-                    else mx0 = fmaxf(mx0, s[j][c]);
+                for (int c = 0; c < 4; ++c) s[j][c] *= kScaleLog2e;
+                mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+                mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+            }
+        } else {
+            vis = 0u;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int p = pbase + 8 * j + 2 * t + (c & 1);
+                    const int pq = (c & 2) ? posq1 : posq0;
+                    const bool own = a.tree == nullptr ? p <= pq : (p < n_ctx || ((((c & 2) ? tmask1 : tmask0) >> (p - n_ctx)) & 1u));
+                    const bool v = own && p < kv_len && (a.window <= 0 || p + a.window >= pq);
+                    vis |= (v ? 1u : 0u) << (4 * j + c);
+                    s[j][c] *= kScaleLog2e;
+                    if (v) {
+                        if (c & 2) mx1 = fmaxf(mx1, s[j][c]);
+                        else mx0 = fmaxf(mx0, s[j][c]);
+                    }
                 }
             }
         }
@@ -174,10 +188,10 @@ __global__ void __launch_bounds__(256, 2) attn_split_kernel(const AttnArgs a) {
         uint32_t pa[4][4];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const float p0 = vis[j][0] ? exp2f(s[j][0] - m0) : 0.f;
-            const float p1 = vis[j][1] ? exp2f(s[j][1] - m0) : 0.f;
-            const float p2 = vis[j][2] ? exp2f(s[j][2] - m1) : 0.f;
-            const float p3 = vis[j][3] ? exp2f(s[j][3] - m1) : 0.f;
+            const float p0 = (vis >> (4 * j)) & 1u ? exp2f(s[j][0] - m0) : 0.f;
+            const float p1 = (vis >> (4 * j + 1)) & 1u ? exp2f(s[j][1] - m0) : 0.f;
+            const float p2 = (vis >> (4 * j + 2)) & 1u ? exp2f(s[j][2] - m1) : 0.f;
+            const float p3 = (vis >> (4 * j + 3)) & 1u ? exp2f(s[j][3] - m1) : 0.f;
             l0 += p0 + p1;
             l1 += p2 + p3;
             pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
