@@ -96,7 +96,8 @@ struct MkLaunch {
     mk::DraftOp* dops;
     int n_dops;
 };
-// exchange points (word index in a rank's flag block) and the default poll budget of a wait (~64 ns a poll: about 0.3 s)
+// exchange points (word index in a rank's flag block) and the default poll budget of a wait (a poll is one round trip to
+// the L2, 0.5 - 1 us: seconds)
 enum XchgPoint { XP_AR = 0, XP_POOL, XP_Z, XP_ZB, XP_UNPOOL, XP_LOGITS };
 static const long long kDefaultWaitBudget = 1ll << 22;
 enum OpKind { OP_FEEDS = 1, OP_ENTRY, OP_GEMM_BF16, OP_SOFTCAP, OP_ACCEPT };

@@ -34,7 +34,7 @@ from ..config import Config
 from . import shim
 from .shim import LogitsProcessorOutput
 
-# polls an exchange wait spends before it gives up (~64 ns each): a quarter of a second
+# polls an exchange wait spends before it gives up (a poll is one round trip to the L2, 0.5 - 1 us: seconds)
 WAIT_BUDGET = 1 << 22
 STATUS_NAMES = {1: "an exchange wait ran out (a peer never signalled)", 2: "a grid barrier ran out",
                 3: "a bulk copy or tensor-core barrier never completed", 4: "an out-of-range position or slot was clamped",

@@ -22,7 +22,7 @@ from .config import Config
 INDEX = "model.safetensors.index.json"  # the checkpoint index the expert reader walks (reference runtime/build.py)
 DRAFT_FILE = "model.safetensors"  # the DFlash2 draft's single weight file (reference sm103/dflash/weights.py)
 # The longest a step can take when a peer never signals, seconds: an exchange wait gives up after the bind's poll budget
-# (runtime.executor.WAIT_BUDGET polls of ~64 ns: a quarter of a second) and records a status instead of trapping; once
+# (runtime.executor.WAIT_BUDGET polls of one L2 round trip each: seconds) and records a status instead of trapping; once
 # a launch's status block holds a failure, its later waits give up after 1024 polls, and the executor raises on the status
 # at the next step. SGLang's watchdog only has to exceed the first wait plus a step.
 LONGEST_WAIT_S = 1.0
