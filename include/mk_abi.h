@@ -56,6 +56,15 @@ typedef struct MkLaunchInfo {
 } MkLaunchInfo;
 int mk_launch_info(const MkLaunch* launch, MkLaunchInfo* out);
 
+// Stands where abi.h:53 mk_launch_params stands (the reference's launch is one kernel whose parameter block that call
+// copies out; here a launch is a list of kernels with one argument record each). Renders, for a layer launch, what the bind
+// wired between those kernels as text, one `name key=value ...` line per producer and consumer of an exchange point:
+//   post_norm wait=packets present=0x3 band=0 contributors=0     (wait: off | counter | packets)
+//   o_proj signal=0 remote=0 target=0                            (signal: receivers' flag words; 0 = none)
+// Works on pack-only records (bound without a module), for tests that check a bind on the CPU. Returns the text's length
+// (without the terminator), -1 when `cap_bytes` is too small or the launch is not a layer launch.
+int mk_launch_params(const MkLaunch* launch, char* text, uint64_t cap_bytes);
+
 // No counterpart in the reference (its waits trap, K/README.md:111-121). Copies the launch's device status block to the
 // host (synchronises the stream first). code 0 = clean; otherwise the wait that gave up.
 typedef struct MkLaunchStatus {

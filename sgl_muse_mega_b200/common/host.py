@@ -78,7 +78,7 @@ SYMM_HANDLE_BYTES = 64  # MK_SYMM_HANDLE_BYTES
 
 EXPORTS = (
     "mk_last_error", "mk_module_load", "mk_module_free", "mk_launch", "mk_launch_step", "mk_launch_free",
-    "mk_launch_info", "mk_launch_status", "mk_layer_constants", "mk_layer_bind", "mk_qkv_constants", "mk_qkv_bind",
+    "mk_launch_info", "mk_launch_params", "mk_launch_status", "mk_layer_constants", "mk_layer_bind", "mk_qkv_constants", "mk_qkv_bind",
     "mk_qkv_launch_static", "mk_feeds_bind", "mk_entry_bind", "mk_lm_head_bind", "mk_softcap_bind", "mk_accept_bind",
     "mk_symm_alloc", "mk_symm_open", "mk_symm_close", "mk_symm_free", "mk_dflash_constants", "mk_dflash_entry_bind",
     "mk_dflash_layer_bind", "mk_dflash_draft_head_bind", "mk_dflash_kv_sync_bind", "mk_dflash_tree_bind",
@@ -104,6 +104,7 @@ class Library:
         d.mk_launch_free.argtypes = [vp]
         d.mk_launch_free.restype = None
         d.mk_launch_info.argtypes = [vp, P(STRUCTS["MkLaunchInfo"])]
+        d.mk_launch_params.argtypes = [vp, ctypes.c_char_p, ctypes.c_uint64]
         d.mk_launch_status.argtypes = [vp, ctypes.c_uint64, P(STRUCTS["MkLaunchStatus"])]
         d.mk_layer_constants.argtypes = [P(STRUCTS["MkLayerShape"]), P(STRUCTS["MkLayerConstants"])]
         d.mk_layer_bind.argtypes = [vp, P(STRUCTS["MkLayerShape"]), P(STRUCTS["MkLayerBind"]), P(vp)]
@@ -225,6 +226,20 @@ class Launch:
         i = STRUCTS["MkLaunchInfo"]()
         self.lib.check(self.lib.dll.mk_launch_info(self.handle, ctypes.byref(i)), "mk_launch_info")
         return i
+
+    def params(self) -> dict:
+        """What a layer bind wired between its kernels (``mk_launch_params``): {"post_norm.wait": {"wait": "packets",
+        "present": 3, ...}, "o_proj.signal": {"signal": 0, ...}, ...}; works on pack-only records."""
+        buf = ctypes.create_string_buffer(4096)
+        n = self.lib.dll.mk_launch_params(self.handle, buf, len(buf))
+        self.lib.check(0 if n >= 0 else -1, "mk_launch_params")
+        out = {}
+        for line in buf.value.decode().splitlines():
+            name, *pairs = line.split()
+            fields = dict(p.split("=", 1) for p in pairs)
+            kind = "wait" if "wait" in fields else "signal" if "signal" in fields else "stages"
+            out[name if kind == "stages" else f"{name}.{kind}"] = {k: (v if k == "wait" else int(v, 0)) for k, v in fields.items()}
+        return out
 
     def status(self, stream: int) -> ctypes.Structure:
         s = STRUCTS["MkLaunchStatus"]()

@@ -988,6 +988,46 @@ void mk_launch_free(MkLaunch* launch) {
     delete launch;
 }
 
+int mk_launch_params(const MkLaunch* launch, char* text, uint64_t cap_bytes) {
+    MK_REQUIRE(launch != nullptr && text != nullptr, "launch or text is NULL");
+    const MkLaunch* L = launch;
+    MK_REQUIRE(L->n_dops == 0 && L->n_ops == 0, "not a layer launch");
+    size_t n = 0;
+    bool full = false;
+    auto put = [&](const char* fmt, ...) {
+        if (full) return;
+        va_list ap;
+        va_start(ap, fmt);
+        const int k = vsnprintf(text + n, cap_bytes - n, fmt, ap);
+        va_end(ap);
+        if (k < 0 || (size_t)k >= cap_bytes - n) full = true;
+        else n += (size_t)k;
+    };
+    auto wait = [&](const char* name, const XchgWait& w) {
+        put("%s wait=%s present=0x%x band=%d contributors=%u target=%d\n", name,
+            w.packets && w.flag == nullptr ? "packets" : w.flag != nullptr ? "counter" : "off", w.present, w.band, w.contributors,
+            w.target != nullptr ? 1 : 0);
+    };
+    auto sig = [&](const char* name, const XchgSignal& x) {
+        put("%s signal=%d remote=%d target=%d\n", name, x.n, x.remote, x.target != nullptr ? 1 : 0);
+    };
+    unsigned on = 0;
+    for (int i = 0; i < ST_COUNT; ++i) on |= (L->stage_on[i] ? 1u : 0u) << i;
+    put("stages on=0x%x fused=%d segments=%d\n", on, L->use_fused ? 1 : 0, L->use_segments ? 1 : 0);
+    sig("o_proj", L->seg_gemms ? L->sg_oproj.sig : L->oproj.sig);
+    wait("post_norm", L->post_norm.wait);
+    sig("pooler", L->seg_gemms ? L->sg_pool.sig : L->pooler.sig);
+    wait("nq", L->nq.wait);
+    sig("g1", L->use_umma ? L->umma_g1.sig : L->ex.sig_g1);
+    wait("g2", L->use_umma ? L->umma_g2.wait : L->hrow_wait);
+    sig("g2", L->use_umma ? L->umma_g2.sig : L->ex.sig_g2);
+    wait("combine", L->combine.wait);
+    sig("unpooler", L->seg_gemms ? L->sg_unpool.sig : L->unpool.sig);
+    wait("cross_norm", L->cross_norm.wait);
+    MK_REQUIRE(!full, "text of %llu bytes is too small", (unsigned long long)cap_bytes);
+    return (int)n;
+}
+
 int mk_launch_info(const MkLaunch* launch, MkLaunchInfo* out) {
     MK_REQUIRE(launch != nullptr && out != nullptr, "launch or out is NULL");
     const MkLaunch* L = launch;

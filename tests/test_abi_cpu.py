@@ -169,6 +169,47 @@ def test_packet_mode_binds_and_marks_the_exchange_rows(lib):
     assert ep.bind(ep_peers=[NS(zb=0x7F0000001000, flags=0), None], ep_rank=1, packets=True).info().kernels == 12
 
 
+def test_launch_params_show_the_exchange_wiring(lib):
+    """``mk_launch_params`` on pack-only records: a lone rank's binds, a two-rank world with counter words and with
+    packets, and ranks 0 / 1 of an eight-rank world alone (a slice: absent sources read as zero, present ones are polled)."""
+    from types import SimpleNamespace as NS
+
+    cfg, kw = CASES["small_fp4_swa_tp2"]
+    case = synthetic.layer_case(cfg, **kw)
+    a, b = (L.LayerRank(lib, None, case, r, torch.device("cpu")) for r in range(2))
+    p = a.bind([a, b]).params()
+    assert p["stages"]["fused"] == 0
+    # counter words: every producer signals both ranks, every consumer counts two contributors
+    for name in ("o_proj", "pooler", "g1", "g2", "unpooler"):
+        assert p[f"{name}.signal"]["signal"] == 2 and p[f"{name}.signal"]["remote"] == 1, name
+    for name in ("post_norm", "nq", "g2", "combine", "cross_norm"):
+        assert p[f"{name}.wait"]["wait"] == "counter" and p[f"{name}.wait"]["contributors"] == 2, name
+    # packets: the four bf16 exchanges neither signal nor count; the h planes keep their counter word, g1 announces its epoch
+    p = a.bind([a, b], packets=True).params()
+    for name in ("o_proj", "pooler", "g2", "unpooler"):
+        assert p[f"{name}.signal"]["signal"] == 0, name
+    assert p["g1.signal"] == {"signal": 2, "remote": 1, "target": 1}
+    assert p["g2.wait"]["wait"] == "counter" and p["g2.wait"]["target"] == 1
+    P, H = cfg.moe_hidden, cfg.hidden
+    assert p["post_norm.wait"] == {"wait": "packets", "present": 3, "band": 0, "contributors": 0, "target": 0}
+    assert p["nq.wait"]["present"] == 3 and p["nq.wait"]["band"] == P // 2
+    assert p["combine.wait"]["present"] == 3 and p["combine.wait"]["band"] == P // 2
+    assert p["cross_norm.wait"]["present"] == 3 and p["cross_norm.wait"]["band"] == H // 2
+    # a lone rank with packets: the rows are handed over inside the rank
+    p = a.bind(packets=True).params()
+    assert p["post_norm.wait"]["wait"] == "packets" and p["post_norm.wait"]["present"] == 1 and p["o_proj.signal"]["signal"] == 0
+    # ranks 0 and 1 of an eight-rank world (node groups of four): the absent ranks' parts are not polled
+    cfg8, kw8 = CASES["small_fp4_swa_tp8"]
+    case8 = synthetic.layer_case(cfg8, **kw8)
+    r0, r1 = (L.LayerRank(lib, None, case8, r, torch.device("cpu")) for r in range(2))
+    p = r1.bind([r0, r1] + [None] * 6, packets=True).params()
+    assert p["post_norm.wait"]["present"] == 0b11 and p["combine.wait"]["present"] == 0b11
+    assert p["combine.wait"]["band"] == cfg8.moe_hidden // 8
+    assert p["nq.wait"]["present"] == 0b11 and p["nq.wait"]["band"] == cfg8.moe_hidden // 4  # the node group's bands
+    assert p["cross_norm.wait"]["band"] == cfg8.hidden // 4
+    assert p["g1.signal"]["signal"] == 2  # the h planes go to the present ranks
+
+
 def test_module_load_needs_builtin_image(lib):
     out = ctypes.c_void_p()
     assert lib.dll.mk_module_load(b"xx", 2, None, ctypes.byref(out)) == -1
