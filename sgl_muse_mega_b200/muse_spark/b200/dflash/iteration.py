@@ -91,7 +91,14 @@ class Iteration:
         self.draft.launch_all(s, pdl, sample)
         if self.tree_walk is not None:
             self.tree_walk.launch(s, pdl)
-        self.stack.launch_all(s, pdl, tail=None if sample is None else ("sample" if sample else "greedy"))
+        if sample is None:
+            # the iteration ends with an accept: the stack's own tail when that is one, else the accept bound beside it
+            # (a serving stack's own tail is the soft cap of the plain verify step)
+            own = self.stack.tail is self.stack.tails.get("greedy") or self.stack.tail is self.stack.tails.get("sample")
+            tail = None if own else ("greedy" if "greedy" in self.stack.tails else "sample")
+        else:
+            tail = "sample" if sample else "greedy"
+        self.stack.launch_all(s, pdl, tail=tail)
         if self.tree_compact is not None:
             self.tree_compact.launch(s, pdl)
 

@@ -15,6 +15,7 @@ asks SGLang's ``runtime_context`` only when they are absent.
 from __future__ import annotations
 
 import json
+import os
 import time
 from pathlib import Path
 from typing import Callable, Optional
@@ -176,6 +177,15 @@ def model_case(model, cfg: Config, rank: int, device, rows: int, experts: Callab
     )  # fmt: skip
 
 
+# opt-in, as the reference's runtime/build.py:94-100: the fused DFlash2 iteration verifies a token tree of the draft's 15
+# likeliest continuations instead of its chain (a 16-row block; greedy requests only: sampled ones run SGLang's step)
+TREE_ENV = "SGLANG_MUSE_MEGA_TREE"
+
+
+def tree_enabled() -> bool:
+    return os.environ.get(TREE_ENV, "0") == "1"
+
+
 def build(model, hf_config, ctx, *, parallel=None, experts: Optional[Callable[[int], dict]] = None, model_path=None,
           cfg: Optional[Config] = None) -> Verify:  # fmt: skip
     """The verify step of a DFlash2 block (``ctx.tokens_per_request`` rows) on this rank: the library loaded (built
@@ -203,9 +213,12 @@ def build(model, hf_config, ctx, *, parallel=None, experts: Optional[Callable[[i
     layout = S.exchange_layout(cfg, block)
     arena = symm.Arena(lib, layout, device) if world > 1 else symm.LocalArena(layout, device)
     case = model_case(model, cfg, rank, device, block, experts)
-    summary = f"TP{cfg.tp}, block {block}, sm_100a library {lib.path.name}; built in {time.perf_counter() - t0:.1f} s"
+    tree = tree_enabled() and block == 16
+    summary = (f"TP{cfg.tp}, block {block}{', token tree' if tree else ''}, sm_100a library {lib.path.name}; "
+               f"built in {time.perf_counter() - t0:.1f} s")  # fmt: skip
     global TARGET
-    TARGET = Verify(cfg, block, case, lib, module, arena, model, rank, device, getattr(parallel, "device_group", None), summary)
+    TARGET = Verify(cfg, block, case, lib, module, arena, model, rank, device, getattr(parallel, "device_group", None), summary,
+                    tree=tree)  # fmt: skip
     try:
         model.built_megakernel = TARGET  # where the hooks of an SGLang without the binding module look it up
     except AttributeError:

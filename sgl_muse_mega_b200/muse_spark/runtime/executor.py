@@ -79,7 +79,8 @@ class Verify:
         self.cfg, self.block, self.case, self.lib, self.module, self.arena = cfg, block, case, lib, module, arena
         self.model, self.rank, self.device, self.group = model, rank, device, group
         self.widths, self._summary = (block,), summary
-        self.tree = tree  # the fused iteration verifies a token tree (not built here: always False)
+        self.tree = tree  # the fused iteration verifies a token tree (runtime.build.tree_enabled)
+        self._chain_table: Optional[torch.Tensor] = None
         self.stack: Optional[S.Stack] = None
         self.peers = None
         self.kv_pool = None
@@ -144,6 +145,8 @@ class Verify:
             extra = dict(accept_too=True, sample_too=True, sampling=torch.zeros(4, dtype=torch.int64),
                          accept_override=None if table is None else table.to(self.device), ring=4096,
                          block_verify=bool(getattr(shim.server_spec(), "speculative_use_block_verification", True)))  # fmt: skip
+            if self.tree:  # the tree's accept is the greedy one: no sampled accept beside it (sampled steps run SGLang's)
+                extra = dict(accept_too=True, tree=True, accept_override=extra["accept_override"], ring=4096)
         self.stack = S.Stack(self.case, self.rank, self.device, self.lib, self.module, arena=self.arena, greedy=False,
                              keep_plain_experts=False, frame=frame, pools=pools, wait_budget=WAIT_BUDGET,
                              shared_status=True, identity_slots=False, packets=True, **extra)  # fmt: skip
@@ -213,6 +216,15 @@ class Verify:
         torch.index_select(pool.full_to_swa_index_mapping, 0, f["out_cache_loc"], out=f["swa_out_cache_loc"])
         f["seq_lens"].copy_(forward_batch.seq_lens[:1], non_blocking=True)
         f["req_pool_indices"].copy_(forward_batch.req_pool_indices[:1], non_blocking=True)
+        if st.tree_table is not None:
+            # a stack bound for the token tree reads its rows' places and masks from the tree's table: SGLang's own verify
+            # step sends a chain, whose table is parent r - 1, depth r, every earlier row an ancestor
+            if self._chain_table is None:
+                r = torch.arange(16, dtype=torch.int32)
+                t = torch.zeros(96, dtype=torch.int32)
+                t[0:16], t[16:32], t[32:48] = r - 1, r, (2 << r) - 1
+                self._chain_table = t.to(self.device)
+            st.tree_table.copy_(self._chain_table, non_blocking=True)
         s = torch.cuda.current_stream(self.device).cuda_stream
         st.launch_all(s, pdl=True, feeds=True)
         if self.capture:

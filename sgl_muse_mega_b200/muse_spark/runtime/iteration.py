@@ -119,7 +119,7 @@ def plain_sampling(batch) -> bool:
 
 class Fused:
     """One process's fused iteration of the target's block size: the greedy graph, the sampled graph (not with a simulated
-    accept length) and the flush graph, each captured twice (the outputs alternate between two sets so that a step's
+    accept length, nor with the token tree, whose accept is the greedy one) and the flush graph, each captured twice (the outputs alternate between two sets so that a step's
     results stay intact while the overlap scheduler launches the next step)."""
 
     def __init__(self, target: Verify, draft_model, draft_kv_pool):
@@ -179,7 +179,8 @@ class Fused:
         self.parity = 0
         self.rid = None
         self.pending = False  # the run's last commit is not in SGLang's draft pool yet
-        logger.info("fused DFlash2 iteration: block %d, %d launches in one graph%s%s", b, self.it.kernels + 2,
+        logger.info("fused DFlash2 iteration: block %d, %d launches in one graph%s%s%s", b, self.it.kernels + 2,
+                    " (token tree)" if st.tree_table is not None else "",
                     " (and a sampled graph)" if self.sample else "",
                     f"; simulated accept length {sim_len:g} ({sim_method}, {sim_tokens} tokens; sampled steps run SGLang's)"
                     if sim_len > 0 else "")  # fmt: skip

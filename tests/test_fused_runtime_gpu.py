@@ -38,10 +38,10 @@ SLOTS_FULL, SLOTS_SWA, WIDTH = 1024, 768, 256
 BONUS = 77
 
 
-def plain_run(case, w0, draft_ctx, sampling=None):
+def plain_run(case, w0, draft_ctx, sampling=None, **stack_kw):
     """STEPS iterations of a plain stack on identity slots from the request's state: per step (tokens, commit, bonus, P)
     and the draft's rings at the end."""
-    st = S.Stack(case, 0, DEV, sampling=sampling)
+    st = S.Stack(case, 0, DEV, sampling=sampling, **stack_kw)
     st.bind()
     it = Iteration(st, DCFG, w0, capture=list(DCFG.capture), pool_rows=256, rope_rows=WIDTH + 2 * ROWS)
     for l, (k, v) in enumerate(draft_ctx):
@@ -242,4 +242,57 @@ def test_simulated_acceptance_forces_the_commit_lengths(monkeypatch):
     sampled = decode_batch([FakeRequest("req-t", temperature=0.7, top_k=40)], shim.DraftInput(bonus_tokens=bonus),
                            seq_lens=torch.tensor([seq], device=DEV), req_pool_indices=torch.tensor([1], device=DEV))  # fmt: skip
     assert fused(sampled, needs_logits=True, on_publish=None) is None
+    shim.install()
+
+
+def test_token_tree_iteration_on_scattered_slots(monkeypatch):
+    """``SGLANG_MUSE_MEGA_TREE=1``: the fused iteration verifies a token tree. With a simulated acceptance (here: the forced
+    leaf rows) the accepted paths move K / V and captured rows; tokens, commits, bonus tokens and lengths of every step, and
+    the target's K / V rows in the framework's scattered slots, equal a plain tree iteration's on identity slots. A sampled
+    request is not the tree's (SGLang's step serves it), and the plain verify step on the tree-bound stack sees a chain."""
+    monkeypatch.setenv(B.TREE_ENV, "1")
+    monkeypatch.setenv("SGLANG_SIMULATE_ACC_LEN", "6")
+    monkeypatch.setenv("SGLANG_SIMULATE_ACC_METHOD", "match-expected")
+    gen = torch.Generator().manual_seed(23)
+    case = synthetic.stack_case(CFG, n_layers=4, rows=ROWS, ctx=CTX, seed=9)
+    dw, dt = dsyn.draft_weights(DCFG, 4), dsyn.target_shared(DCFG, 4)
+    w0, _ = shard(DCFG, dw, dt, 0, 1)
+    serving = Serving(case, gen)
+    verify = built(case, dw)
+    assert verify.tree and "token tree" in verify.summary()
+    table = IT.simulated_accepts(ROWS)
+    assert table is not None
+    ref_st, ref_it, ref_steps = plain_run(case, w0, serving.draft_ctx, tree=True, accept_override=table.to(DEV))
+    assert ref_it.tree_walk is not None and len({c for _, c, _, _ in ref_steps}) > 1  # commits of several lengths
+    verify.prepare(serving.view)
+    st = verify.stack
+    assert st.tree_table is not None and st.accept is not None and st.accept_sampled is None
+    fused = verify.dflash_iteration(block_size=ROWS, draft_model=serving.draft_model, draft_kv_pool=serving.draft_pool)
+    assert not fused.sample and set(fused.graphs) == {"greedy"} and fused.it.tree_walk is not None
+    published = []
+    end = drive(fused, serving, 1, "t", FakeRequest("req-t"), ref_steps, published)
+    kvh = CFG.kv_heads_rank
+    slots = serving.slots[1]
+    for j, lc in enumerate(case.layers):
+        where = slots[CTX:end] if lc.global_attn else serving.full_to_swa[slots[CTX:end]]
+        got = serving.pool.get_key_buffer(j).view(-1, kvh * 64)[where.to(DEV)]
+        assert torch.equal(got, ref_st.pools[j][0][CTX:end]), j
+    sampled = FakeRequest("req-u", temperature=0.8, top_k=50, top_p=0.9, seed=1)
+    batch = decode_batch([sampled], shim.DraftInput(bonus_tokens=torch.tensor([BONUS], device=DEV)),
+                         seq_lens=torch.tensor([CTX], device=DEV), req_pool_indices=torch.tensor([2], device=DEV))  # fmt: skip
+    assert fused.mode(batch, needs_logits=True) is None
+    # SGLang's own verify step on the tree-bound stack: a chain window gives what a chain-bound stack gives
+    ids = torch.randint(0, CFG.vocab, (ROWS,), generator=gen).to(DEV)
+    fb = shim.ForwardBatch(shim.ForwardMode("target_verify"), 1, torch.tensor([CTX], device=DEV), torch.tensor([1], device=DEV),
+                           serving.slots[1][CTX : CTX + ROWS].to(DEV))  # fmt: skip
+    step = verify.plan(ids, fb, view=serving.view)
+    out = verify.forward(step, None, ids, torch.arange(CTX, CTX + ROWS, device=DEV), fb)
+    torch.cuda.synchronize()
+    assert verify.stack.statuses() == []
+    chain = S.Stack(case, 0, DEV, greedy=False)
+    chain.bind()
+    chain.tokens.copy_(ids)
+    chain.launch_all(torch.cuda.current_stream().cuda_stream, pdl=False, feeds=True)
+    torch.cuda.synchronize()
+    assert torch.equal(out.next_token_logits, chain.logits_out)
     shim.install()

@@ -298,6 +298,23 @@ def test_fused_mode_takes_only_the_steps_its_graphs_serve():
     assert f.mode(decode_batch([sampled], spec), needs_logits=True) is None
 
 
+def test_token_tree_is_opt_in_by_environment(monkeypatch):
+    """``SGLANG_MUSE_MEGA_TREE=1`` (the reference's switch, runtime/build.py:94-100) turns the fused iteration's window into
+    a token tree; a tree-bound stack gives SGLang's own verify step (a chain) the chain's table."""
+    from sgl_muse_mega_b200.muse_spark.runtime import build as B
+
+    monkeypatch.delenv(B.TREE_ENV, raising=False)
+    assert not B.tree_enabled()
+    monkeypatch.setenv(B.TREE_ENV, "0")
+    assert not B.tree_enabled()
+    monkeypatch.setenv(B.TREE_ENV, "1")
+    assert B.tree_enabled()
+    # the chain as a tree table: parent r - 1, depth r, ancestors = every earlier row (what Verify.forward writes)
+    r = torch.arange(16, dtype=torch.int32)
+    mask = ((2 << r) - 1).tolist()
+    assert mask[0] == 1 and mask[15] == 0xFFFF and all(m == (1 << (i + 1)) - 1 for i, m in enumerate(mask))
+
+
 def test_request_seed_is_the_same_on_every_rank():
     from fake_sglang import FakeRequest
     from sgl_muse_mega_b200.muse_spark.runtime import iteration as IT
