@@ -69,19 +69,6 @@ __global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[i] += f[i];
             }
-#ifdef ROWS_TRACE
-        {  // probe: the latest arrival over the CTA's threads (kid 5 slot 0) and the column it belonged to (slot 1)
-            unsigned long long t_;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));
-            unsigned long long key_ = ((t_ & ((1ull << 40) - 1)) << 14) | (unsigned long long)(c0 >> 3);  // time (low 40 bits), then the thread
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const unsigned long long other_ = __shfl_xor_sync(0xffffffffu, key_, o);
-                key_ = other_ > key_ ? other_ : key_;
-            }
-            if ((threadIdx.x & 31) == 0) atomicMax(&g_rows_trace[5][blockIdx.x][0], key_);
-        }
-#endif
         const uint4 b = pack8(v);
         *(uint4*)(a.branch + off) = b;
         unpack8(b, v);
@@ -103,9 +90,7 @@ __global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
-    if (a.mode == 0) { RT(6, 0) }
     const float post_rstd = inv_sqrt(block_sum(ss, red) / (float)a.H + 1e-8f);
-    if (a.mode == 0) { RT(6, 1) }
     float ns[8];
     ss = 0.f;
 #pragma unroll
@@ -115,7 +100,6 @@ __global__ void __launch_bounds__(1024) resid_norm_kernel(const NormArgs a) {
         ss += ns[i] * ns[i];
     }
     const float pre_rstd = inv_sqrt(block_sum(ss, red) / (float)a.H + 1e-5f);
-    if (a.mode == 0) { RT(6, 2) }
     *(float4*)(a.stream_out + off) = make_float4(ns[0], ns[1], ns[2], ns[3]);
     *(float4*)(a.stream_out + off + 4) = make_float4(ns[4], ns[5], ns[6], ns[7]);
     float h[8];
